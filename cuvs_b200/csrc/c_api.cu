@@ -1,0 +1,563 @@
+// C interface: the entry points declared in include/cuvs_core_c_api.h and include/cuvs_ivf_pq.h.
+//
+// Mirrors c/src/core/c_api.cpp and c/src/neighbors/ivf_pq.cpp of the reference: every entry point
+// runs inside translate_exceptions (c/src/core/exceptions.hpp:17-33), tensors are validated the
+// way from_dlpack does (c/src/core/detail/interop.hpp:75-139) and dispatched on their dtype.
+#include "../../include/cuvs_ivf_pq.h"
+
+#include "ivf_pq.hpp"
+
+#include <cstring>
+#include <exception>
+#include <string>
+
+namespace ivf_pq = cuvs::neighbors::ivf_pq;
+using cuvs_b200::fail;
+using index_t = ivf_pq::index<int64_t>;
+
+namespace {
+
+thread_local std::string g_last_error;
+thread_local bool g_has_error = false;
+
+template <typename Fn>
+cuvsError_t translate_exceptions(Fn&& fn)
+{
+  try {
+    fn();
+    cuvsSetLastErrorText(nullptr);
+    return CUVS_SUCCESS;
+  } catch (const std::exception& e) {
+    cuvsSetLastErrorText(e.what());
+  } catch (...) {
+    cuvsSetLastErrorText("unknown exception");
+  }
+  return CUVS_ERROR;
+}
+
+bool is_device_compatible(const DLTensor& t)
+{
+  return t.device.device_type == kDLCUDA || t.device.device_type == kDLCUDAHost ||
+         t.device.device_type == kDLCUDAManaged;
+}
+bool is_host_compatible(const DLTensor& t)
+{
+  return t.device.device_type == kDLCPU || t.device.device_type == kDLCUDAHost ||
+         t.device.device_type == kDLCUDAManaged;
+}
+bool is_c_contiguous(const DLTensor& t)
+{
+  if (!t.strides) { return true; }
+  int64_t expected = 1;
+  for (int64_t i = t.ndim - 1; i >= 0; --i) {
+    if (t.strides[i] != expected) { return false; }
+    expected *= t.shape[i];
+  }
+  return true;
+}
+
+// from_dlpack for a row-major tensor of known dtype / rank; returns the data pointer.
+void* checked_data(DLManagedTensor* mt, uint8_t code, uint8_t bits, int ndim, bool device,
+                   const char* name)
+{
+  CUVS_EXPECTS(mt != nullptr, "%s: null tensor", name);
+  const DLTensor& t = mt->dl_tensor;
+  CUVS_EXPECTS(is_c_contiguous(t), "Expected a row-major matrix");
+  CUVS_EXPECTS(code == t.dtype.code, "code mismatch between return mdspan (%i) and DLTensor (%i)",
+               int(code), int(t.dtype.code));
+  CUVS_EXPECTS(bits == t.dtype.bits, "bits mismatch between return mdspan (%i) and DLTensor (%i)",
+               int(bits), int(t.dtype.bits));
+  CUVS_EXPECTS(t.dtype.lanes == 1, "More than 1 DLTensor lanes not supported");
+  if (device) {
+    CUVS_EXPECTS(is_device_compatible(t), "device_type mismatch between return mdspan and DLTensor");
+  } else {
+    CUVS_EXPECTS(is_host_compatible(t), "device_type mismatch between return mdspan and DLTensor");
+  }
+  CUVS_EXPECTS(t.ndim == ndim, "ndim mismatch between return mdspan and DLTensor");
+  return static_cast<char*>(t.data) + t.byte_offset;
+}
+
+ivf_pq::elem_t elem_of_dtype(const DLDataType& d, const char* what)
+{
+  if (d.code == kDLFloat && d.bits == 32) { return ivf_pq::elem_t::f32; }
+  if (d.code == kDLFloat && d.bits == 16) { return ivf_pq::elem_t::f16; }
+  if (d.code == kDLInt && d.bits == 8) { return ivf_pq::elem_t::i8; }
+  if (d.code == kDLUInt && d.bits == 8) { return ivf_pq::elem_t::u8; }
+  fail("Unsupported %s DLtensor dtype: %d and bits: %d", what, int(d.code), int(d.bits));
+}
+
+index_t* index_of(cuvsIvfPqIndex_t index)
+{
+  CUVS_EXPECTS(index != nullptr && index->addr != 0, "the index handle holds no index");
+  return reinterpret_cast<index_t*>(index->addr);
+}
+cuvs_b200::resources* res_of(cuvsResources_t res)
+{
+  CUVS_EXPECTS(res != 0, "null resources handle");
+  return reinterpret_cast<cuvs_b200::resources*>(res);
+}
+
+void tensor_deleter(DLManagedTensor* self)
+{
+  delete[] self->dl_tensor.shape;
+  delete[] self->dl_tensor.strides;
+  self->dl_tensor.shape   = nullptr;
+  self->dl_tensor.strides = nullptr;
+}
+
+// to_dlpack for a non-owning device view (c/src/core/detail/interop.hpp:143-174)
+void make_view(DLManagedTensor* out, void* data, DLDataType dtype, std::initializer_list<int64_t> shape,
+               std::initializer_list<int64_t> strides = {})
+{
+  CUVS_EXPECTS(out != nullptr, "null output tensor");
+  int device = 0;
+  cudaGetDevice(&device);
+  DLTensor& t   = out->dl_tensor;
+  t.data        = data;
+  t.device      = DLDevice{kDLCUDA, device};
+  t.ndim        = int32_t(shape.size());
+  t.dtype       = dtype;
+  t.shape       = new int64_t[shape.size()];
+  std::copy(shape.begin(), shape.end(), t.shape);
+  t.strides = nullptr;
+  if (strides.size()) {
+    t.strides = new int64_t[strides.size()];
+    std::copy(strides.begin(), strides.end(), t.strides);
+  }
+  t.byte_offset    = 0;
+  out->manager_ctx = nullptr;
+  out->deleter     = tensor_deleter;
+}
+
+ivf_pq::index_params convert(const cuvsIvfPqIndexParams& p)
+{
+  ivf_pq::index_params o;
+  o.metric                         = ivf_pq::DistanceType(int(p.metric));
+  o.metric_arg                     = p.metric_arg;
+  o.add_data_on_build              = p.add_data_on_build;
+  o.n_lists                        = p.n_lists;
+  o.kmeans_n_iters                 = p.kmeans_n_iters;
+  o.kmeans_trainset_fraction       = p.kmeans_trainset_fraction;
+  o.pq_bits                        = p.pq_bits;
+  o.pq_dim                         = p.pq_dim;
+  o.codebook_kind                  = ivf_pq::codebook_gen(int(p.codebook_kind));
+  o.force_random_rotation          = p.force_random_rotation;
+  o.conservative_memory_allocation = p.conservative_memory_allocation;
+  o.max_train_points_per_pq_code   = p.max_train_points_per_pq_code;
+  o.codes_layout                   = ivf_pq::list_layout(int(p.codes_layout));
+  return o;
+}
+
+}  // namespace
+
+// ------------------------------------------------------------------------------------------------
+// core
+// ------------------------------------------------------------------------------------------------
+extern "C" const char* cuvsGetLastErrorText(void) { return g_has_error ? g_last_error.c_str() : nullptr; }
+
+extern "C" void cuvsSetLastErrorText(const char* error)
+{
+  if (error) {
+    g_last_error = error;
+    g_has_error  = true;
+  } else {
+    g_last_error.clear();
+    g_has_error = false;
+  }
+}
+
+extern "C" cuvsError_t cuvsResourcesCreate(cuvsResources_t* res)
+{
+  return translate_exceptions([=] {
+    CUVS_EXPECTS(res != nullptr, "null output pointer");
+    *res = reinterpret_cast<cuvsResources_t>(new cuvs_b200::resources());
+  });
+}
+extern "C" cuvsError_t cuvsResourcesDestroy(cuvsResources_t res)
+{
+  return translate_exceptions([=] { delete reinterpret_cast<cuvs_b200::resources*>(res); });
+}
+extern "C" cuvsError_t cuvsStreamSet(cuvsResources_t res, cudaStream_t stream)
+{
+  return translate_exceptions([=] { res_of(res)->stream = stream; });
+}
+extern "C" cuvsError_t cuvsStreamGet(cuvsResources_t res, cudaStream_t* stream)
+{
+  return translate_exceptions([=] { *stream = res_of(res)->stream; });
+}
+extern "C" cuvsError_t cuvsStreamSync(cuvsResources_t res)
+{
+  return translate_exceptions([=] { res_of(res)->sync(); });
+}
+extern "C" cuvsError_t cuvsDeviceIdGet(cuvsResources_t res, int* device_id)
+{
+  return translate_exceptions([=] { *device_id = res_of(res)->device; });
+}
+extern "C" cuvsError_t cuvsResourcesSetWorkspacePool(cuvsResources_t res, size_t initial_size_bytes)
+{
+  return translate_exceptions([=] { res_of(res)->ws.reserve(initial_size_bytes); });
+}
+extern "C" cuvsError_t cuvsRMMAlloc(cuvsResources_t res, void** ptr, size_t bytes)
+{
+  return translate_exceptions([=] {
+    res_of(res);
+    CUDA_TRY(cudaMalloc(ptr, bytes));
+  });
+}
+extern "C" cuvsError_t cuvsRMMFree(cuvsResources_t res, void* ptr, size_t)
+{
+  return translate_exceptions([=] {
+    res_of(res);
+    CUDA_TRY(cudaFree(ptr));
+  });
+}
+extern "C" cuvsError_t cuvsVersionGet(uint16_t* major, uint16_t* minor, uint16_t* patch)
+{
+  return translate_exceptions([=] {
+    *major = 26;  // the interface version mirrored (reference VERSION 26.10.00)
+    *minor = 10;
+    *patch = 0;
+  });
+}
+
+// ------------------------------------------------------------------------------------------------
+// params
+// ------------------------------------------------------------------------------------------------
+extern "C" cuvsError_t cuvsIvfPqIndexParamsCreate(cuvsIvfPqIndexParams_t* params)
+{
+  return translate_exceptions([=] {
+    auto* p                           = new cuvsIvfPqIndexParams{};
+    p->metric                         = L2Expanded;
+    p->metric_arg                     = 2.0f;
+    p->add_data_on_build              = true;
+    p->n_lists                        = 1024;
+    p->kmeans_n_iters                 = 20;
+    p->kmeans_trainset_fraction       = 0.5;
+    p->pq_bits                        = 8;
+    p->pq_dim                         = 0;
+    p->codebook_kind                  = CUVS_IVF_PQ_CODEBOOK_GEN_PER_SUBSPACE;
+    p->force_random_rotation          = false;
+    p->conservative_memory_allocation = false;
+    p->max_train_points_per_pq_code   = 256;
+    p->codes_layout                   = CUVS_IVF_PQ_LIST_LAYOUT_INTERLEAVED;
+    *params                           = p;
+  });
+}
+extern "C" cuvsError_t cuvsIvfPqIndexParamsDestroy(cuvsIvfPqIndexParams_t params)
+{
+  return translate_exceptions([=] { delete params; });
+}
+extern "C" cuvsError_t cuvsIvfPqSearchParamsCreate(cuvsIvfPqSearchParams_t* params)
+{
+  return translate_exceptions([=] {
+    auto* p                     = new cuvsIvfPqSearchParams{};
+    p->n_probes                 = 20;
+    p->lut_dtype                = CUDA_R_32F;
+    p->internal_distance_dtype  = CUDA_R_32F;
+    p->coarse_search_dtype      = CUDA_R_32F;
+    p->max_internal_batch_size  = 4096;
+    p->preferred_shmem_carveout = 1.0;
+    *params                     = p;
+  });
+}
+extern "C" cuvsError_t cuvsIvfPqSearchParamsDestroy(cuvsIvfPqSearchParams_t params)
+{
+  return translate_exceptions([=] { delete params; });
+}
+
+// ------------------------------------------------------------------------------------------------
+// index handle + getters
+// ------------------------------------------------------------------------------------------------
+extern "C" cuvsError_t cuvsIvfPqIndexCreate(cuvsIvfPqIndex_t* index)
+{
+  return translate_exceptions([=] { *index = new cuvsIvfPqIndex{}; });
+}
+extern "C" cuvsError_t cuvsIvfPqIndexDestroy(cuvsIvfPqIndex_t index)
+{
+  return translate_exceptions([=] {
+    if (index) {
+      delete reinterpret_cast<index_t*>(index->addr);
+      delete index;
+    }
+  });
+}
+
+#define SCALAR_GETTER(NAME, EXPR)                                                  \
+  extern "C" cuvsError_t NAME(cuvsIvfPqIndex_t index, int64_t* out)                \
+  {                                                                                \
+    return translate_exceptions([=] { *out = int64_t(index_of(index)->EXPR()); }); \
+  }
+SCALAR_GETTER(cuvsIvfPqIndexGetNLists, n_lists)
+SCALAR_GETTER(cuvsIvfPqIndexGetDim, dim)
+SCALAR_GETTER(cuvsIvfPqIndexGetSize, size)
+SCALAR_GETTER(cuvsIvfPqIndexGetPqDim, pq_dim)
+SCALAR_GETTER(cuvsIvfPqIndexGetPqBits, pq_bits)
+SCALAR_GETTER(cuvsIvfPqIndexGetPqLen, pq_len)
+
+namespace {
+constexpr DLDataType kF32{kDLFloat, 32, 1};
+constexpr DLDataType kU32{kDLUInt, 32, 1};
+constexpr DLDataType kI64{kDLInt, 64, 1};
+}  // namespace
+
+extern "C" cuvsError_t cuvsIvfPqIndexGetCenters(cuvsIvfPqIndex_t index, DLManagedTensor* centers)
+{
+  return translate_exceptions([=] {
+    auto* ix = index_of(index);
+    make_view(centers, ix->centers(), kF32, {int64_t(ix->n_lists()), int64_t(ix->dim())},
+              {int64_t(ix->dim_ext()), 1});
+  });
+}
+extern "C" cuvsError_t cuvsIvfPqIndexGetCentersPadded(cuvsIvfPqIndex_t index, DLManagedTensor* centers)
+{
+  return translate_exceptions([=] {
+    auto* ix = index_of(index);
+    make_view(centers, ix->centers(), kF32, {int64_t(ix->n_lists()), int64_t(ix->dim_ext())});
+  });
+}
+extern "C" cuvsError_t cuvsIvfPqIndexGetPqCenters(cuvsIvfPqIndex_t index, DLManagedTensor* pq_centers)
+{
+  return translate_exceptions([=] {
+    auto* ix            = index_of(index);
+    const int64_t first = ix->codebook_kind() == ivf_pq::codebook_gen::PER_SUBSPACE ? ix->pq_dim()
+                                                                                     : ix->n_lists();
+    make_view(pq_centers, ix->pq_centers(), kF32,
+              {first, int64_t(ix->pq_len()), int64_t(ix->pq_book_size())});
+  });
+}
+extern "C" cuvsError_t cuvsIvfPqIndexGetCentersRot(cuvsIvfPqIndex_t index, DLManagedTensor* centers_rot)
+{
+  return translate_exceptions([=] {
+    auto* ix = index_of(index);
+    make_view(centers_rot, ix->centers_rot(), kF32, {int64_t(ix->n_lists()), int64_t(ix->rot_dim())});
+  });
+}
+extern "C" cuvsError_t cuvsIvfPqIndexGetRotationMatrix(cuvsIvfPqIndex_t index,
+                                                       DLManagedTensor* rotation_matrix)
+{
+  return translate_exceptions([=] {
+    auto* ix = index_of(index);
+    make_view(rotation_matrix, ix->rotation_matrix(), kF32,
+              {int64_t(ix->rot_dim()), int64_t(ix->dim())});
+  });
+}
+extern "C" cuvsError_t cuvsIvfPqIndexGetListSizes(cuvsIvfPqIndex_t index, DLManagedTensor* list_sizes)
+{
+  return translate_exceptions([=] {
+    auto* ix = index_of(index);
+    make_view(list_sizes, ix->list_sizes(), kU32, {int64_t(ix->n_lists())});
+  });
+}
+extern "C" cuvsError_t cuvsIvfPqIndexGetListIndices(cuvsIvfPqIndex_t index, uint32_t label,
+                                                    DLManagedTensor* out_labels)
+{
+  return translate_exceptions([=] {
+    auto* ix = index_of(index);
+    CUVS_EXPECTS(label < ix->n_lists(), "label %u is out of range (n_lists = %u)", label, ix->n_lists());
+    make_view(out_labels, ix->ids() + ix->host_row_offsets()[label], kI64,
+              {int64_t(ix->host_list_sizes()[label])});
+  });
+}
+extern "C" cuvsError_t cuvsIvfPqIndexUnpackContiguousListData(cuvsResources_t res,
+                                                              cuvsIvfPqIndex_t index,
+                                                              DLManagedTensor* out_codes,
+                                                              uint32_t label, uint32_t offset)
+{
+  return translate_exceptions([=] {
+    auto* ix   = index_of(index);
+    auto* data = static_cast<uint8_t*>(checked_data(out_codes, kDLUInt, 8, 2, true, "out_codes"));
+    ivf_pq::helpers::unpack_contiguous_list_data(*res_of(res), *ix, data,
+                                                 uint32_t(out_codes->dl_tensor.shape[0]), label, offset);
+  });
+}
+
+// ------------------------------------------------------------------------------------------------
+// build / extend / transform
+// ------------------------------------------------------------------------------------------------
+extern "C" cuvsError_t cuvsIvfPqBuild(cuvsResources_t res, cuvsIvfPqIndexParams_t params,
+                                      DLManagedTensor* dataset_tensor, cuvsIvfPqIndex_t index)
+{
+  return translate_exceptions([=] {
+    CUVS_EXPECTS(params != nullptr && dataset_tensor != nullptr && index != nullptr, "null argument");
+    const DLTensor& t = dataset_tensor->dl_tensor;
+    auto et           = elem_of_dtype(t.dtype, "dataset");
+    const bool on_dev = is_device_compatible(t);
+    void* data        = checked_data(dataset_tensor, t.dtype.code, t.dtype.bits, 2, on_dev, "dataset");
+    auto* ix          = new index_t();
+    try {
+      ivf_pq::build_any(*res_of(res), convert(*params), data, et, t.shape[0], uint32_t(t.shape[1]),
+                        on_dev, ix);
+    } catch (...) {
+      delete ix;
+      throw;
+    }
+    delete reinterpret_cast<index_t*>(index->addr);
+    index->addr       = reinterpret_cast<uintptr_t>(ix);
+    index->dtype.code = t.dtype.code;
+    index->dtype.bits = t.dtype.bits;
+    index->dtype.lanes = 1;
+  });
+}
+
+extern "C" cuvsError_t cuvsIvfPqBuildPrecomputed(cuvsResources_t res, cuvsIvfPqIndexParams_t params,
+                                                 uint32_t dim, DLManagedTensor* pq_centers,
+                                                 DLManagedTensor* centers, DLManagedTensor* centers_rot,
+                                                 DLManagedTensor* rotation_matrix,
+                                                 cuvsIvfPqIndex_t index)
+{
+  return translate_exceptions([=] {
+    CUVS_EXPECTS(params != nullptr && index != nullptr, "null argument");
+    auto* r   = res_of(res);
+    auto ip   = convert(*params);
+    auto* ix  = new index_t(ip.metric, ip.codebook_kind, ip.n_lists, dim, ip.pq_bits, ip.pq_dim,
+                            ip.conservative_memory_allocation);
+    try {
+      auto* pqc = static_cast<float*>(checked_data(pq_centers, kDLFloat, 32, 3, true, "pq_centers"));
+      auto* cen = static_cast<float*>(checked_data(centers, kDLFloat, 32, 2, true, "centers"));
+      auto* rot = static_cast<float*>(checked_data(centers_rot, kDLFloat, 32, 2, true, "centers_rot"));
+      auto* rm  = static_cast<float*>(checked_data(rotation_matrix, kDLFloat, 32, 2, true, "rotation_matrix"));
+      const auto& ps = pq_centers->dl_tensor;
+      const int64_t first = ip.codebook_kind == ivf_pq::codebook_gen::PER_SUBSPACE ? ix->pq_dim() : ix->n_lists();
+      CUVS_EXPECTS(ps.shape[0] == first && ps.shape[1] == ix->pq_len() && ps.shape[2] == ix->pq_book_size(),
+                   "pq_centers has the wrong shape");
+      CUVS_EXPECTS(centers_rot->dl_tensor.shape[0] == ix->n_lists() &&
+                     centers_rot->dl_tensor.shape[1] == ix->rot_dim(),
+                   "centers_rot must be [n_lists, rot_dim]");
+      CUVS_EXPECTS(rotation_matrix->dl_tensor.shape[0] == ix->rot_dim() &&
+                     rotation_matrix->dl_tensor.shape[1] == ix->dim(),
+                   "rotation_matrix must be [rot_dim, dim]");
+      const auto& cs = centers->dl_tensor;
+      CUVS_EXPECTS(cs.shape[0] == ix->n_lists() && (cs.shape[1] == ix->dim() || cs.shape[1] == ix->dim_ext()),
+                   "centers must be [n_lists, dim] or [n_lists, dim_ext]");
+      ivf_pq::helpers::set_model(*r, ix, pqc, cen, uint32_t(cs.shape[1]), rot, rm);
+    } catch (...) {
+      delete ix;
+      throw;
+    }
+    delete reinterpret_cast<index_t*>(index->addr);
+    index->addr  = reinterpret_cast<uintptr_t>(ix);
+    index->dtype = DLDataType{0, 0, 0};
+  });
+}
+
+extern "C" cuvsError_t cuvsIvfPqExtend(cuvsResources_t res, DLManagedTensor* new_vectors,
+                                       DLManagedTensor* new_indices, cuvsIvfPqIndex_t index)
+{
+  return translate_exceptions([=] {
+    CUVS_EXPECTS(new_vectors != nullptr, "null new_vectors");
+    auto* ix          = index_of(index);
+    const DLTensor& t = new_vectors->dl_tensor;
+    auto et           = elem_of_dtype(t.dtype, "index");
+    const bool on_dev = is_device_compatible(t);
+    if (new_indices) {
+      CUVS_EXPECTS(on_dev == is_device_compatible(new_indices->dl_tensor),
+                   "extend inputs must both either be on device memory or host memory");
+    }
+    if (index->dtype.code == 0 && index->dtype.bits == 0) {
+      index->dtype.code = t.dtype.code;
+      index->dtype.bits = t.dtype.bits;
+    }
+    void* data = checked_data(new_vectors, t.dtype.code, t.dtype.bits, 2, on_dev, "new_vectors");
+    const int64_t* ids = nullptr;
+    if (new_indices) {
+      ids = static_cast<const int64_t*>(checked_data(new_indices, kDLInt, 64, 1, on_dev, "new_indices"));
+      CUVS_EXPECTS(new_indices->dl_tensor.shape[0] == t.shape[0],
+                   "new_indices must have one entry per new vector");
+    }
+    CUVS_EXPECTS(uint32_t(t.shape[1]) == ix->dim(), "new_vectors has the wrong number of columns");
+    ivf_pq::extend_any(*res_of(res), data, et, t.shape[0], ids, on_dev, ix);
+  });
+}
+
+extern "C" cuvsError_t cuvsIvfPqTransform(cuvsResources_t res, cuvsIvfPqIndex_t index,
+                                          DLManagedTensor* input_dataset,
+                                          DLManagedTensor* output_labels,
+                                          DLManagedTensor* output_dataset)
+{
+  return translate_exceptions([=] {
+    auto* ix          = index_of(index);
+    const DLTensor& t = input_dataset->dl_tensor;
+    auto et           = elem_of_dtype(t.dtype, "dataset");
+    void* data   = checked_data(input_dataset, t.dtype.code, t.dtype.bits, 2, true, "input_dataset");
+    auto* labels = static_cast<uint32_t*>(checked_data(output_labels, kDLUInt, 32, 1, true, "output_labels"));
+    auto* codes  = static_cast<uint8_t*>(checked_data(output_dataset, kDLUInt, 8, 2, true, "output_dataset"));
+    CUVS_EXPECTS(uint32_t(t.shape[1]) == ix->dim(), "input_dataset has the wrong number of columns");
+    CUVS_EXPECTS(output_labels->dl_tensor.shape[0] == t.shape[0] &&
+                   output_dataset->dl_tensor.shape[0] == t.shape[0],
+                 "outputs must have one row per input vector");
+    CUVS_EXPECTS(output_dataset->dl_tensor.shape[1] ==
+                   int64_t(cuvs_b200::ceildiv(ix->pq_dim() * ix->pq_bits(), 8u)),
+                 "output_dataset must have ceil(pq_dim * pq_bits / 8) columns");
+    ivf_pq::transform_any(*res_of(res), *ix, data, et, t.shape[0], labels, codes);
+  });
+}
+
+// ------------------------------------------------------------------------------------------------
+// search / serialize / deserialize
+// ------------------------------------------------------------------------------------------------
+extern "C" cuvsError_t cuvsIvfPqSearch(cuvsResources_t res, cuvsIvfPqSearchParams_t params,
+                                       cuvsIvfPqIndex_t index, DLManagedTensor* queries_tensor,
+                                       DLManagedTensor* neighbors_tensor,
+                                       DLManagedTensor* distances_tensor)
+{
+  return translate_exceptions([=] {
+    CUVS_EXPECTS(params && queries_tensor && neighbors_tensor && distances_tensor, "null argument");
+    const DLTensor& queries   = queries_tensor->dl_tensor;
+    const DLTensor& neighbors = neighbors_tensor->dl_tensor;
+    const DLTensor& distances = distances_tensor->dl_tensor;
+    // c/src/neighbors/ivf_pq.cpp:315-325
+    CUVS_EXPECTS(is_device_compatible(queries), "queries should have device compatible memory");
+    CUVS_EXPECTS(is_device_compatible(neighbors), "neighbors should have device compatible memory");
+    CUVS_EXPECTS(is_device_compatible(distances), "distances should have device compatible memory");
+    CUVS_EXPECTS(neighbors.dtype.code == kDLInt && neighbors.dtype.bits == 64,
+                 "neighbors should be of type int64_t");
+    CUVS_EXPECTS(distances.dtype.code == kDLFloat && distances.dtype.bits == 32,
+                 "distances should be of type float32");
+    auto* ix = index_of(index);
+    auto et  = elem_of_dtype(queries.dtype, "queries");
+    void* q  = checked_data(queries_tensor, queries.dtype.code, queries.dtype.bits, 2, true, "queries");
+    auto* nb = static_cast<int64_t*>(checked_data(neighbors_tensor, kDLInt, 64, 2, true, "neighbors"));
+    auto* ds = static_cast<float*>(checked_data(distances_tensor, kDLFloat, 32, 2, true, "distances"));
+    // ivf_pq_search.cuh:1080-1108
+    CUVS_EXPECTS(queries.shape[0] == neighbors.shape[0] && queries.shape[0] == distances.shape[0],
+                 "Number of rows in output neighbors and distances matrices must equal the number "
+                 "of queries.");
+    CUVS_EXPECTS(neighbors.shape[1] == distances.shape[1],
+                 "Number of columns in output neighbors and distances matrices must equal k");
+    CUVS_EXPECTS(queries.shape[1] == int64_t(ix->dim()),
+                 "Number of query dimensions should equal number of dimensions in the index.");
+    ivf_pq::search_params sp;
+    sp.n_probes                 = params->n_probes;
+    sp.lut_dtype                = params->lut_dtype;
+    sp.internal_distance_dtype  = params->internal_distance_dtype;
+    sp.preferred_shmem_carveout = params->preferred_shmem_carveout;
+    sp.coarse_search_dtype      = params->coarse_search_dtype;
+    sp.max_internal_batch_size  = params->max_internal_batch_size;
+    ivf_pq::search_any(*res_of(res), sp, *ix, q, et, uint32_t(queries.shape[0]),
+                       uint32_t(neighbors.shape[1]), nb, ds);
+  });
+}
+
+extern "C" cuvsError_t cuvsIvfPqSerialize(cuvsResources_t res, const char* filename,
+                                          cuvsIvfPqIndex_t index)
+{
+  return translate_exceptions(
+    [=] { ivf_pq::serialize(*res_of(res), std::string(filename), *index_of(index)); });
+}
+
+extern "C" cuvsError_t cuvsIvfPqDeserialize(cuvsResources_t res, const char* filename,
+                                            cuvsIvfPqIndex_t index)
+{
+  return translate_exceptions([=] {
+    CUVS_EXPECTS(index != nullptr && filename != nullptr, "null argument");
+    auto* ix = new index_t();
+    try {
+      ivf_pq::deserialize(*res_of(res), std::string(filename), ix);
+    } catch (...) {
+      delete ix;
+      throw;
+    }
+    delete reinterpret_cast<index_t*>(index->addr);
+    index->addr = reinterpret_cast<uintptr_t>(ix);
+  });
+}

@@ -1,0 +1,123 @@
+// Shared host-side plumbing of the IVF-PQ engine: error type and checks, resources handle, and the
+// grow-only device workspace that lets a steady-state search run without any allocation.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+namespace cuvs_b200 {
+
+// Same role as raft::logic_error in the reference: argument/format errors surfaced to the caller.
+struct error : public std::runtime_error {
+  using std::runtime_error::runtime_error;
+};
+
+[[noreturn]] inline void fail(const char* fmt, ...)
+{
+  char buf[1024];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof(buf), fmt, ap);
+  va_end(ap);
+  throw error(buf);
+}
+
+#define CUVS_EXPECTS(cond, ...)                       \
+  do {                                                \
+    if (!(cond)) { ::cuvs_b200::fail(__VA_ARGS__); }  \
+  } while (0)
+
+#define CUDA_TRY(call)                                                                       \
+  do {                                                                                       \
+    cudaError_t e__ = (call);                                                                \
+    if (e__ != cudaSuccess) {                                                                \
+      ::cuvs_b200::fail("CUDA error %s at %s:%d: %s", cudaGetErrorName(e__), __FILE__,       \
+                        __LINE__, cudaGetErrorString(e__));                                  \
+    }                                                                                        \
+  } while (0)
+
+#ifdef __CUDACC__
+#define CUVS_HD __host__ __device__
+#else
+#define CUVS_HD
+#endif
+
+template <typename T>
+CUVS_HD constexpr T ceildiv(T a, T b)
+{
+  return (a + b - 1) / b;
+}
+template <typename T>
+CUVS_HD constexpr T round_up(T a, T b)
+{
+  return ceildiv(a, b) * b;
+}
+
+// One grow-only device buffer carved into aligned slices per call.
+class workspace {
+ public:
+  ~workspace() { release(); }
+  void reserve(size_t bytes)
+  {
+    if (bytes <= cap_) { return; }
+    release();
+    CUDA_TRY(cudaMalloc(&base_, bytes));
+    cap_ = bytes;
+  }
+  void release()
+  {
+    if (base_) { cudaFree(base_); }
+    base_ = nullptr;
+    cap_  = 0;
+  }
+  size_t capacity() const { return cap_; }
+  char* base() const { return static_cast<char*>(base_); }
+
+ private:
+  void* base_ = nullptr;
+  size_t cap_ = 0;
+};
+
+// Computes slice offsets first (dry run), then hands out pointers from a workspace.
+class ws_layout {
+ public:
+  size_t add(size_t bytes)
+  {
+    size_t off = total_;
+    total_ += round_up<size_t>(bytes ? bytes : 1, 256);
+    return off;
+  }
+  size_t total() const { return total_; }
+
+ private:
+  size_t total_ = 0;
+};
+
+// The opaque object behind cuvsResources_t (raft::resources in the reference): device, stream,
+// workspace.  One per host thread, like the reference handle.
+struct resources {
+  int device            = 0;
+  cudaStream_t stream   = nullptr;  // caller-set; default stream otherwise
+  int sm_count          = 0;
+  int smem_optin        = 0;        // max dynamic shared memory per block (opt-in)
+  int cc_major          = 0;
+  workspace ws;
+  // small pinned host word for an occasional device->host scalar
+  uint32_t* pinned = nullptr;
+  // counters read by the benchmark ("how many kernels of ours ran")
+  uint64_t launches = 0;
+
+  resources();
+  ~resources();
+  resources(const resources&)            = delete;
+  resources& operator=(const resources&) = delete;
+  void sync() const { CUDA_TRY(cudaStreamSynchronize(stream)); }
+};
+
+}  // namespace cuvs_b200

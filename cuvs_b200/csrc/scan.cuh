@@ -1,0 +1,354 @@
+// The fine-search kernel: for every (query, probed list) pair build the look-up table in shared
+// memory, stream the list's interleaved PQ codes, score every vector and keep the k best in
+// registers.  Candidate distances never touch global memory; only k keys per pair are written.
+//
+// Arithmetic follows the reference's compute_similarity kernel so that results can be compared
+// number by number with the CPU oracle:
+//   base diff  .. detail/jit_lto_kernels/precompute_base_diff_impl.cuh:14-39
+//   LUT        .. detail/jit_lto_kernels/create_lut_impl.cuh:17-79 (fp32 FMA chain over pq_len,
+//                 rounded once to the LUT type)
+//   8-bit float . ivf_pq_fp_8bit.cuh:31-100
+//   score      .. detail/jit_lto_kernels/compute_score_impl.cuh:20-79 (entries summed in subspace
+//                 order in the internal distance type)
+//
+// Execution shape (differs from the reference): a persistent grid of one 1024-thread CTA per SM.
+// A CTA keeps the per-subspace PQ codebook in shared memory for its whole life and is split into
+// G independent thread groups (G = 1, 2 or 4, as shared memory allows); each group pulls pairs
+// from a global counter, owns one LUT, and synchronises on its own named barrier.  Pairs are
+// ordered by list so that co-resident groups stream the same bytes out of L2.  LUT entries are
+// computed two at a time with packed fp32x2 arithmetic (IEEE round-to-nearest, identical bits to
+// scalar FMA).  Each warp scores 32 vectors per step (one 16-byte load per lane per code piece,
+// 512 contiguous bytes per warp) and keeps a sorted top-k across its lanes; a per-query bound
+// shared through global memory lets later probes discard almost every candidate with one compare.
+#pragma once
+
+#include "topk.cuh"
+
+#include <cuda_fp16.h>
+
+namespace cuvs_b200 {
+
+struct scan_params {
+  // index
+  const float* pq_centers;
+  const float* centers_rot;
+  const uint8_t* codes;
+  const uint32_t* list_sizes;
+  const uint64_t* row_off;
+  uint32_t pq_dim, pq_len, rot_dim, n_pieces;
+  int per_cluster;
+  int cosine;
+  // batch
+  const float* rot_q;           // [n_q, rot_dim]
+  const uint32_t* probes;       // [n_q, n_probes]
+  const uint32_t* chunk_index;  // [n_q, n_probes] inclusive prefix sums of probed list sizes
+  const uint32_t* pair_order;   // [n_pairs] pair ids (q * n_probes + p) ordered by list
+  uint32_t n_pairs, n_probes, k;
+  uint32_t* query_kth;  // [n_q] ordered-score bound, starts at 0xFFFFFFFF
+  uint64_t* out_keys;   // [n_q, n_probes, k]
+  uint32_t* work_counter;
+  // shared memory plan
+  uint32_t n_groups, group_threads;
+  uint32_t pqc_in_smem, smem_pqc_bytes, smem_group_bytes, lut_bytes, base_bytes, merge_bytes;
+};
+
+enum { LUT_F32 = 0, LUT_F16 = 1, LUT_FP8 = 2 };
+
+// ---- packed fp32x2 arithmetic (sm_100) ---------------------------------------------------------
+__device__ __forceinline__ uint64_t pack2(float x, float y)
+{
+  return (uint64_t(__float_as_uint(y)) << 32) | __float_as_uint(x);
+}
+__device__ __forceinline__ float lo2(uint64_t v) { return __uint_as_float(uint32_t(v)); }
+__device__ __forceinline__ float hi2(uint64_t v) { return __uint_as_float(uint32_t(v >> 32)); }
+__device__ __forceinline__ uint64_t sub2(uint64_t a, uint64_t b)
+{
+  uint64_t d;
+  asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c)
+{
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+
+// ---- 8-bit float, 5 exponent bits (ivf_pq_fp_8bit.cuh) -----------------------------------------
+template <bool Signed>
+__device__ __forceinline__ uint8_t fp8_encode(float v)
+{
+  constexpr uint32_t kExpMask = 15u;
+  constexpr float kMin        = 1.0f / float(1u << kExpMask);
+  constexpr float kMax        = float(1u << (kExpMask + 1u)) * (2.0f - 1.0f / 8.0f);
+  float a                     = Signed ? fabsf(v) : v;
+  uint8_t u;
+  if (a < kMin) {
+    u = 0;
+  } else if (a >= kMax) {
+    u = 0xffu;
+  } else {
+    u = uint8_t((__float_as_uint(a) + (kExpMask << 23u) - 0x3f800000u) >> 20u);
+  }
+  if (Signed) { u = uint8_t((u & 0xfeu) | (v < 0 ? 1u : 0u)); }
+  return u;
+}
+template <bool Signed>
+__device__ __forceinline__ float fp8_to_float(uint32_t b)
+{
+  constexpr uint32_t kBase32 = (0x3f800000u | (0x00400000u >> 3)) - (15u << 23);
+  uint32_t u                 = Signed ? (b & ~1u) : b;
+  uint32_t r                 = kBase32 + (u << 20);
+  if (Signed) { r |= (b & 1u) << 31; }
+  return __uint_as_float(r);
+}
+template <bool Signed>
+__device__ __forceinline__ __half fp8_to_half(uint32_t b)
+{
+  constexpr uint32_t kBase16 = (0x3c00u | (0x0200u >> 3)) - (15u << 10);
+  uint32_t u                 = Signed ? (b & ~1u) : b;
+  uint32_t r                 = (kBase16 + (u << 7)) & 0xffffu;
+  if (Signed) { r ^= (b & 1u) << 15; }
+  return __ushort_as_half(static_cast<unsigned short>(r));
+}
+
+template <int LutKind>
+struct lut_elem;
+template <> struct lut_elem<LUT_F32> { using type = float; };
+template <> struct lut_elem<LUT_F16> { using type = __half; };
+template <> struct lut_elem<LUT_FP8> { using type = uint8_t; };
+
+__device__ __forceinline__ void group_bar(int id, int n)
+{
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(n) : "memory");
+}
+
+// One looked-up entry added to the running score, in the internal distance type.
+template <int LutKind, bool OutHalf, bool IsIP>
+struct accum {
+  using lut_t = typename lut_elem<LutKind>::type;
+  float f;
+  __half h;
+  __device__ __forceinline__ void init()
+  {
+    f = 0.0f;
+    h = __ushort_as_half(0);
+  }
+  __device__ __forceinline__ void add(const lut_t* row, uint32_t code)
+  {
+    if constexpr (!OutHalf) {
+      if constexpr (LutKind == LUT_F32) {
+        f += row[code];
+      } else if constexpr (LutKind == LUT_F16) {
+        f += __half2float(row[code]);
+      } else {
+        f += fp8_to_float<IsIP>(row[code]);
+      }
+    } else {
+      if constexpr (LutKind == LUT_F16) {
+        h = __hadd(h, row[code]);
+      } else {
+        h = __hadd(h, fp8_to_half<IsIP>(row[code]));
+      }
+    }
+  }
+  __device__ __forceinline__ float result(bool cosine)
+  {
+    if constexpr (!OutHalf) {
+      return cosine ? f + 1.0f : f;
+    } else {
+      if (cosine) { h = __hadd(h, __float2half(1.0f)); }
+      return __half2float(h);
+    }
+  }
+};
+
+// Codes of one 16-byte piece -> LUT lookups.  `n_valid` = codes used in this piece.
+template <int PqBits, int LutKind, bool OutHalf, bool IsIP, bool Full>
+__device__ __forceinline__ void score_piece(accum<LutKind, OutHalf, IsIP>& acc, const uint4& v,
+                                            const typename lut_elem<LutKind>::type* lut_row,
+                                            uint32_t n_valid)
+{
+  constexpr uint32_t kBook = 1u << PqBits;
+  constexpr uint32_t kMask = kBook - 1u;
+  constexpr int kPerPiece  = 128 / PqBits;
+  const uint32_t w[4]      = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int c = 0; c < kPerPiece; c++) {
+    constexpr int dummy = 0;
+    (void)dummy;
+    const int bit  = c * PqBits;
+    const int word = bit >> 5;
+    const int sh   = bit & 31;
+    uint32_t code;
+    if (sh + PqBits <= 32) {
+      code = (w[word] >> sh) & kMask;
+    } else {
+      code = __funnelshift_r(w[word], w[word + 1 > 3 ? 3 : word + 1], sh) & kMask;
+    }
+    if (Full || uint32_t(c) < n_valid) { acc.add(lut_row + size_t(c) * kBook, code); }
+  }
+}
+
+template <int PqBits, int LutKind, bool OutHalf, bool IsIP, int KPL>
+__global__ void __launch_bounds__(1024, 1) scan_kernel(const scan_params p)
+{
+  using lut_t               = typename lut_elem<LutKind>::type;
+  constexpr uint32_t kBook  = 1u << PqBits;
+  constexpr int kPerPiece   = 128 / PqBits;
+  extern __shared__ __align__(16) uint8_t smem[];
+
+  const int tid      = threadIdx.x;
+  const int gthreads = int(p.group_threads);
+  const int g        = tid / gthreads;
+  const int gt       = tid - g * gthreads;
+  const int gw       = gt >> 5;
+  const int lane     = tid & 31;
+  const int n_gwarps = gthreads >> 5;
+  const int bar_id   = 1 + g;
+
+  float* s_pqc      = reinterpret_cast<float*>(smem);
+  uint8_t* gbase    = smem + p.smem_pqc_bytes + size_t(g) * p.smem_group_bytes;
+  lut_t* s_lut      = reinterpret_cast<lut_t*>(gbase);
+  float* s_base     = reinterpret_cast<float*>(gbase + p.lut_bytes);
+  uint64_t* s_merge = reinterpret_cast<uint64_t*>(gbase + p.lut_bytes + p.base_bytes);
+  uint32_t* s_item  = reinterpret_cast<uint32_t*>(gbase + p.lut_bytes + p.base_bytes + p.merge_bytes);
+
+  if (p.pqc_in_smem) {
+    const uint32_t n4 = (p.pq_dim * p.pq_len * kBook) / 4;
+    const float4* src = reinterpret_cast<const float4*>(p.pq_centers);
+    float4* dst       = reinterpret_cast<float4*>(s_pqc);
+    for (uint32_t i = tid; i < n4; i += blockDim.x) { dst[i] = __ldg(src + i); }
+  }
+  __syncthreads();
+
+  const uint32_t len     = p.pq_len;
+  const uint32_t k       = p.k;
+  const uint32_t lut_n2  = (p.pq_dim * kBook) >> 1;  // LUT entries, two at a time
+  warp_topk<KPL> queue;
+
+  for (;;) {
+    if (gt == 0) { *s_item = atomicAdd(p.work_counter, 1u); }
+    group_bar(bar_id, gthreads);
+    const uint32_t w = *s_item;
+    if (w >= p.n_pairs) { break; }
+
+    const uint32_t pair  = p.pair_order ? p.pair_order[w] : w;
+    const uint32_t q     = pair / p.n_probes;
+    const uint32_t pi    = pair - q * p.n_probes;
+    const uint32_t label = p.probes[pair];
+    const uint32_t n     = p.list_sizes[label];
+    uint64_t* out        = p.out_keys + size_t(pair) * k;
+
+    if (n == 0) {
+      for (uint32_t i = gt; i < k; i += gthreads) { out[i] = kEmptyKey; }
+      group_bar(bar_id, gthreads);  // keeps s_item stable until every thread has read it
+      continue;
+    }
+    const uint32_t sample_offset = pi > 0 ? p.chunk_index[pair - 1] : 0u;
+
+    // ---- base diff ----
+    {
+      const float* rq = p.rot_q + size_t(q) * p.rot_dim;
+      const float* c  = p.centers_rot + size_t(label) * p.rot_dim;
+      for (uint32_t i = gt; i < p.rot_dim; i += gthreads) {
+        if constexpr (!IsIP) {
+          s_base[i] = __fsub_rn(rq[i], __ldg(c + i));
+        } else {
+          float qv = rq[i];
+          reinterpret_cast<float2*>(s_base)[i] = make_float2(qv, __fmul_rn(__ldg(c + i), qv));
+        }
+      }
+    }
+    group_bar(bar_id, gthreads);
+
+    // ---- LUT ----
+    {
+      const float* pqc = p.pqc_in_smem ? s_pqc
+                                       : (p.per_cluster ? p.pq_centers + size_t(label) * len * kBook
+                                                        : p.pq_centers);
+      for (uint32_t e2 = gt; e2 < lut_n2; e2 += gthreads) {
+        const uint32_t e  = e2 << 1;
+        const uint32_t j  = e >> PqBits;
+        const uint32_t b  = e & (kBook - 1u);
+        const float* cb   = pqc + (p.per_cluster ? 0u : j * len * kBook) + b;
+        uint64_t score    = 0ull;  // (+0.0f, +0.0f)
+        for (uint32_t kk = 0; kk < len; kk++) {
+          const float2 pq = *reinterpret_cast<const float2*>(cb + kk * kBook);
+          const uint64_t pq2 = pack2(pq.x, pq.y);
+          if constexpr (!IsIP) {
+            const float d      = s_base[j * len + kk];
+            const uint64_t dif = sub2(pack2(d, d), pq2);
+            score              = fma2(dif, dif, score);
+          } else {
+            const float2 qy = reinterpret_cast<const float2*>(s_base)[j * len + kk];
+            score           = sub2(score, pack2(qy.y, qy.y));
+            score           = fma2(pack2(-qy.x, -qy.x), pq2, score);
+          }
+        }
+        if constexpr (LutKind == LUT_F32) {
+          reinterpret_cast<float2*>(s_lut)[e2] = make_float2(lo2(score), hi2(score));
+        } else if constexpr (LutKind == LUT_F16) {
+          reinterpret_cast<__half2*>(s_lut)[e2] = __floats2half2_rn(lo2(score), hi2(score));
+        } else {
+          reinterpret_cast<uint16_t*>(s_lut)[e2] =
+            uint16_t(fp8_encode<IsIP>(lo2(score))) | (uint16_t(fp8_encode<IsIP>(hi2(score))) << 8);
+        }
+      }
+    }
+    group_bar(bar_id, gthreads);
+
+    // ---- scan ----
+    queue.init(int(k));
+    {
+      const uint32_t bound    = *reinterpret_cast<volatile uint32_t*>(p.query_kth + q);
+      const uint32_t n_groups = (n + 31u) >> 5;
+      const uint4* list =
+        reinterpret_cast<const uint4*>(p.codes + p.row_off[label] * size_t(p.n_pieces) * 16u);
+      for (uint32_t gi = gw; gi < n_groups; gi += n_gwarps) {
+        const uint4* src = list + size_t(gi) * p.n_pieces * 32u + lane;
+        accum<LutKind, OutHalf, IsIP> acc;
+        acc.init();
+        uint32_t j0 = 0;
+        uint32_t c  = 0;
+        for (; j0 + kPerPiece <= p.pq_dim; j0 += kPerPiece, c++) {
+          const uint4 v = __ldg(src + c * 32u);
+          score_piece<PqBits, LutKind, OutHalf, IsIP, true>(acc, v, s_lut + size_t(j0) * kBook, 0);
+        }
+        if (j0 < p.pq_dim) {
+          const uint4 v = __ldg(src + c * 32u);
+          score_piece<PqBits, LutKind, OutHalf, IsIP, false>(acc, v, s_lut + size_t(j0) * kBook,
+                                                             p.pq_dim - j0);
+        }
+        const float score    = acc.result(p.cosine != 0);
+        const uint32_t row   = gi * 32u + lane;
+        const bool valid     = row < n;
+        const uint32_t ord   = float_to_ordered(score);
+        const uint64_t key   = (uint64_t(ord) << 32) | (sample_offset + row);
+        queue.offer(key, valid && ord <= bound);
+      }
+    }
+
+    // ---- merge the warps' queues, write k keys ----
+    queue.store(s_merge + size_t(gw) * k, int(k));
+    group_bar(bar_id, gthreads);
+    if (gw == 0) {
+      const uint32_t others = uint32_t(n_gwarps - 1) * k;
+      for (uint32_t t0 = 0; t0 < others; t0 += 32) {
+        const uint32_t t = t0 + lane;
+        uint64_t key     = t < others ? s_merge[k + t] : kEmptyKey;
+        queue.offer(key, t < others);
+      }
+      queue.store(out, int(k));
+      const uint32_t kth_score = uint32_t(queue.kth() >> 32);
+      if (lane == 0 && kth_score != kEmptyScore) { atomicMin(p.query_kth + q, kth_score); }
+    }
+    // the barrier at the top of the loop orders warp 0's reads of s_merge before the next writes
+  }
+}
+
+// Host-side launcher of one instantiation family (defined once per PqBits in scan_inst.cu).
+void launch_scan(const scan_params& p, int pq_bits, int lut_kind, bool out_half, bool is_ip,
+                 int kpl, int grid, size_t smem_bytes, cudaStream_t stream);
+
+}  // namespace cuvs_b200

@@ -1,0 +1,597 @@
+// Host orchestration of IVF-PQ search and the small kernels around the two heavy ones
+// (coarse selection in coarse.cu, code scan in scan.cuh).
+//
+// Stage map to the reference (cpp/src/neighbors/ivf_pq/ivf_pq_search.cuh):
+//   prep_queries_kernel ....... query cast + pad (:103-125) and rotation (:996-1025), one kernel
+//   select_clusters ........... coarse.cu (:127-167)
+//   chunk_and_count_kernel .... calc_chunk_indices (cpp/src/neighbors/ivf_common.cu:21-50) fused with
+//                               the histogram of a counting sort by list (replaces the radix sort
+//                               of :483-523)
+//   scan_kernel ............... compute_similarity (scan.cuh)
+//   final_merge_kernel ........ cross-probe select_k (:646-655) + postprocess_distances
+//                               (ivf_common.cuh:175-252) + postprocess_neighbors (:112-169), fused
+#include "ivf_pq.hpp"
+#include "scan.cuh"
+#include "search_internal.hpp"
+#include "topk.cuh"
+
+#include <algorithm>
+#include <cmath>
+
+namespace cuvs_b200 {
+void launch_scan_bits_4(const scan_params&, int, bool, bool, int, int, size_t, cudaStream_t);
+void launch_scan_bits_5(const scan_params&, int, bool, bool, int, int, size_t, cudaStream_t);
+void launch_scan_bits_6(const scan_params&, int, bool, bool, int, int, size_t, cudaStream_t);
+void launch_scan_bits_7(const scan_params&, int, bool, bool, int, int, size_t, cudaStream_t);
+void launch_scan_bits_8(const scan_params&, int, bool, bool, int, int, size_t, cudaStream_t);
+
+void launch_scan(const scan_params& p, int pq_bits, int lut_kind, bool out_half, bool is_ip, int kpl,
+                 int grid, size_t smem, cudaStream_t stream)
+{
+  switch (pq_bits) {
+    case 4: launch_scan_bits_4(p, lut_kind, out_half, is_ip, kpl, grid, smem, stream); break;
+    case 5: launch_scan_bits_5(p, lut_kind, out_half, is_ip, kpl, grid, smem, stream); break;
+    case 6: launch_scan_bits_6(p, lut_kind, out_half, is_ip, kpl, grid, smem, stream); break;
+    case 7: launch_scan_bits_7(p, lut_kind, out_half, is_ip, kpl, grid, smem, stream); break;
+    case 8: launch_scan_bits_8(p, lut_kind, out_half, is_ip, kpl, grid, smem, stream); break;
+    default: fail("pq_bits must be within [4, 8]");
+  }
+}
+}  // namespace cuvs_b200
+
+namespace cuvs::neighbors::ivf_pq {
+
+using namespace cuvs_b200;
+
+namespace {
+
+// ------------------------------------------------------------------------------------------------
+// query preparation
+// ------------------------------------------------------------------------------------------------
+template <typename T>
+__device__ __forceinline__ float map_to_float(T x);
+template <> __device__ __forceinline__ float map_to_float<float>(float x) { return x; }
+template <> __device__ __forceinline__ float map_to_float<__half>(__half x) { return __half2float(x); }
+template <> __device__ __forceinline__ float map_to_float<int8_t>(int8_t x)
+{
+  return __fmul_rn(float(x), 1.0f / 128.0f);
+}
+template <> __device__ __forceinline__ float map_to_float<uint8_t>(uint8_t x)
+{
+  return __fmul_rn(float(x), 1.0f / 256.0f);
+}
+
+// One block per query.  fq = mapping<float>(query) padded to dim_ext with -0.5 (L2) or 0 in column
+// `dim`; rot_q = R * fq[:dim], each output accumulated by one thread in ascending k with FMA.
+template <typename T>
+__global__ void prep_queries_kernel(const T* __restrict__ queries, uint32_t dim, uint32_t dim_ext,
+                                    uint32_t rot_dim, int is_l2, int cosine, int identity,
+                                    const float* __restrict__ rotation, float* __restrict__ fq,
+                                    float* __restrict__ rot_q)
+{
+  extern __shared__ float s_buf[];  // [dim] query, [rot_dim] rotated (cosine only)
+  float* s_q         = s_buf;
+  float* s_r         = s_buf + dim;
+  const uint32_t q   = blockIdx.x;
+  const T* src       = queries + size_t(q) * dim;
+  float* dst         = fq + size_t(q) * dim_ext;
+  for (uint32_t i = threadIdx.x; i < dim_ext; i += blockDim.x) {
+    float v = 0.0f;
+    if (i < dim) {
+      v      = map_to_float<T>(src[i]);
+      s_q[i] = v;
+    } else if (i == dim && is_l2) {
+      v = -0.5f;
+    }
+    dst[i] = v;
+  }
+  __syncthreads();
+  float* out = rot_q + size_t(q) * rot_dim;
+  for (uint32_t r = threadIdx.x; r < rot_dim; r += blockDim.x) {
+    float acc;
+    if (identity) {
+      acc = s_q[r];
+    } else {
+      const float* row = rotation + size_t(r) * dim;
+      acc              = 0.0f;
+      for (uint32_t k = 0; k < dim; k++) { acc = __fmaf_rn(__ldg(row + k), s_q[k], acc); }
+    }
+    if (cosine) {
+      s_r[r] = acc;
+    } else {
+      out[r] = acc;
+    }
+  }
+  if (cosine) {
+    __shared__ float s_norm;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float ss = 0.0f;
+      for (uint32_t i = 0; i < rot_dim; i++) { ss = __fmaf_rn(s_r[i], s_r[i], ss); }
+      s_norm = __fsqrt_rn(ss);
+    }
+    __syncthreads();
+    const float nrm = s_norm;
+    for (uint32_t r = threadIdx.x; r < rot_dim; r += blockDim.x) {
+      out[r] = nrm > 0.0f ? __fdiv_rn(s_r[r], nrm) : s_r[r];
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// per-probe sample offsets + counting sort of the (query, probe) pairs by list
+// ------------------------------------------------------------------------------------------------
+// One warp per query: chunk_index[q, p] = sum_{p' <= p} list_sizes[probes[q, p']]; list_count[l]++.
+__global__ void chunk_and_count_kernel(const uint32_t* __restrict__ probes,
+                                       const uint32_t* __restrict__ list_sizes, uint32_t n_queries,
+                                       uint32_t n_probes, uint32_t* __restrict__ chunk_index,
+                                       uint32_t* __restrict__ list_count)
+{
+  const uint32_t q    = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const uint32_t lane = threadIdx.x & 31;
+  if (q >= n_queries) { return; }
+  uint32_t carry = 0;
+  for (uint32_t p0 = 0; p0 < n_probes; p0 += 32) {
+    const uint32_t p = p0 + lane;
+    uint32_t v       = 0;
+    if (p < n_probes) {
+      const uint32_t label = probes[size_t(q) * n_probes + p];
+      v                    = list_sizes[label];
+      atomicAdd(list_count + label, 1u);
+    }
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      uint32_t t = __shfl_up_sync(kFullMask, v, d);
+      if (lane >= uint32_t(d)) { v += t; }
+    }
+    if (p < n_probes) { chunk_index[size_t(q) * n_probes + p] = carry + v; }
+    carry += __shfl_sync(kFullMask, v, 31);
+  }
+}
+
+// Exclusive prefix sum over n values, in place, by one block of 1024 threads.
+__global__ void exclusive_scan_kernel(uint32_t* __restrict__ data, uint32_t n)
+{
+  __shared__ uint32_t s_warp[32];
+  __shared__ uint32_t s_carry;
+  const uint32_t tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+  if (tid == 0) { s_carry = 0; }
+  __syncthreads();
+  for (uint32_t base = 0; base < n; base += 1024) {
+    const uint32_t i = base + tid;
+    uint32_t v       = i < n ? data[i] : 0u;
+    uint32_t x       = v;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      uint32_t t = __shfl_up_sync(kFullMask, x, d);
+      if (lane >= uint32_t(d)) { x += t; }
+    }
+    if (lane == 31) { s_warp[wid] = x; }
+    __syncthreads();
+    if (wid == 0) {
+      uint32_t w = s_warp[lane];
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        uint32_t t = __shfl_up_sync(kFullMask, w, d);
+        if (lane >= uint32_t(d)) { w += t; }
+      }
+      s_warp[lane] = w;
+    }
+    __syncthreads();
+    const uint32_t carry  = s_carry;
+    const uint32_t before = carry + (wid > 0 ? s_warp[wid - 1] : 0u) + (x - v);
+    if (i < n) { data[i] = before; }
+    __syncthreads();
+    if (tid == 1023) { s_carry = before + v; }
+    __syncthreads();
+  }
+}
+
+__global__ void scatter_pairs_kernel(const uint32_t* __restrict__ probes, uint32_t n_pairs,
+                                     uint32_t* __restrict__ cursor, uint32_t* __restrict__ pair_order)
+{
+  const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n_pairs) { return; }
+  const uint32_t pos = atomicAdd(cursor + probes[i], 1u);
+  pair_order[pos]    = i;
+}
+
+__global__ void fill_u32_kernel(uint32_t* p, size_t n, uint32_t v)
+{
+  size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x;
+  if (i < n) { p[i] = v; }
+}
+
+// ------------------------------------------------------------------------------------------------
+// final selection across probes + post-processing
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ float postprocess_distance(float score, int metric, float scale)
+{
+  switch (metric) {
+    case 0: return scale != 1.0f ? __fmul_rn(score, __fmul_rn(scale, scale)) : score;
+    case 1: return scale != 1.0f ? __fmul_rn(__fsqrt_rn(score), scale) : __fsqrt_rn(score);
+    case 6: return __fmul_rn(score, __fmul_rn(__fmul_rn(-1.0f, scale), scale));
+    default: {
+      const float f = __fmul_rn(scale, scale);
+      return f != 1.0f ? __fmul_rn(score, f) : score;
+    }
+  }
+}
+
+// One warp per query: k smallest of the n_probes * k keys, then id translation
+// (binary search of the sample index in chunk_index, as find_chunk_ix does) and distance scaling.
+template <int KPL>
+__global__ void final_merge_kernel(const uint64_t* __restrict__ keys,
+                                   const uint32_t* __restrict__ probes,
+                                   const uint32_t* __restrict__ chunk_index,
+                                   const uint64_t* __restrict__ row_off,
+                                   const int64_t* __restrict__ ids, uint32_t n_queries,
+                                   uint32_t n_probes, uint32_t k, int metric, float scale,
+                                   int64_t* __restrict__ neighbors, float* __restrict__ distances)
+{
+  const uint32_t q    = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const uint32_t lane = threadIdx.x & 31;
+  if (q >= n_queries) { return; }
+  warp_topk<KPL> queue;
+  queue.init(int(k));
+  const uint64_t* src = keys + size_t(q) * n_probes * k;
+  const uint32_t n    = n_probes * k;
+  for (uint32_t t0 = 0; t0 < n; t0 += 32) {
+    const uint32_t t = t0 + lane;
+    uint64_t key     = t < n ? src[t] : kEmptyKey;
+    queue.offer(key, t < n);
+  }
+  const uint32_t* ci = chunk_index + size_t(q) * n_probes;
+  const uint32_t* pr = probes + size_t(q) * n_probes;
+#pragma unroll
+  for (int r = 0; r < KPL; r++) {
+    const uint32_t pos = lane * KPL + r;
+    if (pos >= k) { continue; }
+    const uint64_t key = queue.a[r];
+    int64_t id         = kOutOfBoundsRecord;
+    float score        = INFINITY;
+    if (uint32_t(key >> 32) != kEmptyScore) {
+      score              = ordered_to_float(uint32_t(key >> 32));
+      uint32_t sample    = uint32_t(key);
+      uint32_t lo = 0, hi = n_probes;
+      while (lo < hi) {
+        uint32_t mid = (lo + hi) >> 1;
+        if (ci[mid] <= sample) {
+          lo = mid + 1;
+        } else {
+          hi = mid;
+        }
+      }
+      if (lo < n_probes) {
+        if (lo > 0) { sample -= ci[lo - 1]; }
+        id = ids[row_off[pr[lo]] + sample];
+      }
+    }
+    neighbors[size_t(q) * k + pos] = id;
+    distances[size_t(q) * k + pos] = postprocess_distance(score, metric, scale);
+  }
+}
+
+// knn_merge_parts (cpp/src/neighbors/detail/knn_merge_parts.cuh:24-97): one warp per query.
+template <int KPL>
+__global__ void merge_parts_kernel(const float* __restrict__ in_dist,
+                                   const int64_t* __restrict__ in_ids, uint32_t n_parts,
+                                   uint32_t n_queries, uint32_t k, int select_min,
+                                   float* __restrict__ out_dist, int64_t* __restrict__ out_ids)
+{
+  const uint32_t q    = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const uint32_t lane = threadIdx.x & 31;
+  if (q >= n_queries) { return; }
+  warp_topk<KPL> queue;
+  queue.init(int(k));
+  const uint32_t n = n_parts * k;
+  for (uint32_t t0 = 0; t0 < n; t0 += 32) {
+    const uint32_t t = t0 + lane;
+    uint64_t key     = kEmptyKey;
+    bool valid       = false;
+    if (t < n) {
+      const uint32_t part = t / k, pos = t - part * k;
+      const size_t src    = (size_t(part) * n_queries + q) * k + pos;
+      const int64_t id    = in_ids[src];
+      if (id != kOutOfBoundsRecord) {
+        float d = in_dist[src];
+        key     = make_key(select_min ? d : -d, t);
+        valid   = true;
+      }
+    }
+    queue.offer(key, valid);
+  }
+#pragma unroll
+  for (int r = 0; r < KPL; r++) {
+    const uint32_t pos = lane * KPL + r;
+    if (pos >= k) { continue; }
+    const uint64_t key = queue.a[r];
+    int64_t id         = kOutOfBoundsRecord;
+    float d            = select_min ? INFINITY : -INFINITY;
+    if (uint32_t(key >> 32) != kEmptyScore) {
+      const uint32_t t    = uint32_t(key);
+      const uint32_t part = t / k, p = t - part * k;
+      const size_t src    = (size_t(part) * n_queries + q) * k + p;
+      id                  = in_ids[src];
+      d                   = in_dist[src];
+    }
+    out_ids[size_t(q) * k + pos]  = id;
+    out_dist[size_t(q) * k + pos] = d;
+  }
+}
+
+int kpl_for_k(uint32_t k) { return k <= 32 ? 1 : (k <= 64 ? 2 : 4); }
+
+}  // namespace
+
+// ------------------------------------------------------------------------------------------------
+// shared-memory plan of the scan kernel
+// ------------------------------------------------------------------------------------------------
+scan_plan plan_scan(const raft::resources& res, const index<int64_t>& idx, int lut_kind, bool is_ip,
+                    uint32_t k)
+{
+  scan_plan plan{};
+  const size_t lut_elem  = lut_kind == LUT_F32 ? 4 : (lut_kind == LUT_F16 ? 2 : 1);
+  const size_t lut_bytes = round_up<size_t>(size_t(idx.pq_dim()) * idx.pq_book_size() * lut_elem, 16);
+  const size_t base_bytes = round_up<size_t>(size_t(idx.rot_dim()) * (is_ip ? 8 : 4), 16);
+  const size_t pqc_bytes =
+    idx.codebook_kind() == codebook_gen::PER_SUBSPACE
+      ? round_up<size_t>(size_t(idx.pq_dim()) * idx.pq_len() * idx.pq_book_size() * 4, 16)
+      : 0;
+  const size_t limit = size_t(res.smem_optin) - 1024;
+  for (int with_pqc = (pqc_bytes > 0 ? 1 : 0); with_pqc >= 0; with_pqc--) {
+    for (int g = 4; g >= 1; g >>= 1) {
+      const size_t merge_bytes = round_up<size_t>(size_t(1024 / g / 32) * k * 8, 16);
+      const size_t group_bytes = lut_bytes + base_bytes + merge_bytes + 16;
+      const size_t total       = (with_pqc ? pqc_bytes : 0) + size_t(g) * group_bytes;
+      if (total <= limit) {
+        plan.n_groups      = g;
+        plan.group_threads = 1024 / g;
+        plan.pqc_in_smem   = with_pqc;
+        plan.pqc_bytes     = with_pqc ? uint32_t(pqc_bytes) : 0;
+        plan.group_bytes   = uint32_t(group_bytes);
+        plan.lut_bytes     = uint32_t(lut_bytes);
+        plan.base_bytes    = uint32_t(base_bytes);
+        plan.merge_bytes   = uint32_t(merge_bytes);
+        plan.total_bytes   = total;
+        return plan;
+      }
+    }
+  }
+  fail("IVF-PQ search: a look-up table of %zu bytes (pq_dim=%u, pq_bits=%u) does not fit in the %d "
+       "bytes of shared memory of this GPU; use a smaller lut_dtype",
+       lut_bytes, idx.pq_dim(), idx.pq_bits(), res.smem_optin);
+}
+
+// ------------------------------------------------------------------------------------------------
+// search
+// ------------------------------------------------------------------------------------------------
+void search_any(raft::resources& res, const search_params& params, const index<int64_t>& idx,
+                const void* queries, elem_t qtype, uint32_t n_queries, uint32_t k,
+                int64_t* neighbors, float* distances)
+{
+  // ivf_pq_search.cuh:901-917
+  CUVS_EXPECTS(params.internal_distance_dtype == CUDA_R_16F ||
+                 params.internal_distance_dtype == CUDA_R_32F,
+               "internal_distance_dtype must be either CUDA_R_16F or CUDA_R_32F");
+  CUVS_EXPECTS(params.lut_dtype == CUDA_R_16F || params.lut_dtype == CUDA_R_32F ||
+                 params.lut_dtype == CUDA_R_8U,
+               "lut_dtype must be CUDA_R_16F, CUDA_R_32F or CUDA_R_8U");
+  CUVS_EXPECTS(k > 0, "parameter `k` in top-k must be positive.");
+  CUVS_EXPECTS(int64_t(k) <= idx.size(),
+               "parameter `k` (%u) in top-k must not be larger that the total size of the index (%zu)",
+               k, size_t(idx.size()));
+  CUVS_EXPECTS(params.n_probes > 0,
+               "n_probes (number of clusters to probe in the search) must be positive.");
+  CUVS_EXPECTS(params.coarse_search_dtype == CUDA_R_32F,
+               "Unsupported coarse_search_dtype (only CUDA_R_32F is supported by this engine)");
+  const bool out_half = params.internal_distance_dtype == CUDA_R_16F;
+  const int lut_kind =
+    params.lut_dtype == CUDA_R_32F ? LUT_F32 : (params.lut_dtype == CUDA_R_16F ? LUT_F16 : LUT_FP8);
+  // ivf_pq_search.cuh:697-708
+  CUVS_EXPECTS(!(out_half && lut_kind == LUT_F32),
+               "Unexpected lut_dtype / internal_distance_dtype combination (%d, %d). Size of the "
+               "internal_distance_dtype should be not smaller than the size of the lut_dtype.",
+               int(params.lut_dtype), int(params.internal_distance_dtype));
+  CUVS_EXPECTS(k <= 128,
+               "k = %u: this engine keeps the top-k in registers and supports k <= 128", k);
+  if (n_queries == 0) { return; }
+  {
+    cudaPointerAttributes a{};
+    for (const void* ptr : {queries, (const void*)neighbors, (const void*)distances}) {
+      cudaError_t e = cudaPointerGetAttributes(&a, ptr);
+      if (e != cudaSuccess || a.type == cudaMemoryTypeUnregistered) {
+        cudaGetLastError();
+        fail("all pointers must be accessible from the device.");
+      }
+    }
+  }
+
+  const cudaStream_t stream = res.stream;
+  const uint32_t n_lists    = idx.n_lists();
+  const uint32_t n_probes   = std::min<uint32_t>(params.n_probes, n_lists);
+  const DistanceType metric = idx.metric();
+  const bool is_l2  = metric == DistanceType::L2Expanded || metric == DistanceType::L2SqrtExpanded;
+  const bool is_ip  = !is_l2;
+  const bool cosine = metric == DistanceType::CosineExpanded;
+  const int kpl     = kpl_for_k(k);
+  const float scale = qtype == elem_t::u8 ? 256.0f : (qtype == elem_t::i8 ? 128.0f : 1.0f);
+  CUVS_EXPECTS(uint64_t(idx.accum_sorted_sizes()[n_probes]) <= 0xFFFFFFFFull,
+               "The maximum sample size is too big.");
+
+  const scan_plan plan = plan_scan(res, idx, lut_kind, is_ip, k);
+  const uint32_t batch = std::min<uint32_t>(n_queries, std::max<uint32_t>(1, params.max_internal_batch_size));
+  const size_t n_pairs_max = size_t(batch) * n_probes;
+  CUVS_EXPECTS(n_pairs_max < (1ull << 31), "max_internal_batch_size * n_probes is too large");
+
+  // ---- workspace ----
+  ws_layout lay;
+  const size_t o_fq      = lay.add(size_t(batch) * idx.dim_ext() * 4);
+  const size_t o_rq      = lay.add(size_t(batch) * idx.rot_dim() * 4);
+  const size_t o_probes  = lay.add(n_pairs_max * 4);
+  const size_t o_chunk   = lay.add(n_pairs_max * 4);
+  const size_t o_order   = lay.add(n_pairs_max * 4);
+  const size_t o_count   = lay.add((size_t(n_lists) + 1) * 4);
+  const size_t o_kth     = lay.add(size_t(batch) * 4);
+  const size_t o_counter = lay.add(256);
+  const size_t o_keys    = lay.add(n_pairs_max * k * 8);
+  const size_t coarse_ws = coarse_workspace_bytes(batch, n_lists, n_probes);
+  const size_t o_coarse  = lay.add(coarse_ws);
+  res.ws.reserve(lay.total());
+  char* ws = res.ws.base();
+  auto* d_fq      = reinterpret_cast<float*>(ws + o_fq);
+  auto* d_rq      = reinterpret_cast<float*>(ws + o_rq);
+  auto* d_probes  = reinterpret_cast<uint32_t*>(ws + o_probes);
+  auto* d_chunk   = reinterpret_cast<uint32_t*>(ws + o_chunk);
+  auto* d_order   = reinterpret_cast<uint32_t*>(ws + o_order);
+  auto* d_count   = reinterpret_cast<uint32_t*>(ws + o_count);
+  auto* d_kth     = reinterpret_cast<uint32_t*>(ws + o_kth);
+  auto* d_counter = reinterpret_cast<uint32_t*>(ws + o_counter);
+  auto* d_keys    = reinterpret_cast<uint64_t*>(ws + o_keys);
+  void* d_coarse  = ws + o_coarse;
+
+  for (uint32_t q0 = 0; q0 < n_queries; q0 += batch) {
+    const uint32_t nq      = std::min(batch, n_queries - q0);
+    const uint32_t n_pairs = nq * n_probes;
+    const char* qptr       = static_cast<const char*>(queries) + size_t(q0) * idx.dim() * elem_size(qtype);
+
+    // 1. cast / pad / rotate
+    {
+      const size_t smem = (size_t(idx.dim()) + idx.rot_dim()) * 4;
+      const int threads = 128;
+      const int is_l2_i = is_l2, cos_i = cosine, ident = idx.rotation_is_identity();
+      switch (qtype) {
+        case elem_t::f32:
+          prep_queries_kernel<float><<<nq, threads, smem, stream>>>(
+            reinterpret_cast<const float*>(qptr), idx.dim(), idx.dim_ext(), idx.rot_dim(), is_l2_i,
+            cos_i, ident, idx.rotation_matrix(), d_fq, d_rq);
+          break;
+        case elem_t::f16:
+          prep_queries_kernel<__half><<<nq, threads, smem, stream>>>(
+            reinterpret_cast<const __half*>(qptr), idx.dim(), idx.dim_ext(), idx.rot_dim(), is_l2_i,
+            cos_i, ident, idx.rotation_matrix(), d_fq, d_rq);
+          break;
+        case elem_t::i8:
+          prep_queries_kernel<int8_t><<<nq, threads, smem, stream>>>(
+            reinterpret_cast<const int8_t*>(qptr), idx.dim(), idx.dim_ext(), idx.rot_dim(), is_l2_i,
+            cos_i, ident, idx.rotation_matrix(), d_fq, d_rq);
+          break;
+        default:
+          prep_queries_kernel<uint8_t><<<nq, threads, smem, stream>>>(
+            reinterpret_cast<const uint8_t*>(qptr), idx.dim(), idx.dim_ext(), idx.rot_dim(), is_l2_i,
+            cos_i, ident, idx.rotation_matrix(), d_fq, d_rq);
+      }
+      CUDA_TRY(cudaGetLastError());
+      res.launches++;
+    }
+
+    // 2. coarse selection: probes sorted by (score, list id)
+    select_clusters(res, idx.centers(), n_lists, idx.dim_ext(), is_l2 ? -2.0f : -1.0f, d_fq, nq,
+                    n_probes, d_probes, nullptr, d_coarse, coarse_ws);
+
+    // 3. sample offsets + counting sort of pairs by list
+    CUDA_TRY(cudaMemsetAsync(d_count, 0, (size_t(n_lists) + 1) * 4, stream));
+    chunk_and_count_kernel<<<ceildiv<uint32_t>(nq * 32, 256), 256, 0, stream>>>(
+      d_probes, idx.list_sizes(), nq, n_probes, d_chunk, d_count);
+    exclusive_scan_kernel<<<1, 1024, 0, stream>>>(d_count, n_lists);
+    scatter_pairs_kernel<<<ceildiv<uint32_t>(n_pairs, 256), 256, 0, stream>>>(d_probes, n_pairs,
+                                                                              d_count, d_order);
+    fill_u32_kernel<<<ceildiv<uint32_t>(nq, 256), 256, 0, stream>>>(d_kth, nq, kEmptyScore);
+    CUDA_TRY(cudaMemsetAsync(d_counter, 0, 4, stream));
+    CUDA_TRY(cudaGetLastError());
+    res.launches += 4;
+
+    // 4. LUT + scan + per-pair top-k
+    {
+      scan_params sp{};
+      sp.pq_centers     = idx.pq_centers();
+      sp.centers_rot    = idx.centers_rot();
+      sp.codes          = idx.codes();
+      sp.list_sizes     = idx.list_sizes();
+      sp.row_off        = idx.row_offsets();
+      sp.pq_dim         = idx.pq_dim();
+      sp.pq_len         = idx.pq_len();
+      sp.rot_dim        = idx.rot_dim();
+      sp.n_pieces       = idx.n_pieces();
+      sp.per_cluster    = idx.codebook_kind() == codebook_gen::PER_CLUSTER;
+      sp.cosine         = cosine;
+      sp.rot_q          = d_rq;
+      sp.probes         = d_probes;
+      sp.chunk_index    = d_chunk;
+      sp.pair_order     = d_order;
+      sp.n_pairs        = n_pairs;
+      sp.n_probes       = n_probes;
+      sp.k              = k;
+      sp.query_kth      = d_kth;
+      sp.out_keys       = d_keys;
+      sp.work_counter   = d_counter;
+      sp.n_groups       = plan.n_groups;
+      sp.group_threads  = plan.group_threads;
+      sp.pqc_in_smem    = plan.pqc_in_smem;
+      sp.smem_pqc_bytes = plan.pqc_bytes;
+      sp.smem_group_bytes = plan.group_bytes;
+      sp.lut_bytes      = plan.lut_bytes;
+      sp.base_bytes     = plan.base_bytes;
+      sp.merge_bytes    = plan.merge_bytes;
+      const int grid    = int(std::min<uint32_t>(uint32_t(res.sm_count),
+                                              ceildiv<uint32_t>(n_pairs, plan.n_groups)));
+      launch_scan(sp, int(idx.pq_bits()), lut_kind, out_half, is_ip, kpl, grid, plan.total_bytes,
+                  stream);
+      res.launches++;
+    }
+
+    // 5. final selection + id translation + distance post-processing
+    {
+      const int blocks = int(ceildiv<uint32_t>(nq * 32, 128));
+      int64_t* nb      = neighbors + size_t(q0) * k;
+      float* ds        = distances + size_t(q0) * k;
+      switch (kpl) {
+        case 1:
+          final_merge_kernel<1><<<blocks, 128, 0, stream>>>(d_keys, d_probes, d_chunk,
+                                                            idx.row_offsets(), idx.ids(), nq, n_probes,
+                                                            k, int(metric), scale, nb, ds);
+          break;
+        case 2:
+          final_merge_kernel<2><<<blocks, 128, 0, stream>>>(d_keys, d_probes, d_chunk,
+                                                            idx.row_offsets(), idx.ids(), nq, n_probes,
+                                                            k, int(metric), scale, nb, ds);
+          break;
+        default:
+          final_merge_kernel<4><<<blocks, 128, 0, stream>>>(d_keys, d_probes, d_chunk,
+                                                            idx.row_offsets(), idx.ids(), nq, n_probes,
+                                                            k, int(metric), scale, nb, ds);
+      }
+      CUDA_TRY(cudaGetLastError());
+      res.launches++;
+    }
+  }
+}
+
+namespace detail {
+void knn_merge_parts(raft::resources& res, const float* in_dist, const int64_t* in_ids,
+                     float* out_dist, int64_t* out_ids, uint32_t n_parts, uint32_t n_queries,
+                     uint32_t k, bool select_min)
+{
+  CUVS_EXPECTS(k > 0 && k <= 128, "knn_merge_parts supports 0 < k <= 128, got %u", k);
+  if (n_queries == 0) { return; }
+  const int blocks = int(ceildiv<uint32_t>(n_queries * 32, 128));
+  const int kpl    = kpl_for_k(k);
+  switch (kpl) {
+    case 1:
+      merge_parts_kernel<1><<<blocks, 128, 0, res.stream>>>(in_dist, in_ids, n_parts, n_queries, k,
+                                                            select_min, out_dist, out_ids);
+      break;
+    case 2:
+      merge_parts_kernel<2><<<blocks, 128, 0, res.stream>>>(in_dist, in_ids, n_parts, n_queries, k,
+                                                            select_min, out_dist, out_ids);
+      break;
+    default:
+      merge_parts_kernel<4><<<blocks, 128, 0, res.stream>>>(in_dist, in_ids, n_parts, n_queries, k,
+                                                            select_min, out_dist, out_ids);
+  }
+  CUDA_TRY(cudaGetLastError());
+  res.launches++;
+}
+}  // namespace detail
+
+}  // namespace cuvs::neighbors::ivf_pq

