@@ -61,6 +61,13 @@ class IndexStruct(C.Structure):
     _fields_ = [("addr", C.c_size_t), ("dtype", DLDataType)]
 
 
+class SearchStats(C.Structure):
+    _fields_ = [("prep_ms", C.c_double), ("coarse_ms", C.c_double), ("sort_ms", C.c_double),
+                ("scan_ms", C.c_double), ("merge_ms", C.c_double), ("batches", C.c_uint64),
+                ("pairs", C.c_uint64), ("scan_groups", C.c_uint64), ("unique_groups", C.c_uint64),
+                ("launches", C.c_uint64)]
+
+
 _P = C.POINTER
 
 # every entry point declared in include/*.h: name -> argument types
@@ -105,6 +112,11 @@ SIGNATURES = {
     "cuvsIvfPqSerialize": [C.c_size_t, C.c_char_p, _P(IndexStruct)],
     "cuvsIvfPqDeserialize": [C.c_size_t, C.c_char_p, _P(IndexStruct)],
     "cuvsIvfPqExtend": [C.c_size_t, _P(DLManagedTensor), _P(DLManagedTensor), _P(IndexStruct)],
+    "cuvsMultiGpuIvfPqDistributeShard": [C.c_size_t, C.c_char_p, C.c_int, C.c_int, _P(IndexStruct)],
+    "cuvsMultiGpuIvfPqMergeParts": [C.c_size_t, _P(DLManagedTensor), _P(DLManagedTensor),
+                                    _P(DLManagedTensor), _P(DLManagedTensor), C.c_bool],
+    "cuvsB200StatsEnable": [C.c_size_t, C.c_bool],
+    "cuvsB200StatsGet": [C.c_size_t, _P(SearchStats), C.c_bool],
     "cuvsIvfPqTransform": [C.c_size_t, _P(IndexStruct), _P(DLManagedTensor), _P(DLManagedTensor),
                            _P(DLManagedTensor)],
 }

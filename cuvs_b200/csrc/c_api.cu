@@ -3,7 +3,9 @@
 // Mirrors c/src/core/c_api.cpp and c/src/neighbors/ivf_pq.cpp of the reference: every entry point
 // runs inside translate_exceptions (c/src/core/exceptions.hpp:17-33), tensors are validated the
 // way from_dlpack does (c/src/core/detail/interop.hpp:75-139) and dispatched on their dtype.
+#include "../../include/cuvs_b200_ext.h"
 #include "../../include/cuvs_ivf_pq.h"
+#include "../../include/cuvs_mg_ivf_pq.h"
 
 #include "ivf_pq.hpp"
 
@@ -559,5 +561,83 @@ extern "C" cuvsError_t cuvsIvfPqDeserialize(cuvsResources_t res, const char* fil
     }
     delete reinterpret_cast<index_t*>(index->addr);
     index->addr = reinterpret_cast<uintptr_t>(ix);
+  });
+}
+
+// ------------------------------------------------------------------------------------------------
+// one-process-per-GPU list sharding
+// ------------------------------------------------------------------------------------------------
+extern "C" cuvsError_t cuvsMultiGpuIvfPqDistributeShard(cuvsResources_t res, const char* filename,
+                                                        int rank, int n_ranks, cuvsIvfPqIndex_t index)
+{
+  return translate_exceptions([=] {
+    CUVS_EXPECTS(index != nullptr && filename != nullptr, "null argument");
+    auto* ix = new index_t();
+    try {
+      ivf_pq::deserialize(*res_of(res), std::string(filename), ix, rank, n_ranks);
+    } catch (...) {
+      delete ix;
+      throw;
+    }
+    delete reinterpret_cast<index_t*>(index->addr);
+    index->addr = reinterpret_cast<uintptr_t>(ix);
+  });
+}
+
+extern "C" cuvsError_t cuvsMultiGpuIvfPqMergeParts(cuvsResources_t res, DLManagedTensor* part_distances,
+                                                   DLManagedTensor* part_neighbors,
+                                                   DLManagedTensor* distances, DLManagedTensor* neighbors,
+                                                   bool select_min)
+{
+  return translate_exceptions([=] {
+    auto* pd = static_cast<float*>(checked_data(part_distances, kDLFloat, 32, 3, true, "part_distances"));
+    auto* pn = static_cast<int64_t*>(checked_data(part_neighbors, kDLInt, 64, 3, true, "part_neighbors"));
+    auto* od = static_cast<float*>(checked_data(distances, kDLFloat, 32, 2, true, "distances"));
+    auto* on = static_cast<int64_t*>(checked_data(neighbors, kDLInt, 64, 2, true, "neighbors"));
+    const int64_t* ps = part_distances->dl_tensor.shape;
+    const int64_t* ns = part_neighbors->dl_tensor.shape;
+    CUVS_EXPECTS(ps[0] == ns[0] && ps[1] == ns[1] && ps[2] == ns[2],
+                 "part_distances and part_neighbors must have the same shape");
+    for (auto* t : {distances, neighbors}) {
+      CUVS_EXPECTS(t->dl_tensor.shape[0] == ps[1] && t->dl_tensor.shape[1] == ps[2],
+                   "outputs must be [n_queries, k]");
+    }
+    ivf_pq::detail::knn_merge_parts(*res_of(res), pd, pn, od, on, uint32_t(ps[0]), uint32_t(ps[1]),
+                                    uint32_t(ps[2]), select_min);
+  });
+}
+
+// ------------------------------------------------------------------------------------------------
+// instrumentation
+// ------------------------------------------------------------------------------------------------
+extern "C" cuvsError_t cuvsB200StatsEnable(cuvsResources_t res, bool enable)
+{
+  return translate_exceptions([=] { res_of(res)->stats_enable(enable); });
+}
+
+extern "C" cuvsError_t cuvsB200StatsGet(cuvsResources_t res, cuvsB200SearchStats* out, bool reset)
+{
+  return translate_exceptions([=] {
+    auto* r = res_of(res);
+    CUVS_EXPECTS(out != nullptr, "null output");
+    r->stats_resolve();
+    unsigned long long h[2] = {0, 0};
+    if (r->d_stats) { CUDA_TRY(cudaMemcpy(h, r->d_stats, 16, cudaMemcpyDeviceToHost)); }
+    out->prep_ms       = r->stage_ms[0];
+    out->coarse_ms     = r->stage_ms[1];
+    out->sort_ms       = r->stage_ms[2];
+    out->scan_ms       = r->stage_ms[3];
+    out->merge_ms      = r->stage_ms[4];
+    out->batches       = r->stat_batches;
+    out->pairs         = r->stat_pairs;
+    out->scan_groups   = h[0];
+    out->unique_groups = h[1];
+    out->launches      = r->launches;
+    if (reset) {
+      for (auto& v : r->stage_ms) { v = 0; }
+      r->stat_batches = 0;
+      r->stat_pairs   = 0;
+      if (r->d_stats) { CUDA_TRY(cudaMemset(r->d_stats, 0, 16)); }
+    }
   });
 }

@@ -113,6 +113,20 @@ struct resources {
   // counters read by the benchmark ("how many kernels of ours ran")
   uint64_t launches = 0;
 
+  // Optional stage timing (off by default): five events per internal batch, resolved on demand.
+  struct stage_events {
+    cudaEvent_t e[6];
+  };
+  bool stats_enabled = false;
+  std::vector<stage_events> pending;
+  double stage_ms[5]      = {0, 0, 0, 0, 0};
+  uint64_t stat_batches   = 0;
+  uint64_t stat_pairs     = 0;
+  unsigned long long* d_stats = nullptr;  // [2] device counters: scan groups, unique groups
+  void stats_enable(bool on);
+  void stats_mark(stage_events& ev, int i);
+  void stats_resolve();
+
   resources();
   ~resources();
   resources(const resources&)            = delete;

@@ -15,7 +15,43 @@ resources::resources()
 
 resources::~resources()
 {
+  for (auto& ev : pending) {
+    for (auto& e : ev.e) { cudaEventDestroy(e); }
+  }
+  if (d_stats) { cudaFree(d_stats); }
   if (pinned) { cudaFreeHost(pinned); }
+}
+
+void resources::stats_enable(bool on)
+{
+  if (on && !d_stats) {
+    CUDA_TRY(cudaMalloc(&d_stats, 16));
+    CUDA_TRY(cudaMemset(d_stats, 0, 16));
+  }
+  stats_enabled = on;
+}
+
+void resources::stats_mark(stage_events& ev, int i)
+{
+  if (i == 0) {
+    for (auto& e : ev.e) { CUDA_TRY(cudaEventCreate(&e)); }
+  }
+  CUDA_TRY(cudaEventRecord(ev.e[i], stream));
+}
+
+void resources::stats_resolve()
+{
+  CUDA_TRY(cudaStreamSynchronize(stream));
+  for (auto& ev : pending) {
+    for (int i = 0; i < 5; i++) {
+      float ms = 0.0f;
+      CUDA_TRY(cudaEventElapsedTime(&ms, ev.e[i], ev.e[i + 1]));
+      stage_ms[i] += ms;
+    }
+    for (auto& e : ev.e) { cudaEventDestroy(e); }
+    stat_batches++;
+  }
+  pending.clear();
 }
 
 }  // namespace cuvs_b200

@@ -187,6 +187,29 @@ __global__ void exclusive_scan_kernel(uint32_t* __restrict__ data, uint32_t n)
   }
 }
 
+// Counters for the benchmark: sum over pairs, and over distinct probed lists, of ceil(size / 32).
+__global__ void scan_stats_kernel(const uint32_t* __restrict__ list_count,
+                                  const uint32_t* __restrict__ list_sizes, uint32_t n_lists,
+                                  unsigned long long* __restrict__ stats)
+{
+  const uint32_t l = blockIdx.x * blockDim.x + threadIdx.x;
+  unsigned long long a = 0, b = 0;
+  if (l < n_lists && list_count[l] > 0) {
+    const unsigned long long g = (list_sizes[l] + 31u) >> 5;
+    a = g * list_count[l];
+    b = g;
+  }
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) {
+    a += __shfl_xor_sync(kFullMask, a, d);
+    b += __shfl_xor_sync(kFullMask, b, d);
+  }
+  if ((threadIdx.x & 31) == 0 && a) {
+    atomicAdd(stats, a);
+    atomicAdd(stats + 1, b);
+  }
+}
+
 __global__ void scatter_pairs_kernel(const uint32_t* __restrict__ probes, uint32_t n_pairs,
                                      uint32_t* __restrict__ cursor, uint32_t* __restrict__ pair_order)
 {
@@ -455,6 +478,10 @@ void search_any(raft::resources& res, const search_params& params, const index<i
     const uint32_t n_pairs = nq * n_probes;
     const char* qptr       = static_cast<const char*>(queries) + size_t(q0) * idx.dim() * elem_size(qtype);
 
+    raft::resources::stage_events ev{};
+    const bool stats = res.stats_enabled;
+    if (stats) { res.stats_mark(ev, 0); }
+
     // 1. cast / pad / rotate
     {
       const size_t smem = (size_t(idx.dim()) + idx.rot_dim()) * 4;
@@ -485,14 +512,21 @@ void search_any(raft::resources& res, const search_params& params, const index<i
       res.launches++;
     }
 
+    if (stats) { res.stats_mark(ev, 1); }
     // 2. coarse selection: probes sorted by (score, list id)
     select_clusters(res, idx.centers(), n_lists, idx.dim_ext(), is_l2 ? -2.0f : -1.0f, d_fq, nq,
                     n_probes, d_probes, nullptr, d_coarse, coarse_ws);
 
+    if (stats) { res.stats_mark(ev, 2); }
     // 3. sample offsets + counting sort of pairs by list
     CUDA_TRY(cudaMemsetAsync(d_count, 0, (size_t(n_lists) + 1) * 4, stream));
     chunk_and_count_kernel<<<ceildiv<uint32_t>(nq * 32, 256), 256, 0, stream>>>(
       d_probes, idx.list_sizes(), nq, n_probes, d_chunk, d_count);
+    if (stats) {
+      scan_stats_kernel<<<ceildiv<uint32_t>(n_lists, 256), 256, 0, stream>>>(d_count, idx.list_sizes(),
+                                                                              n_lists, res.d_stats);
+      res.stat_pairs += n_pairs;
+    }
     exclusive_scan_kernel<<<1, 1024, 0, stream>>>(d_count, n_lists);
     scatter_pairs_kernel<<<ceildiv<uint32_t>(n_pairs, 256), 256, 0, stream>>>(d_probes, n_pairs,
                                                                               d_count, d_order);
@@ -501,6 +535,7 @@ void search_any(raft::resources& res, const search_params& params, const index<i
     CUDA_TRY(cudaGetLastError());
     res.launches += 4;
 
+    if (stats) { res.stats_mark(ev, 3); }
     // 4. LUT + scan + per-pair top-k
     {
       scan_params sp{};
@@ -540,6 +575,7 @@ void search_any(raft::resources& res, const search_params& params, const index<i
       res.launches++;
     }
 
+    if (stats) { res.stats_mark(ev, 4); }
     // 5. final selection + id translation + distance post-processing
     {
       const int blocks = int(ceildiv<uint32_t>(nq * 32, 128));
@@ -563,6 +599,10 @@ void search_any(raft::resources& res, const search_params& params, const index<i
       }
       CUDA_TRY(cudaGetLastError());
       res.launches++;
+    }
+    if (stats) {
+      res.stats_mark(ev, 5);
+      res.pending.push_back(ev);
     }
   }
 }

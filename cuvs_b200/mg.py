@@ -1,0 +1,90 @@
+"""List-sharded multi-GPU IVF-PQ search, one process per GPU over ``torch.distributed``.
+
+Every rank holds the global coarse model and the inverted lists it owns (list ``l`` belongs to rank
+``l % n_ranks``).  A search runs the ordinary single-GPU search on every rank for the whole query
+batch -- the probes chosen are identical on every rank, a rank scans only the ones it owns -- then
+all-gathers the per-rank top-k (``n_queries * k * 12`` bytes per rank, ids already global) and
+merges them on the GPU.  The merged result equals the single-GPU search on the unsharded index.
+
+Reference behaviour this replaces: sharded search with merge in
+cpp/src/neighbors/mg/snmg.cuh:249-561 (one process, one OpenMP thread per GPU, ncclSend/ncclRecv to
+the root, knn_merge_parts); index distribution in snmg.cuh:48-58.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+import torch.distributed as dist
+
+from . import _lib as L
+from . import ivf_pq
+from .common import DLTensorRef, Resources, default_resources
+
+
+def shard_of_list(label: int, n_ranks: int) -> int:
+    """Owner rank of an inverted list (same rule as the C++ loader)."""
+    return int(label) % int(n_ranks)
+
+
+def _rank_world(group=None):
+    if dist.is_available() and dist.is_initialized():
+        return dist.get_rank(group), dist.get_world_size(group)
+    return 0, 1
+
+
+def load_shard(filename: str, rank: int | None = None, n_ranks: int | None = None,
+               resources: Resources | None = None, group=None) -> ivf_pq.Index:
+    """Load this rank's shard of a single-GPU index file (lists owned by other ranks are skipped)."""
+    r, w = _rank_world(group)
+    rank = r if rank is None else rank
+    n_ranks = w if n_ranks is None else n_ranks
+    res = resources or default_resources()
+    res.use_current_stream()
+    idx = ivf_pq.Index()
+    L.check(L.load().cuvsMultiGpuIvfPqDistributeShard(res.handle, filename.encode(), C.c_int(rank),
+                                                      C.c_int(n_ranks), idx._h))
+    return idx
+
+
+def gather_parts(local_d: torch.Tensor, local_i: torch.Tensor, group=None):
+    """All-gather the per-rank results: returns ([R, n, k] distances, [R, n, k] ids)."""
+    _, w = _rank_world(group)
+    if w == 1:
+        return local_d.unsqueeze(0), local_i.unsqueeze(0)
+    part_d = torch.empty((w,) + tuple(local_d.shape), dtype=local_d.dtype, device=local_d.device)
+    part_i = torch.empty((w,) + tuple(local_i.shape), dtype=local_i.dtype, device=local_i.device)
+    dist.all_gather_into_tensor(part_d, local_d.contiguous(), group=group)
+    dist.all_gather_into_tensor(part_i, local_i.contiguous(), group=group)
+    return part_d, part_i
+
+
+def merge_parts(part_d: torch.Tensor, part_i: torch.Tensor, select_min: bool = True,
+                resources: Resources | None = None, sync: bool = True):
+    """Merge [R, n, k] per-part results into [n, k] on the GPU (cuvsMultiGpuIvfPqMergeParts)."""
+    res = resources or default_resources()
+    res.use_current_stream()
+    _, n, k = part_d.shape
+    out_d = torch.empty((n, k), dtype=torch.float32, device=part_d.device)
+    out_i = torch.empty((n, k), dtype=torch.int64, device=part_d.device)
+    a, b, c, d = (DLTensorRef(t) for t in (part_d.contiguous(), part_i.contiguous(), out_d, out_i))
+    L.check(L.load().cuvsMultiGpuIvfPqMergeParts(res.handle, a.ref(), b.ref(), c.ref(), d.ref(),
+                                                 C.c_bool(select_min)))
+    if sync:
+        res.sync()
+    return out_d, out_i
+
+
+def search(search_params: ivf_pq.SearchParams, shard: ivf_pq.Index, queries, k: int,
+           select_min: bool = True, group=None, resources: Resources | None = None,
+           sync: bool = True):
+    """Sharded search: every rank passes the same queries and gets the same merged result."""
+    res = resources or default_resources()
+    d, i = ivf_pq.search(search_params, shard, queries, k, resources=res, sync=False)
+    _, w = _rank_world(group)
+    if w == 1:
+        if sync:
+            res.sync()
+        return d, i
+    part_d, part_i = gather_parts(d, i, group)
+    return merge_parts(part_d, part_i, select_min, res, sync)

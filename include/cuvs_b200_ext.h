@@ -1,0 +1,39 @@
+/*
+ * Instrumentation of the IVF-PQ search path.  These entry points have no counterpart in the
+ * reference; they exist so that a benchmark can report per-stage device times and the bytes the
+ * code scan logically processes without guessing.  Disabled by default; when enabled, search
+ * records CUDA events around its stages on the handle's stream and accumulates two counters on
+ * the device.
+ */
+#ifndef CUVS_B200_EXT_H_
+#define CUVS_B200_EXT_H_
+
+#include "cuvs_core_c_api.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct {
+  double prep_ms;    /* query cast / pad / rotate */
+  double coarse_ms;  /* probe selection */
+  double sort_ms;    /* sample offsets + ordering of (query, probe) pairs by list */
+  double scan_ms;    /* look-up table build + code scan + per-pair top-k (one kernel per batch) */
+  double merge_ms;   /* final selection, id translation, distance post-processing */
+  uint64_t batches;        /* internal batches = launches of the scan kernel */
+  uint64_t pairs;          /* (query, probe) pairs scanned */
+  uint64_t scan_groups;    /* sum over pairs of ceil(list size / 32) */
+  uint64_t unique_groups;  /* sum over distinct probed lists, per batch, of ceil(list size / 32) */
+  uint64_t launches;       /* kernels of this library launched through the handle since creation */
+} cuvsB200SearchStats;
+
+/* No counterpart in the reference: switch stage timing and counters on or off for a handle. */
+CUVS_EXPORT cuvsError_t cuvsB200StatsEnable(cuvsResources_t res, bool enable);
+/* No counterpart in the reference: synchronise the stream, return the accumulated figures and
+ * optionally reset them. */
+CUVS_EXPORT cuvsError_t cuvsB200StatsGet(cuvsResources_t res, cuvsB200SearchStats* out, bool reset);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,48 @@
+/*
+ * List-sharded multi-GPU IVF-PQ, one process per GPU.
+ *
+ * The reference's multi-GPU layer (c/include/cuvs/neighbors/mg_ivf_pq.h, cpp/src/neighbors/mg/snmg.cuh)
+ * drives all GPUs from one process with one OpenMP thread per rank.  Here every rank is its own
+ * process holding an ordinary cuvsIvfPqIndex_t that contains the global coarse model and the
+ * inverted lists this rank owns (list l belongs to rank l % n_ranks; the others are empty).  Every
+ * rank runs the ordinary cuvsIvfPqSearch on the whole query batch -- probe selection is global and
+ * identical everywhere, a rank only scans the probes it owns -- and the per-rank top-k lists, which
+ * already carry global ids, are exchanged by the host framework (NCCL all-gather) and merged with
+ * cuvsMultiGpuIvfPqMergeParts.  The union of the ranks' candidates is exactly the single-GPU
+ * candidate set, so the merged result equals the single-GPU search.
+ */
+#ifndef CUVS_B200_MG_IVF_PQ_H_
+#define CUVS_B200_MG_IVF_PQ_H_
+
+#include "cuvs_ivf_pq.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Stands in for cuvsMultiGpuIvfPqDistribute (c/include/cuvs/neighbors/mg_ivf_pq.h:266;
+ * cpp/src/neighbors/mg/snmg.cuh:48-58) in a one-process-per-GPU deployment: loads a single-GPU
+ * index file (format version 4) and keeps the payload of the lists owned by `rank` only; the
+ * payload of the other lists is skipped in the file, never read. */
+CUVS_EXPORT cuvsError_t cuvsMultiGpuIvfPqDistributeShard(cuvsResources_t res,
+                                                         const char* filename,
+                                                         int rank,
+                                                         int n_ranks,
+                                                         cuvsIvfPqIndex_t index);
+
+/* Stands in for the merge step of the sharded search (cpp/src/neighbors/mg/snmg.cuh:349-392 calling
+ * knn_merge_parts, cpp/src/neighbors/detail/knn_merge_parts.cuh:24-170): part_distances f32 and
+ * part_neighbors i64 are [n_parts, n_queries, k] device tensors; distances / neighbors are
+ * [n_queries, k].  select_min = true keeps the smallest distances (L2, cosine), false the largest
+ * (inner product).  Entries whose neighbour is INT64_MAX are ignored. */
+CUVS_EXPORT cuvsError_t cuvsMultiGpuIvfPqMergeParts(cuvsResources_t res,
+                                                    DLManagedTensor* part_distances,
+                                                    DLManagedTensor* part_neighbors,
+                                                    DLManagedTensor* distances,
+                                                    DLManagedTensor* neighbors,
+                                                    bool select_min);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

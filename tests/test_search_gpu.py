@@ -236,6 +236,9 @@ def test_truncated_file_is_rejected(ivf, small_l2, tmp_path):
         with pytest.raises(CuvsError):
             ivf.load(p)
     p = str(tmp_path / "badver.ivfpq")
-    open(p, "wb").write(blob[:64] + bytes([5]) + blob[65:])
+    import struct
+    off = 10 + struct.unpack("<H", blob[8:10])[0]      # payload of the first record (the version)
+    assert blob[off] == 4
+    open(p, "wb").write(blob[:off] + bytes([5]) + blob[off + 1:])
     with pytest.raises(CuvsError, match="serialization version mismatch"):
         ivf.load(p)
