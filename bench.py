@@ -271,6 +271,7 @@ def run_ours(args):
     if args.rows:
         wl.update(n_rows=args.rows, n_lists=max(64, args.rows // 200),
                   n_queries=min(wl["n_queries"], max(100, args.rows // 100)))
+    probes = tuple(int(p) for p in args.probes.split(",")) if args.probes else wl["probes"]
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -331,7 +332,7 @@ def run_ours(args):
 
     # ---- recall / QPS sweep over n_probes ----
     sweep = []
-    for p in wl["probes"]:
+    for p in probes:
         sp = make_sp(p)
         d, i = one_search(sp)
         torch.cuda.synchronize()
@@ -383,8 +384,11 @@ def run_ours(args):
         i_host.copy_(i, non_blocking=True)
         d_host.copy_(d, non_blocking=True)
 
-    ms_e2e = timed(e2e_step, args.steps, args.warmup)
-    e2e_rec = recall_at_k(i_host.to(device), truth)
+    if args.no_e2e:
+        ms_e2e, e2e_rec = float("nan"), float("nan")
+    else:
+        ms_e2e = timed(e2e_step, args.steps, args.warmup)
+        e2e_rec = recall_at_k(i_host.to(device), truth)
     clocks = sampler.stop() if rank == 0 else None
 
     if rank != 0:
@@ -493,6 +497,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--rows", type=int, default=0, help="shrink the dataset (testing only)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--probes", default="", help="comma-separated n_probes to sweep (default: the workload's)")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end leg (profiling runs)")
     args = ap.parse_args()
     args.warmup = max(3, args.warmup)
     if args.impl == "reference":
