@@ -52,11 +52,13 @@ def gather_parts(local_d: torch.Tensor, local_i: torch.Tensor, group=None):
     _, w = _rank_world(group)
     if w == 1:
         return local_d.unsqueeze(0), local_i.unsqueeze(0)
-    part_d = torch.empty((w,) + tuple(local_d.shape), dtype=local_d.dtype, device=local_d.device)
-    part_i = torch.empty((w,) + tuple(local_i.shape), dtype=local_i.dtype, device=local_i.device)
+    n, k = local_d.shape
+    # concatenated along dim 0 (the form both NCCL and gloo accept), viewed as [R, n, k]
+    part_d = torch.empty((w * n, k), dtype=local_d.dtype, device=local_d.device)
+    part_i = torch.empty((w * n, k), dtype=local_i.dtype, device=local_i.device)
     dist.all_gather_into_tensor(part_d, local_d.contiguous(), group=group)
     dist.all_gather_into_tensor(part_i, local_i.contiguous(), group=group)
-    return part_d, part_i
+    return part_d.view(w, n, k), part_i.view(w, n, k)
 
 
 def merge_parts(part_d: torch.Tensor, part_i: torch.Tensor, select_min: bool = True,

@@ -242,3 +242,29 @@ def test_truncated_file_is_rejected(ivf, small_l2, tmp_path):
     open(p, "wb").write(blob[:off] + bytes([5]) + blob[off + 1:])
     with pytest.raises(CuvsError, match="serialization version mismatch"):
         ivf.load(p)
+
+
+def test_list_sharded_search_merges_to_the_unsharded_result(ivf, oracle_mod, small_l2):
+    """Both shards of a 2-way list sharding on one GPU: shard loader + merge kernel."""
+    from cuvs_b200 import mg
+    q = torch.from_numpy(small_l2["q"]).cuda()
+    full = ivf.load(small_l2["path"])
+    sp = ivf.SearchParams(n_probes=8)
+    d_full, i_full = ivf.search(sp, full, q, 10)
+    parts = []
+    sizes = []
+    for r in range(2):
+        shard = mg.load_shard(small_l2["path"], r, 2)
+        sizes.append(shard.list_sizes.cpu().numpy())
+        parts.append(ivf.search(sp, shard, q, 10))
+    ref_sizes = small_l2["ix"].list_sizes
+    assert (sizes[0][0::2] == ref_sizes[0::2]).all() and (sizes[0][1::2] == 0).all()
+    assert (sizes[1][1::2] == ref_sizes[1::2]).all() and (sizes[1][0::2] == 0).all()
+    pd = torch.stack([p[0] for p in parts])
+    pi = torch.stack([p[1] for p in parts])
+    d, i = mg.merge_parts(pd, pi, True)
+    assert (i == i_full).all()
+    assert (d.view(torch.int32) == d_full.view(torch.int32)).all()
+    # select_max on negated distances gives the same ids (the inner-product direction)
+    d2, i2 = mg.merge_parts(-pd, pi, False)
+    assert (i2 == i_full).all()
