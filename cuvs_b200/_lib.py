@@ -117,6 +117,7 @@ SIGNATURES = {
                                     _P(DLManagedTensor), _P(DLManagedTensor), C.c_bool],
     "cuvsB200StatsEnable": [C.c_size_t, C.c_bool],
     "cuvsB200StatsGet": [C.c_size_t, _P(SearchStats), C.c_bool],
+    "cuvsIvfPqPredictNoAlloc": [C.c_size_t, _P(IndexStruct), _P(DLManagedTensor), _P(DLManagedTensor)],
     "cuvsIvfPqTransform": [C.c_size_t, _P(IndexStruct), _P(DLManagedTensor), _P(DLManagedTensor),
                            _P(DLManagedTensor)],
 }

@@ -169,6 +169,19 @@ CUVS_EXPORT cuvsError_t cuvsIvfPqTransform(cuvsResources_t res,
                                            DLManagedTensor* output_labels,
                                            DLManagedTensor* output_dataset);
 
+/* No counterpart in the reference.  Nearest-list labels (u32 [n]) of up to 65,536 vectors
+ * (f32/f16/i8/u8 [n, dim], device-accessible) computed WITHOUT any allocation: for callers that may
+ * not call cudaMalloc while serving (all device memory pre-claimed by a framework allocator, a
+ * thread that must avoid cudaMalloc's driver lock and implicit sync, a sandboxed plug-in).  The
+ * kernel's scratch is a fixed 512 KiB __device__ array inside the library, shared by all calls:
+ * larger batches are rejected, calls must not overlap on the GPU, and the first call on a device
+ * (which resolves the array's address) should precede any stream capture.  Labels equal those of
+ * cuvsIvfPqTransform.  CosineExpanded indexes are not supported. */
+CUVS_EXPORT cuvsError_t cuvsIvfPqPredictNoAlloc(cuvsResources_t res,
+                                                cuvsIvfPqIndex_t index,
+                                                DLManagedTensor* vectors,
+                                                DLManagedTensor* labels);
+
 #ifdef __cplusplus
 }
 #endif
