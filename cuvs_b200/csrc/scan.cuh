@@ -123,6 +123,128 @@ __device__ __forceinline__ void group_bar(int id, int n)
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(n) : "memory");
 }
 
+// ---- explicit shared-space accesses (32-bit addresses, immediate offsets) ----------------------
+__device__ __forceinline__ uint32_t smem_addr(const void* p)
+{
+  return uint32_t(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ uint64_t lds_b64(uint32_t a)
+{
+  uint64_t v;
+  asm volatile("ld.shared.b64 %0, [%1];" : "=l"(v) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ float lds_f32(uint32_t a)
+{
+  float v;
+  asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ uint32_t lds_u16(uint32_t a)
+{
+  uint16_t v;
+  asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ uint32_t lds_u8(uint32_t a)
+{
+  uint32_t v;
+  asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ void sts_b64(uint32_t a, uint64_t v)
+{
+  asm volatile("st.shared.b64 [%0], %1;" ::"r"(a), "l"(v) : "memory");
+}
+__device__ __forceinline__ void sts_b32(uint32_t a, uint32_t v)
+{
+  asm volatile("st.shared.b32 [%0], %1;" ::"r"(a), "r"(v) : "memory");
+}
+__device__ __forceinline__ void sts_b16(uint32_t a, uint32_t v)
+{
+  asm volatile("st.shared.b16 [%0], %1;" ::"r"(a), "h"(uint16_t(v)) : "memory");
+}
+__device__ __forceinline__ uint64_t dup2(float x)
+{
+  uint64_t v;
+  asm("mov.b64 %0, {%1, %1};" : "=l"(v) : "f"(x));
+  return v;
+}
+
+// LUT of one pair from a codebook resident in shared memory.  A thread owns one pair of adjacent
+// codebook entries (b, b+1) and walks the subspaces with a fixed stride, so all addresses advance
+// by constants; LEN > 0 fixes pq_len at compile time (loads first, then the FMA chain).
+template <int PqBits, int LutKind, bool IsIP, int LEN>
+__device__ __forceinline__ void build_lut_smem(uint32_t pqc_a, uint32_t base_a, uint32_t lut_a,
+                                               uint32_t pq_dim, uint32_t len_rt, uint32_t gt,
+                                               uint32_t gthreads)
+{
+  constexpr uint32_t kBook   = 1u << PqBits;
+  constexpr uint32_t kPairs  = kBook / 2;
+  constexpr uint32_t kLutB   = LutKind == LUT_F32 ? 8u : (LutKind == LUT_F16 ? 4u : 2u);  // per pair
+  constexpr uint32_t kBaseB  = IsIP ? 8u : 4u;
+  const uint32_t len      = LEN > 0 ? uint32_t(LEN) : len_rt;
+  const uint32_t t        = gt % kPairs;
+  const uint32_t j_first  = gt / kPairs;
+  const uint32_t j_stride = gthreads / kPairs;
+  uint32_t cb             = pqc_a + (j_first * len * kBook + 2u * t) * 4u;
+  uint32_t bd             = base_a + j_first * len * kBaseB;
+  uint32_t out            = lut_a + (j_first * kPairs + t) * kLutB;
+  const uint32_t cb_step  = j_stride * len * kBook * 4u;
+  const uint32_t bd_step  = j_stride * len * kBaseB;
+  const uint32_t out_step = j_stride * kPairs * kLutB;
+  for (uint32_t j = j_first; j < pq_dim; j += j_stride) {
+    uint64_t score = 0ull;  // (+0.0f, +0.0f)
+    if constexpr (LEN > 0) {
+      uint64_t pq2[LEN];
+      uint64_t bv[LEN];
+#pragma unroll
+      for (int kk = 0; kk < LEN; kk++) {
+        pq2[kk] = lds_b64(cb + uint32_t(kk) * kBook * 4u);
+        if constexpr (!IsIP) {
+          bv[kk] = dup2(lds_f32(bd + uint32_t(kk) * 4u));
+        } else {
+          bv[kk] = lds_b64(bd + uint32_t(kk) * 8u);
+        }
+      }
+#pragma unroll
+      for (int kk = 0; kk < LEN; kk++) {
+        if constexpr (!IsIP) {
+          const uint64_t dif = sub2(bv[kk], pq2[kk]);
+          score              = fma2(dif, dif, score);
+        } else {
+          const float q = lo2(bv[kk]), y = hi2(bv[kk]);
+          score         = sub2(score, dup2(y));
+          score         = fma2(dup2(-q), pq2[kk], score);
+        }
+      }
+    } else {
+      for (uint32_t kk = 0; kk < len; kk++) {
+        const uint64_t pq2 = lds_b64(cb + kk * kBook * 4u);
+        if constexpr (!IsIP) {
+          const uint64_t dif = sub2(dup2(lds_f32(bd + kk * 4u)), pq2);
+          score              = fma2(dif, dif, score);
+        } else {
+          const uint64_t qy = lds_b64(bd + kk * 8u);
+          score             = sub2(score, dup2(hi2(qy)));
+          score             = fma2(dup2(-lo2(qy)), pq2, score);
+        }
+      }
+    }
+    if constexpr (LutKind == LUT_F32) {
+      sts_b64(out, score);
+    } else if constexpr (LutKind == LUT_F16) {
+      const __half2 h = __floats2half2_rn(lo2(score), hi2(score));
+      sts_b32(out, *reinterpret_cast<const uint32_t*>(&h));
+    } else {
+      sts_b16(out, uint32_t(fp8_encode<IsIP>(lo2(score))) | (uint32_t(fp8_encode<IsIP>(hi2(score))) << 8));
+    }
+    cb += cb_step;
+    bd += bd_step;
+    out += out_step;
+  }
+}
+
 // One looked-up entry added to the running score, in the internal distance type.
 template <int LutKind, bool OutHalf, bool IsIP>
 struct accum {
@@ -134,21 +256,22 @@ struct accum {
     f = 0.0f;
     h = __ushort_as_half(0);
   }
-  __device__ __forceinline__ void add(const lut_t* row, uint32_t code)
+  // `entry` = shared-space byte address of lut[row][code]
+  __device__ __forceinline__ void add(uint32_t entry)
   {
     if constexpr (!OutHalf) {
       if constexpr (LutKind == LUT_F32) {
-        f += row[code];
+        f += lds_f32(entry);
       } else if constexpr (LutKind == LUT_F16) {
-        f += __half2float(row[code]);
+        f += __half2float(__ushort_as_half(static_cast<unsigned short>(lds_u16(entry))));
       } else {
-        f += fp8_to_float<IsIP>(row[code]);
+        f += fp8_to_float<IsIP>(lds_u8(entry));
       }
     } else {
       if constexpr (LutKind == LUT_F16) {
-        h = __hadd(h, row[code]);
+        h = __hadd(h, __ushort_as_half(static_cast<unsigned short>(lds_u16(entry))));
       } else {
-        h = __hadd(h, fp8_to_half<IsIP>(row[code]));
+        h = __hadd(h, fp8_to_half<IsIP>(lds_u8(entry)));
       }
     }
   }
@@ -163,20 +286,19 @@ struct accum {
   }
 };
 
-// Codes of one 16-byte piece -> LUT lookups.  `n_valid` = codes used in this piece.
+// Codes of one 16-byte piece -> LUT lookups.  `row_a` = shared-space address of the LUT row of the
+// piece's first subspace; `n_valid` = codes used in this piece.
 template <int PqBits, int LutKind, bool OutHalf, bool IsIP, bool Full>
 __device__ __forceinline__ void score_piece(accum<LutKind, OutHalf, IsIP>& acc, const uint4& v,
-                                            const typename lut_elem<LutKind>::type* lut_row,
-                                            uint32_t n_valid)
+                                            uint32_t row_a, uint32_t n_valid)
 {
   constexpr uint32_t kBook = 1u << PqBits;
   constexpr uint32_t kMask = kBook - 1u;
   constexpr int kPerPiece  = 128 / PqBits;
+  constexpr uint32_t kElem = LutKind == LUT_F32 ? 4u : (LutKind == LUT_F16 ? 2u : 1u);
   const uint32_t w[4]      = {v.x, v.y, v.z, v.w};
 #pragma unroll
   for (int c = 0; c < kPerPiece; c++) {
-    constexpr int dummy = 0;
-    (void)dummy;
     const int bit  = c * PqBits;
     const int word = bit >> 5;
     const int sh   = bit & 31;
@@ -186,7 +308,7 @@ __device__ __forceinline__ void score_piece(accum<LutKind, OutHalf, IsIP>& acc, 
     } else {
       code = __funnelshift_r(w[word], w[word + 1 > 3 ? 3 : word + 1], sh) & kMask;
     }
-    if (Full || uint32_t(c) < n_valid) { acc.add(lut_row + size_t(c) * kBook, code); }
+    if (Full || uint32_t(c) < n_valid) { acc.add(row_a + (uint32_t(c) * kBook + code) * kElem); }
   }
 }
 
@@ -213,6 +335,7 @@ __global__ void __launch_bounds__(1024, 1) scan_kernel(const scan_params p)
   float* s_base     = reinterpret_cast<float*>(gbase + p.lut_bytes);
   uint64_t* s_merge = reinterpret_cast<uint64_t*>(gbase + p.lut_bytes + p.base_bytes);
   uint32_t* s_item  = reinterpret_cast<uint32_t*>(gbase + p.lut_bytes + p.base_bytes + p.merge_bytes);
+  uint32_t* s_thr   = s_item + 1;  // group-wide bound on the k-th best ordered score of this pair
 
   if (p.pqc_in_smem) {
     const uint32_t n4 = (p.pq_dim * p.pq_len * kBook) / 4;
@@ -224,7 +347,6 @@ __global__ void __launch_bounds__(1024, 1) scan_kernel(const scan_params p)
 
   const uint32_t len     = p.pq_len;
   const uint32_t k       = p.k;
-  const uint32_t lut_n2  = (p.pq_dim * kBook) >> 1;  // LUT entries, two at a time
   warp_topk<KPL> queue;
 
   for (;;) {
@@ -248,6 +370,7 @@ __global__ void __launch_bounds__(1024, 1) scan_kernel(const scan_params p)
     const uint32_t sample_offset = pi > 0 ? p.chunk_index[pair - 1] : 0u;
 
     // ---- base diff ----
+    if (gt == 0) { *s_thr = *reinterpret_cast<volatile uint32_t*>(p.query_kth + q); }
     {
       const float* rq = p.rot_q + size_t(q) * p.rot_dim;
       const float* c  = p.centers_rot + size_t(label) * p.rot_dim;
@@ -263,27 +386,38 @@ __global__ void __launch_bounds__(1024, 1) scan_kernel(const scan_params p)
     group_bar(bar_id, gthreads);
 
     // ---- LUT ----
-    {
-      const float* pqc = p.pqc_in_smem ? s_pqc
-                                       : (p.per_cluster ? p.pq_centers + size_t(label) * len * kBook
-                                                        : p.pq_centers);
-      for (uint32_t e2 = gt; e2 < lut_n2; e2 += gthreads) {
-        const uint32_t e  = e2 << 1;
-        const uint32_t j  = e >> PqBits;
-        const uint32_t b  = e & (kBook - 1u);
-        const float* cb   = pqc + (p.per_cluster ? 0u : j * len * kBook) + b;
-        uint64_t score    = 0ull;  // (+0.0f, +0.0f)
+    if (p.pqc_in_smem) {
+      const uint32_t pqc_a = smem_addr(s_pqc), base_a = smem_addr(s_base), lut_a = smem_addr(s_lut);
+      switch (len) {
+        case 1: build_lut_smem<PqBits, LutKind, IsIP, 1>(pqc_a, base_a, lut_a, p.pq_dim, len, gt, gthreads); break;
+        case 2: build_lut_smem<PqBits, LutKind, IsIP, 2>(pqc_a, base_a, lut_a, p.pq_dim, len, gt, gthreads); break;
+        case 4: build_lut_smem<PqBits, LutKind, IsIP, 4>(pqc_a, base_a, lut_a, p.pq_dim, len, gt, gthreads); break;
+        default: build_lut_smem<PqBits, LutKind, IsIP, 0>(pqc_a, base_a, lut_a, p.pq_dim, len, gt, gthreads);
+      }
+    } else {
+      // codebook read from global memory (PER_CLUSTER, or a per-subspace codebook too large for
+      // shared memory): same arithmetic, generic addressing
+      constexpr uint32_t kPairs = kBook / 2;
+      const float* pqc = p.per_cluster ? p.pq_centers + size_t(label) * len * kBook : p.pq_centers;
+      const uint32_t b        = (uint32_t(gt) % kPairs) * 2u;
+      const uint32_t j_first  = uint32_t(gt) / kPairs;
+      const uint32_t j_stride = uint32_t(gthreads) / kPairs;
+      const uint32_t cb_step  = p.per_cluster ? 0u : len * kBook;
+      const float* cb         = pqc + b + j_first * cb_step;
+      const float* bd         = s_base + j_first * len * (IsIP ? 2u : 1u);
+      uint32_t e2             = j_first * kPairs + (uint32_t(gt) % kPairs);
+      for (uint32_t j = j_first; j < p.pq_dim; j += j_stride) {
+        uint64_t score = 0ull;
         for (uint32_t kk = 0; kk < len; kk++) {
-          const float2 pq = *reinterpret_cast<const float2*>(cb + kk * kBook);
+          const float2 pq    = __ldg(reinterpret_cast<const float2*>(cb + kk * kBook));
           const uint64_t pq2 = pack2(pq.x, pq.y);
           if constexpr (!IsIP) {
-            const float d      = s_base[j * len + kk];
-            const uint64_t dif = sub2(pack2(d, d), pq2);
+            const uint64_t dif = sub2(dup2(bd[kk]), pq2);
             score              = fma2(dif, dif, score);
           } else {
-            const float2 qy = reinterpret_cast<const float2*>(s_base)[j * len + kk];
-            score           = sub2(score, pack2(qy.y, qy.y));
-            score           = fma2(pack2(-qy.x, -qy.x), pq2, score);
+            const float2 qy = reinterpret_cast<const float2*>(bd)[kk];
+            score           = sub2(score, dup2(qy.y));
+            score           = fma2(dup2(-qy.x), pq2, score);
           }
         }
         if constexpr (LutKind == LUT_F32) {
@@ -294,6 +428,9 @@ __global__ void __launch_bounds__(1024, 1) scan_kernel(const scan_params p)
           reinterpret_cast<uint16_t*>(s_lut)[e2] =
             uint16_t(fp8_encode<IsIP>(lo2(score))) | (uint16_t(fp8_encode<IsIP>(hi2(score))) << 8);
         }
+        cb += j_stride * cb_step;
+        bd += j_stride * len * (IsIP ? 2u : 1u);
+        e2 += j_stride * kPairs;
       }
     }
     group_bar(bar_id, gthreads);
@@ -301,31 +438,36 @@ __global__ void __launch_bounds__(1024, 1) scan_kernel(const scan_params p)
     // ---- scan ----
     queue.init(int(k));
     {
-      const uint32_t bound    = *reinterpret_cast<volatile uint32_t*>(p.query_kth + q);
-      const uint32_t n_groups = (n + 31u) >> 5;
+      const uint32_t n_groups   = (n + 31u) >> 5;
+      const uint32_t lut_base_a = smem_addr(s_lut);
       const uint4* list =
         reinterpret_cast<const uint4*>(p.codes + p.row_off[label] * size_t(p.n_pieces) * 16u);
       for (uint32_t gi = gw; gi < n_groups; gi += n_gwarps) {
         const uint4* src = list + size_t(gi) * p.n_pieces * 32u + lane;
         accum<LutKind, OutHalf, IsIP> acc;
         acc.init();
-        uint32_t j0 = 0;
-        uint32_t c  = 0;
-        for (; j0 + kPerPiece <= p.pq_dim; j0 += kPerPiece, c++) {
+        constexpr uint32_t kPieceLutBytes = uint32_t(kPerPiece) * kBook * uint32_t(sizeof(lut_t));
+        uint32_t row_a = lut_base_a;
+        uint32_t j0    = 0;
+        uint32_t c     = 0;
+        for (; j0 + kPerPiece <= p.pq_dim; j0 += kPerPiece, c++, row_a += kPieceLutBytes) {
           const uint4 v = __ldg(src + c * 32u);
-          score_piece<PqBits, LutKind, OutHalf, IsIP, true>(acc, v, s_lut + size_t(j0) * kBook, 0);
+          score_piece<PqBits, LutKind, OutHalf, IsIP, true>(acc, v, row_a, 0);
         }
         if (j0 < p.pq_dim) {
           const uint4 v = __ldg(src + c * 32u);
-          score_piece<PqBits, LutKind, OutHalf, IsIP, false>(acc, v, s_lut + size_t(j0) * kBook,
-                                                             p.pq_dim - j0);
+          score_piece<PqBits, LutKind, OutHalf, IsIP, false>(acc, v, row_a, p.pq_dim - j0);
         }
         const float score    = acc.result(p.cosine != 0);
         const uint32_t row   = gi * 32u + lane;
         const bool valid     = row < n;
         const uint32_t ord   = float_to_ordered(score);
         const uint64_t key   = (uint64_t(ord) << 32) | (sample_offset + row);
-        queue.offer(key, valid && ord <= bound);
+        // s_thr never exceeds the final k-th best score of the query, so nothing wanted is lost
+        const uint32_t thr   = *reinterpret_cast<volatile uint32_t*>(s_thr);
+        const uint64_t before = queue.kth();
+        queue.offer(key, valid && ord <= thr);
+        if (queue.kth() != before && lane == 0) { atomicMin(s_thr, uint32_t(queue.kth() >> 32)); }
       }
     }
 

@@ -98,10 +98,44 @@ struct warp_topk {
     kth_ = shfl_u64(mine, pos / KPL);
   }
 
+  // Merge a whole batch (one key per lane, kEmptyKey where there is none) into the queue:
+  // sort the batch across the warp, keep the 32 smallest of (queue, batch), re-sort.
+  // Only for KPL == 1 (the queue is one key per lane).
+  __device__ __forceinline__ void merge_batch(uint64_t b)
+  {
+    const int lane = threadIdx.x & 31;
+#pragma unroll
+    for (int k = 2; k <= 32; k <<= 1) {
+#pragma unroll
+      for (int j = k >> 1; j > 0; j >>= 1) {
+        const uint64_t o    = shfl_u64(b, lane ^ j);
+        const bool keep_min = ((lane & j) == 0) == ((lane & k) == 0);
+        b                   = keep_min ? (o < b ? o : b) : (o > b ? o : b);
+      }
+    }
+    b = shfl_u64(b, 31 - lane);  // descending
+    // ascending queue against descending batch: the element-wise minimum is a bitonic sequence
+    // that holds the 32 smallest keys of the union
+    uint64_t v = a[0] < b ? a[0] : b;
+#pragma unroll
+    for (int j = 16; j > 0; j >>= 1) {
+      const uint64_t o = shfl_u64(v, lane ^ j);
+      v                = ((lane & j) == 0) ? (o < v ? o : v) : (o > v ? o : v);
+    }
+    a[0] = v;
+    refresh_kth();
+  }
+
   // Offer one key per lane (valid lanes only); keys >= kth() are dropped.
   __device__ __forceinline__ void offer(uint64_t key, bool valid)
   {
-    unsigned m = __ballot_sync(kFullMask, valid && key < kth_);
+    const bool pass = valid && key < kth_;
+    unsigned m      = __ballot_sync(kFullMask, pass);
+    if (m == 0) { return; }
+    if (KPL == 1 && __popc(m) > 3) {
+      merge_batch(pass ? key : kEmptyKey);
+      return;
+    }
     while (m) {
       int src = __ffs(m) - 1;
       m &= m - 1;
