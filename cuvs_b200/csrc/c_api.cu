@@ -8,6 +8,7 @@
 #include "../../include/cuvs_mg_ivf_pq.h"
 
 #include "ivf_pq.hpp"
+#include "search_internal.hpp"
 
 #include <cstring>
 #include <exception>
@@ -639,5 +640,34 @@ extern "C" cuvsError_t cuvsB200StatsGet(cuvsResources_t res, cuvsB200SearchStats
       r->stat_pairs   = 0;
       if (r->d_stats) { CUDA_TRY(cudaMemset(r->d_stats, 0, 16)); }
     }
+  });
+}
+
+extern "C" cuvsError_t cuvsB200CoarseSelect(cuvsResources_t res, void* index_handle,
+                                            DLManagedTensor* queries, DLManagedTensor* probes,
+                                            DLManagedTensor* scores, int mode, uint32_t* status)
+{
+  return translate_exceptions([=] {
+    auto* ix          = index_of(static_cast<cuvsIvfPqIndex_t>(index_handle));
+    const DLTensor& q = queries->dl_tensor;
+    auto et           = elem_of_dtype(q.dtype, "queries");
+    void* qd   = checked_data(queries, q.dtype.code, q.dtype.bits, 2, true, "queries");
+    auto* pd   = static_cast<uint32_t*>(checked_data(probes, kDLUInt, 32, 2, true, "probes"));
+    auto* sd   = static_cast<float*>(checked_data(scores, kDLFloat, 32, 2, true, "scores"));
+    CUVS_EXPECTS(q.shape[1] == int64_t(ix->dim()), "queries have the wrong number of columns");
+    CUVS_EXPECTS(probes->dl_tensor.shape[0] == q.shape[0] && scores->dl_tensor.shape[0] == q.shape[0] &&
+                   probes->dl_tensor.shape[1] == scores->dl_tensor.shape[1],
+                 "probes and scores must be [n_queries, n_probes]");
+    CUVS_EXPECTS(status != nullptr, "null status");
+    ivf_pq::coarse_only(*res_of(res), *ix, qd, et, uint32_t(q.shape[0]),
+                        uint32_t(probes->dl_tensor.shape[1]), mode, pd, sd, status);
+  });
+}
+
+extern "C" cuvsError_t cuvsB200SetCoarseMode(int mode)
+{
+  return translate_exceptions([=] {
+    CUVS_EXPECTS(mode >= 0 && mode <= 2, "mode must be 0, 1 or 2");
+    ivf_pq::set_coarse_mode(mode);
   });
 }

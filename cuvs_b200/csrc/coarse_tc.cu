@@ -1,0 +1,802 @@
+// Coarse stage on the tensor cores: queries x list-centers as a 3xTF32 GEMM (tcgen05.mma, TMEM
+// accumulators, operands staged by TMA), fused with candidate selection, followed by an exact
+// rescoring so that the chosen probes are bit-identical to the exact SIMT path of coarse.cu.
+//
+// Reference semantics: select_clusters, cpp/src/neighbors/ivf_pq/ivf_pq_search.cuh:61-168
+// (fp32 GEMM + select_k).  The full [n_queries, n_lists] score matrix of the reference is never
+// materialised here.
+//
+// Pipeline per batch
+//   1. split_tf32_kernel: every fp32 operand x is written as hi = tf32(x), lo = tf32(x - hi)
+//      (centers once per index, queries per batch).
+//   2. coarse_tc_kernel: CTA tile = 128 queries x 256 lists, K in blocks of 32 floats (one
+//      128-byte swizzle atom).  Per K block three products accumulate into TMEM:
+//      hi*hi + hi*lo + lo*hi.  Warp 0 issues TMA loads (no multicast), warp 1 issues the MMAs,
+//      eight epilogue warps read the accumulator with tcgen05.ld (thread = query row) and keep,
+//      per row and per 128-list half tile, the 8 largest dot products in registers.  Two TMEM
+//      accumulators let the epilogue of one tile overlap the MMAs of the next.
+//      Every mbarrier wait is bounded; on a time-out the kernel raises an error word, lets its
+//      in-flight copies land, frees its TMEM and returns.
+//   3. coarse_finish_kernel (one block per query): the C = n_probes + margin best candidates by
+//      tensor-core score are rescored with the defining fp32 FMA chain, sorted by (score, id), and
+//      the first n_probes become the probes.  A guard proves the selection exact: every list that
+//      was not rescored has a tensor-core score <= T, and T + eps < exact score of the last probe,
+//      eps bounding |tensor-core - exact|.  A query whose guard fails is flagged.
+//   4. coarse_fallback_kernel: flagged queries (rare) are redone exactly over all lists.
+#include "search_internal.hpp"
+#include "topk.cuh"
+
+#include <cuda.h>
+
+#include <algorithm>
+#include <mutex>
+
+namespace cuvs::neighbors::ivf_pq {
+
+using namespace cuvs_b200;
+
+namespace {
+
+constexpr int kBM       = 128;  // queries per tile
+constexpr int kBN       = 256;  // lists per tile
+constexpr int kBK       = 32;   // floats per K block (128 bytes)
+constexpr int kStages   = 2;
+constexpr int kKeep     = 8;    // candidates kept per row per half tile
+constexpr int kHalf     = kBN / 2;
+constexpr int kThreads  = 320;  // warp 0 TMA, warp 1 MMA, warps 2..9 epilogue
+constexpr uint32_t kStageBytes = (2 * kBM + 2 * kBN) * kBK * 4;  // 96 KB
+constexpr uint32_t kSmemBytes  = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
+constexpr uint32_t kSpinLimit  = 1u << 21;  // bounded waits (each try_wait sleeps up to ~1 us)
+
+enum { ERR_NONE = 0, ERR_TIMEOUT = 1 };
+
+// ------------------------------------------------------------------------------------------------
+// operand split
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ float to_tf32(float x)
+{
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+  return __uint_as_float(r);
+}
+
+__global__ void split_tf32_kernel(const float* __restrict__ in, size_t n, float* __restrict__ hi,
+                                  float* __restrict__ lo)
+{
+  const size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x;
+  if (i >= n) { return; }
+  const float x = in[i];
+  const float h = to_tf32(x);
+  hi[i]         = h;
+  lo[i]         = to_tf32(x - h);
+}
+
+// ------------------------------------------------------------------------------------------------
+// PTX wrappers
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p)
+{
+  return uint32_t(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
+{
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar)
+{
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes)
+{
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+// Bounded wait: false on time-out.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity)
+{
+  for (uint32_t it = 0; it < kSpinLimit; it++) {
+    uint32_t done;
+    asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, 1000;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done)
+      : "r"(bar), "r"(parity)
+      : "memory");
+    if (done) { return true; }
+  }
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x,
+                                            int y)
+{
+  asm volatile(
+    "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+    ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
+    : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar)
+{
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ void tc_mma_tf32(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
+                                            uint32_t idesc, uint32_t accumulate)
+{
+  asm volatile(
+    "{\n\t.reg .pred p;\n\t"
+    "setp.ne.b32 p, %4, 0;\n\t"
+    "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+    ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+    : "memory");
+}
+// Shared-memory matrix descriptor of a K-major tile stored as rows of 128 bytes with the 128-byte
+// swizzle: 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t make_desc(uint32_t saddr)
+{
+  uint64_t d = 0;
+  d |= uint64_t((saddr & 0x3FFFFu) >> 4);  // start address, 16-byte units
+  d |= uint64_t(1) << 16;                  // leading byte offset (unused for swizzled K-major)
+  d |= uint64_t(1024 >> 4) << 32;          // stride byte offset between 8-row groups
+  d |= uint64_t(1) << 46;                  // descriptor version of this architecture
+  d |= uint64_t(2) << 61;                  // 128-byte swizzle
+  return d;
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32])
+{
+  asm volatile(
+    "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+    "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+    "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+    : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+      "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]),
+      "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]),
+      "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]),
+      "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+    : "r"(taddr)
+    : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// ------------------------------------------------------------------------------------------------
+// the GEMM + candidate kernel
+// ------------------------------------------------------------------------------------------------
+struct tc_params {
+  uint32_t n_queries, n_lists, k_blocks, n_tiles, tile_stride;
+  float* cand_val;     // [n_queries, n_tiles, 2, kKeep] raw dot products (larger = closer)
+  uint32_t* cand_idx;  // same shape, list ids (0xFFFFFFFF = empty slot)
+  uint32_t* error;     // error word
+};
+
+__global__ void __launch_bounds__(kThreads, 1)
+coarse_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
+                 const __grid_constant__ CUtensorMap map_b_hi, const __grid_constant__ CUtensorMap map_b_lo,
+                 const tc_params p)
+{
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_a  = smem_u32(smem_raw);
+  const uint32_t base_a = (raw_a + 1023u) & ~1023u;             // tiles need 1024-byte alignment
+  uint8_t* base_p       = smem_raw + (base_a - raw_a);
+  uint64_t* bars        = reinterpret_cast<uint64_t*>(base_p + kStages * kStageBytes);
+  // bars: full[kStages], empty[kStages], tmem_full[2], tmem_empty[2], then the TMEM address slot
+  const uint32_t bar_full   = smem_u32(bars);
+  const uint32_t bar_empty  = bar_full + kStages * 8;
+  const uint32_t bar_tfull  = bar_empty + kStages * 8;
+  const uint32_t bar_tempty = bar_tfull + 2 * 8;
+  uint32_t* tmem_slot       = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
+  __shared__ uint32_t s_failed;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t q0 = blockIdx.x * kBM;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; s++) {
+      mbar_init(bar_full + s * 8, 1);
+      mbar_init(bar_empty + s * 8, 1);
+    }
+    for (int a = 0; a < 2; a++) {
+      mbar_init(bar_tfull + a * 8, 1);
+      mbar_init(bar_tempty + a * 8, 8);  // one arrival per epilogue warp
+    }
+    s_failed = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(smem_u32(tmem_slot))
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+
+  // tiles of this CTA: blockIdx.y, blockIdx.y + tile_stride, ...
+  const uint32_t first_tile = blockIdx.y;
+  uint32_t n_my_tiles       = 0;
+  if (first_tile < p.n_tiles) { n_my_tiles = (p.n_tiles - first_tile + p.tile_stride - 1) / p.tile_stride; }
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (uint32_t i = 0; ok && i < n_my_tiles; i++) {
+        const int n0 = int((first_tile + i * p.tile_stride) * kBN);
+        for (uint32_t kb = 0; kb < p.k_blocks; kb++) {
+          if (!mbar_wait(bar_empty + stage * 8, phase ^ 1u)) {
+            ok = false;
+            break;
+          }
+          const uint32_t dst = base_a + stage * kStageBytes;
+          const uint32_t bar = bar_full + stage * 8;
+          mbar_arrive_expect_tx(bar, kStageBytes);
+          tma_load_2d(dst, &map_a_hi, bar, int(kb * kBK), int(q0));
+          tma_load_2d(dst + kBM * kBK * 4, &map_a_lo, bar, int(kb * kBK), int(q0));
+          tma_load_2d(dst + 2 * kBM * kBK * 4, &map_b_hi, bar, int(kb * kBK), n0);
+          tma_load_2d(dst + 2 * kBM * kBK * 4 + kBN * kBK * 4, &map_b_lo, bar, int(kb * kBK), n0);
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+      if (!ok) {
+        atomicExch(p.error, ERR_TIMEOUT);
+        s_failed = 1;
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      // instruction descriptor: fp32 accumulate, tf32 x tf32, both K-major, N = 256, M = 128
+      constexpr uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | (uint32_t(kBN >> 3) << 17) |
+                                 (uint32_t(kBM >> 4) << 24);
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (uint32_t i = 0; ok && i < n_my_tiles; i++) {
+        const uint32_t acc       = i & 1u;
+        const uint32_t acc_phase = (i >> 1) & 1u;
+        if (!mbar_wait(bar_tempty + acc * 8, acc_phase ^ 1u)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + acc * kBN;
+        for (uint32_t kb = 0; kb < p.k_blocks; kb++) {
+          if (!mbar_wait(bar_full + stage * 8, phase)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa      = base_a + stage * kStageBytes;
+          const uint64_t d_a_hi  = make_desc(sa);
+          const uint64_t d_a_lo  = make_desc(sa + kBM * kBK * 4);
+          const uint64_t d_b_hi  = make_desc(sa + 2 * kBM * kBK * 4);
+          const uint64_t d_b_lo  = make_desc(sa + 2 * kBM * kBK * 4 + kBN * kBK * 4);
+#pragma unroll
+          for (uint32_t k8 = 0; k8 < kBK / 8; k8++) {
+            const uint64_t adv = uint64_t(k8 * 2);  // 32 bytes per MMA along K, in 16-byte units
+            tc_mma_tf32(tmem_d, d_a_lo + adv, d_b_hi + adv, idesc, (kb | k8) != 0);
+            tc_mma_tf32(tmem_d, d_a_hi + adv, d_b_lo + adv, idesc, 1);
+            tc_mma_tf32(tmem_d, d_a_hi + adv, d_b_hi + adv, idesc, 1);
+          }
+          tc_commit(bar_empty + stage * 8);  // the stage may be refilled once these MMAs have read it
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (ok) { tc_commit(bar_tfull + acc * 8); }
+      }
+      if (!ok) {
+        atomicExch(p.error, ERR_TIMEOUT);
+        s_failed = 1;
+      }
+    }
+    __syncwarp();
+  } else {
+    // ---------------- epilogue: thread = query row, warp = (lane quarter, column half) ----------------
+    const uint32_t quarter = uint32_t(warp) & 3u;        // TMEM lanes a warp may read: 32 * (warp % 4)
+    const uint32_t half    = uint32_t(warp - 2) >> 2;    // warps 2..5 -> columns 0..127, 6..9 -> 128..255
+    const uint32_t row     = quarter * 32 + lane;
+    const uint32_t q       = q0 + row;
+    bool ok = true;
+    for (uint32_t i = 0; i < n_my_tiles; i++) {
+      const uint32_t tile      = first_tile + i * p.tile_stride;
+      const uint32_t acc       = i & 1u;
+      const uint32_t acc_phase = (i >> 1) & 1u;
+      if (ok && !mbar_wait(bar_tfull + acc * 8, acc_phase)) { ok = false; }
+      // a time-out on any lane ends the loop for the whole warp
+      if (__any_sync(kFullMask, !ok)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      float val[kKeep];
+      uint32_t idx[kKeep];
+#pragma unroll
+      for (int t = 0; t < kKeep; t++) {
+        val[t] = -INFINITY;
+        idx[t] = 0xFFFFFFFFu;
+      }
+      const uint32_t col0 = half * kHalf;
+      const uint32_t n0   = tile * kBN + col0;
+#pragma unroll 1
+      for (uint32_t c = 0; c < kHalf; c += 32) {
+        uint32_t r[32];
+        tmem_ld32(tmem_base + ((quarter * 32u) << 16) + acc * kBN + col0 + c, r);
+        const uint32_t list0 = n0 + c;
+#pragma unroll
+        for (int e = 0; e < 32; e++) {
+          const float x = __uint_as_float(r[e]);
+          if (list0 + e < p.n_lists && x > val[kKeep - 1]) {
+            // sorted insert (descending); strict '>' keeps the lower list id among equal values
+            float xv    = x;
+            uint32_t xi = list0 + e;
+#pragma unroll
+            for (int t = 0; t < kKeep; t++) {
+              if (xv > val[t]) {
+                const float tv    = val[t];
+                const uint32_t ti = idx[t];
+                val[t]            = xv;
+                idx[t]            = xi;
+                xv                = tv;
+                xi                = ti;
+              }
+            }
+          }
+        }
+      }
+      // the accumulator may be overwritten now
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) { mbar_arrive(bar_tempty + acc * 8); }
+      if (q < p.n_queries) {
+        const size_t o = ((size_t(q) * p.n_tiles + tile) * 2 + half) * kKeep;
+#pragma unroll
+        for (int t = 0; t < kKeep; t++) {
+          p.cand_val[o + t] = val[t];
+          p.cand_idx[o + t] = idx[t];
+        }
+      }
+    }
+    if (!ok && lane == 0) {
+      atomicExch(p.error, ERR_TIMEOUT);
+      s_failed = 1;
+    }
+  }
+
+  // ---------------- teardown ----------------
+  tc_fence_before();
+  __syncthreads();
+  if (s_failed) {
+    // give copies that are still in flight time to land before the shared memory is released
+    for (int i = 0; i < 64; i++) { __nanosleep(1000); }
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem_base) : "memory");
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// finish: select C best candidates by tensor-core score, rescore exactly, sort, guard
+// ------------------------------------------------------------------------------------------------
+constexpr uint32_t kMaxC = 1024;
+
+__global__ void __launch_bounds__(256)
+coarse_finish_kernel(const float* __restrict__ cand_val, const uint32_t* __restrict__ cand_idx,
+                     uint32_t n_cand /* per query */, const float* __restrict__ centers,
+                     const float* __restrict__ fq, uint32_t n_lists, uint32_t dim_ext, float alpha,
+                     uint32_t n_probes, uint32_t C, uint32_t cap /* pow2 >= C */, float cmax,
+                     uint32_t* __restrict__ probes, float* __restrict__ scores_out,
+                     uint8_t* __restrict__ flags)
+{
+  extern __shared__ uint64_t s_keys[];                 // [cap] keys; then the query [dim_ext] floats
+  float* s_q = reinterpret_cast<float*>(s_keys + cap);
+  __shared__ uint32_t s_hist[256];
+  __shared__ uint32_t s_prefix, s_remaining, s_count;
+  __shared__ float s_red[8];
+  const uint32_t q   = blockIdx.x;
+  const uint32_t tid = threadIdx.x;
+  const float* val   = cand_val + size_t(q) * n_cand;
+  const uint32_t* id = cand_idx + size_t(q) * n_cand;
+
+  float qq = 0.0f;
+  for (uint32_t i = tid; i < dim_ext; i += 256) {
+    const float v = fq[size_t(q) * dim_ext + i];
+    s_q[i]        = v;
+    qq += v * v;
+  }
+  if (tid == 0) {
+    s_prefix    = 0;
+    s_remaining = C;
+  }
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) { qq += __shfl_xor_sync(kFullMask, qq, d); }
+  if ((tid & 31) == 0) { s_red[tid >> 5] = qq; }
+
+  // radix select of the C LARGEST values: use the order-preserving image of -value
+  for (int pass = 0; pass < 4; pass++) {
+    const int shift = 24 - 8 * pass;
+    s_hist[tid]     = 0;
+    __syncthreads();
+    const uint32_t prefix = s_prefix;
+    const uint32_t mask   = pass == 0 ? 0u : (0xFFFFFFFFu << (shift + 8));
+    for (uint32_t i = tid; i < n_cand; i += 256) {
+      if (id[i] == 0xFFFFFFFFu) { continue; }
+      const uint32_t o = float_to_ordered(-val[i]);
+      if ((o & mask) == prefix) { atomicAdd(&s_hist[(o >> shift) & 0xFFu], 1u); }
+    }
+    __syncthreads();
+    if (tid == 0) {
+      uint32_t rem = s_remaining, d = 0;
+      for (; d < 256; d++) {
+        const uint32_t c = s_hist[d];
+        if (c >= rem) { break; }
+        rem -= c;
+      }
+      if (d == 256) {  // fewer valid candidates than C: take everything
+        d   = 255;
+        rem = 0xFFFFFFFFu;
+      }
+      s_prefix    = prefix | (d << shift);
+      s_remaining = rem;
+    }
+    __syncthreads();
+  }
+  const uint32_t T = s_prefix;  // ordered image of -(C-th largest value)
+  if (tid == 0) { s_count = 0; }
+  for (uint32_t i = tid; i < cap; i += 256) { s_keys[i] = kEmptyKey; }
+  __syncthreads();
+  // gather: everything at least as good as T (ties at T may push the count above C: capped at cap),
+  // and the bound contributed by full half tiles (their last kept value)
+  float tb = -INFINITY;
+  for (uint32_t i = tid; i < n_cand; i += 256) {
+    const uint32_t l = id[i];
+    if (l == 0xFFFFFFFFu) { continue; }
+    const float v = val[i];
+    if ((i % kKeep) == kKeep - 1) { tb = fmaxf(tb, v); }
+    if (float_to_ordered(-v) <= T) {
+      const uint32_t slot = atomicAdd(&s_count, 1u);
+      if (slot < cap) { s_keys[slot] = l; }
+    }
+  }
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) { tb = fmaxf(tb, __shfl_xor_sync(kFullMask, tb, d)); }
+  __shared__ float s_tb[8];
+  if ((tid & 31) == 0) { s_tb[tid >> 5] = tb; }
+  __syncthreads();
+  float tilebound = s_tb[0];
+#pragma unroll
+  for (int w = 1; w < 8; w++) { tilebound = fmaxf(tilebound, s_tb[w]); }
+  const uint32_t n_sel    = min(s_count, cap);
+  const bool overflow     = s_count > cap;
+  // exact rescoring: the defining FMA chain, ascending k
+  for (uint32_t i = tid; i < n_sel; i += 256) {
+    const uint32_t l = uint32_t(s_keys[i]);
+    const float* c   = centers + size_t(l) * dim_ext;
+    float acc        = 0.0f;
+    for (uint32_t k = 0; k < dim_ext; k++) { acc = __fmaf_rn(__ldg(c + k), s_q[k], acc); }
+    s_keys[i] = (uint64_t(float_to_ordered(__fmul_rn(alpha, acc))) << 32) | l;
+  }
+  __syncthreads();
+  for (uint32_t size = 2; size <= cap; size <<= 1) {
+    for (uint32_t stride = size >> 1; stride > 0; stride >>= 1) {
+      for (uint32_t i = tid; i < cap / 2; i += 256) {
+        const uint32_t lo = 2 * i - (i & (stride - 1));
+        const uint32_t hi = lo + stride;
+        const bool up     = (lo & size) == 0;
+        const uint64_t a = s_keys[lo], b = s_keys[hi];
+        if ((a > b) == up) {
+          s_keys[lo] = b;
+          s_keys[hi] = a;
+        }
+      }
+      __syncthreads();
+    }
+  }
+  for (uint32_t pi = tid; pi < n_probes; pi += 256) {
+    const uint64_t key               = s_keys[pi];
+    probes[size_t(q) * n_probes + pi] = uint32_t(key);
+    if (scores_out) { scores_out[size_t(q) * n_probes + pi] = ordered_to_float(uint32_t(key >> 32)); }
+  }
+  if (tid == 0) {
+    // guard, in dot-product units (score = alpha * dot, alpha < 0)
+    float qnorm = 0.0f;
+    for (int w = 0; w < 8; w++) { qnorm += s_red[w]; }
+    qnorm = sqrtf(qnorm);
+    const float eps       = float(dim_ext + 8) * 2.4e-7f * qnorm * cmax;
+    const float t_c       = -ordered_to_float(T);  // C-th largest tensor-core value
+    const float unseen    = fmaxf(t_c, tilebound);
+    bool ok               = !overflow && n_sel >= n_probes;
+    if (ok) {
+      const float last_dot = ordered_to_float(uint32_t(s_keys[n_probes - 1] >> 32)) / alpha;
+      // all lists rescored (n_sel == every valid candidate == every list) needs no proof
+      ok = (last_dot - unseen > eps) || (n_sel >= n_lists);
+    }
+    flags[q] = ok ? 0 : 1;
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// exact redo of flagged queries
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+coarse_fallback_kernel(const uint8_t* __restrict__ flags, const float* __restrict__ centers,
+                       const float* __restrict__ fq, uint32_t n_queries, uint32_t n_lists,
+                       uint32_t dim_ext, float alpha, uint32_t n_probes, uint32_t cap,
+                       float* __restrict__ scratch /* [gridDim.x, n_lists] */,
+                       uint32_t* __restrict__ probes, float* __restrict__ scores_out,
+                       uint32_t* __restrict__ n_fallback)
+{
+  extern __shared__ uint64_t s_keys[];  // [cap], then the query
+  float* s_q = reinterpret_cast<float*>(s_keys + cap);
+  __shared__ uint32_t s_hist[256];
+  __shared__ uint32_t s_prefix, s_remaining, s_count, s_eq_taken;
+  const uint32_t tid = threadIdx.x;
+  float* row         = scratch + size_t(blockIdx.x) * n_lists;
+  for (uint32_t q = blockIdx.x; q < n_queries; q += gridDim.x) {
+    if (!flags[q]) { continue; }  // uniform per block
+    if (tid == 0) { atomicAdd(n_fallback, 1u); }
+    for (uint32_t i = tid; i < dim_ext; i += 256) { s_q[i] = fq[size_t(q) * dim_ext + i]; }
+    __syncthreads();
+    for (uint32_t l = tid; l < n_lists; l += 256) {
+      const float* c = centers + size_t(l) * dim_ext;
+      float acc      = 0.0f;
+      for (uint32_t k = 0; k < dim_ext; k++) { acc = __fmaf_rn(__ldg(c + k), s_q[k], acc); }
+      row[l] = __fmul_rn(alpha, acc);
+    }
+    if (tid == 0) {
+      s_prefix    = 0;
+      s_remaining = n_probes;
+    }
+    __syncthreads();
+    for (int pass = 0; pass < 4; pass++) {
+      const int shift = 24 - 8 * pass;
+      s_hist[tid]     = 0;
+      __syncthreads();
+      const uint32_t prefix = s_prefix;
+      const uint32_t mask   = pass == 0 ? 0u : (0xFFFFFFFFu << (shift + 8));
+      for (uint32_t l = tid; l < n_lists; l += 256) {
+        const uint32_t o = float_to_ordered(row[l]);
+        if ((o & mask) == prefix) { atomicAdd(&s_hist[(o >> shift) & 0xFFu], 1u); }
+      }
+      __syncthreads();
+      if (tid == 0) {
+        uint32_t rem = s_remaining, d = 0;
+        for (; d < 256; d++) {
+          const uint32_t c = s_hist[d];
+          if (c >= rem) { break; }
+          rem -= c;
+        }
+        s_prefix    = prefix | (d << shift);
+        s_remaining = rem;
+      }
+      __syncthreads();
+    }
+    const uint32_t T = s_prefix, want_eq = s_remaining;
+    if (tid == 0) {
+      s_count    = 0;
+      s_eq_taken = 0;
+    }
+    for (uint32_t i = tid; i < cap; i += 256) { s_keys[i] = kEmptyKey; }
+    __syncthreads();
+    for (uint32_t base = 0; base < n_lists; base += 256) {
+      const uint32_t l = base + tid;
+      uint32_t o       = 0xFFFFFFFFu;
+      if (l < n_lists) { o = float_to_ordered(row[l]); }
+      if (l < n_lists && o < T) { s_keys[atomicAdd(&s_count, 1u)] = (uint64_t(o) << 32) | l; }
+      const bool eq = l < n_lists && o == T;
+      if (__syncthreads_or(eq)) {
+        for (int w = 0; w < 8; w++) {
+          if (int(tid >> 5) == w) {
+            const unsigned m = __ballot_sync(kFullMask, eq);
+            if (m) {
+              const uint32_t start = s_eq_taken;
+              const uint32_t rank  = start + __popc(m & ((1u << (tid & 31)) - 1u));
+              if (eq && rank < want_eq) { s_keys[atomicAdd(&s_count, 1u)] = (uint64_t(o) << 32) | l; }
+              __syncwarp();
+              if ((tid & 31) == 0) { s_eq_taken = start + __popc(m); }
+            }
+          }
+          __syncthreads();
+        }
+      }
+    }
+    __syncthreads();
+    for (uint32_t size = 2; size <= cap; size <<= 1) {
+      for (uint32_t stride = size >> 1; stride > 0; stride >>= 1) {
+        for (uint32_t i = tid; i < cap / 2; i += 256) {
+          const uint32_t lo = 2 * i - (i & (stride - 1));
+          const uint32_t hi = lo + stride;
+          const bool up     = (lo & size) == 0;
+          const uint64_t a = s_keys[lo], b = s_keys[hi];
+          if ((a > b) == up) {
+            s_keys[lo] = b;
+            s_keys[hi] = a;
+          }
+        }
+        __syncthreads();
+      }
+    }
+    for (uint32_t pi = tid; pi < n_probes; pi += 256) {
+      const uint64_t key               = s_keys[pi];
+      probes[size_t(q) * n_probes + pi] = uint32_t(key);
+      if (scores_out) { scores_out[size_t(q) * n_probes + pi] = ordered_to_float(uint32_t(key >> 32)); }
+    }
+    __syncthreads();
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// host side
+// ------------------------------------------------------------------------------------------------
+using encode_fn_t = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                 const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                 CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                 CUtensorMapFloatOOBfill);
+
+encode_fn_t get_encode_fn()
+{
+  static encode_fn_t fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<encode_fn_t>(p);
+    }
+  });
+  CUVS_EXPECTS(fn != nullptr, "cuTensorMapEncodeTiled is not available in this driver");
+  return fn;
+}
+
+// 2-D fp32 row-major [rows, cols] tensor, box [box_rows, 32 columns], 128-byte swizzle, zero fill.
+CUtensorMap make_map(const float* ptr, uint64_t rows, uint64_t cols, uint32_t box_rows)
+{
+  CUtensorMap m;
+  const cuuint64_t dims[2]    = {cols, rows};
+  const cuuint64_t strides[1] = {cols * 4};
+  const cuuint32_t box[2]     = {kBK, box_rows};
+  const cuuint32_t elem[2]    = {1, 1};
+  CUresult r = get_encode_fn()(&m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(ptr), dims,
+                               strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  CUVS_EXPECTS(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed with code %d", int(r));
+  return m;
+}
+
+uint32_t margin_for(uint32_t n_probes) { return std::max<uint32_t>(16, n_probes / 4); }
+
+}  // namespace
+
+bool coarse_tc_usable(uint32_t n_lists, uint32_t n_probes, uint32_t dim_ext)
+{
+  if (n_lists < 2048 || (dim_ext % 4) != 0) { return false; }
+  const uint32_t C = n_probes + margin_for(n_probes);
+  if (C > kMaxC / 2) { return false; }
+  // expected number of wanted lists per 128-list half tile; the 8 kept per half tile must cover it
+  const double lambda = double(C) * kHalf / double(n_lists);
+  return lambda <= 1.5;
+}
+
+size_t coarse_tc_workspace_bytes(uint32_t n_queries, uint32_t n_lists, uint32_t dim_ext)
+{
+  const size_t n_tiles = ceildiv<uint32_t>(n_lists, kBN);
+  ws_layout lay;
+  lay.add(size_t(n_queries) * dim_ext * 4);  // fq hi
+  lay.add(size_t(n_queries) * dim_ext * 4);  // fq lo
+  lay.add(size_t(n_queries) * n_tiles * 2 * kKeep * 4);
+  lay.add(size_t(n_queries) * n_tiles * 2 * kKeep * 4);
+  lay.add(n_queries);                        // flags
+  lay.add(256);                              // error word + fallback counter
+  lay.add(size_t(64) * n_lists * 4);         // fallback scratch rows
+  return lay.total();
+}
+
+void split_centers_tf32(cudaStream_t stream, const float* centers, size_t n, float* hi, float* lo)
+{
+  if (n == 0) { return; }
+  split_tf32_kernel<<<unsigned(ceildiv<size_t>(n, 256)), 256, 0, stream>>>(centers, n, hi, lo);
+  CUDA_TRY(cudaGetLastError());
+}
+
+void select_clusters_tc(raft::resources& res, const float* centers, const float* centers_hi,
+                        const float* centers_lo, float cmax, uint32_t n_lists, uint32_t dim_ext,
+                        float alpha, const float* fq, uint32_t n_queries, uint32_t n_probes,
+                        uint32_t* probes, float* scores_out, void* workspace, size_t workspace_bytes)
+{
+  CUVS_EXPECTS(alpha < 0.0f, "the tensor-core coarse search expects a negative scale");
+  CUVS_EXPECTS(workspace_bytes >= coarse_tc_workspace_bytes(n_queries, n_lists, dim_ext),
+               "coarse workspace too small");
+  const uint32_t n_tiles = ceildiv<uint32_t>(n_lists, kBN);
+  const uint32_t n_cand  = n_tiles * 2 * kKeep;
+  ws_layout lay;
+  char* ws        = static_cast<char*>(workspace);
+  float* fq_hi    = reinterpret_cast<float*>(ws + lay.add(size_t(n_queries) * dim_ext * 4));
+  float* fq_lo    = reinterpret_cast<float*>(ws + lay.add(size_t(n_queries) * dim_ext * 4));
+  float* cand_val = reinterpret_cast<float*>(ws + lay.add(size_t(n_queries) * n_cand * 4));
+  auto* cand_idx  = reinterpret_cast<uint32_t*>(ws + lay.add(size_t(n_queries) * n_cand * 4));
+  auto* flags     = reinterpret_cast<uint8_t*>(ws + lay.add(n_queries));
+  auto* words     = reinterpret_cast<uint32_t*>(ws + lay.add(256));
+  float* scratch  = reinterpret_cast<float*>(ws + lay.add(size_t(64) * n_lists * 4));
+  cudaStream_t stream = res.stream;
+
+  split_tf32_kernel<<<unsigned(ceildiv<size_t>(size_t(n_queries) * dim_ext, 256)), 256, 0, stream>>>(
+    fq, size_t(n_queries) * dim_ext, fq_hi, fq_lo);
+  CUDA_TRY(cudaMemsetAsync(words, 0, 8, stream));
+
+  const CUtensorMap m_a_hi = make_map(fq_hi, n_queries, dim_ext, kBM);
+  const CUtensorMap m_a_lo = make_map(fq_lo, n_queries, dim_ext, kBM);
+  const CUtensorMap m_b_hi = make_map(centers_hi, n_lists, dim_ext, kBN);
+  const CUtensorMap m_b_lo = make_map(centers_lo, n_lists, dim_ext, kBN);
+
+  tc_params p{};
+  p.n_queries = n_queries;
+  p.n_lists   = n_lists;
+  p.k_blocks  = ceildiv<uint32_t>(dim_ext, kBK);
+  p.n_tiles   = n_tiles;
+  p.cand_val  = cand_val;
+  p.cand_idx  = cand_idx;
+  p.error     = words;
+  const uint32_t q_tiles = ceildiv<uint32_t>(n_queries, kBM);
+  // list-tile splits per query tile: enough CTAs for a few waves, never more than the tiles
+  uint32_t splits = std::max<uint32_t>(1, (uint32_t(res.sm_count) * 4 + q_tiles - 1) / q_tiles);
+  splits          = std::min(splits, n_tiles);
+  splits          = std::min<uint32_t>(splits, 65535);
+  p.tile_stride   = splits;
+  static bool configured = false;
+  if (!configured) {
+    CUDA_TRY(cudaFuncSetAttribute(coarse_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  int(kSmemBytes)));
+    configured = true;
+  }
+  coarse_tc_kernel<<<dim3(q_tiles, splits), kThreads, kSmemBytes, stream>>>(m_a_hi, m_a_lo, m_b_hi,
+                                                                           m_b_lo, p);
+  CUDA_TRY(cudaGetLastError());
+
+  const uint32_t C = std::min<uint32_t>(n_probes + margin_for(n_probes), n_lists);
+  uint32_t cap     = 2;
+  while (cap < 2 * C) { cap <<= 1; }  // room for ties at the selection threshold
+  const size_t fin_smem = size_t(cap) * 8 + size_t(dim_ext) * 4;
+  coarse_finish_kernel<<<n_queries, 256, fin_smem, stream>>>(cand_val, cand_idx, n_cand, centers, fq,
+                                                             n_lists, dim_ext, alpha, n_probes, C, cap,
+                                                             cmax, probes, scores_out, flags);
+  uint32_t cap_fb = 2;
+  while (cap_fb < n_probes) { cap_fb <<= 1; }
+  const size_t fb_smem = size_t(cap_fb) * 8 + size_t(dim_ext) * 4;
+  coarse_fallback_kernel<<<64, 256, fb_smem, stream>>>(flags, centers, fq, n_queries, n_lists, dim_ext,
+                                                       alpha, n_probes, cap_fb, scratch, probes,
+                                                       scores_out, words + 1);
+  CUDA_TRY(cudaGetLastError());
+  res.launches += 4;
+}
+
+// Reads back the error word and the number of queries redone exactly by the last call that used
+// `workspace` (synchronises the stream; used by tests and the benchmark).
+void coarse_tc_status(raft::resources& res, const void* workspace, uint32_t n_queries, uint32_t n_lists,
+                      uint32_t dim_ext, uint32_t* error, uint32_t* n_fallback)
+{
+  const uint32_t n_tiles = ceildiv<uint32_t>(n_lists, kBN);
+  ws_layout lay;
+  lay.add(size_t(n_queries) * dim_ext * 4);
+  lay.add(size_t(n_queries) * dim_ext * 4);
+  lay.add(size_t(n_queries) * n_tiles * 2 * kKeep * 4);
+  lay.add(size_t(n_queries) * n_tiles * 2 * kKeep * 4);
+  lay.add(n_queries);
+  const size_t o = lay.add(256);
+  uint32_t h[2]  = {0, 0};
+  CUDA_TRY(cudaMemcpyAsync(h, static_cast<const char*>(workspace) + o, 8, cudaMemcpyDeviceToHost, res.stream));
+  res.sync();
+  *error      = h[0];
+  *n_fallback = h[1];
+}
+
+}  // namespace cuvs::neighbors::ivf_pq

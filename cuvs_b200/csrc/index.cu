@@ -10,10 +10,12 @@
 // The reader accepts any well-formed v1.0/2.0 header and checks element size and element count
 // of every record against what the format calls for.
 #include "ivf_pq.hpp"
+#include "search_internal.hpp"
 
 #include <algorithm>
 #include <cstring>
 #include <fstream>
+#include <cmath>
 #include <numeric>
 
 namespace cuvs::neighbors::ivf_pq {
@@ -117,6 +119,27 @@ void index<int64_t>::recompute_internal_state(cudaStream_t stream)
     }
   }
   rotation_is_identity_ = ident;
+  // derived data of the tensor-core coarse search
+  const size_t nc = size_t(n_lists_) * dim_ext();
+  std::vector<float> hc(nc);
+  CUDA_TRY(cudaMemcpyAsync(hc.data(), centers_.data(), nc * 4, cudaMemcpyDeviceToHost, stream));
+  CUDA_TRY(cudaStreamSynchronize(stream));
+  double mx = 0.0;
+  for (uint32_t l = 0; l < n_lists_; l++) {
+    double ss = 0.0;
+    for (uint32_t k = 0; k < dim_ext(); k++) {
+      const double v = hc[size_t(l) * dim_ext() + k];
+      ss += v * v;
+    }
+    mx = std::max(mx, ss);
+  }
+  centers_max_norm_ = float(std::sqrt(mx)) * 1.0001f;
+  if (centers_hi_.size() != nc) {
+    centers_hi_.resize(nc);
+    centers_lo_.resize(nc);
+  }
+  split_centers_tf32(stream, centers_.data(), nc, centers_hi_.data(), centers_lo_.data());
+  CUDA_TRY(cudaStreamSynchronize(stream));
 }
 
 // ------------------------------------------------------------------------------------------------

@@ -200,6 +200,10 @@ class index<int64_t> {
   // accum_sorted_sizes()[p] = total size of the p largest lists (ivf_common.cuh:255-290)
   const std::vector<int64_t>& accum_sorted_sizes() const { return accum_sorted_sizes_; }
   bool rotation_is_identity() const { return rotation_is_identity_; }
+  // TF32 split of `centers` for the tensor-core coarse search, and the largest padded-row norm
+  float* centers_hi() const { return centers_hi_.data(); }
+  float* centers_lo() const { return centers_lo_.data(); }
+  float centers_max_norm() const { return centers_max_norm_; }
   uint64_t total_rows_padded() const { return h_row_off_.empty() ? 0 : h_row_off_.back(); }
 
   // (Re)create the arenas for the given list sizes; contents are zero codes / -1 ids.
@@ -209,6 +213,8 @@ class index<int64_t> {
 
   // model arrays are public to the builder / loader
   dev_array<float> pq_centers_, centers_, centers_rot_, rotation_;
+  dev_array<float> centers_hi_, centers_lo_;
+  float centers_max_norm_ = 0.0f;
   dev_array<uint32_t> list_sizes_;
   dev_array<uint64_t> row_off_;
   dev_array<uint8_t> codes_;

@@ -345,6 +345,49 @@ __global__ void merge_parts_kernel(const float* __restrict__ in_dist,
 
 int kpl_for_k(uint32_t k) { return k <= 32 ? 1 : (k <= 64 ? 2 : 4); }
 
+// Process-wide override of the coarse path (diagnostics): 0 automatic, 1 exact SIMT, 2 tensor core.
+int& coarse_mode_ref()
+{
+  static int mode = 0;
+  return mode;
+}
+int coarse_mode() { return coarse_mode_ref(); }
+
+void launch_prep(raft::resources& res, const index<int64_t>& idx, const void* qptr, elem_t qtype,
+                 uint32_t nq, float* d_fq, float* d_rq)
+{
+  const DistanceType metric = idx.metric();
+  const int is_l2  = metric == DistanceType::L2Expanded || metric == DistanceType::L2SqrtExpanded;
+  const int cosine = metric == DistanceType::CosineExpanded;
+  const int ident  = idx.rotation_is_identity();
+  const size_t smem = (size_t(idx.dim()) + idx.rot_dim()) * 4;
+  const int threads = 128;
+  cudaStream_t stream = res.stream;
+  switch (qtype) {
+    case elem_t::f32:
+      prep_queries_kernel<float><<<nq, threads, smem, stream>>>(
+        reinterpret_cast<const float*>(qptr), idx.dim(), idx.dim_ext(), idx.rot_dim(), is_l2, cosine,
+        ident, idx.rotation_matrix(), d_fq, d_rq);
+      break;
+    case elem_t::f16:
+      prep_queries_kernel<__half><<<nq, threads, smem, stream>>>(
+        reinterpret_cast<const __half*>(qptr), idx.dim(), idx.dim_ext(), idx.rot_dim(), is_l2, cosine,
+        ident, idx.rotation_matrix(), d_fq, d_rq);
+      break;
+    case elem_t::i8:
+      prep_queries_kernel<int8_t><<<nq, threads, smem, stream>>>(
+        reinterpret_cast<const int8_t*>(qptr), idx.dim(), idx.dim_ext(), idx.rot_dim(), is_l2, cosine,
+        ident, idx.rotation_matrix(), d_fq, d_rq);
+      break;
+    default:
+      prep_queries_kernel<uint8_t><<<nq, threads, smem, stream>>>(
+        reinterpret_cast<const uint8_t*>(qptr), idx.dim(), idx.dim_ext(), idx.rot_dim(), is_l2, cosine,
+        ident, idx.rotation_matrix(), d_fq, d_rq);
+  }
+  CUDA_TRY(cudaGetLastError());
+  res.launches++;
+}
+
 }  // namespace
 
 // ------------------------------------------------------------------------------------------------
@@ -458,7 +501,10 @@ void search_any(raft::resources& res, const search_params& params, const index<i
   const size_t o_kth     = lay.add(size_t(batch) * 4);
   const size_t o_counter = lay.add(256);
   const size_t o_keys    = lay.add(n_pairs_max * k * 8);
-  const size_t coarse_ws = coarse_workspace_bytes(batch, n_lists, n_probes);
+  const bool use_tc = coarse_mode() != 1 && coarse_tc_usable(n_lists, n_probes, idx.dim_ext());
+  const size_t coarse_ws =
+    use_tc ? coarse_tc_workspace_bytes(batch, n_lists, idx.dim_ext())
+           : coarse_workspace_bytes(batch, n_lists, n_probes);
   const size_t o_coarse  = lay.add(coarse_ws);
   res.ws.reserve(lay.total());
   char* ws = res.ws.base();
@@ -483,39 +529,18 @@ void search_any(raft::resources& res, const search_params& params, const index<i
     if (stats) { res.stats_mark(ev, 0); }
 
     // 1. cast / pad / rotate
-    {
-      const size_t smem = (size_t(idx.dim()) + idx.rot_dim()) * 4;
-      const int threads = 128;
-      const int is_l2_i = is_l2, cos_i = cosine, ident = idx.rotation_is_identity();
-      switch (qtype) {
-        case elem_t::f32:
-          prep_queries_kernel<float><<<nq, threads, smem, stream>>>(
-            reinterpret_cast<const float*>(qptr), idx.dim(), idx.dim_ext(), idx.rot_dim(), is_l2_i,
-            cos_i, ident, idx.rotation_matrix(), d_fq, d_rq);
-          break;
-        case elem_t::f16:
-          prep_queries_kernel<__half><<<nq, threads, smem, stream>>>(
-            reinterpret_cast<const __half*>(qptr), idx.dim(), idx.dim_ext(), idx.rot_dim(), is_l2_i,
-            cos_i, ident, idx.rotation_matrix(), d_fq, d_rq);
-          break;
-        case elem_t::i8:
-          prep_queries_kernel<int8_t><<<nq, threads, smem, stream>>>(
-            reinterpret_cast<const int8_t*>(qptr), idx.dim(), idx.dim_ext(), idx.rot_dim(), is_l2_i,
-            cos_i, ident, idx.rotation_matrix(), d_fq, d_rq);
-          break;
-        default:
-          prep_queries_kernel<uint8_t><<<nq, threads, smem, stream>>>(
-            reinterpret_cast<const uint8_t*>(qptr), idx.dim(), idx.dim_ext(), idx.rot_dim(), is_l2_i,
-            cos_i, ident, idx.rotation_matrix(), d_fq, d_rq);
-      }
-      CUDA_TRY(cudaGetLastError());
-      res.launches++;
-    }
+    launch_prep(res, idx, qptr, qtype, nq, d_fq, d_rq);
 
     if (stats) { res.stats_mark(ev, 1); }
     // 2. coarse selection: probes sorted by (score, list id)
-    select_clusters(res, idx.centers(), n_lists, idx.dim_ext(), is_l2 ? -2.0f : -1.0f, d_fq, nq,
-                    n_probes, d_probes, nullptr, d_coarse, coarse_ws);
+    if (use_tc) {
+      select_clusters_tc(res, idx.centers(), idx.centers_hi(), idx.centers_lo(), idx.centers_max_norm(),
+                         n_lists, idx.dim_ext(), is_l2 ? -2.0f : -1.0f, d_fq, nq, n_probes, d_probes,
+                         nullptr, d_coarse, coarse_ws);
+    } else {
+      select_clusters(res, idx.centers(), n_lists, idx.dim_ext(), is_l2 ? -2.0f : -1.0f, d_fq, nq,
+                      n_probes, d_probes, nullptr, d_coarse, coarse_ws);
+    }
 
     if (stats) { res.stats_mark(ev, 2); }
     // 3. sample offsets + counting sort of pairs by list
@@ -604,6 +629,45 @@ void search_any(raft::resources& res, const search_params& params, const index<i
       res.stats_mark(ev, 5);
       res.pending.push_back(ev);
     }
+  }
+}
+
+void set_coarse_mode(int mode) { coarse_mode_ref() = mode; }
+
+void coarse_only(raft::resources& res, const index<int64_t>& idx, const void* queries, elem_t qtype,
+                 uint32_t n_queries, uint32_t n_probes_in, int mode, uint32_t* probes, float* scores,
+                 uint32_t* status)
+{
+  CUVS_EXPECTS(n_queries > 0 && n_probes_in > 0, "coarse_only: empty request");
+  const uint32_t n_lists  = idx.n_lists();
+  const uint32_t n_probes = std::min(n_probes_in, n_lists);
+  CUVS_EXPECTS(n_probes == n_probes_in, "coarse_only: n_probes exceeds n_lists");
+  const DistanceType metric = idx.metric();
+  const bool is_l2 = metric == DistanceType::L2Expanded || metric == DistanceType::L2SqrtExpanded;
+  const bool tc_ok = coarse_tc_usable(n_lists, n_probes, idx.dim_ext());
+  CUVS_EXPECTS(mode != 2 || tc_ok, "coarse_only: the tensor-core path does not cover this shape");
+  const bool use_tc = mode == 2 || (mode == 0 && tc_ok);
+  ws_layout lay;
+  const size_t o_fq = lay.add(size_t(n_queries) * idx.dim_ext() * 4);
+  const size_t o_rq = lay.add(size_t(n_queries) * idx.rot_dim() * 4);
+  const size_t cws  = use_tc ? coarse_tc_workspace_bytes(n_queries, n_lists, idx.dim_ext())
+                             : coarse_workspace_bytes(n_queries, n_lists, n_probes);
+  const size_t o_c  = lay.add(cws);
+  res.ws.reserve(lay.total());
+  char* ws    = res.ws.base();
+  auto* d_fq  = reinterpret_cast<float*>(ws + o_fq);
+  auto* d_rq  = reinterpret_cast<float*>(ws + o_rq);
+  launch_prep(res, idx, queries, qtype, n_queries, d_fq, d_rq);
+  status[0] = status[1] = 0;
+  if (use_tc) {
+    select_clusters_tc(res, idx.centers(), idx.centers_hi(), idx.centers_lo(), idx.centers_max_norm(),
+                       n_lists, idx.dim_ext(), is_l2 ? -2.0f : -1.0f, d_fq, n_queries, n_probes, probes,
+                       scores, ws + o_c, cws);
+    coarse_tc_status(res, ws + o_c, n_queries, n_lists, idx.dim_ext(), &status[0], &status[1]);
+  } else {
+    select_clusters(res, idx.centers(), n_lists, idx.dim_ext(), is_l2 ? -2.0f : -1.0f, d_fq, n_queries,
+                    n_probes, probes, scores, ws + o_c, cws);
+    res.sync();
   }
 }
 

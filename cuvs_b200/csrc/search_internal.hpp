@@ -21,6 +21,26 @@ void select_clusters(raft::resources& res, const float* centers, uint32_t n_list
                      float alpha, const float* fq, uint32_t n_queries, uint32_t n_probes,
                      uint32_t* probes, float* scores_out, void* workspace, size_t workspace_bytes);
 
+// Tensor-core coarse stage (coarse_tc.cu): same contract and bit-identical probes as
+// select_clusters; `centers_hi/lo` are the TF32 split of `centers`, `cmax` the largest row norm.
+bool coarse_tc_usable(uint32_t n_lists, uint32_t n_probes, uint32_t dim_ext);
+size_t coarse_tc_workspace_bytes(uint32_t n_queries, uint32_t n_lists, uint32_t dim_ext);
+void split_centers_tf32(cudaStream_t stream, const float* centers, size_t n, float* hi, float* lo);
+void select_clusters_tc(raft::resources& res, const float* centers, const float* centers_hi,
+                        const float* centers_lo, float cmax, uint32_t n_lists, uint32_t dim_ext,
+                        float alpha, const float* fq, uint32_t n_queries, uint32_t n_probes,
+                        uint32_t* probes, float* scores_out, void* workspace, size_t workspace_bytes);
+void coarse_tc_status(raft::resources& res, const void* workspace, uint32_t n_queries, uint32_t n_lists,
+                      uint32_t dim_ext, uint32_t* error, uint32_t* n_fallback);
+
+// Probe selection alone (diagnostics / stage-wise tests): mode 0 = automatic, 1 = exact SIMT path,
+// 2 = tensor-core path.  status[0] = error word, status[1] = queries redone exactly (mode 2).
+void coarse_only(raft::resources& res, const index<int64_t>& idx, const void* queries, elem_t qtype,
+                 uint32_t n_queries, uint32_t n_probes, int mode, uint32_t* probes, float* scores,
+                 uint32_t* status);
+
+void set_coarse_mode(int mode);  // process-wide override used by tests: 0 auto, 1 SIMT, 2 tensor core
+
 // Nearest list of every row: labels[i] = argmin_l alpha * sum_k centers[l,k] * x[i,k], ties to the
 // lowest l (equals select_clusters with n_probes = 1).  `best` is scratch of n_rows * 8 bytes.
 void assign_nearest(raft::resources& res, const float* centers, uint32_t n_lists, uint32_t dim_ext,

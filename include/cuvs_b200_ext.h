@@ -33,6 +33,18 @@ CUVS_EXPORT cuvsError_t cuvsB200StatsEnable(cuvsResources_t res, bool enable);
  * optionally reset them. */
 CUVS_EXPORT cuvsError_t cuvsB200StatsGet(cuvsResources_t res, cuvsB200SearchStats* out, bool reset);
 
+/* No counterpart in the reference: run the probe-selection stage alone (for stage-wise checks).
+ * queries f32/f16/i8/u8 [n, dim]; probes u32 [n, n_probes] (ascending by (score, list id));
+ * scores f32 [n, n_probes]; mode 0 = automatic, 1 = exact SIMT path, 2 = tensor-core path;
+ * status[0] = device error word (0 = none), status[1] = queries the tensor-core path had to redo
+ * exactly.  Synchronises the stream. */
+CUVS_EXPORT cuvsError_t cuvsB200CoarseSelect(cuvsResources_t res, void* index /* cuvsIvfPqIndex_t */,
+                                             DLManagedTensor* queries, DLManagedTensor* probes,
+                                             DLManagedTensor* scores, int mode, uint32_t* status);
+/* No counterpart in the reference: force the probe-selection path used by cuvsIvfPqSearch in this
+ * process (0 = automatic, 1 = exact SIMT path, 2 = tensor-core path where it applies). */
+CUVS_EXPORT cuvsError_t cuvsB200SetCoarseMode(int mode);
+
 #ifdef __cplusplus
 }
 #endif

@@ -268,3 +268,67 @@ def test_list_sharded_search_merges_to_the_unsharded_result(ivf, oracle_mod, sma
     # select_max on negated distances gives the same ids (the inner-product direction)
     d2, i2 = mg.merge_parts(-pd, pi, False)
     assert (i2 == i_full).all()
+
+
+# ------------------------------------------------------------------------------------------------
+# probe selection stage alone: exact SIMT path, tensor-core path and the oracle must agree
+# ------------------------------------------------------------------------------------------------
+def coarse_select(index, q, n_probes, mode):
+    import ctypes as C
+    from cuvs_b200 import _lib as L
+    from cuvs_b200.common import DLTensorRef, default_resources
+    res = default_resources()
+    res.use_current_stream()
+    qd = torch.from_numpy(np.ascontiguousarray(q)).cuda()
+    probes = torch.empty((q.shape[0], n_probes), dtype=torch.uint32, device="cuda")
+    scores = torch.empty((q.shape[0], n_probes), dtype=torch.float32, device="cuda")
+    status = (C.c_uint32 * 2)()
+    a, b, c = DLTensorRef(qd), DLTensorRef(probes), DLTensorRef(scores)
+    L.check(L.load().cuvsB200CoarseSelect(res.handle, C.cast(index._h, C.c_void_p), a.ref(), b.ref(),
+                                          c.ref(), mode, status))
+    return probes.cpu().numpy().astype(np.uint32), scores.cpu().numpy(), (status[0], status[1])
+
+
+@pytest.fixture(scope="module")
+def many_lists(ivf):
+    """120,000 x 64 fp32 in 8,192 lists (enough lists for the tensor-core path)."""
+    x = make_mixture(120000, 64, 512, 0.25, seed=70)
+    g = ivf.build(ivf.IndexParams(n_lists=8192, pq_dim=32, kmeans_n_iters=3,
+                                  kmeans_trainset_fraction=0.5), torch.from_numpy(x).cuda())
+    return x, g
+
+
+@pytest.mark.parametrize("nq,n_probes", [(1, 1), (7, 20), (128, 32), (300, 64), (1000, 20)])
+def test_coarse_tensor_core_path_equals_exact_path(ivf, oracle_mod, many_lists, tmp_path, nq, n_probes):
+    x, g = many_lists
+    q = make_mixture(nq, 64, 512, 0.25, seed=71 + nq)
+    p1, s1, st1 = coarse_select(g, q, n_probes, 1)
+    p2, s2, st2 = coarse_select(g, q, n_probes, 2)
+    assert st2[0] == 0, "device-side wait timed out"
+    assert (p1 == p2).all()
+    assert (s1.view(np.uint32) == s2.view(np.uint32)).all()
+    print(f"exact-path fallbacks: {st2[1]} of {nq}")
+    assert st2[1] <= max(1, nq // 20), f"{st2[1]} of {nq} queries fell back to the exact path"
+    # and both equal the oracle's selection on the same model
+    path = str(tmp_path / "many.ivfpq")
+    ivf.save(path, g)
+    ix = oracle_mod.OracleIndex.load(path)
+    fq, _ = oracle_mod.prepare_queries(ix, q)
+    po, so = oracle_mod.select_clusters(ix, fq, n_probes)
+    assert (po == p1).all()
+    assert (so.view(np.uint32) == s1.view(np.uint32)).all()
+
+
+def test_search_is_identical_under_both_coarse_paths(ivf, many_lists):
+    from cuvs_b200 import _lib as L
+    x, g = many_lists
+    q = make_mixture(500, 64, 512, 0.25, seed=80)
+    lib = L.load()
+    try:
+        L.check(lib.cuvsB200SetCoarseMode(1))
+        d1, i1 = gpu_search(ivf, g, q, 10, 24, "f16")
+        L.check(lib.cuvsB200SetCoarseMode(2))
+        d2, i2 = gpu_search(ivf, g, q, 10, 24, "f16")
+    finally:
+        L.check(lib.cuvsB200SetCoarseMode(0))
+    assert (i1 == i2).all() and (d1.view(np.uint32) == d2.view(np.uint32)).all()
