@@ -13,8 +13,10 @@
 //      128-byte swizzle atom).  Per K block three products accumulate into TMEM:
 //      hi*hi + hi*lo + lo*hi.  Warp 0 issues TMA loads (no multicast), warp 1 issues the MMAs,
 //      eight epilogue warps read the accumulator with tcgen05.ld (thread = query row) and keep,
-//      per row and per 128-list half tile, the 8 largest dot products in registers.  Two TMEM
-//      accumulators let the epilogue of one tile overlap the MMAs of the next.
+//      per row and per 128-list half tile, the 8 largest dot products in registers as packed
+//      32-bit keys (order-preserving image of the value, low 7 bits replaced by the column tag)
+//      so that insertion is a branch-free chain of integer max/min.  Two TMEM accumulators let
+//      the epilogue of one tile overlap the MMAs of the next.
 //      Every mbarrier wait is bounded; on a time-out the kernel raises an error word, lets its
 //      in-flight copies land, frees its TMEM and returns.
 //   3. coarse_finish_kernel (one block per query): the C = n_probes + margin best candidates by
@@ -164,8 +166,7 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32])
 // ------------------------------------------------------------------------------------------------
 struct tc_params {
   uint32_t n_queries, n_lists, k_blocks, n_tiles, tile_stride;
-  float* cand_val;     // [n_queries, n_tiles, 2, kKeep] raw dot products (larger = closer)
-  uint32_t* cand_idx;  // same shape, list ids (0xFFFFFFFF = empty slot)
+  uint32_t* cand_key;  // [n_queries, n_tiles, 2, kKeep] packed keys, descending (larger = closer)
   uint32_t* error;     // error word
 };
 
@@ -315,13 +316,11 @@ coarse_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
         break;
       }
       tc_fence_after();
-      float val[kKeep];
-      uint32_t idx[kKeep];
+      // Packed key: order-preserving image of the dot product with its low 7 bits replaced by
+      // (127 - column in the half tile); empty / out-of-range columns are key 0.
+      uint32_t key[kKeep];
 #pragma unroll
-      for (int t = 0; t < kKeep; t++) {
-        val[t] = -INFINITY;
-        idx[t] = 0xFFFFFFFFu;
-      }
+      for (int t = 0; t < kKeep; t++) { key[t] = 0u; }
       const uint32_t col0 = half * kHalf;
       const uint32_t n0   = tile * kBN + col0;
 #pragma unroll 1
@@ -329,24 +328,18 @@ coarse_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
         uint32_t r[32];
         tmem_ld32(tmem_base + ((quarter * 32u) << 16) + acc * kBN + col0 + c, r);
         const uint32_t list0 = n0 + c;
+        const bool full      = list0 + 32 <= p.n_lists;
 #pragma unroll
         for (int e = 0; e < 32; e++) {
-          const float x = __uint_as_float(r[e]);
-          if (list0 + e < p.n_lists && x > val[kKeep - 1]) {
-            // sorted insert (descending); strict '>' keeps the lower list id among equal values
-            float xv    = x;
-            uint32_t xi = list0 + e;
+          const uint32_t u = r[e];
+          uint32_t k = (u ^ (uint32_t(int32_t(u) >> 31) | 0x80000000u)) & ~127u;
+          k |= 127u - (c + uint32_t(e));
+          if (!full && list0 + e >= p.n_lists) { k = 0u; }
 #pragma unroll
-            for (int t = 0; t < kKeep; t++) {
-              if (xv > val[t]) {
-                const float tv    = val[t];
-                const uint32_t ti = idx[t];
-                val[t]            = xv;
-                idx[t]            = xi;
-                xv                = tv;
-                xi                = ti;
-              }
-            }
+          for (int t = 0; t < kKeep; t++) {
+            const uint32_t hi = max(key[t], k);
+            k                 = min(key[t], k);
+            key[t]            = hi;
           }
         }
       }
@@ -355,12 +348,9 @@ coarse_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
       __syncwarp();
       if (lane == 0) { mbar_arrive(bar_tempty + acc * 8); }
       if (q < p.n_queries) {
-        const size_t o = ((size_t(q) * p.n_tiles + tile) * 2 + half) * kKeep;
-#pragma unroll
-        for (int t = 0; t < kKeep; t++) {
-          p.cand_val[o + t] = val[t];
-          p.cand_idx[o + t] = idx[t];
-        }
+        uint4* o = reinterpret_cast<uint4*>(p.cand_key + ((size_t(q) * p.n_tiles + tile) * 2 + half) * kKeep);
+        o[0]     = make_uint4(key[0], key[1], key[2], key[3]);
+        o[1]     = make_uint4(key[4], key[5], key[6], key[7]);
       }
     }
     if (!ok && lane == 0) {
@@ -388,23 +378,26 @@ coarse_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
 // ------------------------------------------------------------------------------------------------
 constexpr uint32_t kMaxC = 1024;
 
+// Key helpers shared with the GEMM epilogue.
+__device__ __forceinline__ bool key_valid(uint32_t key) { return key >= 0x00800000u; }
+__device__ __forceinline__ float key_value(uint32_t key) { return ordered_to_float(key & ~127u); }
+
 __global__ void __launch_bounds__(256)
-coarse_finish_kernel(const float* __restrict__ cand_val, const uint32_t* __restrict__ cand_idx,
-                     uint32_t n_cand /* per query */, const float* __restrict__ centers,
-                     const float* __restrict__ fq, uint32_t n_lists, uint32_t dim_ext, float alpha,
-                     uint32_t n_probes, uint32_t C, uint32_t cap /* pow2 >= C */, float cmax,
-                     uint32_t* __restrict__ probes, float* __restrict__ scores_out,
-                     uint8_t* __restrict__ flags)
+coarse_finish_kernel(const uint32_t* __restrict__ cand_key, uint32_t n_cand /* per query */,
+                     const float* __restrict__ centers, const float* __restrict__ fq,
+                     uint32_t n_lists, uint32_t dim_ext, float alpha, uint32_t n_probes, uint32_t C,
+                     uint32_t cap /* pow2 >= C */, float cmax, uint32_t* __restrict__ probes,
+                     float* __restrict__ scores_out, uint8_t* __restrict__ flags)
 {
   extern __shared__ uint64_t s_keys[];                 // [cap] keys; then the query [dim_ext] floats
   float* s_q = reinterpret_cast<float*>(s_keys + cap);
   __shared__ uint32_t s_hist[256];
   __shared__ uint32_t s_prefix, s_remaining, s_count;
   __shared__ float s_red[8];
-  const uint32_t q   = blockIdx.x;
-  const uint32_t tid = threadIdx.x;
-  const float* val   = cand_val + size_t(q) * n_cand;
-  const uint32_t* id = cand_idx + size_t(q) * n_cand;
+  __shared__ uint32_t s_tb[8];
+  const uint32_t q    = blockIdx.x;
+  const uint32_t tid  = threadIdx.x;
+  const uint32_t* key = cand_key + size_t(q) * n_cand;
 
   float qq = 0.0f;
   for (uint32_t i = tid; i < dim_ext; i += 256) {
@@ -420,7 +413,7 @@ coarse_finish_kernel(const float* __restrict__ cand_val, const uint32_t* __restr
   for (int d = 16; d > 0; d >>= 1) { qq += __shfl_xor_sync(kFullMask, qq, d); }
   if ((tid & 31) == 0) { s_red[tid >> 5] = qq; }
 
-  // radix select of the C LARGEST values: use the order-preserving image of -value
+  // radix select of the C LARGEST keys: ascending order of the complement
   for (int pass = 0; pass < 4; pass++) {
     const int shift = 24 - 8 * pass;
     s_hist[tid]     = 0;
@@ -428,8 +421,9 @@ coarse_finish_kernel(const float* __restrict__ cand_val, const uint32_t* __restr
     const uint32_t prefix = s_prefix;
     const uint32_t mask   = pass == 0 ? 0u : (0xFFFFFFFFu << (shift + 8));
     for (uint32_t i = tid; i < n_cand; i += 256) {
-      if (id[i] == 0xFFFFFFFFu) { continue; }
-      const uint32_t o = float_to_ordered(-val[i]);
+      const uint32_t kk = key[i];
+      if (!key_valid(kk)) { continue; }
+      const uint32_t o = ~kk;
       if ((o & mask) == prefix) { atomicAdd(&s_hist[(o >> shift) & 0xFFu], 1u); }
     }
     __syncthreads();
@@ -449,33 +443,33 @@ coarse_finish_kernel(const float* __restrict__ cand_val, const uint32_t* __restr
     }
     __syncthreads();
   }
-  const uint32_t T = s_prefix;  // ordered image of -(C-th largest value)
+  const uint32_t T = s_prefix;  // complement of the C-th largest key
   if (tid == 0) { s_count = 0; }
   for (uint32_t i = tid; i < cap; i += 256) { s_keys[i] = kEmptyKey; }
   __syncthreads();
-  // gather: everything at least as good as T (ties at T may push the count above C: capped at cap),
-  // and the bound contributed by full half tiles (their last kept value)
-  float tb = -INFINITY;
+  // gather everything at least as good as the threshold, and the bound contributed by full half
+  // tiles (their last kept key: whatever they dropped is not larger)
+  uint32_t tb = 0;
   for (uint32_t i = tid; i < n_cand; i += 256) {
-    const uint32_t l = id[i];
-    if (l == 0xFFFFFFFFu) { continue; }
-    const float v = val[i];
-    if ((i % kKeep) == kKeep - 1) { tb = fmaxf(tb, v); }
-    if (float_to_ordered(-v) <= T) {
+    const uint32_t kk = key[i];
+    if (!key_valid(kk)) { continue; }
+    if ((i % kKeep) == kKeep - 1) { tb = max(tb, kk); }
+    if (~kk <= T) {
       const uint32_t slot = atomicAdd(&s_count, 1u);
-      if (slot < cap) { s_keys[slot] = l; }
+      // list id = tile * 256 + half * 128 + column; i / kKeep enumerates (tile, half)
+      if (slot < cap) { s_keys[slot] = (i / kKeep) * kHalf + (127u - (kk & 127u)); }
     }
   }
 #pragma unroll
-  for (int d = 16; d > 0; d >>= 1) { tb = fmaxf(tb, __shfl_xor_sync(kFullMask, tb, d)); }
-  __shared__ float s_tb[8];
+  for (int d = 16; d > 0; d >>= 1) { tb = max(tb, __shfl_xor_sync(kFullMask, tb, d)); }
   if ((tid & 31) == 0) { s_tb[tid >> 5] = tb; }
   __syncthreads();
-  float tilebound = s_tb[0];
+  uint32_t tile_key = s_tb[0];
 #pragma unroll
-  for (int w = 1; w < 8; w++) { tilebound = fmaxf(tilebound, s_tb[w]); }
-  const uint32_t n_sel    = min(s_count, cap);
-  const bool overflow     = s_count > cap;
+  for (int w = 1; w < 8; w++) { tile_key = max(tile_key, s_tb[w]); }
+  const float tilebound = key_valid(tile_key) ? key_value(tile_key) : -INFINITY;
+  const uint32_t n_sel  = min(s_count, cap);
+  const bool overflow   = s_count > cap;
   // exact rescoring: the defining FMA chain, ascending k
   for (uint32_t i = tid; i < n_sel; i += 256) {
     const uint32_t l = uint32_t(s_keys[i]);
@@ -510,8 +504,10 @@ coarse_finish_kernel(const float* __restrict__ cand_val, const uint32_t* __restr
     float qnorm = 0.0f;
     for (int w = 0; w < 8; w++) { qnorm += s_red[w]; }
     qnorm = sqrtf(qnorm);
-    const float eps       = float(dim_ext + 8) * 2.4e-7f * qnorm * cmax;
-    const float t_c       = -ordered_to_float(T);  // C-th largest tensor-core value
+    // |tensor-core - exact| (accumulation order, dropped lo*lo term) plus the 7 low bits the packed
+    // keys give up (a relative 2^-16 of the value)
+    const float eps       = (float(dim_ext + 8) * 2.4e-7f + 3.1e-5f) * qnorm * cmax;
+    const float t_c       = key_valid(~T) ? key_value(~T) : -INFINITY;  // C-th largest key, as a value
     const float unseen    = fmaxf(t_c, tilebound);
     bool ok               = !overflow && n_sel >= n_probes;
     if (ok) {
@@ -693,8 +689,7 @@ size_t coarse_tc_workspace_bytes(uint32_t n_queries, uint32_t n_lists, uint32_t 
   ws_layout lay;
   lay.add(size_t(n_queries) * dim_ext * 4);  // fq hi
   lay.add(size_t(n_queries) * dim_ext * 4);  // fq lo
-  lay.add(size_t(n_queries) * n_tiles * 2 * kKeep * 4);
-  lay.add(size_t(n_queries) * n_tiles * 2 * kKeep * 4);
+  lay.add(size_t(n_queries) * n_tiles * 2 * kKeep * 4);  // candidate keys
   lay.add(n_queries);                        // flags
   lay.add(256);                              // error word + fallback counter
   lay.add(size_t(64) * n_lists * 4);         // fallback scratch rows
@@ -722,8 +717,7 @@ void select_clusters_tc(raft::resources& res, const float* centers, const float*
   char* ws        = static_cast<char*>(workspace);
   float* fq_hi    = reinterpret_cast<float*>(ws + lay.add(size_t(n_queries) * dim_ext * 4));
   float* fq_lo    = reinterpret_cast<float*>(ws + lay.add(size_t(n_queries) * dim_ext * 4));
-  float* cand_val = reinterpret_cast<float*>(ws + lay.add(size_t(n_queries) * n_cand * 4));
-  auto* cand_idx  = reinterpret_cast<uint32_t*>(ws + lay.add(size_t(n_queries) * n_cand * 4));
+  auto* cand_key  = reinterpret_cast<uint32_t*>(ws + lay.add(size_t(n_queries) * n_cand * 4));
   auto* flags     = reinterpret_cast<uint8_t*>(ws + lay.add(n_queries));
   auto* words     = reinterpret_cast<uint32_t*>(ws + lay.add(256));
   float* scratch  = reinterpret_cast<float*>(ws + lay.add(size_t(64) * n_lists * 4));
@@ -743,8 +737,7 @@ void select_clusters_tc(raft::resources& res, const float* centers, const float*
   p.n_lists   = n_lists;
   p.k_blocks  = ceildiv<uint32_t>(dim_ext, kBK);
   p.n_tiles   = n_tiles;
-  p.cand_val  = cand_val;
-  p.cand_idx  = cand_idx;
+  p.cand_key  = cand_key;
   p.error     = words;
   const uint32_t q_tiles = ceildiv<uint32_t>(n_queries, kBM);
   // list-tile splits per query tile: enough CTAs for a few waves, never more than the tiles
@@ -766,9 +759,9 @@ void select_clusters_tc(raft::resources& res, const float* centers, const float*
   uint32_t cap     = 2;
   while (cap < 2 * C) { cap <<= 1; }  // room for ties at the selection threshold
   const size_t fin_smem = size_t(cap) * 8 + size_t(dim_ext) * 4;
-  coarse_finish_kernel<<<n_queries, 256, fin_smem, stream>>>(cand_val, cand_idx, n_cand, centers, fq,
-                                                             n_lists, dim_ext, alpha, n_probes, C, cap,
-                                                             cmax, probes, scores_out, flags);
+  coarse_finish_kernel<<<n_queries, 256, fin_smem, stream>>>(cand_key, n_cand, centers, fq, n_lists,
+                                                             dim_ext, alpha, n_probes, C, cap, cmax,
+                                                             probes, scores_out, flags);
   uint32_t cap_fb = 2;
   while (cap_fb < n_probes) { cap_fb <<= 1; }
   const size_t fb_smem = size_t(cap_fb) * 8 + size_t(dim_ext) * 4;
@@ -788,7 +781,6 @@ void coarse_tc_status(raft::resources& res, const void* workspace, uint32_t n_qu
   ws_layout lay;
   lay.add(size_t(n_queries) * dim_ext * 4);
   lay.add(size_t(n_queries) * dim_ext * 4);
-  lay.add(size_t(n_queries) * n_tiles * 2 * kKeep * 4);
   lay.add(size_t(n_queries) * n_tiles * 2 * kKeep * 4);
   lay.add(n_queries);
   const size_t o = lay.add(256);
