@@ -38,13 +38,14 @@ if ROOT not in sys.path:
 WORKLOAD = dict(name="deep-embedding-shaped L2, 10M x 96 f32", n_rows=10_000_000, dim=96,
                 n_components=4096, seed=1, n_queries=10_000, n_lists=50_000, pq_dim=48, pq_bits=8,
                 k=10, probes=(20, 50, 100, 200), lut="float16", internal="float32",
-                kmeans_n_iters=10, kmeans_trainset_fraction=0.1)
+                kmeans_n_iters=10, kmeans_trainset_fraction=0.1, refine_ratio=4)
 METRIC = "IVF-PQ search QPS @ recall@10>=0.95"
 FALLBACK_HBM_GBS = 6650.0
 
 
 def log(*a):
-    print(*a, file=sys.stderr, flush=True)
+    if int(os.environ.get("RANK", "0")) == 0:
+        print(*a, file=sys.stderr, flush=True)
 
 
 # --------------------------------------------------------------------------------------------
@@ -203,13 +204,18 @@ def prepare_fixture(wl, device, need_dataset=False):
         open(done, "w").write("ok")
     out["queries"] = torch.from_numpy(np.load(qpath)).to(device)
     out["truth"] = torch.from_numpy(np.load(tpath)).to(device)
+    if need_dataset:      # regenerated from the seeds (refinement reads the original vectors)
+        out["dataset"] = gen_dataset(wl, device)[0]
     return out
 
 
 # --------------------------------------------------------------------------------------------
 # CPU baseline (oracle port), bounded sample
 # --------------------------------------------------------------------------------------------
-def cpu_baseline(index_path, queries_np, wl, n_probes, budget_s=12.0, steps=1, warmup=0):
+def cpu_baseline(index_path, queries_np, wl, n_probes, budget_s=12.0, steps=1, warmup=0,
+                 dataset_np=None):
+    """The CPU port on all host threads: IVF-PQ search for k0 candidates and, when the workload
+    refines, exact re-ranking of those candidates with numpy."""
     from oracle import oracle as O
     t0 = time.time()
     ix = O.OracleIndex.load(index_path)
@@ -218,22 +224,38 @@ def cpu_baseline(index_path, queries_np, wl, n_probes, budget_s=12.0, steps=1, w
     cores = O.lib().orc_num_threads()
     lut = {"float32": O.CUDA_R_32F, "float16": O.CUDA_R_16F, "uint8": O.CUDA_R_8U}[wl["lut"]]
     internal = {"float32": O.CUDA_R_32F, "float16": O.CUDA_R_16F}[wl["internal"]]
+    k = wl["k"]
+    k0 = int(wl["refine_ratio"] * k) if (wl["refine_ratio"] > 1 and dataset_np is not None) else k
+
+    def run(q):
+        d, i = O.search(ix, q, k0, n_probes=n_probes, lut_dtype=lut, internal_dtype=internal)
+        if k0 > k:
+            safe = np.where(i == O.OUT_OF_BOUNDS, 0, i)
+            v = dataset_np[safe]                                   # [n, k0, dim]
+            dd = ((v - q[:, None, :]) ** 2).sum(2)
+            dd = np.where(i == O.OUT_OF_BOUNDS, np.inf, dd)
+            o = np.argsort(dd, axis=1)[:, :k]
+            i = np.take_along_axis(i, o, 1)
+        return i
+
     # size the sample from a probe run
     n0 = min(len(queries_np), max(cores, 32))
     t0 = time.time()
-    O.search(ix, queries_np[:n0], wl["k"], n_probes=n_probes, lut_dtype=lut, internal_dtype=internal)
+    run(queries_np[:n0])
     per_q = (time.time() - t0) / n0
     n = int(min(len(queries_np), max(n0, budget_s / max(per_q, 1e-9))))
     times = []
     for it in range(warmup + steps):
         t0 = time.time()
-        O.search(ix, queries_np[:n], wl["k"], n_probes=n_probes, lut_dtype=lut, internal_dtype=internal)
+        run(queries_np[:n])
         if it >= warmup:
             times.append(time.time() - t0)
     dt = float(np.mean(times))
+    what = f"first {n} of {len(queries_np)} queries, n_probes={n_probes}, k={k}"
+    if k0 > k:
+        what += f", {k0} candidates re-ranked exactly"
     return {"value": n / dt, "unit": "queries/s", "cores": int(cores), "kind": "port",
-            "sample": f"first {n} of {len(queries_np)} queries, n_probes={n_probes}, k={wl['k']}, "
-                      f"same index file; C port of the reference arithmetic, OpenMP over queries"}, dt, n
+            "sample": what + "; same index file; C port of the reference arithmetic, OpenMP over queries"}, dt, n
 
 
 # --------------------------------------------------------------------------------------------
@@ -254,19 +276,27 @@ def hbm_peak():
 DRAM_BYTES_PER_UNIQUE_GROUP = 1799.6
 
 
-def run_ours(args):
-    import torch
-    import torch.distributed as dist
-
-    from cuvs_b200 import _lib as L
-    from cuvs_b200 import ivf_pq, mg
-    from cuvs_b200.common import default_resources
-    import ctypes as C
-
+def workload_from_args(args):
     wl = dict(WORKLOAD)
     if args.rows:
         wl.update(n_rows=args.rows, n_lists=max(64, args.rows // 200),
                   n_queries=min(wl["n_queries"], max(100, args.rows // 100)))
+    if args.refine_ratio is not None:
+        wl["refine_ratio"] = args.refine_ratio
+    return wl
+
+
+def run_ours(args):
+    import ctypes as C
+
+    import torch
+    import torch.distributed as dist
+
+    from cuvs_b200 import _lib as L
+    from cuvs_b200 import ivf_pq, mg, refine
+    from cuvs_b200.common import default_resources
+
+    wl = workload_from_args(args)
     probes = tuple(int(p) for p in args.probes.split(",")) if args.probes else wl["probes"]
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -274,20 +304,27 @@ def run_ours(args):
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
     if world > 1:
+        # keep stdout to the one JSON line (NCCL prints its version banner there at VERSION level)
+        if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
+            os.environ["NCCL_DEBUG"] = "WARN"
         dist.init_process_group("nccl", device_id=device)
     res = default_resources()
     lib = L.load()
+    k = wl["k"]
+    k0 = int(wl["refine_ratio"] * k) if wl["refine_ratio"] > 1 else k
+    refining = k0 > k
 
     # ---- fixture: rank 0 builds (or finds) it, everyone loads its shard ----
     if rank == 0:
-        fx = prepare_fixture(wl, device)
+        fx = prepare_fixture(wl, device, need_dataset=refining)
     if world > 1:
         dist.barrier()
     if rank != 0:
-        fx = prepare_fixture(wl, device)
+        fx = prepare_fixture(wl, device, need_dataset=refining)
     index = mg.load_shard(fx["index_path"], rank, world, res) if world > 1 else ivf_pq.load(fx["index_path"])
     queries, truth = fx["queries"], fx["truth"]
-    nq, k = queries.shape[0], wl["k"]
+    dataset = fx.get("dataset")
+    nq = queries.shape[0]
     lut_dt = {"float32": np.float32, "float16": np.float16, "uint8": np.uint8}[wl["lut"]]
     int_dt = {"float32": np.float32, "float16": np.float16}[wl["internal"]]
 
@@ -295,13 +332,23 @@ def run_ours(args):
         return ivf_pq.SearchParams(n_probes=p, lut_dtype=lut_dt, internal_distance_dtype=int_dt,
                                    max_internal_batch_size=max(nq, 1))
 
+    cand_i = torch.empty((nq, k0), dtype=torch.int64, device=device)
+    cand_d = torch.empty((nq, k0), dtype=torch.float32, device=device)
     out_i = torch.empty((nq, k), dtype=torch.int64, device=device)
     out_d = torch.empty((nq, k), dtype=torch.float32, device=device)
 
-    def one_search(sp):
+    def one_search(sp, q=None):
+        """The whole step: IVF-PQ search for k0 candidates (+ merge across ranks) and, with a
+        refine ratio above 1, exact re-ranking down to k."""
+        q = queries if q is None else q
         if world > 1:
-            return mg.search(sp, index, queries, k, True, None, res, sync=False)
-        return ivf_pq.search(sp, index, queries, k, out_i, out_d, res, sync=False)
+            d, i = mg.search(sp, index, q, k0, True, None, res, sync=False)
+        else:
+            d, i = ivf_pq.search(sp, index, q, k0, cand_i, cand_d, res, sync=False)
+        if refining:
+            d, i = refine(dataset, q, i, k=k, metric="sqeuclidean", indices=out_i, distances=out_d,
+                          resources=res, sync=False)
+        return d, i
 
     def timed(fn, steps, warmup):
         for _ in range(warmup):
@@ -364,6 +411,10 @@ def run_ours(args):
     stage = {k2: round(getattr(stats, k2) / max(1, stats.batches), 4)
              for k2 in ("prep_ms", "coarse_ms", "sort_ms", "scan_ms", "merge_ms")}
     L.check(lib.cuvsB200StatsEnable(res.handle, False))
+    if refining:
+        stage["refine_ms"] = round(timed(lambda: refine(dataset, queries, cand_i, k=k, indices=out_i,
+                                                        distances=out_d, resources=res, sync=False),
+                                         args.steps, 1), 4)
 
     # ---- end to end: pinned host buffers, copies inside the timed region ----
     q_host = queries.cpu().pin_memory()
@@ -373,10 +424,7 @@ def run_ours(args):
 
     def e2e_step():
         q_dev.copy_(q_host, non_blocking=True)
-        if world > 1:
-            d, i = mg.search(sp, index, q_dev, k, True, None, res, sync=False)
-        else:
-            d, i = ivf_pq.search(sp, index, q_dev, k, out_i, out_d, res, sync=False)
+        d, i = one_search(sp, q_dev)
         i_host.copy_(i, non_blocking=True)
         d_host.copy_(d, non_blocking=True)
 
@@ -405,7 +453,8 @@ def run_ours(args):
         "config": {"workload": wl["name"], "n_rows": wl["n_rows"], "dim": wl["dim"],
                    "n_lists": wl["n_lists"], "pq_dim": wl["pq_dim"], "pq_bits": wl["pq_bits"],
                    "k": k, "batch": nq, "n_probes": p_star, "lut_dtype": wl["lut"],
-                   "internal_distance_dtype": wl["internal"], "recall_at_10": chosen["recall_at_10"],
+                   "internal_distance_dtype": wl["internal"], "refine_ratio": wl["refine_ratio"],
+                   "recall_at_10": chosen["recall_at_10"],
                    "recall_target_met": target_met, "sweep": sweep,
                    "parallelism": f"list-sharded x{world}" if world > 1 else "single GPU",
                    "l2": "inputs larger than L2: 480 MB of codes + 80 MB of ids per pass",
@@ -425,7 +474,8 @@ def run_ours(args):
                      "kernel_ms": round(scan_ms, 4)},
     }
     if world == 1 and not args.no_cpu:
-        cb, _, _ = cpu_baseline(fx["index_path"], queries.cpu().numpy(), wl, p_star)
+        cb, _, _ = cpu_baseline(fx["index_path"], queries.cpu().numpy(), wl, p_star,
+                                dataset_np=dataset.cpu().numpy() if refining else None)
         cb["value"] = round(cb["value"], 1)
         line["cpu_baseline"] = cb
     print(json.dumps(line), flush=True)
@@ -439,34 +489,37 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    wl = dict(WORKLOAD)
-    if args.rows:
-        wl.update(n_rows=args.rows, n_lists=max(64, args.rows // 200),
-                  n_queries=min(wl["n_queries"], max(100, args.rows // 100)))
+    wl = workload_from_args(args)
     import torch
     if not torch.cuda.is_available():
         print(json.dumps({"impl": "reference",
                           "unavailable": "the 10M-vector index fixture is built on the GPU; no GPU here"}))
         return
     torch.cuda.set_device(0)
-    fx = prepare_fixture(wl, torch.device("cuda", 0))
+    k = wl["k"]
+    k0 = int(wl["refine_ratio"] * k) if wl["refine_ratio"] > 1 else k
+    fx = prepare_fixture(wl, torch.device("cuda", 0), need_dataset=k0 > k)
     # operating point: the same rule as the GPU arm, evaluated with the GPU search (fixture work)
-    from cuvs_b200 import ivf_pq
+    from cuvs_b200 import ivf_pq, refine
     index = ivf_pq.load(fx["index_path"])
     lut_dt = {"float32": np.float32, "float16": np.float16, "uint8": np.uint8}[wl["lut"]]
     recs = []
     for p in wl["probes"]:
         d, i = ivf_pq.search(ivf_pq.SearchParams(n_probes=p, lut_dtype=lut_dt,
                                                  max_internal_batch_size=fx["queries"].shape[0]),
-                             index, fx["queries"], wl["k"])
+                             index, fx["queries"], k0)
+        if k0 > k:
+            d, i = refine(fx["dataset"], fx["queries"], i, k=k)
         recs.append((p, recall_at_k(i, fx["truth"])))
     ok = [p for p, r in recs if r >= 0.95]
     best = max(r for _, r in recs)
     p_star = ok[0] if ok else [p for p, r in recs if r >= best - 0.005][0]
     del index
+    dataset_np = fx["dataset"].cpu().numpy() if k0 > k else None
+    fx.pop("dataset", None)
     torch.cuda.empty_cache()
     cb, dt, n = cpu_baseline(fx["index_path"], fx["queries"].cpu().numpy(), wl, p_star,
-                             budget_s=8.0, steps=args.steps, warmup=args.warmup)
+                             budget_s=8.0, steps=args.steps, warmup=args.warmup, dataset_np=dataset_np)
     line = {"impl": "reference", "metric": METRIC, "value": round(cb["value"], 1), "unit": "queries/s",
             "n_gpus": int(os.environ.get("WORLD_SIZE", "1")), "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": round(dt * 1e3, 3), "higher_is_better": True, "scaling": "weak",
@@ -474,7 +527,7 @@ def run_reference(args):
             "config": {"workload": wl["name"], "n_rows": wl["n_rows"], "dim": wl["dim"],
                        "n_lists": wl["n_lists"], "pq_dim": wl["pq_dim"], "pq_bits": wl["pq_bits"],
                        "k": wl["k"], "batch": n, "n_probes": p_star, "lut_dtype": wl["lut"],
-                       "internal_distance_dtype": wl["internal"]},
+                       "internal_distance_dtype": wl["internal"], "refine_ratio": wl["refine_ratio"]},
             "cpu_baseline": dict(cb, value=round(cb["value"], 1)),
             "e2e": {"value": round(cb["value"], 1), "unit": "queries/s", "h2d_bytes_per_step": 0,
                     "d2h_bytes_per_step": 0},
@@ -492,6 +545,8 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--probes", default="", help="comma-separated n_probes to sweep (default: the workload's)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end leg (profiling runs)")
+    ap.add_argument("--refine-ratio", type=float, default=None,
+                    help="candidates fetched per result before exact re-ranking (1 = no refinement)")
     args = ap.parse_args()
     args.warmup = max(3, args.warmup)
     if args.impl == "reference":

@@ -9,6 +9,7 @@ from . import _lib
 _lib.load()
 
 from . import ivf_pq  # noqa: E402
+from .refine import refine  # noqa: E402
 from .common import Resources  # noqa: E402
 
-__all__ = ["ivf_pq", "Resources"]
+__all__ = ["ivf_pq", "refine", "Resources"]

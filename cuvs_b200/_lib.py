@@ -121,6 +121,8 @@ SIGNATURES = {
     "cuvsB200StatsEnable": [C.c_size_t, C.c_bool],
     "cuvsB200StatsGet": [C.c_size_t, _P(SearchStats), C.c_bool],
     "cuvsIvfPqPredictNoAlloc": [C.c_size_t, _P(IndexStruct), _P(DLManagedTensor), _P(DLManagedTensor)],
+    "cuvsRefine": [C.c_size_t, _P(DLManagedTensor), _P(DLManagedTensor), _P(DLManagedTensor), C.c_int,
+                   _P(DLManagedTensor), _P(DLManagedTensor)],
     "cuvsIvfPqTransform": [C.c_size_t, _P(IndexStruct), _P(DLManagedTensor), _P(DLManagedTensor),
                            _P(DLManagedTensor)],
 }

@@ -6,6 +6,7 @@
 #include "../../include/cuvs_b200_ext.h"
 #include "../../include/cuvs_ivf_pq.h"
 #include "../../include/cuvs_mg_ivf_pq.h"
+#include "../../include/cuvs_refine.h"
 
 #include "ivf_pq.hpp"
 #include "search_internal.hpp"
@@ -14,6 +15,12 @@
 #include <exception>
 #include <string>
 
+namespace cuvs::neighbors {
+void refine_any(raft::resources& res, const void* dataset, ivf_pq::elem_t dtype, int64_t n_rows,
+                uint32_t dim, const void* queries, uint32_t n_queries, const int64_t* candidates,
+                uint32_t n_cand, ivf_pq::DistanceType metric, int64_t* indices, float* distances,
+                uint32_t k);
+}
 namespace ivf_pq = cuvs::neighbors::ivf_pq;
 using cuvs_b200::fail;
 using index_t = ivf_pq::index<int64_t>;
@@ -669,5 +676,37 @@ extern "C" cuvsError_t cuvsB200SetCoarseMode(int mode)
   return translate_exceptions([=] {
     CUVS_EXPECTS(mode >= 0 && mode <= 2, "mode must be 0, 1 or 2");
     ivf_pq::set_coarse_mode(mode);
+  });
+}
+
+// ------------------------------------------------------------------------------------------------
+// refine (c/src/neighbors/refine.cpp)
+// ------------------------------------------------------------------------------------------------
+extern "C" cuvsError_t cuvsRefine(cuvsResources_t res, DLManagedTensor* dataset, DLManagedTensor* queries,
+                                  DLManagedTensor* candidates, cuvsDistanceType metric,
+                                  DLManagedTensor* indices, DLManagedTensor* distances)
+{
+  return translate_exceptions([=] {
+    CUVS_EXPECTS(dataset && queries && candidates && indices && distances, "null argument");
+    const DLTensor& d = dataset->dl_tensor;
+    const DLTensor& q = queries->dl_tensor;
+    auto et           = elem_of_dtype(d.dtype, "dataset");
+    CUVS_EXPECTS(q.dtype.code == d.dtype.code && q.dtype.bits == d.dtype.bits,
+                 "dataset and queries must have the same element type");
+    void* dd = checked_data(dataset, d.dtype.code, d.dtype.bits, 2, true, "dataset");
+    void* qd = checked_data(queries, q.dtype.code, q.dtype.bits, 2, true, "queries");
+    auto* cd = static_cast<int64_t*>(checked_data(candidates, kDLInt, 64, 2, true, "candidates"));
+    auto* id = static_cast<int64_t*>(checked_data(indices, kDLInt, 64, 2, true, "indices"));
+    auto* dsd = static_cast<float*>(checked_data(distances, kDLFloat, 32, 2, true, "distances"));
+    CUVS_EXPECTS(q.shape[1] == d.shape[1], "dataset and queries must have the same number of columns");
+    CUVS_EXPECTS(candidates->dl_tensor.shape[0] == q.shape[0] && indices->dl_tensor.shape[0] == q.shape[0] &&
+                   distances->dl_tensor.shape[0] == q.shape[0],
+                 "candidates, indices and distances must have one row per query");
+    CUVS_EXPECTS(indices->dl_tensor.shape[1] == distances->dl_tensor.shape[1],
+                 "indices and distances must have the same number of columns");
+    cuvs::neighbors::refine_any(*res_of(res), dd, et, d.shape[0], uint32_t(d.shape[1]), qd,
+                                uint32_t(q.shape[0]), cd, uint32_t(candidates->dl_tensor.shape[1]),
+                                ivf_pq::DistanceType(int(metric)), id, dsd,
+                                uint32_t(indices->dl_tensor.shape[1]));
   });
 }
