@@ -38,7 +38,7 @@ if ROOT not in sys.path:
 WORKLOAD = dict(name="deep-embedding-shaped L2, 10M x 96 f32", n_rows=10_000_000, dim=96,
                 n_components=4096, seed=1, n_queries=10_000, n_lists=50_000, pq_dim=48, pq_bits=8,
                 k=10, probes=(20, 50, 100, 200), lut="float16", internal="float32",
-                kmeans_n_iters=10, kmeans_trainset_fraction=0.1, refine_ratio=4)
+                kmeans_n_iters=10, kmeans_trainset_fraction=0.1, refine_ratio=2)
 METRIC = "IVF-PQ search QPS @ recall@10>=0.95"
 FALLBACK_HBM_GBS = 6650.0
 

@@ -91,7 +91,7 @@ __global__ void refine_kernel(const T* __restrict__ dataset, int64_t n_rows, uin
   }
 #pragma unroll
   for (int r = 0; r < KPL; r++) {
-    const uint32_t pos = lane * KPL + r;
+    const uint32_t pos = uint32_t(r) * 32u + lane;
     if (pos >= k) { continue; }
     const uint64_t key = queue.a[r];
     int64_t id         = ivf_pq::kOutOfBoundsRecord;

@@ -33,16 +33,13 @@ struct scan_params {
   const float* pq_centers;
   const float* centers_rot;
   const uint8_t* codes;
-  const uint32_t* list_sizes;
-  const uint64_t* row_off;
   uint32_t pq_dim, pq_len, rot_dim, n_pieces;
   int per_cluster;
   int cosine;
   // batch
   const float* rot_q;           // [n_q, rot_dim]
-  const uint32_t* probes;       // [n_q, n_probes]
-  const uint32_t* chunk_index;  // [n_q, n_probes] inclusive prefix sums of probed list sizes
-  const uint32_t* pair_order;   // [n_pairs] pair ids (q * n_probes + p) ordered by list
+  const uint4* work;            // [n_pairs][2] descriptors ordered by list: {pair, query, list, size},
+                                //   {sample offset, first row lo, first row hi, 0}
   uint32_t n_pairs, n_probes, k;
   uint32_t* query_kth;  // [n_q] ordered-score bound, starts at 0xFFFFFFFF
   uint64_t* out_keys;   // [n_q, n_probes, k]
@@ -335,7 +332,7 @@ __global__ void __launch_bounds__(1024, 1) scan_kernel(const scan_params p)
   float* s_base     = reinterpret_cast<float*>(gbase + p.lut_bytes);
   uint64_t* s_merge = reinterpret_cast<uint64_t*>(gbase + p.lut_bytes + p.base_bytes);
   uint32_t* s_item  = reinterpret_cast<uint32_t*>(gbase + p.lut_bytes + p.base_bytes + p.merge_bytes);
-  uint32_t* s_thr   = s_item + 1;  // group-wide bound on the k-th best ordered score of this pair
+  uint32_t* s_thr   = s_item + 2;  // group-wide bound on the k-th best ordered score of this pair
 
   if (p.pqc_in_smem) {
     const uint32_t n4 = (p.pq_dim * p.pq_len * kBook) / 4;
@@ -349,25 +346,28 @@ __global__ void __launch_bounds__(1024, 1) scan_kernel(const scan_params p)
   const uint32_t k       = p.k;
   warp_topk<KPL> queue;
 
-  for (;;) {
-    if (gt == 0) { *s_item = atomicAdd(p.work_counter, 1u); }
+  // The next work item is claimed one pair ahead so that the atomic's latency is hidden.
+  if (gt == 0) { s_item[0] = atomicAdd(p.work_counter, 1u); }
+  for (uint32_t it = 0;; it++) {
     group_bar(bar_id, gthreads);
-    const uint32_t w = *s_item;
+    const uint32_t w = s_item[it & 1u];
     if (w >= p.n_pairs) { break; }
+    if (gt == 0) { s_item[(it + 1u) & 1u] = atomicAdd(p.work_counter, 1u); }
 
-    const uint32_t pair  = p.pair_order ? p.pair_order[w] : w;
-    const uint32_t q     = pair / p.n_probes;
-    const uint32_t pi    = pair - q * p.n_probes;
-    const uint32_t label = p.probes[pair];
-    const uint32_t n     = p.list_sizes[label];
+    const uint4 d0       = __ldg(p.work + 2 * size_t(w));
+    const uint4 d1       = __ldg(p.work + 2 * size_t(w) + 1);
+    const uint32_t pair  = d0.x;
+    const uint32_t q     = d0.y;
+    const uint32_t label = d0.z;
+    const uint32_t n     = d0.w;
+    const uint32_t sample_offset = d1.x;
+    const uint64_t first_row     = (uint64_t(d1.z) << 32) | d1.y;
     uint64_t* out        = p.out_keys + size_t(pair) * k;
 
     if (n == 0) {
       for (uint32_t i = gt; i < k; i += gthreads) { out[i] = kEmptyKey; }
-      group_bar(bar_id, gthreads);  // keeps s_item stable until every thread has read it
       continue;
     }
-    const uint32_t sample_offset = pi > 0 ? p.chunk_index[pair - 1] : 0u;
 
     // ---- base diff ----
     if (gt == 0) { *s_thr = *reinterpret_cast<volatile uint32_t*>(p.query_kth + q); }
@@ -384,6 +384,14 @@ __global__ void __launch_bounds__(1024, 1) scan_kernel(const scan_params p)
       }
     }
     group_bar(bar_id, gthreads);
+
+    // The first 16-byte piece of this warp's first group is requested now, so that its latency
+    // hides behind the LUT build; afterwards each piece is requested one piece ahead of its use.
+    const uint32_t n_groups = (n + 31u) >> 5;
+    const uint4* src = reinterpret_cast<const uint4*>(p.codes + first_row * size_t(p.n_pieces) * 16u) +
+                       size_t(gw) * p.n_pieces * 32u + lane;
+    uint4 nxt = make_uint4(0u, 0u, 0u, 0u);
+    if (uint32_t(gw) < n_groups) { nxt = __ldg(src); }
 
     // ---- LUT ----
     if (p.pqc_in_smem) {
@@ -438,25 +446,26 @@ __global__ void __launch_bounds__(1024, 1) scan_kernel(const scan_params p)
     // ---- scan ----
     queue.init(int(k));
     {
-      const uint32_t n_groups   = (n + 31u) >> 5;
-      const uint32_t lut_base_a = smem_addr(s_lut);
-      const uint4* list =
-        reinterpret_cast<const uint4*>(p.codes + p.row_off[label] * size_t(p.n_pieces) * 16u);
-      for (uint32_t gi = gw; gi < n_groups; gi += n_gwarps) {
-        const uint4* src = list + size_t(gi) * p.n_pieces * 32u + lane;
+      const uint32_t lut_base_a   = smem_addr(s_lut);
+      const uint32_t group_stride = uint32_t(n_gwarps) * p.n_pieces * 32u;  // in 16-byte pieces
+      constexpr uint32_t kPieceLutBytes = uint32_t(kPerPiece) * kBook * uint32_t(sizeof(lut_t));
+      for (uint32_t gi = gw; gi < n_groups; gi += n_gwarps, src += group_stride) {
         accum<LutKind, OutHalf, IsIP> acc;
         acc.init();
-        constexpr uint32_t kPieceLutBytes = uint32_t(kPerPiece) * kBook * uint32_t(sizeof(lut_t));
         uint32_t row_a = lut_base_a;
         uint32_t j0    = 0;
-        uint32_t c     = 0;
-        for (; j0 + kPerPiece <= p.pq_dim; j0 += kPerPiece, c++, row_a += kPieceLutBytes) {
-          const uint4 v = __ldg(src + c * 32u);
-          score_piece<PqBits, LutKind, OutHalf, IsIP, true>(acc, v, row_a, 0);
-        }
-        if (j0 < p.pq_dim) {
-          const uint4 v = __ldg(src + c * 32u);
-          score_piece<PqBits, LutKind, OutHalf, IsIP, false>(acc, v, row_a, p.pq_dim - j0);
+        for (uint32_t c = 0; c < p.n_pieces; c++, j0 += kPerPiece, row_a += kPieceLutBytes) {
+          const uint4 v = nxt;
+          if (c + 1 < p.n_pieces) {
+            nxt = __ldg(src + (c + 1) * 32u);
+          } else if (gi + n_gwarps < n_groups) {
+            nxt = __ldg(src + group_stride);
+          }
+          if (j0 + kPerPiece <= p.pq_dim) {
+            score_piece<PqBits, LutKind, OutHalf, IsIP, true>(acc, v, row_a, 0);
+          } else {
+            score_piece<PqBits, LutKind, OutHalf, IsIP, false>(acc, v, row_a, p.pq_dim - j0);
+          }
         }
         const float score    = acc.result(p.cosine != 0);
         const uint32_t row   = gi * 32u + lane;

@@ -210,13 +210,24 @@ __global__ void scan_stats_kernel(const uint32_t* __restrict__ list_count,
   }
 }
 
-__global__ void scatter_pairs_kernel(const uint32_t* __restrict__ probes, uint32_t n_pairs,
-                                     uint32_t* __restrict__ cursor, uint32_t* __restrict__ pair_order)
+// Work list of the scan kernel, ordered by list: one 32-byte descriptor per (query, probe) pair
+// {pair id, query, list, list size, sample offset, first row of the list (lo, hi), 0}.
+__global__ void scatter_pairs_kernel(const uint32_t* __restrict__ probes,
+                                     const uint32_t* __restrict__ chunk_index,
+                                     const uint32_t* __restrict__ list_sizes,
+                                     const uint64_t* __restrict__ row_off, uint32_t n_pairs,
+                                     uint32_t n_probes, uint32_t* __restrict__ cursor,
+                                     uint4* __restrict__ work)
 {
   const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n_pairs) { return; }
-  const uint32_t pos = atomicAdd(cursor + probes[i], 1u);
-  pair_order[pos]    = i;
+  const uint32_t label = probes[i];
+  const uint32_t q     = i / n_probes;
+  const uint32_t pi    = i - q * n_probes;
+  const uint32_t pos   = atomicAdd(cursor + label, 1u);
+  const uint64_t ro    = row_off[label];
+  work[2 * size_t(pos)]     = make_uint4(i, q, label, list_sizes[label]);
+  work[2 * size_t(pos) + 1] = make_uint4(pi > 0 ? chunk_index[i - 1] : 0u, uint32_t(ro), uint32_t(ro >> 32), 0u);
 }
 
 __global__ void fill_u32_kernel(uint32_t* p, size_t n, uint32_t v)
@@ -268,7 +279,7 @@ __global__ void final_merge_kernel(const uint64_t* __restrict__ keys,
   const uint32_t* pr = probes + size_t(q) * n_probes;
 #pragma unroll
   for (int r = 0; r < KPL; r++) {
-    const uint32_t pos = lane * KPL + r;
+    const uint32_t pos = uint32_t(r) * 32u + lane;
     if (pos >= k) { continue; }
     const uint64_t key = queue.a[r];
     int64_t id         = kOutOfBoundsRecord;
@@ -326,7 +337,7 @@ __global__ void merge_parts_kernel(const float* __restrict__ in_dist,
   }
 #pragma unroll
   for (int r = 0; r < KPL; r++) {
-    const uint32_t pos = lane * KPL + r;
+    const uint32_t pos = uint32_t(r) * 32u + lane;
     if (pos >= k) { continue; }
     const uint64_t key = queue.a[r];
     int64_t id         = kOutOfBoundsRecord;
@@ -496,7 +507,7 @@ void search_any(raft::resources& res, const search_params& params, const index<i
   const size_t o_rq      = lay.add(size_t(batch) * idx.rot_dim() * 4);
   const size_t o_probes  = lay.add(n_pairs_max * 4);
   const size_t o_chunk   = lay.add(n_pairs_max * 4);
-  const size_t o_order   = lay.add(n_pairs_max * 4);
+  const size_t o_order   = lay.add(n_pairs_max * 32);
   const size_t o_count   = lay.add((size_t(n_lists) + 1) * 4);
   const size_t o_kth     = lay.add(size_t(batch) * 4);
   const size_t o_counter = lay.add(256);
@@ -512,7 +523,7 @@ void search_any(raft::resources& res, const search_params& params, const index<i
   auto* d_rq      = reinterpret_cast<float*>(ws + o_rq);
   auto* d_probes  = reinterpret_cast<uint32_t*>(ws + o_probes);
   auto* d_chunk   = reinterpret_cast<uint32_t*>(ws + o_chunk);
-  auto* d_order   = reinterpret_cast<uint32_t*>(ws + o_order);
+  auto* d_order   = reinterpret_cast<uint4*>(ws + o_order);
   auto* d_count   = reinterpret_cast<uint32_t*>(ws + o_count);
   auto* d_kth     = reinterpret_cast<uint32_t*>(ws + o_kth);
   auto* d_counter = reinterpret_cast<uint32_t*>(ws + o_counter);
@@ -553,8 +564,8 @@ void search_any(raft::resources& res, const search_params& params, const index<i
       res.stat_pairs += n_pairs;
     }
     exclusive_scan_kernel<<<1, 1024, 0, stream>>>(d_count, n_lists);
-    scatter_pairs_kernel<<<ceildiv<uint32_t>(n_pairs, 256), 256, 0, stream>>>(d_probes, n_pairs,
-                                                                              d_count, d_order);
+    scatter_pairs_kernel<<<ceildiv<uint32_t>(n_pairs, 256), 256, 0, stream>>>(
+      d_probes, d_chunk, idx.list_sizes(), idx.row_offsets(), n_pairs, n_probes, d_count, d_order);
     fill_u32_kernel<<<ceildiv<uint32_t>(nq, 256), 256, 0, stream>>>(d_kth, nq, kEmptyScore);
     CUDA_TRY(cudaMemsetAsync(d_counter, 0, 4, stream));
     CUDA_TRY(cudaGetLastError());
@@ -567,8 +578,6 @@ void search_any(raft::resources& res, const search_params& params, const index<i
       sp.pq_centers     = idx.pq_centers();
       sp.centers_rot    = idx.centers_rot();
       sp.codes          = idx.codes();
-      sp.list_sizes     = idx.list_sizes();
-      sp.row_off        = idx.row_offsets();
       sp.pq_dim         = idx.pq_dim();
       sp.pq_len         = idx.pq_len();
       sp.rot_dim        = idx.rot_dim();
@@ -576,9 +585,7 @@ void search_any(raft::resources& res, const search_params& params, const index<i
       sp.per_cluster    = idx.codebook_kind() == codebook_gen::PER_CLUSTER;
       sp.cosine         = cosine;
       sp.rot_q          = d_rq;
-      sp.probes         = d_probes;
-      sp.chunk_index    = d_chunk;
-      sp.pair_order     = d_order;
+      sp.work           = d_order;
       sp.n_pairs        = n_pairs;
       sp.n_probes       = n_probes;
       sp.k              = k;

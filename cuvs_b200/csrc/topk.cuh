@@ -5,8 +5,9 @@
 // path is a total order and the results do not depend on scheduling.
 //
 // warp_topk<KPL> keeps the 32*KPL smallest keys seen so far, sorted ascending across the warp:
-// position p lives in register a[p % KPL] of lane p / KPL.  Insertion is a warp-wide shift; callers
-// pre-filter against kth() so that, after warm-up, almost no candidate reaches insert().
+// position p lives in register a[p / 32] of lane p % 32.  A few candidates are inserted one by
+// one (a warp-wide shift); many at once are merged as a sorted batch (bitonic networks).  Callers
+// pre-filter against kth() so that, after warm-up, almost no candidate reaches either path.
 #pragma once
 
 #include <cstdint>
@@ -76,14 +77,16 @@ struct warp_topk {
   // Insert a warp-uniform key c with c < kth().
   __device__ __forceinline__ void insert(uint64_t c)
   {
-    const int lane   = threadIdx.x & 31;
-    uint64_t up_last = shfl_up_u64(a[KPL - 1], 1);
-    if (lane == 0) { up_last = 0; }
+    const int lane = threadIdx.x & 31;
+    uint64_t carry = 0;  // key preceding this row (last key of the previous row)
 #pragma unroll
-    for (int r = KPL - 1; r >= 0; r--) {
-      uint64_t prev = (r == 0) ? up_last : a[r - 1];
-      uint64_t cur  = a[r];
-      a[r]          = (cur <= c) ? cur : (prev > c ? prev : c);
+    for (int r = 0; r < KPL; r++) {
+      const uint64_t cur  = a[r];
+      uint64_t prev       = shfl_up_u64(cur, 1);
+      const uint64_t last = shfl_u64(cur, 31);
+      if (lane == 0) { prev = carry; }
+      a[r]  = (cur <= c) ? cur : (prev > c ? prev : c);
+      carry = last;
     }
     refresh_kth();
   }
@@ -93,14 +96,26 @@ struct warp_topk {
     uint64_t mine = a[0];
 #pragma unroll
     for (int r = 1; r < KPL; r++) {
-      if ((pos % KPL) == r) { mine = a[r]; }
+      if ((pos >> 5) == r) { mine = a[r]; }
     }
-    kth_ = shfl_u64(mine, pos / KPL);
+    kth_ = shfl_u64(mine, pos & 31);
   }
 
-  // Merge a whole batch (one key per lane, kEmptyKey where there is none) into the queue:
-  // sort the batch across the warp, keep the 32 smallest of (queue, batch), re-sort.
-  // Only for KPL == 1 (the queue is one key per lane).
+  // Bitonic merge step over the 32 lanes of one register: v holds a bitonic sequence -> ascending.
+  static __device__ __forceinline__ uint64_t bitonic_finish(uint64_t v)
+  {
+    const int lane = threadIdx.x & 31;
+#pragma unroll
+    for (int j = 16; j > 0; j >>= 1) {
+      const uint64_t o = shfl_u64(v, lane ^ j);
+      v                = ((lane & j) == 0) ? (o < v ? o : v) : (o > v ? o : v);
+    }
+    return v;
+  }
+
+  // Merge a whole batch (one key per lane, kEmptyKey where there is none) into the queue: sort the
+  // batch across the warp, then row by row split (row, batch) into the 32 smallest (stay in the
+  // row) and the 32 largest (carried to the next row).
   __device__ __forceinline__ void merge_batch(uint64_t b)
   {
     const int lane = threadIdx.x & 31;
@@ -113,16 +128,16 @@ struct warp_topk {
         b                   = keep_min ? (o < b ? o : b) : (o > b ? o : b);
       }
     }
-    b = shfl_u64(b, 31 - lane);  // descending
-    // ascending queue against descending batch: the element-wise minimum is a bitonic sequence
-    // that holds the 32 smallest keys of the union
-    uint64_t v = a[0] < b ? a[0] : b;
 #pragma unroll
-    for (int j = 16; j > 0; j >>= 1) {
-      const uint64_t o = shfl_u64(v, lane ^ j);
-      v                = ((lane & j) == 0) ? (o < v ? o : v) : (o > v ? o : v);
+    for (int r = 0; r < KPL; r++) {
+      const uint64_t rev = shfl_u64(b, 31 - lane);  // descending
+      // ascending row against descending batch: element-wise min / max are both bitonic and hold
+      // the 32 smallest / 32 largest keys of the union
+      const uint64_t lo = a[r] < rev ? a[r] : rev;
+      const uint64_t hi = a[r] < rev ? rev : a[r];
+      a[r]              = bitonic_finish(lo);
+      if (r + 1 < KPL) { b = bitonic_finish(hi); }
     }
-    a[0] = v;
     refresh_kth();
   }
 
@@ -132,7 +147,7 @@ struct warp_topk {
     const bool pass = valid && key < kth_;
     unsigned m      = __ballot_sync(kFullMask, pass);
     if (m == 0) { return; }
-    if (KPL == 1 && __popc(m) > 3) {
+    if (__popc(m) > 2 + 2 * KPL) {
       merge_batch(pass ? key : kEmptyKey);
       return;
     }
@@ -144,23 +159,15 @@ struct warp_topk {
     }
   }
 
-  // Key at sorted position p (p < 32*KPL), valid on the lane that owns it; use with owner(p).
-  __device__ __forceinline__ uint64_t at_local(int r) const
-  {
-    uint64_t v = a[0];
-#pragma unroll
-    for (int i = 1; i < KPL; i++) {
-      if (i == r) { v = a[i]; }
-    }
-    return v;
-  }
+  // Sorted position of register r on this lane.
+  static __device__ __forceinline__ uint32_t position(int r) { return uint32_t(r) * 32u + (threadIdx.x & 31); }
+
   // Store the first n sorted keys to dst[0..n).
   __device__ __forceinline__ void store(uint64_t* dst, int n) const
   {
-    const int lane = threadIdx.x & 31;
 #pragma unroll
     for (int r = 0; r < KPL; r++) {
-      int p = lane * KPL + r;
+      const int p = int(position(r));
       if (p < n) { dst[p] = a[r]; }
     }
   }
