@@ -287,6 +287,19 @@ void select_clusters(raft::resources& res, const float* centers, uint32_t n_list
   }
 }
 
+void select_rows(raft::resources& res, const float* rows, uint32_t n_rows, uint32_t row_len, uint32_t k,
+                 uint32_t* out_idx, float* out_scores)
+{
+  CUVS_EXPECTS(k <= kMaxProbes && k <= row_len, "select_rows: k = %u out of range", k);
+  if (n_rows == 0) { return; }
+  uint32_t cap = 2;
+  while (cap < k) { cap <<= 1; }
+  select_probes_kernel<<<n_rows, 256, size_t(cap) * 8, res.stream>>>(rows, row_len, k, cap, out_idx,
+                                                                     out_scores);
+  CUDA_TRY(cudaGetLastError());
+  res.launches++;
+}
+
 void assign_nearest(raft::resources& res, const float* centers, uint32_t n_lists, uint32_t dim_ext,
                     float alpha, const float* x_ext, uint32_t n_rows, uint32_t* labels,
                     unsigned long long* best)

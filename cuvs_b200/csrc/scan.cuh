@@ -43,6 +43,8 @@ struct scan_params {
   uint32_t n_pairs, n_probes, k;
   uint32_t* query_kth;  // [n_q] ordered-score bound, starts at 0xFFFFFFFF
   uint64_t* out_keys;   // [n_q, n_probes, k]
+  float* all_scores;    // store-all mode (KPL == 0): [n_q, max_samples] every score, no top-k
+  uint32_t max_samples;
   uint32_t* work_counter;
   // shared memory plan
   uint32_t n_groups, group_threads;
@@ -344,7 +346,8 @@ __global__ void __launch_bounds__(1024, 1) scan_kernel(const scan_params p)
 
   const uint32_t len     = p.pq_len;
   const uint32_t k       = p.k;
-  warp_topk<KPL> queue;
+  constexpr bool kStoreAll = KPL == 0;  // k too large for registers: write every score instead
+  warp_topk<(KPL > 0 ? KPL : 1)> queue;
 
   // The next work item is claimed one pair ahead so that the atomic's latency is hidden.
   if (gt == 0) { s_item[0] = atomicAdd(p.work_counter, 1u); }
@@ -365,7 +368,9 @@ __global__ void __launch_bounds__(1024, 1) scan_kernel(const scan_params p)
     uint64_t* out        = p.out_keys + size_t(pair) * k;
 
     if (n == 0) {
-      for (uint32_t i = gt; i < k; i += gthreads) { out[i] = kEmptyKey; }
+      if constexpr (!kStoreAll) {
+        for (uint32_t i = gt; i < k; i += gthreads) { out[i] = kEmptyKey; }
+      }
       continue;
     }
 
@@ -470,16 +475,21 @@ __global__ void __launch_bounds__(1024, 1) scan_kernel(const scan_params p)
         const float score    = acc.result(p.cosine != 0);
         const uint32_t row   = gi * 32u + lane;
         const bool valid     = row < n;
-        const uint32_t ord   = float_to_ordered(score);
-        const uint64_t key   = (uint64_t(ord) << 32) | (sample_offset + row);
-        // s_thr never exceeds the final k-th best score of the query, so nothing wanted is lost
-        const uint32_t thr   = *reinterpret_cast<volatile uint32_t*>(s_thr);
-        const uint64_t before = queue.kth();
-        queue.offer(key, valid && ord <= thr);
-        if (queue.kth() != before && lane == 0) { atomicMin(s_thr, uint32_t(queue.kth() >> 32)); }
+        if constexpr (kStoreAll) {
+          if (valid) { p.all_scores[size_t(q) * p.max_samples + sample_offset + row] = score; }
+        } else {
+          const uint32_t ord   = float_to_ordered(score);
+          const uint64_t key   = (uint64_t(ord) << 32) | (sample_offset + row);
+          // s_thr never exceeds the final k-th best score of the query, so nothing wanted is lost
+          const uint32_t thr   = *reinterpret_cast<volatile uint32_t*>(s_thr);
+          const uint64_t before = queue.kth();
+          queue.offer(key, valid && ord <= thr);
+          if (queue.kth() != before && lane == 0) { atomicMin(s_thr, uint32_t(queue.kth() >> 32)); }
+        }
       }
     }
 
+    if constexpr (!kStoreAll) {
     // ---- merge the warps' queues, write k keys ----
     queue.store(s_merge + size_t(gw) * k, int(k));
     group_bar(bar_id, gthreads);
@@ -493,6 +503,7 @@ __global__ void __launch_bounds__(1024, 1) scan_kernel(const scan_params p)
       queue.store(out, int(k));
       const uint32_t kth_score = uint32_t(queue.kth() >> 32);
       if (lane == 0 && kth_score != kEmptyScore) { atomicMin(p.query_kth + q, kth_score); }
+    }
     }
     // the barrier at the top of the loop orders warp 0's reads of s_merge before the next writes
   }

@@ -27,6 +27,7 @@ template <int LutKind, bool OutHalf, bool IsIP>
 void launch_kpl(const scan_params& p, int kpl, int grid, size_t smem, cudaStream_t stream)
 {
   switch (kpl) {
+    case 0: launch_one<LutKind, OutHalf, IsIP, 0>(p, grid, smem, stream); break;
     case 1: launch_one<LutKind, OutHalf, IsIP, 1>(p, grid, smem, stream); break;
     case 2: launch_one<LutKind, OutHalf, IsIP, 2>(p, grid, smem, stream); break;
     default: launch_one<LutKind, OutHalf, IsIP, 4>(p, grid, smem, stream); break;

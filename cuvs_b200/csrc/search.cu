@@ -306,6 +306,49 @@ __global__ void final_merge_kernel(const uint64_t* __restrict__ keys,
   }
 }
 
+// Store-all path (k > 128): selected (score, sample index) pairs -> ids and final distances.
+__global__ void translate_selected_kernel(const float* __restrict__ sel_scores,
+                                          const uint32_t* __restrict__ sel_idx,
+                                          const uint32_t* __restrict__ probes,
+                                          const uint32_t* __restrict__ chunk_index,
+                                          const uint64_t* __restrict__ row_off,
+                                          const int64_t* __restrict__ ids, uint32_t n_queries,
+                                          uint32_t n_probes, uint32_t k, int metric, float scale,
+                                          int64_t* __restrict__ neighbors, float* __restrict__ distances)
+{
+  const uint64_t i = blockIdx.x * uint64_t(blockDim.x) + threadIdx.x;
+  if (i >= uint64_t(n_queries) * k) { return; }
+  const uint32_t q   = uint32_t(i / k);
+  const uint32_t* ci = chunk_index + size_t(q) * n_probes;
+  const uint32_t* pr = probes + size_t(q) * n_probes;
+  uint32_t sample    = sel_idx[i];
+  float score        = sel_scores[i];
+  int64_t id         = kOutOfBoundsRecord;
+  uint32_t lo = 0, hi = n_probes;
+  while (lo < hi) {
+    uint32_t mid = (lo + hi) >> 1;
+    if (ci[mid] <= sample) {
+      lo = mid + 1;
+    } else {
+      hi = mid;
+    }
+  }
+  if (lo < n_probes && score < INFINITY) {
+    if (lo > 0) { sample -= ci[lo - 1]; }
+    id = ids[row_off[pr[lo]] + sample];
+  } else {
+    score = INFINITY;
+  }
+  neighbors[i] = id;
+  distances[i] = postprocess_distance(score, metric, scale);
+}
+
+__global__ void fill_f32_kernel(float* p, size_t n, float v)
+{
+  size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x;
+  if (i < n) { p[i] = v; }
+}
+
 // knn_merge_parts (cpp/src/neighbors/detail/knn_merge_parts.cuh:24-97): one warp per query.
 template <int KPL>
 __global__ void merge_parts_kernel(const float* __restrict__ in_dist,
@@ -470,8 +513,10 @@ void search_any(raft::resources& res, const search_params& params, const index<i
                "Unexpected lut_dtype / internal_distance_dtype combination (%d, %d). Size of the "
                "internal_distance_dtype should be not smaller than the size of the lut_dtype.",
                int(params.lut_dtype), int(params.internal_distance_dtype));
-  CUVS_EXPECTS(k <= 128,
-               "k = %u: this engine keeps the top-k in registers and supports k <= 128", k);
+  CUVS_EXPECTS(k <= 4096, "k = %u: this engine supports k <= 4096", k);
+  // k <= 128: top-k fused into the scan (registers).  Larger k: the scan stores every score and a
+  // separate selection follows (the reference's non-fused mode, ivf_pq_compute_similarity_impl.cuh:34-45).
+  const bool store_all = k > 128;
   if (n_queries == 0) { return; }
   {
     cudaPointerAttributes a{};
@@ -491,13 +536,21 @@ void search_any(raft::resources& res, const search_params& params, const index<i
   const bool is_l2  = metric == DistanceType::L2Expanded || metric == DistanceType::L2SqrtExpanded;
   const bool is_ip  = !is_l2;
   const bool cosine = metric == DistanceType::CosineExpanded;
-  const int kpl     = kpl_for_k(k);
+  const int kpl     = store_all ? 0 : kpl_for_k(k);
   const float scale = qtype == elem_t::u8 ? 256.0f : (qtype == elem_t::i8 ? 128.0f : 1.0f);
   CUVS_EXPECTS(uint64_t(idx.accum_sorted_sizes()[n_probes]) <= 0xFFFFFFFFull,
                "The maximum sample size is too big.");
 
-  const scan_plan plan = plan_scan(res, idx, lut_kind, is_ip, k);
-  const uint32_t batch = std::min<uint32_t>(n_queries, std::max<uint32_t>(1, params.max_internal_batch_size));
+  const scan_plan plan = plan_scan(res, idx, lut_kind, is_ip, store_all ? 1 : k);
+  uint32_t batch = std::min<uint32_t>(n_queries, std::max<uint32_t>(1, params.max_internal_batch_size));
+  // worst-case samples per query: the n_probes largest lists (ivf_pq_search.cuh:934-940)
+  const uint32_t max_samples =
+    round_up<uint32_t>(std::max<uint32_t>(uint32_t(idx.accum_sorted_sizes()[n_probes]), k), 128);
+  if (store_all) {
+    // keep the score matrix of one internal batch within 1 GiB
+    const uint64_t cap_q = std::max<uint64_t>(1, (1ull << 30) / (uint64_t(max_samples) * 4));
+    batch                = uint32_t(std::min<uint64_t>(batch, cap_q));
+  }
   const size_t n_pairs_max = size_t(batch) * n_probes;
   CUVS_EXPECTS(n_pairs_max < (1ull << 31), "max_internal_batch_size * n_probes is too large");
 
@@ -511,7 +564,8 @@ void search_any(raft::resources& res, const search_params& params, const index<i
   const size_t o_count   = lay.add((size_t(n_lists) + 1) * 4);
   const size_t o_kth     = lay.add(size_t(batch) * 4);
   const size_t o_counter = lay.add(256);
-  const size_t o_keys    = lay.add(n_pairs_max * k * 8);
+  const size_t o_keys    = lay.add(store_all ? size_t(batch) * k * 8 : n_pairs_max * k * 8);
+  const size_t o_all     = lay.add(store_all ? size_t(batch) * max_samples * 4 : 0);
   const bool use_tc = coarse_mode() != 1 && coarse_tc_usable(n_lists, n_probes, idx.dim_ext());
   const size_t coarse_ws =
     use_tc ? coarse_tc_workspace_bytes(batch, n_lists, idx.dim_ext())
@@ -528,6 +582,7 @@ void search_any(raft::resources& res, const search_params& params, const index<i
   auto* d_kth     = reinterpret_cast<uint32_t*>(ws + o_kth);
   auto* d_counter = reinterpret_cast<uint32_t*>(ws + o_counter);
   auto* d_keys    = reinterpret_cast<uint64_t*>(ws + o_keys);
+  auto* d_all     = reinterpret_cast<float*>(ws + o_all);
   void* d_coarse  = ws + o_coarse;
 
   for (uint32_t q0 = 0; q0 < n_queries; q0 += batch) {
@@ -573,6 +628,11 @@ void search_any(raft::resources& res, const search_params& params, const index<i
 
     if (stats) { res.stats_mark(ev, 3); }
     // 4. LUT + scan + per-pair top-k
+    if (store_all) {
+      const size_t n_all = size_t(nq) * max_samples;
+      fill_f32_kernel<<<unsigned(ceildiv<size_t>(n_all, 256)), 256, 0, stream>>>(d_all, n_all, INFINITY);
+      res.launches++;
+    }
     {
       scan_params sp{};
       sp.pq_centers     = idx.pq_centers();
@@ -591,6 +651,8 @@ void search_any(raft::resources& res, const search_params& params, const index<i
       sp.k              = k;
       sp.query_kth      = d_kth;
       sp.out_keys       = d_keys;
+      sp.all_scores     = d_all;
+      sp.max_samples    = max_samples;
       sp.work_counter   = d_counter;
       sp.n_groups       = plan.n_groups;
       sp.group_threads  = plan.group_threads;
@@ -609,7 +671,16 @@ void search_any(raft::resources& res, const search_params& params, const index<i
 
     if (stats) { res.stats_mark(ev, 4); }
     // 5. final selection + id translation + distance post-processing
-    {
+    if (store_all) {
+      auto* sel_scores = reinterpret_cast<float*>(d_keys);
+      auto* sel_idx    = reinterpret_cast<uint32_t*>(d_keys) + size_t(nq) * k;
+      select_rows(res, d_all, nq, max_samples, k, sel_idx, sel_scores);
+      translate_selected_kernel<<<unsigned(ceildiv<uint64_t>(uint64_t(nq) * k, 256)), 256, 0, stream>>>(
+        sel_scores, sel_idx, d_probes, d_chunk, idx.row_offsets(), idx.ids(), nq, n_probes, k,
+        int(metric), scale, neighbors + size_t(q0) * k, distances + size_t(q0) * k);
+      CUDA_TRY(cudaGetLastError());
+      res.launches++;
+    } else {
       const int blocks = int(ceildiv<uint32_t>(nq * 32, 128));
       int64_t* nb      = neighbors + size_t(q0) * k;
       float* ds        = distances + size_t(q0) * k;

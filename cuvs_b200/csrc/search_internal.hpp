@@ -21,6 +21,10 @@ void select_clusters(raft::resources& res, const float* centers, uint32_t n_list
                      float alpha, const float* fq, uint32_t n_queries, uint32_t n_probes,
                      uint32_t* probes, float* scores_out, void* workspace, size_t workspace_bytes);
 
+// Per row the k smallest (value, position), ascending (radix select + sort; k <= 4096).
+void select_rows(raft::resources& res, const float* rows, uint32_t n_rows, uint32_t row_len, uint32_t k,
+                 uint32_t* out_idx, float* out_scores);
+
 // Tensor-core coarse stage (coarse_tc.cu): same contract and bit-identical probes as
 // select_clusters; `centers_hi/lo` are the TF32 split of `centers`, `cmax` the largest row norm.
 bool coarse_tc_usable(uint32_t n_lists, uint32_t n_probes, uint32_t dim_ext);

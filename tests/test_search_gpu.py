@@ -332,3 +332,17 @@ def test_search_is_identical_under_both_coarse_paths(ivf, many_lists):
     finally:
         L.check(lib.cuvsB200SetCoarseMode(0))
     assert (i1 == i2).all() and (d1.view(np.uint32) == d2.view(np.uint32)).all()
+
+
+@pytest.mark.parametrize("k,lut,internal", [(129, "f32", "f32"), (200, "f16", "f32"), (513, "fp8", "f16")])
+def test_search_parity_large_k_store_all_path(ivf, oracle_mod, small_l2, k, lut, internal):
+    """k > 128 switches to the mode where the scan stores every score and a selection follows
+    (the reference's non-fused kernel, cpp/tests/neighbors/ann_ivf_pq.cuh var_k cases)."""
+    g = ivf.load(small_l2["path"])
+    q = small_l2["q"][:48]
+    for p in (6, 32):
+        d, i = gpu_search(ivf, g, q, k, p, lut, internal)
+        do, io = oracle_mod.search(small_l2["ix"], q, k, n_probes=p, lut_dtype=LUT[lut][1],
+                                   internal_dtype=LUT[internal][1])
+        assert_parity(d, i, do, io, 1e-5 if lut == "f32" else 1e-2, max_tie_rows=0.05)
+        assert ((i == oracle_mod.OUT_OF_BOUNDS) == (io == oracle_mod.OUT_OF_BOUNDS)).all()
