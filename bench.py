@@ -39,6 +39,13 @@ WORKLOAD = dict(name="deep-embedding-shaped L2, 10M x 96 f32", n_rows=10_000_000
                 n_components=4096, seed=1, n_queries=10_000, n_lists=50_000, pq_dim=48, pq_bits=8,
                 k=10, probes=(20, 50, 100, 200), lut="float16", internal="float32",
                 kmeans_n_iters=10, kmeans_trainset_fraction=0.1, refine_ratio=2)
+# A second, optional workload (--workload sift): the SIFT-shaped integer configuration in miniature
+# (one GPU's share of it): long lists, 8-bit look-up table, k = 100 -- the regime where the code scan
+# rather than the look-up-table build dominates.  Not the headline; used for the scan roofline.
+SIFT_WORKLOAD = dict(name="SIFT-shaped L2, 20M x 128 u8", kind="sift", n_rows=20_000_000, dim=128,
+                     n_components=16384, seed=2, n_queries=10_000, n_lists=20_000, pq_dim=64,
+                     pq_bits=8, k=100, probes=(64,), lut="uint8", internal="float32",
+                     kmeans_n_iters=10, kmeans_trainset_fraction=0.1, refine_ratio=1)
 METRIC = "IVF-PQ search QPS @ recall@10>=0.95"
 FALLBACK_HBM_GBS = 6650.0
 
@@ -54,6 +61,12 @@ def log(*a):
 def mixture_model(wl, device):
     import torch
     g = torch.Generator(device="cpu").manual_seed(wl["seed"] * 7919 + 17)
+    if wl.get("kind") == "sift":
+        # centres in [0, 120] plus a per-dimension exponential offset (mean 20): mass skewed to 0-40
+        centers = torch.rand(wl["n_components"], wl["dim"], generator=g) * 60.0
+        centers = centers + torch.empty(wl["n_components"], wl["dim"]).exponential_(1.0 / 20.0, generator=g)
+        scales = torch.full((wl["n_components"], wl["dim"]), 12.0)
+        return centers.to(device), scales.to(device)
     centers = torch.randn(wl["n_components"], wl["dim"], generator=g)
     lo, hi = np.log(0.05), np.log(0.5)
     scales = torch.exp(torch.rand(wl["n_components"], wl["dim"], generator=g) * (hi - lo) + lo)
@@ -69,13 +82,16 @@ def gen_rows(wl, model, start, count, device, stream_id=0):
     g = torch.Generator(device=device).manual_seed(wl["seed"] * 1_000_003 + start + stream_id * 977)
     comp = torch.randint(0, wl["n_components"], (count,), generator=g, device=device)
     x = centers[comp] + scales[comp] * torch.randn(count, wl["dim"], generator=g, device=device)
+    if wl.get("kind") == "sift":
+        return x.round_().clamp_(0, 255).to(torch.uint8)
     return torch.nn.functional.normalize(x, dim=1)
 
 
 def gen_dataset(wl, device):
     import torch
     model = mixture_model(wl, device)
-    x = torch.empty((wl["n_rows"], wl["dim"]), dtype=torch.float32, device=device)
+    x = torch.empty((wl["n_rows"], wl["dim"]), device=device,
+                    dtype=torch.uint8 if wl.get("kind") == "sift" else torch.float32)
     step = 1_000_000
     for s in range(0, wl["n_rows"], step):
         c = min(step, wl["n_rows"] - s)
@@ -87,12 +103,13 @@ def gen_dataset(wl, device):
 def ground_truth(x, q, k):
     """Exact top-k by squared L2 distance, fp32, in row chunks."""
     import torch
+    q = q.float()
     qn = (q * q).sum(1, keepdim=True)
     best_d = torch.full((q.shape[0], k), float("inf"), device=q.device)
     best_i = torch.zeros((q.shape[0], k), dtype=torch.int64, device=q.device)
     step = 200_000
     for s in range(0, x.shape[0], step):
-        xb = x[s:s + step]
+        xb = x[s:s + step].float()
         d = qn + (xb * xb).sum(1)[None, :] - 2.0 * (q @ xb.T)
         dd, ii = torch.topk(d, k, dim=1, largest=False)
         cat_d = torch.cat([best_d, dd], 1)
@@ -277,9 +294,10 @@ DRAM_BYTES_PER_UNIQUE_GROUP = 1799.6
 
 
 def workload_from_args(args):
-    wl = dict(WORKLOAD)
+    wl = dict(SIFT_WORKLOAD if args.workload == "sift" else WORKLOAD)
     if args.rows:
-        wl.update(n_rows=args.rows, n_lists=max(64, args.rows // 200),
+        per_list = wl["n_rows"] // wl["n_lists"]
+        wl.update(n_rows=args.rows, n_lists=max(64, args.rows // per_list),
                   n_queries=min(wl["n_queries"], max(100, args.rows // 100)))
     if args.refine_ratio is not None:
         wl["refine_ratio"] = args.refine_ratio
@@ -448,19 +466,20 @@ def run_ours(args):
         "metric": METRIC, "value": round(nq / ms_step * 1e3, 1), "unit": "queries/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(ms_step, 4), "higher_is_better": True,
-        "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "f32",
+        "scaling": "strong" if world > 1 else "weak", "vs_baseline": None,
+        "dtype": "f32" if wl["lut"] != "uint8" else "f32 (8-bit float look-up table)",
         "data": "synthetic",
         "config": {"workload": wl["name"], "n_rows": wl["n_rows"], "dim": wl["dim"],
                    "n_lists": wl["n_lists"], "pq_dim": wl["pq_dim"], "pq_bits": wl["pq_bits"],
-                   "k": k, "batch": nq, "n_probes": p_star, "lut_dtype": wl["lut"],
+                   "k": k, "recall_k": k, "batch": nq, "n_probes": p_star, "lut_dtype": wl["lut"],
                    "internal_distance_dtype": wl["internal"], "refine_ratio": wl["refine_ratio"],
                    "recall_at_10": chosen["recall_at_10"],
                    "recall_target_met": target_met, "sweep": sweep,
                    "parallelism": f"list-sharded x{world}" if world > 1 else "single GPU",
-                   "l2": "inputs larger than L2: 480 MB of codes + 80 MB of ids per pass",
+                   "l2": f"inputs larger than L2: {wl['n_rows'] * n_pieces * 16 // 1_000_000} MB of codes per pass",
                    "stage_ms": stage, "build_s": fx.get("build_s")},
         "e2e": {"value": round(nq / ms_e2e * 1e3, 1), "unit": "queries/s",
-                "h2d_bytes_per_step": int(q_host.numel() * 4),
+                "h2d_bytes_per_step": int(q_host.numel() * q_host.element_size()),
                 "d2h_bytes_per_step": int(nq * k * 12), "ms_per_step": round(ms_e2e, 4),
                 "recall_at_10": round(e2e_rec, 4)},
         "gpu_launches": gpu_launches,
@@ -543,6 +562,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--rows", type=int, default=0, help="shrink the dataset (testing only)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--workload", default="deep", choices=["deep", "sift"],
+                    help="deep = the headline configuration; sift = long-list integer data (scan roofline)")
     ap.add_argument("--probes", default="", help="comma-separated n_probes to sweep (default: the workload's)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end leg (profiling runs)")
     ap.add_argument("--refine-ratio", type=float, default=None,
