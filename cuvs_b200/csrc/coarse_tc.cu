@@ -13,10 +13,12 @@
 //      128-byte swizzle atom).  Per K block three products accumulate into TMEM:
 //      hi*hi + hi*lo + lo*hi.  Warp 0 issues TMA loads (no multicast), warp 1 issues the MMAs,
 //      eight epilogue warps read the accumulator with tcgen05.ld (thread = query row) and keep,
-//      per row and per 128-list half tile, the 8 largest dot products in registers as packed
-//      32-bit keys (order-preserving image of the value, low 7 bits replaced by the column tag)
-//      so that insertion is a branch-free chain of integer max/min.  Two TMEM accumulators let
-//      the epilogue of one tile overlap the MMAs of the next.
+//      per row and per 128-list half tile, the largest dot products in registers, as packed
+//      32-bit keys (order-preserving image of the value, low 7 bits replaced by the column tag):
+//      insertion is a branch-free chain of integer max/min.  Two variants: four independent
+//      top-4 chains (column % 4) or one top-8 chain; the last key of a chain bounds everything the
+//      chain dropped.  Two TMEM accumulators let the epilogue of one tile overlap the MMAs of the
+//      next.
 //      Every mbarrier wait is bounded; on a time-out the kernel raises an error word, lets its
 //      in-flight copies land, frees its TMEM and returns.
 //   3. coarse_finish_kernel (one block per query): the C = n_probes + margin best candidates by
@@ -43,7 +45,11 @@ constexpr int kBM       = 128;  // queries per tile
 constexpr int kBN       = 256;  // lists per tile
 constexpr int kBK       = 32;   // floats per K block (128 bytes)
 constexpr int kStages   = 2;
-constexpr int kKeep     = 8;    // candidates kept per row per half tile
+// Epilogue variants <STREAMS, KEEP>: the columns of a half tile are dealt to STREAMS independent
+// chains (column % STREAMS), each keeping its KEEP largest keys.  <4, 4> is the cheaper one
+// (8 min/max per column, four independent chains); <1, 8> keeps more per chain and is chosen when
+// many wanted lists per half tile are likely (large n_probes relative to n_lists).
+constexpr int kMaxKph   = 16;   // keys written per row per half tile, at most
 constexpr int kHalf     = kBN / 2;
 constexpr int kThreads  = 320;  // warp 0 TMA, warp 1 MMA, warps 2..9 epilogue
 constexpr uint32_t kStageBytes = (2 * kBM + 2 * kBN) * kBK * 4;  // 96 KB
@@ -166,10 +172,12 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32])
 // ------------------------------------------------------------------------------------------------
 struct tc_params {
   uint32_t n_queries, n_lists, k_blocks, n_tiles, tile_stride;
-  uint32_t* cand_key;  // [n_queries, n_tiles, 2, kKeep] packed keys, descending (larger = closer)
+  uint32_t* cand_key;    // [n_queries, n_tiles, 2, keys per half tile] packed keys (larger = closer)
+  uint32_t* cand_bound;  // [n_queries, n_tiles, 2] key bounding everything the half tile dropped
   uint32_t* error;     // error word
 };
 
+template <int kStreams, int kKeep>
 __global__ void __launch_bounds__(kThreads, 1)
 coarse_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
                  const __grid_constant__ CUtensorMap map_b_hi, const __grid_constant__ CUtensorMap map_b_lo,
@@ -318,9 +326,12 @@ coarse_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
       tc_fence_after();
       // Packed key: order-preserving image of the dot product with its low 7 bits replaced by
       // (127 - column in the half tile); empty / out-of-range columns are key 0.
-      uint32_t key[kKeep];
+      uint32_t key[kStreams][kKeep];
 #pragma unroll
-      for (int t = 0; t < kKeep; t++) { key[t] = 0u; }
+      for (int st = 0; st < kStreams; st++) {
+#pragma unroll
+        for (int t = 0; t < kKeep; t++) { key[st][t] = 0u; }
+      }
       const uint32_t col0 = half * kHalf;
       const uint32_t n0   = tile * kBN + col0;
 #pragma unroll 1
@@ -337,9 +348,9 @@ coarse_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
           if (!full && list0 + e >= p.n_lists) { k = 0u; }
 #pragma unroll
           for (int t = 0; t < kKeep; t++) {
-            const uint32_t hi = max(key[t], k);
-            k                 = min(key[t], k);
-            key[t]            = hi;
+            const uint32_t hi = max(key[e % kStreams][t], k);
+            k                 = min(key[e % kStreams][t], k);
+            key[e % kStreams][t] = hi;
           }
         }
       }
@@ -348,9 +359,21 @@ coarse_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
       __syncwarp();
       if (lane == 0) { mbar_arrive(bar_tempty + acc * 8); }
       if (q < p.n_queries) {
-        uint4* o = reinterpret_cast<uint4*>(p.cand_key + ((size_t(q) * p.n_tiles + tile) * 2 + half) * kKeep);
-        o[0]     = make_uint4(key[0], key[1], key[2], key[3]);
-        o[1]     = make_uint4(key[4], key[5], key[6], key[7]);
+        // whatever a chain dropped is not larger than its last key
+        uint32_t bound = key[0][kKeep - 1];
+#pragma unroll
+        for (int st = 1; st < kStreams; st++) { bound = max(bound, key[st][kKeep - 1]); }
+        const size_t slot = (size_t(q) * p.n_tiles + tile) * 2 + half;
+        uint4* o          = reinterpret_cast<uint4*>(p.cand_key + slot * (kStreams * kKeep));
+#pragma unroll
+        for (int st = 0; st < kStreams; st++) {
+#pragma unroll
+          for (int u = 0; u < kKeep / 4; u++) {
+            o[st * (kKeep / 4) + u] =
+              make_uint4(key[st][4 * u], key[st][4 * u + 1], key[st][4 * u + 2], key[st][4 * u + 3]);
+          }
+        }
+        p.cand_bound[slot] = bound;
       }
     }
     if (!ok && lane == 0) {
@@ -383,21 +406,27 @@ __device__ __forceinline__ bool key_valid(uint32_t key) { return key >= 0x008000
 __device__ __forceinline__ float key_value(uint32_t key) { return ordered_to_float(key & ~127u); }
 
 __global__ void __launch_bounds__(256)
-coarse_finish_kernel(const uint32_t* __restrict__ cand_key, uint32_t n_cand /* per query */,
+coarse_finish_kernel(const uint32_t* __restrict__ cand_key, const uint32_t* __restrict__ cand_bound,
+                     uint32_t n_cand /* per query */, uint32_t kph /* keys per half tile */,
                      const float* __restrict__ centers, const float* __restrict__ fq,
                      uint32_t n_lists, uint32_t dim_ext, float alpha, uint32_t n_probes, uint32_t C,
                      uint32_t cap /* pow2 >= C */, float cmax, uint32_t* __restrict__ probes,
                      float* __restrict__ scores_out, uint8_t* __restrict__ flags)
 {
-  extern __shared__ uint64_t s_keys[];                 // [cap] keys; then the query [dim_ext] floats
-  float* s_q = reinterpret_cast<float*>(s_keys + cap);
+  extern __shared__ uint64_t s_keys[];                 // [cap] keys; the query; the candidates
+  float* s_q      = reinterpret_cast<float*>(s_keys + cap);
+  uint32_t* key   = reinterpret_cast<uint32_t*>(s_q + dim_ext);  // [n_cand] staged once
   __shared__ uint32_t s_hist[256];
   __shared__ uint32_t s_prefix, s_remaining, s_count;
   __shared__ float s_red[8];
   __shared__ uint32_t s_tb[8];
   const uint32_t q    = blockIdx.x;
   const uint32_t tid  = threadIdx.x;
-  const uint32_t* key = cand_key + size_t(q) * n_cand;
+  {
+    const uint4* src = reinterpret_cast<const uint4*>(cand_key + size_t(q) * n_cand);
+    uint4* dst       = reinterpret_cast<uint4*>(key);
+    for (uint32_t i = tid; i < n_cand / 4; i += 256) { dst[i] = __ldg(src + i); }
+  }
 
   float qq = 0.0f;
   for (uint32_t i = tid; i < dim_ext; i += 256) {
@@ -447,18 +476,20 @@ coarse_finish_kernel(const uint32_t* __restrict__ cand_key, uint32_t n_cand /* p
   if (tid == 0) { s_count = 0; }
   for (uint32_t i = tid; i < cap; i += 256) { s_keys[i] = kEmptyKey; }
   __syncthreads();
-  // gather everything at least as good as the threshold, and the bound contributed by full half
-  // tiles (their last kept key: whatever they dropped is not larger)
+  // gather everything at least as good as the threshold; then the bound on what the half tiles dropped
   uint32_t tb = 0;
   for (uint32_t i = tid; i < n_cand; i += 256) {
     const uint32_t kk = key[i];
     if (!key_valid(kk)) { continue; }
-    if ((i % kKeep) == kKeep - 1) { tb = max(tb, kk); }
     if (~kk <= T) {
       const uint32_t slot = atomicAdd(&s_count, 1u);
-      // list id = tile * 256 + half * 128 + column; i / kKeep enumerates (tile, half)
-      if (slot < cap) { s_keys[slot] = (i / kKeep) * kHalf + (127u - (kk & 127u)); }
+      // list id = tile * 256 + half * 128 + column; i / kph enumerates (tile, half)
+      if (slot < cap) { s_keys[slot] = (i / kph) * kHalf + (127u - (kk & 127u)); }
     }
+  }
+  {
+    const uint32_t* bnd = cand_bound + size_t(q) * (n_cand / kph);
+    for (uint32_t i = tid; i < n_cand / kph; i += 256) { tb = max(tb, bnd[i]); }
   }
 #pragma unroll
   for (int d = 16; d > 0; d >>= 1) { tb = max(tb, __shfl_xor_sync(kFullMask, tb, d)); }
@@ -473,9 +504,15 @@ coarse_finish_kernel(const uint32_t* __restrict__ cand_key, uint32_t n_cand /* p
   // exact rescoring: the defining FMA chain, ascending k
   for (uint32_t i = tid; i < n_sel; i += 256) {
     const uint32_t l = uint32_t(s_keys[i]);
-    const float* c   = centers + size_t(l) * dim_ext;
+    const float4* c  = reinterpret_cast<const float4*>(centers + size_t(l) * dim_ext);
     float acc        = 0.0f;
-    for (uint32_t k = 0; k < dim_ext; k++) { acc = __fmaf_rn(__ldg(c + k), s_q[k], acc); }
+    for (uint32_t k4 = 0; k4 < dim_ext / 4; k4++) {  // dim_ext is a multiple of 8
+      const float4 cv = __ldg(c + k4);
+      acc             = __fmaf_rn(cv.x, s_q[4 * k4], acc);
+      acc             = __fmaf_rn(cv.y, s_q[4 * k4 + 1], acc);
+      acc             = __fmaf_rn(cv.z, s_q[4 * k4 + 2], acc);
+      acc             = __fmaf_rn(cv.w, s_q[4 * k4 + 3], acc);
+    }
     s_keys[i] = (uint64_t(float_to_ordered(__fmul_rn(alpha, acc))) << 32) | l;
   }
   __syncthreads();
@@ -678,9 +715,11 @@ bool coarse_tc_usable(uint32_t n_lists, uint32_t n_probes, uint32_t dim_ext)
   if (n_lists < 2048 || (dim_ext % 4) != 0) { return false; }
   const uint32_t C = n_probes + margin_for(n_probes);
   if (C > kMaxC / 2) { return false; }
-  // expected number of wanted lists per 128-list half tile; the 8 kept per half tile must cover it
+  // expected number of wanted lists per 128-list half tile; the 8 kept per half tile must cover
+  // it, and the candidates of one query must fit the finish kernel's shared memory
   const double lambda = double(C) * kHalf / double(n_lists);
-  return lambda <= 1.5;
+  const size_t n_cand = size_t(ceildiv<uint32_t>(n_lists, kBN)) * 2 * kMaxKph;
+  return lambda <= 1.5 && n_cand * 4 <= 160 * 1024;
 }
 
 size_t coarse_tc_workspace_bytes(uint32_t n_queries, uint32_t n_lists, uint32_t dim_ext)
@@ -689,7 +728,8 @@ size_t coarse_tc_workspace_bytes(uint32_t n_queries, uint32_t n_lists, uint32_t 
   ws_layout lay;
   lay.add(size_t(n_queries) * dim_ext * 4);  // fq hi
   lay.add(size_t(n_queries) * dim_ext * 4);  // fq lo
-  lay.add(size_t(n_queries) * n_tiles * 2 * kKeep * 4);  // candidate keys
+  lay.add(size_t(n_queries) * n_tiles * 2 * kMaxKph * 4);  // candidate keys
+  lay.add(size_t(n_queries) * n_tiles * 2 * 4);          // per half tile bound
   lay.add(n_queries);                        // flags
   lay.add(256);                              // error word + fallback counter
   lay.add(size_t(64) * n_lists * 4);         // fallback scratch rows
@@ -712,12 +752,19 @@ void select_clusters_tc(raft::resources& res, const float* centers, const float*
   CUVS_EXPECTS(workspace_bytes >= coarse_tc_workspace_bytes(n_queries, n_lists, dim_ext),
                "coarse workspace too small");
   const uint32_t n_tiles = ceildiv<uint32_t>(n_lists, kBN);
-  const uint32_t n_cand  = n_tiles * 2 * kKeep;
+  const uint32_t C = std::min<uint32_t>(n_probes + margin_for(n_probes), n_lists);
+  // <4,4> drops a wanted list when 4 of the 32 lists of a chain are wanted: expected fraction of
+  // queries hit = n_chains * C(32,4) * (C/L)^4; above 0.02% use the single top-8 chain instead
+  const double frac    = double(C) / double(n_lists);
+  const bool four_by_4 = (double(n_lists) / 32.0) * 35960.0 * frac * frac * frac * frac <= 2e-4;
+  const uint32_t kph   = four_by_4 ? 16 : 8;
+  const uint32_t n_cand  = n_tiles * 2 * kph;
   ws_layout lay;
   char* ws        = static_cast<char*>(workspace);
   float* fq_hi    = reinterpret_cast<float*>(ws + lay.add(size_t(n_queries) * dim_ext * 4));
   float* fq_lo    = reinterpret_cast<float*>(ws + lay.add(size_t(n_queries) * dim_ext * 4));
-  auto* cand_key  = reinterpret_cast<uint32_t*>(ws + lay.add(size_t(n_queries) * n_cand * 4));
+  auto* cand_key  = reinterpret_cast<uint32_t*>(ws + lay.add(size_t(n_queries) * n_tiles * 2 * kMaxKph * 4));
+  auto* cand_bnd  = reinterpret_cast<uint32_t*>(ws + lay.add(size_t(n_queries) * n_tiles * 2 * 4));
   auto* flags     = reinterpret_cast<uint8_t*>(ws + lay.add(n_queries));
   auto* words     = reinterpret_cast<uint32_t*>(ws + lay.add(256));
   float* scratch  = reinterpret_cast<float*>(ws + lay.add(size_t(64) * n_lists * 4));
@@ -738,6 +785,7 @@ void select_clusters_tc(raft::resources& res, const float* centers, const float*
   p.k_blocks  = ceildiv<uint32_t>(dim_ext, kBK);
   p.n_tiles   = n_tiles;
   p.cand_key  = cand_key;
+  p.cand_bound = cand_bnd;
   p.error     = words;
   const uint32_t q_tiles = ceildiv<uint32_t>(n_queries, kBM);
   // list-tile splits per query tile: enough CTAs for a few waves, never more than the tiles
@@ -747,19 +795,31 @@ void select_clusters_tc(raft::resources& res, const float* centers, const float*
   p.tile_stride   = splits;
   static bool configured = false;
   if (!configured) {
-    CUDA_TRY(cudaFuncSetAttribute(coarse_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    CUDA_TRY(cudaFuncSetAttribute(coarse_tc_kernel<4, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  int(kSmemBytes)));
+    CUDA_TRY(cudaFuncSetAttribute(coarse_tc_kernel<1, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                   int(kSmemBytes)));
     configured = true;
   }
-  coarse_tc_kernel<<<dim3(q_tiles, splits), kThreads, kSmemBytes, stream>>>(m_a_hi, m_a_lo, m_b_hi,
-                                                                           m_b_lo, p);
+  if (four_by_4) {
+    coarse_tc_kernel<4, 4><<<dim3(q_tiles, splits), kThreads, kSmemBytes, stream>>>(m_a_hi, m_a_lo, m_b_hi,
+                                                                                   m_b_lo, p);
+  } else {
+    coarse_tc_kernel<1, 8><<<dim3(q_tiles, splits), kThreads, kSmemBytes, stream>>>(m_a_hi, m_a_lo, m_b_hi,
+                                                                                   m_b_lo, p);
+  }
   CUDA_TRY(cudaGetLastError());
 
-  const uint32_t C = std::min<uint32_t>(n_probes + margin_for(n_probes), n_lists);
   uint32_t cap     = 2;
   while (cap < 2 * C) { cap <<= 1; }  // room for ties at the selection threshold
-  const size_t fin_smem = size_t(cap) * 8 + size_t(dim_ext) * 4;
-  coarse_finish_kernel<<<n_queries, 256, fin_smem, stream>>>(cand_key, n_cand, centers, fq, n_lists,
+  const size_t fin_smem = size_t(cap) * 8 + size_t(dim_ext) * 4 + size_t(n_cand) * 4;
+  static size_t fin_configured = 48 * 1024;
+  if (fin_smem > fin_configured) {
+    CUDA_TRY(cudaFuncSetAttribute(coarse_finish_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  int(fin_smem)));
+    fin_configured = fin_smem;
+  }
+  coarse_finish_kernel<<<n_queries, 256, fin_smem, stream>>>(cand_key, cand_bnd, n_cand, kph, centers, fq, n_lists,
                                                              dim_ext, alpha, n_probes, C, cap, cmax,
                                                              probes, scores_out, flags);
   uint32_t cap_fb = 2;
@@ -781,7 +841,8 @@ void coarse_tc_status(raft::resources& res, const void* workspace, uint32_t n_qu
   ws_layout lay;
   lay.add(size_t(n_queries) * dim_ext * 4);
   lay.add(size_t(n_queries) * dim_ext * 4);
-  lay.add(size_t(n_queries) * n_tiles * 2 * kKeep * 4);
+  lay.add(size_t(n_queries) * n_tiles * 2 * kMaxKph * 4);
+  lay.add(size_t(n_queries) * n_tiles * 2 * 4);
   lay.add(n_queries);
   const size_t o = lay.add(256);
   uint32_t h[2]  = {0, 0};

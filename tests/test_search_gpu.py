@@ -298,7 +298,7 @@ def many_lists(ivf):
     return x, g
 
 
-@pytest.mark.parametrize("nq,n_probes", [(1, 1), (7, 20), (128, 32), (300, 64), (1000, 20)])
+@pytest.mark.parametrize("nq,n_probes", [(1, 1), (7, 20), (128, 32), (300, 40), (1000, 20)])
 def test_coarse_tensor_core_path_equals_exact_path(ivf, oracle_mod, many_lists, tmp_path, nq, n_probes):
     x, g = many_lists
     q = make_mixture(nq, 64, 512, 0.25, seed=71 + nq)
