@@ -497,7 +497,7 @@ def run_ours(args):
                                 dataset_np=dataset.cpu().numpy() if refining else None)
         cb["value"] = round(cb["value"], 1)
         line["cpu_baseline"] = cb
-    print(json.dumps(line), flush=True)
+    emit(line)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
@@ -511,8 +511,8 @@ def run_reference(args):
     wl = workload_from_args(args)
     import torch
     if not torch.cuda.is_available():
-        print(json.dumps({"impl": "reference",
-                          "unavailable": "the 10M-vector index fixture is built on the GPU; no GPU here"}))
+        emit({"impl": "reference",
+              "unavailable": "the 10M-vector index fixture is built on the GPU; no GPU here"})
         return
     torch.cuda.set_device(0)
     k = wl["k"]
@@ -551,10 +551,25 @@ def run_reference(args):
             "e2e": {"value": round(cb["value"], 1), "unit": "queries/s", "h2d_bytes_per_step": 0,
                     "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
-    print(json.dumps(line), flush=True)
+    emit(line)
+
+
+def emit(line: dict):
+    """Write the one JSON line to the process's original stdout."""
+    data = (json.dumps(line) + "\n").encode()
+    os.write(_REAL_STDOUT, data)
+
+
+_REAL_STDOUT = 1
 
 
 def main():
+    # Libraries (NCCL's version banner, for one) print to stdout; the contract is ONE JSON line
+    # there.  Keep the original stdout for that line and point fd 1 at stderr for everything else.
+    global _REAL_STDOUT
+    sys.stdout.flush()
+    _REAL_STDOUT = os.dup(1)
+    os.dup2(2, 1)
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)

@@ -115,6 +115,10 @@ SIGNATURES = {
     "cuvsMultiGpuIvfPqDistributeShard": [C.c_size_t, C.c_char_p, C.c_int, C.c_int, _P(IndexStruct)],
     "cuvsMultiGpuIvfPqMergeParts": [C.c_size_t, _P(DLManagedTensor), _P(DLManagedTensor),
                                     _P(DLManagedTensor), _P(DLManagedTensor), C.c_bool],
+    "cuvsMultiGpuIvfPqSelectProbes": [C.c_size_t, _P(IndexStruct), _P(DLManagedTensor), _P(DLManagedTensor)],
+    "cuvsMultiGpuIvfPqSearchWithProbes": [C.c_size_t, _P(SearchParamsStruct), _P(IndexStruct),
+                                          _P(DLManagedTensor), _P(DLManagedTensor), _P(DLManagedTensor),
+                                          _P(DLManagedTensor)],
     "cuvsB200CoarseSelect": [C.c_size_t, C.c_void_p, _P(DLManagedTensor), _P(DLManagedTensor),
                              _P(DLManagedTensor), C.c_int, _P(C.c_uint32)],
     "cuvsB200SetCoarseMode": [C.c_int],

@@ -11,6 +11,7 @@
 #include "ivf_pq.hpp"
 #include "search_internal.hpp"
 
+#include <algorithm>
 #include <cstring>
 #include <exception>
 #include <string>
@@ -708,5 +709,59 @@ extern "C" cuvsError_t cuvsRefine(cuvsResources_t res, DLManagedTensor* dataset,
                                 uint32_t(q.shape[0]), cd, uint32_t(candidates->dl_tensor.shape[1]),
                                 ivf_pq::DistanceType(int(metric)), id, dsd,
                                 uint32_t(indices->dl_tensor.shape[1]));
+  });
+}
+
+extern "C" cuvsError_t cuvsMultiGpuIvfPqSelectProbes(cuvsResources_t res, cuvsIvfPqIndex_t index,
+                                                     DLManagedTensor* queries, DLManagedTensor* probes)
+{
+  return translate_exceptions([=] {
+    auto* ix          = index_of(index);
+    const DLTensor& q = queries->dl_tensor;
+    auto et           = elem_of_dtype(q.dtype, "queries");
+    void* qd = checked_data(queries, q.dtype.code, q.dtype.bits, 2, true, "queries");
+    auto* pd = static_cast<uint32_t*>(checked_data(probes, kDLUInt, 32, 2, true, "probes"));
+    CUVS_EXPECTS(q.shape[1] == int64_t(ix->dim()),
+                 "Number of query dimensions should equal number of dimensions in the index.");
+    CUVS_EXPECTS(probes->dl_tensor.shape[0] == q.shape[0], "probes must have one row per query");
+    ivf_pq::select_probes_any(*res_of(res), *ix, qd, et, uint32_t(q.shape[0]),
+                              uint32_t(probes->dl_tensor.shape[1]), pd);
+  });
+}
+
+extern "C" cuvsError_t cuvsMultiGpuIvfPqSearchWithProbes(cuvsResources_t res,
+                                                         cuvsIvfPqSearchParams_t params,
+                                                         cuvsIvfPqIndex_t index, DLManagedTensor* queries,
+                                                         DLManagedTensor* probes,
+                                                         DLManagedTensor* neighbors,
+                                                         DLManagedTensor* distances)
+{
+  return translate_exceptions([=] {
+    CUVS_EXPECTS(params && queries && probes && neighbors && distances, "null argument");
+    auto* ix          = index_of(index);
+    const DLTensor& q = queries->dl_tensor;
+    auto et           = elem_of_dtype(q.dtype, "queries");
+    void* qd = checked_data(queries, q.dtype.code, q.dtype.bits, 2, true, "queries");
+    auto* pd = static_cast<uint32_t*>(checked_data(probes, kDLUInt, 32, 2, true, "probes"));
+    auto* nb = static_cast<int64_t*>(checked_data(neighbors, kDLInt, 64, 2, true, "neighbors"));
+    auto* ds = static_cast<float*>(checked_data(distances, kDLFloat, 32, 2, true, "distances"));
+    CUVS_EXPECTS(q.shape[0] == neighbors->dl_tensor.shape[0] && q.shape[0] == distances->dl_tensor.shape[0] &&
+                   q.shape[0] == probes->dl_tensor.shape[0],
+                 "Number of rows in probes, neighbors and distances must equal the number of queries.");
+    CUVS_EXPECTS(neighbors->dl_tensor.shape[1] == distances->dl_tensor.shape[1],
+                 "Number of columns in output neighbors and distances matrices must equal k");
+    CUVS_EXPECTS(q.shape[1] == int64_t(ix->dim()),
+                 "Number of query dimensions should equal number of dimensions in the index.");
+    ivf_pq::search_params sp;
+    sp.n_probes                 = params->n_probes;
+    sp.lut_dtype                = params->lut_dtype;
+    sp.internal_distance_dtype  = params->internal_distance_dtype;
+    sp.preferred_shmem_carveout = params->preferred_shmem_carveout;
+    sp.coarse_search_dtype      = params->coarse_search_dtype;
+    sp.max_internal_batch_size  = params->max_internal_batch_size;
+    CUVS_EXPECTS(int64_t(std::min<uint32_t>(sp.n_probes, ix->n_lists())) == probes->dl_tensor.shape[1],
+                 "probes must have min(n_probes, n_lists) columns");
+    ivf_pq::search_any(*res_of(res), sp, *ix, qd, et, uint32_t(q.shape[0]),
+                       uint32_t(neighbors->dl_tensor.shape[1]), nb, ds, pd);
   });
 }

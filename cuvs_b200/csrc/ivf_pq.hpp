@@ -239,9 +239,15 @@ enum class elem_t { f32 = 0, f16 = 1, i8 = 2, u8 = 3 };
 inline size_t elem_size(elem_t t) { return t == elem_t::f32 ? 4 : (t == elem_t::f16 ? 2 : 1); }
 
 // Type-erased workers behind the typed overloads below.
+// `given_probes` (optional, device, [n_queries, min(n_probes, n_lists)] u32): lists to scan per
+// query, replacing the coarse stage (used when probe selection is shared between GPUs).
 void search_any(raft::resources& res, const search_params& params, const index<int64_t>& idx,
                 const void* queries, elem_t qtype, uint32_t n_queries, uint32_t k,
-                int64_t* neighbors, float* distances);
+                int64_t* neighbors, float* distances, const uint32_t* given_probes = nullptr);
+// Probe selection alone, asynchronous on the handle's stream: probes [n_queries, n_probes] u32,
+// ascending by (score, list id).
+void select_probes_any(raft::resources& res, const index<int64_t>& idx, const void* queries,
+                       elem_t qtype, uint32_t n_queries, uint32_t n_probes, uint32_t* probes);
 void build_any(raft::resources& res, const index_params& params, const void* dataset,
                elem_t dtype, int64_t n_rows, uint32_t dim, bool on_device, index<int64_t>* idx);
 void extend_any(raft::resources& res, const void* new_vectors, elem_t dtype, int64_t n_rows,

@@ -488,7 +488,7 @@ scan_plan plan_scan(const raft::resources& res, const index<int64_t>& idx, int l
 // ------------------------------------------------------------------------------------------------
 void search_any(raft::resources& res, const search_params& params, const index<int64_t>& idx,
                 const void* queries, elem_t qtype, uint32_t n_queries, uint32_t k,
-                int64_t* neighbors, float* distances)
+                int64_t* neighbors, float* distances, const uint32_t* given_probes)
 {
   // ivf_pq_search.cuh:901-917
   CUVS_EXPECTS(params.internal_distance_dtype == CUDA_R_16F ||
@@ -568,8 +568,9 @@ void search_any(raft::resources& res, const search_params& params, const index<i
   const size_t o_all     = lay.add(store_all ? size_t(batch) * max_samples * 4 : 0);
   const bool use_tc = coarse_mode() != 1 && coarse_tc_usable(n_lists, n_probes, idx.dim_ext());
   const size_t coarse_ws =
-    use_tc ? coarse_tc_workspace_bytes(batch, n_lists, idx.dim_ext())
-           : coarse_workspace_bytes(batch, n_lists, n_probes);
+    given_probes ? 0
+                 : (use_tc ? coarse_tc_workspace_bytes(batch, n_lists, idx.dim_ext())
+                           : coarse_workspace_bytes(batch, n_lists, n_probes));
   const size_t o_coarse  = lay.add(coarse_ws);
   res.ws.reserve(lay.total());
   char* ws = res.ws.base();
@@ -599,7 +600,10 @@ void search_any(raft::resources& res, const search_params& params, const index<i
 
     if (stats) { res.stats_mark(ev, 1); }
     // 2. coarse selection: probes sorted by (score, list id)
-    if (use_tc) {
+    if (given_probes) {
+      CUDA_TRY(cudaMemcpyAsync(d_probes, given_probes + size_t(q0) * n_probes, size_t(nq) * n_probes * 4,
+                               cudaMemcpyDeviceToDevice, stream));
+    } else if (use_tc) {
       select_clusters_tc(res, idx.centers(), idx.centers_hi(), idx.centers_lo(), idx.centers_max_norm(),
                          n_lists, idx.dim_ext(), is_l2 ? -2.0f : -1.0f, d_fq, nq, n_probes, d_probes,
                          nullptr, d_coarse, coarse_ws);
@@ -711,6 +715,41 @@ void search_any(raft::resources& res, const search_params& params, const index<i
 }
 
 void set_coarse_mode(int mode) { coarse_mode_ref() = mode; }
+
+void select_probes_any(raft::resources& res, const index<int64_t>& idx, const void* queries,
+                       elem_t qtype, uint32_t n_queries, uint32_t n_probes, uint32_t* probes)
+{
+  if (n_queries == 0) { return; }
+  const uint32_t n_lists = idx.n_lists();
+  CUVS_EXPECTS(n_probes > 0 && n_probes <= n_lists, "n_probes must be within [1, n_lists]");
+  const DistanceType metric = idx.metric();
+  const bool is_l2  = metric == DistanceType::L2Expanded || metric == DistanceType::L2SqrtExpanded;
+  const bool use_tc = coarse_mode() != 1 && coarse_tc_usable(n_lists, n_probes, idx.dim_ext());
+  const uint32_t batch = std::min<uint32_t>(n_queries, 16384);
+  ws_layout lay;
+  const size_t o_fq = lay.add(size_t(batch) * idx.dim_ext() * 4);
+  const size_t o_rq = lay.add(size_t(batch) * idx.rot_dim() * 4);
+  const size_t cws  = use_tc ? coarse_tc_workspace_bytes(batch, n_lists, idx.dim_ext())
+                             : coarse_workspace_bytes(batch, n_lists, n_probes);
+  const size_t o_c  = lay.add(cws);
+  res.ws.reserve(lay.total());
+  char* ws   = res.ws.base();
+  auto* d_fq = reinterpret_cast<float*>(ws + o_fq);
+  auto* d_rq = reinterpret_cast<float*>(ws + o_rq);
+  for (uint32_t q0 = 0; q0 < n_queries; q0 += batch) {
+    const uint32_t nq = std::min(batch, n_queries - q0);
+    const char* qptr  = static_cast<const char*>(queries) + size_t(q0) * idx.dim() * elem_size(qtype);
+    launch_prep(res, idx, qptr, qtype, nq, d_fq, d_rq);
+    if (use_tc) {
+      select_clusters_tc(res, idx.centers(), idx.centers_hi(), idx.centers_lo(), idx.centers_max_norm(),
+                         n_lists, idx.dim_ext(), is_l2 ? -2.0f : -1.0f, d_fq, nq, n_probes,
+                         probes + size_t(q0) * n_probes, nullptr, ws + o_c, cws);
+    } else {
+      select_clusters(res, idx.centers(), n_lists, idx.dim_ext(), is_l2 ? -2.0f : -1.0f, d_fq, nq,
+                      n_probes, probes + size_t(q0) * n_probes, nullptr, ws + o_c, cws);
+    }
+  }
+}
 
 void coarse_only(raft::resources& res, const index<int64_t>& idx, const void* queries, elem_t qtype,
                  uint32_t n_queries, uint32_t n_probes_in, int mode, uint32_t* probes, float* scores,

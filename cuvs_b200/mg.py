@@ -77,16 +77,63 @@ def merge_parts(part_d: torch.Tensor, part_i: torch.Tensor, select_min: bool = T
     return out_d, out_i
 
 
+def select_probes(shard: ivf_pq.Index, queries, n_probes: int, resources: Resources | None = None):
+    """Probes of `queries` (u32 [n, n_probes], ascending by (score, list id)); asynchronous."""
+    res = resources or default_resources()
+    res.use_current_stream()
+    probes = torch.empty((queries.shape[0], n_probes), dtype=torch.uint32, device=queries.device)
+    if queries.shape[0]:
+        q, p = DLTensorRef(queries), DLTensorRef(probes)
+        L.check(L.load().cuvsMultiGpuIvfPqSelectProbes(res.handle, shard._h, q.ref(), p.ref()))
+    return probes
+
+
+def shared_probes(shard: ivf_pq.Index, queries, n_probes: int, group=None,
+                  resources: Resources | None = None):
+    """Probe selection shared between the ranks: rank r selects the probes of the r-th slice of the
+    batch (the global coarse model is replicated, so every rank would choose the same lists), the
+    slices are all-gathered (n_queries * n_probes * 4 bytes in total)."""
+    rank, w = _rank_world(group)
+    n = queries.shape[0]
+    if w == 1:
+        return select_probes(shard, queries, n_probes, resources)
+    s = -(-n // w)
+    lo, hi = min(n, rank * s), min(n, (rank + 1) * s)
+    mine = torch.zeros((s, n_probes), dtype=torch.uint32, device=queries.device)
+    if hi > lo:
+        mine[: hi - lo] = select_probes(shard, queries[lo:hi], n_probes, resources)
+    every = torch.empty((w * s, n_probes), dtype=torch.uint32, device=queries.device)
+    # NCCL has no uint32: exchange the same bytes as int32
+    dist.all_gather_into_tensor(every.view(torch.int32), mine.view(torch.int32), group=group)
+    return every[:n]
+
+
+def search_with_probes(search_params: ivf_pq.SearchParams, shard: ivf_pq.Index, queries, probes,
+                       k: int, resources: Resources | None = None, sync: bool = True):
+    res = resources or default_resources()
+    res.use_current_stream()
+    n = queries.shape[0]
+    d = torch.empty((n, k), dtype=torch.float32, device=queries.device)
+    i = torch.empty((n, k), dtype=torch.int64, device=queries.device)
+    a, b, c, e = DLTensorRef(queries), DLTensorRef(probes.contiguous()), DLTensorRef(i), DLTensorRef(d)
+    L.check(L.load().cuvsMultiGpuIvfPqSearchWithProbes(res.handle, search_params._p, shard._h, a.ref(),
+                                                       b.ref(), c.ref(), e.ref()))
+    if sync:
+        res.sync()
+    return d, i
+
+
 def search(search_params: ivf_pq.SearchParams, shard: ivf_pq.Index, queries, k: int,
            select_min: bool = True, group=None, resources: Resources | None = None,
            sync: bool = True):
-    """Sharded search: every rank passes the same queries and gets the same merged result."""
+    """Sharded search: every rank passes the same queries and gets the same merged result.
+    Probe selection is split between the ranks by query slice, the code scan by inverted list."""
     res = resources or default_resources()
-    d, i = ivf_pq.search(search_params, shard, queries, k, resources=res, sync=False)
     _, w = _rank_world(group)
     if w == 1:
-        if sync:
-            res.sync()
-        return d, i
+        return ivf_pq.search(search_params, shard, queries, k, resources=res, sync=sync)
+    n_probes = min(search_params.n_probes, shard.n_lists)
+    probes = shared_probes(shard, queries, n_probes, group, res)
+    d, i = search_with_probes(search_params, shard, queries, probes, k, res, sync=False)
     part_d, part_i = gather_parts(d, i, group)
     return merge_parts(part_d, part_i, select_min, res, sync)

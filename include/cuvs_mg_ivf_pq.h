@@ -42,6 +42,26 @@ CUVS_EXPORT cuvsError_t cuvsMultiGpuIvfPqMergeParts(cuvsResources_t res,
                                                     DLManagedTensor* neighbors,
                                                     bool select_min);
 
+/* Probe selection alone (the coarse stage of cpp/src/neighbors/ivf_pq/ivf_pq_search.cuh:61-168), so
+ * that ranks can share it: each rank selects the probes of a slice of the query batch, the slices are
+ * all-gathered, and every rank then scans its own lists for the whole batch with
+ * cuvsMultiGpuIvfPqSearchWithProbes.  queries f32/f16/i8/u8 [n, dim]; probes u32 [n, n_probes]
+ * (device), ascending by (score, list id).  Asynchronous on the handle's stream. */
+CUVS_EXPORT cuvsError_t cuvsMultiGpuIvfPqSelectProbes(cuvsResources_t res,
+                                                      cuvsIvfPqIndex_t index,
+                                                      DLManagedTensor* queries,
+                                                      DLManagedTensor* probes);
+
+/* cuvsIvfPqSearch (c/include/cuvs/neighbors/ivf_pq.h:536) with the probes given instead of selected:
+ * probes u32 [n_queries, n_probes] (device); search_params->n_probes must equal probes.shape[1]. */
+CUVS_EXPORT cuvsError_t cuvsMultiGpuIvfPqSearchWithProbes(cuvsResources_t res,
+                                                          cuvsIvfPqSearchParams_t search_params,
+                                                          cuvsIvfPqIndex_t index,
+                                                          DLManagedTensor* queries,
+                                                          DLManagedTensor* probes,
+                                                          DLManagedTensor* neighbors,
+                                                          DLManagedTensor* distances);
+
 #ifdef __cplusplus
 }
 #endif

@@ -346,3 +346,15 @@ def test_search_parity_large_k_store_all_path(ivf, oracle_mod, small_l2, k, lut,
                                    internal_dtype=LUT[internal][1])
         assert_parity(d, i, do, io, 1e-5 if lut == "f32" else 1e-2, max_tie_rows=0.05)
         assert ((i == oracle_mod.OUT_OF_BOUNDS) == (io == oracle_mod.OUT_OF_BOUNDS)).all()
+
+
+def test_search_with_given_probes_equals_plain_search(ivf, many_lists):
+    """The two halves of the shared probe selection: select_probes then search_with_probes."""
+    from cuvs_b200 import mg
+    x, g = many_lists
+    q = torch.from_numpy(make_mixture(333, 64, 512, 0.25, seed=90)).cuda()
+    sp = ivf.SearchParams(n_probes=24, lut_dtype=np.float16)
+    d0, i0 = ivf.search(sp, g, q, 10)
+    probes = torch.cat([mg.select_probes(g, q[:100], 24), mg.select_probes(g, q[100:], 24)])
+    d1, i1 = mg.search_with_probes(sp, g, q, probes, 10)
+    assert (i0 == i1).all() and (d0.view(torch.int32) == d1.view(torch.int32)).all()
