@@ -57,6 +57,10 @@ class SearchParamsStruct(C.Structure):
                 ("max_internal_batch_size", C.c_uint32), ("preferred_shmem_carveout", C.c_double)]
 
 
+class FilterStruct(C.Structure):
+    _fields_ = [("addr", C.c_size_t), ("type", C.c_int)]
+
+
 class IndexStruct(C.Structure):
     _fields_ = [("addr", C.c_size_t), ("dtype", DLDataType)]
 
@@ -109,6 +113,9 @@ SIGNATURES = {
                                   _P(DLManagedTensor), _P(IndexStruct)],
     "cuvsIvfPqSearch": [C.c_size_t, _P(SearchParamsStruct), _P(IndexStruct), _P(DLManagedTensor),
                         _P(DLManagedTensor), _P(DLManagedTensor)],
+    "cuvsIvfPqSearchWithFilter": [C.c_size_t, _P(SearchParamsStruct), _P(IndexStruct),
+                                  _P(DLManagedTensor), _P(DLManagedTensor), _P(DLManagedTensor),
+                                  FilterStruct],
     "cuvsIvfPqSerialize": [C.c_size_t, C.c_char_p, _P(IndexStruct)],
     "cuvsIvfPqDeserialize": [C.c_size_t, C.c_char_p, _P(IndexStruct)],
     "cuvsIvfPqExtend": [C.c_size_t, _P(DLManagedTensor), _P(DLManagedTensor), _P(IndexStruct)],

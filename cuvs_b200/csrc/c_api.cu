@@ -506,46 +506,72 @@ extern "C" cuvsError_t cuvsIvfPqTransform(cuvsResources_t res, cuvsIvfPqIndex_t 
 // ------------------------------------------------------------------------------------------------
 // search / serialize / deserialize
 // ------------------------------------------------------------------------------------------------
+namespace {
+void search_entry(cuvsResources_t res, cuvsIvfPqSearchParams_t params, cuvsIvfPqIndex_t index,
+                  DLManagedTensor* queries_tensor, DLManagedTensor* neighbors_tensor,
+                  DLManagedTensor* distances_tensor, ivf_pq::bitset_view filter)
+{
+  CUVS_EXPECTS(params && queries_tensor && neighbors_tensor && distances_tensor, "null argument");
+  const DLTensor& queries   = queries_tensor->dl_tensor;
+  const DLTensor& neighbors = neighbors_tensor->dl_tensor;
+  const DLTensor& distances = distances_tensor->dl_tensor;
+  // c/src/neighbors/ivf_pq.cpp:315-325
+  CUVS_EXPECTS(is_device_compatible(queries), "queries should have device compatible memory");
+  CUVS_EXPECTS(is_device_compatible(neighbors), "neighbors should have device compatible memory");
+  CUVS_EXPECTS(is_device_compatible(distances), "distances should have device compatible memory");
+  CUVS_EXPECTS(neighbors.dtype.code == kDLInt && neighbors.dtype.bits == 64,
+               "neighbors should be of type int64_t");
+  CUVS_EXPECTS(distances.dtype.code == kDLFloat && distances.dtype.bits == 32,
+               "distances should be of type float32");
+  auto* ix = index_of(index);
+  auto et  = elem_of_dtype(queries.dtype, "queries");
+  void* q  = checked_data(queries_tensor, queries.dtype.code, queries.dtype.bits, 2, true, "queries");
+  auto* nb = static_cast<int64_t*>(checked_data(neighbors_tensor, kDLInt, 64, 2, true, "neighbors"));
+  auto* ds = static_cast<float*>(checked_data(distances_tensor, kDLFloat, 32, 2, true, "distances"));
+  // ivf_pq_search.cuh:1080-1108
+  CUVS_EXPECTS(queries.shape[0] == neighbors.shape[0] && queries.shape[0] == distances.shape[0],
+               "Number of rows in output neighbors and distances matrices must equal the number "
+               "of queries.");
+  CUVS_EXPECTS(neighbors.shape[1] == distances.shape[1],
+               "Number of columns in output neighbors and distances matrices must equal k");
+  CUVS_EXPECTS(queries.shape[1] == int64_t(ix->dim()),
+               "Number of query dimensions should equal number of dimensions in the index.");
+  ivf_pq::search_params sp;
+  sp.n_probes                 = params->n_probes;
+  sp.lut_dtype                = params->lut_dtype;
+  sp.internal_distance_dtype  = params->internal_distance_dtype;
+  sp.preferred_shmem_carveout = params->preferred_shmem_carveout;
+  sp.coarse_search_dtype      = params->coarse_search_dtype;
+  sp.max_internal_batch_size  = params->max_internal_batch_size;
+  ivf_pq::search_any(*res_of(res), sp, *ix, q, et, uint32_t(queries.shape[0]),
+                     uint32_t(neighbors.shape[1]), nb, ds, nullptr, filter);
+}
+}  // namespace
+
 extern "C" cuvsError_t cuvsIvfPqSearch(cuvsResources_t res, cuvsIvfPqSearchParams_t params,
                                        cuvsIvfPqIndex_t index, DLManagedTensor* queries_tensor,
                                        DLManagedTensor* neighbors_tensor,
                                        DLManagedTensor* distances_tensor)
 {
+  return translate_exceptions(
+    [=] { search_entry(res, params, index, queries_tensor, neighbors_tensor, distances_tensor, {}); });
+}
+
+extern "C" cuvsError_t cuvsIvfPqSearchWithFilter(cuvsResources_t res, cuvsIvfPqSearchParams_t params,
+                                                 cuvsIvfPqIndex_t index, DLManagedTensor* queries_tensor,
+                                                 DLManagedTensor* neighbors_tensor,
+                                                 DLManagedTensor* distances_tensor, cuvsFilter filter)
+{
   return translate_exceptions([=] {
-    CUVS_EXPECTS(params && queries_tensor && neighbors_tensor && distances_tensor, "null argument");
-    const DLTensor& queries   = queries_tensor->dl_tensor;
-    const DLTensor& neighbors = neighbors_tensor->dl_tensor;
-    const DLTensor& distances = distances_tensor->dl_tensor;
-    // c/src/neighbors/ivf_pq.cpp:315-325
-    CUVS_EXPECTS(is_device_compatible(queries), "queries should have device compatible memory");
-    CUVS_EXPECTS(is_device_compatible(neighbors), "neighbors should have device compatible memory");
-    CUVS_EXPECTS(is_device_compatible(distances), "distances should have device compatible memory");
-    CUVS_EXPECTS(neighbors.dtype.code == kDLInt && neighbors.dtype.bits == 64,
-                 "neighbors should be of type int64_t");
-    CUVS_EXPECTS(distances.dtype.code == kDLFloat && distances.dtype.bits == 32,
-                 "distances should be of type float32");
-    auto* ix = index_of(index);
-    auto et  = elem_of_dtype(queries.dtype, "queries");
-    void* q  = checked_data(queries_tensor, queries.dtype.code, queries.dtype.bits, 2, true, "queries");
-    auto* nb = static_cast<int64_t*>(checked_data(neighbors_tensor, kDLInt, 64, 2, true, "neighbors"));
-    auto* ds = static_cast<float*>(checked_data(distances_tensor, kDLFloat, 32, 2, true, "distances"));
-    // ivf_pq_search.cuh:1080-1108
-    CUVS_EXPECTS(queries.shape[0] == neighbors.shape[0] && queries.shape[0] == distances.shape[0],
-                 "Number of rows in output neighbors and distances matrices must equal the number "
-                 "of queries.");
-    CUVS_EXPECTS(neighbors.shape[1] == distances.shape[1],
-                 "Number of columns in output neighbors and distances matrices must equal k");
-    CUVS_EXPECTS(queries.shape[1] == int64_t(ix->dim()),
-                 "Number of query dimensions should equal number of dimensions in the index.");
-    ivf_pq::search_params sp;
-    sp.n_probes                 = params->n_probes;
-    sp.lut_dtype                = params->lut_dtype;
-    sp.internal_distance_dtype  = params->internal_distance_dtype;
-    sp.preferred_shmem_carveout = params->preferred_shmem_carveout;
-    sp.coarse_search_dtype      = params->coarse_search_dtype;
-    sp.max_internal_batch_size  = params->max_internal_batch_size;
-    ivf_pq::search_any(*res_of(res), sp, *ix, q, et, uint32_t(queries.shape[0]),
-                       uint32_t(neighbors.shape[1]), nb, ds);
+    ivf_pq::bitset_view view{};
+    if (filter.type == BITSET) {
+      auto* bt = reinterpret_cast<DLManagedTensor*>(filter.addr);
+      view.bits = static_cast<const uint32_t*>(checked_data(bt, kDLUInt, 32, 1, true, "filter bitset"));
+      view.n_bits = uint64_t(bt->dl_tensor.shape[0]) * 32u;
+    } else {
+      CUVS_EXPECTS(filter.type == NO_FILTER, "Unsupported sample filter type");
+    }
+    search_entry(res, params, index, queries_tensor, neighbors_tensor, distances_tensor, view);
   });
 }
 

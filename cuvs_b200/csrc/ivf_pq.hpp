@@ -241,9 +241,16 @@ inline size_t elem_size(elem_t t) { return t == elem_t::f32 ? 4 : (t == elem_t::
 // Type-erased workers behind the typed overloads below.
 // `given_probes` (optional, device, [n_queries, min(n_probes, n_lists)] u32): lists to scan per
 // query, replacing the coarse stage (used when probe selection is shared between GPUs).
+// Bitset sample filter of the reference (cuvs::neighbors::filtering::bitset_filter<uint32_t, int64_t>,
+// cpp/src/neighbors/sample_filter.cuh:162-176): vector with source id i is searched iff bit i is set.
+struct bitset_view {
+  const uint32_t* bits = nullptr;  // device
+  uint64_t n_bits      = 0;
+};
 void search_any(raft::resources& res, const search_params& params, const index<int64_t>& idx,
                 const void* queries, elem_t qtype, uint32_t n_queries, uint32_t k,
-                int64_t* neighbors, float* distances, const uint32_t* given_probes = nullptr);
+                int64_t* neighbors, float* distances, const uint32_t* given_probes = nullptr,
+                bitset_view filter = {});
 // Probe selection alone, asynchronous on the handle's stream: probes [n_queries, n_probes] u32,
 // ascending by (score, list id).
 void select_probes_any(raft::resources& res, const index<int64_t>& idx, const void* queries,

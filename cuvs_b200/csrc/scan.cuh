@@ -46,6 +46,11 @@ struct scan_params {
   float* all_scores;    // store-all mode (KPL == 0): [n_q, max_samples] every score, no top-k
   uint32_t max_samples;
   uint32_t* work_counter;
+  const uint32_t* n_work;  // number of work items (non-empty pairs), on the device
+  // optional bitset filter over source ids (cpp/src/neighbors/sample_filter.cuh:162-176)
+  const int64_t* ids;
+  const uint32_t* filter_bits;
+  uint64_t filter_nbits;
   // shared memory plan
   uint32_t n_groups, group_threads;
   uint32_t pqc_in_smem, smem_pqc_bytes, smem_group_bytes, lut_bytes, base_bytes, merge_bytes;
@@ -350,11 +355,12 @@ __global__ void __launch_bounds__(1024, 1) scan_kernel(const scan_params p)
   warp_topk<(KPL > 0 ? KPL : 1)> queue;
 
   // The next work item is claimed one pair ahead so that the atomic's latency is hidden.
+  const uint32_t n_work = __ldg(p.n_work);
   if (gt == 0) { s_item[0] = atomicAdd(p.work_counter, 1u); }
   for (uint32_t it = 0;; it++) {
     group_bar(bar_id, gthreads);
     const uint32_t w = s_item[it & 1u];
-    if (w >= p.n_pairs) { break; }
+    if (w >= n_work) { break; }
     if (gt == 0) { s_item[(it + 1u) & 1u] = atomicAdd(p.work_counter, 1u); }
 
     const uint4 d0       = __ldg(p.work + 2 * size_t(w));
@@ -474,7 +480,11 @@ __global__ void __launch_bounds__(1024, 1) scan_kernel(const scan_params p)
         }
         const float score    = acc.result(p.cosine != 0);
         const uint32_t row   = gi * 32u + lane;
-        const bool valid     = row < n;
+        bool valid           = row < n;
+        if (p.filter_bits != nullptr && valid) {
+          const int64_t id = p.ids[first_row + row];
+          valid = id >= 0 && uint64_t(id) < p.filter_nbits && ((p.filter_bits[id >> 5] >> (id & 31)) & 1u);
+        }
         if constexpr (kStoreAll) {
           if (valid) { p.all_scores[size_t(q) * p.max_samples + sample_offset + row] = score; }
         } else {

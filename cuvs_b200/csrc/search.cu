@@ -121,7 +121,8 @@ __global__ void prep_queries_kernel(const T* __restrict__ queries, uint32_t dim,
 // ------------------------------------------------------------------------------------------------
 // per-probe sample offsets + counting sort of the (query, probe) pairs by list
 // ------------------------------------------------------------------------------------------------
-// One warp per query: chunk_index[q, p] = sum_{p' <= p} list_sizes[probes[q, p']]; list_count[l]++.
+// One warp per query: chunk_index[q, p] = sum_{p' <= p} list_sizes[probes[q, p']]; list_count[l]++
+// for every probe of a non-empty list.
 __global__ void chunk_and_count_kernel(const uint32_t* __restrict__ probes,
                                        const uint32_t* __restrict__ list_sizes, uint32_t n_queries,
                                        uint32_t n_probes, uint32_t* __restrict__ chunk_index,
@@ -137,7 +138,7 @@ __global__ void chunk_and_count_kernel(const uint32_t* __restrict__ probes,
     if (p < n_probes) {
       const uint32_t label = probes[size_t(q) * n_probes + p];
       v                    = list_sizes[label];
-      atomicAdd(list_count + label, 1u);
+      if (v > 0) { atomicAdd(list_count + label, 1u); }  // empty lists never reach the work list
     }
 #pragma unroll
     for (int d = 1; d < 32; d <<= 1) {
@@ -149,7 +150,8 @@ __global__ void chunk_and_count_kernel(const uint32_t* __restrict__ probes,
   }
 }
 
-// Exclusive prefix sum over n values, in place, by one block of 1024 threads.
+// Exclusive prefix sum over n values, in place, by one block of 1024 threads, 4 values per thread
+// per step.  data[n] must exist: it receives the total.
 __global__ void exclusive_scan_kernel(uint32_t* __restrict__ data, uint32_t n)
 {
   __shared__ uint32_t s_warp[32];
@@ -157,10 +159,13 @@ __global__ void exclusive_scan_kernel(uint32_t* __restrict__ data, uint32_t n)
   const uint32_t tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
   if (tid == 0) { s_carry = 0; }
   __syncthreads();
-  for (uint32_t base = 0; base < n; base += 1024) {
-    const uint32_t i = base + tid;
-    uint32_t v       = i < n ? data[i] : 0u;
-    uint32_t x       = v;
+  for (uint32_t base = 0; base < n; base += 4096) {
+    const uint32_t i0 = base + tid * 4;
+    uint32_t v[4];
+#pragma unroll
+    for (int e = 0; e < 4; e++) { v[e] = (i0 + e < n) ? data[i0 + e] : 0u; }
+    const uint32_t mine = v[0] + v[1] + v[2] + v[3];
+    uint32_t x          = mine;
 #pragma unroll
     for (int d = 1; d < 32; d <<= 1) {
       uint32_t t = __shfl_up_sync(kFullMask, x, d);
@@ -178,13 +183,17 @@ __global__ void exclusive_scan_kernel(uint32_t* __restrict__ data, uint32_t n)
       s_warp[lane] = w;
     }
     __syncthreads();
-    const uint32_t carry  = s_carry;
-    const uint32_t before = carry + (wid > 0 ? s_warp[wid - 1] : 0u) + (x - v);
-    if (i < n) { data[i] = before; }
+    uint32_t run = s_carry + (wid > 0 ? s_warp[wid - 1] : 0u) + (x - mine);
+#pragma unroll
+    for (int e = 0; e < 4; e++) {
+      if (i0 + e < n) { data[i0 + e] = run; }
+      run += v[e];
+    }
     __syncthreads();
-    if (tid == 1023) { s_carry = before + v; }
+    if (tid == 1023) { s_carry = run; }
     __syncthreads();
   }
+  if (tid == 0) { data[n] = s_carry; }
 }
 
 // Counters for the benchmark: sum over pairs, and over distinct probed lists, of ceil(size / 32).
@@ -217,11 +226,18 @@ __global__ void scatter_pairs_kernel(const uint32_t* __restrict__ probes,
                                      const uint32_t* __restrict__ list_sizes,
                                      const uint64_t* __restrict__ row_off, uint32_t n_pairs,
                                      uint32_t n_probes, uint32_t* __restrict__ cursor,
-                                     uint4* __restrict__ work)
+                                     uint4* __restrict__ work, uint64_t* __restrict__ out_keys, uint32_t k)
 {
   const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n_pairs) { return; }
   const uint32_t label = probes[i];
+  if (list_sizes[label] == 0) {
+    // nothing to scan (e.g. a list owned by another GPU): the pair's result slots are empty
+    if (out_keys) {
+      for (uint32_t t = 0; t < k; t++) { out_keys[size_t(i) * k + t] = kEmptyKey; }
+    }
+    return;
+  }
   const uint32_t q     = i / n_probes;
   const uint32_t pi    = i - q * n_probes;
   const uint32_t pos   = atomicAdd(cursor + label, 1u);
@@ -488,7 +504,7 @@ scan_plan plan_scan(const raft::resources& res, const index<int64_t>& idx, int l
 // ------------------------------------------------------------------------------------------------
 void search_any(raft::resources& res, const search_params& params, const index<int64_t>& idx,
                 const void* queries, elem_t qtype, uint32_t n_queries, uint32_t k,
-                int64_t* neighbors, float* distances, const uint32_t* given_probes)
+                int64_t* neighbors, float* distances, const uint32_t* given_probes, bitset_view filter)
 {
   // ivf_pq_search.cuh:901-917
   CUVS_EXPECTS(params.internal_distance_dtype == CUDA_R_16F ||
@@ -622,9 +638,11 @@ void search_any(raft::resources& res, const search_params& params, const index<i
                                                                               n_lists, res.d_stats);
       res.stat_pairs += n_pairs;
     }
-    exclusive_scan_kernel<<<1, 1024, 0, stream>>>(d_count, n_lists);
+    exclusive_scan_kernel<<<1, 1024, 0, stream>>>(d_count, n_lists);  // d_count[n_lists] = work items
+    CUDA_TRY(cudaMemcpyAsync(d_counter + 1, d_count + n_lists, 4, cudaMemcpyDeviceToDevice, stream));
     scatter_pairs_kernel<<<ceildiv<uint32_t>(n_pairs, 256), 256, 0, stream>>>(
-      d_probes, d_chunk, idx.list_sizes(), idx.row_offsets(), n_pairs, n_probes, d_count, d_order);
+      d_probes, d_chunk, idx.list_sizes(), idx.row_offsets(), n_pairs, n_probes, d_count, d_order,
+      store_all ? nullptr : d_keys, k);
     fill_u32_kernel<<<ceildiv<uint32_t>(nq, 256), 256, 0, stream>>>(d_kth, nq, kEmptyScore);
     CUDA_TRY(cudaMemsetAsync(d_counter, 0, 4, stream));
     CUDA_TRY(cudaGetLastError());
@@ -658,6 +676,10 @@ void search_any(raft::resources& res, const search_params& params, const index<i
       sp.all_scores     = d_all;
       sp.max_samples    = max_samples;
       sp.work_counter   = d_counter;
+      sp.n_work         = d_counter + 1;
+      sp.ids            = idx.ids();
+      sp.filter_bits    = filter.bits;
+      sp.filter_nbits   = filter.n_bits;
       sp.n_groups       = plan.n_groups;
       sp.group_threads  = plan.group_threads;
       sp.pqc_in_smem    = plan.pqc_in_smem;

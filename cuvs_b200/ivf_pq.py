@@ -234,8 +234,11 @@ def build_precomputed(index_params: IndexParams, dim, pq_centers, centers, cente
 
 
 def search(search_params: SearchParams, index: Index, queries, k, neighbors=None, distances=None,
-           resources: Resources | None = None, sync: bool = True):
-    """Returns ``(distances, neighbors)`` -- f32 and i64 device tensors of shape [n_queries, k]."""
+           resources: Resources | None = None, sync: bool = True, filter=None):
+    """Returns ``(distances, neighbors)`` -- f32 and i64 device tensors of shape [n_queries, k].
+
+    ``filter``: optional uint32 device tensor, the reference's bitset filter -- the vector with
+    source id ``i`` may be returned only if bit ``i`` (bit ``i % 32`` of word ``i // 32``) is set."""
     if not index.trained:
         raise ValueError("Index needs to be built before calling search.")
     res = _res(resources)
@@ -245,8 +248,14 @@ def search(search_params: SearchParams, index: Index, queries, k, neighbors=None
     if distances is None:
         distances = torch.empty((n, k), dtype=torch.float32, device="cuda")
     q, nb, ds = DLTensorRef(queries), DLTensorRef(neighbors), DLTensorRef(distances)
-    L.check(L.load().cuvsIvfPqSearch(res.handle, search_params._p, index._h, q.ref(), nb.ref(),
-                                     ds.ref()))
+    if filter is None:
+        L.check(L.load().cuvsIvfPqSearch(res.handle, search_params._p, index._h, q.ref(), nb.ref(),
+                                         ds.ref()))
+    else:
+        fb = DLTensorRef(filter)
+        f = L.FilterStruct(C.addressof(fb.managed), 1)   # BITSET
+        L.check(L.load().cuvsIvfPqSearchWithFilter(res.handle, search_params._p, index._h, q.ref(),
+                                                   nb.ref(), ds.ref(), f))
     if sync:
         res.sync()
     return distances, neighbors

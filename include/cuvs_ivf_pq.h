@@ -149,6 +149,25 @@ CUVS_EXPORT cuvsError_t cuvsIvfPqSearch(cuvsResources_t res,
                                         DLManagedTensor* queries,
                                         DLManagedTensor* neighbors,
                                         DLManagedTensor* distances);
+/* c/include/cuvs/neighbors/common.h:25-47 -- filter handle shared by the reference's search calls */
+enum cuvsFilterType { NO_FILTER = 0, BITSET = 1, BITMAP = 2 };
+typedef struct {
+  uintptr_t addr; /* BITSET: DLManagedTensor* of uint32 words on the device, bit i = source id i allowed */
+  enum cuvsFilterType type;
+} cuvsFilter;
+
+/* The reference's C entry takes no filter; its C++ search does (cpp/include/cuvs/neighbors/ivf_pq.hpp,
+ * overload with cuvs::neighbors::filtering::base_filter; device side
+ * cpp/src/neighbors/sample_filter.cuh:162-176).  This entry exposes that overload with the
+ * cuvsFilter convention the reference uses for its other indexes: NO_FILTER or BITSET. */
+CUVS_EXPORT cuvsError_t cuvsIvfPqSearchWithFilter(cuvsResources_t res,
+                                                  cuvsIvfPqSearchParams_t search_params,
+                                                  cuvsIvfPqIndex_t index,
+                                                  DLManagedTensor* queries,
+                                                  DLManagedTensor* neighbors,
+                                                  DLManagedTensor* distances,
+                                                  cuvsFilter filter);
+
 /* c/include/cuvs/neighbors/ivf_pq.h:570 -- writes the reference's file format, version 4 */
 CUVS_EXPORT cuvsError_t cuvsIvfPqSerialize(cuvsResources_t res,
                                            const char* filename,

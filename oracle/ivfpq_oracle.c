@@ -571,6 +571,22 @@ ORC_EXPORT void orc_build_lut(const orc_index* ix, uint32_t label, const float* 
 
 /* Fine search given the probes: neighbours [n_q,k] int64, distances [n_q,k] f32.
  * Optional raw outputs: internal scores before post-processing. */
+/* Bitset sample filter (cpp/src/neighbors/sample_filter.cuh:162-176): a vector is searched only if
+ * bit `source id` of the bitset is set.  NULL = no filter. */
+static const uint32_t* g_filter_bits = NULL;
+static uint64_t g_filter_nbits       = 0;
+ORC_EXPORT void orc_set_filter(const uint32_t* bits, uint64_t nbits)
+{
+  g_filter_bits  = bits;
+  g_filter_nbits = nbits;
+}
+static inline int filter_pass(int64_t id)
+{
+  if (!g_filter_bits) { return 1; }
+  if (id < 0 || (uint64_t)id >= g_filter_nbits) { return 0; }
+  return (g_filter_bits[id >> 5] >> (id & 31)) & 1u;
+}
+
 ORC_EXPORT int orc_search_probes(const orc_index* ix, const float* rot_q, const uint32_t* probes,
                                  uint32_t n_q, uint32_t n_probes, uint32_t k, int lut_dtype,
                                  int internal_dtype, float scale, int64_t* neighbors,
@@ -617,6 +633,7 @@ ORC_EXPORT int orc_search_probes(const orc_index* ix, const float* rot_q, const 
             scan_list_f16(ix, label, luth, cosine, scores);
           }
           for (uint32_t i = 0; i < n; i++) {
+            if (!filter_pass(ix->ids[ix->id_offsets[label] + i])) { continue; }
             cand_t c = {scores[i], offset + i};
             heap_push(hp, &nh, k, c);
           }

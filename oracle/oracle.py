@@ -439,9 +439,21 @@ def search_probes(ix: OracleIndex, rot_q, probes, k, lut_dtype=CUDA_R_32F,
 
 
 def search(ix: OracleIndex, queries: np.ndarray, k: int, n_probes: int = 20,
-           lut_dtype=CUDA_R_32F, internal_dtype=CUDA_R_32F, return_probes=False):
-    """Returns (distances f32 [n_q,k], neighbors i64 [n_q,k]) like the reference's search."""
+           lut_dtype=CUDA_R_32F, internal_dtype=CUDA_R_32F, return_probes=False, bitset=None):
+    """Returns (distances f32 [n_q,k], neighbors i64 [n_q,k]) like the reference's search.
+    `bitset` (u32 words, bit i = source id i may be returned) is the reference's bitset filter."""
     q = np.ascontiguousarray(queries)
+    if bitset is not None:
+        bits = np.ascontiguousarray(bitset, dtype=np.uint32)
+        lib().orc_set_filter(_ptr(bits), C.c_uint64(bits.size * 32))
+    try:
+        return _search(ix, q, k, n_probes, lut_dtype, internal_dtype, return_probes)
+    finally:
+        if bitset is not None:
+            lib().orc_set_filter(None, C.c_uint64(0))
+
+
+def _search(ix, q, k, n_probes, lut_dtype, internal_dtype, return_probes):
     n_q = q.shape[0]
     if q.shape[1] != ix.dim:
         raise ValueError("Number of query dimensions should equal number of dimensions in the index.")

@@ -358,3 +358,28 @@ def test_search_with_given_probes_equals_plain_search(ivf, many_lists):
     probes = torch.cat([mg.select_probes(g, q[:100], 24), mg.select_probes(g, q[100:], 24)])
     d1, i1 = mg.search_with_probes(sp, g, q, probes, 10)
     assert (i0 == i1).all() and (d0.view(torch.int32) == d1.view(torch.int32)).all()
+
+
+def test_bitset_filter_parity(ivf, oracle_mod, small_l2):
+    """cpp/tests/neighbors/ann_ivf_pq.cuh:724-876: a bitset removes ids from the search; here a
+    random third of the ids plus the first 300, checked id-for-id against the filtered oracle."""
+    O = oracle_mod
+    ix, q = small_l2["ix"], small_l2["q"]
+    n = ix.size
+    rng = np.random.default_rng(11)
+    allowed = rng.random(n) > 0.33
+    allowed[:300] = False
+    words = np.zeros((n + 31) // 32, dtype=np.uint32)
+    idx = np.nonzero(allowed)[0]
+    np.bitwise_or.at(words, idx // 32, (np.uint32(1) << (idx % 32).astype(np.uint32)))
+    g = ivf.load(small_l2["path"])
+    qd = torch.from_numpy(q).cuda()
+    fd = torch.from_numpy(words.view(np.int32)).cuda().view(torch.uint32)
+    for k, p, lut in ((10, 8, "f32"), (40, 32, "fp8"), (200, 16, "f16")):
+        sp = ivf.SearchParams(n_probes=p, lut_dtype=LUT[lut][0])
+        d, i = ivf.search(sp, g, qd, k, filter=fd)
+        d, i = d.cpu().numpy(), i.cpu().numpy()
+        do, io = O.search(ix, q, k, n_probes=p, lut_dtype=LUT[lut][1], bitset=words)
+        assert_parity(d, i, do, io, 1e-5 if lut == "f32" else 1e-2, max_tie_rows=0.05)
+        found = i[i != O.OUT_OF_BOUNDS]
+        assert allowed[found].all()
