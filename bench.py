@@ -376,11 +376,16 @@ def run_ours(args):
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
+        t_host = time.perf_counter()
         for _ in range(steps):
             fn()
+        t_host = time.perf_counter() - t_host
         e1.record()
         torch.cuda.synchronize()
         ms = e0.elapsed_time(e1)
+        if rank == 0:
+            log(f"[bench] timed {steps} steps: device {ms / steps:.3f} ms/step, "
+                f"host issue {t_host / steps * 1e3:.3f} ms/step")
         if world > 1:
             t = torch.tensor([ms], device=device)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)

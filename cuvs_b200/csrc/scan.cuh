@@ -168,6 +168,14 @@ __device__ __forceinline__ void sts_b16(uint32_t a, uint32_t v)
 {
   asm volatile("st.shared.b16 [%0], %1;" ::"r"(a), "h"(uint16_t(v)) : "memory");
 }
+__device__ __forceinline__ void lds_2xb64(uint32_t a, uint64_t& x, uint64_t& y)
+{
+  asm volatile("ld.shared.v2.b64 {%0, %1}, [%2];" : "=l"(x), "=l"(y) : "r"(a));
+}
+__device__ __forceinline__ void sts_b128(uint32_t a, uint64_t x, uint64_t y)
+{
+  asm volatile("st.shared.v2.b64 [%0], {%1, %2};" ::"r"(a), "l"(x), "l"(y) : "memory");
+}
 __device__ __forceinline__ uint64_t dup2(float x)
 {
   uint64_t v;
@@ -175,78 +183,119 @@ __device__ __forceinline__ uint64_t dup2(float x)
   return v;
 }
 
-// LUT of one pair from a codebook resident in shared memory.  A thread owns one pair of adjacent
-// codebook entries (b, b+1) and walks the subspaces with a fixed stride, so all addresses advance
-// by constants; LEN > 0 fixes pq_len at compile time (loads first, then the FMA chain).
+// LUT of one pair from a codebook resident in shared memory.  A thread owns four adjacent codebook
+// entries (b .. b+3) and walks the subspaces with a fixed stride, so all addresses advance by
+// constants; per subspace and component it issues one 16-byte codebook load and one broadcast load
+// of the pre-duplicated base difference.  LEN > 0 fixes pq_len at compile time.
+// Base layout (per rotated dimension): L2 (d, d); inner product (-q, -q, q*c, q*c).
 template <int PqBits, int LutKind, bool IsIP, int LEN>
 __device__ __forceinline__ void build_lut_smem(uint32_t pqc_a, uint32_t base_a, uint32_t lut_a,
                                                uint32_t pq_dim, uint32_t len_rt, uint32_t gt,
                                                uint32_t gthreads)
 {
-  constexpr uint32_t kBook   = 1u << PqBits;
-  constexpr uint32_t kPairs  = kBook / 2;
-  constexpr uint32_t kLutB   = LutKind == LUT_F32 ? 8u : (LutKind == LUT_F16 ? 4u : 2u);  // per pair
-  constexpr uint32_t kBaseB  = IsIP ? 8u : 4u;
+  constexpr uint32_t kBook  = 1u << PqBits;
+  constexpr uint32_t kUPJ   = kBook / 4;  // four-entry units per subspace
+  constexpr uint32_t kElem  = LutKind == LUT_F32 ? 4u : (LutKind == LUT_F16 ? 2u : 1u);
+  constexpr uint32_t kBaseB = IsIP ? 16u : 8u;
   const uint32_t len      = LEN > 0 ? uint32_t(LEN) : len_rt;
-  const uint32_t t        = gt % kPairs;
-  const uint32_t j_first  = gt / kPairs;
-  const uint32_t j_stride = gthreads / kPairs;
-  uint32_t cb             = pqc_a + (j_first * len * kBook + 2u * t) * 4u;
+  const uint32_t u        = gt % kUPJ;
+  const uint32_t j_first  = gt / kUPJ;
+  const uint32_t j_stride = gthreads / kUPJ;
+  uint32_t cb             = pqc_a + (j_first * len * kBook + 4u * u) * 4u;
   uint32_t bd             = base_a + j_first * len * kBaseB;
-  uint32_t out            = lut_a + (j_first * kPairs + t) * kLutB;
+  uint32_t out            = lut_a + (j_first * kBook + 4u * u) * kElem;
   const uint32_t cb_step  = j_stride * len * kBook * 4u;
   const uint32_t bd_step  = j_stride * len * kBaseB;
-  const uint32_t out_step = j_stride * kPairs * kLutB;
+  const uint32_t out_step = j_stride * kBook * kElem;
   for (uint32_t j = j_first; j < pq_dim; j += j_stride) {
-    uint64_t score = 0ull;  // (+0.0f, +0.0f)
+    uint64_t s0 = 0ull, s1 = 0ull;  // entries (b, b+1) and (b+2, b+3), each (+0.0f, +0.0f)
+    auto step = [&](uint64_t c0, uint64_t c1, uint64_t x, uint64_t y) {
+      if constexpr (!IsIP) {  // x = (d, d)
+        const uint64_t e0 = sub2(x, c0);
+        const uint64_t e1 = sub2(x, c1);
+        s0                = fma2(e0, e0, s0);
+        s1                = fma2(e1, e1, s1);
+      } else {  // x = (-q, -q), y = (q*c, q*c)
+        s0 = sub2(s0, y);
+        s1 = sub2(s1, y);
+        s0 = fma2(x, c0, s0);
+        s1 = fma2(x, c1, s1);
+      }
+    };
     if constexpr (LEN > 0) {
-      uint64_t pq2[LEN];
-      uint64_t bv[LEN];
+      uint64_t c0[LEN], c1[LEN], x[LEN], y[LEN];
 #pragma unroll
-      for (int kk = 0; kk < LEN; kk++) {
-        pq2[kk] = lds_b64(cb + uint32_t(kk) * kBook * 4u);
-        if constexpr (!IsIP) {
-          bv[kk] = dup2(lds_f32(bd + uint32_t(kk) * 4u));
-        } else {
-          bv[kk] = lds_b64(bd + uint32_t(kk) * 8u);
-        }
+      for (int kk = 0; kk < LEN; kk++) { lds_2xb64(cb + uint32_t(kk) * kBook * 4u, c0[kk], c1[kk]); }
+      if constexpr (IsIP) {
+#pragma unroll
+        for (int kk = 0; kk < LEN; kk++) { lds_2xb64(bd + uint32_t(kk) * 16u, x[kk], y[kk]); }
+      } else if constexpr (LEN == 1) {
+        x[0] = lds_b64(bd);
+      } else {
+#pragma unroll
+        for (int kk = 0; kk < LEN; kk += 2) { lds_2xb64(bd + uint32_t(kk) * 8u, x[kk], x[kk + 1]); }
       }
 #pragma unroll
-      for (int kk = 0; kk < LEN; kk++) {
-        if constexpr (!IsIP) {
-          const uint64_t dif = sub2(bv[kk], pq2[kk]);
-          score              = fma2(dif, dif, score);
-        } else {
-          const float q = lo2(bv[kk]), y = hi2(bv[kk]);
-          score         = sub2(score, dup2(y));
-          score         = fma2(dup2(-q), pq2[kk], score);
-        }
-      }
+      for (int kk = 0; kk < LEN; kk++) { step(c0[kk], c1[kk], x[kk], IsIP ? y[kk] : 0ull); }
     } else {
       for (uint32_t kk = 0; kk < len; kk++) {
-        const uint64_t pq2 = lds_b64(cb + kk * kBook * 4u);
-        if constexpr (!IsIP) {
-          const uint64_t dif = sub2(dup2(lds_f32(bd + kk * 4u)), pq2);
-          score              = fma2(dif, dif, score);
+        uint64_t c0, c1, x, y = 0ull;
+        lds_2xb64(cb + kk * kBook * 4u, c0, c1);
+        if constexpr (IsIP) {
+          lds_2xb64(bd + kk * 16u, x, y);
         } else {
-          const uint64_t qy = lds_b64(bd + kk * 8u);
-          score             = sub2(score, dup2(hi2(qy)));
-          score             = fma2(dup2(-lo2(qy)), pq2, score);
+          x = lds_b64(bd + kk * 8u);
         }
+        step(c0, c1, x, y);
       }
     }
     if constexpr (LutKind == LUT_F32) {
-      sts_b64(out, score);
+      sts_b128(out, s0, s1);
     } else if constexpr (LutKind == LUT_F16) {
-      const __half2 h = __floats2half2_rn(lo2(score), hi2(score));
-      sts_b32(out, *reinterpret_cast<const uint32_t*>(&h));
+      const __half2 h0 = __floats2half2_rn(lo2(s0), hi2(s0));
+      const __half2 h1 = __floats2half2_rn(lo2(s1), hi2(s1));
+      sts_b64(out, (uint64_t(*reinterpret_cast<const uint32_t*>(&h1)) << 32) |
+                     *reinterpret_cast<const uint32_t*>(&h0));
     } else {
-      sts_b16(out, uint32_t(fp8_encode<IsIP>(lo2(score))) | (uint32_t(fp8_encode<IsIP>(hi2(score))) << 8));
+      sts_b32(out, uint32_t(fp8_encode<IsIP>(lo2(s0))) | (uint32_t(fp8_encode<IsIP>(hi2(s0))) << 8) |
+                     (uint32_t(fp8_encode<IsIP>(lo2(s1))) << 16) | (uint32_t(fp8_encode<IsIP>(hi2(s1))) << 24));
     }
     cb += cb_step;
     bd += bd_step;
     out += out_step;
   }
+}
+
+// Shared-space loads with an immediate byte offset: [a + OFF].
+template <uint32_t OFF>
+__device__ __forceinline__ float lds_f32_off(uint32_t a)
+{
+  float v;
+  asm volatile("ld.shared.f32 %0, [%1+%2];" : "=f"(v) : "r"(a), "n"(OFF));
+  return v;
+}
+template <uint32_t OFF>
+__device__ __forceinline__ float lds_f16_as_f32_off(uint32_t a)
+{
+  float v;
+  asm volatile("{\n\t.reg .b16 h;\n\tld.shared.b16 h, [%1+%2];\n\tcvt.f32.f16 %0, h;\n\t}"
+               : "=f"(v)
+               : "r"(a), "n"(OFF));
+  return v;
+}
+template <uint32_t OFF>
+__device__ __forceinline__ __half lds_f16_off(uint32_t a)
+{
+  uint16_t v;
+  asm volatile("ld.shared.b16 %0, [%1+%2];" : "=h"(v) : "r"(a), "n"(OFF));
+  return __ushort_as_half(v);
+}
+template <uint32_t OFF>
+__device__ __forceinline__ uint32_t lds_u8_off(uint32_t a)
+{
+  uint32_t v;
+  asm volatile("ld.shared.u8 %0, [%1+%2];" : "=r"(v) : "r"(a), "n"(OFF));
+  return v;
 }
 
 // One looked-up entry added to the running score, in the internal distance type.
@@ -260,22 +309,23 @@ struct accum {
     f = 0.0f;
     h = __ushort_as_half(0);
   }
-  // `entry` = shared-space byte address of lut[row][code]
+  // lut[row][code] lives at shared-space byte address `entry` + OFF
+  template <uint32_t OFF>
   __device__ __forceinline__ void add(uint32_t entry)
   {
     if constexpr (!OutHalf) {
       if constexpr (LutKind == LUT_F32) {
-        f += lds_f32(entry);
+        f += lds_f32_off<OFF>(entry);
       } else if constexpr (LutKind == LUT_F16) {
-        f += __half2float(__ushort_as_half(static_cast<unsigned short>(lds_u16(entry))));
+        f += lds_f16_as_f32_off<OFF>(entry);
       } else {
-        f += fp8_to_float<IsIP>(lds_u8(entry));
+        f += fp8_to_float<IsIP>(lds_u8_off<OFF>(entry));
       }
     } else {
       if constexpr (LutKind == LUT_F16) {
-        h = __hadd(h, __ushort_as_half(static_cast<unsigned short>(lds_u16(entry))));
+        h = __hadd(h, lds_f16_off<OFF>(entry));
       } else {
-        h = __hadd(h, fp8_to_half<IsIP>(lds_u8(entry)));
+        h = __hadd(h, fp8_to_half<IsIP>(lds_u8_off<OFF>(entry)));
       }
     }
   }
@@ -291,29 +341,38 @@ struct accum {
 };
 
 // Codes of one 16-byte piece -> LUT lookups.  `row_a` = shared-space address of the LUT row of the
-// piece's first subspace; `n_valid` = codes used in this piece.
-template <int PqBits, int LutKind, bool OutHalf, bool IsIP, bool Full>
-__device__ __forceinline__ void score_piece(accum<LutKind, OutHalf, IsIP>& acc, const uint4& v,
+// piece's first subspace; `n_valid` = codes used in this piece.  The row offset of code C is an
+// immediate of the load, so a lookup costs: extract, scale-and-add, load, (convert,) add.
+template <int PqBits, int LutKind, bool OutHalf, bool IsIP, bool Full, int C>
+__device__ __forceinline__ void score_codes(accum<LutKind, OutHalf, IsIP>& acc, const uint32_t (&w)[4],
                                             uint32_t row_a, uint32_t n_valid)
 {
   constexpr uint32_t kBook = 1u << PqBits;
   constexpr uint32_t kMask = kBook - 1u;
   constexpr int kPerPiece  = 128 / PqBits;
   constexpr uint32_t kElem = LutKind == LUT_F32 ? 4u : (LutKind == LUT_F16 ? 2u : 1u);
-  const uint32_t w[4]      = {v.x, v.y, v.z, v.w};
-#pragma unroll
-  for (int c = 0; c < kPerPiece; c++) {
-    const int bit  = c * PqBits;
-    const int word = bit >> 5;
-    const int sh   = bit & 31;
+  if constexpr (C < kPerPiece) {
+    constexpr int bit  = C * PqBits;
+    constexpr int word = bit >> 5;
+    constexpr int sh   = bit & 31;
     uint32_t code;
-    if (sh + PqBits <= 32) {
+    if constexpr (PqBits == 8) {
+      code = __byte_perm(w[word], 0u, 0x4440u + uint32_t(sh >> 3));
+    } else if constexpr (sh + PqBits <= 32) {
       code = (w[word] >> sh) & kMask;
     } else {
       code = __funnelshift_r(w[word], w[word + 1 > 3 ? 3 : word + 1], sh) & kMask;
     }
-    if (Full || uint32_t(c) < n_valid) { acc.add(row_a + (uint32_t(c) * kBook + code) * kElem); }
+    if (Full || uint32_t(C) < n_valid) { acc.template add<uint32_t(C) * kBook * kElem>(row_a + code * kElem); }
+    score_codes<PqBits, LutKind, OutHalf, IsIP, Full, C + 1>(acc, w, row_a, n_valid);
   }
+}
+template <int PqBits, int LutKind, bool OutHalf, bool IsIP, bool Full>
+__device__ __forceinline__ void score_piece(accum<LutKind, OutHalf, IsIP>& acc, const uint4& v,
+                                            uint32_t row_a, uint32_t n_valid)
+{
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+  score_codes<PqBits, LutKind, OutHalf, IsIP, Full, 0>(acc, w, row_a, n_valid);
 }
 
 template <int PqBits, int LutKind, bool OutHalf, bool IsIP, int KPL>
@@ -354,14 +413,16 @@ __global__ void __launch_bounds__(1024, 1) scan_kernel(const scan_params p)
   constexpr bool kStoreAll = KPL == 0;  // k too large for registers: write every score instead
   warp_topk<(KPL > 0 ? KPL : 1)> queue;
 
-  // The next work item is claimed one pair ahead so that the atomic's latency is hidden.
+  // Work items are claimed four at a time (one atomic per four pairs keeps the single counter off
+  // the critical path), one claim ahead so that the atomic's latency is hidden.
+  constexpr uint32_t kClaim = 4;
   const uint32_t n_work = __ldg(p.n_work);
-  if (gt == 0) { s_item[0] = atomicAdd(p.work_counter, 1u); }
+  if (gt == 0) { s_item[0] = atomicAdd(p.work_counter, kClaim); }
   for (uint32_t it = 0;; it++) {
     group_bar(bar_id, gthreads);
-    const uint32_t w = s_item[it & 1u];
+    const uint32_t w = s_item[(it / kClaim) & 1u] + (it % kClaim);
     if (w >= n_work) { break; }
-    if (gt == 0) { s_item[(it + 1u) & 1u] = atomicAdd(p.work_counter, 1u); }
+    if (gt == 0 && (it % kClaim) == 0) { s_item[((it / kClaim) + 1u) & 1u] = atomicAdd(p.work_counter, kClaim); }
 
     const uint4 d0       = __ldg(p.work + 2 * size_t(w));
     const uint4 d1       = __ldg(p.work + 2 * size_t(w) + 1);
@@ -385,12 +446,15 @@ __global__ void __launch_bounds__(1024, 1) scan_kernel(const scan_params p)
     {
       const float* rq = p.rot_q + size_t(q) * p.rot_dim;
       const float* c  = p.centers_rot + size_t(label) * p.rot_dim;
+      // stored pre-duplicated for the packed arithmetic: L2 (d, d); inner product (-q, -q, q*c, q*c)
       for (uint32_t i = gt; i < p.rot_dim; i += gthreads) {
         if constexpr (!IsIP) {
-          s_base[i] = __fsub_rn(rq[i], __ldg(c + i));
+          const float d = __fsub_rn(rq[i], __ldg(c + i));
+          reinterpret_cast<float2*>(s_base)[i] = make_float2(d, d);
         } else {
-          float qv = rq[i];
-          reinterpret_cast<float2*>(s_base)[i] = make_float2(qv, __fmul_rn(__ldg(c + i), qv));
+          const float qv = rq[i];
+          const float y  = __fmul_rn(__ldg(c + i), qv);
+          reinterpret_cast<float4*>(s_base)[i] = make_float4(-qv, -qv, y, y);
         }
       }
     }
@@ -423,7 +487,7 @@ __global__ void __launch_bounds__(1024, 1) scan_kernel(const scan_params p)
       const uint32_t j_stride = uint32_t(gthreads) / kPairs;
       const uint32_t cb_step  = p.per_cluster ? 0u : len * kBook;
       const float* cb         = pqc + b + j_first * cb_step;
-      const float* bd         = s_base + j_first * len * (IsIP ? 2u : 1u);
+      const uint64_t* bd      = reinterpret_cast<const uint64_t*>(s_base) + j_first * len * (IsIP ? 2u : 1u);
       uint32_t e2             = j_first * kPairs + (uint32_t(gt) % kPairs);
       for (uint32_t j = j_first; j < p.pq_dim; j += j_stride) {
         uint64_t score = 0ull;
@@ -431,12 +495,11 @@ __global__ void __launch_bounds__(1024, 1) scan_kernel(const scan_params p)
           const float2 pq    = __ldg(reinterpret_cast<const float2*>(cb + kk * kBook));
           const uint64_t pq2 = pack2(pq.x, pq.y);
           if constexpr (!IsIP) {
-            const uint64_t dif = sub2(dup2(bd[kk]), pq2);
+            const uint64_t dif = sub2(bd[kk], pq2);
             score              = fma2(dif, dif, score);
           } else {
-            const float2 qy = reinterpret_cast<const float2*>(bd)[kk];
-            score           = sub2(score, dup2(qy.y));
-            score           = fma2(dup2(-qy.x), pq2, score);
+            score = sub2(score, bd[2 * kk + 1]);
+            score = fma2(bd[2 * kk], pq2, score);
           }
         }
         if constexpr (LutKind == LUT_F32) {

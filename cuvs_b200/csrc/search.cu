@@ -469,7 +469,8 @@ scan_plan plan_scan(const raft::resources& res, const index<int64_t>& idx, int l
   scan_plan plan{};
   const size_t lut_elem  = lut_kind == LUT_F32 ? 4 : (lut_kind == LUT_F16 ? 2 : 1);
   const size_t lut_bytes = round_up<size_t>(size_t(idx.pq_dim()) * idx.pq_book_size() * lut_elem, 16);
-  const size_t base_bytes = round_up<size_t>(size_t(idx.rot_dim()) * (is_ip ? 8 : 4), 16);
+  // base differences are stored pre-duplicated: (d, d) or (-q, -q, q*c, q*c) per rotated dimension
+  const size_t base_bytes = round_up<size_t>(size_t(idx.rot_dim()) * (is_ip ? 16 : 8), 16);
   const size_t pqc_bytes =
     idx.codebook_kind() == codebook_gen::PER_SUBSPACE
       ? round_up<size_t>(size_t(idx.pq_dim()) * idx.pq_len() * idx.pq_book_size() * 4, 16)
