@@ -129,6 +129,7 @@ SIGNATURES = {
     "cuvsB200CoarseSelect": [C.c_size_t, C.c_void_p, _P(DLManagedTensor), _P(DLManagedTensor),
                              _P(DLManagedTensor), C.c_int, _P(C.c_uint32)],
     "cuvsB200SetCoarseMode": [C.c_int],
+    "cuvsB200SetScanCodebookHome": [C.c_int],
     "cuvsB200StatsEnable": [C.c_size_t, C.c_bool],
     "cuvsB200StatsGet": [C.c_size_t, _P(SearchStats), C.c_bool],
     "cuvsIvfPqPredictNoAlloc": [C.c_size_t, _P(IndexStruct), _P(DLManagedTensor), _P(DLManagedTensor)],

@@ -706,6 +706,14 @@ extern "C" cuvsError_t cuvsB200SetCoarseMode(int mode)
   });
 }
 
+extern "C" cuvsError_t cuvsB200SetScanCodebookHome(int home)
+{
+  return translate_exceptions([=] {
+    CUVS_EXPECTS(home == 0 || home == 1, "home must be 0 or 1");
+    ivf_pq::set_scan_codebook_home(home);
+  });
+}
+
 // ------------------------------------------------------------------------------------------------
 // refine (c/src/neighbors/refine.cpp)
 // ------------------------------------------------------------------------------------------------

@@ -54,6 +54,9 @@ struct scan_params {
   // shared memory plan
   uint32_t n_groups, group_threads;
   uint32_t pqc_in_smem, smem_pqc_bytes, smem_group_bytes, lut_bytes, base_bytes, merge_bytes;
+  // codebook in tensor memory: columns allocated (0 = not used), byte offset in shared memory of
+  // the word that receives the allocation's address
+  uint32_t tmem_cols, tmem_slot_off;
 };
 
 enum { LUT_F32 = 0, LUT_F16 = 1, LUT_FP8 = 2 };
@@ -266,6 +269,175 @@ __device__ __forceinline__ void build_lut_smem(uint32_t pqc_a, uint32_t base_a, 
   }
 }
 
+// ---- tensor memory (TMEM) as a per-SM store for the codebook -------------------------------------
+// Warp w reaches TMEM lanes 32 * (w % 4) .. + 31 (one lane per thread, 32x32b shape); an address is
+// (lane << 16) | column.
+__device__ __forceinline__ void tmem_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tmem_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tmem_st4(uint32_t taddr, float a, float b, float c, float d)
+{
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};" ::"r"(taddr),
+               "r"(__float_as_uint(a)), "r"(__float_as_uint(b)), "r"(__float_as_uint(c)),
+               "r"(__float_as_uint(d))
+               : "memory");
+}
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void tmem_ld(uint32_t taddr, uint32_t (&r)[N])
+{
+  static_assert(N == 4 || N == 8 || N == 16, "4, 8 or 16 columns");
+  if constexpr (N == 4) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(taddr)
+                 : "memory");
+  } else if constexpr (N == 8) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "r"(taddr)
+                 : "memory");
+  } else {
+    asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+  }
+}
+
+// Codebook layout in TMEM (written once per CTA by threads 0..127, read by every thread from the
+// lane tid % 128): lane L holds, for the four-entry unit u = L % kUPJ, the subspaces
+// j = L / kUPJ + m * (128 / kUPJ), m = 0, 1, ...; columns (m * LEN + kk) * 4 .. + 3 hold entries
+// 4u .. 4u+3 of component kk.  A group of a multiple of 128 threads therefore finds the units of its
+// usual assignment (unit gt % kUPJ, subspaces gt / kUPJ + i * gthreads / kUPJ) in its own lanes at
+// m = gt / 128 + i * gthreads / 128.
+template <int PqBits, int LEN>
+__device__ __forceinline__ void fill_codebook_tmem(uint32_t tmem_lane_a, const float* pq_centers,
+                                                   uint32_t pq_dim, uint32_t lane128)
+{
+  constexpr uint32_t kBook  = 1u << PqBits;
+  constexpr uint32_t kUPJ   = kBook / 4;
+  constexpr uint32_t kJPerM = 128u / kUPJ;
+  const uint32_t u          = lane128 % kUPJ;
+  const uint32_t n_m        = (pq_dim + kJPerM - 1) / kJPerM;
+  for (uint32_t m = 0; m < n_m; m++) {
+    const uint32_t j = lane128 / kUPJ + m * kJPerM;
+#pragma unroll
+    for (int kk = 0; kk < LEN; kk++) {
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (j < pq_dim) {
+        v = __ldg(reinterpret_cast<const float4*>(pq_centers + (size_t(j) * LEN + kk) * kBook + 4u * u));
+      }
+      tmem_st4(tmem_lane_a + (m * LEN + uint32_t(kk)) * 4u, v.x, v.y, v.z, v.w);
+    }
+  }
+  tmem_wait_st();
+}
+
+// LUT of one pair from the codebook in TMEM: same thread-to-entry assignment and arithmetic as
+// build_lut_smem, the codebook operand arrives through tcgen05.ld (one load of 4 * LEN columns per
+// subspace, requested one subspace ahead) and no longer occupies the shared-memory pipe.
+template <int PqBits, int LutKind, bool IsIP, int LEN>
+__device__ __forceinline__ void build_lut_tmem(uint32_t tmem_lane_a, uint32_t base_a, uint32_t lut_a,
+                                               uint32_t pq_dim, uint32_t gt, uint32_t gthreads)
+{
+  constexpr uint32_t kBook  = 1u << PqBits;
+  constexpr uint32_t kUPJ   = kBook / 4;
+  constexpr uint32_t kJPerM = 128u / kUPJ;
+  constexpr uint32_t kElem  = LutKind == LUT_F32 ? 4u : (LutKind == LUT_F16 ? 2u : 1u);
+  constexpr uint32_t kBaseB = IsIP ? 16u : 8u;
+  constexpr int kCols       = 4 * LEN;
+  const uint32_t u          = gt % kUPJ;
+  const uint32_t j_first    = gt / kUPJ;
+  const uint32_t j_stride   = gthreads / kUPJ;
+  const uint32_t n_m        = (pq_dim + kJPerM - 1) / kJPerM;
+  const uint32_t m_stride   = gthreads / 128u;
+  // warp-uniform trip count (the tensor-memory loads need the whole warp): subspaces of the warp's
+  // first lane; a lane whose subspace falls beyond pq_dim computes nothing
+  const uint32_t j_warp     = (gt & ~31u) / kUPJ;
+  const uint32_t n_iter     = j_warp < pq_dim ? (pq_dim - j_warp + j_stride - 1) / j_stride : 0u;
+  uint32_t m                = gt / 128u;
+  uint32_t j                = j_first;
+  uint32_t bd               = base_a + j_first * LEN * kBaseB;
+  uint32_t out              = lut_a + (j_first * kBook + 4u * u) * kElem;
+  const uint32_t bd_step    = j_stride * LEN * kBaseB;
+  const uint32_t out_step   = j_stride * kBook * kElem;
+
+  auto col_of = [&](uint32_t mm) { return tmem_lane_a + min(mm, n_m - 1u) * uint32_t(kCols); };
+  auto compute = [&](const uint32_t (&c)[kCols]) {
+    if (j < pq_dim) {
+      uint64_t s0 = 0ull, s1 = 0ull;  // entries (b, b+1) and (b+2, b+3), each (+0.0f, +0.0f)
+      uint64_t x[LEN], y[LEN];
+      if constexpr (IsIP) {
+#pragma unroll
+        for (int kk = 0; kk < LEN; kk++) { lds_2xb64(bd + uint32_t(kk) * 16u, x[kk], y[kk]); }
+      } else if constexpr (LEN == 1) {
+        x[0] = lds_b64(bd);
+      } else {
+#pragma unroll
+        for (int kk = 0; kk < LEN; kk += 2) { lds_2xb64(bd + uint32_t(kk) * 8u, x[kk], x[kk + 1]); }
+      }
+#pragma unroll
+      for (int kk = 0; kk < LEN; kk++) {
+        const uint64_t c0 = (uint64_t(c[kk * 4 + 1]) << 32) | c[kk * 4 + 0];
+        const uint64_t c1 = (uint64_t(c[kk * 4 + 3]) << 32) | c[kk * 4 + 2];
+        if constexpr (!IsIP) {  // x = (d, d)
+          const uint64_t e0 = sub2(x[kk], c0);
+          const uint64_t e1 = sub2(x[kk], c1);
+          s0                = fma2(e0, e0, s0);
+          s1                = fma2(e1, e1, s1);
+        } else {  // x = (-q, -q), y = (q*c, q*c)
+          s0 = sub2(s0, y[kk]);
+          s1 = sub2(s1, y[kk]);
+          s0 = fma2(x[kk], c0, s0);
+          s1 = fma2(x[kk], c1, s1);
+        }
+      }
+      if constexpr (LutKind == LUT_F32) {
+        sts_b128(out, s0, s1);
+      } else if constexpr (LutKind == LUT_F16) {
+        const __half2 h0 = __floats2half2_rn(lo2(s0), hi2(s0));
+        const __half2 h1 = __floats2half2_rn(lo2(s1), hi2(s1));
+        sts_b64(out, (uint64_t(*reinterpret_cast<const uint32_t*>(&h1)) << 32) |
+                       *reinterpret_cast<const uint32_t*>(&h0));
+      } else {
+        sts_b32(out, uint32_t(fp8_encode<IsIP>(lo2(s0))) | (uint32_t(fp8_encode<IsIP>(hi2(s0))) << 8) |
+                       (uint32_t(fp8_encode<IsIP>(lo2(s1))) << 16) | (uint32_t(fp8_encode<IsIP>(hi2(s1))) << 24));
+      }
+    }
+    j += j_stride;
+    bd += bd_step;
+    out += out_step;
+  };
+
+  if constexpr (LEN <= 2) {
+    // two register buffers: the next subspace's load is in flight while this one is computed
+    uint32_t ca[kCols], cb[kCols];
+    if (n_iter > 0) { tmem_ld<kCols>(col_of(m), ca); }
+    for (uint32_t i = 0; i < n_iter; i += 2) {
+      tmem_wait_ld();
+      if (i + 1 < n_iter) { tmem_ld<kCols>(col_of(m + m_stride), cb); }
+      compute(ca);
+      if (i + 1 < n_iter) {
+        tmem_wait_ld();
+        if (i + 2 < n_iter) { tmem_ld<kCols>(col_of(m + 2u * m_stride), ca); }
+        compute(cb);
+      }
+      m += 2u * m_stride;
+    }
+  } else {
+    uint32_t ca[kCols];
+    for (uint32_t i = 0; i < n_iter; i++, m += m_stride) {
+      tmem_ld<kCols>(col_of(m), ca);
+      tmem_wait_ld();
+      compute(ca);
+    }
+  }
+}
+
 // Shared-space loads with an immediate byte offset: [a + OFF].
 template <uint32_t OFF>
 __device__ __forceinline__ float lds_f32_off(uint32_t a)
@@ -400,6 +572,30 @@ __global__ void __launch_bounds__(1024, 1) scan_kernel(const scan_params p)
   uint32_t* s_item  = reinterpret_cast<uint32_t*>(gbase + p.lut_bytes + p.base_bytes + p.merge_bytes);
   uint32_t* s_thr   = s_item + 2;  // group-wide bound on the k-th best ordered score of this pair
 
+  uint32_t tmem_base = 0;
+  if (p.tmem_cols) {
+    // per-subspace codebook -> tensor memory, once per CTA
+    uint32_t* slot = reinterpret_cast<uint32_t*>(smem + p.tmem_slot_off);
+    if (tid < 32) {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(slot)),
+                   "r"(p.tmem_cols)
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tmem_fence_before();
+    __syncthreads();
+    tmem_fence_after();
+    tmem_base = *reinterpret_cast<volatile uint32_t*>(slot);
+    if (tid < 128) {
+      const uint32_t lane_a = tmem_base + ((uint32_t(tid) & ~31u) << 16);
+      switch (p.pq_len) {
+        case 1: fill_codebook_tmem<PqBits, 1>(lane_a, p.pq_centers, p.pq_dim, uint32_t(tid)); break;
+        case 2: fill_codebook_tmem<PqBits, 2>(lane_a, p.pq_centers, p.pq_dim, uint32_t(tid)); break;
+        default: fill_codebook_tmem<PqBits, 4>(lane_a, p.pq_centers, p.pq_dim, uint32_t(tid)); break;
+      }
+    }
+    tmem_fence_before();
+  }
   if (p.pqc_in_smem) {
     const uint32_t n4 = (p.pq_dim * p.pq_len * kBook) / 4;
     const float4* src = reinterpret_cast<const float4*>(p.pq_centers);
@@ -407,6 +603,9 @@ __global__ void __launch_bounds__(1024, 1) scan_kernel(const scan_params p)
     for (uint32_t i = tid; i < n4; i += blockDim.x) { dst[i] = __ldg(src + i); }
   }
   __syncthreads();
+  tmem_fence_after();
+  // this warp's window into tensor memory: lanes 32 * (warp % 4) .. + 31
+  const uint32_t tmem_lane_a = tmem_base + (((uint32_t(tid) >> 5) & 3u) << 21);
 
   const uint32_t len     = p.pq_len;
   const uint32_t k       = p.k;
@@ -469,7 +668,14 @@ __global__ void __launch_bounds__(1024, 1) scan_kernel(const scan_params p)
     if (uint32_t(gw) < n_groups) { nxt = __ldg(src); }
 
     // ---- LUT ----
-    if (p.pqc_in_smem) {
+    if (p.tmem_cols) {
+      const uint32_t base_a = smem_addr(s_base), lut_a = smem_addr(s_lut);
+      switch (len) {
+        case 1: build_lut_tmem<PqBits, LutKind, IsIP, 1>(tmem_lane_a, base_a, lut_a, p.pq_dim, gt, gthreads); break;
+        case 2: build_lut_tmem<PqBits, LutKind, IsIP, 2>(tmem_lane_a, base_a, lut_a, p.pq_dim, gt, gthreads); break;
+        default: build_lut_tmem<PqBits, LutKind, IsIP, 4>(tmem_lane_a, base_a, lut_a, p.pq_dim, gt, gthreads); break;
+      }
+    } else if (p.pqc_in_smem) {
       const uint32_t pqc_a = smem_addr(s_pqc), base_a = smem_addr(s_base), lut_a = smem_addr(s_lut);
       switch (len) {
         case 1: build_lut_smem<PqBits, LutKind, IsIP, 1>(pqc_a, base_a, lut_a, p.pq_dim, len, gt, gthreads); break;
@@ -579,6 +785,14 @@ __global__ void __launch_bounds__(1024, 1) scan_kernel(const scan_params p)
     }
     }
     // the barrier at the top of the loop orders warp 0's reads of s_merge before the next writes
+  }
+  if (p.tmem_cols) {
+    tmem_fence_before();
+    __syncthreads();
+    if (tid < 32) {
+      asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(p.tmem_cols)
+                   : "memory");
+    }
   }
 }
 

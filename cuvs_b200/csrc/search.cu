@@ -463,6 +463,12 @@ void launch_prep(raft::resources& res, const index<int64_t>& idx, const void* qp
 // ------------------------------------------------------------------------------------------------
 // shared-memory plan of the scan kernel
 // ------------------------------------------------------------------------------------------------
+int& scan_codebook_home()
+{
+  static int home = 0;  // 0 = choose, 1 = never tensor memory (shared or global memory instead)
+  return home;
+}
+
 scan_plan plan_scan(const raft::resources& res, const index<int64_t>& idx, int lut_kind, bool is_ip,
                     uint32_t k)
 {
@@ -476,21 +482,36 @@ scan_plan plan_scan(const raft::resources& res, const index<int64_t>& idx, int l
       ? round_up<size_t>(size_t(idx.pq_dim()) * idx.pq_len() * idx.pq_book_size() * 4, 16)
       : 0;
   const size_t limit = size_t(res.smem_optin) - 1024;
-  for (int with_pqc = (pqc_bytes > 0 ? 1 : 0); with_pqc >= 0; with_pqc--) {
-    for (int g = 4; g >= 1; g >>= 1) {
+  // Where the per-subspace codebook lives while the kernel runs: 2 = tensor memory (pq_len 1, 2 or
+  // 4 and at most 128 lanes x 512 columns of fp32), 1 = shared memory, 0 = global memory.
+  const uint32_t upj      = idx.pq_book_size() / 4;
+  const uint32_t n_m      = ceildiv<uint32_t>(idx.pq_dim(), 128 / upj);
+  const uint32_t need_col = n_m * idx.pq_len() * 4;
+  const bool tmem_ok      = pqc_bytes > 0 && scan_codebook_home() != 1 && need_col <= 512 &&
+                       (idx.pq_len() == 1 || idx.pq_len() == 2 || idx.pq_len() == 4);
+  for (int home = tmem_ok ? 2 : (pqc_bytes > 0 ? 1 : 0); home >= 0; home--) {
+    if (home == 1 && pqc_bytes == 0) { continue; }
+    for (int g = (home == 2 ? 8 : 4); g >= 1; g >>= 1) {
       const size_t merge_bytes = round_up<size_t>(size_t(1024 / g / 32) * k * 8, 16);
       const size_t group_bytes = lut_bytes + base_bytes + merge_bytes + 16;
-      const size_t total       = (with_pqc ? pqc_bytes : 0) + size_t(g) * group_bytes;
+      const size_t total       = (home == 1 ? pqc_bytes : 0) + size_t(g) * group_bytes + 16;
       if (total <= limit) {
         plan.n_groups      = g;
         plan.group_threads = 1024 / g;
-        plan.pqc_in_smem   = with_pqc;
-        plan.pqc_bytes     = with_pqc ? uint32_t(pqc_bytes) : 0;
+        plan.pqc_in_smem   = home == 1;
+        plan.pqc_bytes     = home == 1 ? uint32_t(pqc_bytes) : 0;
         plan.group_bytes   = uint32_t(group_bytes);
         plan.lut_bytes     = uint32_t(lut_bytes);
         plan.base_bytes    = uint32_t(base_bytes);
         plan.merge_bytes   = uint32_t(merge_bytes);
         plan.total_bytes   = total;
+        plan.tmem_slot_off = uint32_t(total - 16);
+        plan.tmem_cols     = 0;
+        if (home == 2) {
+          uint32_t cols = 32;
+          while (cols < need_col) { cols <<= 1; }
+          plan.tmem_cols = cols;
+        }
         return plan;
       }
     }
@@ -684,6 +705,8 @@ void search_any(raft::resources& res, const search_params& params, const index<i
       sp.n_groups       = plan.n_groups;
       sp.group_threads  = plan.group_threads;
       sp.pqc_in_smem    = plan.pqc_in_smem;
+      sp.tmem_cols      = plan.tmem_cols;
+      sp.tmem_slot_off  = plan.tmem_slot_off;
       sp.smem_pqc_bytes = plan.pqc_bytes;
       sp.smem_group_bytes = plan.group_bytes;
       sp.lut_bytes      = plan.lut_bytes;
@@ -738,6 +761,7 @@ void search_any(raft::resources& res, const search_params& params, const index<i
 }
 
 void set_coarse_mode(int mode) { coarse_mode_ref() = mode; }
+void set_scan_codebook_home(int home) { scan_codebook_home() = home; }
 
 void select_probes_any(raft::resources& res, const index<int64_t>& idx, const void* queries,
                        elem_t qtype, uint32_t n_queries, uint32_t n_probes, uint32_t* probes)

@@ -7,7 +7,7 @@ namespace cuvs::neighbors::ivf_pq {
 
 struct scan_plan {
   uint32_t n_groups, group_threads, pqc_in_smem, pqc_bytes, group_bytes, lut_bytes, base_bytes,
-    merge_bytes;
+    merge_bytes, tmem_cols, tmem_slot_off;
   size_t total_bytes;
 };
 scan_plan plan_scan(const raft::resources& res, const index<int64_t>& idx, int lut_kind, bool is_ip,
@@ -44,6 +44,9 @@ void coarse_only(raft::resources& res, const index<int64_t>& idx, const void* qu
                  uint32_t* status);
 
 void set_coarse_mode(int mode);  // process-wide override used by tests: 0 auto, 1 SIMT, 2 tensor core
+// process-wide override used by tests: 0 = the per-subspace codebook goes to tensor memory where it
+// fits, 1 = never (shared memory, else global memory)
+void set_scan_codebook_home(int home);
 
 // Nearest list of every row: labels[i] = argmin_l alpha * sum_k centers[l,k] * x[i,k], ties to the
 // lowest l (equals select_clusters with n_probes = 1).  `best` is scratch of n_rows * 8 bytes.

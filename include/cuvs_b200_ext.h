@@ -44,6 +44,10 @@ CUVS_EXPORT cuvsError_t cuvsB200CoarseSelect(cuvsResources_t res, void* index /*
 /* No counterpart in the reference: force the probe-selection path used by cuvsIvfPqSearch in this
  * process (0 = automatic, 1 = exact SIMT path, 2 = tensor-core path where it applies). */
 CUVS_EXPORT cuvsError_t cuvsB200SetCoarseMode(int mode);
+/* No counterpart in the reference: where the fine-search kernel of cuvsIvfPqSearch keeps a
+ * per-subspace PQ codebook in this process: 0 = tensor memory where it fits (the default),
+ * 1 = never tensor memory (shared memory, else global memory). */
+CUVS_EXPORT cuvsError_t cuvsB200SetScanCodebookHome(int home);
 
 #ifdef __cplusplus
 }

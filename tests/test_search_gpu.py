@@ -27,6 +27,17 @@ def ivf():
     return ivf_pq
 
 
+@pytest.fixture(autouse=True, params=["codebook-auto", "codebook-not-in-tmem"])
+def scan_codebook_home(request, ivf):
+    """Every test of this module runs twice: with the fine-search kernel keeping the per-subspace
+    codebook in tensor memory wherever it fits (the default) and with tensor memory ruled out
+    (codebook in shared or global memory)."""
+    from cuvs_b200 import _lib as L
+    L.check(L.load().cuvsB200SetScanCodebookHome(0 if request.param == "codebook-auto" else 1))
+    yield
+    L.check(L.load().cuvsB200SetScanCodebookHome(0))
+
+
 def assert_parity(d_gpu, i_gpu, d_orc, i_orc, rel_tol, max_tie_rows=0.01):
     d_gpu, i_gpu = np.asarray(d_gpu), np.asarray(i_gpu)
     assert d_gpu.shape == d_orc.shape and i_gpu.shape == i_orc.shape
