@@ -62,12 +62,33 @@ struct scan_params {
 enum { LUT_F32 = 0, LUT_F16 = 1, LUT_FP8 = 2 };
 
 // ---- packed fp32x2 arithmetic (sm_100) ---------------------------------------------------------
+// register-pair packing spelled as mov.b64 so that it costs no shift/or arithmetic
+__device__ __forceinline__ uint64_t pack_b32x2(uint32_t lo, uint32_t hi)
+{
+  uint64_t v;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(v) : "r"(lo), "r"(hi));
+  return v;
+}
 __device__ __forceinline__ uint64_t pack2(float x, float y)
 {
-  return (uint64_t(__float_as_uint(y)) << 32) | __float_as_uint(x);
+  return pack_b32x2(__float_as_uint(x), __float_as_uint(y));
 }
-__device__ __forceinline__ float lo2(uint64_t v) { return __uint_as_float(uint32_t(v)); }
-__device__ __forceinline__ float hi2(uint64_t v) { return __uint_as_float(uint32_t(v >> 32)); }
+__device__ __forceinline__ float lo2(uint64_t v)
+{
+  float lo, hi;
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+  return lo;
+}
+__device__ __forceinline__ float hi2(uint64_t v)
+{
+  float lo, hi;
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+  return hi;
+}
+__device__ __forceinline__ void sts_2xb32(uint32_t a, uint32_t x, uint32_t y)
+{
+  asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(a), "r"(x), "r"(y) : "memory");
+}
 __device__ __forceinline__ uint64_t sub2(uint64_t a, uint64_t b)
 {
   uint64_t d;
@@ -257,8 +278,7 @@ __device__ __forceinline__ void build_lut_smem(uint32_t pqc_a, uint32_t base_a, 
     } else if constexpr (LutKind == LUT_F16) {
       const __half2 h0 = __floats2half2_rn(lo2(s0), hi2(s0));
       const __half2 h1 = __floats2half2_rn(lo2(s1), hi2(s1));
-      sts_b64(out, (uint64_t(*reinterpret_cast<const uint32_t*>(&h1)) << 32) |
-                     *reinterpret_cast<const uint32_t*>(&h0));
+      sts_2xb32(out, *reinterpret_cast<const uint32_t*>(&h0), *reinterpret_cast<const uint32_t*>(&h1));
     } else {
       sts_b32(out, uint32_t(fp8_encode<IsIP>(lo2(s0))) | (uint32_t(fp8_encode<IsIP>(hi2(s0))) << 8) |
                      (uint32_t(fp8_encode<IsIP>(lo2(s1))) << 16) | (uint32_t(fp8_encode<IsIP>(hi2(s1))) << 24));
@@ -309,37 +329,45 @@ __device__ __forceinline__ void tmem_ld(uint32_t taddr, uint32_t (&r)[N])
 }
 
 // Codebook layout in TMEM (written once per CTA by threads 0..127, read by every thread from the
-// lane tid % 128): lane L holds, for the four-entry unit u = L % kUPJ, the subspaces
-// j = L / kUPJ + m * (128 / kUPJ), m = 0, 1, ...; columns (m * LEN + kk) * 4 .. + 3 hold entries
-// 4u .. 4u+3 of component kk.  A group of a multiple of 128 threads therefore finds the units of its
-// usual assignment (unit gt % kUPJ, subspaces gt / kUPJ + i * gthreads / kUPJ) in its own lanes at
-// m = gt / 128 + i * gthreads / 128.
+// lane tid % 128).  Lane L serves the four-entry unit u = L % kUPJ of the subspaces
+// j = L / kUPJ + m * (128 / kUPJ), m = 0, 1, ...  A group of `gthreads` threads (a multiple of 128)
+// gives thread gt the unit gt % kUPJ of subspaces gt / kUPJ + i * gthreads / kUPJ, i.e.
+// m = gt / 128 + i * m_stride with m_stride = gthreads / 128; the blocks of one thread's successive
+// iterations are stored side by side: block(m) = (m % m_stride) * ipt + m / m_stride, ipt =
+// iterations per thread.  A block is 4 * LEN columns: entries 4u .. 4u+3 of component 0, then of
+// component 1, ...
+__device__ __forceinline__ uint32_t tmem_iters_per_thread(uint32_t pq_dim, uint32_t j_per_m, uint32_t m_stride)
+{
+  const uint32_t n_m = (pq_dim + j_per_m - 1) / j_per_m;
+  return (n_m + m_stride - 1) / m_stride;
+}
 template <int PqBits, int LEN>
 __device__ __forceinline__ void fill_codebook_tmem(uint32_t tmem_lane_a, const float* pq_centers,
-                                                   uint32_t pq_dim, uint32_t lane128)
+                                                   uint32_t pq_dim, uint32_t lane128, uint32_t m_stride)
 {
   constexpr uint32_t kBook  = 1u << PqBits;
   constexpr uint32_t kUPJ   = kBook / 4;
   constexpr uint32_t kJPerM = 128u / kUPJ;
   const uint32_t u          = lane128 % kUPJ;
-  const uint32_t n_m        = (pq_dim + kJPerM - 1) / kJPerM;
-  for (uint32_t m = 0; m < n_m; m++) {
-    const uint32_t j = lane128 / kUPJ + m * kJPerM;
+  const uint32_t ipt        = tmem_iters_per_thread(pq_dim, kJPerM, m_stride);
+  for (uint32_t m = 0; m < ipt * m_stride; m++) {
+    const uint32_t j     = lane128 / kUPJ + m * kJPerM;
+    const uint32_t block = (m % m_stride) * ipt + m / m_stride;
 #pragma unroll
     for (int kk = 0; kk < LEN; kk++) {
       float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
       if (j < pq_dim) {
         v = __ldg(reinterpret_cast<const float4*>(pq_centers + (size_t(j) * LEN + kk) * kBook + 4u * u));
       }
-      tmem_st4(tmem_lane_a + (m * LEN + uint32_t(kk)) * 4u, v.x, v.y, v.z, v.w);
+      tmem_st4(tmem_lane_a + (block * LEN + uint32_t(kk)) * 4u, v.x, v.y, v.z, v.w);
     }
   }
   tmem_wait_st();
 }
 
 // LUT of one pair from the codebook in TMEM: same thread-to-entry assignment and arithmetic as
-// build_lut_smem, the codebook operand arrives through tcgen05.ld (one load of 4 * LEN columns per
-// subspace, requested one subspace ahead) and no longer occupies the shared-memory pipe.
+// build_lut_smem; the codebook operand arrives through tcgen05.ld, 16 columns (4 / LEN subspaces)
+// per load, and no longer occupies the shared-memory pipe.
 template <int PqBits, int LutKind, bool IsIP, int LEN>
 __device__ __forceinline__ void build_lut_tmem(uint32_t tmem_lane_a, uint32_t base_a, uint32_t lut_a,
                                                uint32_t pq_dim, uint32_t gt, uint32_t gthreads)
@@ -349,91 +377,73 @@ __device__ __forceinline__ void build_lut_tmem(uint32_t tmem_lane_a, uint32_t ba
   constexpr uint32_t kJPerM = 128u / kUPJ;
   constexpr uint32_t kElem  = LutKind == LUT_F32 ? 4u : (LutKind == LUT_F16 ? 2u : 1u);
   constexpr uint32_t kBaseB = IsIP ? 16u : 8u;
-  constexpr int kCols       = 4 * LEN;
+  constexpr int kCols       = 4 * LEN;     // columns of one subspace
+  constexpr int kPerLoad    = 16 / kCols;  // subspaces per 16-column load
+  // every lane of a warp works on the same subspace when a subspace has at least 32 units
+  constexpr bool kWarpSameJ = kUPJ >= 32;
   const uint32_t u          = gt % kUPJ;
   const uint32_t j_first    = gt / kUPJ;
   const uint32_t j_stride   = gthreads / kUPJ;
-  const uint32_t n_m        = (pq_dim + kJPerM - 1) / kJPerM;
-  const uint32_t m_stride   = gthreads / 128u;
-  // warp-uniform trip count (the tensor-memory loads need the whole warp): subspaces of the warp's
-  // first lane; a lane whose subspace falls beyond pq_dim computes nothing
+  const uint32_t ipt        = tmem_iters_per_thread(pq_dim, kJPerM, gthreads / 128u);
+  // warp-uniform trip count (the tensor-memory loads need the whole warp): a lane whose subspace
+  // falls beyond pq_dim computes nothing
   const uint32_t j_warp     = (gt & ~31u) / kUPJ;
   const uint32_t n_iter     = j_warp < pq_dim ? (pq_dim - j_warp + j_stride - 1) / j_stride : 0u;
-  uint32_t m                = gt / 128u;
   uint32_t j                = j_first;
   uint32_t bd               = base_a + j_first * LEN * kBaseB;
   uint32_t out              = lut_a + (j_first * kBook + 4u * u) * kElem;
+  uint32_t taddr            = tmem_lane_a + (gt / 128u) * ipt * uint32_t(kCols);
   const uint32_t bd_step    = j_stride * LEN * kBaseB;
   const uint32_t out_step   = j_stride * kBook * kElem;
 
-  auto col_of = [&](uint32_t mm) { return tmem_lane_a + min(mm, n_m - 1u) * uint32_t(kCols); };
-  auto compute = [&](const uint32_t (&c)[kCols]) {
-    if (j < pq_dim) {
-      uint64_t s0 = 0ull, s1 = 0ull;  // entries (b, b+1) and (b+2, b+3), each (+0.0f, +0.0f)
-      uint64_t x[LEN], y[LEN];
-      if constexpr (IsIP) {
+  for (uint32_t i = 0; i < n_iter; i += kPerLoad, taddr += 16u) {
+    uint32_t c[16];
+    tmem_ld<16>(taddr, c);  // may run past this thread's blocks into other columns of the allocation
+    tmem_wait_ld();
 #pragma unroll
-        for (int kk = 0; kk < LEN; kk++) { lds_2xb64(bd + uint32_t(kk) * 16u, x[kk], y[kk]); }
-      } else if constexpr (LEN == 1) {
-        x[0] = lds_b64(bd);
-      } else {
+    for (int t = 0; t < kPerLoad; t++) {
+      if (i + uint32_t(t) < n_iter && (kWarpSameJ || j < pq_dim)) {
+        uint64_t s0 = 0ull, s1 = 0ull;  // entries (b, b+1) and (b+2, b+3), each (+0.0f, +0.0f)
+        uint64_t x[LEN], y[LEN];
+        if constexpr (IsIP) {
 #pragma unroll
-        for (int kk = 0; kk < LEN; kk += 2) { lds_2xb64(bd + uint32_t(kk) * 8u, x[kk], x[kk + 1]); }
-      }
+          for (int kk = 0; kk < LEN; kk++) { lds_2xb64(bd + uint32_t(kk) * 16u, x[kk], y[kk]); }
+        } else if constexpr (LEN == 1) {
+          x[0] = lds_b64(bd);
+        } else {
 #pragma unroll
-      for (int kk = 0; kk < LEN; kk++) {
-        const uint64_t c0 = (uint64_t(c[kk * 4 + 1]) << 32) | c[kk * 4 + 0];
-        const uint64_t c1 = (uint64_t(c[kk * 4 + 3]) << 32) | c[kk * 4 + 2];
-        if constexpr (!IsIP) {  // x = (d, d)
-          const uint64_t e0 = sub2(x[kk], c0);
-          const uint64_t e1 = sub2(x[kk], c1);
-          s0                = fma2(e0, e0, s0);
-          s1                = fma2(e1, e1, s1);
-        } else {  // x = (-q, -q), y = (q*c, q*c)
-          s0 = sub2(s0, y[kk]);
-          s1 = sub2(s1, y[kk]);
-          s0 = fma2(x[kk], c0, s0);
-          s1 = fma2(x[kk], c1, s1);
+          for (int kk = 0; kk < LEN; kk += 2) { lds_2xb64(bd + uint32_t(kk) * 8u, x[kk], x[kk + 1]); }
+        }
+#pragma unroll
+        for (int kk = 0; kk < LEN; kk++) {
+          const uint64_t c0 = pack_b32x2(c[t * kCols + kk * 4 + 0], c[t * kCols + kk * 4 + 1]);
+          const uint64_t c1 = pack_b32x2(c[t * kCols + kk * 4 + 2], c[t * kCols + kk * 4 + 3]);
+          if constexpr (!IsIP) {  // x = (d, d)
+            const uint64_t e0 = sub2(x[kk], c0);
+            const uint64_t e1 = sub2(x[kk], c1);
+            s0                = fma2(e0, e0, s0);
+            s1                = fma2(e1, e1, s1);
+          } else {  // x = (-q, -q), y = (q*c, q*c)
+            s0 = sub2(s0, y[kk]);
+            s1 = sub2(s1, y[kk]);
+            s0 = fma2(x[kk], c0, s0);
+            s1 = fma2(x[kk], c1, s1);
+          }
+        }
+        if constexpr (LutKind == LUT_F32) {
+          sts_b128(out, s0, s1);
+        } else if constexpr (LutKind == LUT_F16) {
+          const __half2 h0 = __floats2half2_rn(lo2(s0), hi2(s0));
+          const __half2 h1 = __floats2half2_rn(lo2(s1), hi2(s1));
+          sts_2xb32(out, *reinterpret_cast<const uint32_t*>(&h0), *reinterpret_cast<const uint32_t*>(&h1));
+        } else {
+          sts_b32(out, uint32_t(fp8_encode<IsIP>(lo2(s0))) | (uint32_t(fp8_encode<IsIP>(hi2(s0))) << 8) |
+                         (uint32_t(fp8_encode<IsIP>(lo2(s1))) << 16) | (uint32_t(fp8_encode<IsIP>(hi2(s1))) << 24));
         }
       }
-      if constexpr (LutKind == LUT_F32) {
-        sts_b128(out, s0, s1);
-      } else if constexpr (LutKind == LUT_F16) {
-        const __half2 h0 = __floats2half2_rn(lo2(s0), hi2(s0));
-        const __half2 h1 = __floats2half2_rn(lo2(s1), hi2(s1));
-        sts_b64(out, (uint64_t(*reinterpret_cast<const uint32_t*>(&h1)) << 32) |
-                       *reinterpret_cast<const uint32_t*>(&h0));
-      } else {
-        sts_b32(out, uint32_t(fp8_encode<IsIP>(lo2(s0))) | (uint32_t(fp8_encode<IsIP>(hi2(s0))) << 8) |
-                       (uint32_t(fp8_encode<IsIP>(lo2(s1))) << 16) | (uint32_t(fp8_encode<IsIP>(hi2(s1))) << 24));
-      }
-    }
-    j += j_stride;
-    bd += bd_step;
-    out += out_step;
-  };
-
-  if constexpr (LEN <= 2) {
-    // two register buffers: the next subspace's load is in flight while this one is computed
-    uint32_t ca[kCols], cb[kCols];
-    if (n_iter > 0) { tmem_ld<kCols>(col_of(m), ca); }
-    for (uint32_t i = 0; i < n_iter; i += 2) {
-      tmem_wait_ld();
-      if (i + 1 < n_iter) { tmem_ld<kCols>(col_of(m + m_stride), cb); }
-      compute(ca);
-      if (i + 1 < n_iter) {
-        tmem_wait_ld();
-        if (i + 2 < n_iter) { tmem_ld<kCols>(col_of(m + 2u * m_stride), ca); }
-        compute(cb);
-      }
-      m += 2u * m_stride;
-    }
-  } else {
-    uint32_t ca[kCols];
-    for (uint32_t i = 0; i < n_iter; i++, m += m_stride) {
-      tmem_ld<kCols>(col_of(m), ca);
-      tmem_wait_ld();
-      compute(ca);
+      j += j_stride;
+      bd += bd_step;
+      out += out_step;
     }
   }
 }
@@ -589,9 +599,9 @@ __global__ void __launch_bounds__(1024, 1) scan_kernel(const scan_params p)
     if (tid < 128) {
       const uint32_t lane_a = tmem_base + ((uint32_t(tid) & ~31u) << 16);
       switch (p.pq_len) {
-        case 1: fill_codebook_tmem<PqBits, 1>(lane_a, p.pq_centers, p.pq_dim, uint32_t(tid)); break;
-        case 2: fill_codebook_tmem<PqBits, 2>(lane_a, p.pq_centers, p.pq_dim, uint32_t(tid)); break;
-        default: fill_codebook_tmem<PqBits, 4>(lane_a, p.pq_centers, p.pq_dim, uint32_t(tid)); break;
+        case 1: fill_codebook_tmem<PqBits, 1>(lane_a, p.pq_centers, p.pq_dim, uint32_t(tid), p.group_threads / 128u); break;
+        case 2: fill_codebook_tmem<PqBits, 2>(lane_a, p.pq_centers, p.pq_dim, uint32_t(tid), p.group_threads / 128u); break;
+        default: fill_codebook_tmem<PqBits, 4>(lane_a, p.pq_centers, p.pq_dim, uint32_t(tid), p.group_threads / 128u); break;
       }
     }
     tmem_fence_before();

@@ -508,8 +508,14 @@ scan_plan plan_scan(const raft::resources& res, const index<int64_t>& idx, int l
         plan.tmem_slot_off = uint32_t(total - 16);
         plan.tmem_cols     = 0;
         if (home == 2) {
+          // blocks of one thread's successive subspaces side by side, plus slack for the last
+          // 16-column load of a thread, rounded to a power of two
+          const uint32_t m_stride = plan.group_threads / 128;
+          const uint32_t ipt      = ceildiv<uint32_t>(n_m, m_stride);
+          const uint32_t need     = m_stride * ipt * idx.pq_len() * 4 + 16;
+          if (need > 512) { continue; }
           uint32_t cols = 32;
-          while (cols < need_col) { cols <<= 1; }
+          while (cols < need) { cols <<= 1; }
           plan.tmem_cols = cols;
         }
         return plan;
