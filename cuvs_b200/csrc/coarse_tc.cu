@@ -411,7 +411,8 @@ coarse_finish_kernel(const uint32_t* __restrict__ cand_key, const uint32_t* __re
                      const float* __restrict__ centers, const float* __restrict__ fq,
                      uint32_t n_lists, uint32_t dim_ext, float alpha, uint32_t n_probes, uint32_t C,
                      uint32_t cap /* pow2 >= C */, float cmax, uint32_t* __restrict__ probes,
-                     float* __restrict__ scores_out, uint8_t* __restrict__ flags)
+                     float* __restrict__ scores_out, uint32_t* __restrict__ redo_list,
+                     uint32_t* __restrict__ redo_count)
 {
   extern __shared__ uint64_t s_keys[];                 // [cap] keys; the query; the candidates
   float* s_q      = reinterpret_cast<float*>(s_keys + cap);
@@ -552,7 +553,179 @@ coarse_finish_kernel(const uint32_t* __restrict__ cand_key, const uint32_t* __re
       // all lists rescored (n_sel == every valid candidate == every list) needs no proof
       ok = (last_dot - unseen > eps) || (n_sel >= n_lists);
     }
-    flags[q] = ok ? 0 : 1;
+    if (!ok) { redo_list[atomicAdd(redo_count, 1u)] = q; }
+  }
+}
+
+// Faster finish for the common case (at most 512 half tiles, C <= 128): instead of a radix select
+// over every candidate key, the selection threshold is the C-th largest of the per-half-tile maxima
+// (at least C keys are then at or above it, and everything above it is rescored, usually little more
+// than C lists), the rows to rescore are first copied to shared memory with coalesced loads, and the
+// defining FMA chains then run out of shared memory.  Same result contract as coarse_finish_kernel:
+// probes by (exact score, list id), the guard proves them exact or the query is queued for the
+// exact redo.
+constexpr uint32_t kFinMaxHalfTiles = 512;
+constexpr uint32_t kFinMaxSel       = 256;
+
+__global__ void __launch_bounds__(256)
+coarse_finish_small_kernel(const uint32_t* __restrict__ cand_key, const uint32_t* __restrict__ cand_bound,
+                           uint32_t n_cand /* per query */, uint32_t kph /* keys per half tile */,
+                           const float* __restrict__ centers, const float* __restrict__ fq,
+                           uint32_t n_lists, uint32_t dim_ext, float alpha, uint32_t n_probes, uint32_t C,
+                           uint32_t cap /* pow2 >= C, <= kFinMaxSel */, float cmax,
+                           uint32_t* __restrict__ probes, float* __restrict__ scores_out,
+                           uint32_t* __restrict__ redo_list, uint32_t* __restrict__ redo_count)
+{
+  // dynamic: [cap] u64 keys | query [dim_ext] | staged candidate keys [n_cand], later reused for the
+  // rows to rescore ([rows_fit][dim_ext + 1])
+  extern __shared__ uint64_t s_keys[];
+  float* s_q    = reinterpret_cast<float*>(s_keys + cap);
+  uint32_t* key = reinterpret_cast<uint32_t*>(s_q + dim_ext);
+  __shared__ uint32_t s_max[kFinMaxHalfTiles];
+  __shared__ uint32_t s_count;
+  __shared__ float s_red[8];
+  __shared__ uint32_t s_tb[8];
+  const uint32_t q       = blockIdx.x;
+  const uint32_t tid     = threadIdx.x;
+  const uint32_t n_half  = n_cand / kph;
+  {
+    const uint4* src = reinterpret_cast<const uint4*>(cand_key + size_t(q) * n_cand);
+    uint4* dst       = reinterpret_cast<uint4*>(key);
+    for (uint32_t i = tid; i < n_cand / 4; i += 256) { dst[i] = __ldg(src + i); }
+  }
+  float qq = 0.0f;
+  for (uint32_t i = tid; i < dim_ext; i += 256) {
+    const float v = fq[size_t(q) * dim_ext + i];
+    s_q[i]        = v;
+    qq += v * v;
+  }
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) { qq += __shfl_xor_sync(kFullMask, qq, d); }
+  if ((tid & 31) == 0) { s_red[tid >> 5] = qq; }
+  if (tid == 0) { s_count = 0; }
+  for (uint32_t i = tid; i < cap; i += 256) { s_keys[i] = kEmptyKey; }
+  // bound on what the half tiles dropped
+  uint32_t tb = 0;
+  {
+    const uint32_t* bnd = cand_bound + size_t(q) * n_half;
+    for (uint32_t i = tid; i < n_half; i += 256) { tb = max(tb, __ldg(bnd + i)); }
+  }
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) { tb = max(tb, __shfl_xor_sync(kFullMask, tb, d)); }
+  if ((tid & 31) == 0) { s_tb[tid >> 5] = tb; }
+  __syncthreads();
+
+  // ---- largest key of every half tile (invalid keys count as 0), sorted descending ----
+  for (uint32_t h = tid; h < kFinMaxHalfTiles; h += 256) {
+    uint32_t m = 0;
+    if (h < n_half) {
+      const uint4* kk = reinterpret_cast<const uint4*>(key + h * kph);
+      for (uint32_t i = 0; i < kph / 4; i++) {
+        const uint4 v = kk[i];
+        m             = max(max(m, v.x), max(v.y, max(v.z, v.w)));
+      }
+      if (!key_valid(m)) { m = 0; }
+    }
+    s_max[h] = m;
+  }
+  __syncthreads();
+  for (uint32_t size = 2; size <= kFinMaxHalfTiles; size <<= 1) {
+    for (uint32_t stride = size >> 1; stride > 0; stride >>= 1) {
+      const uint32_t i  = tid;  // 256 compare-exchanges cover 512 elements
+      const uint32_t lo = 2 * i - (i & (stride - 1));
+      const uint32_t hi = lo + stride;
+      const bool down   = (lo & size) == 0;
+      const uint32_t a = s_max[lo], b = s_max[hi];
+      if ((a < b) == down) {
+        s_max[lo] = b;
+        s_max[hi] = a;
+      }
+      __syncthreads();
+    }
+  }
+  // Threshold: the C-th largest half-tile maximum (0 = fewer than C valid half tiles: take every valid
+  // key).  At least C keys are >= t0, every key >= t0 is rescored.
+  const uint32_t t0 = s_max[C - 1];
+  for (uint32_t i = tid; i < n_cand; i += 256) {
+    const uint32_t kk = key[i];
+    if (key_valid(kk) && kk >= t0) {
+      const uint32_t slot = atomicAdd(&s_count, 1u);
+      // list id = tile * 256 + half * 128 + column; i / kph enumerates (tile, half)
+      if (slot < cap) { s_keys[slot] = (i / kph) * kHalf + (127u - (kk & 127u)); }
+    }
+  }
+  __syncthreads();  // the staged keys are dead from here on
+  uint32_t tile_key = s_tb[0];
+#pragma unroll
+  for (int w = 1; w < 8; w++) { tile_key = max(tile_key, s_tb[w]); }
+  const float tilebound = key_valid(tile_key) ? key_value(tile_key) : -INFINITY;
+  const uint32_t n_sel  = min(s_count, cap);
+  const bool overflow   = s_count > cap;
+
+  // ---- exact rescoring: rows copied to shared memory (padded against bank conflicts), then the
+  //      defining FMA chain, ascending k, one thread per list ----
+  float* s_rows            = reinterpret_cast<float*>(key);
+  const uint32_t row_words = dim_ext + 1;
+  const uint32_t rows_fit  = max(1u, (n_cand * 4u) / (row_words * 4u));
+  for (uint32_t r0 = 0; r0 < n_sel; r0 += rows_fit) {
+    const uint32_t n_rows = min(rows_fit, n_sel - r0);
+    const uint32_t per4   = dim_ext / 4;  // dim_ext is a multiple of 4
+    for (uint32_t e = tid; e < n_rows * per4; e += 256) {
+      const uint32_t r = e / per4, c4 = e - r * per4;
+      const uint32_t l = uint32_t(s_keys[r0 + r]);
+      const float4 v   = __ldg(reinterpret_cast<const float4*>(centers + size_t(l) * dim_ext) + c4);
+      float* dst       = s_rows + r * row_words + 4 * c4;
+      dst[0] = v.x;
+      dst[1] = v.y;
+      dst[2] = v.z;
+      dst[3] = v.w;
+    }
+    __syncthreads();
+    if (tid < n_rows) {
+      const uint32_t l = uint32_t(s_keys[r0 + tid]);
+      const float* c   = s_rows + tid * row_words;
+      float acc        = 0.0f;
+      for (uint32_t k = 0; k < dim_ext; k++) { acc = __fmaf_rn(c[k], s_q[k], acc); }
+      s_keys[r0 + tid] = (uint64_t(float_to_ordered(__fmul_rn(alpha, acc))) << 32) | l;
+    }
+    __syncthreads();
+  }
+  for (uint32_t size = 2; size <= cap; size <<= 1) {
+    for (uint32_t stride = size >> 1; stride > 0; stride >>= 1) {
+      for (uint32_t i = tid; i < cap / 2; i += 256) {
+        const uint32_t lo = 2 * i - (i & (stride - 1));
+        const uint32_t hi = lo + stride;
+        const bool up     = (lo & size) == 0;
+        const uint64_t a = s_keys[lo], b = s_keys[hi];
+        if ((a > b) == up) {
+          s_keys[lo] = b;
+          s_keys[hi] = a;
+        }
+      }
+      __syncthreads();
+    }
+  }
+  for (uint32_t pi = tid; pi < n_probes; pi += 256) {
+    const uint64_t kk                 = s_keys[pi];
+    probes[size_t(q) * n_probes + pi] = uint32_t(kk);
+    if (scores_out) { scores_out[size_t(q) * n_probes + pi] = ordered_to_float(uint32_t(kk >> 32)); }
+  }
+  if (tid == 0) {
+    // guard, in dot-product units (score = alpha * dot, alpha < 0)
+    float qnorm = 0.0f;
+    for (int w = 0; w < 8; w++) { qnorm += s_red[w]; }
+    qnorm = sqrtf(qnorm);
+    const float eps = (float(dim_ext + 8) * 2.4e-7f + 3.1e-5f) * qnorm * cmax;
+    // every list that was not rescored has a key below t0 or was dropped by its half tile
+    const float t_c    = key_valid(t0) ? key_value(t0) : -INFINITY;
+    const float unseen = fmaxf(t_c, tilebound);
+    bool ok            = !overflow && n_sel >= n_probes;
+    if (ok) {
+      const float last_dot = ordered_to_float(uint32_t(s_keys[n_probes - 1] >> 32)) / alpha;
+      // all lists rescored (n_sel == every valid candidate == every list) needs no proof
+      ok = (last_dot - unseen > eps) || (n_sel >= n_lists);
+    }
+    if (!ok) { redo_list[atomicAdd(redo_count, 1u)] = q; }
   }
 }
 
@@ -560,7 +733,8 @@ coarse_finish_kernel(const uint32_t* __restrict__ cand_key, const uint32_t* __re
 // exact redo of flagged queries
 // ------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256)
-coarse_fallback_kernel(const uint8_t* __restrict__ flags, const float* __restrict__ centers,
+coarse_fallback_kernel(const uint32_t* __restrict__ redo_list, const uint32_t* __restrict__ redo_count,
+                       const float* __restrict__ centers,
                        const float* __restrict__ fq, uint32_t n_queries, uint32_t n_lists,
                        uint32_t dim_ext, float alpha, uint32_t n_probes, uint32_t cap,
                        float* __restrict__ scratch /* [gridDim.x, n_lists] */,
@@ -573,9 +747,10 @@ coarse_fallback_kernel(const uint8_t* __restrict__ flags, const float* __restric
   __shared__ uint32_t s_prefix, s_remaining, s_count, s_eq_taken;
   const uint32_t tid = threadIdx.x;
   float* row         = scratch + size_t(blockIdx.x) * n_lists;
-  for (uint32_t q = blockIdx.x; q < n_queries; q += gridDim.x) {
-    if (!flags[q]) { continue; }  // uniform per block
-    if (tid == 0) { atomicAdd(n_fallback, 1u); }
+  const uint32_t n_redo = min(*redo_count, n_queries);
+  if (blockIdx.x == 0 && tid == 0) { *n_fallback = n_redo; }
+  for (uint32_t ri = blockIdx.x; ri < n_redo; ri += gridDim.x) {
+    const uint32_t q = redo_list[ri];
     for (uint32_t i = tid; i < dim_ext; i += 256) { s_q[i] = fq[size_t(q) * dim_ext + i]; }
     __syncthreads();
     for (uint32_t l = tid; l < n_lists; l += 256) {
@@ -730,8 +905,8 @@ size_t coarse_tc_workspace_bytes(uint32_t n_queries, uint32_t n_lists, uint32_t 
   lay.add(size_t(n_queries) * dim_ext * 4);  // fq lo
   lay.add(size_t(n_queries) * n_tiles * 2 * kMaxKph * 4);  // candidate keys
   lay.add(size_t(n_queries) * n_tiles * 2 * 4);          // per half tile bound
-  lay.add(n_queries);                        // flags
-  lay.add(256);                              // error word + fallback counter
+  lay.add(size_t(n_queries) * 4);            // queries to redo exactly
+  lay.add(256);                              // error word, fallback counter, redo counter
   lay.add(size_t(64) * n_lists * 4);         // fallback scratch rows
   return lay.total();
 }
@@ -765,14 +940,14 @@ void select_clusters_tc(raft::resources& res, const float* centers, const float*
   float* fq_lo    = reinterpret_cast<float*>(ws + lay.add(size_t(n_queries) * dim_ext * 4));
   auto* cand_key  = reinterpret_cast<uint32_t*>(ws + lay.add(size_t(n_queries) * n_tiles * 2 * kMaxKph * 4));
   auto* cand_bnd  = reinterpret_cast<uint32_t*>(ws + lay.add(size_t(n_queries) * n_tiles * 2 * 4));
-  auto* flags     = reinterpret_cast<uint8_t*>(ws + lay.add(n_queries));
+  auto* redo_list = reinterpret_cast<uint32_t*>(ws + lay.add(size_t(n_queries) * 4));
   auto* words     = reinterpret_cast<uint32_t*>(ws + lay.add(256));
   float* scratch  = reinterpret_cast<float*>(ws + lay.add(size_t(64) * n_lists * 4));
   cudaStream_t stream = res.stream;
 
   split_tf32_kernel<<<unsigned(ceildiv<size_t>(size_t(n_queries) * dim_ext, 256)), 256, 0, stream>>>(
     fq, size_t(n_queries) * dim_ext, fq_hi, fq_lo);
-  CUDA_TRY(cudaMemsetAsync(words, 0, 8, stream));
+  CUDA_TRY(cudaMemsetAsync(words, 0, 12, stream));
 
   const CUtensorMap m_a_hi = make_map(fq_hi, n_queries, dim_ext, kBM);
   const CUtensorMap m_a_lo = make_map(fq_lo, n_queries, dim_ext, kBM);
@@ -813,20 +988,32 @@ void select_clusters_tc(raft::resources& res, const float* centers, const float*
   uint32_t cap     = 2;
   while (cap < 2 * C) { cap <<= 1; }  // room for ties at the selection threshold
   const size_t fin_smem = size_t(cap) * 8 + size_t(dim_ext) * 4 + size_t(n_cand) * 4;
-  static size_t fin_configured = 48 * 1024;
-  if (fin_smem > fin_configured) {
-    CUDA_TRY(cudaFuncSetAttribute(coarse_finish_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                  int(fin_smem)));
-    fin_configured = fin_smem;
+  static size_t fin_configured = 48 * 1024, fin_small_configured = 48 * 1024;
+  // the half-tile-maxima threshold is tight only when C is small against the number of half tiles
+  if (n_tiles * 2 <= kFinMaxHalfTiles && cap <= kFinMaxSel && C * 4 <= n_tiles * 2) {
+    if (fin_smem > fin_small_configured) {
+      CUDA_TRY(cudaFuncSetAttribute(coarse_finish_small_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    int(fin_smem)));
+      fin_small_configured = fin_smem;
+    }
+    coarse_finish_small_kernel<<<n_queries, 256, fin_smem, stream>>>(
+      cand_key, cand_bnd, n_cand, kph, centers, fq, n_lists, dim_ext, alpha, n_probes, C, cap, cmax, probes,
+      scores_out, redo_list, words + 2);
+  } else {
+    if (fin_smem > fin_configured) {
+      CUDA_TRY(cudaFuncSetAttribute(coarse_finish_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    int(fin_smem)));
+      fin_configured = fin_smem;
+    }
+    coarse_finish_kernel<<<n_queries, 256, fin_smem, stream>>>(cand_key, cand_bnd, n_cand, kph, centers, fq,
+                                                               n_lists, dim_ext, alpha, n_probes, C, cap,
+                                                               cmax, probes, scores_out, redo_list, words + 2);
   }
-  coarse_finish_kernel<<<n_queries, 256, fin_smem, stream>>>(cand_key, cand_bnd, n_cand, kph, centers, fq, n_lists,
-                                                             dim_ext, alpha, n_probes, C, cap, cmax,
-                                                             probes, scores_out, flags);
   uint32_t cap_fb = 2;
   while (cap_fb < n_probes) { cap_fb <<= 1; }
   const size_t fb_smem = size_t(cap_fb) * 8 + size_t(dim_ext) * 4;
-  coarse_fallback_kernel<<<64, 256, fb_smem, stream>>>(flags, centers, fq, n_queries, n_lists, dim_ext,
-                                                       alpha, n_probes, cap_fb, scratch, probes,
+  coarse_fallback_kernel<<<64, 256, fb_smem, stream>>>(redo_list, words + 2, centers, fq, n_queries, n_lists,
+                                                       dim_ext, alpha, n_probes, cap_fb, scratch, probes,
                                                        scores_out, words + 1);
   CUDA_TRY(cudaGetLastError());
   res.launches += 4;
@@ -843,7 +1030,7 @@ void coarse_tc_status(raft::resources& res, const void* workspace, uint32_t n_qu
   lay.add(size_t(n_queries) * dim_ext * 4);
   lay.add(size_t(n_queries) * n_tiles * 2 * kMaxKph * 4);
   lay.add(size_t(n_queries) * n_tiles * 2 * 4);
-  lay.add(n_queries);
+  lay.add(size_t(n_queries) * 4);
   const size_t o = lay.add(256);
   uint32_t h[2]  = {0, 0};
   CUDA_TRY(cudaMemcpyAsync(h, static_cast<const char*>(workspace) + o, 8, cudaMemcpyDeviceToHost, res.stream));
