@@ -439,6 +439,38 @@ def run_ours(args):
                                                         distances=out_d, resources=res, sync=False),
                                          args.steps, 1), 4)
 
+    # ---- the configuration's small batches (1 and 100 queries): latency per call, synchronised ----
+    small = []
+    if not args.no_e2e:
+        for b in (1, 100):
+            if b >= nq:
+                continue
+            qb = queries[:b].contiguous()
+            cb_i = torch.empty((b, k0), dtype=torch.int64, device=device)
+            cb_d = torch.empty((b, k0), dtype=torch.float32, device=device)
+            ob_i = torch.empty((b, k), dtype=torch.int64, device=device)
+            ob_d = torch.empty((b, k), dtype=torch.float32, device=device)
+
+            def small_step():
+                if world > 1:
+                    d, i = mg.search(sp, index, qb, k0, True, None, res, sync=False)
+                else:
+                    d, i = ivf_pq.search(sp, index, qb, k0, cb_i, cb_d, res, sync=False)
+                if refining:
+                    refine(dataset, qb, i, k=k, metric="sqeuclidean", indices=ob_i, distances=ob_d,
+                           resources=res, sync=False)
+                torch.cuda.synchronize()      # latency mode: the caller waits for every batch
+
+            for _ in range(5):
+                small_step()
+            t0 = time.perf_counter()
+            n_rep = 50
+            for _ in range(n_rep):
+                small_step()
+            dt = (time.perf_counter() - t0) / n_rep
+            small.append({"batch": b, "latency_ms": round(dt * 1e3, 4), "qps": round(b / dt, 1)})
+            log(f"[bench] batch {b}: {dt * 1e3:.3f} ms per call, {b / dt:,.0f} q/s")
+
     # ---- end to end: pinned host buffers, copies inside the timed region ----
     q_host = queries.cpu().pin_memory()
     q_dev = torch.empty_like(queries)
@@ -479,7 +511,7 @@ def run_ours(args):
                    "k": k, "recall_k": k, "batch": nq, "n_probes": p_star, "lut_dtype": wl["lut"],
                    "internal_distance_dtype": wl["internal"], "refine_ratio": wl["refine_ratio"],
                    "recall_at_10": chosen["recall_at_10"],
-                   "recall_target_met": target_met, "sweep": sweep,
+                   "recall_target_met": target_met, "sweep": sweep, "small_batches": small,
                    "parallelism": f"list-sharded x{world}" if world > 1 else "single GPU",
                    "l2": f"inputs larger than L2: {wl['n_rows'] * n_pieces * 16 // 1_000_000} MB of codes per pass",
                    "stage_ms": stage, "build_s": fx.get("build_s")},

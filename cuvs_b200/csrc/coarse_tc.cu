@@ -557,41 +557,126 @@ coarse_finish_kernel(const uint32_t* __restrict__ cand_key, const uint32_t* __re
   }
 }
 
-// Faster finish for the common case (at most 512 half tiles, C <= 128): instead of a radix select
-// over every candidate key, the selection threshold is the C-th largest of the per-half-tile maxima
-// (at least C keys are then at or above it, and everything above it is rescored, usually little more
-// than C lists), the rows to rescore are first copied to shared memory with coalesced loads, and the
-// defining FMA chains then run out of shared memory.  Same result contract as coarse_finish_kernel:
-// probes by (exact score, list id), the guard proves them exact or the query is queued for the
-// exact redo.
+// Faster finish for the common case (at most 512 half tiles, C <= 64 and small against the number of
+// half tiles).  Instead of a radix select over every candidate key:
+//   A. every thread keeps the keys of up to two half tiles in registers and finds their maxima;
+//   B. the 64 largest maxima are found with register bitonic sorts (64 values per warp, two per
+//      lane) and three rounds of pairwise merges through shared memory; the C-th largest maximum
+//      is the threshold t0: at least C keys are >= t0;
+//   C. every key >= t0 is a list to rescore (usually little more than C lists);
+//   D. their rows are copied to shared memory with coalesced loads and the defining FMA chains run
+//      out of shared memory, one thread per list;
+//   E. one warp sorts the rescored lists by (exact score, list id) in registers.
+// Same result contract as coarse_finish_kernel: the guard proves the probes exact or the query is
+// queued for the exact redo.
 constexpr uint32_t kFinMaxHalfTiles = 512;
-constexpr uint32_t kFinMaxSel       = 256;
+constexpr uint32_t kFinMaxC         = 64;
+constexpr uint32_t kFinRows         = 32;  // rows rescored per round
 
+// 64 values per warp, value e = r * 32 + lane in register a<r>: full bitonic sort.
+template <typename T, bool Desc>
+__device__ __forceinline__ void warp_sort64(T& a0, T& a1)
+{
+  const uint32_t lane = threadIdx.x & 31u;
+  auto shfl = [](T v, int j) {
+    if constexpr (sizeof(T) == 8) {
+      const uint32_t lo = __shfl_xor_sync(kFullMask, uint32_t(v), j);
+      const uint32_t hi = __shfl_xor_sync(kFullMask, uint32_t(uint64_t(v) >> 32), j);
+      return T((uint64_t(hi) << 32) | lo);
+    } else {
+      return T(__shfl_xor_sync(kFullMask, v, j));
+    }
+  };
+#pragma unroll
+  for (uint32_t k = 2; k <= 64; k <<= 1) {
+#pragma unroll
+    for (uint32_t j = k >> 1; j > 0; j >>= 1) {
+      if (j == 32) {  // k == 64: partner is the other register of the same lane, ascending block
+        const T lo = a0 < a1 ? a0 : a1, hi = a0 < a1 ? a1 : a0;
+        a0 = Desc ? hi : lo;
+        a1 = Desc ? lo : hi;
+      } else {
+        const T o0 = shfl(a0, int(j)), o1 = shfl(a1, int(j));
+        // value index e = r * 32 + lane; block direction from bit k of e (k == 64: one block)
+        const bool up0 = ((lane & k) == 0) || k >= 32;         // r = 0: bit 5 of e is 0
+        const bool up1 = k == 64 || (k < 32 && (lane & k) == 0);  // r = 1: bit 5 of e is 1
+        const bool low = (lane & j) == 0;
+        const bool min0 = (low == up0) != Desc, min1 = (low == up1) != Desc;
+        a0 = min0 ? (a0 < o0 ? a0 : o0) : (a0 < o0 ? o0 : a0);
+        a1 = min1 ? (a1 < o1 ? a1 : o1) : (a1 < o1 ? o1 : a1);
+      }
+    }
+  }
+}
+// (a0, a1) sorted descending, `other` = 64 values sorted descending in shared memory: afterwards
+// (a0, a1) = the 64 largest of the union, sorted descending.
+__device__ __forceinline__ void warp_merge_top64_desc(uint32_t& a0, uint32_t& a1, const uint32_t* other)
+{
+  const uint32_t lane = threadIdx.x & 31u;
+  a0 = max(a0, other[63u - lane]);
+  a1 = max(a1, other[31u - lane]);
+  // bitonic sequence -> descending
+  {
+    const uint32_t hi = max(a0, a1), lo = min(a0, a1);
+    a0 = hi;
+    a1 = lo;
+  }
+#pragma unroll
+  for (uint32_t j = 16; j > 0; j >>= 1) {
+    const uint32_t o0 = __shfl_xor_sync(kFullMask, a0, int(j)), o1 = __shfl_xor_sync(kFullMask, a1, int(j));
+    const bool keep_max = (lane & j) == 0;
+    a0 = keep_max ? max(a0, o0) : min(a0, o0);
+    a1 = keep_max ? max(a1, o1) : min(a1, o1);
+  }
+}
+
+template <int KPH>
 __global__ void __launch_bounds__(256)
 coarse_finish_small_kernel(const uint32_t* __restrict__ cand_key, const uint32_t* __restrict__ cand_bound,
-                           uint32_t n_cand /* per query */, uint32_t kph /* keys per half tile */,
-                           const float* __restrict__ centers, const float* __restrict__ fq,
-                           uint32_t n_lists, uint32_t dim_ext, float alpha, uint32_t n_probes, uint32_t C,
-                           uint32_t cap /* pow2 >= C, <= kFinMaxSel */, float cmax,
-                           uint32_t* __restrict__ probes, float* __restrict__ scores_out,
-                           uint32_t* __restrict__ redo_list, uint32_t* __restrict__ redo_count)
+                           uint32_t n_cand /* per query */, const float* __restrict__ centers,
+                           const float* __restrict__ fq, uint32_t n_lists, uint32_t dim_ext, float alpha,
+                           uint32_t n_probes, uint32_t C, float cmax, uint32_t* __restrict__ probes,
+                           float* __restrict__ scores_out, uint32_t* __restrict__ redo_list,
+                           uint32_t* __restrict__ redo_count)
 {
-  // dynamic: [cap] u64 keys | query [dim_ext] | staged candidate keys [n_cand], later reused for the
-  // rows to rescore ([rows_fit][dim_ext + 1])
-  extern __shared__ uint64_t s_keys[];
-  float* s_q    = reinterpret_cast<float*>(s_keys + cap);
-  uint32_t* key = reinterpret_cast<uint32_t*>(s_q + dim_ext);
-  __shared__ uint32_t s_max[kFinMaxHalfTiles];
-  __shared__ uint32_t s_count;
+  // dynamic: query [dim_ext] | rows to rescore [kFinRows][dim_ext + 1]
+  extern __shared__ float s_dyn[];
+  float* s_q    = s_dyn;
+  float* s_rows = s_dyn + dim_ext;
+  __shared__ uint32_t s_top[8][64];
+  __shared__ uint64_t s_keys[128];  // lists to rescore, then (ordered exact score << 32 | list)
+  __shared__ uint32_t s_count, s_t0;
   __shared__ float s_red[8];
   __shared__ uint32_t s_tb[8];
-  const uint32_t q       = blockIdx.x;
-  const uint32_t tid     = threadIdx.x;
-  const uint32_t n_half  = n_cand / kph;
-  {
-    const uint4* src = reinterpret_cast<const uint4*>(cand_key + size_t(q) * n_cand);
-    uint4* dst       = reinterpret_cast<uint4*>(key);
-    for (uint32_t i = tid; i < n_cand / 4; i += 256) { dst[i] = __ldg(src + i); }
+  const uint32_t q      = blockIdx.x;
+  const uint32_t tid    = threadIdx.x;
+  const uint32_t lane   = tid & 31u;
+  const uint32_t warp   = tid >> 5;
+  const uint32_t n_half = n_cand / KPH;
+
+  // ---- A: the keys of half tiles tid and tid + 256, their maxima (invalid keys count as 0) ----
+  uint32_t keys[2][KPH];
+  uint32_t mx[2];
+#pragma unroll
+  for (int s = 0; s < 2; s++) {
+    const uint32_t h = tid + uint32_t(s) * 256u;
+    mx[s]            = 0;
+    if (h < n_half) {
+      const uint4* src = reinterpret_cast<const uint4*>(cand_key + size_t(q) * n_cand + size_t(h) * KPH);
+#pragma unroll
+      for (int i = 0; i < KPH / 4; i++) {
+        const uint4 v      = __ldg(src + i);
+        keys[s][4 * i]     = v.x;
+        keys[s][4 * i + 1] = v.y;
+        keys[s][4 * i + 2] = v.z;
+        keys[s][4 * i + 3] = v.w;
+        mx[s]              = max(max(mx[s], v.x), max(v.y, max(v.z, v.w)));
+      }
+      if (!key_valid(mx[s])) { mx[s] = 0; }
+    } else {
+#pragma unroll
+      for (int i = 0; i < KPH; i++) { keys[s][i] = 0; }
+    }
   }
   float qq = 0.0f;
   for (uint32_t i = tid; i < dim_ext; i += 256) {
@@ -601,74 +686,67 @@ coarse_finish_small_kernel(const uint32_t* __restrict__ cand_key, const uint32_t
   }
 #pragma unroll
   for (int d = 16; d > 0; d >>= 1) { qq += __shfl_xor_sync(kFullMask, qq, d); }
-  if ((tid & 31) == 0) { s_red[tid >> 5] = qq; }
+  if (lane == 0) { s_red[warp] = qq; }
   if (tid == 0) { s_count = 0; }
-  for (uint32_t i = tid; i < cap; i += 256) { s_keys[i] = kEmptyKey; }
-  // bound on what the half tiles dropped
-  uint32_t tb = 0;
+  if (tid < 128) { s_keys[tid] = kEmptyKey; }
+  uint32_t tb = 0;  // bound on what the half tiles dropped
   {
     const uint32_t* bnd = cand_bound + size_t(q) * n_half;
     for (uint32_t i = tid; i < n_half; i += 256) { tb = max(tb, __ldg(bnd + i)); }
   }
 #pragma unroll
   for (int d = 16; d > 0; d >>= 1) { tb = max(tb, __shfl_xor_sync(kFullMask, tb, d)); }
-  if ((tid & 31) == 0) { s_tb[tid >> 5] = tb; }
-  __syncthreads();
+  if (lane == 0) { s_tb[warp] = tb; }
 
-  // ---- largest key of every half tile (invalid keys count as 0), sorted descending ----
-  for (uint32_t h = tid; h < kFinMaxHalfTiles; h += 256) {
-    uint32_t m = 0;
-    if (h < n_half) {
-      const uint4* kk = reinterpret_cast<const uint4*>(key + h * kph);
-      for (uint32_t i = 0; i < kph / 4; i++) {
-        const uint4 v = kk[i];
-        m             = max(max(m, v.x), max(v.y, max(v.z, v.w)));
-      }
-      if (!key_valid(m)) { m = 0; }
+  // ---- B: the 64 largest maxima, descending; t0 = the C-th largest ----
+  uint32_t a0 = mx[0], a1 = mx[1];
+  warp_sort64<uint32_t, true>(a0, a1);
+#pragma unroll
+  for (uint32_t half = 4; half > 0; half >>= 1) {
+    if (warp >= half && warp < 2 * half) {
+      s_top[warp][lane]       = a0;
+      s_top[warp][32u + lane] = a1;
     }
-    s_max[h] = m;
+    __syncthreads();
+    if (warp < half) { warp_merge_top64_desc(a0, a1, s_top[warp + half]); }
+  }
+  if (warp == 0) {
+    // the C-th largest maximum (0 = fewer than C valid half tiles: every valid key is taken)
+    const uint32_t pos = C - 1;
+    const uint32_t v   = __shfl_sync(kFullMask, pos < 32 ? a0 : a1, int(pos & 31u));
+    if (lane == 0) { s_t0 = v; }
   }
   __syncthreads();
-  for (uint32_t size = 2; size <= kFinMaxHalfTiles; size <<= 1) {
-    for (uint32_t stride = size >> 1; stride > 0; stride >>= 1) {
-      const uint32_t i  = tid;  // 256 compare-exchanges cover 512 elements
-      const uint32_t lo = 2 * i - (i & (stride - 1));
-      const uint32_t hi = lo + stride;
-      const bool down   = (lo & size) == 0;
-      const uint32_t a = s_max[lo], b = s_max[hi];
-      if ((a < b) == down) {
-        s_max[lo] = b;
-        s_max[hi] = a;
+  const uint32_t t0 = s_t0;
+
+  // ---- C: every key >= t0 names a list to rescore ----
+#pragma unroll
+  for (int s = 0; s < 2; s++) {
+    const uint32_t h = tid + uint32_t(s) * 256u;
+    if (mx[s] >= t0 && mx[s] != 0) {
+#pragma unroll
+      for (int i = 0; i < KPH; i++) {
+        const uint32_t kk = keys[s][i];
+        if (key_valid(kk) && kk >= t0) {
+          const uint32_t slot = atomicAdd(&s_count, 1u);
+          // list id = tile * 256 + half * 128 + column; h enumerates (tile, half)
+          if (slot < 128u) { s_keys[slot] = h * kHalf + (127u - (kk & 127u)); }
+        }
       }
-      __syncthreads();
     }
   }
-  // Threshold: the C-th largest half-tile maximum (0 = fewer than C valid half tiles: take every valid
-  // key).  At least C keys are >= t0, every key >= t0 is rescored.
-  const uint32_t t0 = s_max[C - 1];
-  for (uint32_t i = tid; i < n_cand; i += 256) {
-    const uint32_t kk = key[i];
-    if (key_valid(kk) && kk >= t0) {
-      const uint32_t slot = atomicAdd(&s_count, 1u);
-      // list id = tile * 256 + half * 128 + column; i / kph enumerates (tile, half)
-      if (slot < cap) { s_keys[slot] = (i / kph) * kHalf + (127u - (kk & 127u)); }
-    }
-  }
-  __syncthreads();  // the staged keys are dead from here on
+  __syncthreads();
   uint32_t tile_key = s_tb[0];
 #pragma unroll
   for (int w = 1; w < 8; w++) { tile_key = max(tile_key, s_tb[w]); }
   const float tilebound = key_valid(tile_key) ? key_value(tile_key) : -INFINITY;
-  const uint32_t n_sel  = min(s_count, cap);
-  const bool overflow   = s_count > cap;
+  const uint32_t n_sel  = min(s_count, 64u);
+  const bool overflow   = s_count > 64u;
 
-  // ---- exact rescoring: rows copied to shared memory (padded against bank conflicts), then the
-  //      defining FMA chain, ascending k, one thread per list ----
-  float* s_rows            = reinterpret_cast<float*>(key);
+  // ---- D: exact rescoring out of shared memory (rows padded against bank conflicts) ----
   const uint32_t row_words = dim_ext + 1;
-  const uint32_t rows_fit  = max(1u, (n_cand * 4u) / (row_words * 4u));
-  for (uint32_t r0 = 0; r0 < n_sel; r0 += rows_fit) {
-    const uint32_t n_rows = min(rows_fit, n_sel - r0);
+  for (uint32_t r0 = 0; r0 < n_sel; r0 += kFinRows) {
+    const uint32_t n_rows = min(kFinRows, n_sel - r0);
     const uint32_t per4   = dim_ext / 4;  // dim_ext is a multiple of 4
     for (uint32_t e = tid; e < n_rows * per4; e += 256) {
       const uint32_t r = e / per4, c4 = e - r * per4;
@@ -685,47 +763,48 @@ coarse_finish_small_kernel(const uint32_t* __restrict__ cand_key, const uint32_t
       const uint32_t l = uint32_t(s_keys[r0 + tid]);
       const float* c   = s_rows + tid * row_words;
       float acc        = 0.0f;
-      for (uint32_t k = 0; k < dim_ext; k++) { acc = __fmaf_rn(c[k], s_q[k], acc); }
+      uint32_t k       = 0;
+      for (; k + 4 <= dim_ext; k += 4) {
+        acc = __fmaf_rn(c[k], s_q[k], acc);
+        acc = __fmaf_rn(c[k + 1], s_q[k + 1], acc);
+        acc = __fmaf_rn(c[k + 2], s_q[k + 2], acc);
+        acc = __fmaf_rn(c[k + 3], s_q[k + 3], acc);
+      }
       s_keys[r0 + tid] = (uint64_t(float_to_ordered(__fmul_rn(alpha, acc))) << 32) | l;
     }
     __syncthreads();
   }
-  for (uint32_t size = 2; size <= cap; size <<= 1) {
-    for (uint32_t stride = size >> 1; stride > 0; stride >>= 1) {
-      for (uint32_t i = tid; i < cap / 2; i += 256) {
-        const uint32_t lo = 2 * i - (i & (stride - 1));
-        const uint32_t hi = lo + stride;
-        const bool up     = (lo & size) == 0;
-        const uint64_t a = s_keys[lo], b = s_keys[hi];
-        if ((a > b) == up) {
-          s_keys[lo] = b;
-          s_keys[hi] = a;
-        }
+
+  // ---- E: sort by (exact score, list id), write the probes, guard ----
+  if (warp == 0) {
+    uint64_t b0 = s_keys[lane], b1 = s_keys[32u + lane];
+    warp_sort64<uint64_t, false>(b0, b1);
+    for (uint32_t pi = lane; pi < n_probes; pi += 32) {
+      const uint64_t kk                 = pi < 32 ? b0 : b1;  // n_probes <= C <= 64
+      probes[size_t(q) * n_probes + pi] = uint32_t(kk);
+      if (scores_out) { scores_out[size_t(q) * n_probes + pi] = ordered_to_float(uint32_t(kk >> 32)); }
+    }
+    const uint32_t last_pos = n_probes - 1;
+    const uint64_t last_key = (uint64_t(__shfl_sync(kFullMask, uint32_t((last_pos < 32 ? b0 : b1) >> 32),
+                                                    int(last_pos & 31u)))
+                               << 32);
+    if (lane == 0) {
+      // guard, in dot-product units (score = alpha * dot, alpha < 0)
+      float qnorm = 0.0f;
+      for (int w = 0; w < 8; w++) { qnorm += s_red[w]; }
+      qnorm = sqrtf(qnorm);
+      const float eps = (float(dim_ext + 8) * 2.4e-7f + 3.1e-5f) * qnorm * cmax;
+      // every list that was not rescored has a key below t0 or was dropped by its half tile
+      const float t_c    = key_valid(t0) ? key_value(t0) : -INFINITY;
+      const float unseen = fmaxf(t_c, tilebound);
+      bool ok            = !overflow && n_sel >= n_probes;
+      if (ok) {
+        const float last_dot = ordered_to_float(uint32_t(last_key >> 32)) / alpha;
+        // all lists rescored (n_sel == every valid candidate == every list) needs no proof
+        ok = (last_dot - unseen > eps) || (n_sel >= n_lists);
       }
-      __syncthreads();
+      if (!ok) { redo_list[atomicAdd(redo_count, 1u)] = q; }
     }
-  }
-  for (uint32_t pi = tid; pi < n_probes; pi += 256) {
-    const uint64_t kk                 = s_keys[pi];
-    probes[size_t(q) * n_probes + pi] = uint32_t(kk);
-    if (scores_out) { scores_out[size_t(q) * n_probes + pi] = ordered_to_float(uint32_t(kk >> 32)); }
-  }
-  if (tid == 0) {
-    // guard, in dot-product units (score = alpha * dot, alpha < 0)
-    float qnorm = 0.0f;
-    for (int w = 0; w < 8; w++) { qnorm += s_red[w]; }
-    qnorm = sqrtf(qnorm);
-    const float eps = (float(dim_ext + 8) * 2.4e-7f + 3.1e-5f) * qnorm * cmax;
-    // every list that was not rescored has a key below t0 or was dropped by its half tile
-    const float t_c    = key_valid(t0) ? key_value(t0) : -INFINITY;
-    const float unseen = fmaxf(t_c, tilebound);
-    bool ok            = !overflow && n_sel >= n_probes;
-    if (ok) {
-      const float last_dot = ordered_to_float(uint32_t(s_keys[n_probes - 1] >> 32)) / alpha;
-      // all lists rescored (n_sel == every valid candidate == every list) needs no proof
-      ok = (last_dot - unseen > eps) || (n_sel >= n_lists);
-    }
-    if (!ok) { redo_list[atomicAdd(redo_count, 1u)] = q; }
   }
 }
 
@@ -988,17 +1067,19 @@ void select_clusters_tc(raft::resources& res, const float* centers, const float*
   uint32_t cap     = 2;
   while (cap < 2 * C) { cap <<= 1; }  // room for ties at the selection threshold
   const size_t fin_smem = size_t(cap) * 8 + size_t(dim_ext) * 4 + size_t(n_cand) * 4;
-  static size_t fin_configured = 48 * 1024, fin_small_configured = 48 * 1024;
+  static size_t fin_configured = 48 * 1024;
   // the half-tile-maxima threshold is tight only when C is small against the number of half tiles
-  if (n_tiles * 2 <= kFinMaxHalfTiles && cap <= kFinMaxSel && C * 4 <= n_tiles * 2) {
-    if (fin_smem > fin_small_configured) {
-      CUDA_TRY(cudaFuncSetAttribute(coarse_finish_small_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    int(fin_smem)));
-      fin_small_configured = fin_smem;
+  const size_t fin_small_smem = (size_t(dim_ext) + size_t(kFinRows) * (dim_ext + 1)) * 4;
+  if (n_tiles * 2 <= kFinMaxHalfTiles && C <= kFinMaxC && C * 4 <= n_tiles * 2 && fin_small_smem <= 48 * 1024) {
+    if (kph == 16) {
+      coarse_finish_small_kernel<16><<<n_queries, 256, fin_small_smem, stream>>>(
+        cand_key, cand_bnd, n_cand, centers, fq, n_lists, dim_ext, alpha, n_probes, C, cmax, probes, scores_out,
+        redo_list, words + 2);
+    } else {
+      coarse_finish_small_kernel<8><<<n_queries, 256, fin_small_smem, stream>>>(
+        cand_key, cand_bnd, n_cand, centers, fq, n_lists, dim_ext, alpha, n_probes, C, cmax, probes, scores_out,
+        redo_list, words + 2);
     }
-    coarse_finish_small_kernel<<<n_queries, 256, fin_smem, stream>>>(
-      cand_key, cand_bnd, n_cand, kph, centers, fq, n_lists, dim_ext, alpha, n_probes, C, cap, cmax, probes,
-      scores_out, redo_list, words + 2);
   } else {
     if (fin_smem > fin_configured) {
       CUDA_TRY(cudaFuncSetAttribute(coarse_finish_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
