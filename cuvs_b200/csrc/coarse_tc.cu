@@ -9,8 +9,8 @@
 // Pipeline per batch
 //   1. split_tf32_kernel: every fp32 operand x is written as hi = tf32(x), lo = tf32(x - hi)
 //      (centers once per index, queries per batch).
-//   2. coarse_tc_kernel: CTA tile = 128 queries x 256 lists, K in blocks of 32 floats (one
-//      128-byte swizzle atom).  Per K block three products accumulate into TMEM:
+//   2. coarse_tc_kernel: CTA tile = 128 queries x 256 lists, K in blocks of 16 floats (one
+//      64-byte swizzle atom), four pipeline stages.  Per K block three products accumulate into TMEM:
 //      hi*hi + hi*lo + lo*hi.  Warp 0 issues TMA loads (no multicast), warp 1 issues the MMAs,
 //      eight epilogue warps read the accumulator with tcgen05.ld (thread = query row) and keep,
 //      per row and per 128-list half tile, the largest dot products in registers, as packed
@@ -43,20 +43,39 @@ namespace {
 
 constexpr int kBM       = 128;  // queries per tile
 constexpr int kBN       = 256;  // lists per tile
-constexpr int kBK       = 32;   // floats per K block (128 bytes)
-constexpr int kStages   = 2;
-// Epilogue variants <STREAMS, KEEP>: the columns of a half tile are dealt to STREAMS independent
-// chains (column % STREAMS), each keeping its KEEP largest keys.  <4, 4> is the cheaper one
-// (8 min/max per column, four independent chains); <1, 8> keeps more per chain and is chosen when
-// many wanted lists per half tile are likely (large n_probes relative to n_lists).
-constexpr int kMaxKph   = 16;   // keys written per row per half tile, at most
+constexpr int kBK       = 16;   // floats per K block (64 bytes: four pipeline stages fit, and more bytes
+                                // stay in flight than with two 128-byte stages)
+constexpr int kStages   = 4;
+// Epilogue: sixteen warps, one per (32-row lane quarter, 64-column unit) of the accumulator; every
+// unit contributes eight keys per row.  Variants <STREAMS, KEEP> (STREAMS * KEEP = 8): the columns of
+// a unit are dealt to STREAMS independent chains (column % STREAMS), each keeping its KEEP largest
+// keys.  <2, 4> is the cheaper one (8 min/max per column, two independent chains of 32 lists);
+// <1, 8> keeps more per chain and is chosen when many wanted lists per unit are likely (large
+// n_probes relative to n_lists).  Keys are stored per 128-column half tile (two units side by side).
+constexpr int kMaxKph   = 16;   // keys written per row per half tile
 constexpr int kHalf     = kBN / 2;
-constexpr int kThreads  = 320;  // warp 0 TMA, warp 1 MMA, warps 2..9 epilogue
-constexpr uint32_t kStageBytes = (2 * kBM + 2 * kBN) * kBK * 4;  // 96 KB
+constexpr int kUnit     = 64;   // columns per epilogue warp
+constexpr int kEpiWarps = 16;
+constexpr int kThreads  = (2 + kEpiWarps) * 32;  // warp 0 TMA, warp 1 MMA, warps 2..17 epilogue
+constexpr uint32_t kStageBytes = (2 * kBM + 2 * kBN) * kBK * 4;  // 48 KB
 constexpr uint32_t kSmemBytes  = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
 constexpr uint32_t kSpinLimit  = 1u << 21;  // bounded waits (each try_wait sleeps up to ~1 us)
 
 enum { ERR_NONE = 0, ERR_TIMEOUT = 1 };
+
+#ifdef TC_PROFILE
+// debug build only: cycles the three roles spend waiting on their barriers
+__device__ unsigned long long g_tc_prof[16];
+#define TC_WAIT(idx, expr)                                          \
+  [&]() {                                                           \
+    const long long t0_ = clock64();                                \
+    const bool r_ = (expr);                                         \
+    atomicAdd(&g_tc_prof[idx], (unsigned long long)(clock64() - t0_)); \
+    return r_;                                                      \
+  }()
+#else
+#define TC_WAIT(idx, expr) (expr)
+#endif
 
 // ------------------------------------------------------------------------------------------------
 // operand split
@@ -139,18 +158,19 @@ __device__ __forceinline__ void tc_mma_tf32(uint32_t tmem_d, uint64_t desc_a, ui
     ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
     : "memory");
 }
-// Shared-memory matrix descriptor of a K-major tile stored as rows of 128 bytes with the 128-byte
-// swizzle: 8-row groups 1024 bytes apart.
+// Shared-memory matrix descriptor of a K-major tile stored as rows of 64 bytes with the 64-byte
+// swizzle: 8-row groups 512 bytes apart.
 __device__ __forceinline__ uint64_t make_desc(uint32_t saddr)
 {
   uint64_t d = 0;
   d |= uint64_t((saddr & 0x3FFFFu) >> 4);  // start address, 16-byte units
   d |= uint64_t(1) << 16;                  // leading byte offset (unused for swizzled K-major)
-  d |= uint64_t(1024 >> 4) << 32;          // stride byte offset between 8-row groups
+  d |= uint64_t((8 * kBK * 4) >> 4) << 32; // stride byte offset between 8-row groups
   d |= uint64_t(1) << 46;                  // descriptor version of this architecture
-  d |= uint64_t(2) << 61;                  // 128-byte swizzle
+  d |= uint64_t(4) << 61;                  // 64-byte swizzle
   return d;
 }
+static_assert(kBK * 4 == 64, "descriptor and tensor maps are written for 64-byte rows");
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32])
 {
   asm volatile(
@@ -171,9 +191,9 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32])
 // the GEMM + candidate kernel
 // ------------------------------------------------------------------------------------------------
 struct tc_params {
-  uint32_t n_queries, n_lists, k_blocks, n_tiles, tile_stride;
+  uint32_t n_queries, n_lists, k_blocks, n_tiles /* list tiles */, n_work /* query tiles x list tiles */;
   uint32_t* cand_key;    // [n_queries, n_tiles, 2, keys per half tile] packed keys (larger = closer)
-  uint32_t* cand_bound;  // [n_queries, n_tiles, 2] key bounding everything the half tile dropped
+  uint32_t* cand_bound;  // [n_queries, n_tiles, 2, 2] key bounding everything a 64-column unit dropped
   uint32_t* error;     // error word
 };
 
@@ -197,7 +217,9 @@ coarse_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
   __shared__ uint32_t s_failed;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const uint32_t q0 = blockIdx.x * kBM;
+#ifdef TC_PROFILE
+  const long long tc_start = clock64();
+#endif
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; s++) {
@@ -206,7 +228,7 @@ coarse_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
     }
     for (int a = 0; a < 2; a++) {
       mbar_init(bar_tfull + a * 8, 1);
-      mbar_init(bar_tempty + a * 8, 8);  // one arrival per epilogue warp
+      mbar_init(bar_tempty + a * 8, kEpiWarps);  // one arrival per epilogue warp
     }
     s_failed = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -221,10 +243,11 @@ coarse_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
   tc_fence_after();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
 
-  // tiles of this CTA: blockIdx.y, blockIdx.y + tile_stride, ...
-  const uint32_t first_tile = blockIdx.y;
-  uint32_t n_my_tiles       = 0;
-  if (first_tile < p.n_tiles) { n_my_tiles = (p.n_tiles - first_tile + p.tile_stride - 1) / p.tile_stride; }
+  // Persistent CTAs (one per SM): output tiles blockIdx.x, blockIdx.x + gridDim.x, ... of the
+  // n_work = query tiles x list tiles, list tile fastest, so every SM gets the same number of tiles
+  // to within one.
+  uint32_t n_my_tiles = 0;
+  if (blockIdx.x < p.n_work) { n_my_tiles = (p.n_work - blockIdx.x + gridDim.x - 1) / gridDim.x; }
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
@@ -232,9 +255,11 @@ coarse_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
       uint32_t stage = 0, phase = 0;
       bool ok = true;
       for (uint32_t i = 0; ok && i < n_my_tiles; i++) {
-        const int n0 = int((first_tile + i * p.tile_stride) * kBN);
+        const uint32_t g  = blockIdx.x + i * gridDim.x;
+        const uint32_t q0 = (g / p.n_tiles) * kBM;
+        const int n0      = int((g % p.n_tiles) * kBN);
         for (uint32_t kb = 0; kb < p.k_blocks; kb++) {
-          if (!mbar_wait(bar_empty + stage * 8, phase ^ 1u)) {
+          if (!TC_WAIT(0, mbar_wait(bar_empty + stage * 8, phase ^ 1u))) {
             ok = false;
             break;
           }
@@ -268,14 +293,14 @@ coarse_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
       for (uint32_t i = 0; ok && i < n_my_tiles; i++) {
         const uint32_t acc       = i & 1u;
         const uint32_t acc_phase = (i >> 1) & 1u;
-        if (!mbar_wait(bar_tempty + acc * 8, acc_phase ^ 1u)) {
+        if (!TC_WAIT(1, mbar_wait(bar_tempty + acc * 8, acc_phase ^ 1u))) {
           ok = false;
           break;
         }
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + acc * kBN;
         for (uint32_t kb = 0; kb < p.k_blocks; kb++) {
-          if (!mbar_wait(bar_full + stage * 8, phase)) {
+          if (!TC_WAIT(2, mbar_wait(bar_full + stage * 8, phase))) {
             ok = false;
             break;
           }
@@ -307,17 +332,20 @@ coarse_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
     }
     __syncwarp();
   } else {
-    // ---------------- epilogue: thread = query row, warp = (lane quarter, column half) ----------------
+    // ---------------- epilogue: thread = query row, warp = (lane quarter, 64-column unit) ----------------
     const uint32_t quarter = uint32_t(warp) & 3u;        // TMEM lanes a warp may read: 32 * (warp % 4)
-    const uint32_t half    = uint32_t(warp - 2) >> 2;    // warps 2..5 -> columns 0..127, 6..9 -> 128..255
+    const uint32_t unit    = uint32_t(warp - 2) >> 2;    // warps 2..5 -> columns 0..63, 6..9 -> 64..127, ...
+    const uint32_t half    = unit >> 1;                  // 128-column half tile the unit belongs to
+    const uint32_t sub     = unit & 1u;                  // first or second unit of the half tile
     const uint32_t row     = quarter * 32 + lane;
-    const uint32_t q       = q0 + row;
     bool ok = true;
     for (uint32_t i = 0; i < n_my_tiles; i++) {
-      const uint32_t tile      = first_tile + i * p.tile_stride;
+      const uint32_t g         = blockIdx.x + i * gridDim.x;
+      const uint32_t tile      = g % p.n_tiles;
+      const uint32_t q         = (g / p.n_tiles) * kBM + row;
       const uint32_t acc       = i & 1u;
       const uint32_t acc_phase = (i >> 1) & 1u;
-      if (ok && !mbar_wait(bar_tfull + acc * 8, acc_phase)) { ok = false; }
+      if (ok && !(lane == 0 && warp == 2 ? TC_WAIT(3, mbar_wait(bar_tfull + acc * 8, acc_phase)) : mbar_wait(bar_tfull + acc * 8, acc_phase))) { ok = false; }
       // a time-out on any lane ends the loop for the whole warp
       if (__any_sync(kFullMask, !ok)) {
         ok = false;
@@ -325,17 +353,17 @@ coarse_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
       }
       tc_fence_after();
       // Packed key: order-preserving image of the dot product with its low 7 bits replaced by
-      // (127 - column in the half tile); empty / out-of-range columns are key 0.
+      // (127 - column in the 128-column half tile); empty / out-of-range columns are key 0.
       uint32_t key[kStreams][kKeep];
 #pragma unroll
       for (int st = 0; st < kStreams; st++) {
 #pragma unroll
         for (int t = 0; t < kKeep; t++) { key[st][t] = 0u; }
       }
-      const uint32_t col0 = half * kHalf;
+      const uint32_t col0 = unit * kUnit;
       const uint32_t n0   = tile * kBN + col0;
 #pragma unroll 1
-      for (uint32_t c = 0; c < kHalf; c += 32) {
+      for (uint32_t c = 0; c < kUnit; c += 32) {
         uint32_t r[32];
         tmem_ld32(tmem_base + ((quarter * 32u) << 16) + acc * kBN + col0 + c, r);
         const uint32_t list0 = n0 + c;
@@ -344,7 +372,7 @@ coarse_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
         for (int e = 0; e < 32; e++) {
           const uint32_t u = r[e];
           uint32_t k = (u ^ (uint32_t(int32_t(u) >> 31) | 0x80000000u)) & ~127u;
-          k |= 127u - (c + uint32_t(e));
+          k |= 127u - (sub * kUnit + c + uint32_t(e));
           if (!full && list0 + e >= p.n_lists) { k = 0u; }
 #pragma unroll
           for (int t = 0; t < kKeep; t++) {
@@ -364,7 +392,7 @@ coarse_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
 #pragma unroll
         for (int st = 1; st < kStreams; st++) { bound = max(bound, key[st][kKeep - 1]); }
         const size_t slot = (size_t(q) * p.n_tiles + tile) * 2 + half;
-        uint4* o          = reinterpret_cast<uint4*>(p.cand_key + slot * (kStreams * kKeep));
+        uint4* o          = reinterpret_cast<uint4*>(p.cand_key + slot * kMaxKph + sub * (kStreams * kKeep));
 #pragma unroll
         for (int st = 0; st < kStreams; st++) {
 #pragma unroll
@@ -373,7 +401,7 @@ coarse_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
               make_uint4(key[st][4 * u], key[st][4 * u + 1], key[st][4 * u + 2], key[st][4 * u + 3]);
           }
         }
-        p.cand_bound[slot] = bound;
+        p.cand_bound[slot * 2 + sub] = bound;
       }
     }
     if (!ok && lane == 0) {
@@ -385,6 +413,13 @@ coarse_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
   // ---------------- teardown ----------------
   tc_fence_before();
   __syncthreads();
+#ifdef TC_PROFILE
+  if (threadIdx.x == 0) {
+    atomicAdd(&g_tc_prof[4], (unsigned long long)(clock64() - tc_start));
+    atomicAdd(&g_tc_prof[5], 1ull);
+    atomicAdd(&g_tc_prof[6], (unsigned long long)n_my_tiles);
+  }
+#endif
   if (s_failed) {
     // give copies that are still in flight time to land before the shared memory is released
     for (int i = 0; i < 64; i++) { __nanosleep(1000); }
@@ -489,8 +524,9 @@ coarse_finish_kernel(const uint32_t* __restrict__ cand_key, const uint32_t* __re
     }
   }
   {
-    const uint32_t* bnd = cand_bound + size_t(q) * (n_cand / kph);
-    for (uint32_t i = tid; i < n_cand / kph; i += 256) { tb = max(tb, bnd[i]); }
+    const uint32_t n_bnd = 2 * (n_cand / kph);  // one bound per 64-column unit
+    const uint32_t* bnd  = cand_bound + size_t(q) * n_bnd;
+    for (uint32_t i = tid; i < n_bnd; i += 256) { tb = max(tb, bnd[i]); }
   }
 #pragma unroll
   for (int d = 16; d > 0; d >>= 1) { tb = max(tb, __shfl_xor_sync(kFullMask, tb, d)); }
@@ -691,8 +727,8 @@ coarse_finish_small_kernel(const uint32_t* __restrict__ cand_key, const uint32_t
   if (tid < 128) { s_keys[tid] = kEmptyKey; }
   uint32_t tb = 0;  // bound on what the half tiles dropped
   {
-    const uint32_t* bnd = cand_bound + size_t(q) * n_half;
-    for (uint32_t i = tid; i < n_half; i += 256) { tb = max(tb, __ldg(bnd + i)); }
+    const uint32_t* bnd = cand_bound + size_t(q) * 2 * n_half;  // one bound per 64-column unit
+    for (uint32_t i = tid; i < 2 * n_half; i += 256) { tb = max(tb, __ldg(bnd + i)); }
   }
 #pragma unroll
   for (int d = 16; d > 0; d >>= 1) { tb = max(tb, __shfl_xor_sync(kFullMask, tb, d)); }
@@ -944,7 +980,7 @@ encode_fn_t get_encode_fn()
   return fn;
 }
 
-// 2-D fp32 row-major [rows, cols] tensor, box [box_rows, 32 columns], 128-byte swizzle, zero fill.
+// 2-D fp32 row-major [rows, cols] tensor, box [box_rows, kBK columns], 64-byte swizzle, zero fill.
 CUtensorMap make_map(const float* ptr, uint64_t rows, uint64_t cols, uint32_t box_rows)
 {
   CUtensorMap m;
@@ -954,7 +990,7 @@ CUtensorMap make_map(const float* ptr, uint64_t rows, uint64_t cols, uint32_t bo
   const cuuint32_t elem[2]    = {1, 1};
   CUresult r = get_encode_fn()(&m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(ptr), dims,
                                strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                               CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   CUVS_EXPECTS(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed with code %d", int(r));
   return m;
@@ -983,7 +1019,7 @@ size_t coarse_tc_workspace_bytes(uint32_t n_queries, uint32_t n_lists, uint32_t 
   lay.add(size_t(n_queries) * dim_ext * 4);  // fq hi
   lay.add(size_t(n_queries) * dim_ext * 4);  // fq lo
   lay.add(size_t(n_queries) * n_tiles * 2 * kMaxKph * 4);  // candidate keys
-  lay.add(size_t(n_queries) * n_tiles * 2 * 4);          // per half tile bound
+  lay.add(size_t(n_queries) * n_tiles * 4 * 4);          // bound per 64-column unit
   lay.add(size_t(n_queries) * 4);            // queries to redo exactly
   lay.add(256);                              // error word, fallback counter, redo counter
   lay.add(size_t(64) * n_lists * 4);         // fallback scratch rows
@@ -1007,18 +1043,19 @@ void select_clusters_tc(raft::resources& res, const float* centers, const float*
                "coarse workspace too small");
   const uint32_t n_tiles = ceildiv<uint32_t>(n_lists, kBN);
   const uint32_t C = std::min<uint32_t>(n_probes + margin_for(n_probes), n_lists);
-  // <4,4> drops a wanted list when 4 of the 32 lists of a chain are wanted: expected fraction of
-  // queries hit = n_chains * C(32,4) * (C/L)^4; above 0.02% use the single top-8 chain instead
+  // <2,4> drops a wanted list when more than 4 of the 32 lists of a chain are wanted: expected
+  // fraction of queries hit = n_chains * C(32,4) * (C/L)^4; above 0.02% use one top-8 chain per
+  // 64-column unit instead
   const double frac    = double(C) / double(n_lists);
   const bool four_by_4 = (double(n_lists) / 32.0) * 35960.0 * frac * frac * frac * frac <= 2e-4;
-  const uint32_t kph   = four_by_4 ? 16 : 8;
+  const uint32_t kph   = kMaxKph;
   const uint32_t n_cand  = n_tiles * 2 * kph;
   ws_layout lay;
   char* ws        = static_cast<char*>(workspace);
   float* fq_hi    = reinterpret_cast<float*>(ws + lay.add(size_t(n_queries) * dim_ext * 4));
   float* fq_lo    = reinterpret_cast<float*>(ws + lay.add(size_t(n_queries) * dim_ext * 4));
   auto* cand_key  = reinterpret_cast<uint32_t*>(ws + lay.add(size_t(n_queries) * n_tiles * 2 * kMaxKph * 4));
-  auto* cand_bnd  = reinterpret_cast<uint32_t*>(ws + lay.add(size_t(n_queries) * n_tiles * 2 * 4));
+  auto* cand_bnd  = reinterpret_cast<uint32_t*>(ws + lay.add(size_t(n_queries) * n_tiles * 4 * 4));
   auto* redo_list = reinterpret_cast<uint32_t*>(ws + lay.add(size_t(n_queries) * 4));
   auto* words     = reinterpret_cast<uint32_t*>(ws + lay.add(256));
   float* scratch  = reinterpret_cast<float*>(ws + lay.add(size_t(64) * n_lists * 4));
@@ -1042,24 +1079,21 @@ void select_clusters_tc(raft::resources& res, const float* centers, const float*
   p.cand_bound = cand_bnd;
   p.error     = words;
   const uint32_t q_tiles = ceildiv<uint32_t>(n_queries, kBM);
-  // list-tile splits per query tile: enough CTAs for a few waves, never more than the tiles
-  uint32_t splits = std::max<uint32_t>(1, (uint32_t(res.sm_count) * 4 + q_tiles - 1) / q_tiles);
-  splits          = std::min(splits, n_tiles);
-  splits          = std::min<uint32_t>(splits, 65535);
-  p.tile_stride   = splits;
+  p.n_work               = q_tiles * n_tiles;
+  const uint32_t grid    = std::min<uint32_t>(uint32_t(res.sm_count), p.n_work);
   static bool configured = false;
   if (!configured) {
-    CUDA_TRY(cudaFuncSetAttribute(coarse_tc_kernel<4, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    CUDA_TRY(cudaFuncSetAttribute(coarse_tc_kernel<2, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                   int(kSmemBytes)));
     CUDA_TRY(cudaFuncSetAttribute(coarse_tc_kernel<1, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                   int(kSmemBytes)));
     configured = true;
   }
   if (four_by_4) {
-    coarse_tc_kernel<4, 4><<<dim3(q_tiles, splits), kThreads, kSmemBytes, stream>>>(m_a_hi, m_a_lo, m_b_hi,
+    coarse_tc_kernel<2, 4><<<grid, kThreads, kSmemBytes, stream>>>(m_a_hi, m_a_lo, m_b_hi,
                                                                                    m_b_lo, p);
   } else {
-    coarse_tc_kernel<1, 8><<<dim3(q_tiles, splits), kThreads, kSmemBytes, stream>>>(m_a_hi, m_a_lo, m_b_hi,
+    coarse_tc_kernel<1, 8><<<grid, kThreads, kSmemBytes, stream>>>(m_a_hi, m_a_lo, m_b_hi,
                                                                                    m_b_lo, p);
   }
   CUDA_TRY(cudaGetLastError());
@@ -1110,7 +1144,7 @@ void coarse_tc_status(raft::resources& res, const void* workspace, uint32_t n_qu
   lay.add(size_t(n_queries) * dim_ext * 4);
   lay.add(size_t(n_queries) * dim_ext * 4);
   lay.add(size_t(n_queries) * n_tiles * 2 * kMaxKph * 4);
-  lay.add(size_t(n_queries) * n_tiles * 2 * 4);
+  lay.add(size_t(n_queries) * n_tiles * 4 * 4);
   lay.add(size_t(n_queries) * 4);
   const size_t o = lay.add(256);
   uint32_t h[2]  = {0, 0};
@@ -1121,3 +1155,13 @@ void coarse_tc_status(raft::resources& res, const void* workspace, uint32_t n_qu
 }
 
 }  // namespace cuvs::neighbors::ivf_pq
+
+#ifdef TC_PROFILE
+extern "C" __attribute__((visibility("default"))) void cuvsB200TcProfile(unsigned long long* out16)
+{
+  cudaDeviceSynchronize();
+  cudaMemcpyFromSymbol(out16, cuvs::neighbors::ivf_pq::g_tc_prof, 16 * sizeof(unsigned long long));
+  unsigned long long zero[16] = {};
+  cudaMemcpyToSymbol(cuvs::neighbors::ivf_pq::g_tc_prof, zero, sizeof(zero));
+}
+#endif
