@@ -701,7 +701,7 @@ extern "C" cuvsError_t cuvsB200CoarseSelect(cuvsResources_t res, void* index_han
 extern "C" cuvsError_t cuvsB200SetCoarseMode(int mode)
 {
   return translate_exceptions([=] {
-    CUVS_EXPECTS(mode >= 0 && mode <= 2, "mode must be 0, 1 or 2");
+    CUVS_EXPECTS((mode >= 0 && mode <= 2) || (mode >= 11 && mode <= 13), "mode must be 0, 1, 2, 11, 12 or 13");
     ivf_pq::set_coarse_mode(mode);
   });
 }

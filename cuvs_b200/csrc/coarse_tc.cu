@@ -197,7 +197,7 @@ struct tc_params {
   uint32_t* error;     // error word
 };
 
-template <int kStreams, int kKeep>
+template <int kStreams, int kKeep, int kProducts>
 __global__ void __launch_bounds__(kThreads, 1)
 coarse_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
                  const __grid_constant__ CUtensorMap map_b_hi, const __grid_constant__ CUtensorMap map_b_lo,
@@ -265,11 +265,15 @@ coarse_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
           }
           const uint32_t dst = base_a + stage * kStageBytes;
           const uint32_t bar = bar_full + stage * 8;
-          mbar_arrive_expect_tx(bar, kStageBytes);
+          // operands the chosen number of products needs: 1: hi*hi; 2: + lo*hi; 3: + hi*lo
+          constexpr uint32_t kBytes = (kBM + kBN + (kProducts >= 2 ? kBM : 0) + (kProducts >= 3 ? kBN : 0)) * kBK * 4;
+          mbar_arrive_expect_tx(bar, kBytes);
           tma_load_2d(dst, &map_a_hi, bar, int(kb * kBK), int(q0));
-          tma_load_2d(dst + kBM * kBK * 4, &map_a_lo, bar, int(kb * kBK), int(q0));
+          if constexpr (kProducts >= 2) { tma_load_2d(dst + kBM * kBK * 4, &map_a_lo, bar, int(kb * kBK), int(q0)); }
           tma_load_2d(dst + 2 * kBM * kBK * 4, &map_b_hi, bar, int(kb * kBK), n0);
-          tma_load_2d(dst + 2 * kBM * kBK * 4 + kBN * kBK * 4, &map_b_lo, bar, int(kb * kBK), n0);
+          if constexpr (kProducts >= 3) {
+            tma_load_2d(dst + 2 * kBM * kBK * 4 + kBN * kBK * 4, &map_b_lo, bar, int(kb * kBK), n0);
+          }
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1u;
@@ -313,9 +317,9 @@ coarse_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
 #pragma unroll
           for (uint32_t k8 = 0; k8 < kBK / 8; k8++) {
             const uint64_t adv = uint64_t(k8 * 2);  // 32 bytes per MMA along K, in 16-byte units
-            tc_mma_tf32(tmem_d, d_a_lo + adv, d_b_hi + adv, idesc, (kb | k8) != 0);
-            tc_mma_tf32(tmem_d, d_a_hi + adv, d_b_lo + adv, idesc, 1);
-            tc_mma_tf32(tmem_d, d_a_hi + adv, d_b_hi + adv, idesc, 1);
+            if constexpr (kProducts >= 2) { tc_mma_tf32(tmem_d, d_a_lo + adv, d_b_hi + adv, idesc, (kb | k8) != 0); }
+            if constexpr (kProducts >= 3) { tc_mma_tf32(tmem_d, d_a_hi + adv, d_b_lo + adv, idesc, 1); }
+            tc_mma_tf32(tmem_d, d_a_hi + adv, d_b_hi + adv, idesc, kProducts >= 2 || (kb | k8) != 0);
           }
           tc_commit(bar_empty + stage * 8);  // the stage may be refilled once these MMAs have read it
           if (++stage == kStages) {
@@ -445,9 +449,9 @@ coarse_finish_kernel(const uint32_t* __restrict__ cand_key, const uint32_t* __re
                      uint32_t n_cand /* per query */, uint32_t kph /* keys per half tile */,
                      const float* __restrict__ centers, const float* __restrict__ fq,
                      uint32_t n_lists, uint32_t dim_ext, float alpha, uint32_t n_probes, uint32_t C,
-                     uint32_t cap /* pow2 >= C */, float cmax, uint32_t* __restrict__ probes,
-                     float* __restrict__ scores_out, uint32_t* __restrict__ redo_list,
-                     uint32_t* __restrict__ redo_count)
+                     uint32_t cap /* pow2 >= C */, float cmax, float eps_rel,
+                     uint32_t* __restrict__ probes, float* __restrict__ scores_out,
+                     uint32_t* __restrict__ redo_list, uint32_t* __restrict__ redo_count)
 {
   extern __shared__ uint64_t s_keys[];                 // [cap] keys; the query; the candidates
   float* s_q      = reinterpret_cast<float*>(s_keys + cap);
@@ -580,7 +584,7 @@ coarse_finish_kernel(const uint32_t* __restrict__ cand_key, const uint32_t* __re
     qnorm = sqrtf(qnorm);
     // |tensor-core - exact| (accumulation order, dropped lo*lo term) plus the 7 low bits the packed
     // keys give up (a relative 2^-16 of the value)
-    const float eps       = (float(dim_ext + 8) * 2.4e-7f + 3.1e-5f) * qnorm * cmax;
+    const float eps       = eps_rel * qnorm * cmax;
     const float t_c       = key_valid(~T) ? key_value(~T) : -INFINITY;  // C-th largest key, as a value
     const float unseen    = fmaxf(t_c, tilebound);
     bool ok               = !overflow && n_sel >= n_probes;
@@ -671,9 +675,9 @@ __global__ void __launch_bounds__(256)
 coarse_finish_small_kernel(const uint32_t* __restrict__ cand_key, const uint32_t* __restrict__ cand_bound,
                            uint32_t n_cand /* per query */, const float* __restrict__ centers,
                            const float* __restrict__ fq, uint32_t n_lists, uint32_t dim_ext, float alpha,
-                           uint32_t n_probes, uint32_t C, float cmax, uint32_t* __restrict__ probes,
-                           float* __restrict__ scores_out, uint32_t* __restrict__ redo_list,
-                           uint32_t* __restrict__ redo_count)
+                           uint32_t n_probes, uint32_t C, float cmax, float eps_rel,
+                           uint32_t* __restrict__ probes, float* __restrict__ scores_out,
+                           uint32_t* __restrict__ redo_list, uint32_t* __restrict__ redo_count)
 {
   // dynamic: query [dim_ext] | rows to rescore [kFinRows][dim_ext + 1]
   extern __shared__ float s_dyn[];
@@ -829,7 +833,7 @@ coarse_finish_small_kernel(const uint32_t* __restrict__ cand_key, const uint32_t
       float qnorm = 0.0f;
       for (int w = 0; w < 8; w++) { qnorm += s_red[w]; }
       qnorm = sqrtf(qnorm);
-      const float eps = (float(dim_ext + 8) * 2.4e-7f + 3.1e-5f) * qnorm * cmax;
+      const float eps = eps_rel * qnorm * cmax;
       // every list that was not rescored has a key below t0 or was dropped by its half tile
       const float t_c    = key_valid(t0) ? key_value(t0) : -INFINITY;
       const float unseen = fmaxf(t_c, tilebound);
@@ -998,7 +1002,15 @@ CUtensorMap make_map(const float* ptr, uint64_t rows, uint64_t cols, uint32_t bo
 
 uint32_t margin_for(uint32_t n_probes) { return std::max<uint32_t>(16, n_probes / 4); }
 
+int& tc_products_ref()
+{
+  static int products = 0;  // 0 = every handle adapts on its own, 1..3 = forced (tests)
+  return products;
+}
+
 }  // namespace
+
+void set_coarse_tc_products(int products) { tc_products_ref() = products; }
 
 bool coarse_tc_usable(uint32_t n_lists, uint32_t n_probes, uint32_t dim_ext)
 {
@@ -1081,20 +1093,52 @@ void select_clusters_tc(raft::resources& res, const float* centers, const float*
   const uint32_t q_tiles = ceildiv<uint32_t>(n_queries, kBM);
   p.n_work               = q_tiles * n_tiles;
   const uint32_t grid    = std::min<uint32_t>(uint32_t(res.sm_count), p.n_work);
-  static bool configured = false;
-  if (!configured) {
-    CUDA_TRY(cudaFuncSetAttribute(coarse_tc_kernel<2, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                  int(kSmemBytes)));
-    CUDA_TRY(cudaFuncSetAttribute(coarse_tc_kernel<1, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                  int(kSmemBytes)));
-    configured = true;
+  // Products of the TF32 split per K step: 3 (hi*hi + lo*hi + hi*lo, error ~ fp32 rounding),
+  // 2 (without hi*lo: |error| <= 2^-11 |q||c|) or 1 (hi*hi only: <= 2^-10 |q||c|).  Fewer products
+  // make the GEMM cheaper and the guard's error bound wider; the probes stay exact either way.
+  int products = tc_products_ref();
+  if (products == 0) {
+    // adopt the verdict on the last batch of this handle, if it has arrived
+    if (res.tc_redo_pending && cudaEventQuery(res.tc_redo_event) == cudaSuccess) {
+      res.tc_redo_pending = false;
+      if (uint64_t(res.pinned[8]) * 256 > res.tc_redo_queries && res.tc_products < 3) { res.tc_products++; }
+    }
+    products = res.tc_products;
   }
+  const float eps_rel = float(dim_ext + 8) * 2.4e-7f + 3.1e-5f +
+                        (products == 1 ? 9.8e-4f : (products == 2 ? 4.9e-4f : 0.0f));
+  auto launch = [&](auto kernel) {
+    // every instantiation needs its shared-memory limit raised once
+    static thread_local const void* configured[8] = {};
+    bool seen = false;
+    for (const void* c : configured) { seen = seen || c == reinterpret_cast<const void*>(kernel); }
+    if (!seen) {
+      CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kSmemBytes)));
+      for (const void*& c : configured) {
+        if (c == nullptr) {
+          c = reinterpret_cast<const void*>(kernel);
+          break;
+        }
+      }
+    }
+    kernel<<<grid, kThreads, kSmemBytes, stream>>>(m_a_hi, m_a_lo, m_b_hi, m_b_lo, p);
+  };
   if (four_by_4) {
-    coarse_tc_kernel<2, 4><<<grid, kThreads, kSmemBytes, stream>>>(m_a_hi, m_a_lo, m_b_hi,
-                                                                                   m_b_lo, p);
+    if (products == 1) {
+      launch(coarse_tc_kernel<2, 4, 1>);
+    } else if (products == 2) {
+      launch(coarse_tc_kernel<2, 4, 2>);
+    } else {
+      launch(coarse_tc_kernel<2, 4, 3>);
+    }
   } else {
-    coarse_tc_kernel<1, 8><<<grid, kThreads, kSmemBytes, stream>>>(m_a_hi, m_a_lo, m_b_hi,
-                                                                                   m_b_lo, p);
+    if (products == 1) {
+      launch(coarse_tc_kernel<1, 8, 1>);
+    } else if (products == 2) {
+      launch(coarse_tc_kernel<1, 8, 2>);
+    } else {
+      launch(coarse_tc_kernel<1, 8, 3>);
+    }
   }
   CUDA_TRY(cudaGetLastError());
 
@@ -1107,12 +1151,12 @@ void select_clusters_tc(raft::resources& res, const float* centers, const float*
   if (n_tiles * 2 <= kFinMaxHalfTiles && C <= kFinMaxC && C * 4 <= n_tiles * 2 && fin_small_smem <= 48 * 1024) {
     if (kph == 16) {
       coarse_finish_small_kernel<16><<<n_queries, 256, fin_small_smem, stream>>>(
-        cand_key, cand_bnd, n_cand, centers, fq, n_lists, dim_ext, alpha, n_probes, C, cmax, probes, scores_out,
-        redo_list, words + 2);
+        cand_key, cand_bnd, n_cand, centers, fq, n_lists, dim_ext, alpha, n_probes, C, cmax, eps_rel, probes,
+        scores_out, redo_list, words + 2);
     } else {
       coarse_finish_small_kernel<8><<<n_queries, 256, fin_small_smem, stream>>>(
-        cand_key, cand_bnd, n_cand, centers, fq, n_lists, dim_ext, alpha, n_probes, C, cmax, probes, scores_out,
-        redo_list, words + 2);
+        cand_key, cand_bnd, n_cand, centers, fq, n_lists, dim_ext, alpha, n_probes, C, cmax, eps_rel, probes,
+        scores_out, redo_list, words + 2);
     }
   } else {
     if (fin_smem > fin_configured) {
@@ -1122,7 +1166,8 @@ void select_clusters_tc(raft::resources& res, const float* centers, const float*
     }
     coarse_finish_kernel<<<n_queries, 256, fin_smem, stream>>>(cand_key, cand_bnd, n_cand, kph, centers, fq,
                                                                n_lists, dim_ext, alpha, n_probes, C, cap,
-                                                               cmax, probes, scores_out, redo_list, words + 2);
+                                                               cmax, eps_rel, probes, scores_out, redo_list,
+                                                               words + 2);
   }
   uint32_t cap_fb = 2;
   while (cap_fb < n_probes) { cap_fb <<= 1; }
@@ -1132,6 +1177,14 @@ void select_clusters_tc(raft::resources& res, const float* centers, const float*
                                                        scores_out, words + 1);
   CUDA_TRY(cudaGetLastError());
   res.launches += 4;
+  if (tc_products_ref() == 0 && !res.tc_redo_pending && res.tc_products < 3) {
+    // how many queries this batch redid exactly: read back without waiting, looked at before a later batch
+    if (!res.tc_redo_event) { CUDA_TRY(cudaEventCreateWithFlags(&res.tc_redo_event, cudaEventDisableTiming)); }
+    CUDA_TRY(cudaMemcpyAsync(res.pinned + 8, words + 1, 4, cudaMemcpyDeviceToHost, stream));
+    CUDA_TRY(cudaEventRecord(res.tc_redo_event, stream));
+    res.tc_redo_queries = n_queries;
+    res.tc_redo_pending = true;
+  }
 }
 
 // Reads back the error word and the number of queries redone exactly by the last call that used

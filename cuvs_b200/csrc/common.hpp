@@ -127,6 +127,14 @@ struct resources {
   void stats_mark(stage_events& ev, int i);
   void stats_resolve();
 
+  // Tensor-core coarse stage: products of the TF32 split per K step used by this handle (starts at
+  // two, raised when a finished batch had to redo more than 1/256 of its queries exactly); the count
+  // of the last batch arrives in pinned[8] once tc_redo_event has completed.
+  int tc_products            = 2;
+  cudaEvent_t tc_redo_event  = nullptr;
+  bool tc_redo_pending       = false;
+  uint32_t tc_redo_queries   = 0;
+
   resources();
   ~resources();
   resources(const resources&)            = delete;

@@ -18,6 +18,7 @@ resources::~resources()
   for (auto& ev : pending) {
     for (auto& e : ev.e) { cudaEventDestroy(e); }
   }
+  if (tc_redo_event) { cudaEventDestroy(tc_redo_event); }
   if (d_stats) { cudaFree(d_stats); }
   if (pinned) { cudaFreeHost(pinned); }
 }

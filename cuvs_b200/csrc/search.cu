@@ -766,7 +766,18 @@ void search_any(raft::resources& res, const search_params& params, const index<i
   }
 }
 
-void set_coarse_mode(int mode) { coarse_mode_ref() = mode; }
+void set_coarse_mode(int mode)
+{
+  // 0 auto, 1 exact SIMT path, 2 tensor-core path; 11 / 12 / 13: tensor-core path with 1 / 2 / 3
+  // products of the TF32 split
+  if (mode >= 11 && mode <= 13) {
+    set_coarse_tc_products(mode - 10);
+    mode = 2;
+  } else {
+    set_coarse_tc_products(0);  // every handle chooses (and adapts) the number of products itself
+  }
+  coarse_mode_ref() = mode;
+}
 void set_scan_codebook_home(int home) { scan_codebook_home() = home; }
 
 void select_probes_any(raft::resources& res, const index<int64_t>& idx, const void* queries,

@@ -43,6 +43,8 @@ void coarse_only(raft::resources& res, const index<int64_t>& idx, const void* qu
                  uint32_t n_queries, uint32_t n_probes, int mode, uint32_t* probes, float* scores,
                  uint32_t* status);
 
+// products of the TF32 split the tensor-core coarse GEMM issues per K step (1, 2 or 3)
+void set_coarse_tc_products(int products);
 void set_coarse_mode(int mode);  // process-wide override used by tests: 0 auto, 1 SIMT, 2 tensor core
 // process-wide override used by tests: 0 = the per-subspace codebook goes to tensor memory where it
 // fits, 1 = never (shared memory, else global memory)

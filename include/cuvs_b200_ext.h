@@ -42,7 +42,9 @@ CUVS_EXPORT cuvsError_t cuvsB200CoarseSelect(cuvsResources_t res, void* index /*
                                              DLManagedTensor* queries, DLManagedTensor* probes,
                                              DLManagedTensor* scores, int mode, uint32_t* status);
 /* No counterpart in the reference: force the probe-selection path used by cuvsIvfPqSearch in this
- * process (0 = automatic, 1 = exact SIMT path, 2 = tensor-core path where it applies). */
+ * process (0 = automatic, 1 = exact SIMT path, 2 = tensor-core path where it applies; 11, 12, 13 =
+ * tensor-core path with exactly 1, 2 or 3 products of the TF32 operand split per K step instead
+ * of the per-handle adaptive choice). */
 CUVS_EXPORT cuvsError_t cuvsB200SetCoarseMode(int mode);
 /* No counterpart in the reference: where the fine-search kernel of cuvsIvfPqSearch keeps a
  * per-subspace PQ codebook in this process: 0 = tensor memory where it fits (the default),

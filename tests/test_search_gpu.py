@@ -345,6 +345,26 @@ def test_search_is_identical_under_both_coarse_paths(ivf, many_lists):
     assert (i1 == i2).all() and (d1.view(np.uint32) == d2.view(np.uint32)).all()
 
 
+@pytest.mark.parametrize("products", [1, 2, 3])
+def test_coarse_tensor_core_products_all_give_the_exact_probes(ivf, many_lists, products):
+    """The tensor-core coarse GEMM may issue 1, 2 or 3 products of the TF32 operand split per K step
+    (a handle starts with 2 and raises the number if too many queries need the exact redo); the guard
+    widens its error bound accordingly, so the probes and their scores equal the exact path's."""
+    from cuvs_b200 import _lib as L
+    x, g = many_lists
+    q = make_mixture(700, 64, 512, 0.25, seed=81)
+    lib = L.load()
+    try:
+        p1, s1, _ = coarse_select(g, q, 20, 1)
+        L.check(lib.cuvsB200SetCoarseMode(10 + products))
+        p2, s2, st = coarse_select(g, q, 20, 2)
+    finally:
+        L.check(lib.cuvsB200SetCoarseMode(0))
+    assert st[0] == 0
+    assert (p1 == p2).all() and (s1.view(np.uint32) == s2.view(np.uint32)).all()
+    assert st[1] <= len(q) // 20          # the exact redo stays the exception
+
+
 @pytest.mark.parametrize("k,lut,internal", [(129, "f32", "f32"), (200, "f16", "f32"), (513, "fp8", "f16")])
 def test_search_parity_large_k_store_all_path(ivf, oracle_mod, small_l2, k, lut, internal):
     """k > 128 switches to the mode where the scan stores every score and a selection follows
