@@ -1,4 +1,4 @@
-// Coarse stage on the tensor cores: queries x list-centers as a 3xTF32 GEMM (tcgen05.mma, TMEM
+// Coarse stage on the tensor cores: queries x list-centers as a TF32-split GEMM (tcgen05.mma, TMEM
 // accumulators, operands staged by TMA), fused with candidate selection, followed by an exact
 // rescoring so that the chosen probes are bit-identical to the exact SIMT path of coarse.cu.
 //
@@ -9,24 +9,27 @@
 // Pipeline per batch
 //   1. split_tf32_kernel: every fp32 operand x is written as hi = tf32(x), lo = tf32(x - hi)
 //      (centers once per index, queries per batch).
-//   2. coarse_tc_kernel: CTA tile = 128 queries x 256 lists, K in blocks of 16 floats (one
-//      64-byte swizzle atom), four pipeline stages.  Per K block three products accumulate into TMEM:
-//      hi*hi + hi*lo + lo*hi.  Warp 0 issues TMA loads (no multicast), warp 1 issues the MMAs,
-//      eight epilogue warps read the accumulator with tcgen05.ld (thread = query row) and keep,
-//      per row and per 128-list half tile, the largest dot products in registers, as packed
+//   2. coarse_tc_kernel: one persistent CTA per SM walks the output tiles (128 queries x 256
+//      lists); K in blocks of 16 floats (one 64-byte swizzle atom), four pipeline stages.  Per K
+//      step one, two or three products of the split accumulate into TMEM: hi*hi (+ lo*hi (+ hi*lo)).
+//      Warp 0 issues TMA loads (no multicast), warp 1 issues the MMAs, sixteen epilogue warps read
+//      the accumulator with tcgen05.ld (thread = query row, warp = 32 rows x 64 columns) and keep,
+//      per row and per 64-list unit, the eight largest dot products in registers, as packed
 //      32-bit keys (order-preserving image of the value, low 7 bits replaced by the column tag):
-//      insertion is a branch-free chain of integer max/min.  Two variants: four independent
-//      top-4 chains (column % 4) or one top-8 chain; the last key of a chain bounds everything the
+//      insertion is a branch-free chain of integer max/min.  Two variants: two independent
+//      top-4 chains (column % 2) or one top-8 chain; the last key of a chain bounds everything the
 //      chain dropped.  Two TMEM accumulators let the epilogue of one tile overlap the MMAs of the
 //      next.
 //      Every mbarrier wait is bounded; on a time-out the kernel raises an error word, lets its
 //      in-flight copies land, frees its TMEM and returns.
-//   3. coarse_finish_kernel (one block per query): the C = n_probes + margin best candidates by
-//      tensor-core score are rescored with the defining fp32 FMA chain, sorted by (score, id), and
-//      the first n_probes become the probes.  A guard proves the selection exact: every list that
-//      was not rescored has a tensor-core score <= T, and T + eps < exact score of the last probe,
-//      eps bounding |tensor-core - exact|.  A query whose guard fails is flagged.
-//   4. coarse_fallback_kernel: flagged queries (rare) are redone exactly over all lists.
+//   3. finish kernel (one block per query): candidates at or above a threshold (the C-th largest
+//      half-tile maximum, C = n_probes + margin; or, for large C, the C best keys by radix select)
+//      are rescored with the defining fp32 FMA chain, sorted by (score, id), and the first
+//      n_probes become the probes.  A guard proves the selection exact: every list that was not
+//      rescored has a tensor-core score <= T, and T + eps < exact score of the last probe, eps
+//      bounding |tensor-core - exact| for the number of products in use.  A query whose guard
+//      fails is queued.
+//   4. coarse_fallback_kernel: queued queries (rare) are redone exactly over all lists.
 #include "search_internal.hpp"
 #include "topk.cuh"
 
