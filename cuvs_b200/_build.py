@@ -25,7 +25,8 @@ NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-std=c++17", "-O3",
 UNITS = [("resources.cu", "resources.o", []), ("index.cu", "index.o", []),
          ("coarse.cu", "coarse.o", []), ("coarse_tc.cu", "coarse_tc.o", []), ("search.cu", "search.o", []),
          ("build.cu", "build.o", []), ("c_api.cu", "c_api.o", []),
-         ("no_alloc.cu", "no_alloc.o", []), ("refine.cu", "refine.o", [])]
+         ("no_alloc.cu", "no_alloc.o", []), ("refine.cu", "refine.o", []),
+         ("dynamic_batching.cu", "dynamic_batching.o", [])]
 UNITS += [("scan_inst.cu", f"scan_{b}.o", [f"-DPQ_BITS={b}"]) for b in (4, 5, 6, 7, 8)]
 
 

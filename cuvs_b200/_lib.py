@@ -61,6 +61,15 @@ class FilterStruct(C.Structure):
     _fields_ = [("addr", C.c_size_t), ("type", C.c_int)]
 
 
+class DynamicBatchingIndexParamsStruct(C.Structure):
+    _fields_ = [("k", C.c_int64), ("max_batch_size", C.c_int64), ("n_queues", C.c_size_t),
+                ("conservative_dispatch", C.c_bool)]
+
+
+class DynamicBatchingIndexStruct(C.Structure):
+    _fields_ = [("addr", C.c_size_t)]
+
+
 class IndexStruct(C.Structure):
     _fields_ = [("addr", C.c_size_t), ("dtype", DLDataType)]
 
@@ -133,6 +142,14 @@ SIGNATURES = {
     "cuvsB200StatsEnable": [C.c_size_t, C.c_bool],
     "cuvsB200StatsGet": [C.c_size_t, _P(SearchStats), C.c_bool],
     "cuvsIvfPqPredictNoAlloc": [C.c_size_t, _P(IndexStruct), _P(DLManagedTensor), _P(DLManagedTensor)],
+    "cuvsDynamicBatchingIndexParamsCreate": [_P(_P(DynamicBatchingIndexParamsStruct))],
+    "cuvsDynamicBatchingIndexParamsDestroy": [_P(DynamicBatchingIndexParamsStruct)],
+    "cuvsDynamicBatchingIndexCreate": [C.c_size_t, _P(DynamicBatchingIndexParamsStruct), _P(IndexStruct),
+                                       _P(SearchParamsStruct), _P(_P(DynamicBatchingIndexStruct))],
+    "cuvsDynamicBatchingIndexDestroy": [_P(DynamicBatchingIndexStruct)],
+    "cuvsDynamicBatchingSearch": [C.c_size_t, _P(DynamicBatchingIndexStruct), C.c_double,
+                                  _P(DLManagedTensor), _P(DLManagedTensor), _P(DLManagedTensor)],
+    "cuvsDynamicBatchingStats": [_P(DynamicBatchingIndexStruct), _P(C.c_uint64), _P(C.c_uint64)],
     "cuvsRefine": [C.c_size_t, _P(DLManagedTensor), _P(DLManagedTensor), _P(DLManagedTensor), C.c_int,
                    _P(DLManagedTensor), _P(DLManagedTensor)],
     "cuvsIvfPqTransform": [C.c_size_t, _P(IndexStruct), _P(DLManagedTensor), _P(DLManagedTensor),

@@ -4,10 +4,12 @@
 // runs inside translate_exceptions (c/src/core/exceptions.hpp:17-33), tensors are validated the
 // way from_dlpack does (c/src/core/detail/interop.hpp:75-139) and dispatched on their dtype.
 #include "../../include/cuvs_b200_ext.h"
+#include "../../include/cuvs_dynamic_batching.h"
 #include "../../include/cuvs_ivf_pq.h"
 #include "../../include/cuvs_mg_ivf_pq.h"
 #include "../../include/cuvs_refine.h"
 
+#include "dynamic_batching.hpp"
 #include "ivf_pq.hpp"
 #include "search_internal.hpp"
 
@@ -711,6 +713,87 @@ extern "C" cuvsError_t cuvsB200SetScanCodebookHome(int home)
   return translate_exceptions([=] {
     CUVS_EXPECTS(home == 0 || home == 1, "home must be 0 or 1");
     ivf_pq::set_scan_codebook_home(home);
+  });
+}
+
+// ------------------------------------------------------------------------------------------------
+// dynamic batching (C++ only in the reference: cpp/include/cuvs/neighbors/dynamic_batching.hpp)
+// ------------------------------------------------------------------------------------------------
+namespace db = cuvs::neighbors::dynamic_batching;
+
+extern "C" cuvsError_t cuvsDynamicBatchingIndexParamsCreate(cuvsDynamicBatchingIndexParams_t* params)
+{
+  return translate_exceptions([=] {
+    CUVS_EXPECTS(params != nullptr, "null argument");
+    *params = new cuvsDynamicBatchingIndexParams{10, 100, 3, false};
+  });
+}
+extern "C" cuvsError_t cuvsDynamicBatchingIndexParamsDestroy(cuvsDynamicBatchingIndexParams_t params)
+{
+  return translate_exceptions([=] { delete params; });
+}
+extern "C" cuvsError_t cuvsDynamicBatchingIndexCreate(cuvsResources_t res, cuvsDynamicBatchingIndexParams_t params,
+                                                      cuvsIvfPqIndex_t upstream,
+                                                      cuvsIvfPqSearchParams_t upstream_params,
+                                                      cuvsDynamicBatchingIndex_t* index)
+{
+  return translate_exceptions([=] {
+    CUVS_EXPECTS(params && upstream_params && index, "null argument");
+    auto* ix = index_of(upstream);
+    CUVS_EXPECTS(params->k > 0 && params->k <= ix->size(), "k must be within [1, index size]");
+    db::index_params ip;
+    ip.k                     = params->k;
+    ip.max_batch_size        = params->max_batch_size;
+    ip.n_queues              = params->n_queues;
+    ip.conservative_dispatch = params->conservative_dispatch;
+    ivf_pq::search_params sp;
+    sp.n_probes                 = upstream_params->n_probes;
+    sp.lut_dtype                = upstream_params->lut_dtype;
+    sp.internal_distance_dtype  = upstream_params->internal_distance_dtype;
+    sp.preferred_shmem_carveout = upstream_params->preferred_shmem_carveout;
+    sp.coarse_search_dtype      = upstream_params->coarse_search_dtype;
+    sp.max_internal_batch_size  = upstream_params->max_internal_batch_size;
+    auto* obj = new db::index<float, int64_t>(*res_of(res), ip, *ix, sp);
+    *index    = new cuvsDynamicBatchingIndex{reinterpret_cast<uintptr_t>(obj)};
+  });
+}
+extern "C" cuvsError_t cuvsDynamicBatchingIndexDestroy(cuvsDynamicBatchingIndex_t index)
+{
+  return translate_exceptions([=] {
+    if (index) {
+      delete reinterpret_cast<db::index<float, int64_t>*>(index->addr);
+      delete index;
+    }
+  });
+}
+extern "C" cuvsError_t cuvsDynamicBatchingSearch(cuvsResources_t res, cuvsDynamicBatchingIndex_t index,
+                                                 double dispatch_timeout_ms, DLManagedTensor* queries,
+                                                 DLManagedTensor* neighbors, DLManagedTensor* distances)
+{
+  return translate_exceptions([=] {
+    CUVS_EXPECTS(index && index->addr && queries && neighbors && distances, "null argument");
+    auto* obj = reinterpret_cast<db::index<float, int64_t>*>(index->addr);
+    auto* q   = static_cast<const float*>(checked_data(queries, kDLFloat, 32, 2, true, "queries"));
+    auto* nb  = static_cast<int64_t*>(checked_data(neighbors, kDLInt, 64, 2, true, "neighbors"));
+    auto* ds  = static_cast<float*>(checked_data(distances, kDLFloat, 32, 2, true, "distances"));
+    const int64_t n = queries->dl_tensor.shape[0];
+    CUVS_EXPECTS(neighbors->dl_tensor.shape[0] == n && distances->dl_tensor.shape[0] == n,
+                 "Number of rows in output neighbors and distances matrices must equal the number "
+                 "of queries.");
+    CUVS_EXPECTS(neighbors->dl_tensor.shape[1] == distances->dl_tensor.shape[1],
+                 "Number of columns in output neighbors and distances matrices must equal k");
+    db::search_params sp;
+    sp.dispatch_timeout_ms = dispatch_timeout_ms;
+    db::search_checked(*res_of(res), sp, *obj, q, uint32_t(n), uint32_t(queries->dl_tensor.shape[1]),
+                       uint32_t(neighbors->dl_tensor.shape[1]), nb, ds);
+  });
+}
+extern "C" cuvsError_t cuvsDynamicBatchingStats(cuvsDynamicBatchingIndex_t index, uint64_t* n_batches,
+                                                uint64_t* n_rows)
+{
+  return translate_exceptions([=] {
+    CUVS_EXPECTS(index && index->addr && n_batches && n_rows, "null argument");
+    db::stats(*reinterpret_cast<db::index<float, int64_t>*>(index->addr), n_batches, n_rows);
   });
 }
 
