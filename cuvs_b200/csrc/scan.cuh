@@ -26,6 +26,8 @@
 
 #include <cuda_fp16.h>
 
+#include <type_traits>
+
 namespace cuvs_b200 {
 
 struct scan_params {
@@ -396,54 +398,87 @@ __device__ __forceinline__ void build_lut_tmem(uint32_t tmem_lane_a, uint32_t ba
   const uint32_t bd_step    = j_stride * LEN * kBaseB;
   const uint32_t out_step   = j_stride * kBook * kElem;
 
-  for (uint32_t i = 0; i < n_iter; i += kPerLoad, taddr += 16u) {
+  // one subspace: sub-iteration T of the 16 columns in `c`
+  auto entry = [&](const uint32_t (&c)[16], auto tc) {
+    constexpr int T = decltype(tc)::value;
+    uint64_t s0 = 0ull, s1 = 0ull;  // entries (b, b+1) and (b+2, b+3), each (+0.0f, +0.0f)
+    uint64_t x[LEN], y[LEN];
+    if constexpr (IsIP) {
+#pragma unroll
+      for (int kk = 0; kk < LEN; kk++) { lds_2xb64(bd + uint32_t(kk) * 16u, x[kk], y[kk]); }
+    } else if constexpr (LEN == 1) {
+      x[0] = lds_b64(bd);
+    } else {
+#pragma unroll
+      for (int kk = 0; kk < LEN; kk += 2) { lds_2xb64(bd + uint32_t(kk) * 8u, x[kk], x[kk + 1]); }
+    }
+#pragma unroll
+    for (int kk = 0; kk < LEN; kk++) {
+      const uint64_t c0 = pack_b32x2(c[T * kCols + kk * 4 + 0], c[T * kCols + kk * 4 + 1]);
+      const uint64_t c1 = pack_b32x2(c[T * kCols + kk * 4 + 2], c[T * kCols + kk * 4 + 3]);
+      if constexpr (!IsIP) {  // x = (d, d)
+        const uint64_t e0 = sub2(x[kk], c0);
+        const uint64_t e1 = sub2(x[kk], c1);
+        s0                = fma2(e0, e0, s0);
+        s1                = fma2(e1, e1, s1);
+      } else {  // x = (-q, -q), y = (q*c, q*c)
+        s0 = sub2(s0, y[kk]);
+        s1 = sub2(s1, y[kk]);
+        s0 = fma2(x[kk], c0, s0);
+        s1 = fma2(x[kk], c1, s1);
+      }
+    }
+    if constexpr (LutKind == LUT_F32) {
+      sts_b128(out, s0, s1);
+    } else if constexpr (LutKind == LUT_F16) {
+      const __half2 h0 = __floats2half2_rn(lo2(s0), hi2(s0));
+      const __half2 h1 = __floats2half2_rn(lo2(s1), hi2(s1));
+      sts_2xb32(out, *reinterpret_cast<const uint32_t*>(&h0), *reinterpret_cast<const uint32_t*>(&h1));
+    } else {
+      sts_b32(out, uint32_t(fp8_encode<IsIP>(lo2(s0))) | (uint32_t(fp8_encode<IsIP>(hi2(s0))) << 8) |
+                     (uint32_t(fp8_encode<IsIP>(lo2(s1))) << 16) | (uint32_t(fp8_encode<IsIP>(hi2(s1))) << 24));
+    }
+  };
+  auto advance = [&]() {
+    j += j_stride;
+    bd += bd_step;
+    out += out_step;
+  };
+  // Whole loads first, without per-subspace checks where the warp shares its subspace; then the rest.
+  const uint32_t n_whole = kWarpSameJ ? (n_iter / kPerLoad) * kPerLoad : 0u;
+  uint32_t i             = 0;
+  for (; i < n_whole; i += kPerLoad, taddr += 16u) {
+    uint32_t c[16];
+    tmem_ld<16>(taddr, c);
+    tmem_wait_ld();
+    entry(c, std::integral_constant<int, 0>{});
+    advance();
+    if constexpr (kPerLoad >= 2) {
+      entry(c, std::integral_constant<int, 1>{});
+      advance();
+    }
+    if constexpr (kPerLoad >= 4) {
+      entry(c, std::integral_constant<int, 2>{});
+      advance();
+      entry(c, std::integral_constant<int, 3>{});
+      advance();
+    }
+  }
+  for (; i < n_iter; i += kPerLoad, taddr += 16u) {
     uint32_t c[16];
     tmem_ld<16>(taddr, c);  // may run past this thread's blocks into other columns of the allocation
     tmem_wait_ld();
-#pragma unroll
-    for (int t = 0; t < kPerLoad; t++) {
-      if (i + uint32_t(t) < n_iter && (kWarpSameJ || j < pq_dim)) {
-        uint64_t s0 = 0ull, s1 = 0ull;  // entries (b, b+1) and (b+2, b+3), each (+0.0f, +0.0f)
-        uint64_t x[LEN], y[LEN];
-        if constexpr (IsIP) {
-#pragma unroll
-          for (int kk = 0; kk < LEN; kk++) { lds_2xb64(bd + uint32_t(kk) * 16u, x[kk], y[kk]); }
-        } else if constexpr (LEN == 1) {
-          x[0] = lds_b64(bd);
-        } else {
-#pragma unroll
-          for (int kk = 0; kk < LEN; kk += 2) { lds_2xb64(bd + uint32_t(kk) * 8u, x[kk], x[kk + 1]); }
-        }
-#pragma unroll
-        for (int kk = 0; kk < LEN; kk++) {
-          const uint64_t c0 = pack_b32x2(c[t * kCols + kk * 4 + 0], c[t * kCols + kk * 4 + 1]);
-          const uint64_t c1 = pack_b32x2(c[t * kCols + kk * 4 + 2], c[t * kCols + kk * 4 + 3]);
-          if constexpr (!IsIP) {  // x = (d, d)
-            const uint64_t e0 = sub2(x[kk], c0);
-            const uint64_t e1 = sub2(x[kk], c1);
-            s0                = fma2(e0, e0, s0);
-            s1                = fma2(e1, e1, s1);
-          } else {  // x = (-q, -q), y = (q*c, q*c)
-            s0 = sub2(s0, y[kk]);
-            s1 = sub2(s1, y[kk]);
-            s0 = fma2(x[kk], c0, s0);
-            s1 = fma2(x[kk], c1, s1);
-          }
-        }
-        if constexpr (LutKind == LUT_F32) {
-          sts_b128(out, s0, s1);
-        } else if constexpr (LutKind == LUT_F16) {
-          const __half2 h0 = __floats2half2_rn(lo2(s0), hi2(s0));
-          const __half2 h1 = __floats2half2_rn(lo2(s1), hi2(s1));
-          sts_2xb32(out, *reinterpret_cast<const uint32_t*>(&h0), *reinterpret_cast<const uint32_t*>(&h1));
-        } else {
-          sts_b32(out, uint32_t(fp8_encode<IsIP>(lo2(s0))) | (uint32_t(fp8_encode<IsIP>(hi2(s0))) << 8) |
-                         (uint32_t(fp8_encode<IsIP>(lo2(s1))) << 16) | (uint32_t(fp8_encode<IsIP>(hi2(s1))) << 24));
-        }
-      }
-      j += j_stride;
-      bd += bd_step;
-      out += out_step;
+    if (i < n_iter && (kWarpSameJ || j < pq_dim)) { entry(c, std::integral_constant<int, 0>{}); }
+    advance();
+    if constexpr (kPerLoad >= 2) {
+      if (i + 1u < n_iter && (kWarpSameJ || j < pq_dim)) { entry(c, std::integral_constant<int, 1>{}); }
+      advance();
+    }
+    if constexpr (kPerLoad >= 4) {
+      if (i + 2u < n_iter && (kWarpSameJ || j < pq_dim)) { entry(c, std::integral_constant<int, 2>{}); }
+      advance();
+      if (i + 3u < n_iter && (kWarpSameJ || j < pq_dim)) { entry(c, std::integral_constant<int, 3>{}); }
+      advance();
     }
   }
 }
