@@ -57,34 +57,51 @@ __global__ void refine_kernel(const T* __restrict__ dataset, int64_t n_rows, uin
     float my_score = INFINITY;
     bool my_valid  = false;
     const uint32_t n_here = min(32u, n_cand - c0);
-    for (uint32_t j = 0; j < n_here; j++) {
-      const int64_t id = cand[c0 + j];
-      if (id < 0 || id >= n_rows) { continue; }  // uniform across the warp
-      const T* x = dataset + size_t(id) * dim;
-      float acc = 0.0f, xn = 0.0f;
+    // four candidates at a time, so that their rows are in flight together (each candidate's own
+    // summation order is unchanged)
+    for (uint32_t j = 0; j < n_here; j += 4) {
+      const T* x[4];
+      bool ok[4];  // uniform across the warp
+      float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f}, xn[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+      for (int u = 0; u < 4; u++) {
+        const int64_t id = j + u < n_here ? cand[c0 + j + u] : int64_t(-1);
+        ok[u]            = id >= 0 && id < n_rows;
+        x[u]             = dataset + size_t(ok[u] ? id : 0) * dim;
+      }
       for (uint32_t d = lane; d < dim; d += 32) {
-        const float xv = ld_as_float<T>(x, d);
-        if (mode == REF_IP) {
-          acc = __fmaf_rn(sq[d], xv, acc);
-        } else if (mode == REF_COS) {
-          acc = __fmaf_rn(sq[d], xv, acc);
-          xn  = __fmaf_rn(xv, xv, xn);
-        } else {
-          const float t = sq[d] - xv;
-          acc           = __fmaf_rn(t, t, acc);
+        const float qv = sq[d];
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+          if (!ok[u]) { continue; }
+          const float xv = ld_as_float<T>(x[u], d);
+          if (mode == REF_IP) {
+            acc[u] = __fmaf_rn(qv, xv, acc[u]);
+          } else if (mode == REF_COS) {
+            acc[u] = __fmaf_rn(qv, xv, acc[u]);
+            xn[u]  = __fmaf_rn(xv, xv, xn[u]);
+          } else {
+            const float t = qv - xv;
+            acc[u]        = __fmaf_rn(t, t, acc[u]);
+          }
         }
       }
 #pragma unroll
-      for (int o = 16; o > 0; o >>= 1) {
-        acc += __shfl_xor_sync(kFullMask, acc, o);
-        xn += __shfl_xor_sync(kFullMask, xn, o);
-      }
-      float score = acc;                       // smaller is better
-      if (mode == REF_IP) { score = -acc; }
-      if (mode == REF_COS) { score = 1.0f - acc / (sqrtf(qn) * sqrtf(xn) + 1e-30f); }
-      if (lane == j) {
-        my_score = score;
-        my_valid = true;
+      for (int u = 0; u < 4; u++) {
+        if (!ok[u]) { continue; }
+        float a = acc[u], b = xn[u];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+          a += __shfl_xor_sync(kFullMask, a, o);
+          b += __shfl_xor_sync(kFullMask, b, o);
+        }
+        float score = a;                       // smaller is better
+        if (mode == REF_IP) { score = -a; }
+        if (mode == REF_COS) { score = 1.0f - a / (sqrtf(qn) * sqrtf(b) + 1e-30f); }
+        if (lane == j + uint32_t(u)) {
+          my_score = score;
+          my_valid = true;
+        }
       }
     }
     queue.offer(make_key(my_score, c0 + lane), my_valid);

@@ -352,6 +352,7 @@ __device__ __forceinline__ void fill_codebook_tmem(uint32_t tmem_lane_a, const f
   constexpr uint32_t kJPerM = 128u / kUPJ;
   const uint32_t u          = lane128 % kUPJ;
   const uint32_t ipt        = tmem_iters_per_thread(pq_dim, kJPerM, m_stride);
+#pragma unroll 4
   for (uint32_t m = 0; m < ipt * m_stride; m++) {
     const uint32_t j     = lane128 / kUPJ + m * kJPerM;
     const uint32_t block = (m % m_stride) * ipt + m / m_stride;
@@ -658,15 +659,16 @@ __global__ void __launch_bounds__(1024, 1) scan_kernel(const scan_params p)
   warp_topk<(KPL > 0 ? KPL : 1)> queue;
 
   // Work items are claimed four at a time (one atomic per four pairs keeps the single counter off
-  // the critical path), one claim ahead so that the atomic's latency is hidden.
-  constexpr uint32_t kClaim = 4;
+  // the critical path), one claim ahead so that the atomic's latency is hidden; a short work list
+  // is dealt pair by pair so that it spreads over all groups.
   const uint32_t n_work = __ldg(p.n_work);
-  if (gt == 0) { s_item[0] = atomicAdd(p.work_counter, kClaim); }
+  const uint32_t claim  = n_work >= 8u * gridDim.x * p.n_groups ? 4u : 1u;
+  if (gt == 0) { s_item[0] = atomicAdd(p.work_counter, claim); }
   for (uint32_t it = 0;; it++) {
     group_bar(bar_id, gthreads);
-    const uint32_t w = s_item[(it / kClaim) & 1u] + (it % kClaim);
+    const uint32_t w = s_item[(it / claim) & 1u] + (it % claim);
     if (w >= n_work) { break; }
-    if (gt == 0 && (it % kClaim) == 0) { s_item[((it / kClaim) + 1u) & 1u] = atomicAdd(p.work_counter, kClaim); }
+    if (gt == 0 && (it % claim) == 0) { s_item[((it / claim) + 1u) & 1u] = atomicAdd(p.work_counter, claim); }
 
     const uint4 d0       = __ldg(p.work + 2 * size_t(w));
     const uint4 d1       = __ldg(p.work + 2 * size_t(w) + 1);

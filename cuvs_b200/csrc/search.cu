@@ -246,6 +246,51 @@ __global__ void scatter_pairs_kernel(const uint32_t* __restrict__ probes,
   work[2 * size_t(pos) + 1] = make_uint4(pi > 0 ? chunk_index[i - 1] : 0u, uint32_t(ro), uint32_t(ro >> 32), 0u);
 }
 
+// Small batches: sample offsets, work descriptors (in arrival order: no sort by list), empty result
+// slots and the per-query bounds in one launch.  One warp per query; `n_work` counts the non-empty
+// pairs and must be zero on entry.
+__global__ void small_batch_pairs_kernel(const uint32_t* __restrict__ probes,
+                                         const uint32_t* __restrict__ list_sizes,
+                                         const uint64_t* __restrict__ row_off, uint32_t n_queries,
+                                         uint32_t n_probes, uint32_t* __restrict__ chunk_index,
+                                         uint4* __restrict__ work, uint32_t* __restrict__ n_work,
+                                         uint32_t* __restrict__ query_kth, uint64_t* __restrict__ out_keys,
+                                         uint32_t k)
+{
+  const uint32_t q    = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const uint32_t lane = threadIdx.x & 31;
+  if (q >= n_queries) { return; }
+  uint32_t carry = 0;
+  for (uint32_t p0 = 0; p0 < n_probes; p0 += 32) {
+    const uint32_t p = p0 + lane;
+    uint32_t label = 0, size = 0;
+    if (p < n_probes) {
+      label = probes[size_t(q) * n_probes + p];
+      size  = list_sizes[label];
+    }
+    uint32_t v = size;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      uint32_t t = __shfl_up_sync(kFullMask, v, d);
+      if (lane >= uint32_t(d)) { v += t; }
+    }
+    if (p < n_probes) {
+      const uint32_t pair = q * n_probes + p;
+      chunk_index[pair]   = carry + v;
+      if (size > 0) {
+        const uint32_t pos = atomicAdd(n_work, 1u);
+        const uint64_t ro  = row_off[label];
+        work[2 * size_t(pos)]     = make_uint4(pair, q, label, size);
+        work[2 * size_t(pos) + 1] = make_uint4(carry + v - size, uint32_t(ro), uint32_t(ro >> 32), 0u);
+      } else if (out_keys) {
+        for (uint32_t t = 0; t < k; t++) { out_keys[size_t(pair) * k + t] = kEmptyKey; }
+      }
+    }
+    carry += __shfl_sync(kFullMask, v, 31);
+  }
+  if (lane == 0) { query_kth[q] = kEmptyScore; }
+}
+
 __global__ void fill_u32_kernel(uint32_t* p, size_t n, uint32_t v)
 {
   size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x;
@@ -657,24 +702,35 @@ void search_any(raft::resources& res, const search_params& params, const index<i
     }
 
     if (stats) { res.stats_mark(ev, 2); }
-    // 3. sample offsets + counting sort of pairs by list
-    CUDA_TRY(cudaMemsetAsync(d_count, 0, (size_t(n_lists) + 1) * 4, stream));
-    chunk_and_count_kernel<<<ceildiv<uint32_t>(nq * 32, 256), 256, 0, stream>>>(
-      d_probes, idx.list_sizes(), nq, n_probes, d_chunk, d_count);
-    if (stats) {
-      scan_stats_kernel<<<ceildiv<uint32_t>(n_lists, 256), 256, 0, stream>>>(d_count, idx.list_sizes(),
-                                                                              n_lists, res.d_stats);
-      res.stat_pairs += n_pairs;
+    // 3. sample offsets + work list of the scan
+    if (!stats && n_pairs <= 4096) {
+      // small batch: one launch, pairs in arrival order (a sort by list has nothing to gain here)
+      CUDA_TRY(cudaMemsetAsync(d_counter, 0, 8, stream));
+      small_batch_pairs_kernel<<<ceildiv<uint32_t>(nq * 32, 128), 128, 0, stream>>>(
+        d_probes, idx.list_sizes(), idx.row_offsets(), nq, n_probes, d_chunk, d_order, d_counter + 1, d_kth,
+        store_all ? nullptr : d_keys, k);
+      CUDA_TRY(cudaGetLastError());
+      res.launches += 1;
+    } else {
+      // counting sort of the pairs by list
+      CUDA_TRY(cudaMemsetAsync(d_count, 0, (size_t(n_lists) + 1) * 4, stream));
+      chunk_and_count_kernel<<<ceildiv<uint32_t>(nq * 32, 256), 256, 0, stream>>>(
+        d_probes, idx.list_sizes(), nq, n_probes, d_chunk, d_count);
+      if (stats) {
+        scan_stats_kernel<<<ceildiv<uint32_t>(n_lists, 256), 256, 0, stream>>>(d_count, idx.list_sizes(),
+                                                                                n_lists, res.d_stats);
+        res.stat_pairs += n_pairs;
+      }
+      exclusive_scan_kernel<<<1, 1024, 0, stream>>>(d_count, n_lists);  // d_count[n_lists] = work items
+      CUDA_TRY(cudaMemcpyAsync(d_counter + 1, d_count + n_lists, 4, cudaMemcpyDeviceToDevice, stream));
+      scatter_pairs_kernel<<<ceildiv<uint32_t>(n_pairs, 256), 256, 0, stream>>>(
+        d_probes, d_chunk, idx.list_sizes(), idx.row_offsets(), n_pairs, n_probes, d_count, d_order,
+        store_all ? nullptr : d_keys, k);
+      fill_u32_kernel<<<ceildiv<uint32_t>(nq, 256), 256, 0, stream>>>(d_kth, nq, kEmptyScore);
+      CUDA_TRY(cudaMemsetAsync(d_counter, 0, 4, stream));
+      CUDA_TRY(cudaGetLastError());
+      res.launches += 4;
     }
-    exclusive_scan_kernel<<<1, 1024, 0, stream>>>(d_count, n_lists);  // d_count[n_lists] = work items
-    CUDA_TRY(cudaMemcpyAsync(d_counter + 1, d_count + n_lists, 4, cudaMemcpyDeviceToDevice, stream));
-    scatter_pairs_kernel<<<ceildiv<uint32_t>(n_pairs, 256), 256, 0, stream>>>(
-      d_probes, d_chunk, idx.list_sizes(), idx.row_offsets(), n_pairs, n_probes, d_count, d_order,
-      store_all ? nullptr : d_keys, k);
-    fill_u32_kernel<<<ceildiv<uint32_t>(nq, 256), 256, 0, stream>>>(d_kth, nq, kEmptyScore);
-    CUDA_TRY(cudaMemsetAsync(d_counter, 0, 4, stream));
-    CUDA_TRY(cudaGetLastError());
-    res.launches += 4;
 
     if (stats) { res.stats_mark(ev, 3); }
     // 4. LUT + scan + per-pair top-k
