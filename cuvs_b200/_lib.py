@@ -150,6 +150,10 @@ SIGNATURES = {
     "cuvsDynamicBatchingSearch": [C.c_size_t, _P(DynamicBatchingIndexStruct), C.c_double,
                                   _P(DLManagedTensor), _P(DLManagedTensor), _P(DLManagedTensor)],
     "cuvsDynamicBatchingStats": [_P(DynamicBatchingIndexStruct), _P(C.c_uint64), _P(C.c_uint64)],
+    "cuvsMultiGpuIvfPqDeserializeRank": [C.c_size_t, C.c_char_p, C.c_int, C.c_int, _P(IndexStruct), _P(C.c_int),
+                                         _P(C.c_int64)],
+    "cuvsMultiGpuIvfPqSerializeRanks": [C.c_size_t, C.c_char_p, C.c_int, DLDataType, _P(_P(IndexStruct)),
+                                        C.c_int],
     "cuvsRefine": [C.c_size_t, _P(DLManagedTensor), _P(DLManagedTensor), _P(DLManagedTensor), C.c_int,
                    _P(DLManagedTensor), _P(DLManagedTensor)],
     "cuvsIvfPqTransform": [C.c_size_t, _P(IndexStruct), _P(DLManagedTensor), _P(DLManagedTensor),

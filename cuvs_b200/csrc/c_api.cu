@@ -17,6 +17,7 @@
 #include <cstring>
 #include <exception>
 #include <string>
+#include <vector>
 
 namespace cuvs::neighbors {
 void refine_any(raft::resources& res, const void* dataset, ivf_pq::elem_t dtype, int64_t n_rows,
@@ -618,6 +619,44 @@ extern "C" cuvsError_t cuvsMultiGpuIvfPqDistributeShard(cuvsResources_t res, con
     }
     delete reinterpret_cast<index_t*>(index->addr);
     index->addr = reinterpret_cast<uintptr_t>(ix);
+  });
+}
+
+extern "C" cuvsError_t cuvsMultiGpuIvfPqDeserializeRank(cuvsResources_t res, const char* filename, int rank,
+                                                        int n_ranks, cuvsIvfPqIndex_t index, int* mode,
+                                                        int64_t* id_offset)
+{
+  return translate_exceptions([=] {
+    CUVS_EXPECTS(index && filename && mode && id_offset, "null argument");
+    auto* ix = new index_t();
+    try {
+      ivf_pq::deserialize_mg_rank(*res_of(res), std::string(filename), rank, n_ranks, ix, mode, id_offset);
+    } catch (...) {
+      delete ix;
+      throw;
+    }
+    delete reinterpret_cast<index_t*>(index->addr);
+    index->addr = reinterpret_cast<uintptr_t>(ix);
+  });
+}
+
+extern "C" cuvsError_t cuvsMultiGpuIvfPqSerializeRanks(cuvsResources_t res, const char* filename, int mode,
+                                                       DLDataType dataset_dtype, cuvsIvfPqIndex_t* indexes,
+                                                       int n_ranks)
+{
+  return translate_exceptions([=] {
+    CUVS_EXPECTS(filename && indexes && n_ranks > 0, "null argument");
+    // numpy dtype strings as raft::numpy_serializer::get_numpy_dtype<T>() spells them
+    const char* ds = nullptr;
+    switch (elem_of_dtype(dataset_dtype, "dataset")) {
+      case ivf_pq::elem_t::f32: ds = "<f4"; break;
+      case ivf_pq::elem_t::f16: ds = "<f2"; break;
+      case ivf_pq::elem_t::i8: ds = "|i1"; break;
+      default: ds = "|u1"; break;
+    }
+    std::vector<const index_t*> per_rank;
+    for (int r = 0; r < n_ranks; r++) { per_rank.push_back(index_of(indexes[r])); }
+    ivf_pq::serialize_mg(*res_of(res), std::string(filename), mode, ds, per_rank);
   });
 }
 

@@ -494,4 +494,88 @@ void deserialize(raft::resources& res, const std::string& filename, index<int64_
   deserialize(res, in, idx, shard_rank, shard_count);
 }
 
+// ------------------------------------------------------------------------------------------------
+// multi-GPU index files of the reference (cpp/src/neighbors/mg/snmg.cuh:60-91 reader, :780-805 writer):
+// four bytes with the numpy dtype string of the dataset type, the distribution mode and the number
+// of ranks as scalar records, then one complete index stream per rank.
+// ------------------------------------------------------------------------------------------------
+namespace {
+
+// Steps over one index stream; returns its size (number of vectors).
+int64_t skip_index(std::istream& is)
+{
+  auto ver = read_scalar<int32_t>(is);
+  CUVS_EXPECTS(ver == 4, "serialization version mismatch %d vs. %d", ver, 4);
+  auto n_rows = read_scalar<int64_t>(is);
+  read_scalar<uint32_t>(is);  // dim
+  read_scalar<uint32_t>(is);  // pq_bits
+  read_scalar<uint32_t>(is);  // pq_dim
+  read_scalar<uint8_t>(is);   // conservative_memory_allocation
+  read_scalar<int32_t>(is);   // metric
+  read_scalar<int32_t>(is);   // codebook kind
+  read_scalar<int32_t>(is);   // list layout
+  auto n_lists = read_scalar<uint32_t>(is);
+  CUVS_EXPECTS(n_lists > 0 && n_lists <= kMaxIvfNLists, "ivf_pq::deserialize: n_lists=%u exceeds maximum %u",
+               n_lists, kMaxIvfNLists);
+  auto skip_any = [&](const char* what) {
+    npy_header h = read_header(is);
+    is.seekg(std::streamoff(h.itemsize * h.count()), std::ios::cur);
+    CUVS_EXPECTS(is.good(), "ivf_pq::deserialize: truncated record `%s`", what);
+  };
+  skip_any("pq_centers");
+  skip_any("centers");
+  skip_any("centers_rot");
+  skip_any("rotation_matrix");
+  std::vector<uint32_t> sizes(n_lists);
+  read_array(is, sizes.data(), 4, n_lists, "list_sizes");
+  for (uint32_t l = 0; l < n_lists; l++) {
+    auto sz = read_scalar<uint32_t>(is);
+    CUVS_EXPECTS(sz == sizes[l], "ivf_pq::deserialize: list %u has size %u, header says %u", l, sz, sizes[l]);
+    if (sz == 0) { continue; }
+    skip_any("list codes");
+    skip_any("list indices");
+  }
+  return n_rows;
+}
+
+}  // namespace
+
+void deserialize_mg_rank(raft::resources& res, const std::string& filename, int rank, int n_ranks,
+                         index<int64_t>* idx, int* mode, int64_t* id_offset)
+{
+  std::ifstream is(filename, std::ios::in | std::ios::binary);
+  CUVS_EXPECTS(bool(is), "Cannot open file %s", filename.c_str());
+  char dtype_string[4];
+  is.read(dtype_string, 4);
+  CUVS_EXPECTS(is.good(), "Cannot read the header of %s", filename.c_str());
+  const int m      = read_scalar<int32_t>(is);
+  const int stored = read_scalar<int32_t>(is);
+  CUVS_EXPECTS(m == 0 || m == 1, "multi-GPU index file: invalid distribution mode %d", m);
+  // snmg.cuh:77-81
+  CUVS_EXPECTS(stored == n_ranks, "Serialized index has %d ranks whereas NCCL clique has %d ranks", stored,
+               n_ranks);
+  CUVS_EXPECTS(rank >= 0 && rank < n_ranks, "invalid rank %d of %d", rank, n_ranks);
+  int64_t offset = 0;
+  for (int r = 0; r < rank; r++) { offset += skip_index(is); }
+  deserialize(res, is, idx, 0, 1);
+  *mode      = m;
+  *id_offset = m == 1 ? offset : 0;  // SHARDED: ids are local to a rank's rows (snmg.cuh:351-355)
+}
+
+void serialize_mg(raft::resources& res, const std::string& filename, int mode, const char* dtype_string,
+                  const std::vector<const index<int64_t>*>& per_rank)
+{
+  CUVS_EXPECTS(mode == 0 || mode == 1, "invalid distribution mode %d", mode);
+  std::ofstream of(filename, std::ios::out | std::ios::binary);
+  CUVS_EXPECTS(bool(of), "Cannot open file %s", filename.c_str());
+  char d[4] = {0, 0, 0, 0};
+  std::strncpy(d, dtype_string, 4);
+  of.write(d, 4);
+  write_scalar<int32_t>(of, mode);
+  write_scalar<int32_t>(of, int32_t(per_rank.size()));
+  for (auto* ix : per_rank) { serialize(res, of, *ix); }
+  of.close();
+  CUVS_EXPECTS(bool(of), "Error writing output %s", filename.c_str());
+}
+
 }  // namespace cuvs::neighbors::ivf_pq

@@ -317,6 +317,15 @@ void deserialize(raft::resources& res, std::istream& is, index<int64_t>* idx, in
 void deserialize(raft::resources& res, const std::string& filename, index<int64_t>* idx,
                  int shard_rank = 0, int shard_count = 1);
 
+// Multi-GPU index files of the reference (cpp/src/neighbors/mg/snmg.cuh:60-91, 780-805): dtype string,
+// distribution mode (0 = REPLICATED, 1 = SHARDED by rows), number of ranks, one index stream per rank.
+// One process per GPU reads its own rank's index; `id_offset` = rows held by the ranks before it
+// (what the reference adds to a shard's local ids when it merges, snmg.cuh:351-355), 0 when replicated.
+void deserialize_mg_rank(raft::resources& res, const std::string& filename, int rank, int n_ranks,
+                         index<int64_t>* idx, int* mode, int64_t* id_offset);
+void serialize_mg(raft::resources& res, const std::string& filename, int mode, const char* dtype_string,
+                  const std::vector<const index<int64_t>*>& per_rank);
+
 // Which rank of a list-sharded deployment holds list `label`.
 inline int shard_of_list(uint32_t label, int shard_count) { return int(label % uint32_t(shard_count)); }
 

@@ -47,6 +47,84 @@ def load_shard(filename: str, rank: int | None = None, n_ranks: int | None = Non
     return idx
 
 
+REPLICATED, SHARDED = 0, 1      # cuvs::neighbors::distribution_mode (common.hpp:1843-1848)
+
+
+def load_reference_mg(filename: str, rank: int | None = None, n_ranks: int | None = None,
+                      resources: Resources | None = None, group=None):
+    """This rank's index out of a multi-GPU index file written by the reference
+    (``cuvsMultiGpuIvfPqSerialize``).  Returns ``(index, mode, id_offset)``: ``mode`` is
+    ``REPLICATED`` or ``SHARDED`` (by rows), ``id_offset`` what has to be added to this rank's
+    neighbour ids in sharded mode."""
+    r, w = _rank_world(group)
+    rank = r if rank is None else rank
+    n_ranks = w if n_ranks is None else n_ranks
+    res = resources or default_resources()
+    res.use_current_stream()
+    idx = ivf_pq.Index()
+    mode, off = C.c_int(), C.c_int64()
+    L.check(L.load().cuvsMultiGpuIvfPqDeserializeRank(res.handle, filename.encode(), C.c_int(rank),
+                                                      C.c_int(n_ranks), idx._h, C.byref(mode), C.byref(off)))
+    return idx, mode.value, off.value
+
+
+def save_reference_mg(filename: str, indexes, mode: int, dataset_dtype=torch.float32,
+                      resources: Resources | None = None):
+    """Write ``indexes`` (one per rank, all in this process) as one multi-GPU index file of the
+    reference's format."""
+    res = resources or default_resources()
+    code_bits = {torch.float32: (2, 32), torch.float16: (2, 16), torch.int8: (0, 8), torch.uint8: (1, 8)}
+    code, bits = code_bits[dataset_dtype]
+    arr = (C.POINTER(L.IndexStruct) * len(indexes))(*[ix._h for ix in indexes])
+    L.check(L.load().cuvsMultiGpuIvfPqSerializeRanks(res.handle, filename.encode(), C.c_int(mode),
+                                                     L.DLDataType(code, bits, 1), arr, C.c_int(len(indexes))))
+
+
+def translate_ids(neighbors: torch.Tensor, id_offset: int) -> torch.Tensor:
+    """Local ids of a row shard -> global ids (missing results, INT64_MAX, stay as they are)."""
+    if id_offset == 0:
+        return neighbors
+    missing = neighbors == torch.iinfo(torch.int64).max
+    return torch.where(missing, neighbors, neighbors + id_offset)
+
+
+def search_reference_mg(search_params: ivf_pq.SearchParams, index: ivf_pq.Index, mode: int, id_offset: int,
+                        queries, k: int, select_min: bool = True, group=None,
+                        resources: Resources | None = None, sync: bool = True):
+    """Search an index loaded with :func:`load_reference_mg`, with the reference's semantics
+    (cpp/src/neighbors/mg/snmg.cuh:249-561): SHARDED -- every rank searches its own rows for the whole
+    batch, ids are made global, the per-rank lists are merged; REPLICATED -- the batch is split between
+    the ranks and the slices are gathered.  Every rank passes the same queries and gets the result."""
+    res = resources or default_resources()
+    rank, w = _rank_world(group)
+    if mode == SHARDED:
+        d, i = ivf_pq.search(search_params, index, queries, k, resources=res, sync=False)
+        i = translate_ids(i, id_offset)
+        if w == 1:
+            if sync:
+                res.sync()
+            return d, i
+        part_d, part_i = gather_parts(d, i, group)
+        return merge_parts(part_d, part_i, select_min, res, sync)
+    n = queries.shape[0]
+    if w == 1:
+        return ivf_pq.search(search_params, index, queries, k, resources=res, sync=sync)
+    s = -(-n // w)
+    lo, hi = min(n, rank * s), min(n, (rank + 1) * s)
+    mine_d = torch.zeros((s, k), dtype=torch.float32, device=queries.device)
+    mine_i = torch.zeros((s, k), dtype=torch.int64, device=queries.device)
+    if hi > lo:
+        d, i = ivf_pq.search(search_params, index, queries[lo:hi].contiguous(), k, resources=res, sync=False)
+        mine_d[: hi - lo], mine_i[: hi - lo] = d, i
+    all_d = torch.empty((w * s, k), dtype=torch.float32, device=queries.device)
+    all_i = torch.empty((w * s, k), dtype=torch.int64, device=queries.device)
+    dist.all_gather_into_tensor(all_d, mine_d, group=group)
+    dist.all_gather_into_tensor(all_i, mine_i, group=group)
+    if sync:
+        res.sync()
+    return all_d[:n], all_i[:n]
+
+
 def gather_parts(local_d: torch.Tensor, local_i: torch.Tensor, group=None):
     """All-gather the per-rank results: returns ([R, n, k] distances, [R, n, k] ids)."""
     _, w = _rank_world(group)

@@ -30,6 +30,32 @@ CUVS_EXPORT cuvsError_t cuvsMultiGpuIvfPqDistributeShard(cuvsResources_t res,
                                                          int n_ranks,
                                                          cuvsIvfPqIndex_t index);
 
+/* Stands in for cuvsMultiGpuIvfPqDeserialize (c/include/cuvs/neighbors/mg_ivf_pq.h:245;
+ * cpp/src/neighbors/mg/snmg.cuh:60-91) in a one-process-per-GPU deployment: reads the index of `rank`
+ * out of a multi-GPU index file written by the reference's cuvsMultiGpuIvfPqSerialize (dtype string,
+ * distribution mode, number of ranks, one index stream per rank; the streams of the other ranks are
+ * stepped over).  n_ranks must equal the number stored in the file.  mode receives 0 (REPLICATED:
+ * every rank holds the whole index) or 1 (SHARDED by rows); id_offset receives the number of rows
+ * held by the ranks before this one -- what the reference adds to this rank's neighbour ids when it
+ * merges (snmg.cuh:351-355) -- or 0 when replicated. */
+CUVS_EXPORT cuvsError_t cuvsMultiGpuIvfPqDeserializeRank(cuvsResources_t res,
+                                                         const char* filename,
+                                                         int rank,
+                                                         int n_ranks,
+                                                         cuvsIvfPqIndex_t index,
+                                                         int* mode,
+                                                         int64_t* id_offset);
+
+/* Counterpart of cuvsMultiGpuIvfPqSerialize (mg_ivf_pq.h:224; snmg.cuh:780-805) for indexes that live
+ * in this process: writes `n_ranks` indexes as one multi-GPU index file of the reference's format.
+ * dataset_dtype is the element type the reference records in the file's first four bytes. */
+CUVS_EXPORT cuvsError_t cuvsMultiGpuIvfPqSerializeRanks(cuvsResources_t res,
+                                                        const char* filename,
+                                                        int mode,
+                                                        DLDataType dataset_dtype,
+                                                        cuvsIvfPqIndex_t* indexes,
+                                                        int n_ranks);
+
 /* Stands in for the merge step of the sharded search (cpp/src/neighbors/mg/snmg.cuh:349-392 calling
  * knn_merge_parts, cpp/src/neighbors/detail/knn_merge_parts.cuh:24-170): part_distances f32 and
  * part_neighbors i64 are [n_parts, n_queries, k] device tensors; distances / neighbors are

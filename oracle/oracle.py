@@ -191,6 +191,33 @@ def read_record(f, expect_dtype=None, expect_shape=None) -> np.ndarray:
 
 
 # --------------------------------------------------------------------------------------------
+# multi-GPU index files (cpp/src/neighbors/mg/snmg.cuh:60-91 reader, :780-805 writer): four bytes with
+# the numpy dtype string of the dataset type, distribution mode and number of ranks as scalar
+# records (C++ int), then one complete index stream per rank.  Parity unpinned for the framing, like
+# the single-index format: no file written by the reference was available.
+# --------------------------------------------------------------------------------------------
+REPLICATED, SHARDED = 0, 1
+
+
+def save_mg(path, mode: int, indexes, dtype_string: str = "<f4") -> None:
+    with open(path, "wb") as f:
+        f.write(dtype_string.encode("latin1").ljust(4, b"\0")[:4])
+        write_record(f, np.int32(mode))
+        write_record(f, np.int32(len(indexes)))
+        for ix in indexes:
+            ix.save(f)
+
+
+def load_mg(path):
+    """Returns (dtype_string, mode, [OracleIndex per rank])."""
+    with open(path, "rb") as f:
+        dtype_string = f.read(4).rstrip(b"\0").decode("latin1")
+        mode = int(read_record(f))
+        n = int(read_record(f))
+        return dtype_string, mode, [OracleIndex.load(f) for _ in range(n)]
+
+
+# --------------------------------------------------------------------------------------------
 # index
 # --------------------------------------------------------------------------------------------
 

@@ -168,3 +168,24 @@ def test_oracle_other_metrics(oracle_mod, metric):
     if metric == 1:      # sqrt of the squared distance
         d2, _ = O.search(O.build_index(x, 16, pq_dim=12, pq_bits=8, metric=0, kmeans_iters=3), q, 10, n_probes=16)
         assert np.allclose(d, np.sqrt(d2), rtol=1e-5)
+
+
+def test_multi_gpu_index_file_round_trip(oracle_mod, tmp_path):
+    """cpp/src/neighbors/mg/snmg.cuh:780-805: dtype string, mode, rank count, one index per rank."""
+    O = oracle_mod
+    rng = np.random.default_rng(3)
+    x = rng.standard_normal((900, 16)).astype(np.float32)
+    parts = [O.build_index(x[:500], 8, pq_dim=8, kmeans_iters=2, seed=0),
+             O.build_index(x[500:], 8, pq_dim=8, kmeans_iters=2, seed=1)]
+    path = str(tmp_path / "mg.bin")
+    O.save_mg(path, O.SHARDED, parts)
+    blob = open(path, "rb").read()
+    assert blob[:4] == b"<f4\x00" and blob[4:10] == b"\x93NUMPY"
+    dtype_string, mode, back = O.load_mg(path)
+    assert dtype_string == "<f4" and mode == O.SHARDED and len(back) == 2
+    for a, b in zip(parts, back):
+        assert a.size == b.size and (a.list_sizes == b.list_sizes).all()
+        assert (a.centers == b.centers).all() and (a.pq_centers == b.pq_centers).all()
+        for l in range(a.n_lists):
+            s = int(a.list_sizes[l])
+            assert (np.asarray(a.list_ids[l][:s]) == np.asarray(b.list_ids[l][:s])).all()
