@@ -432,12 +432,13 @@ def run_ours(args):
     launches_before = stats.launches
     ms_step = timed(lambda: one_search(sp), args.steps, args.warmup)
     ms_single = ms_step
-    # Throughput mode on one GPU: two batches in flight, each on its own stream and resources handle
+    # Throughput mode: two batches in flight per GPU, each on its own stream and resources handle
     # (the serving pattern of the reference's benchmark in throughput mode: several host threads, one
-    # stream each), so that the small kernels of one batch fill the tails of the other's large ones.
+    # stream each), so that the small kernels (and, with several GPUs, the NCCL exchanges) of one batch
+    # fill the tails of the other's large kernels.
     # The per-kernel figures above (stage times, roofline, launches) come from the single-stream pass.
     n_streams = 1
-    if world == 1:
+    if True:
         from cuvs_b200.common import Resources
         n_streams = 2
         lanes = []
@@ -456,7 +457,10 @@ def run_ours(args):
                     for ev in stream_wait:
                         lane["stream"].wait_event(ev)
                 lane["res"].use_current_stream()
-                d, i = ivf_pq.search(sp, index, q, k0, lane["ci"], lane["cd"], lane["res"], sync=False)
+                if world > 1:
+                    d, i = mg.search(sp, index, q, k0, True, None, lane["res"], sync=False)
+                else:
+                    d, i = ivf_pq.search(sp, index, q, k0, lane["ci"], lane["cd"], lane["res"], sync=False)
                 oi, od = outs if outs is not None else (lane["oi"], lane["od"])
                 if refining:
                     refine(dataset, q, i, k=k, metric="sqeuclidean", indices=oi, distances=od,
