@@ -1,7 +1,8 @@
 """Generates tests/golden/ref_pin.npz from the reference's own code.
 
-Run in an environment where the reference checkout is present (default /root/reference):
-    python tests/golden/make_golden.py
+Run in an environment where the reference checkout is present (its location is the argument,
+by default the one oracle/Makefile uses):
+    python tests/golden/make_golden.py [reference_root]
 It builds oracle/_ref/libref_pin.so (two reference headers compiled on the host, see
 oracle/ref_pin.cpp) and records, for seeded inputs,
   * the reference's 8-bit float: encodings of a float sweep, both decodings of all 256 codes;
