@@ -128,6 +128,20 @@ SIGNATURES = {
     "cuvsIvfPqSerialize": [C.c_size_t, C.c_char_p, _P(IndexStruct)],
     "cuvsIvfPqDeserialize": [C.c_size_t, C.c_char_p, _P(IndexStruct)],
     "cuvsIvfPqExtend": [C.c_size_t, _P(DLManagedTensor), _P(DLManagedTensor), _P(IndexStruct)],
+    "cuvsIvfPqHelpersUnpackListData": [C.c_size_t, _P(IndexStruct), _P(DLManagedTensor), C.c_uint32,
+                                       C.c_uint32, _P(DLManagedTensor)],
+    "cuvsIvfPqHelpersPackListData": [C.c_size_t, _P(IndexStruct), _P(DLManagedTensor), C.c_uint32,
+                                     C.c_uint32],
+    "cuvsIvfPqHelpersPackContiguousListData": [C.c_size_t, _P(IndexStruct), _P(DLManagedTensor),
+                                               C.c_uint32, C.c_uint32],
+    "cuvsIvfPqHelpersReconstructListData": [C.c_size_t, _P(IndexStruct), _P(DLManagedTensor),
+                                            C.c_uint32, C.c_uint32, _P(DLManagedTensor)],
+    "cuvsIvfPqHelpersExtendListWithCodes": [C.c_size_t, _P(IndexStruct), _P(DLManagedTensor),
+                                            _P(DLManagedTensor), C.c_uint32, C.c_bool],
+    "cuvsIvfPqHelpersExtendList": [C.c_size_t, _P(IndexStruct), _P(DLManagedTensor),
+                                   _P(DLManagedTensor), C.c_uint32],
+    "cuvsIvfPqHelpersEraseList": [C.c_size_t, _P(IndexStruct), C.c_uint32],
+    "cuvsIvfPqHelpersResetIndex": [C.c_size_t, _P(IndexStruct)],
     "cuvsMultiGpuIvfPqDistributeShard": [C.c_size_t, C.c_char_p, C.c_int, C.c_int, _P(IndexStruct)],
     "cuvsMultiGpuIvfPqMergeParts": [C.c_size_t, _P(DLManagedTensor), _P(DLManagedTensor),
                                     _P(DLManagedTensor), _P(DLManagedTensor), C.c_bool],
@@ -174,7 +188,7 @@ def load():
         return _lib
     if not os.path.exists(LIB_PATH):
         raise ImportError(
-            f"{LIB_PATH} is missing: build it with `python -m cuvs_b200._build` "
+            f"{LIB_PATH} is missing: build it with `python cuvs_b200/_build.py` "
             "(or __graft_entry__.build()).  There is no fallback implementation.")
     lib = C.CDLL(LIB_PATH)
     for name, args in SIGNATURES.items():

@@ -451,6 +451,110 @@ __global__ void unpack_contiguous_kernel(const uint8_t* __restrict__ list, uint3
   }
 }
 
+// Code j of one interleaved list row.
+__device__ __forceinline__ uint32_t list_code(const uint8_t* __restrict__ list, uint32_t row, uint32_t j,
+                                              uint32_t n_pieces, uint32_t bits)
+{
+  const uint32_t cpp = 128u / bits;
+  const uint32_t p = j / cpp, bit = (j % cpp) * bits;
+  const uint8_t* piece = list + ((size_t(row >> 5) * n_pieces + p) * 32 + (row & 31)) * 16;
+  uint32_t pair        = piece[bit >> 3];
+  if ((bit & 7) + bits > 8) { pair |= uint32_t(piece[(bit >> 3) + 1]) << 8; }
+  return (pair >> (bit & 7)) & ((1u << bits) - 1u);
+}
+
+// One thread per (row, subspace): interleaved list rows -> one code per byte.
+__global__ void unpack_codes_kernel(const uint8_t* __restrict__ list, uint32_t n, uint32_t offset,
+                                    const uint32_t* __restrict__ indices, uint32_t pq_dim, uint32_t bits,
+                                    uint32_t n_pieces, uint8_t* __restrict__ out)
+{
+  const uint64_t t = blockIdx.x * uint64_t(blockDim.x) + threadIdx.x;
+  if (t >= uint64_t(n) * pq_dim) { return; }
+  const uint32_t i = uint32_t(t / pq_dim), j = uint32_t(t % pq_dim);
+  const uint32_t row = indices ? indices[i] : offset + i;
+  out[t] = uint8_t(list_code(list, row, j, n_pieces, bits));
+}
+
+// One thread per (row, 16-byte piece): codes (one per byte, or bit-packed rows when kContiguous)
+// -> interleaved list rows [offset, offset + n).  Unused bits of the last piece are zero.
+template <bool kContiguous>
+__global__ void pack_codes_kernel(const uint8_t* __restrict__ codes, uint32_t n, uint32_t offset,
+                                  uint32_t pq_dim, uint32_t bits, uint32_t n_pieces,
+                                  uint32_t flat_row_bytes, uint8_t* __restrict__ list)
+{
+  const uint64_t t = blockIdx.x * uint64_t(blockDim.x) + threadIdx.x;
+  if (t >= uint64_t(n) * n_pieces) { return; }
+  const uint32_t i = uint32_t(t / n_pieces), p = uint32_t(t % n_pieces);
+  const uint32_t cpp = 128u / bits, mask = (1u << bits) - 1u;
+  const uint8_t* src = codes + size_t(i) * (kContiguous ? flat_row_bytes : pq_dim);
+  uint32_t w[4] = {0, 0, 0, 0};
+  for (uint32_t c = 0; c < cpp && p * cpp + c < pq_dim; c++) {
+    const uint32_t j = p * cpp + c;
+    uint32_t code;
+    if (kContiguous) {
+      const uint32_t ib = j * bits;
+      uint32_t pair     = src[ib >> 3];
+      if ((ib & 7) + bits > 8) { pair |= uint32_t(src[(ib >> 3) + 1]) << 8; }
+      code = (pair >> (ib & 7)) & mask;
+    } else {
+      code = src[j] & mask;
+    }
+    const uint32_t bit = c * bits;
+    w[bit >> 5] |= code << (bit & 31);
+    if ((bit & 31) + bits > 32) { w[(bit >> 5) + 1] |= code >> (32 - (bit & 31)); }
+  }
+  const uint32_t row = offset + i;
+  *reinterpret_cast<uint4*>(list + ((size_t(row >> 5) * n_pieces + p) * 32 + (row & 31)) * 16) =
+    make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+template <typename T>
+__device__ __forceinline__ T from_float(float x);
+template <> __device__ __forceinline__ float from_float<float>(float x) { return x; }
+template <> __device__ __forceinline__ __half from_float<__half>(float x) { return __float2half_rn(x); }
+template <> __device__ __forceinline__ int8_t from_float<int8_t>(float x) { return static_cast<int8_t>(x * 128.0f); }
+template <> __device__ __forceinline__ uint8_t from_float<uint8_t>(float x) { return static_cast<uint8_t>(x * 256.0f); }
+
+// One block per row: decode the row in the rotated space (codeword + rotated list center, one add
+// per component), then out[i, d] = sum over r, in order, of rotation[r, d] * decoded[r] (fp32 fma).
+template <typename T>
+__global__ void reconstruct_kernel(const uint8_t* __restrict__ list, uint32_t offset,
+                                   const uint32_t* __restrict__ indices, const float* __restrict__ pq_centers,
+                                   int per_cluster, const float* __restrict__ center_rot,
+                                   const float* __restrict__ rot, uint32_t label, uint32_t dim,
+                                   uint32_t rot_dim, uint32_t pq_dim, uint32_t len, uint32_t bits,
+                                   uint32_t n_pieces, T* __restrict__ out)
+{
+  extern __shared__ float s_dec[];
+  const uint32_t i    = blockIdx.x;
+  const uint32_t row  = indices ? indices[i] : offset + i;
+  const uint32_t book = 1u << bits;
+  for (uint32_t r = threadIdx.x; r < rot_dim; r += blockDim.x) {
+    const uint32_t j = r / len, k = r % len;
+    const uint32_t code = list_code(list, row, j, n_pieces, bits);
+    const float* pqc    = pq_centers + size_t(per_cluster ? label : j) * len * book;
+    s_dec[r]            = __fadd_rn(pqc[size_t(k) * book + code], center_rot[r]);
+  }
+  __syncthreads();
+  for (uint32_t d = threadIdx.x; d < dim; d += blockDim.x) {
+    float acc = 0.0f;
+    for (uint32_t r = 0; r < rot_dim; r++) { acc = __fmaf_rn(rot[size_t(r) * dim + d], s_dec[r], acc); }
+    out[size_t(i) * dim + d] = from_float<T>(acc);
+  }
+}
+
+__global__ void fill_u32_kernel(uint32_t* p, uint32_t n, uint32_t v)
+{
+  const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) { p[i] = v; }
+}
+
+__global__ void add_scalar_u32_kernel(uint32_t* p, uint32_t n, uint32_t v)
+{
+  const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) { p[i] += v; }
+}
+
 // ------------------------------------------------------------------------------------------------
 // extend helpers
 // ------------------------------------------------------------------------------------------------
@@ -589,6 +693,36 @@ void launch_encode(raft::resources& res, const index<int64_t>& idx, const float*
   res.launches++;
 }
 
+
+// Re-create the arenas for `new_sizes`, keeping the first min(old, new) rows (codes and ids) of every list.
+void resize_lists(raft::resources& res, index<int64_t>* idx, const std::vector<uint32_t>& new_sizes)
+{
+  const uint32_t n_lists    = idx->n_lists();
+  const cudaStream_t stream = res.stream;
+  std::vector<uint32_t> keep(n_lists);
+  bool any = false;
+  for (uint32_t l = 0; l < n_lists; l++) {
+    keep[l] = std::min(idx->host_list_sizes()[l], new_sizes[l]);
+    any |= keep[l] > 0;
+  }
+  dev_array<uint8_t> old_codes = std::move(idx->codes_);
+  dev_array<int64_t> old_ids   = std::move(idx->ids_);
+  dev_array<uint64_t> old_off(size_t(n_lists) + 1);
+  dev_array<uint32_t> keep_d(n_lists);
+  CUDA_TRY(cudaMemcpyAsync(old_off.data(), idx->row_offsets(), (size_t(n_lists) + 1) * 8, cudaMemcpyDeviceToDevice, stream));
+  CUDA_TRY(cudaMemcpyAsync(keep_d.data(), keep.data(), size_t(n_lists) * 4, cudaMemcpyHostToDevice, stream));
+  idx->allocate_lists(new_sizes, stream);
+  if (any) {
+    relocate_lists_kernel<<<n_lists, 128, 0, stream>>>(old_codes.data(), old_ids.data(), old_off.data(),
+                                                       keep_d.data(), idx->row_offsets(),
+                                                       idx->n_pieces() * kIndexGroupVecLen, idx->codes(),
+                                                       idx->ids());
+    CUDA_TRY(cudaGetLastError());
+    res.launches++;
+  }
+  res.sync();  // the old arenas are released on return
+}
+
 }  // namespace
 
 // ------------------------------------------------------------------------------------------------
@@ -629,6 +763,158 @@ void set_model(raft::resources& res, index<int64_t>* idx, const float* pq_center
   CUDA_TRY(cudaMemcpyAsync(idx->rotation_matrix(), rotation_matrix,
                            size_t(idx->rot_dim()) * idx->dim() * 4, cudaMemcpyDefault, res.stream));
   res.sync();
+  idx->allocate_lists(std::vector<uint32_t>(idx->n_lists(), 0), res.stream);
+}
+
+namespace {
+void check_rows(const index<int64_t>& idx, uint32_t label, uint32_t offset, uint32_t n_rows)
+{
+  CUVS_EXPECTS(label < idx.n_lists(), "label %u is out of range", label);
+  // ivf_pq_build.cuh:611-612
+  CUVS_EXPECTS(uint64_t(offset) + n_rows <= idx.host_list_sizes()[label],
+               "offset + output size must be not bigger than the cluster size.");
+}
+uint8_t* list_base(const index<int64_t>& idx, uint32_t label)
+{
+  return idx.codes() + idx.host_row_offsets()[label] * size_t(idx.n_pieces()) * kIndexGroupVecLen;
+}
+// Grow list `label` by n_rows, write the new source ids; returns the first new row.
+uint32_t extend_list_prepare(raft::resources& res, index<int64_t>* idx, const int64_t* new_indices,
+                             uint32_t n_rows, uint32_t label)
+{
+  CUVS_EXPECTS(idx != nullptr && label < idx->n_lists(), "label %u is out of range", label);
+  const uint32_t offset = idx->host_list_sizes()[label];
+  CUVS_EXPECTS(uint64_t(offset) + n_rows < (1ull << 32), "list %u grows beyond 2^32 rows", label);
+  std::vector<uint32_t> sizes = idx->host_list_sizes();
+  sizes[label] += n_rows;
+  resize_lists(res, idx, sizes);
+  CUDA_TRY(cudaMemcpyAsync(idx->ids() + idx->host_row_offsets()[label] + offset, new_indices,
+                           size_t(n_rows) * 8, cudaMemcpyDefault, res.stream));
+  return offset;
+}
+}  // namespace
+
+namespace codepacker {
+
+void unpack_list_data(raft::resources& res, const index<int64_t>& idx, uint8_t* out_codes,
+                      uint32_t n_rows, uint32_t label, uint32_t offset,
+                      const uint32_t* in_cluster_indices)
+{
+  check_rows(idx, label, in_cluster_indices ? 0 : offset, in_cluster_indices ? 0 : n_rows);
+  if (n_rows == 0) { return; }
+  const uint64_t n_threads = uint64_t(n_rows) * idx.pq_dim();
+  unpack_codes_kernel<<<unsigned(ceildiv<uint64_t>(n_threads, 256)), 256, 0, res.stream>>>(
+    list_base(idx, label), n_rows, offset, in_cluster_indices, idx.pq_dim(), idx.pq_bits(),
+    idx.n_pieces(), out_codes);
+  CUDA_TRY(cudaGetLastError());
+  res.launches++;
+}
+
+namespace {
+template <bool kContiguous>
+void pack_rows(raft::resources& res, index<int64_t>* idx, const uint8_t* codes, uint32_t n_rows,
+               uint32_t label, uint32_t offset)
+{
+  CUVS_EXPECTS(idx != nullptr, "null index");
+  check_rows(*idx, label, offset, n_rows);
+  if (n_rows == 0) { return; }
+  const uint64_t n_threads = uint64_t(n_rows) * idx->n_pieces();
+  pack_codes_kernel<kContiguous><<<unsigned(ceildiv<uint64_t>(n_threads, 256)), 256, 0, res.stream>>>(
+    codes, n_rows, offset, idx->pq_dim(), idx->pq_bits(), idx->n_pieces(),
+    ceildiv(idx->pq_dim() * idx->pq_bits(), 8u), list_base(*idx, label));
+  CUDA_TRY(cudaGetLastError());
+  res.launches++;
+}
+}  // namespace
+
+void pack_list_data(raft::resources& res, index<int64_t>* idx, const uint8_t* codes, uint32_t n_rows,
+                    uint32_t label, uint32_t offset)
+{
+  pack_rows<false>(res, idx, codes, n_rows, label, offset);
+}
+
+void pack_contiguous_list_data(raft::resources& res, index<int64_t>* idx, const uint8_t* codes,
+                               uint32_t n_rows, uint32_t label, uint32_t offset)
+{
+  pack_rows<true>(res, idx, codes, n_rows, label, offset);
+}
+
+void reconstruct_list_data(raft::resources& res, const index<int64_t>& idx, void* out_vectors,
+                           elem_t out_type, uint32_t n_rows, uint32_t label, uint32_t offset,
+                           const uint32_t* in_cluster_indices)
+{
+  if (n_rows == 0) { return; }
+  check_rows(idx, label, in_cluster_indices ? 0 : offset, in_cluster_indices ? 0 : n_rows);
+  const size_t smem = size_t(idx.rot_dim()) * 4;
+  CUVS_EXPECTS(smem <= 48 * 1024, "rot_dim = %u is too large to reconstruct", idx.rot_dim());
+  auto launch = [&](auto* out) {
+    using T = std::remove_pointer_t<decltype(out)>;
+    reconstruct_kernel<T><<<n_rows, 128, smem, res.stream>>>(
+      list_base(idx, label), offset, in_cluster_indices, idx.pq_centers(),
+      idx.codebook_kind() == codebook_gen::PER_CLUSTER, idx.centers_rot() + size_t(label) * idx.rot_dim(),
+      idx.rotation_matrix(), label, idx.dim(), idx.rot_dim(), idx.pq_dim(), idx.pq_len(), idx.pq_bits(),
+      idx.n_pieces(), out);
+  };
+  switch (out_type) {
+    case elem_t::f32: launch(static_cast<float*>(out_vectors)); break;
+    case elem_t::f16: launch(static_cast<__half*>(out_vectors)); break;
+    case elem_t::i8: launch(static_cast<int8_t*>(out_vectors)); break;
+    default: launch(static_cast<uint8_t*>(out_vectors));
+  }
+  CUDA_TRY(cudaGetLastError());
+  res.launches++;
+}
+
+void extend_list_with_codes(raft::resources& res, index<int64_t>* idx, const uint8_t* new_codes,
+                            const int64_t* new_indices, uint32_t n_rows, uint32_t label)
+{
+  const uint32_t offset = extend_list_prepare(res, idx, new_indices, n_rows, label);
+  pack_rows<false>(res, idx, new_codes, n_rows, label, offset);
+  res.sync();
+}
+
+void extend_list_with_contiguous_codes(raft::resources& res, index<int64_t>* idx,
+                                       const uint8_t* new_codes, const int64_t* new_indices,
+                                       uint32_t n_rows, uint32_t label)
+{
+  const uint32_t offset = extend_list_prepare(res, idx, new_indices, n_rows, label);
+  pack_rows<true>(res, idx, new_codes, n_rows, label, offset);
+  res.sync();
+}
+
+void extend_list(raft::resources& res, index<int64_t>* idx, const void* new_vectors, elem_t dtype,
+                 const int64_t* new_indices, uint32_t n_rows, uint32_t label)
+{
+  const uint32_t offset = extend_list_prepare(res, idx, new_indices, n_rows, label);
+  if (n_rows == 0) { return; }
+  const label_ctx lc = labeling_of(idx->metric());
+  dev_array<float> x_ext(size_t(n_rows) * idx->dim_ext());
+  dev_array<uint32_t> labels(n_rows), slots(n_rows);
+  to_float_ext(res, new_vectors, dtype, n_rows, 1, idx->dim(), idx->dim_ext(), lc.pad, lc.normalize,
+               x_ext.data());
+  fill_u32_kernel<<<ceildiv(n_rows, 256u), 256, 0, res.stream>>>(labels.data(), n_rows, label);
+  iota_kernel<<<ceildiv(n_rows, 256u), 256, 0, res.stream>>>(slots.data(), n_rows);
+  add_scalar_u32_kernel<<<ceildiv(n_rows, 256u), 256, 0, res.stream>>>(slots.data(), n_rows, offset);
+  res.launches += 3;
+  // ids were written by extend_list_prepare: the encoder gets the same array, so it rewrites them
+  launch_encode(res, *idx, x_ext.data(), labels.data(), nullptr, slots.data(), n_rows, true, idx->codes(),
+                idx->ids(), new_indices, 0);
+  res.sync();
+}
+
+}  // namespace codepacker
+
+void erase_list(raft::resources& res, index<int64_t>* idx, uint32_t label)
+{
+  CUVS_EXPECTS(idx != nullptr && label < idx->n_lists(), "label %u is out of range", label);
+  std::vector<uint32_t> sizes = idx->host_list_sizes();
+  sizes[label]                = 0;
+  resize_lists(res, idx, sizes);
+}
+
+void reset_index(raft::resources& res, index<int64_t>* idx)
+{
+  CUVS_EXPECTS(idx != nullptr, "null index");
   idx->allocate_lists(std::vector<uint32_t>(idx->n_lists(), 0), res.stream);
 }
 
@@ -680,25 +966,11 @@ void extend_any(raft::resources& res, const void* new_vectors, elem_t dtype, int
     CUVS_EXPECTS(uint64_t(old_sizes[l]) + h_counts[l] < (1ull << 32), "list %u grows beyond 2^32 rows", l);
     new_sizes[l] = old_sizes[l] + h_counts[l];
   }
-  const int64_t old_total = idx->size();
-  dev_array<uint8_t> old_codes = std::move(idx->codes_);
-  dev_array<int64_t> old_ids   = std::move(idx->ids_);
-  dev_array<uint64_t> old_off(size_t(n_lists) + 1);
-  dev_array<uint32_t> old_sz(n_lists);
-  CUDA_TRY(cudaMemcpyAsync(old_off.data(), idx->row_offsets(), (size_t(n_lists) + 1) * 8, cudaMemcpyDeviceToDevice, stream));
-  CUDA_TRY(cudaMemcpyAsync(old_sz.data(), idx->list_sizes(), size_t(n_lists) * 4, cudaMemcpyDeviceToDevice, stream));
-  idx->allocate_lists(new_sizes, stream);
-  if (old_total > 0) {
-    relocate_lists_kernel<<<n_lists, 128, 0, stream>>>(old_codes.data(), old_ids.data(), old_off.data(),
-                                                       old_sz.data(), idx->row_offsets(),
-                                                       idx->n_pieces() * kIndexGroupVecLen, idx->codes(),
-                                                       idx->ids());
-    res.launches++;
-  }
+  resize_lists(res, idx, new_sizes);
 
   // pass 2: per chunk, order rows by list (stable), give each its slot, encode
   dev_array<uint32_t> fill(n_lists);  // rows already placed in each list
-  CUDA_TRY(cudaMemcpyAsync(fill.data(), old_sz.data(), size_t(n_lists) * 4, cudaMemcpyDeviceToDevice, stream));
+  CUDA_TRY(cudaMemcpyAsync(fill.data(), old_sizes.data(), size_t(n_lists) * 4, cudaMemcpyHostToDevice, stream));
   dev_array<uint32_t> iota(chunk), order(chunk), sorted_labels(chunk), slots(chunk), chunk_counts(n_lists);
   size_t cub_bytes = 0;
   int end_bit      = 1;

@@ -6,6 +6,7 @@
 #include "../../include/cuvs_b200_ext.h"
 #include "../../include/cuvs_dynamic_batching.h"
 #include "../../include/cuvs_ivf_pq.h"
+#include "../../include/cuvs_ivf_pq_helpers.h"
 #include "../../include/cuvs_mg_ivf_pq.h"
 #include "../../include/cuvs_refine.h"
 
@@ -383,6 +384,123 @@ extern "C" cuvsError_t cuvsIvfPqIndexUnpackContiguousListData(cuvsResources_t re
     ivf_pq::helpers::unpack_contiguous_list_data(*res_of(res), *ix, data,
                                                  uint32_t(out_codes->dl_tensor.shape[0]), label, offset);
   });
+}
+
+// ------------------------------------------------------------------------------------------------
+// single-list helpers (C++ only in the reference: ivf_pq.hpp:2564-3166, namespace helpers)
+// ------------------------------------------------------------------------------------------------
+namespace {
+const uint32_t* optional_row_indices(DLManagedTensor* t, int64_t n_rows)
+{
+  if (t == nullptr) { return nullptr; }
+  auto* p = static_cast<const uint32_t*>(checked_data(t, kDLUInt, 32, 1, true, "in_cluster_indices"));
+  CUVS_EXPECTS(t->dl_tensor.shape[0] == n_rows, "in_cluster_indices must have one entry per output row");
+  return p;
+}
+}  // namespace
+
+extern "C" cuvsError_t cuvsIvfPqHelpersUnpackListData(cuvsResources_t res, cuvsIvfPqIndex_t index,
+                                                      DLManagedTensor* out_codes, uint32_t label,
+                                                      uint32_t offset, DLManagedTensor* in_cluster_indices)
+{
+  return translate_exceptions([=] {
+    auto* ix   = index_of(index);
+    auto* data = static_cast<uint8_t*>(checked_data(out_codes, kDLUInt, 8, 2, true, "out_codes"));
+    CUVS_EXPECTS(out_codes->dl_tensor.shape[1] == int64_t(ix->pq_dim()), "out_codes must have pq_dim columns");
+    const int64_t n = out_codes->dl_tensor.shape[0];
+    ivf_pq::helpers::codepacker::unpack_list_data(*res_of(res), *ix, data, uint32_t(n), label, offset,
+                                                  optional_row_indices(in_cluster_indices, n));
+  });
+}
+
+extern "C" cuvsError_t cuvsIvfPqHelpersPackListData(cuvsResources_t res, cuvsIvfPqIndex_t index,
+                                                    DLManagedTensor* codes, uint32_t label, uint32_t offset)
+{
+  return translate_exceptions([=] {
+    auto* ix   = index_of(index);
+    auto* data = static_cast<const uint8_t*>(checked_data(codes, kDLUInt, 8, 2, true, "codes"));
+    CUVS_EXPECTS(codes->dl_tensor.shape[1] == int64_t(ix->pq_dim()), "codes must have pq_dim columns");
+    ivf_pq::helpers::codepacker::pack_list_data(*res_of(res), ix, data, uint32_t(codes->dl_tensor.shape[0]),
+                                                label, offset);
+  });
+}
+
+extern "C" cuvsError_t cuvsIvfPqHelpersPackContiguousListData(cuvsResources_t res, cuvsIvfPqIndex_t index,
+                                                              DLManagedTensor* codes, uint32_t label,
+                                                              uint32_t offset)
+{
+  return translate_exceptions([=] {
+    auto* ix   = index_of(index);
+    auto* data = static_cast<const uint8_t*>(checked_data(codes, kDLUInt, 8, 2, true, "codes"));
+    CUVS_EXPECTS(codes->dl_tensor.shape[1] == int64_t(cuvs_b200::ceildiv(ix->pq_dim() * ix->pq_bits(), 8u)),
+                 "codes must have ceil(pq_dim * pq_bits / 8) columns");
+    ivf_pq::helpers::codepacker::pack_contiguous_list_data(*res_of(res), ix, data,
+                                                           uint32_t(codes->dl_tensor.shape[0]), label, offset);
+  });
+}
+
+extern "C" cuvsError_t cuvsIvfPqHelpersReconstructListData(cuvsResources_t res, cuvsIvfPqIndex_t index,
+                                                           DLManagedTensor* out_vectors, uint32_t label,
+                                                           uint32_t offset, DLManagedTensor* in_cluster_indices)
+{
+  return translate_exceptions([=] {
+    auto* ix = index_of(index);
+    CUVS_EXPECTS(out_vectors != nullptr, "null out_vectors");
+    const DLTensor& t = out_vectors->dl_tensor;
+    auto et           = elem_of_dtype(t.dtype, "out_vectors");
+    void* data        = checked_data(out_vectors, t.dtype.code, t.dtype.bits, 2, true, "out_vectors");
+    CUVS_EXPECTS(t.shape[1] == int64_t(ix->dim()), "out_vectors must have dim columns");
+    ivf_pq::helpers::codepacker::reconstruct_list_data(*res_of(res), *ix, data, et, uint32_t(t.shape[0]), label,
+                                                       offset, optional_row_indices(in_cluster_indices, t.shape[0]));
+  });
+}
+
+extern "C" cuvsError_t cuvsIvfPqHelpersExtendListWithCodes(cuvsResources_t res, cuvsIvfPqIndex_t index,
+                                                           DLManagedTensor* new_codes,
+                                                           DLManagedTensor* new_indices, uint32_t label,
+                                                           bool contiguous)
+{
+  return translate_exceptions([=] {
+    auto* ix   = index_of(index);
+    auto* data = static_cast<const uint8_t*>(checked_data(new_codes, kDLUInt, 8, 2, true, "new_codes"));
+    auto* ids  = static_cast<const int64_t*>(checked_data(new_indices, kDLInt, 64, 1, true, "new_indices"));
+    const int64_t n = new_codes->dl_tensor.shape[0];
+    CUVS_EXPECTS(new_indices->dl_tensor.shape[0] == n, "new_indices must have one entry per new row");
+    const uint32_t cols = contiguous ? cuvs_b200::ceildiv(ix->pq_dim() * ix->pq_bits(), 8u) : ix->pq_dim();
+    CUVS_EXPECTS(new_codes->dl_tensor.shape[1] == int64_t(cols), "new_codes must have %u columns", cols);
+    if (contiguous) {
+      ivf_pq::helpers::codepacker::extend_list_with_contiguous_codes(*res_of(res), ix, data, ids, uint32_t(n), label);
+    } else {
+      ivf_pq::helpers::codepacker::extend_list_with_codes(*res_of(res), ix, data, ids, uint32_t(n), label);
+    }
+  });
+}
+
+extern "C" cuvsError_t cuvsIvfPqHelpersExtendList(cuvsResources_t res, cuvsIvfPqIndex_t index,
+                                                  DLManagedTensor* new_vectors, DLManagedTensor* new_indices,
+                                                  uint32_t label)
+{
+  return translate_exceptions([=] {
+    auto* ix = index_of(index);
+    CUVS_EXPECTS(new_vectors != nullptr, "null new_vectors");
+    const DLTensor& t = new_vectors->dl_tensor;
+    auto et           = elem_of_dtype(t.dtype, "new_vectors");
+    void* data        = checked_data(new_vectors, t.dtype.code, t.dtype.bits, 2, true, "new_vectors");
+    auto* ids = static_cast<const int64_t*>(checked_data(new_indices, kDLInt, 64, 1, true, "new_indices"));
+    CUVS_EXPECTS(t.shape[1] == int64_t(ix->dim()), "new_vectors has the wrong number of columns");
+    CUVS_EXPECTS(new_indices->dl_tensor.shape[0] == t.shape[0], "new_indices must have one entry per new vector");
+    ivf_pq::helpers::codepacker::extend_list(*res_of(res), ix, data, et, ids, uint32_t(t.shape[0]), label);
+  });
+}
+
+extern "C" cuvsError_t cuvsIvfPqHelpersEraseList(cuvsResources_t res, cuvsIvfPqIndex_t index, uint32_t label)
+{
+  return translate_exceptions([=] { ivf_pq::helpers::erase_list(*res_of(res), index_of(index), label); });
+}
+
+extern "C" cuvsError_t cuvsIvfPqHelpersResetIndex(cuvsResources_t res, cuvsIvfPqIndex_t index)
+{
+  return translate_exceptions([=] { ivf_pq::helpers::reset_index(*res_of(res), index_of(index)); });
 }
 
 // ------------------------------------------------------------------------------------------------

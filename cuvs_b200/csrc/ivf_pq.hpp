@@ -339,6 +339,42 @@ void unpack_contiguous_list_data(raft::resources& res, const index<int64_t>& idx
 // `centers` is [n_lists, centers_cols] with centers_cols == dim (norms are computed) or dim_ext.
 void set_model(raft::resources& res, index<int64_t>* idx, const float* pq_centers, const float* centers,
                uint32_t centers_cols, const float* centers_rot, const float* rotation_matrix);
+
+// Single-list helpers of the reference (ivf_pq.hpp:2564-3128, cpp/src/neighbors/ivf_pq/
+// ivf_pq_build_common.cu:30-225).  All pointers are device pointers; all calls are asynchronous on
+// the handle's stream unless they change a list's size.  `in_cluster_indices`, where given, selects
+// rows by their position in the list instead of the range [offset, offset + n_rows).
+namespace codepacker {
+using helpers::unpack_contiguous_list_data;
+// Codes of list rows, one code per byte: out_codes u8 [n_rows, pq_dim].
+void unpack_list_data(raft::resources& res, const index<int64_t>& idx, uint8_t* out_codes,
+                      uint32_t n_rows, uint32_t label, uint32_t offset,
+                      const uint32_t* in_cluster_indices = nullptr);
+// Overwrite list rows [offset, offset + n_rows) with codes given one per byte, u8 [n_rows, pq_dim].
+// No allocation: the rows must exist.
+void pack_list_data(raft::resources& res, index<int64_t>* idx, const uint8_t* codes, uint32_t n_rows,
+                    uint32_t label, uint32_t offset);
+// Same with bit-packed rows, u8 [n_rows, ceil(pq_dim * pq_bits / 8)].
+void pack_contiguous_list_data(raft::resources& res, index<int64_t>* idx, const uint8_t* codes,
+                               uint32_t n_rows, uint32_t label, uint32_t offset);
+// Decode list rows back to the input space: out [n_rows, dim] of type `out_type`
+//   out[i, :] = mapping<T>( rotation^T * (pq_center(code(i, j)) + center_rot[label, j]) ).
+void reconstruct_list_data(raft::resources& res, const index<int64_t>& idx, void* out_vectors,
+                           elem_t out_type, uint32_t n_rows, uint32_t label, uint32_t offset,
+                           const uint32_t* in_cluster_indices = nullptr);
+// Append rows to one list, skipping the classification (and, with codes, the encoding):
+// new_codes u8 [n_rows, pq_dim] / [n_rows, ceil(pq_dim * pq_bits / 8)], new_indices i64 [n_rows].
+void extend_list_with_codes(raft::resources& res, index<int64_t>* idx, const uint8_t* new_codes,
+                            const int64_t* new_indices, uint32_t n_rows, uint32_t label);
+void extend_list_with_contiguous_codes(raft::resources& res, index<int64_t>* idx,
+                                       const uint8_t* new_codes, const int64_t* new_indices,
+                                       uint32_t n_rows, uint32_t label);
+void extend_list(raft::resources& res, index<int64_t>* idx, const void* new_vectors, elem_t dtype,
+                 const int64_t* new_indices, uint32_t n_rows, uint32_t label);
+}  // namespace codepacker
+// Remove all rows of one list / of every list (ivf_pq.hpp:3144, :3166).
+void erase_list(raft::resources& res, index<int64_t>* idx, uint32_t label);
+void reset_index(raft::resources& res, index<int64_t>* idx);
 }  // namespace helpers
 
 namespace detail {

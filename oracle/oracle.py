@@ -400,6 +400,51 @@ def pack_list_numpy(codes: np.ndarray, pq_bits: int) -> np.ndarray:
     return out
 
 
+def pack_contiguous(codes: np.ndarray, pq_bits: int) -> np.ndarray:
+    """[n, pq_dim] one code per byte -> bit-packed rows u8 [n, ceil(pq_dim * pq_bits / 8)], code j
+    at bits [j * pq_bits, (j + 1) * pq_bits) of the row's little-endian bit stream
+    (bitfield_view_t over the row, cpp/src/neighbors/ivf_pq/ivf_pq_codepacking.cuh:201-218)."""
+    codes = np.asarray(codes, dtype=np.uint8)
+    n, pq_dim = codes.shape
+    bits = ((codes[:, :, None] >> np.arange(pq_bits, dtype=np.uint8)) & 1).reshape(n, pq_dim * pq_bits)
+    pad = (-bits.shape[1]) % 8
+    bits = np.concatenate([bits, np.zeros((n, pad), dtype=np.uint8)], axis=1)
+    return np.packbits(bits.reshape(n, -1, 8), axis=2, bitorder="little").reshape(n, -1)
+
+
+def map_from_float(x: np.ndarray, dtype) -> np.ndarray:
+    """mapping<T> applied to f32 values (cpp/src/neighbors/detail/ann_utils.cuh:168-199): scale by
+    128 (int8) or 256 (uint8), then the C++ float -> integer cast (truncation toward zero)."""
+    dtype = np.dtype(dtype)
+    x = np.asarray(x, dtype=np.float32)
+    if dtype == np.int8:
+        return np.trunc(x * np.float32(128.0)).astype(np.int8)
+    if dtype == np.uint8:
+        return np.trunc(x * np.float32(256.0)).astype(np.uint8)
+    return x.astype(dtype)
+
+
+def reconstruct_list(ix: "OracleIndex", label: int, rows: np.ndarray) -> np.ndarray:
+    """Decoded vectors f32 [len(rows), dim] of rows of one list
+    (reconstruct_vectors + the product with the rotation matrix,
+    cpp/src/neighbors/ivf_pq/ivf_pq_build.cuh:519-571 and :593-676):
+    rotated[i, j, k] = pq_centers[j or label, k, code(i, j)] + centers_rot[label, j, k] in fp32,
+    out[i, :] = rotation^T @ rotated[i, :] (the reference calls a library GEMM there, whose summation
+    order is not specified; this restatement accumulates in float64 and callers compare with a
+    tolerance)."""
+    n = int(ix.list_sizes[label])
+    codes = unpack_list(ix.list_codes[label], n, ix.pq_dim, ix.pq_bits)[np.asarray(rows, dtype=np.int64)]
+    j = np.arange(ix.pq_dim)
+    if ix.codebook_kind == 1:
+        book = ix.pq_centers[label][None, :, :].repeat(ix.pq_dim, axis=0)    # [pq_dim, len, book]
+    else:
+        book = ix.pq_centers
+    dec = book[j[None, :], :, codes.astype(np.int64)]                        # [n, pq_dim, len]
+    rot = dec.astype(np.float32) + ix.centers_rot[label].reshape(1, ix.pq_dim, ix.pq_len)
+    rot = rot.reshape(len(codes), ix.rot_dim).astype(np.float32)
+    return (rot.astype(np.float64) @ ix.rotation.astype(np.float64)).astype(np.float32)
+
+
 # --------------------------------------------------------------------------------------------
 # search
 # --------------------------------------------------------------------------------------------

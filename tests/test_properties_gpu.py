@@ -113,8 +113,16 @@ def test_three_list_shards_merge_to_the_unsharded_result(big):
         parts.append(mg.search_with_probes(sp, shard, q, probes, K))
     assert total == N
     d, i = mg.merge_parts(torch.stack([p[0] for p in parts]), torch.stack([p[1] for p in parts]), True)
-    assert (i == i_full).all()
+    # distances bit for bit; ids wherever the distance is not shared with a neighbour in the row or
+    # with the k-th place (the merge orders equal distances by id, the one-index search by position
+    # in the probed lists, and f16 look-up tables do produce equal distances)
     assert (d.view(torch.int32) == d_full.view(torch.int32)).all()
+    tied = torch.zeros_like(i, dtype=torch.bool)
+    tied[:, 1:] |= d[:, 1:] == d[:, :-1]
+    tied[:, :-1] |= d[:, :-1] == d[:, 1:]
+    tied |= d == d[:, -1:]
+    assert ((i == i_full) | tied).all()
+    assert tied.float().mean().item() < 0.05
 
 
 def test_database_vectors_find_themselves(big):
