@@ -44,7 +44,8 @@ def biggest_list(g):
 def test_unpack_list_data_matches_the_layout(mods, oracle_mod, tmp_path, bits):
     ivf, H = mods
     O = oracle_mod
-    _, g = build_small(ivf, bits=bits, pq_dim=21 if bits != 8 else 20)
+    # pq_bits * pq_dim must be a multiple of 8; 22 and 24 leave a partly filled last 16-byte piece
+    _, g = build_small(ivf, bits=bits, pq_dim={4: 22, 5: 24, 6: 20, 7: 24, 8: 21}[bits])
     ix = to_oracle(ivf, O, g, tmp_path)
     label, n = biggest_list(g)
     want = O.unpack_list(ix.list_codes[label], n, ix.pq_dim, bits)
@@ -65,7 +66,7 @@ def test_unpack_list_data_matches_the_layout(mods, oracle_mod, tmp_path, bits):
 def test_pack_list_data_writes_the_layout(mods, oracle_mod, tmp_path, bits):
     ivf, H = mods
     O = oracle_mod
-    _, g = build_small(ivf, bits=bits, pq_dim=19)
+    _, g = build_small(ivf, bits=bits, pq_dim={4: 18, 5: 24, 7: 24, 8: 19}[bits])
     label, n = biggest_list(g)
     before = H.unpack_list_data(g, label).cpu().numpy()
     rng = np.random.default_rng(bits)
@@ -92,7 +93,7 @@ def test_pack_list_data_writes_the_layout(mods, oracle_mod, tmp_path, bits):
             == O.unpack_list(ix0.list_codes[other], m, ix0.pq_dim, bits)).all()
 
 
-@pytest.mark.parametrize("bits,kind,force_rot", [(8, "subspace", False), (5, "cluster", False),
+@pytest.mark.parametrize("bits,kind,force_rot", [(8, "subspace", False), (4, "cluster", False),
                                                  (6, "subspace", True)])
 def test_reconstruct_list_data(mods, oracle_mod, tmp_path, bits, kind, force_rot):
     ivf, H = mods

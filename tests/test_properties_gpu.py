@@ -122,7 +122,7 @@ def test_three_list_shards_merge_to_the_unsharded_result(big):
     tied[:, :-1] |= d[:, :-1] == d[:, 1:]
     tied |= d == d[:, -1:]
     assert ((i == i_full) | tied).all()
-    assert tied.float().mean().item() < 0.05
+    assert tied[:, :-1].float().mean().item() < 0.05      # the k-th place always counts as tied
 
 
 def test_database_vectors_find_themselves(big):
