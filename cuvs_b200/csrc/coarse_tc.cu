@@ -1051,7 +1051,8 @@ void split_centers_tf32(cudaStream_t stream, const float* centers, size_t n, flo
 void select_clusters_tc(raft::resources& res, const float* centers, const float* centers_hi,
                         const float* centers_lo, float cmax, uint32_t n_lists, uint32_t dim_ext,
                         float alpha, const float* fq, uint32_t n_queries, uint32_t n_probes,
-                        uint32_t* probes, float* scores_out, void* workspace, size_t workspace_bytes)
+                        uint32_t* probes, float* scores_out, void* workspace, size_t workspace_bytes,
+                        bool exact_operands)
 {
   CUVS_EXPECTS(alpha < 0.0f, "the tensor-core coarse search expects a negative scale");
   CUVS_EXPECTS(workspace_bytes >= coarse_tc_workspace_bytes(n_queries, n_lists, dim_ext),
@@ -1099,7 +1100,7 @@ void select_clusters_tc(raft::resources& res, const float* centers, const float*
   // Products of the TF32 split per K step: 3 (hi*hi + lo*hi + hi*lo, error ~ fp32 rounding),
   // 2 (without hi*lo: |error| <= 2^-11 |q||c|) or 1 (hi*hi only: <= 2^-10 |q||c|).  Fewer products
   // make the GEMM cheaper and the guard's error bound wider; the probes stay exact either way.
-  int products = tc_products_ref();
+  int products = exact_operands ? 1 : tc_products_ref();
   if (products == 0) {
     // adopt the verdict on the last batch of this handle, if it has arrived
     if (res.tc_redo_pending && cudaEventQuery(res.tc_redo_event) == cudaSuccess) {
@@ -1109,7 +1110,7 @@ void select_clusters_tc(raft::resources& res, const float* centers, const float*
     products = res.tc_products;
   }
   const float eps_rel = float(dim_ext + 8) * 2.4e-7f + 3.1e-5f +
-                        (products == 1 ? 9.8e-4f : (products == 2 ? 4.9e-4f : 0.0f));
+                        (exact_operands ? 0.0f : (products == 1 ? 9.8e-4f : (products == 2 ? 4.9e-4f : 0.0f)));
   auto launch = [&](auto kernel) {
     // every instantiation needs its shared-memory limit raised once
     static thread_local const void* configured[8] = {};
@@ -1180,7 +1181,7 @@ void select_clusters_tc(raft::resources& res, const float* centers, const float*
                                                        scores_out, words + 1);
   CUDA_TRY(cudaGetLastError());
   res.launches += 4;
-  if (tc_products_ref() == 0 && !res.tc_redo_pending && res.tc_products < 3) {
+  if (!exact_operands && tc_products_ref() == 0 && !res.tc_redo_pending && res.tc_products < 3) {
     // how many queries this batch redid exactly: read back without waiting, looked at before a later batch
     if (!res.tc_redo_event) { CUDA_TRY(cudaEventCreateWithFlags(&res.tc_redo_event, cudaEventDisableTiming)); }
     CUDA_TRY(cudaMemcpyAsync(res.pinned + 8, words + 1, 4, cudaMemcpyDeviceToHost, stream));

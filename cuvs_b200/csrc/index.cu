@@ -15,6 +15,7 @@
 #include <algorithm>
 #include <cstring>
 #include <fstream>
+#include <mutex>
 #include <cmath>
 #include <numeric>
 
@@ -72,6 +73,67 @@ __global__ void fill_i64_kernel(int64_t* p, size_t n, int64_t v)
   if (i < n) { p[i] = v; }
 }
 
+// int8 image of the padded centers (ivf_pq_index.cu:661-738): components scaled by 128 and clamped;
+// the squared norm x of column `dim` is spread over the m - 1 spare columns as y = round(x * 64 /
+// (m - 1)) each, the rounding remainder z = (y - round(y)) * 128 goes to column `dim`.
+__global__ void centers_to_int8_kernel(const float* __restrict__ centers, size_t n, uint32_t dim,
+                                       uint32_t dim_ext, uint32_t dim_ext8, float* __restrict__ out)
+{
+  const size_t ix = blockIdx.x * size_t(blockDim.x) + threadIdx.x;
+  if (ix >= n) { return; }
+  const uint32_t col = uint32_t(ix % dim_ext8);
+  const size_t row   = ix / dim_ext8;
+  int8_t v;
+  if (col < dim) {
+    v = static_cast<int8_t>(fmaxf(-128.0f, fminf(127.0f, __fmul_rn(centers[row * dim_ext + col], 128.0f))));
+  } else {
+    const float x = centers[row * dim_ext + dim];
+    const float c = __fdiv_rn(64.0f, static_cast<float>(dim_ext8 - dim - 1));
+    const float y = fmaxf(-128.0f, fminf(127.0f, __fmul_rn(x, c)));
+    const float z = fmaxf(-128.0f, fminf(127.0f, __fmul_rn(__fsub_rn(y, roundf(y)), 128.0f)));
+    v             = col > dim ? static_cast<int8_t>(roundf(y)) : static_cast<int8_t>(z);
+  }
+  out[ix] = static_cast<float>(v);
+}
+
+// mapping<int8_t> of the rotation matrix (ivf_pq_index.cu:624-658; ann_utils.cuh:184-191).
+__global__ void rotation_to_int8_kernel(const float* __restrict__ rot, size_t n, float* __restrict__ out)
+{
+  const size_t ix = blockIdx.x * size_t(blockDim.x) + threadIdx.x;
+  if (ix < n) { out[ix] = static_cast<float>(static_cast<int8_t>(__fmul_rn(rot[ix], 128.0f))); }
+}
+
+index<int64_t>::int8_operands index<int64_t>::int8_coarse_operands(cudaStream_t stream) const
+{
+  static std::mutex lock;  // first use may come from several searching threads at once
+  std::lock_guard<std::mutex> guard(lock);
+  const uint32_t d8 = dim_ext_int8();
+  const size_t nc = size_t(n_lists_) * d8, nr = size_t(rot_dim()) * dim_;
+  if (centers_i8f_.size() != nc || rotation_i8f_.size() != nr) {
+    centers_i8f_.resize(nc);
+    rotation_i8f_.resize(nr);
+    centers_to_int8_kernel<<<unsigned(ceildiv<size_t>(nc, 256)), 256, 0, stream>>>(
+      centers_.data(), nc, dim_, dim_ext(), d8, centers_i8f_.data());
+    rotation_to_int8_kernel<<<unsigned(ceildiv<size_t>(nr, 256)), 256, 0, stream>>>(rotation_.data(), nr,
+                                                                                     rotation_i8f_.data());
+    CUDA_TRY(cudaGetLastError());
+    std::vector<float> hc(nc);
+    CUDA_TRY(cudaMemcpyAsync(hc.data(), centers_i8f_.data(), nc * 4, cudaMemcpyDeviceToHost, stream));
+    CUDA_TRY(cudaStreamSynchronize(stream));  // other streams may use the arrays right after this call
+    double mx = 0.0;
+    for (uint32_t l = 0; l < n_lists_; l++) {
+      double ss = 0.0;
+      for (uint32_t k = 0; k < d8; k++) {
+        const double v = hc[size_t(l) * d8 + k];
+        ss += v * v;
+      }
+      mx = std::max(mx, ss);
+    }
+    centers_i8f_max_norm_ = float(std::sqrt(mx)) * 1.0001f;
+  }
+  return {centers_i8f_.data(), rotation_i8f_.data(), centers_i8f_max_norm_};
+}
+
 void index<int64_t>::allocate_lists(const std::vector<uint32_t>& sizes, cudaStream_t stream)
 {
   CUVS_EXPECTS(sizes.size() == n_lists_, "list size vector has the wrong length");
@@ -119,6 +181,8 @@ void index<int64_t>::recompute_internal_state(cudaStream_t stream)
     }
   }
   rotation_is_identity_ = ident;
+  centers_i8f_.reset();  // rebuilt from the current model on next use
+  rotation_i8f_.reset();
   // derived data of the tensor-core coarse search
   const size_t nc = size_t(n_lists_) * dim_ext();
   std::vector<float> hc(nc);

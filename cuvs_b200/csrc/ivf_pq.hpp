@@ -205,6 +205,17 @@ class index<int64_t> {
   float* centers_lo() const { return centers_lo_.data(); }
   float centers_max_norm() const { return centers_max_norm_; }
   uint64_t total_rows_padded() const { return h_row_off_.empty() ? 0 : h_row_off_.back(); }
+  // Operands of the int8 coarse search (coarse_search_dtype = CUDA_R_8I; centers_int8 and
+  // rotation_matrix_int8 of cpp/src/neighbors/ivf_pq_index.cu:624-738), created on first use.  The
+  // int8 values are held as fp32 numbers: every one is exact in TF32, so the tensor-core product
+  // with fp32 accumulation gives the reference's int32 scores exactly.
+  uint32_t dim_ext_int8() const { return cuvs_b200::round_up(dim_ + 2, 16u); }  // ivf_pq_index.cu:667
+  struct int8_operands {
+    const float* centers;   // [n_lists, dim_ext_int8]
+    const float* rotation;  // [rot_dim, dim]
+    float centers_max_norm;
+  };
+  int8_operands int8_coarse_operands(cudaStream_t stream) const;
 
   // (Re)create the arenas for the given list sizes; contents are zero codes / -1 ids.
   void allocate_lists(const std::vector<uint32_t>& sizes, cudaStream_t stream);
@@ -215,6 +226,8 @@ class index<int64_t> {
   dev_array<float> pq_centers_, centers_, centers_rot_, rotation_;
   dev_array<float> centers_hi_, centers_lo_;
   float centers_max_norm_ = 0.0f;
+  mutable dev_array<float> centers_i8f_, rotation_i8f_;
+  mutable float centers_i8f_max_norm_ = 0.0f;
   dev_array<uint32_t> list_sizes_;
   dev_array<uint64_t> row_off_;
   dev_array<uint8_t> codes_;

@@ -492,14 +492,14 @@ __device__ __forceinline__ float lds_f32_off(uint32_t a)
   asm volatile("ld.shared.f32 %0, [%1+%2];" : "=f"(v) : "r"(a), "n"(OFF));
   return v;
 }
+// acc += float(lut[a + OFF]) in one mixed-precision add (the fp16 operand widens exactly, the sum is
+// rounded once in fp32: the same value as convert-then-add).
 template <uint32_t OFF>
-__device__ __forceinline__ float lds_f16_as_f32_off(uint32_t a)
+__device__ __forceinline__ void lds_f16_add_f32_off(uint32_t a, float& acc)
 {
-  float v;
-  asm volatile("{\n\t.reg .b16 h;\n\tld.shared.b16 h, [%1+%2];\n\tcvt.f32.f16 %0, h;\n\t}"
-               : "=f"(v)
+  asm volatile("{\n\t.reg .b16 h;\n\tld.shared.b16 h, [%1+%2];\n\tadd.rn.f32.f16 %0, h, %0;\n\t}"
+               : "+f"(acc)
                : "r"(a), "n"(OFF));
-  return v;
 }
 template <uint32_t OFF>
 __device__ __forceinline__ __half lds_f16_off(uint32_t a)
@@ -535,7 +535,7 @@ struct accum {
       if constexpr (LutKind == LUT_F32) {
         f += lds_f32_off<OFF>(entry);
       } else if constexpr (LutKind == LUT_F16) {
-        f += lds_f16_as_f32_off<OFF>(entry);
+        lds_f16_add_f32_off<OFF>(entry, f);
       } else {
         f += fp8_to_float<IsIP>(lds_u8_off<OFF>(entry));
       }

@@ -61,9 +61,25 @@ template <> __device__ __forceinline__ float map_to_float<uint8_t>(uint8_t x)
   return __fmul_rn(float(x), 1.0f / 256.0f);
 }
 
+// mapping<int8_t> (cpp/src/neighbors/detail/ann_utils.cuh:178-209): floating types scale by 128 in
+// their own precision and convert, int8 passes, uint8 halves.
+template <typename T>
+__device__ __forceinline__ int8_t map_to_int8(T x);
+template <> __device__ __forceinline__ int8_t map_to_int8<float>(float x) { return static_cast<int8_t>(__fmul_rn(x, 128.0f)); }
+template <> __device__ __forceinline__ int8_t map_to_int8<__half>(__half x)
+{
+  return static_cast<int8_t>(__hmul(x, __float2half(128.0f)));
+}
+template <> __device__ __forceinline__ int8_t map_to_int8<int8_t>(int8_t x) { return x; }
+template <> __device__ __forceinline__ int8_t map_to_int8<uint8_t>(uint8_t x) { return static_cast<int8_t>(x >> 1); }
+
 // One block per query.  fq = mapping<float>(query) padded to dim_ext with -0.5 (L2) or 0 in column
 // `dim`; rot_q = R * fq[:dim], each output accumulated by one thread in ascending k with FMA.
-template <typename T>
+// kInt8 (coarse_search_dtype = CUDA_R_8I, ivf_pq_search.cuh:171-256 and :996-1025): fq holds the
+// int8 image of the query as numbers, dim_ext = round_up(dim + 2, 16) with 1 - m in column `dim` and
+// -128 (L2) or 0 in the m - 1 columns after it; `rotation` is the int8 image of the rotation matrix
+// and rot_q = (R8 * q8) / 128^2 (sums of integers below 2^24: exact in fp32 in any order).
+template <typename T, bool kInt8>
 __global__ void prep_queries_kernel(const T* __restrict__ queries, uint32_t dim, uint32_t dim_ext,
                                     uint32_t rot_dim, int is_l2, int cosine, int identity,
                                     const float* __restrict__ rotation, float* __restrict__ fq,
@@ -78,8 +94,11 @@ __global__ void prep_queries_kernel(const T* __restrict__ queries, uint32_t dim,
   for (uint32_t i = threadIdx.x; i < dim_ext; i += blockDim.x) {
     float v = 0.0f;
     if (i < dim) {
-      v      = map_to_float<T>(src[i]);
+      v      = kInt8 ? static_cast<float>(map_to_int8<T>(src[i])) : map_to_float<T>(src[i]);
       s_q[i] = v;
+    } else if constexpr (kInt8) {
+      const uint32_t m = dim_ext - dim;
+      v = (m == 1 || i > dim) ? (is_l2 ? -128.0f : 0.0f) : static_cast<float>(1 - int(m));
     } else if (i == dim && is_l2) {
       v = -0.5f;
     }
@@ -95,6 +114,7 @@ __global__ void prep_queries_kernel(const T* __restrict__ queries, uint32_t dim,
       const float* row = rotation + size_t(r) * dim;
       acc              = 0.0f;
       for (uint32_t k = 0; k < dim; k++) { acc = __fmaf_rn(__ldg(row + k), s_q[k], acc); }
+      if constexpr (kInt8) { acc = __fmul_rn(acc, 1.0f / 16384.0f); }
     }
     if (cosine) {
       s_r[r] = acc;
@@ -469,35 +489,34 @@ int& coarse_mode_ref()
 int coarse_mode() { return coarse_mode_ref(); }
 
 void launch_prep(raft::resources& res, const index<int64_t>& idx, const void* qptr, elem_t qtype,
-                 uint32_t nq, float* d_fq, float* d_rq)
+                 uint32_t nq, float* d_fq, float* d_rq, const float* rotation_int8 = nullptr)
 {
   const DistanceType metric = idx.metric();
   const int is_l2  = metric == DistanceType::L2Expanded || metric == DistanceType::L2SqrtExpanded;
   const int cosine = metric == DistanceType::CosineExpanded;
-  const int ident  = idx.rotation_is_identity();
+  const bool i8    = rotation_int8 != nullptr;
+  // the int8 image of an identity rotation is 127 on the diagonal: no shortcut there
+  const int ident  = !i8 && idx.rotation_is_identity();
+  const float* rot = i8 ? rotation_int8 : idx.rotation_matrix();
+  const uint32_t dim_ext = i8 ? idx.dim_ext_int8() : idx.dim_ext();
   const size_t smem = (size_t(idx.dim()) + idx.rot_dim()) * 4;
   const int threads = 128;
   cudaStream_t stream = res.stream;
+  auto launch = [&](auto* q) {
+    using T = std::remove_const_t<std::remove_pointer_t<decltype(q)>>;
+    if (i8) {
+      prep_queries_kernel<T, true><<<nq, threads, smem, stream>>>(q, idx.dim(), dim_ext, idx.rot_dim(), is_l2,
+                                                                  cosine, ident, rot, d_fq, d_rq);
+    } else {
+      prep_queries_kernel<T, false><<<nq, threads, smem, stream>>>(q, idx.dim(), dim_ext, idx.rot_dim(), is_l2,
+                                                                   cosine, ident, rot, d_fq, d_rq);
+    }
+  };
   switch (qtype) {
-    case elem_t::f32:
-      prep_queries_kernel<float><<<nq, threads, smem, stream>>>(
-        reinterpret_cast<const float*>(qptr), idx.dim(), idx.dim_ext(), idx.rot_dim(), is_l2, cosine,
-        ident, idx.rotation_matrix(), d_fq, d_rq);
-      break;
-    case elem_t::f16:
-      prep_queries_kernel<__half><<<nq, threads, smem, stream>>>(
-        reinterpret_cast<const __half*>(qptr), idx.dim(), idx.dim_ext(), idx.rot_dim(), is_l2, cosine,
-        ident, idx.rotation_matrix(), d_fq, d_rq);
-      break;
-    case elem_t::i8:
-      prep_queries_kernel<int8_t><<<nq, threads, smem, stream>>>(
-        reinterpret_cast<const int8_t*>(qptr), idx.dim(), idx.dim_ext(), idx.rot_dim(), is_l2, cosine,
-        ident, idx.rotation_matrix(), d_fq, d_rq);
-      break;
-    default:
-      prep_queries_kernel<uint8_t><<<nq, threads, smem, stream>>>(
-        reinterpret_cast<const uint8_t*>(qptr), idx.dim(), idx.dim_ext(), idx.rot_dim(), is_l2, cosine,
-        ident, idx.rotation_matrix(), d_fq, d_rq);
+    case elem_t::f32: launch(reinterpret_cast<const float*>(qptr)); break;
+    case elem_t::f16: launch(reinterpret_cast<const __half*>(qptr)); break;
+    case elem_t::i8: launch(reinterpret_cast<const int8_t*>(qptr)); break;
+    default: launch(reinterpret_cast<const uint8_t*>(qptr));
   }
   CUDA_TRY(cudaGetLastError());
   res.launches++;
@@ -592,8 +611,12 @@ void search_any(raft::resources& res, const search_params& params, const index<i
                k, size_t(idx.size()));
   CUVS_EXPECTS(params.n_probes > 0,
                "n_probes (number of clusters to probe in the search) must be positive.");
-  CUVS_EXPECTS(params.coarse_search_dtype == CUDA_R_32F,
-               "Unsupported coarse_search_dtype (only CUDA_R_32F is supported by this engine)");
+  CUVS_EXPECTS(params.coarse_search_dtype == CUDA_R_32F || params.coarse_search_dtype == CUDA_R_8I,
+               "Unsupported coarse_search_dtype (only CUDA_R_32F and CUDA_R_8I are supported by this engine)");
+  const bool coarse_i8 = params.coarse_search_dtype == CUDA_R_8I;
+  // integer scores and rotated queries stay exact in fp32 while dim_ext * 128 * 128 <= 2^24
+  CUVS_EXPECTS(!coarse_i8 || idx.dim_ext_int8() <= 1024,
+               "coarse_search_dtype CUDA_R_8I: dim = %u is too large for this engine (at most 1022)", idx.dim());
   const bool out_half = params.internal_distance_dtype == CUDA_R_16F;
   const int lut_kind =
     params.lut_dtype == CUDA_R_32F ? LUT_F32 : (params.lut_dtype == CUDA_R_16F ? LUT_F16 : LUT_FP8);
@@ -645,7 +668,11 @@ void search_any(raft::resources& res, const search_params& params, const index<i
 
   // ---- workspace ----
   ws_layout lay;
-  const size_t o_fq      = lay.add(size_t(batch) * idx.dim_ext() * 4);
+  // the coarse stage works on the padded fp32 rows, or on the int8 images of queries and centers
+  const uint32_t cdim_ext = coarse_i8 ? idx.dim_ext_int8() : idx.dim_ext();
+  index<int64_t>::int8_operands op8{};
+  if (coarse_i8) { op8 = idx.int8_coarse_operands(stream); }
+  const size_t o_fq      = lay.add(size_t(batch) * cdim_ext * 4);
   const size_t o_rq      = lay.add(size_t(batch) * idx.rot_dim() * 4);
   const size_t o_probes  = lay.add(n_pairs_max * 4);
   const size_t o_chunk   = lay.add(n_pairs_max * 4);
@@ -655,10 +682,10 @@ void search_any(raft::resources& res, const search_params& params, const index<i
   const size_t o_counter = lay.add(256);
   const size_t o_keys    = lay.add(store_all ? size_t(batch) * k * 8 : n_pairs_max * k * 8);
   const size_t o_all     = lay.add(store_all ? size_t(batch) * max_samples * 4 : 0);
-  const bool use_tc = coarse_mode() != 1 && coarse_tc_usable(n_lists, n_probes, idx.dim_ext());
+  const bool use_tc = coarse_mode() != 1 && coarse_tc_usable(n_lists, n_probes, cdim_ext);
   const size_t coarse_ws =
     given_probes ? 0
-                 : (use_tc ? coarse_tc_workspace_bytes(batch, n_lists, idx.dim_ext())
+                 : (use_tc ? coarse_tc_workspace_bytes(batch, n_lists, cdim_ext)
                            : coarse_workspace_bytes(batch, n_lists, n_probes));
   const size_t o_coarse  = lay.add(coarse_ws);
   res.ws.reserve(lay.total());
@@ -685,13 +712,23 @@ void search_any(raft::resources& res, const search_params& params, const index<i
     if (stats) { res.stats_mark(ev, 0); }
 
     // 1. cast / pad / rotate
-    launch_prep(res, idx, qptr, qtype, nq, d_fq, d_rq);
+    launch_prep(res, idx, qptr, qtype, nq, d_fq, d_rq, coarse_i8 ? op8.rotation : nullptr);
 
     if (stats) { res.stats_mark(ev, 1); }
     // 2. coarse selection: probes sorted by (score, list id)
     if (given_probes) {
       CUDA_TRY(cudaMemcpyAsync(d_probes, given_probes + size_t(q0) * n_probes, size_t(nq) * n_probes * 4,
                                cudaMemcpyDeviceToDevice, stream));
+    } else if (coarse_i8) {
+      // integer operands are exact in TF32 and their sums in fp32: one product, no split error
+      if (use_tc) {
+        select_clusters_tc(res, op8.centers, op8.centers, op8.centers, op8.centers_max_norm, n_lists, cdim_ext,
+                           is_l2 ? -2.0f : -1.0f, d_fq, nq, n_probes, d_probes, nullptr, d_coarse, coarse_ws,
+                           /*exact_operands=*/true);
+      } else {
+        select_clusters(res, op8.centers, n_lists, cdim_ext, is_l2 ? -2.0f : -1.0f, d_fq, nq, n_probes,
+                        d_probes, nullptr, d_coarse, coarse_ws);
+      }
     } else if (use_tc) {
       select_clusters_tc(res, idx.centers(), idx.centers_hi(), idx.centers_lo(), idx.centers_max_norm(),
                          n_lists, idx.dim_ext(), is_l2 ? -2.0f : -1.0f, d_fq, nq, n_probes, d_probes,

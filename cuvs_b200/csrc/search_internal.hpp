@@ -27,13 +27,16 @@ void select_rows(raft::resources& res, const float* rows, uint32_t n_rows, uint3
 
 // Tensor-core coarse stage (coarse_tc.cu): same contract and bit-identical probes as
 // select_clusters; `centers_hi/lo` are the TF32 split of `centers`, `cmax` the largest row norm.
+// `exact_operands`: every operand is exact in TF32 and every partial sum in fp32 (small integers):
+// one product per K step, and the guard allows for no split error.
 bool coarse_tc_usable(uint32_t n_lists, uint32_t n_probes, uint32_t dim_ext);
 size_t coarse_tc_workspace_bytes(uint32_t n_queries, uint32_t n_lists, uint32_t dim_ext);
 void split_centers_tf32(cudaStream_t stream, const float* centers, size_t n, float* hi, float* lo);
 void select_clusters_tc(raft::resources& res, const float* centers, const float* centers_hi,
                         const float* centers_lo, float cmax, uint32_t n_lists, uint32_t dim_ext,
                         float alpha, const float* fq, uint32_t n_queries, uint32_t n_probes,
-                        uint32_t* probes, float* scores_out, void* workspace, size_t workspace_bytes);
+                        uint32_t* probes, float* scores_out, void* workspace, size_t workspace_bytes,
+                        bool exact_operands = false);
 void coarse_tc_status(raft::resources& res, const void* workspace, uint32_t n_queries, uint32_t n_lists,
                       uint32_t dim_ext, uint32_t* error, uint32_t* n_fallback);
 

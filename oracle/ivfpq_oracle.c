@@ -553,6 +553,137 @@ ORC_EXPORT void orc_select_clusters(const orc_index* ix, const float* fq_ext, ui
   }
 }
 
+/* ============================ int8 coarse search (coarse_search_dtype = CUDA_R_8I) =========== */
+
+/* Device conversion float -> int8 of `static_cast<int8_t>(x)`: toward zero, clamped to the range of
+ * the target type (the behaviour of the device's float-to-integer conversion; NaN gives 0). */
+static int8_t f32_to_i8(float x)
+{
+  if (x != x) { return 0; }
+  if (x >= 127.0f) { return 127; }
+  if (x <= -128.0f) { return -128; }
+  return (int8_t)x;
+}
+
+ORC_EXPORT uint32_t orc_dim_ext_int8(uint32_t dim) { return (dim + 2 + 15) / 16 * 16; } /* ivf_pq_index.cu:667 */
+
+/* centers_int8 (cpp/src/neighbors/ivf_pq_index.cu:661-738): out [n_lists, dim_ext_int8]. */
+ORC_EXPORT void orc_centers_int8(const orc_index* ix, int8_t* out)
+{
+  const uint32_t d8 = orc_dim_ext_int8(ix->dim);
+  for (uint32_t row = 0; row < ix->n_lists; row++) {
+    const float* in = ix->centers + (size_t)row * ix->dim_ext;
+    for (uint32_t col = 0; col < d8; col++) {
+      int8_t v;
+      if (col < ix->dim) {
+        v = (int8_t)fmaxf(-128.0f, fminf(127.0f, in[col] * 128.0f));
+      } else {
+        const float x = in[ix->dim];
+        const float c = 64.0f / (float)(d8 - ix->dim - 1);
+        const float y = fmaxf(-128.0f, fminf(127.0f, x * c));
+        const float z = fmaxf(-128.0f, fminf(127.0f, (y - roundf(y)) * 128.0f));
+        v             = col > ix->dim ? (int8_t)roundf(y) : (int8_t)z;
+      }
+      out[(size_t)row * d8 + col] = v;
+    }
+  }
+}
+
+/* rotation_matrix_int8 (ivf_pq_index.cu:624-658): mapping<int8_t> of every element. */
+ORC_EXPORT void orc_rotation_int8(const orc_index* ix, int8_t* out)
+{
+  const size_t n = (size_t)ix->rot_dim * ix->dim;
+  for (size_t i = 0; i < n; i++) { out[i] = f32_to_i8(ix->rotation[i] * 128.0f); }
+}
+
+/* mapping<int8_t> of a query (ann_utils.cuh:178-209). */
+static void map_query_int8(const void* q, int qtype, uint32_t dim, int8_t* out)
+{
+  switch (qtype) {
+    case Q_F32:
+      for (uint32_t i = 0; i < dim; i++) { out[i] = f32_to_i8(((const float*)q)[i] * 128.0f); }
+      break;
+    case Q_F16: /* the product with 128 is exact in half precision */
+      for (uint32_t i = 0; i < dim; i++) { out[i] = f32_to_i8(f16_to_f32(((const uint16_t*)q)[i]) * 128.0f); }
+      break;
+    case Q_I8: memcpy(out, q, dim); break;
+    default:
+      for (uint32_t i = 0; i < dim; i++) { out[i] = (int8_t)(((const uint8_t*)q)[i] >> 1); }
+  }
+}
+
+/* Queries of the int8 coarse search (ivf_pq_search.cuh:171-256) and their rotation
+ * (:996-1025, alpha = 1/128/128): q8_ext [n_q, dim_ext_int8], rot_q [n_q, rot_dim]. */
+ORC_EXPORT void orc_prepare_queries_int8(const orc_index* ix, const void* queries, int qtype, uint32_t n_q,
+                                         const int8_t* rot8, int8_t* q8_ext, float* rot_q)
+{
+  init_tables();
+  const uint32_t d8 = orc_dim_ext_int8(ix->dim);
+  const uint32_t m  = d8 - ix->dim;
+  const int8_t norm_factor = is_l2(ix->metric) ? -128 : 0;
+  const size_t qs   = qtype_size(qtype);
+  for (uint32_t q = 0; q < n_q; q++) {
+    int8_t* f = q8_ext + (size_t)q * d8;
+    map_query_int8((const uint8_t*)queries + (size_t)q * ix->dim * qs, qtype, ix->dim, f);
+    for (uint32_t col = ix->dim; col < d8; col++) {
+      f[col] = (m == 1 || col > ix->dim) ? norm_factor : (int8_t)(1 - (int)m);
+    }
+    float* r = rot_q + (size_t)q * ix->rot_dim;
+    for (uint32_t i = 0; i < ix->rot_dim; i++) {
+      const int8_t* row = rot8 + (size_t)i * ix->dim;
+      int32_t acc       = 0;
+      for (uint32_t k = 0; k < ix->dim; k++) { acc += (int32_t)row[k] * (int32_t)f[k]; }
+      r[i] = (float)acc * (1.0f / 128.0f / 128.0f);
+    }
+    if (ix->metric == M_COSINE) {
+      float ss = 0.0f;
+      for (uint32_t i = 0; i < ix->rot_dim; i++) { ss = fmaf(r[i], r[i], ss); }
+      float nrm = sqrtf(ss);
+      if (nrm > 0.0f) {
+        for (uint32_t i = 0; i < ix->rot_dim; i++) { r[i] = r[i] / nrm; }
+      }
+    }
+  }
+}
+
+typedef struct {
+  int32_t s;
+  uint32_t i;
+} icand_t;
+static int icand_cmp(const void* a, const void* b)
+{
+  const icand_t x = *(const icand_t*)a, y = *(const icand_t*)b;
+  if (x.s != y.s) { return x.s < y.s ? -1 : 1; }
+  return x.i < y.i ? -1 : (x.i > y.i ? 1 : 0);
+}
+
+/* int32 scores alpha * <c8, q8> (alpha = -2 for L2, -1 otherwise), the n_probes smallest by
+ * (score, list id).  The reference's selection does not define the order of equal scores. */
+ORC_EXPORT void orc_select_clusters_int8(const orc_index* ix, const int8_t* c8, const int8_t* q8_ext,
+                                         uint32_t n_q, uint32_t n_probes, uint32_t* probes, int32_t* probe_scores)
+{
+  const uint32_t d8   = orc_dim_ext_int8(ix->dim);
+  const int32_t alpha = is_l2(ix->metric) ? -2 : -1;
+  if (n_probes > ix->n_lists) { n_probes = ix->n_lists; }
+  icand_t* all = (icand_t*)malloc((size_t)ix->n_lists * sizeof(icand_t));
+  for (uint32_t q = 0; q < n_q; q++) {
+    const int8_t* f = q8_ext + (size_t)q * d8;
+    for (uint32_t l = 0; l < ix->n_lists; l++) {
+      const int8_t* c = c8 + (size_t)l * d8;
+      int32_t acc     = 0;
+      for (uint32_t k = 0; k < d8; k++) { acc += (int32_t)c[k] * (int32_t)f[k]; }
+      all[l].s = alpha * acc;
+      all[l].i = l;
+    }
+    qsort(all, ix->n_lists, sizeof(icand_t), icand_cmp);
+    for (uint32_t p = 0; p < n_probes; p++) {
+      probes[(size_t)q * n_probes + p] = all[p].i;
+      if (probe_scores) { probe_scores[(size_t)q * n_probes + p] = all[p].s; }
+    }
+  }
+  free(all);
+}
+
 /* LUT of one (query, list) pair in its storage type (4, 2 or 1 bytes per entry). */
 ORC_EXPORT void orc_build_lut(const orc_index* ix, uint32_t label, const float* rot_q, int lut_dtype,
                               void* out)

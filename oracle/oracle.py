@@ -482,6 +482,55 @@ def select_clusters(ix: OracleIndex, fq: np.ndarray, n_probes: int, want_all: bo
     return (probes, scores, all_scores) if want_all else (probes, scores)
 
 
+def int8_operands(ix: OracleIndex):
+    """(centers_int8 [n_lists, dim_ext_int8], rotation_int8 [rot_dim, dim]) of the int8 coarse search
+    (cpp/src/neighbors/ivf_pq_index.cu:624-738)."""
+    d8 = int(lib().orc_dim_ext_int8(C.c_uint32(ix.dim)))
+    c8 = np.zeros((ix.n_lists, d8), dtype=np.int8)
+    r8 = np.zeros((ix.rot_dim, ix.dim), dtype=np.int8)
+    s = ix.c_struct()
+    lib().orc_centers_int8(C.byref(s), _ptr(c8))
+    lib().orc_rotation_int8(C.byref(s), _ptr(r8))
+    return c8, r8
+
+
+def prepare_queries_int8(ix: OracleIndex, queries: np.ndarray, r8: np.ndarray):
+    q = np.ascontiguousarray(queries)
+    n_q = q.shape[0]
+    d8 = int(lib().orc_dim_ext_int8(C.c_uint32(ix.dim)))
+    q8 = np.zeros((n_q, d8), dtype=np.int8)
+    rq = np.zeros((n_q, ix.rot_dim), dtype=np.float32)
+    s = ix.c_struct()
+    lib().orc_prepare_queries_int8(C.byref(s), _ptr(q), C.c_int(_QTYPE[q.dtype]), C.c_uint32(n_q),
+                                   _ptr(r8), _ptr(q8), _ptr(rq))
+    return q8, rq
+
+
+def select_clusters_int8(ix: OracleIndex, c8: np.ndarray, q8: np.ndarray, n_probes: int):
+    n_q = q8.shape[0]
+    n_probes = min(n_probes, ix.n_lists)
+    probes = np.zeros((n_q, n_probes), dtype=np.uint32)
+    scores = np.zeros((n_q, n_probes), dtype=np.int32)
+    s = ix.c_struct()
+    lib().orc_select_clusters_int8(C.byref(s), _ptr(c8), _ptr(q8), C.c_uint32(n_q),
+                                   C.c_uint32(n_probes), _ptr(probes), _ptr(scores))
+    return probes, scores
+
+
+def search_int8_coarse(ix: OracleIndex, queries: np.ndarray, k: int, n_probes: int = 20,
+                       lut_dtype=CUDA_R_32F, internal_dtype=CUDA_R_32F, return_probes=False):
+    """search with coarse_search_dtype = CUDA_R_8I (ivf_pq_search.cuh:171-256, :926-1048): int8 images
+    of centers, rotation matrix and queries, int32 coarse scores, rotated queries (R8 q8) / 128^2;
+    the fine search is the usual one."""
+    q = np.ascontiguousarray(queries)
+    c8, r8 = int8_operands(ix)
+    q8, rq = prepare_queries_int8(ix, q, r8)
+    probes, scores = select_clusters_int8(ix, c8, q8, n_probes)
+    scale = {np.dtype(np.uint8): 256.0, np.dtype(np.int8): 128.0}.get(q.dtype, 1.0)
+    ds, nb, _ = search_probes(ix, rq, probes, k, lut_dtype, internal_dtype, scale)
+    return (ds, nb, probes, scores) if return_probes else (ds, nb)
+
+
 def build_lut(ix: OracleIndex, label: int, rot_q: np.ndarray, lut_dtype: int) -> np.ndarray:
     n = ix.pq_dim << ix.pq_bits
     dt = {CUDA_R_32F: np.float32, CUDA_R_16F: np.float16, CUDA_R_8U: np.uint8}[lut_dtype]

@@ -189,3 +189,41 @@ def test_multi_gpu_index_file_round_trip(oracle_mod, tmp_path):
         for l in range(a.n_lists):
             s = int(a.list_sizes[l])
             assert (np.asarray(a.list_ids[l][:s]) == np.asarray(b.list_ids[l][:s])).all()
+
+
+def test_int8_coarse_search_restatement(oracle_mod):
+    """coarse_search_dtype = CUDA_R_8I (ivf_pq_index.cu:661-738, ivf_pq_search.cuh:171-256): the int8
+    operands encode 128^2 * (<q, c> - |c|^2 / 2) up to quantisation, so the int32 scores order the
+    lists nearly as the fp32 scores do, and the search built on them keeps its recall."""
+    O = oracle_mod
+    rng = np.random.default_rng(11)
+    cent = rng.uniform(-0.6, 0.6, (40, 32)).astype(np.float32)
+    x = (cent[rng.integers(0, 40, 5000)] + 0.08 * rng.standard_normal((5000, 32))).astype(np.float32)
+    q = (cent[rng.integers(0, 40, 100)] + 0.08 * rng.standard_normal((100, 32))).astype(np.float32)
+    ix = O.build_index(x, 48, pq_dim=16, pq_bits=8, kmeans_iters=4)
+    c8, r8 = O.int8_operands(ix)
+    d8 = c8.shape[1]
+    assert d8 == 48 and r8.shape == (ix.rot_dim, ix.dim)          # round_up(32 + 2, 16)
+    # the norm slots: z in column dim, round(y) in the m - 1 columns after it, with
+    # (m - 1) * (z + 128 * round(y)) ~ 128 * 64 * |c|^2
+    m = d8 - ix.dim
+    n2 = ix.centers[:, ix.dim].astype(np.float64)
+    enc = (m - 1) * (c8[:, ix.dim].astype(np.float64) + 128.0 * c8[:, ix.dim + 1].astype(np.float64))
+    assert (c8[:, ix.dim + 1:] == c8[:, ix.dim + 1:ix.dim + 2]).all()
+    assert np.abs(enc - 8192.0 * n2).max() <= (m - 1) * 1.0 + 1e-6
+    q8, rq = O.prepare_queries_int8(ix, q, r8)
+    assert (q8[:, ix.dim] == 1 - m).all() and (q8[:, ix.dim + 1:] == -128).all()
+    assert (q8[:, :ix.dim] == np.trunc(q * 128.0).astype(np.int8)).all()
+    # int32 scores against the fp32 ones: -2 * 128^2 * (<q,c> - |c|^2/2) = 128^2 * (|c|^2 - 2<q,c>)
+    fq, rq32 = O.prepare_queries(ix, q)
+    p32, s32, all32 = O.select_clusters(ix, fq, 8, want_all=True)
+    p8, s8 = O.select_clusters_int8(ix, c8, q8, 8)
+    first = np.take_along_axis(all32, p8[:, :1].astype(np.int64), axis=1)[:, 0]
+    assert np.abs(s8[:, 0] / 16384.0 - first).max() < 0.3          # truncation toward zero shrinks the products
+    overlap = np.mean([len(set(a) & set(b)) / 8 for a, b in zip(p8.tolist(), p32.tolist())])
+    assert overlap > 0.85, overlap
+    assert np.abs(rq - rq32).max() < 0.03                          # rotated queries, 1/128 grid
+    gt_d, gt_i = O.brute_force(x, q, 10)
+    r32 = O.recall(O.search(ix, q, 10, n_probes=8)[1], gt_i)
+    r8 = O.recall(O.search_int8_coarse(ix, q, 10, n_probes=8)[1], gt_i)
+    assert r8 > r32 - 0.08, (r8, r32)
