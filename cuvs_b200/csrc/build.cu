@@ -512,8 +512,12 @@ template <typename T>
 __device__ __forceinline__ T from_float(float x);
 template <> __device__ __forceinline__ float from_float<float>(float x) { return x; }
 template <> __device__ __forceinline__ __half from_float<__half>(float x) { return __float2half_rn(x); }
-template <> __device__ __forceinline__ int8_t from_float<int8_t>(float x) { return static_cast<int8_t>(x * 128.0f); }
-template <> __device__ __forceinline__ uint8_t from_float<uint8_t>(float x) { return static_cast<uint8_t>(x * 256.0f); }
+// mapping<int8_t>(float) clamps before it converts (ann_utils.cuh:211-217); the uint8 mapping does not
+template <> __device__ __forceinline__ int8_t from_float<int8_t>(float x)
+{
+  return static_cast<int8_t>(fminf(fmaxf(__fmul_rn(x, 128.0f), -128.0f), 127.0f));
+}
+template <> __device__ __forceinline__ uint8_t from_float<uint8_t>(float x) { return static_cast<uint8_t>(__fmul_rn(x, 256.0f)); }
 
 // One block per row: decode the row in the rotated space (codeword + rotated list center, one add
 // per component), then out[i, d] = sum over r, in order, of rotation[r, d] * decoded[r] (fp32 fma).

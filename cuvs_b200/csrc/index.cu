@@ -96,11 +96,14 @@ __global__ void centers_to_int8_kernel(const float* __restrict__ centers, size_t
   out[ix] = static_cast<float>(v);
 }
 
-// mapping<int8_t> of the rotation matrix (ivf_pq_index.cu:624-658; ann_utils.cuh:184-191).
+// mapping<int8_t> of the rotation matrix (ivf_pq_index.cu:624-658; ann_utils.cuh:211-217).
 __global__ void rotation_to_int8_kernel(const float* __restrict__ rot, size_t n, float* __restrict__ out)
 {
   const size_t ix = blockIdx.x * size_t(blockDim.x) + threadIdx.x;
-  if (ix < n) { out[ix] = static_cast<float>(static_cast<int8_t>(__fmul_rn(rot[ix], 128.0f))); }
+  // the float -> int8 mapping clamps before it converts (ann_utils.cuh:211-217): 1.0 becomes 127
+  if (ix < n) {
+    out[ix] = static_cast<float>(static_cast<int8_t>(fminf(fmaxf(__fmul_rn(rot[ix], 128.0f), -128.0f), 127.0f)));
+  }
 }
 
 index<int64_t>::int8_operands index<int64_t>::int8_coarse_operands(cudaStream_t stream) const

@@ -65,7 +65,11 @@ template <> __device__ __forceinline__ float map_to_float<uint8_t>(uint8_t x)
 // their own precision and convert, int8 passes, uint8 halves.
 template <typename T>
 __device__ __forceinline__ int8_t map_to_int8(T x);
-template <> __device__ __forceinline__ int8_t map_to_int8<float>(float x) { return static_cast<int8_t>(__fmul_rn(x, 128.0f)); }
+template <> __device__ __forceinline__ int8_t map_to_int8<float>(float x)
+{
+  // the float specialisation clamps before it converts (ann_utils.cuh:211-217)
+  return static_cast<int8_t>(fminf(fmaxf(__fmul_rn(x, 128.0f), -128.0f), 127.0f));
+}
 template <> __device__ __forceinline__ int8_t map_to_int8<__half>(__half x)
 {
   return static_cast<int8_t>(__hmul(x, __float2half(128.0f)));

@@ -555,8 +555,9 @@ ORC_EXPORT void orc_select_clusters(const orc_index* ix, const float* fq_ext, ui
 
 /* ============================ int8 coarse search (coarse_search_dtype = CUDA_R_8I) =========== */
 
-/* Device conversion float -> int8 of `static_cast<int8_t>(x)`: toward zero, clamped to the range of
- * the target type (the behaviour of the device's float-to-integer conversion; NaN gives 0). */
+/* mapping<int8_t> of a float after the scaling (ann_utils.cuh:211-217): clamped to [-128, 127], then
+ * converted toward zero.  The half-precision source takes the generic path, whose device
+ * conversion half -> int8 saturates to the same range. */
 static int8_t f32_to_i8(float x)
 {
   if (x != x) { return 0; }

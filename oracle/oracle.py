@@ -413,12 +413,13 @@ def pack_contiguous(codes: np.ndarray, pq_bits: int) -> np.ndarray:
 
 
 def map_from_float(x: np.ndarray, dtype) -> np.ndarray:
-    """mapping<T> applied to f32 values (cpp/src/neighbors/detail/ann_utils.cuh:168-199): scale by
-    128 (int8) or 256 (uint8), then the C++ float -> integer cast (truncation toward zero)."""
+    """mapping<T> applied to f32 values (cpp/src/neighbors/detail/ann_utils.cuh:168-217): scale by
+    128 (int8, clamped to [-128, 127] first) or 256 (uint8, in-range values only: the conversion of
+    the others is whatever the device's float -> integer cast does), then truncation toward zero."""
     dtype = np.dtype(dtype)
     x = np.asarray(x, dtype=np.float32)
     if dtype == np.int8:
-        return np.trunc(x * np.float32(128.0)).astype(np.int8)
+        return np.trunc(np.clip(x * np.float32(128.0), -128.0, 127.0)).astype(np.int8)
     if dtype == np.uint8:
         return np.trunc(x * np.float32(256.0)).astype(np.uint8)
     return x.astype(dtype)
