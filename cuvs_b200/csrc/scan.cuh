@@ -194,6 +194,16 @@ __device__ __forceinline__ void sts_b16(uint32_t a, uint32_t v)
 {
   asm volatile("st.shared.b16 [%0], %1;" ::"r"(a), "h"(uint16_t(v)) : "memory");
 }
+__device__ __forceinline__ uint32_t lds_b32_volatile(uint32_t a)
+{
+  uint32_t v;
+  asm volatile("ld.volatile.shared.b32 %0, [%1];" : "=r"(v) : "r"(a) : "memory");
+  return v;
+}
+__device__ __forceinline__ void atoms_min_u32(uint32_t a, uint32_t v)
+{
+  asm volatile("red.shared.min.u32 [%0], %1;" ::"r"(a), "r"(v) : "memory");
+}
 __device__ __forceinline__ void lds_2xb64(uint32_t a, uint64_t& x, uint64_t& y)
 {
   asm volatile("ld.shared.v2.b64 {%0, %1}, [%2];" : "=l"(x), "=l"(y) : "r"(a));
@@ -371,6 +381,12 @@ __device__ __forceinline__ void fill_codebook_tmem(uint32_t tmem_lane_a, const f
 // LUT of one pair from the codebook in TMEM: same thread-to-entry assignment and arithmetic as
 // build_lut_smem; the codebook operand arrives through tcgen05.ld, 16 columns (4 / LEN subspaces)
 // per load, and no longer occupies the shared-memory pipe.
+// Columns fetched by one tcgen05.ld of the table builder.  Eight (one subspace at two components
+// per codeword) keeps the kernel inside its 64 registers per thread; with sixteen, ten to fourteen
+// kernel-lifetime values were spilled and re-read from local memory for every pair, and those loads
+// miss L1 (the shared-memory carve-out leaves it almost no room): 1.57 ms against 1.50 ms per launch
+// on the 10 M-row workload.
+constexpr int kTmemLoadCols = 8;
 template <int PqBits, int LutKind, bool IsIP, int LEN>
 __device__ __forceinline__ void build_lut_tmem(uint32_t tmem_lane_a, uint32_t base_a, uint32_t lut_a,
                                                uint32_t pq_dim, uint32_t gt, uint32_t gthreads)
@@ -381,7 +397,8 @@ __device__ __forceinline__ void build_lut_tmem(uint32_t tmem_lane_a, uint32_t ba
   constexpr uint32_t kElem  = LutKind == LUT_F32 ? 4u : (LutKind == LUT_F16 ? 2u : 1u);
   constexpr uint32_t kBaseB = IsIP ? 16u : 8u;
   constexpr int kCols       = 4 * LEN;     // columns of one subspace
-  constexpr int kPerLoad    = 16 / kCols;  // subspaces per 16-column load
+  constexpr int kLoad       = kTmemLoadCols < kCols ? kCols : kTmemLoadCols;  // columns per load
+  constexpr int kPerLoad    = kLoad / kCols;  // subspaces per load
   // every lane of a warp works on the same subspace when a subspace has at least 32 units
   constexpr bool kWarpSameJ = kUPJ >= 32;
   const uint32_t u          = gt % kUPJ;
@@ -400,7 +417,7 @@ __device__ __forceinline__ void build_lut_tmem(uint32_t tmem_lane_a, uint32_t ba
   const uint32_t out_step   = j_stride * kBook * kElem;
 
   // one subspace: sub-iteration T of the 16 columns in `c`
-  auto entry = [&](const uint32_t (&c)[16], auto tc) {
+  auto entry = [&](const auto& c, auto tc) {
     constexpr int T = decltype(tc)::value;
     uint64_t s0 = 0ull, s1 = 0ull;  // entries (b, b+1) and (b+2, b+3), each (+0.0f, +0.0f)
     uint64_t x[LEN], y[LEN];
@@ -448,9 +465,9 @@ __device__ __forceinline__ void build_lut_tmem(uint32_t tmem_lane_a, uint32_t ba
   // Whole loads first, without per-subspace checks where the warp shares its subspace; then the rest.
   const uint32_t n_whole = kWarpSameJ ? (n_iter / kPerLoad) * kPerLoad : 0u;
   uint32_t i             = 0;
-  for (; i < n_whole; i += kPerLoad, taddr += 16u) {
-    uint32_t c[16];
-    tmem_ld<16>(taddr, c);
+  for (; i < n_whole; i += kPerLoad, taddr += uint32_t(kLoad)) {
+    uint32_t c[kLoad];
+    tmem_ld<kLoad>(taddr, c);
     tmem_wait_ld();
     entry(c, std::integral_constant<int, 0>{});
     advance();
@@ -465,9 +482,9 @@ __device__ __forceinline__ void build_lut_tmem(uint32_t tmem_lane_a, uint32_t ba
       advance();
     }
   }
-  for (; i < n_iter; i += kPerLoad, taddr += 16u) {
-    uint32_t c[16];
-    tmem_ld<16>(taddr, c);  // may run past this thread's blocks into other columns of the allocation
+  for (; i < n_iter; i += kPerLoad, taddr += uint32_t(kLoad)) {
+    uint32_t c[kLoad];
+    tmem_ld<kLoad>(taddr, c);  // may run past this thread's blocks into other columns of the allocation
     tmem_wait_ld();
     if (i < n_iter && (kWarpSameJ || j < pq_dim)) { entry(c, std::integral_constant<int, 0>{}); }
     advance();
@@ -611,12 +628,15 @@ __global__ void __launch_bounds__(1024, 1) scan_kernel(const scan_params p)
   const int bar_id   = 1 + g;
 
   float* s_pqc      = reinterpret_cast<float*>(smem);
-  uint8_t* gbase    = smem + p.smem_pqc_bytes + size_t(g) * p.smem_group_bytes;
-  lut_t* s_lut      = reinterpret_cast<lut_t*>(gbase);
-  float* s_base     = reinterpret_cast<float*>(gbase + p.lut_bytes);
-  uint64_t* s_merge = reinterpret_cast<uint64_t*>(gbase + p.lut_bytes + p.base_bytes);
-  uint32_t* s_item  = reinterpret_cast<uint32_t*>(gbase + p.lut_bytes + p.base_bytes + p.merge_bytes);
-  uint32_t* s_thr   = s_item + 2;  // group-wide bound on the k-th best ordered score of this pair
+  // This group's areas, as 32-bit shared-space addresses derived from one register (the offsets are
+  // kernel parameters): LUT, base difference, merge buffer, two work-item slots, then the group-wide
+  // bound on the k-th best ordered score of the current pair.
+  const uint32_t goff    = p.smem_pqc_bytes + uint32_t(g) * p.smem_group_bytes;
+  const uint32_t lut_a   = smem_addr(smem) + goff;
+#define S_BASE_A (lut_a + p.lut_bytes)
+#define S_MERGE_A (lut_a + p.lut_bytes + p.base_bytes)
+#define S_ITEM_A (lut_a + p.lut_bytes + p.base_bytes + p.merge_bytes)
+#define S_THR_A (S_ITEM_A + 8u)
 
   uint32_t tmem_base = 0;
   if (p.tmem_cols) {
@@ -663,12 +683,14 @@ __global__ void __launch_bounds__(1024, 1) scan_kernel(const scan_params p)
   // is dealt pair by pair so that it spreads over all groups.
   const uint32_t n_work = __ldg(p.n_work);
   const uint32_t claim  = n_work >= 8u * gridDim.x * p.n_groups ? 4u : 1u;
-  if (gt == 0) { s_item[0] = atomicAdd(p.work_counter, claim); }
+  if (gt == 0) { sts_b32(S_ITEM_A, atomicAdd(p.work_counter, claim)); }
   for (uint32_t it = 0;; it++) {
     group_bar(bar_id, gthreads);
-    const uint32_t w = s_item[(it / claim) & 1u] + (it % claim);
+    const uint32_t w = lds_b32_volatile(S_ITEM_A + 4u * ((it / claim) & 1u)) + (it % claim);
     if (w >= n_work) { break; }
-    if (gt == 0 && (it % claim) == 0) { s_item[((it / claim) + 1u) & 1u] = atomicAdd(p.work_counter, claim); }
+    if (gt == 0 && (it % claim) == 0) {
+      sts_b32(S_ITEM_A + 4u * (((it / claim) + 1u) & 1u), atomicAdd(p.work_counter, claim));
+    }
 
     const uint4 d0       = __ldg(p.work + 2 * size_t(w));
     const uint4 d1       = __ldg(p.work + 2 * size_t(w) + 1);
@@ -688,7 +710,7 @@ __global__ void __launch_bounds__(1024, 1) scan_kernel(const scan_params p)
     }
 
     // ---- base diff ----
-    if (gt == 0) { *s_thr = *reinterpret_cast<volatile uint32_t*>(p.query_kth + q); }
+    if (gt == 0) { sts_b32(S_THR_A, *reinterpret_cast<volatile uint32_t*>(p.query_kth + q)); }
     {
       const float* rq = p.rot_q + size_t(q) * p.rot_dim;
       const float* c  = p.centers_rot + size_t(label) * p.rot_dim;
@@ -696,34 +718,35 @@ __global__ void __launch_bounds__(1024, 1) scan_kernel(const scan_params p)
       for (uint32_t i = gt; i < p.rot_dim; i += gthreads) {
         if constexpr (!IsIP) {
           const float d = __fsub_rn(rq[i], __ldg(c + i));
-          reinterpret_cast<float2*>(s_base)[i] = make_float2(d, d);
+          sts_b64(S_BASE_A + 8u * i, pack2(d, d));
         } else {
           const float qv = rq[i];
           const float y  = __fmul_rn(__ldg(c + i), qv);
-          reinterpret_cast<float4*>(s_base)[i] = make_float4(-qv, -qv, y, y);
+          sts_b128(S_BASE_A + 16u * i, pack2(-qv, -qv), pack2(y, y));
         }
       }
     }
     group_bar(bar_id, gthreads);
 
-    // The first 16-byte piece of this warp's first group is requested now, so that its latency
-    // hides behind the LUT build; afterwards each piece is requested one piece ahead of its use.
+    // The first 16-byte piece of this warp's first group is brought to L2 now, behind the LUT build
+    // (a load into registers here would hold four of them through the build); afterwards each piece
+    // is requested one piece ahead of its use.
     const uint32_t n_groups = (n + 31u) >> 5;
     const uint4* src = reinterpret_cast<const uint4*>(p.codes + first_row * size_t(p.n_pieces) * 16u) +
                        size_t(gw) * p.n_pieces * 32u + lane;
     uint4 nxt = make_uint4(0u, 0u, 0u, 0u);
-    if (uint32_t(gw) < n_groups) { nxt = __ldg(src); }
+    if (uint32_t(gw) < n_groups) { asm volatile("prefetch.global.L2 [%0];" ::"l"(src)); }
 
     // ---- LUT ----
     if (p.tmem_cols) {
-      const uint32_t base_a = smem_addr(s_base), lut_a = smem_addr(s_lut);
+      const uint32_t base_a = S_BASE_A;
       switch (len) {
         case 1: build_lut_tmem<PqBits, LutKind, IsIP, 1>(tmem_lane_a, base_a, lut_a, p.pq_dim, gt, gthreads); break;
         case 2: build_lut_tmem<PqBits, LutKind, IsIP, 2>(tmem_lane_a, base_a, lut_a, p.pq_dim, gt, gthreads); break;
         default: build_lut_tmem<PqBits, LutKind, IsIP, 4>(tmem_lane_a, base_a, lut_a, p.pq_dim, gt, gthreads); break;
       }
     } else if (p.pqc_in_smem) {
-      const uint32_t pqc_a = smem_addr(s_pqc), base_a = smem_addr(s_base), lut_a = smem_addr(s_lut);
+      const uint32_t pqc_a = smem_addr(s_pqc), base_a = S_BASE_A;
       switch (len) {
         case 1: build_lut_smem<PqBits, LutKind, IsIP, 1>(pqc_a, base_a, lut_a, p.pq_dim, len, gt, gthreads); break;
         case 2: build_lut_smem<PqBits, LutKind, IsIP, 2>(pqc_a, base_a, lut_a, p.pq_dim, len, gt, gthreads); break;
@@ -734,6 +757,8 @@ __global__ void __launch_bounds__(1024, 1) scan_kernel(const scan_params p)
       // codebook read from global memory (PER_CLUSTER, or a per-subspace codebook too large for
       // shared memory): same arithmetic, generic addressing
       constexpr uint32_t kPairs = kBook / 2;
+      lut_t* s_lut        = reinterpret_cast<lut_t*>(smem + goff);
+      const float* s_base = reinterpret_cast<const float*>(smem + goff + p.lut_bytes);
       const float* pqc = p.per_cluster ? p.pq_centers + size_t(label) * len * kBook : p.pq_centers;
       const uint32_t b        = (uint32_t(gt) % kPairs) * 2u;
       const uint32_t j_first  = uint32_t(gt) / kPairs;
@@ -772,8 +797,9 @@ __global__ void __launch_bounds__(1024, 1) scan_kernel(const scan_params p)
 
     // ---- scan ----
     queue.init(int(k));
+    if (uint32_t(gw) < n_groups) { nxt = __ldg(src); }
     {
-      const uint32_t lut_base_a   = smem_addr(s_lut);
+      const uint32_t lut_base_a   = lut_a;
       const uint32_t group_stride = uint32_t(n_gwarps) * p.n_pieces * 32u;  // in 16-byte pieces
       constexpr uint32_t kPieceLutBytes = uint32_t(kPerPiece) * kBook * uint32_t(sizeof(lut_t));
       for (uint32_t gi = gw; gi < n_groups; gi += n_gwarps, src += group_stride) {
@@ -807,16 +833,17 @@ __global__ void __launch_bounds__(1024, 1) scan_kernel(const scan_params p)
           const uint32_t ord   = float_to_ordered(score);
           const uint64_t key   = (uint64_t(ord) << 32) | (sample_offset + row);
           // s_thr never exceeds the final k-th best score of the query, so nothing wanted is lost
-          const uint32_t thr   = *reinterpret_cast<volatile uint32_t*>(s_thr);
+          const uint32_t thr   = lds_b32_volatile(S_THR_A);
           const uint64_t before = queue.kth();
           queue.offer(key, valid && ord <= thr);
-          if (queue.kth() != before && lane == 0) { atomicMin(s_thr, uint32_t(queue.kth() >> 32)); }
+          if (queue.kth() != before && lane == 0) { atoms_min_u32(S_THR_A, uint32_t(queue.kth() >> 32)); }
         }
       }
     }
 
     if constexpr (!kStoreAll) {
     // ---- merge the warps' queues, write k keys ----
+    uint64_t* s_merge = reinterpret_cast<uint64_t*>(smem + goff + p.lut_bytes + p.base_bytes);
     queue.store(s_merge + size_t(gw) * k, int(k));
     group_bar(bar_id, gthreads);
     if (gw == 0) {
@@ -842,6 +869,11 @@ __global__ void __launch_bounds__(1024, 1) scan_kernel(const scan_params p)
     }
   }
 }
+
+#undef S_BASE_A
+#undef S_MERGE_A
+#undef S_ITEM_A
+#undef S_THR_A
 
 // Host-side launcher of one instantiation family (defined once per PqBits in scan_inst.cu).
 void launch_scan(const scan_params& p, int pq_bits, int lut_kind, bool out_half, bool is_ip,
