@@ -97,6 +97,14 @@ __device__ __forceinline__ uint64_t sub2(uint64_t a, uint64_t b)
   asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
   return d;
 }
+// a * b: the first term of a sum that starts from +0 (fma(a, a, +0) rounds to the same value, and
+// a square is never -0), without materialising a zero register pair
+__device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b)
+{
+  uint64_t d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
 __device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c)
 {
   uint64_t d;
@@ -437,8 +445,8 @@ __device__ __forceinline__ void build_lut_tmem(uint32_t tmem_lane_a, uint32_t ba
       if constexpr (!IsIP) {  // x = (d, d)
         const uint64_t e0 = sub2(x[kk], c0);
         const uint64_t e1 = sub2(x[kk], c1);
-        s0                = fma2(e0, e0, s0);
-        s1                = fma2(e1, e1, s1);
+        s0                = kk == 0 ? mul2(e0, e0) : fma2(e0, e0, s0);
+        s1                = kk == 0 ? mul2(e1, e1) : fma2(e1, e1, s1);
       } else {  // x = (-q, -q), y = (q*c, q*c)
         s0 = sub2(s0, y[kk]);
         s1 = sub2(s1, y[kk]);
