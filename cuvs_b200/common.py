@@ -66,10 +66,15 @@ def default_resources() -> Resources:
 class DLTensorRef:
     """A DLManagedTensor describing (not owning) a torch tensor or a numpy array."""
 
-    def __init__(self, obj):
+    def __init__(self, obj, strided: bool = False):
+        """`strided`: describe a non-contiguous torch tensor by its strides (only entry points that
+        say so accept one) instead of refusing it."""
+        strides = None
         if isinstance(obj, torch.Tensor):
             if not obj.is_contiguous():
-                raise ValueError("Expected a row-major matrix")
+                if not strided:
+                    raise ValueError("Expected a row-major matrix")
+                strides = tuple(obj.stride())
             code, bits = _TORCH_DL[obj.dtype]
             if obj.is_cuda:
                 dev = L.DLDevice(L.kDLCUDA, obj.device.index or 0)
@@ -95,7 +100,11 @@ class DLTensorRef:
         t.ndim = len(shape)
         t.dtype = L.DLDataType(code, bits, 1)
         t.shape = C.cast(self._shape, C.POINTER(C.c_int64))
-        t.strides = None
+        if strides is None:
+            t.strides = None
+        else:
+            self._strides = (C.c_int64 * len(strides))(*strides)
+            t.strides = C.cast(self._strides, C.POINTER(C.c_int64))
         t.byte_offset = 0
 
     def ref(self):

@@ -92,6 +92,26 @@ void* checked_data(DLManagedTensor* mt, uint8_t code, uint8_t bits, int ndim, bo
   return static_cast<char*>(t.data) + t.byte_offset;
 }
 
+// [n_parts, n, k] device tensor whose parts are row-major and may be separated by any stride
+// (in elements, at least n * k); returns the data pointer and the stride between parts.
+void* checked_parts(DLManagedTensor* mt, uint8_t code, uint8_t bits, const char* name, size_t* part_stride)
+{
+  CUVS_EXPECTS(mt != nullptr, "%s: null tensor", name);
+  const DLTensor& t = mt->dl_tensor;
+  CUVS_EXPECTS(t.ndim == 3, "ndim mismatch between return mdspan and DLTensor");
+  CUVS_EXPECTS(code == t.dtype.code && bits == t.dtype.bits && t.dtype.lanes == 1,
+               "%s: unexpected element type", name);
+  CUVS_EXPECTS(is_device_compatible(t), "device_type mismatch between return mdspan and DLTensor");
+  *part_stride = size_t(t.shape[1]) * size_t(t.shape[2]);
+  if (t.strides) {
+    CUVS_EXPECTS(t.strides[2] == 1 && t.strides[1] == t.shape[2] &&
+                   (t.shape[0] <= 1 || t.strides[0] >= t.shape[1] * t.shape[2]),
+                 "Expected row-major parts");
+    if (t.shape[0] > 1) { *part_stride = size_t(t.strides[0]); }
+  }
+  return static_cast<char*>(t.data) + t.byte_offset;
+}
+
 ivf_pq::elem_t elem_of_dtype(const DLDataType& d, const char* what)
 {
   if (d.code == kDLFloat && d.bits == 32) { return ivf_pq::elem_t::f32; }
@@ -784,8 +804,10 @@ extern "C" cuvsError_t cuvsMultiGpuIvfPqMergeParts(cuvsResources_t res, DLManage
                                                    bool select_min)
 {
   return translate_exceptions([=] {
-    auto* pd = static_cast<float*>(checked_data(part_distances, kDLFloat, 32, 3, true, "part_distances"));
-    auto* pn = static_cast<int64_t*>(checked_data(part_neighbors, kDLInt, 64, 3, true, "part_neighbors"));
+    // the parts may lie apart (one stride between them): e.g. views into one gathered buffer
+    size_t stride_d = 0, stride_n = 0;
+    auto* pd = static_cast<float*>(checked_parts(part_distances, kDLFloat, 32, "part_distances", &stride_d));
+    auto* pn = static_cast<int64_t*>(checked_parts(part_neighbors, kDLInt, 64, "part_neighbors", &stride_n));
     auto* od = static_cast<float*>(checked_data(distances, kDLFloat, 32, 2, true, "distances"));
     auto* on = static_cast<int64_t*>(checked_data(neighbors, kDLInt, 64, 2, true, "neighbors"));
     const int64_t* ps = part_distances->dl_tensor.shape;
@@ -797,7 +819,7 @@ extern "C" cuvsError_t cuvsMultiGpuIvfPqMergeParts(cuvsResources_t res, DLManage
                    "outputs must be [n_queries, k]");
     }
     ivf_pq::detail::knn_merge_parts(*res_of(res), pd, pn, od, on, uint32_t(ps[0]), uint32_t(ps[1]),
-                                    uint32_t(ps[2]), select_min);
+                                    uint32_t(ps[2]), select_min, stride_d, stride_n);
   });
 }
 

@@ -393,9 +393,10 @@ void reset_index(raft::resources& res, index<int64_t>* idx);
 namespace detail {
 // Merge `n_parts` per-part top-k lists into one (cpp/src/neighbors/detail/knn_merge_parts.cuh:24-170).
 // in_* : [n_parts, n_queries, k]; out_*: [n_queries, k]; select_min picks the smallest distances.
+// part_stride_*: elements between consecutive parts (0 = n_queries * k, parts back to back).
 void knn_merge_parts(raft::resources& res, const float* in_dist, const int64_t* in_ids,
                      float* out_dist, int64_t* out_ids, uint32_t n_parts, uint32_t n_queries,
-                     uint32_t k, bool select_min);
+                     uint32_t k, bool select_min, size_t part_stride_dist = 0, size_t part_stride_ids = 0);
 }  // namespace detail
 
 }  // namespace cuvs::neighbors::ivf_pq

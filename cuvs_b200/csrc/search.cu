@@ -437,8 +437,8 @@ __global__ void fill_f32_kernel(float* p, size_t n, float v)
 // knn_merge_parts (cpp/src/neighbors/detail/knn_merge_parts.cuh:24-97): one warp per query.
 template <int KPL>
 __global__ void merge_parts_kernel(const float* __restrict__ in_dist,
-                                   const int64_t* __restrict__ in_ids, uint32_t n_parts,
-                                   uint32_t n_queries, uint32_t k, int select_min,
+                                   const int64_t* __restrict__ in_ids, size_t stride_d, size_t stride_i,
+                                   uint32_t n_parts, uint32_t n_queries, uint32_t k, int select_min,
                                    float* __restrict__ out_dist, int64_t* __restrict__ out_ids)
 {
   const uint32_t q    = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
@@ -453,10 +453,10 @@ __global__ void merge_parts_kernel(const float* __restrict__ in_dist,
     bool valid       = false;
     if (t < n) {
       const uint32_t part = t / k, pos = t - part * k;
-      const size_t src    = (size_t(part) * n_queries + q) * k + pos;
-      const int64_t id    = in_ids[src];
+      const size_t src    = size_t(q) * k + pos;
+      const int64_t id    = in_ids[part * stride_i + src];
       if (id != kOutOfBoundsRecord) {
-        float d = in_dist[src];
+        float d = in_dist[part * stride_d + src];
         key     = make_key(select_min ? d : -d, t);
         valid   = true;
       }
@@ -473,9 +473,9 @@ __global__ void merge_parts_kernel(const float* __restrict__ in_dist,
     if (uint32_t(key >> 32) != kEmptyScore) {
       const uint32_t t    = uint32_t(key);
       const uint32_t part = t / k, p = t - part * k;
-      const size_t src    = (size_t(part) * n_queries + q) * k + p;
-      id                  = in_ids[src];
-      d                   = in_dist[src];
+      const size_t src    = size_t(q) * k + p;
+      id                  = in_ids[part * stride_i + src];
+      d                   = in_dist[part * stride_d + src];
     }
     out_ids[size_t(q) * k + pos]  = id;
     out_dist[size_t(q) * k + pos] = d;
@@ -952,23 +952,25 @@ void coarse_only(raft::resources& res, const index<int64_t>& idx, const void* qu
 namespace detail {
 void knn_merge_parts(raft::resources& res, const float* in_dist, const int64_t* in_ids,
                      float* out_dist, int64_t* out_ids, uint32_t n_parts, uint32_t n_queries,
-                     uint32_t k, bool select_min)
+                     uint32_t k, bool select_min, size_t part_stride_dist, size_t part_stride_ids)
 {
   CUVS_EXPECTS(k > 0 && k <= 128, "knn_merge_parts supports 0 < k <= 128, got %u", k);
   if (n_queries == 0) { return; }
+  const size_t sd = part_stride_dist ? part_stride_dist : size_t(n_queries) * k;
+  const size_t si = part_stride_ids ? part_stride_ids : size_t(n_queries) * k;
   const int blocks = int(ceildiv<uint32_t>(n_queries * 32, 128));
   const int kpl    = kpl_for_k(k);
   switch (kpl) {
     case 1:
-      merge_parts_kernel<1><<<blocks, 128, 0, res.stream>>>(in_dist, in_ids, n_parts, n_queries, k,
+      merge_parts_kernel<1><<<blocks, 128, 0, res.stream>>>(in_dist, in_ids, sd, si, n_parts, n_queries, k,
                                                             select_min, out_dist, out_ids);
       break;
     case 2:
-      merge_parts_kernel<2><<<blocks, 128, 0, res.stream>>>(in_dist, in_ids, n_parts, n_queries, k,
+      merge_parts_kernel<2><<<blocks, 128, 0, res.stream>>>(in_dist, in_ids, sd, si, n_parts, n_queries, k,
                                                             select_min, out_dist, out_ids);
       break;
     default:
-      merge_parts_kernel<4><<<blocks, 128, 0, res.stream>>>(in_dist, in_ids, n_parts, n_queries, k,
+      merge_parts_kernel<4><<<blocks, 128, 0, res.stream>>>(in_dist, in_ids, sd, si, n_parts, n_queries, k,
                                                             select_min, out_dist, out_ids);
   }
   CUDA_TRY(cudaGetLastError());

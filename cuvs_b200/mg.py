@@ -147,7 +147,9 @@ def merge_parts(part_d: torch.Tensor, part_i: torch.Tensor, select_min: bool = T
     _, n, k = part_d.shape
     out_d = torch.empty((n, k), dtype=torch.float32, device=part_d.device)
     out_i = torch.empty((n, k), dtype=torch.int64, device=part_d.device)
-    a, b, c, d = (DLTensorRef(t) for t in (part_d.contiguous(), part_i.contiguous(), out_d, out_i))
+    # the parts may be views into one gathered buffer: row-major each, any stride between them
+    a, b = DLTensorRef(part_d, strided=True), DLTensorRef(part_i, strided=True)
+    c, d = DLTensorRef(out_d), DLTensorRef(out_i)
     L.check(L.load().cuvsMultiGpuIvfPqMergeParts(res.handle, a.ref(), b.ref(), c.ref(), d.ref(),
                                                  C.c_bool(select_min)))
     if sync:
@@ -155,11 +157,14 @@ def merge_parts(part_d: torch.Tensor, part_i: torch.Tensor, select_min: bool = T
     return out_d, out_i
 
 
-def select_probes(shard: ivf_pq.Index, queries, n_probes: int, resources: Resources | None = None):
-    """Probes of `queries` (u32 [n, n_probes], ascending by (score, list id)); asynchronous."""
+def select_probes(shard: ivf_pq.Index, queries, n_probes: int, resources: Resources | None = None,
+                  out=None):
+    """Probes of `queries` (u32 [n, n_probes], ascending by (score, list id)); asynchronous.
+    `out`: optional destination (contiguous u32 [n, n_probes])."""
     res = resources or default_resources()
     res.use_current_stream()
-    probes = torch.empty((queries.shape[0], n_probes), dtype=torch.uint32, device=queries.device)
+    probes = out if out is not None else \
+        torch.empty((queries.shape[0], n_probes), dtype=torch.uint32, device=queries.device)
     if queries.shape[0]:
         q, p = DLTensorRef(queries), DLTensorRef(probes)
         L.check(L.load().cuvsMultiGpuIvfPqSelectProbes(res.handle, shard._h, q.ref(), p.ref()))
@@ -177,22 +182,38 @@ def shared_probes(shard: ivf_pq.Index, queries, n_probes: int, group=None,
         return select_probes(shard, queries, n_probes, resources)
     s = -(-n // w)
     lo, hi = min(n, rank * s), min(n, (rank + 1) * s)
-    mine = torch.zeros((s, n_probes), dtype=torch.uint32, device=queries.device)
-    if hi > lo:
-        mine[: hi - lo] = select_probes(shard, queries[lo:hi], n_probes, resources)
     every = torch.empty((w * s, n_probes), dtype=torch.uint32, device=queries.device)
+    if _in_place_gather(group):
+        # this rank's slice is written where the gather wants it and gathered in place (rows past
+        # n exist only as padding of the last slice and are never read)
+        if hi > lo:
+            select_probes(shard, queries[lo:hi], n_probes, resources, out=every[lo:hi])
+        mine = every[rank * s:(rank + 1) * s]
+    else:
+        mine = torch.zeros((s, n_probes), dtype=torch.uint32, device=queries.device)
+        if hi > lo:
+            mine[: hi - lo] = select_probes(shard, queries[lo:hi], n_probes, resources)
     # NCCL has no uint32: exchange the same bytes as int32
     dist.all_gather_into_tensor(every.view(torch.int32), mine.view(torch.int32), group=group)
     return every[:n]
 
 
+def _in_place_gather(group=None) -> bool:
+    """NCCL gathers in place when a rank's input is its own slot of the output."""
+    return dist.get_backend(group) == "nccl"
+
+
 def search_with_probes(search_params: ivf_pq.SearchParams, shard: ivf_pq.Index, queries, probes,
-                       k: int, resources: Resources | None = None, sync: bool = True):
+                       k: int, resources: Resources | None = None, sync: bool = True, out=None):
+    """Fine search of this rank's lists for given probes; `out` = optional (distances, neighbors)."""
     res = resources or default_resources()
     res.use_current_stream()
     n = queries.shape[0]
-    d = torch.empty((n, k), dtype=torch.float32, device=queries.device)
-    i = torch.empty((n, k), dtype=torch.int64, device=queries.device)
+    if out is not None:
+        d, i = out
+    else:
+        d = torch.empty((n, k), dtype=torch.float32, device=queries.device)
+        i = torch.empty((n, k), dtype=torch.int64, device=queries.device)
     a, b, c, e = DLTensorRef(queries), DLTensorRef(probes.contiguous()), DLTensorRef(i), DLTensorRef(d)
     L.check(L.load().cuvsMultiGpuIvfPqSearchWithProbes(res.handle, search_params._p, shard._h, a.ref(),
                                                        b.ref(), c.ref(), e.ref()))
@@ -212,6 +233,19 @@ def search(search_params: ivf_pq.SearchParams, shard: ivf_pq.Index, queries, k: 
         return ivf_pq.search(search_params, shard, queries, k, resources=res, sync=sync)
     n_probes = min(search_params.n_probes, shard.n_lists)
     probes = shared_probes(shard, queries, n_probes, group, res)
+    n = queries.shape[0]
+    nk = n * k
+    if _in_place_gather(group) and nk % 2 == 0 and nk > 0:
+        # one exchange for ids and distances: every rank's block is [n*k int64 ids | n*k f32
+        # distances], written by the search straight into this rank's slot of the gathered buffer
+        rank = dist.get_rank(group)
+        blocks = torch.empty((w, nk * 12), dtype=torch.uint8, device=queries.device)
+        part_i = blocks[:, :nk * 8].view(torch.int64).view(w, n, k)
+        part_d = blocks[:, nk * 8:].view(torch.float32).view(w, n, k)
+        search_with_probes(search_params, shard, queries, probes, k, res, sync=False,
+                           out=(part_d[rank], part_i[rank]))
+        dist.all_gather_into_tensor(blocks, blocks[rank], group=group)
+        return merge_parts(part_d, part_i, select_min, res, sync)
     d, i = search_with_probes(search_params, shard, queries, probes, k, res, sync=False)
     part_d, part_i = gather_parts(d, i, group)
     return merge_parts(part_d, part_i, select_min, res, sync)
