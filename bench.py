@@ -287,10 +287,10 @@ def hbm_peak():
 
 
 # DRAM bytes (read + write) per DISTINCT 32-row group scanned in a launch, from the ncu capture of the
-# scan kernel on a 4 M-row case of this workload (255.4 MB over 135,125 distinct groups of
+# scan kernel on a 4 M-row case of this workload (246.8 MB over 135,125 distinct groups of
 # 3 x 512 B; summary under profiles/).  Traffic grows with the distinct groups of a launch, so the
 # full-size figure is this constant times the launch's distinct groups.
-DRAM_BYTES_PER_UNIQUE_GROUP = 1890.0
+DRAM_BYTES_PER_UNIQUE_GROUP = 1826.0
 
 
 def workload_from_args(args):

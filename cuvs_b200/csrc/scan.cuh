@@ -686,11 +686,11 @@ __global__ void __launch_bounds__(1024, 1) scan_kernel(const scan_params p)
   constexpr bool kStoreAll = KPL == 0;  // k too large for registers: write every score instead
   warp_topk<(KPL > 0 ? KPL : 1)> queue;
 
-  // Work items are claimed four at a time (one atomic per four pairs keeps the single counter off
-  // the critical path), one claim ahead so that the atomic's latency is hidden; a short work list
-  // is dealt pair by pair so that it spreads over all groups.
+  // Work items are claimed one pair at a time, one claim ahead so that the atomic's latency is
+  // hidden (claims of four pairs per atomic measured slower at every work-list length: the tail of
+  // the launch is dealt more evenly pair by pair).
   const uint32_t n_work = __ldg(p.n_work);
-  const uint32_t claim  = n_work >= 8u * gridDim.x * p.n_groups ? 4u : 1u;
+  constexpr uint32_t claim = 1u;
   if (gt == 0) { sts_b32(S_ITEM_A, atomicAdd(p.work_counter, claim)); }
   for (uint32_t it = 0;; it++) {
     group_bar(bar_id, gthreads);
