@@ -206,17 +206,26 @@ coarse_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
                  const __grid_constant__ CUtensorMap map_b_hi, const __grid_constant__ CUtensorMap map_b_lo,
                  const tc_params p)
 {
+  // Only the operands the chosen number of products reads are staged, and the 192 KB of stage memory
+  // hold as many stages of that size as fit: 4 x 48 KB (three products), 6 x 32 KB (two), 8 x 24 KB
+  // (one).  With fewer than three products the loop is bound by the latency of the operand loads,
+  // so more of them in flight is what shortens it.
+  constexpr uint32_t kOffALo = kBM * kBK * 4;
+  constexpr uint32_t kOffBHi = kBM * kBK * 4 * (kProducts >= 2 ? 2 : 1);
+  constexpr uint32_t kOffBLo = kOffBHi + kBN * kBK * 4;
+  constexpr uint32_t kStageB = kOffBHi + kBN * kBK * 4 * (kProducts >= 3 ? 2 : 1);
+  constexpr int kNS          = int((kStages * kStageBytes) / kStageB);
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_a  = smem_u32(smem_raw);
   const uint32_t base_a = (raw_a + 1023u) & ~1023u;             // tiles need 1024-byte alignment
   uint8_t* base_p       = smem_raw + (base_a - raw_a);
   uint64_t* bars        = reinterpret_cast<uint64_t*>(base_p + kStages * kStageBytes);
-  // bars: full[kStages], empty[kStages], tmem_full[2], tmem_empty[2], then the TMEM address slot
+  // bars: full[kNS], empty[kNS], tmem_full[2], tmem_empty[2], then the TMEM address slot
   const uint32_t bar_full   = smem_u32(bars);
-  const uint32_t bar_empty  = bar_full + kStages * 8;
-  const uint32_t bar_tfull  = bar_empty + kStages * 8;
+  const uint32_t bar_empty  = bar_full + kNS * 8;
+  const uint32_t bar_tfull  = bar_empty + kNS * 8;
   const uint32_t bar_tempty = bar_tfull + 2 * 8;
-  uint32_t* tmem_slot       = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
+  uint32_t* tmem_slot       = reinterpret_cast<uint32_t*>(bars + 2 * kNS + 4);
   __shared__ uint32_t s_failed;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -225,7 +234,7 @@ coarse_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
 #endif
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kStages; s++) {
+    for (int s = 0; s < kNS; s++) {
       mbar_init(bar_full + s * 8, 1);
       mbar_init(bar_empty + s * 8, 1);
     }
@@ -266,18 +275,18 @@ coarse_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
             ok = false;
             break;
           }
-          const uint32_t dst = base_a + stage * kStageBytes;
+          const uint32_t dst = base_a + stage * kStageB;
           const uint32_t bar = bar_full + stage * 8;
           // operands the chosen number of products needs: 1: hi*hi; 2: + lo*hi; 3: + hi*lo
           constexpr uint32_t kBytes = (kBM + kBN + (kProducts >= 2 ? kBM : 0) + (kProducts >= 3 ? kBN : 0)) * kBK * 4;
           mbar_arrive_expect_tx(bar, kBytes);
           tma_load_2d(dst, &map_a_hi, bar, int(kb * kBK), int(q0));
-          if constexpr (kProducts >= 2) { tma_load_2d(dst + kBM * kBK * 4, &map_a_lo, bar, int(kb * kBK), int(q0)); }
-          tma_load_2d(dst + 2 * kBM * kBK * 4, &map_b_hi, bar, int(kb * kBK), n0);
+          if constexpr (kProducts >= 2) { tma_load_2d(dst + kOffALo, &map_a_lo, bar, int(kb * kBK), int(q0)); }
+          tma_load_2d(dst + kOffBHi, &map_b_hi, bar, int(kb * kBK), n0);
           if constexpr (kProducts >= 3) {
-            tma_load_2d(dst + 2 * kBM * kBK * 4 + kBN * kBK * 4, &map_b_lo, bar, int(kb * kBK), n0);
+            tma_load_2d(dst + kOffBLo, &map_b_lo, bar, int(kb * kBK), n0);
           }
-          if (++stage == kStages) {
+          if (++stage == kNS) {
             stage = 0;
             phase ^= 1u;
           }
@@ -312,11 +321,11 @@ coarse_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
             break;
           }
           tc_fence_after();
-          const uint32_t sa      = base_a + stage * kStageBytes;
+          const uint32_t sa      = base_a + stage * kStageB;
           const uint64_t d_a_hi  = make_desc(sa);
-          const uint64_t d_a_lo  = make_desc(sa + kBM * kBK * 4);
-          const uint64_t d_b_hi  = make_desc(sa + 2 * kBM * kBK * 4);
-          const uint64_t d_b_lo  = make_desc(sa + 2 * kBM * kBK * 4 + kBN * kBK * 4);
+          const uint64_t d_a_lo  = make_desc(sa + kOffALo);
+          const uint64_t d_b_hi  = make_desc(sa + kOffBHi);
+          const uint64_t d_b_lo  = make_desc(sa + kOffBLo);
 #pragma unroll
           for (uint32_t k8 = 0; k8 < kBK / 8; k8++) {
             const uint64_t adv = uint64_t(k8 * 2);  // 32 bytes per MMA along K, in 16-byte units
@@ -325,7 +334,7 @@ coarse_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
             tc_mma_tf32(tmem_d, d_a_hi + adv, d_b_hi + adv, idesc, kProducts >= 2 || (kb | k8) != 0);
           }
           tc_commit(bar_empty + stage * 8);  // the stage may be refilled once these MMAs have read it
-          if (++stage == kStages) {
+          if (++stage == kNS) {
             stage = 0;
             phase ^= 1u;
           }
@@ -381,12 +390,14 @@ coarse_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
           uint32_t k = (u ^ (uint32_t(int32_t(u) >> 31) | 0x80000000u)) & ~127u;
           k |= 127u - (sub * kUnit + c + uint32_t(e));
           if (!full && list0 + e >= p.n_lists) { k = 0u; }
+          // sorted insert (key[.][0] >= key[.][1] >= ...): new key[t] = min(old key[t-1], max(old
+          // key[t], k)) -- 2 * kKeep - 1 independent min/max instead of a serial chain of 2 * kKeep
+          uint32_t up[kKeep];
 #pragma unroll
-          for (int t = 0; t < kKeep; t++) {
-            const uint32_t hi = max(key[e % kStreams][t], k);
-            k                 = min(key[e % kStreams][t], k);
-            key[e % kStreams][t] = hi;
-          }
+          for (int t = 0; t < kKeep; t++) { up[t] = max(key[e % kStreams][t], k); }
+#pragma unroll
+          for (int t = kKeep - 1; t > 0; t--) { key[e % kStreams][t] = min(key[e % kStreams][t - 1], up[t]); }
+          key[e % kStreams][0] = up[0];
         }
       }
       // the accumulator may be overwritten now
@@ -614,7 +625,7 @@ coarse_finish_kernel(const uint32_t* __restrict__ cand_key, const uint32_t* __re
 // queued for the exact redo.
 constexpr uint32_t kFinMaxHalfTiles = 512;
 constexpr uint32_t kFinMaxC         = 64;
-constexpr uint32_t kFinRows         = 32;  // rows rescored per round
+constexpr uint32_t kFinRows         = 64;  // most rows rescored per round (all selected lists at once)
 
 // 64 values per warp, value e = r * 32 + lane in register a<r>: full bitonic sort.
 template <typename T, bool Desc>
@@ -680,9 +691,10 @@ coarse_finish_small_kernel(const uint32_t* __restrict__ cand_key, const uint32_t
                            const float* __restrict__ fq, uint32_t n_lists, uint32_t dim_ext, float alpha,
                            uint32_t n_probes, uint32_t C, float cmax, float eps_rel,
                            uint32_t* __restrict__ probes, float* __restrict__ scores_out,
-                           uint32_t* __restrict__ redo_list, uint32_t* __restrict__ redo_count)
+                           uint32_t* __restrict__ redo_list, uint32_t* __restrict__ redo_count,
+                           uint32_t rows_per_round)
 {
-  // dynamic: query [dim_ext] | rows to rescore [kFinRows][dim_ext + 1]
+  // dynamic: query [dim_ext] | rows to rescore [rows_per_round][dim_ext + 1]
   extern __shared__ float s_dyn[];
   float* s_q    = s_dyn;
   float* s_rows = s_dyn + dim_ext;
@@ -788,8 +800,8 @@ coarse_finish_small_kernel(const uint32_t* __restrict__ cand_key, const uint32_t
 
   // ---- D: exact rescoring out of shared memory (rows padded against bank conflicts) ----
   const uint32_t row_words = dim_ext + 1;
-  for (uint32_t r0 = 0; r0 < n_sel; r0 += kFinRows) {
-    const uint32_t n_rows = min(kFinRows, n_sel - r0);
+  for (uint32_t r0 = 0; r0 < n_sel; r0 += rows_per_round) {
+    const uint32_t n_rows = min(rows_per_round, n_sel - r0);
     const uint32_t per4   = dim_ext / 4;  // dim_ext is a multiple of 4
     for (uint32_t e = tid; e < n_rows * per4; e += 256) {
       const uint32_t r = e / per4, c4 = e - r * per4;
@@ -1151,16 +1163,19 @@ void select_clusters_tc(raft::resources& res, const float* centers, const float*
   const size_t fin_smem = size_t(cap) * 8 + size_t(dim_ext) * 4 + size_t(n_cand) * 4;
   static size_t fin_configured = 48 * 1024;
   // the half-tile-maxima threshold is tight only when C is small against the number of half tiles
-  const size_t fin_small_smem = (size_t(dim_ext) + size_t(kFinRows) * (dim_ext + 1)) * 4;
+  // rows rescored per round: all 64 a query can select if they fit 48 KB of shared memory, else fewer
+  uint32_t fin_rows = kFinRows;
+  while (fin_rows > 32 && (size_t(dim_ext) + size_t(fin_rows) * (dim_ext + 1)) * 4 > 48 * 1024) { fin_rows /= 2; }
+  const size_t fin_small_smem = (size_t(dim_ext) + size_t(fin_rows) * (dim_ext + 1)) * 4;
   if (n_tiles * 2 <= kFinMaxHalfTiles && C <= kFinMaxC && C * 4 <= n_tiles * 2 && fin_small_smem <= 48 * 1024) {
     if (kph == 16) {
       coarse_finish_small_kernel<16><<<n_queries, 256, fin_small_smem, stream>>>(
         cand_key, cand_bnd, n_cand, centers, fq, n_lists, dim_ext, alpha, n_probes, C, cmax, eps_rel, probes,
-        scores_out, redo_list, words + 2);
+        scores_out, redo_list, words + 2, fin_rows);
     } else {
       coarse_finish_small_kernel<8><<<n_queries, 256, fin_small_smem, stream>>>(
         cand_key, cand_bnd, n_cand, centers, fq, n_lists, dim_ext, alpha, n_probes, C, cmax, eps_rel, probes,
-        scores_out, redo_list, words + 2);
+        scores_out, redo_list, words + 2, fin_rows);
     }
   } else {
     if (fin_smem > fin_configured) {
