@@ -174,50 +174,74 @@ __global__ void chunk_and_count_kernel(const uint32_t* __restrict__ probes,
   }
 }
 
-// Exclusive prefix sum over n values, in place, by one block of 1024 threads, 4 values per thread
-// per step.  data[n] must exist: it receives the total.
-__global__ void exclusive_scan_kernel(uint32_t* __restrict__ data, uint32_t n)
+// Exclusive prefix sum over n values, in place, by one block of 1024 threads.  data[n] must exist:
+// it receives the total; data must be 16-byte aligned.  Every thread owns one contiguous chunk: it
+// sums the chunk (independent 16-byte loads), the 1024 sums are scanned once across the block, and
+// the chunk is read again (from cache) to write the running prefix -- two barriers in all, where a
+// loop over 4096-value slices needed three per slice (26 us for 50,000 lists; 6 us this way).
+// `work_words` (optional): [0] = 0 (the scan kernel's work counter), [1] = the total.
+__global__ void __launch_bounds__(1024) exclusive_scan_kernel(uint32_t* __restrict__ data, uint32_t n,
+                                                              uint32_t* __restrict__ work_words)
 {
   __shared__ uint32_t s_warp[32];
-  __shared__ uint32_t s_carry;
   const uint32_t tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
-  if (tid == 0) { s_carry = 0; }
-  __syncthreads();
-  for (uint32_t base = 0; base < n; base += 4096) {
-    const uint32_t i0 = base + tid * 4;
-    uint32_t v[4];
+  const uint32_t per = round_up<uint32_t>(ceildiv<uint32_t>(n, 1024u), 4u);
+  const uint32_t lo  = min(n, tid * per);
+  const uint32_t hi  = min(n, lo + per);
+  uint32_t mine      = 0;
+  {
+    uint32_t i = lo;
+#pragma unroll 4
+    for (; i + 4 <= hi; i += 4) {
+      const uint4 v = *reinterpret_cast<const uint4*>(data + i);
+      mine += v.x + v.y + v.z + v.w;
+    }
+    for (; i < hi; i++) { mine += data[i]; }
+  }
+  uint32_t x = mine;
 #pragma unroll
-    for (int e = 0; e < 4; e++) { v[e] = (i0 + e < n) ? data[i0 + e] : 0u; }
-    const uint32_t mine = v[0] + v[1] + v[2] + v[3];
-    uint32_t x          = mine;
+  for (int d = 1; d < 32; d <<= 1) {
+    const uint32_t t = __shfl_up_sync(kFullMask, x, d);
+    if (lane >= uint32_t(d)) { x += t; }
+  }
+  if (lane == 31) { s_warp[wid] = x; }
+  __syncthreads();
+  if (wid == 0) {
+    uint32_t w = s_warp[lane];
 #pragma unroll
     for (int d = 1; d < 32; d <<= 1) {
-      uint32_t t = __shfl_up_sync(kFullMask, x, d);
-      if (lane >= uint32_t(d)) { x += t; }
+      const uint32_t t = __shfl_up_sync(kFullMask, w, d);
+      if (lane >= uint32_t(d)) { w += t; }
     }
-    if (lane == 31) { s_warp[wid] = x; }
-    __syncthreads();
-    if (wid == 0) {
-      uint32_t w = s_warp[lane];
-#pragma unroll
-      for (int d = 1; d < 32; d <<= 1) {
-        uint32_t t = __shfl_up_sync(kFullMask, w, d);
-        if (lane >= uint32_t(d)) { w += t; }
-      }
-      s_warp[lane] = w;
-    }
-    __syncthreads();
-    uint32_t run = s_carry + (wid > 0 ? s_warp[wid - 1] : 0u) + (x - mine);
-#pragma unroll
-    for (int e = 0; e < 4; e++) {
-      if (i0 + e < n) { data[i0 + e] = run; }
-      run += v[e];
-    }
-    __syncthreads();
-    if (tid == 1023) { s_carry = run; }
-    __syncthreads();
+    s_warp[lane] = w;
   }
-  if (tid == 0) { data[n] = s_carry; }
+  __syncthreads();
+  uint32_t run = (wid > 0 ? s_warp[wid - 1] : 0u) + (x - mine);
+  {
+    uint32_t i = lo;
+    for (; i + 4 <= hi; i += 4) {
+      const uint4 v = *reinterpret_cast<const uint4*>(data + i);
+      uint4 o;
+      o.x = run;
+      o.y = o.x + v.x;
+      o.z = o.y + v.y;
+      o.w = o.z + v.z;
+      run = o.w + v.w;
+      *reinterpret_cast<uint4*>(data + i) = o;
+    }
+    for (; i < hi; i++) {
+      const uint32_t v = data[i];
+      data[i]          = run;
+      run += v;
+    }
+  }
+  if (tid == 0) {
+    data[n] = s_warp[31];
+    if (work_words) {
+      work_words[0] = 0u;
+      work_words[1] = s_warp[31];
+    }
+  }
 }
 
 // Counters for the benchmark: sum over pairs, and over distinct probed lists, of ceil(size / 32).
@@ -250,10 +274,12 @@ __global__ void scatter_pairs_kernel(const uint32_t* __restrict__ probes,
                                      const uint32_t* __restrict__ list_sizes,
                                      const uint64_t* __restrict__ row_off, uint32_t n_pairs,
                                      uint32_t n_probes, uint32_t* __restrict__ cursor,
-                                     uint4* __restrict__ work, uint64_t* __restrict__ out_keys, uint32_t k)
+                                     uint4* __restrict__ work, uint64_t* __restrict__ out_keys, uint32_t k,
+                                     uint32_t* __restrict__ query_kth, uint32_t n_queries)
 {
   const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n_pairs) { return; }
+  if (i < n_queries) { query_kth[i] = kEmptyScore; }  // no bound on any query's k-th best yet
   const uint32_t label = probes[i];
   if (list_sizes[label] == 0) {
     // nothing to scan (e.g. a list owned by another GPU): the pair's result slots are empty
@@ -762,15 +788,13 @@ void search_any(raft::resources& res, const search_params& params, const index<i
                                                                                 n_lists, res.d_stats);
         res.stat_pairs += n_pairs;
       }
-      exclusive_scan_kernel<<<1, 1024, 0, stream>>>(d_count, n_lists);  // d_count[n_lists] = work items
-      CUDA_TRY(cudaMemcpyAsync(d_counter + 1, d_count + n_lists, 4, cudaMemcpyDeviceToDevice, stream));
+      // d_counter[0] = 0 (work counter), d_counter[1] = d_count[n_lists] = number of work items
+      exclusive_scan_kernel<<<1, 1024, 0, stream>>>(d_count, n_lists, d_counter);
       scatter_pairs_kernel<<<ceildiv<uint32_t>(n_pairs, 256), 256, 0, stream>>>(
         d_probes, d_chunk, idx.list_sizes(), idx.row_offsets(), n_pairs, n_probes, d_count, d_order,
-        store_all ? nullptr : d_keys, k);
-      fill_u32_kernel<<<ceildiv<uint32_t>(nq, 256), 256, 0, stream>>>(d_kth, nq, kEmptyScore);
-      CUDA_TRY(cudaMemsetAsync(d_counter, 0, 4, stream));
+        store_all ? nullptr : d_keys, k, d_kth, nq);
       CUDA_TRY(cudaGetLastError());
-      res.launches += 4;
+      res.launches += 3;
     }
 
     if (stats) { res.stats_mark(ev, 3); }
