@@ -74,3 +74,23 @@ def test_error_text_convention():
     assert lib.cuvsVersionGet(C.byref(a), C.byref(b), C.byref(c)) == _lib.CUVS_SUCCESS
     assert (a.value, b.value) == (26, 10)
     assert lib.cuvsGetLastErrorText() is None
+
+
+def test_tensor_descriptions_carry_strides_only_on_request():
+    """A non-contiguous tensor is refused unless the caller says the entry point takes strides (the
+    merge of gathered per-rank blocks does); then shape and strides are passed in elements."""
+    import pytest
+    import torch
+    from cuvs_b200.common import DLTensorRef
+    block = torch.zeros((3, 40), dtype=torch.float32)
+    parts = block[:, 8:32].view(3, 4, 6)                  # three [4, 6] parts, 40 elements apart
+    assert not parts.is_contiguous()
+    with pytest.raises(ValueError, match="row-major"):
+        DLTensorRef(parts)
+    ref = DLTensorRef(parts, strided=True)
+    t = ref.managed.dl_tensor
+    assert [t.shape[i] for i in range(3)] == [3, 4, 6]
+    assert [t.strides[i] for i in range(3)] == [40, 6, 1]
+    assert t.data == parts.data_ptr()
+    whole = DLTensorRef(block)
+    assert not whole.managed.dl_tensor.strides            # contiguous: no strides, as before
