@@ -60,7 +60,9 @@ CUVS_EXPORT cuvsError_t cuvsMultiGpuIvfPqSerializeRanks(cuvsResources_t res,
  * knn_merge_parts, cpp/src/neighbors/detail/knn_merge_parts.cuh:24-170): part_distances f32 and
  * part_neighbors i64 are [n_parts, n_queries, k] device tensors; distances / neighbors are
  * [n_queries, k].  select_min = true keeps the smallest distances (L2, cosine), false the largest
- * (inner product).  Entries whose neighbour is INT64_MAX are ignored. */
+ * (inner product).  Entries whose neighbour is INT64_MAX are ignored.  Each part must be row-major;
+ * the parts themselves may lie apart (DLPack strides {s, k, 1} with s >= n_queries * k), e.g. as
+ * views into one buffer that an all-gather filled with a block of ids and distances per rank. */
 CUVS_EXPORT cuvsError_t cuvsMultiGpuIvfPqMergeParts(cuvsResources_t res,
                                                     DLManagedTensor* part_distances,
                                                     DLManagedTensor* part_neighbors,
