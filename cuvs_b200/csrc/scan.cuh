@@ -348,8 +348,8 @@ __device__ __forceinline__ void tmem_ld(uint32_t taddr, uint32_t (&r)[N])
   }
 }
 
-// Codebook layout in TMEM (written once per CTA by threads 0..127, read by every thread from the
-// lane tid % 128).  Lane L serves the four-entry unit u = L % kUPJ of the subspaces
+// Codebook layout in TMEM (written once per CTA, lane L by the threads with tid % 128 == L, and read
+// by every thread from the lane tid % 128).  Lane L serves the four-entry unit u = L % kUPJ of the subspaces
 // j = L / kUPJ + m * (128 / kUPJ), m = 0, 1, ...  A group of `gthreads` threads (a multiple of 128)
 // gives thread gt the unit gt % kUPJ of subspaces gt / kUPJ + i * gthreads / kUPJ, i.e.
 // m = gt / 128 + i * m_stride with m_stride = gthreads / 128; the blocks of one thread's successive
@@ -363,15 +363,17 @@ __device__ __forceinline__ uint32_t tmem_iters_per_thread(uint32_t pq_dim, uint3
 }
 template <int PqBits, int LEN>
 __device__ __forceinline__ void fill_codebook_tmem(uint32_t tmem_lane_a, const float* pq_centers,
-                                                   uint32_t pq_dim, uint32_t lane128, uint32_t m_stride)
+                                                   uint32_t pq_dim, uint32_t lane128, uint32_t m_stride,
+                                                   uint32_t part, uint32_t n_parts)
 {
   constexpr uint32_t kBook  = 1u << PqBits;
   constexpr uint32_t kUPJ   = kBook / 4;
   constexpr uint32_t kJPerM = 128u / kUPJ;
   const uint32_t u          = lane128 % kUPJ;
   const uint32_t ipt        = tmem_iters_per_thread(pq_dim, kJPerM, m_stride);
+  // the 128-thread slices of the CTA (every fourth warp reaches the same TMEM lanes) share the blocks
 #pragma unroll 4
-  for (uint32_t m = 0; m < ipt * m_stride; m++) {
+  for (uint32_t m = part; m < ipt * m_stride; m += n_parts) {
     const uint32_t j     = lane128 / kUPJ + m * kJPerM;
     const uint32_t block = (m % m_stride) * ipt + m / m_stride;
 #pragma unroll
@@ -660,12 +662,14 @@ __global__ void __launch_bounds__(1024, 1) scan_kernel(const scan_params p)
     __syncthreads();
     tmem_fence_after();
     tmem_base = *reinterpret_cast<volatile uint32_t*>(slot);
-    if (tid < 128) {
-      const uint32_t lane_a = tmem_base + ((uint32_t(tid) & ~31u) << 16);
+    {
+      // lane L of tensor memory is written by the threads with tid % 128 == L
+      const uint32_t lane128 = uint32_t(tid) & 127u, part = uint32_t(tid) >> 7, n_parts = blockDim.x >> 7;
+      const uint32_t lane_a  = tmem_base + ((lane128 & ~31u) << 16);
       switch (p.pq_len) {
-        case 1: fill_codebook_tmem<PqBits, 1>(lane_a, p.pq_centers, p.pq_dim, uint32_t(tid), p.group_threads / 128u); break;
-        case 2: fill_codebook_tmem<PqBits, 2>(lane_a, p.pq_centers, p.pq_dim, uint32_t(tid), p.group_threads / 128u); break;
-        default: fill_codebook_tmem<PqBits, 4>(lane_a, p.pq_centers, p.pq_dim, uint32_t(tid), p.group_threads / 128u); break;
+        case 1: fill_codebook_tmem<PqBits, 1>(lane_a, p.pq_centers, p.pq_dim, lane128, p.group_threads / 128u, part, n_parts); break;
+        case 2: fill_codebook_tmem<PqBits, 2>(lane_a, p.pq_centers, p.pq_dim, lane128, p.group_threads / 128u, part, n_parts); break;
+        default: fill_codebook_tmem<PqBits, 4>(lane_a, p.pq_centers, p.pq_dim, lane128, p.group_threads / 128u, part, n_parts); break;
       }
     }
     tmem_fence_before();
