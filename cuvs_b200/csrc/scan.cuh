@@ -643,10 +643,11 @@ __global__ void __launch_bounds__(1024, 1) scan_kernel(const scan_params p)
   // bound on the k-th best ordered score of the current pair.
   const uint32_t goff    = p.smem_pqc_bytes + uint32_t(g) * p.smem_group_bytes;
   const uint32_t lut_a   = smem_addr(smem) + goff;
-#define S_BASE_A (lut_a + p.lut_bytes)
-#define S_MERGE_A (lut_a + p.lut_bytes + p.base_bytes)
-#define S_ITEM_A (lut_a + p.lut_bytes + p.base_bytes + p.merge_bytes)
-#define S_THR_A (S_ITEM_A + 8u)
+  // (recomputed from the parameters where used, so that none of them occupies a register for the
+  // life of the kernel)
+  const auto s_base_a = [&] { return lut_a + p.lut_bytes; };
+  const auto s_item_a = [&] { return lut_a + p.lut_bytes + p.base_bytes + p.merge_bytes; };
+  const auto s_thr_a  = [&] { return s_item_a() + 8u; };
 
   uint32_t tmem_base = 0;
   if (p.tmem_cols) {
@@ -695,13 +696,13 @@ __global__ void __launch_bounds__(1024, 1) scan_kernel(const scan_params p)
   // the launch is dealt more evenly pair by pair).
   const uint32_t n_work = __ldg(p.n_work);
   constexpr uint32_t claim = 1u;
-  if (gt == 0) { sts_b32(S_ITEM_A, atomicAdd(p.work_counter, claim)); }
+  if (gt == 0) { sts_b32(s_item_a(), atomicAdd(p.work_counter, claim)); }
   for (uint32_t it = 0;; it++) {
     group_bar(bar_id, gthreads);
-    const uint32_t w = lds_b32_volatile(S_ITEM_A + 4u * ((it / claim) & 1u)) + (it % claim);
+    const uint32_t w = lds_b32_volatile(s_item_a() + 4u * ((it / claim) & 1u)) + (it % claim);
     if (w >= n_work) { break; }
     if (gt == 0 && (it % claim) == 0) {
-      sts_b32(S_ITEM_A + 4u * (((it / claim) + 1u) & 1u), atomicAdd(p.work_counter, claim));
+      sts_b32(s_item_a() + 4u * (((it / claim) + 1u) & 1u), atomicAdd(p.work_counter, claim));
     }
 
     const uint4 d0       = __ldg(p.work + 2 * size_t(w));
@@ -722,7 +723,7 @@ __global__ void __launch_bounds__(1024, 1) scan_kernel(const scan_params p)
     }
 
     // ---- base diff ----
-    if (gt == 0) { sts_b32(S_THR_A, *reinterpret_cast<volatile uint32_t*>(p.query_kth + q)); }
+    if (gt == 0) { sts_b32(s_thr_a(), *reinterpret_cast<volatile uint32_t*>(p.query_kth + q)); }
     {
       const float* rq = p.rot_q + size_t(q) * p.rot_dim;
       const float* c  = p.centers_rot + size_t(label) * p.rot_dim;
@@ -730,11 +731,11 @@ __global__ void __launch_bounds__(1024, 1) scan_kernel(const scan_params p)
       for (uint32_t i = gt; i < p.rot_dim; i += gthreads) {
         if constexpr (!IsIP) {
           const float d = __fsub_rn(rq[i], __ldg(c + i));
-          sts_b64(S_BASE_A + 8u * i, pack2(d, d));
+          sts_b64(s_base_a() + 8u * i, pack2(d, d));
         } else {
           const float qv = rq[i];
           const float y  = __fmul_rn(__ldg(c + i), qv);
-          sts_b128(S_BASE_A + 16u * i, pack2(-qv, -qv), pack2(y, y));
+          sts_b128(s_base_a() + 16u * i, pack2(-qv, -qv), pack2(y, y));
         }
       }
     }
@@ -751,14 +752,14 @@ __global__ void __launch_bounds__(1024, 1) scan_kernel(const scan_params p)
 
     // ---- LUT ----
     if (p.tmem_cols) {
-      const uint32_t base_a = S_BASE_A;
+      const uint32_t base_a = s_base_a();
       switch (len) {
         case 1: build_lut_tmem<PqBits, LutKind, IsIP, 1>(tmem_lane_a, base_a, lut_a, p.pq_dim, gt, gthreads); break;
         case 2: build_lut_tmem<PqBits, LutKind, IsIP, 2>(tmem_lane_a, base_a, lut_a, p.pq_dim, gt, gthreads); break;
         default: build_lut_tmem<PqBits, LutKind, IsIP, 4>(tmem_lane_a, base_a, lut_a, p.pq_dim, gt, gthreads); break;
       }
     } else if (p.pqc_in_smem) {
-      const uint32_t pqc_a = smem_addr(s_pqc), base_a = S_BASE_A;
+      const uint32_t pqc_a = smem_addr(s_pqc), base_a = s_base_a();
       switch (len) {
         case 1: build_lut_smem<PqBits, LutKind, IsIP, 1>(pqc_a, base_a, lut_a, p.pq_dim, len, gt, gthreads); break;
         case 2: build_lut_smem<PqBits, LutKind, IsIP, 2>(pqc_a, base_a, lut_a, p.pq_dim, len, gt, gthreads); break;
@@ -845,10 +846,10 @@ __global__ void __launch_bounds__(1024, 1) scan_kernel(const scan_params p)
           const uint32_t ord   = float_to_ordered(score);
           const uint64_t key   = (uint64_t(ord) << 32) | (sample_offset + row);
           // s_thr never exceeds the final k-th best score of the query, so nothing wanted is lost
-          const uint32_t thr   = lds_b32_volatile(S_THR_A);
+          const uint32_t thr   = lds_b32_volatile(s_thr_a());
           const uint64_t before = queue.kth();
           queue.offer(key, valid && ord <= thr);
-          if (queue.kth() != before && lane == 0) { atoms_min_u32(S_THR_A, uint32_t(queue.kth() >> 32)); }
+          if (queue.kth() != before && lane == 0) { atoms_min_u32(s_thr_a(), uint32_t(queue.kth() >> 32)); }
         }
       }
     }
@@ -881,11 +882,6 @@ __global__ void __launch_bounds__(1024, 1) scan_kernel(const scan_params p)
     }
   }
 }
-
-#undef S_BASE_A
-#undef S_MERGE_A
-#undef S_ITEM_A
-#undef S_THR_A
 
 // Host-side launcher of one instantiation family (defined once per PqBits in scan_inst.cu).
 void launch_scan(const scan_params& p, int pq_bits, int lut_kind, bool out_half, bool is_ip,
