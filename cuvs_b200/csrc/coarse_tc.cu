@@ -36,6 +36,7 @@
 #include <cuda.h>
 
 #include <algorithm>
+#include <type_traits>
 #include <mutex>
 
 namespace cuvs::neighbors::ivf_pq {
@@ -384,20 +385,35 @@ coarse_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
         tmem_ld32(tmem_base + ((quarter * 32u) << 16) + acc * kBN + col0 + c, r);
         const uint32_t list0 = n0 + c;
         const bool full      = list0 + 32 <= p.n_lists;
+        // The epilogue is bound by the integer pipe, so the per-element sequence is kept minimal:
+        // shift, xor (order-preserving image), and-or with this 32-column group's tag base, xor with
+        // the column (the base ends in five one bits, so base ^ e == base - e), then the insert.
+        // The range check exists only in the version used by the last, partial list tile.
+        const uint32_t tag_base = 127u - (sub * kUnit + c);
+        auto take = [&](auto full_c) {
+          constexpr bool kFull = decltype(full_c)::value;
 #pragma unroll
-        for (int e = 0; e < 32; e++) {
-          const uint32_t u = r[e];
-          uint32_t k = (u ^ (uint32_t(int32_t(u) >> 31) | 0x80000000u)) & ~127u;
-          k |= 127u - (sub * kUnit + c + uint32_t(e));
-          if (!full && list0 + e >= p.n_lists) { k = 0u; }
-          // sorted insert (key[.][0] >= key[.][1] >= ...): new key[t] = min(old key[t-1], max(old
-          // key[t], k)) -- 2 * kKeep - 1 independent min/max instead of a serial chain of 2 * kKeep
-          uint32_t up[kKeep];
+          for (int e = 0; e < 32; e++) {
+            const uint32_t u = r[e];
+            uint32_t k = u ^ (uint32_t(int32_t(u) >> 31) | 0x80000000u);
+            k          = ((k & ~127u) | tag_base) ^ uint32_t(e);
+            if constexpr (!kFull) {
+              if (list0 + e >= p.n_lists) { k = 0u; }
+            }
+            // sorted insert (key[.][0] >= key[.][1] >= ...): new key[t] = min(old key[t-1], max(old
+            // key[t], k)) -- 2 * kKeep - 1 independent min/max
+            uint32_t up[kKeep];
 #pragma unroll
-          for (int t = 0; t < kKeep; t++) { up[t] = max(key[e % kStreams][t], k); }
+            for (int t = 0; t < kKeep; t++) { up[t] = max(key[e % kStreams][t], k); }
 #pragma unroll
-          for (int t = kKeep - 1; t > 0; t--) { key[e % kStreams][t] = min(key[e % kStreams][t - 1], up[t]); }
-          key[e % kStreams][0] = up[0];
+            for (int t = kKeep - 1; t > 0; t--) { key[e % kStreams][t] = min(key[e % kStreams][t - 1], up[t]); }
+            key[e % kStreams][0] = up[0];
+          }
+        };
+        if (full) {
+          take(std::true_type{});
+        } else {
+          take(std::false_type{});
         }
       }
       // the accumulator may be overwritten now
