@@ -701,6 +701,41 @@ ORC_EXPORT void orc_build_lut(const orc_index* ix, uint32_t label, const float* 
   free(base);
 }
 
+/* Internal scores of every vector of one (query, list) pair, widened to fp32, in stored order:
+ * what compute_distances_impl.cuh:73-90 produces before the top-k.  Returns -1 for the one invalid
+ * pairing (fp32 table with fp16 internal distances). */
+ORC_EXPORT int orc_pair_scores(const orc_index* ix, uint32_t label, const float* rot_q, int lut_dtype,
+                               int internal_dtype, float* scores)
+{
+  init_tables();
+  if (internal_dtype == DT_F16 && lut_dtype == DT_F32) { return -1; }
+  const size_t lut_n = (size_t)ix->pq_dim << ix->pq_bits;
+  lut_t lut;
+  void* lut_raw  = malloc(lut_n * 4);
+  lut.lut_dtype  = lut_dtype;
+  lut.is_signed  = !is_l2(ix->metric);
+  lut.f32        = (float*)lut_raw;
+  lut.f16        = (uint16_t*)lut_raw;
+  lut.u8         = (uint8_t*)lut_raw;
+  float* lutf    = (float*)malloc(lut_n * 4);
+  uint16_t* luth = (uint16_t*)malloc(lut_n * 2);
+  float* base    = (float*)malloc((size_t)ix->rot_dim * 2 * sizeof(float));
+  build_lut(ix, label, rot_q, &lut, base);
+  decode_lut(&lut, lut_n, internal_dtype, lutf, luth);
+  if (internal_dtype == DT_F32) {
+    scan_list_f32(ix, label, lutf, ix->metric == M_COSINE, scores);
+  } else {
+    scan_list_f16(ix, label, luth, ix->metric == M_COSINE, scores);
+  }
+  free(lut_raw);
+  free(lutf);
+  free(luth);
+  free(base);
+  return 0;
+}
+
+ORC_EXPORT float orc_postprocess(float score, int metric, float scale) { return postprocess(score, metric, scale); }
+
 /* Fine search given the probes: neighbours [n_q,k] int64, distances [n_q,k] f32.
  * Optional raw outputs: internal scores before post-processing. */
 /* Bitset sample filter (cpp/src/neighbors/sample_filter.cuh:162-176): a vector is searched only if

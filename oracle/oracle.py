@@ -55,15 +55,63 @@ def build_lib(force: bool = False) -> str:
     return so
 
 
-def build_ref_pin(reference_root: str = "/root/reference") -> str | None:
+def reference_root() -> str | None:
+    """The reference checkout, named by the environment variable CUVS_REFERENCE_ROOT or found as a
+    `reference` folder beside this repository; None where there is none (e.g. on a GPU box)."""
+    cand = os.environ.get("CUVS_REFERENCE_ROOT") or os.path.join(
+        os.path.dirname(os.path.dirname(_HERE)), "reference")
+    return cand if os.path.isdir(os.path.join(cand, "cpp", "src", "neighbors", "ivf_pq")) else None
+
+
+def _make(target: str, ref: str) -> None:
+    env = dict(os.environ)
+    env.pop("CC", None)
+    env.pop("CXX", None)
+    subprocess.check_call(["make", "-C", _HERE, target, f"REF={ref}"], env=env, stdout=subprocess.DEVNULL)
+
+
+def build_ref_pin(root: str | None = None) -> str | None:
     """Compile oracle/_ref/libref_pin.so from two headers of the reference checkout, if present."""
     so = os.path.join(_HERE, "_ref", "libref_pin.so")
-    if os.path.isdir(reference_root):
-        env = dict(os.environ)
-        env.pop("CC", None)
-        env.pop("CXX", None)
-        subprocess.check_call(["make", "-C", _HERE, "ref", f"REF={reference_root}"], env=env,
-                              stdout=subprocess.DEVNULL)
+    root = root or reference_root()
+    if root:
+        _make("ref", root)
+    return so if os.path.exists(so) else None
+
+
+def _cut(text: str, start: str, end: str, what: str) -> str:
+    a = text.find(start)
+    b = text.find(end, a + 1) if a >= 0 else -1
+    if a < 0 or b < 0:
+        raise RuntimeError(f"reference layout changed: cannot find {what}")
+    return text[a:b]
+
+
+def build_ref_pin_dev(root: str | None = None) -> str | None:
+    """Compile oracle/_ref/libref_pin_dev.so (nvcc, sm_100a) from the reference's scoring headers, if
+    the checkout is present.  Two of the headers drag in the un-vendored memory libraries, so only the
+    parts under test are cut out of them, verbatim, into oracle/_ref/extract/ (untracked):
+    `config<>` + `mapping<>` of cpp/src/neighbors/detail/ann_utils.cuh, and kOutOfBoundsRecord,
+    find_chunk_ix, postprocess_neighbors and postprocess_distances of cpp/src/neighbors/ivf_common.cuh."""
+    so = os.path.join(_HERE, "_ref", "libref_pin_dev.so")
+    root = root or reference_root()
+    if root:
+        ext = os.path.join(_HERE, "_ref", "extract")
+        os.makedirs(ext, exist_ok=True)
+        ann = open(os.path.join(root, "cpp/src/neighbors/detail/ann_utils.cuh")).read()
+        part = _cut(ann, "template <typename T>\nstruct config {};", "/**\n * @brief Sets the first num bytes",
+                    "config<> / mapping<> in ann_utils.cuh")
+        com = open(os.path.join(root, "cpp/src/neighbors/ivf_common.cuh")).read()
+        oob = _cut(com, "template <typename IdxT>\nconstexpr static IdxT kOutOfBoundsRecord", "\n\n",
+                   "kOutOfBoundsRecord in ivf_common.cuh")
+        post = _cut(com, "__device__ inline auto find_chunk_ix", "/** Update the state of the dependent index",
+                    "the post-processing functions in ivf_common.cuh")
+        for name, body in (("ann_utils_mapping.inc", part), ("ivf_common_postprocess.inc", oob + "\n\n" + post)):
+            path = os.path.join(ext, name)
+            if not os.path.exists(path) or open(path).read() != body:
+                with open(path, "w") as f:
+                    f.write(body)
+        _make("refdev", root)
     return so if os.path.exists(so) else None
 
 
@@ -540,6 +588,28 @@ def build_lut(ix: OracleIndex, label: int, rot_q: np.ndarray, lut_dtype: int) ->
     rq = np.ascontiguousarray(rot_q, dtype=np.float32)
     lib().orc_build_lut(C.byref(s), C.c_uint32(label), _ptr(rq), C.c_int(lut_dtype), _ptr(out))
     return out
+
+
+def pair_scores(ix: OracleIndex, label: int, rot_q: np.ndarray, lut_dtype: int,
+                internal_dtype: int = CUDA_R_32F) -> np.ndarray:
+    """Internal score of every vector of list `label` for one rotated query, in stored order."""
+    out = np.zeros(int(ix.list_sizes[label]), dtype=np.float32)
+    s = ix.c_struct()
+    rq = np.ascontiguousarray(rot_q, dtype=np.float32)
+    rc = lib().orc_pair_scores(C.byref(s), C.c_uint32(label), _ptr(rq), C.c_int(lut_dtype),
+                               C.c_int(internal_dtype), _ptr(out))
+    if rc != 0:
+        raise ValueError("unsupported lut_dtype / internal_distance_dtype combination")
+    return out
+
+
+def postprocess(scores: np.ndarray, metric: int, scale: float = 1.0) -> np.ndarray:
+    f = lib().orc_postprocess
+    f.restype = C.c_float
+    f.argtypes = [C.c_float, C.c_int, C.c_float]
+    flat = np.asarray(scores, dtype=np.float32).reshape(-1)
+    return np.array([f(float(v), int(metric), float(scale)) for v in flat],
+                    dtype=np.float32).reshape(np.shape(scores))
 
 
 def search_probes(ix: OracleIndex, rot_q, probes, k, lut_dtype=CUDA_R_32F,

@@ -1,11 +1,12 @@
-// Shim standing in for the reference's public header when its fp_8bit and code-packing headers are
-// compiled on the host for the oracle pin.  Only the three declarations those headers use are
-// restated here (group size, piece size, extents of an interleaved list:
-// cpp/include/cuvs/neighbors/ivf_pq.hpp:222-247).
+// Shim standing in for the reference's public header when single headers of its search path are
+// compiled for the oracle pins.  Only the declarations those headers use are restated here
+// (codebook kind, group size, piece size, extents of an interleaved list:
+// cpp/include/cuvs/neighbors/ivf_pq.hpp:34-37, 222-247).
 #pragma once
 #include <cstdint>
 #include <raft/core/device_mdspan.hpp>
 namespace cuvs::neighbors::ivf_pq {
+enum class codebook_gen { PER_SUBSPACE = 0, PER_CLUSTER = 1 };
 constexpr static uint32_t kIndexGroupSize   = 32;
 constexpr static uint32_t kIndexGroupVecLen = 16;
 template <typename SizeT, typename IdxT>
