@@ -20,15 +20,24 @@
  *   - final selection, id translation .. cpp/src/neighbors/ivf_pq/ivf_pq_search.cuh:646-674,
  *                                       cpp/src/neighbors/ivf_common.cuh:94-252
  *
- * PARITY UNPINNED for neighbour ids and distances: the reference ships no golden vectors for this
- * path and cannot be compiled in the authoring environment (it needs RAFT, RMM, rtcx).  What is
- * pinned: the 8-bit float (against the reference header compiled into oracle/_ref, see
- * oracle/ref_pin.cpp) and the bit-field code layout (same).  Two summation orders live in binary-only
- * cuBLAS in the reference (coarse GEMM, rotation GEMM); here they are sequential fused
- * multiply-adds over the inner dimension, which is also what the GPU rescoring pass computes.
+ * PINNED against the reference's own code: the 8-bit float and the bit-field code layout (host build
+ * of two reference headers, oracle/ref_pin.cpp); base differences, look-up tables in their three
+ * storage types, code unpack + per-vector scores in both internal distance types, the cosine
+ * increment, the value mappings, distance post-processing and the sample-index -> source-id
+ * translation (device build of the reference's headers by nvcc, oracle/ref_pin_dev.cu, run on a B200;
+ * its outputs are the golden vectors tests/golden/ref_dev.npz, and the GPU tests compare the three
+ * implementations live).  NOT PINNED, because the reference has no code of its own to pin against:
+ * the summation order of the two library GEMMs (coarse scores, query rotation: binary-only cuBLAS in
+ * the reference; here sequential fused multiply-adds over the inner dimension, which is also what the
+ * GPU rescoring pass computes), the order of equal scores in select_k (un-vendored RAFT; the
+ * reference calls it with sorted=false, so the order is unspecified; fixed here to (score, sample
+ * index) ascending), and the .npy framing of index files (un-vendored RAFT serializer; checked against
+ * numpy instead).  The reference's inner-product table has a second variant, taken when shared
+ * memory is short (base differences not precomputed), in which nvcc contracts q * c into the
+ * subtraction: its tables differ from the precomputed variant in the last bit of some entries.  This
+ * file, and the engine, follow the precomputed variant (the reference's first choice).
  * The reference's pruning (per-query k-th bound, L2 early exit) is dropped: it only discards
- * candidates that cannot reach the top-k.  Tie order, unspecified in the reference
- * (select_k is called with sorted=false), is fixed here to (score, sample index) ascending.
+ * candidates that cannot reach the top-k.
  */
 #include <math.h>
 #include <stdint.h>

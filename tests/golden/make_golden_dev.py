@@ -13,6 +13,7 @@ repository; the CPU tests that read it need neither the reference nor a GPU.
 """
 import os
 import sys
+import zlib
 
 import numpy as np
 
@@ -67,7 +68,11 @@ def main(out_path):
                                   c["pq_centers"], c["codes"], c["code_off"], c["list_sizes"], lut_dtype, out_half)
                 tag = f"c{i}_t{lut_dtype}_h{int(out_half)}_p{precomp}"
                 if not out_half:
-                    out[tag + "_lut"] = lut.view(np.uint8)
+                    # the table itself where it is small, its CRC-32 always
+                    raw = np.ascontiguousarray(lut).view(np.uint8)
+                    out[tag + "_lutcrc"] = np.uint32(zlib.crc32(raw.tobytes()))
+                    if raw.size <= 16384 and precomp:
+                        out[tag + "_lut"] = raw
                 out[tag + "_scores"] = sc.view(np.uint32)
     rng = np.random.default_rng(77)
     sweep = np.concatenate([rng.standard_normal(400).astype(np.float32) * np.float32(s)

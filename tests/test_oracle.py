@@ -227,3 +227,100 @@ def test_int8_coarse_search_restatement(oracle_mod):
     r32 = O.recall(O.search(ix, q, 10, n_probes=8)[1], gt_i)
     r8 = O.recall(O.search_int8_coarse(ix, q, 10, n_probes=8)[1], gt_i)
     assert r8 > r32 - 0.08, (r8, r32)
+
+
+# ------------------------------------------------------------------------------------------------
+# Pins against tests/golden/ref_dev.npz: outputs of the reference's own scoring code (look-up table,
+# code unpack + score, cosine increment, 8-bit float, value mappings, distance and neighbour
+# post-processing) compiled by nvcc from the reference checkout and run on a B200
+# (oracle/ref_pin_dev.cu, generator tests/golden/make_golden_dev.py).
+# ------------------------------------------------------------------------------------------------
+GOLDEN_DEV = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "ref_dev.npz")
+
+
+@pytest.fixture(scope="module")
+def gdev():
+    return np.load(GOLDEN_DEV)
+
+
+def _index_from_golden(O, g, i):
+    bits, pq_dim, pq_len, metric, kind, n_lists = (int(v) for v in g[f"c{i}_meta"])
+    dim = pq_dim * pq_len
+    sizes = g[f"c{i}_list_sizes"]
+    ix = O.OracleIndex(metric, kind, dim, pq_dim, bits, n_lists, g[f"c{i}_pq_centers"],
+                       np.zeros((n_lists, O.round_up(dim + 1, 8)), np.float32), g[f"c{i}_centers_rot"],
+                       np.eye(dim, dtype=np.float32), sizes)
+    codes, off = g[f"c{i}_codes"], g[f"c{i}_code_off"]
+    ix.list_codes = [codes[int(off[l]):int(off[l]) + O.list_bytes(int(sizes[l]), pq_dim, bits)].copy()
+                     for l in range(n_lists)]
+    ix.list_ids = [np.arange(int(s), dtype=np.int64) for s in sizes]
+    return ix
+
+
+@pytest.mark.parametrize("case", range(13))
+def test_tables_and_scores_match_reference_golden(oracle_mod, gdev, case):
+    import zlib
+    O, g = oracle_mod, gdev
+    assert case < int(g["n_cases"])
+    ix = _index_from_golden(O, g, case)
+    pq, pl = g[f"c{case}_pair_query"], g[f"c{case}_pair_label"]
+    for lut_dtype, out_half in ((O.CUDA_R_32F, 0), (O.CUDA_R_16F, 0), (O.CUDA_R_16F, 1), (O.CUDA_R_8U, 0),
+                                (O.CUDA_R_8U, 1)):
+        tag = f"c{case}_t{lut_dtype}_h{out_half}_p1"
+        luts = np.stack([O.build_lut(ix, int(pl[p]), pq[p], lut_dtype) for p in range(pl.shape[0])])
+        if not out_half:
+            raw = np.ascontiguousarray(luts).view(np.uint8)
+            assert np.uint32(zlib.crc32(raw.tobytes())) == g[tag + "_lutcrc"]
+            if tag + "_lut" in g:
+                assert (raw.reshape(-1) == g[tag + "_lut"].reshape(-1)).all()
+        ref = g[tag + "_scores"]
+        for p in range(pl.shape[0]):
+            s = O.pair_scores(ix, int(pl[p]), pq[p], lut_dtype, O.CUDA_R_16F if out_half else O.CUDA_R_32F)
+            assert (s.view(np.uint32) == ref[p, :s.size]).all(), (lut_dtype, out_half, p)
+        # L2: the reference's variant without precomputed base differences is the same arithmetic
+        if ix.metric in (O.L2Expanded, O.L2SqrtExpanded):
+            assert (g[f"c{case}_t{lut_dtype}_h{out_half}_p0_scores"] == ref).all()
+
+
+def test_value_types_match_reference_device_golden(oracle_mod, gdev):
+    O, g = oracle_mod, gdev
+    L = O.lib()
+    for sg in (0, 1):
+        enc = np.array([L.orc_fp8_encode(float(v), sg) for v in g["fp8_inputs"]], dtype=np.uint8)
+        assert (enc == g[f"fp8_enc_s{sg}"]).all()
+        d32 = np.array([L.orc_fp8_decode(b, sg) for b in range(256)], dtype=np.float32)
+        assert (d32.view(np.uint32) == g[f"fp8_all32_s{sg}"]).all()
+        d16 = np.array([L.orc_fp8_decode_half(b, sg) for b in range(256)], dtype=np.uint16)
+        fin = np.isfinite(g[f"fp8_all16_s{sg}"].view(np.float16))
+        assert (d16[fin] == g[f"fp8_all16_s{sg}"][fin]).all()
+    for name in ("f16", "i8", "u8"):
+        assert (O.map_to_float(g[f"map_in_{name}"]).view(np.uint32) == g[f"map_{name}_to_f32"]).all()
+    # mapping<int8_t>: fp32 (clamped), uint8 (halved), int8 (identity)
+    assert (O.map_from_float(g["map_in_f32"], np.int8) == g["map_f32_to_i8"]).all()
+    assert ((g["map_in_u8"] >> 1).astype(np.int8) == g["map_u8_to_i8"]).all()
+    assert (g["map_in_i8"] == g["map_i8_to_i8"]).all()
+
+
+def test_postprocessing_matches_reference_device_golden(oracle_mod, gdev):
+    O, g = oracle_mod, gdev
+    sc = g["post_in"]
+    for metric in (O.L2Expanded, O.L2SqrtExpanded, O.CosineExpanded, O.InnerProduct):
+        for scale in (1, 128, 256):
+            src = -sc if metric == O.InnerProduct else sc
+            mine = O.postprocess(src, metric, float(scale)).view(np.uint32)
+            for in_place in (0, 1):
+                assert (mine == g[f"post_m{metric}_s{scale}_i{in_place}"]).all(), (metric, scale)
+    # sample index -> probe -> source id (find_chunk_ix + postprocess_neighbors_kernel)
+    sizes, ids, probes, chunk, samples = (g[k] for k in ("nb_sizes", "nb_ids", "nb_probes", "nb_chunk", "nb_samples"))
+    id_off = np.concatenate([[0], np.cumsum(sizes)[:-1]])
+    for r in range(samples.shape[0]):
+        for c in range(samples.shape[1]):
+            s, p = int(samples[r, c]), 0
+            while p < probes.shape[1] and chunk[r, p] <= s:
+                p += 1
+            if p < probes.shape[1]:
+                row = s - (int(chunk[r, p - 1]) if p else 0)
+                exp = ids[int(id_off[probes[r, p]]) + row]
+            else:
+                exp = O.OUT_OF_BOUNDS
+            assert g["nb_out"][r, c] == exp
