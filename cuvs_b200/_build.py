@@ -26,7 +26,8 @@ UNITS = [("resources.cu", "resources.o", []), ("index.cu", "index.o", []),
          ("coarse.cu", "coarse.o", []), ("coarse_tc.cu", "coarse_tc.o", []), ("search.cu", "search.o", []),
          ("build.cu", "build.o", []), ("c_api.cu", "c_api.o", []),
          ("no_alloc.cu", "no_alloc.o", []), ("refine.cu", "refine.o", []),
-         ("dynamic_batching.cu", "dynamic_batching.o", [])]
+         ("dynamic_batching.cu", "dynamic_batching.o", []), ("mg.cu", "mg.o", []),
+         ("c_api_mg.cu", "c_api_mg.o", [])]
 UNITS += [("scan_inst.cu", f"scan_{b}.o", [f"-DPQ_BITS={b}"]) for b in (4, 5, 6, 7, 8)]
 
 
@@ -73,7 +74,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
         results = list(ex.map(compile_one, UNITS))
     objs = [o for o, _ in results]
     if force or any(c for _, c in results) or not os.path.exists(LIB):
-        cmd = [nvcc, "-shared", "-o", LIB, *objs]
+        cmd = [nvcc, "-shared", "-o", LIB, *objs, "-ldl"]
         r = subprocess.run(cmd, env=env, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")

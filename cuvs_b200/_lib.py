@@ -74,6 +74,19 @@ class IndexStruct(C.Structure):
     _fields_ = [("addr", C.c_size_t), ("dtype", DLDataType)]
 
 
+class MgIndexParamsStruct(C.Structure):
+    _fields_ = [("base_params", C.POINTER(IndexParamsStruct)), ("mode", C.c_int)]
+
+
+class MgSearchParamsStruct(C.Structure):
+    _fields_ = [("base_params", C.POINTER(SearchParamsStruct)), ("search_mode", C.c_int),
+                ("merge_mode", C.c_int), ("n_rows_per_batch", C.c_int64)]
+
+
+class CommId(C.Structure):
+    _fields_ = [("bytes", C.c_char * 128)]
+
+
 class SearchStats(C.Structure):
     _fields_ = [("prep_ms", C.c_double), ("coarse_ms", C.c_double), ("sort_ms", C.c_double),
                 ("scan_ms", C.c_double), ("merge_ms", C.c_double), ("batches", C.c_uint64),
@@ -172,6 +185,32 @@ SIGNATURES = {
                    _P(DLManagedTensor), _P(DLManagedTensor)],
     "cuvsIvfPqTransform": [C.c_size_t, _P(IndexStruct), _P(DLManagedTensor), _P(DLManagedTensor),
                            _P(DLManagedTensor)],
+    "cuvsMultiGpuResourcesCreate": [_P(C.c_size_t)],
+    "cuvsMultiGpuResourcesCreateWithDeviceIds": [_P(C.c_size_t), _P(DLManagedTensor)],
+    "cuvsMultiGpuResourcesDestroy": [C.c_size_t],
+    "cuvsMultiGpuResourcesSetMemoryPool": [C.c_size_t, C.c_int],
+    "cuvsMultiGpuIvfPqIndexParamsCreate": [_P(_P(MgIndexParamsStruct))],
+    "cuvsMultiGpuIvfPqIndexParamsDestroy": [_P(MgIndexParamsStruct)],
+    "cuvsMultiGpuIvfPqSearchParamsCreate": [_P(_P(MgSearchParamsStruct))],
+    "cuvsMultiGpuIvfPqSearchParamsDestroy": [_P(MgSearchParamsStruct)],
+    "cuvsMultiGpuIvfPqIndexCreate": [_P(_P(IndexStruct))],
+    "cuvsMultiGpuIvfPqIndexDestroy": [_P(IndexStruct)],
+    "cuvsMultiGpuIvfPqBuild": [C.c_size_t, _P(MgIndexParamsStruct), _P(DLManagedTensor), _P(IndexStruct)],
+    "cuvsMultiGpuIvfPqSearch": [C.c_size_t, _P(MgSearchParamsStruct), _P(IndexStruct), _P(DLManagedTensor),
+                                _P(DLManagedTensor), _P(DLManagedTensor)],
+    "cuvsMultiGpuIvfPqExtend": [C.c_size_t, _P(IndexStruct), _P(DLManagedTensor), _P(DLManagedTensor)],
+    "cuvsMultiGpuIvfPqSerialize": [C.c_size_t, _P(IndexStruct), C.c_char_p],
+    "cuvsMultiGpuIvfPqDeserialize": [C.c_size_t, C.c_char_p, _P(IndexStruct)],
+    "cuvsMultiGpuIvfPqDistribute": [C.c_size_t, C.c_char_p, _P(IndexStruct)],
+    "cuvsMultiGpuIvfPqDistributeByList": [C.c_size_t, C.c_char_p, _P(IndexStruct)],
+    "cuvsMultiGpuCommIdCreate": [_P(CommId)],
+    "cuvsMultiGpuRankCommCreate": [C.c_size_t, _P(CommId), C.c_int, C.c_int, _P(C.c_void_p)],
+    "cuvsMultiGpuRankCommAdopt": [C.c_void_p, C.c_int, C.c_int, _P(C.c_void_p)],
+    "cuvsMultiGpuRankCommDestroy": [C.c_void_p],
+    "cuvsMultiGpuIvfPqSearchRank": [C.c_size_t, C.c_void_p, _P(SearchParamsStruct), _P(IndexStruct),
+                                    _P(DLManagedTensor), _P(DLManagedTensor), _P(DLManagedTensor)],
+    "cuvsMultiGpuRankCommStats": [C.c_void_p, _P(C.c_double), _P(C.c_uint64), C.c_bool],
+    "cuvsMultiGpuIvfPqListOwners": [_P(C.c_uint32), C.c_uint32, C.c_int, _P(C.c_int32)],
 }
 
 _lib = None

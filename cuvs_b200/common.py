@@ -13,7 +13,8 @@ _TORCH_DL = {torch.float32: (L.kDLFloat, 32), torch.float16: (L.kDLFloat, 16),
              torch.uint32: (L.kDLUInt, 32), torch.int32: (L.kDLInt, 32)}
 _NP_DL = {np.dtype(np.float32): (L.kDLFloat, 32), np.dtype(np.float16): (L.kDLFloat, 16),
           np.dtype(np.int8): (L.kDLInt, 8), np.dtype(np.uint8): (L.kDLUInt, 8),
-          np.dtype(np.int64): (L.kDLInt, 64), np.dtype(np.uint32): (L.kDLUInt, 32)}
+          np.dtype(np.int64): (L.kDLInt, 64), np.dtype(np.uint32): (L.kDLUInt, 32),
+          np.dtype(np.int32): (L.kDLInt, 32)}
 
 
 class Resources:

@@ -102,6 +102,7 @@ class ws_layout {
 // The opaque object behind cuvsResources_t (raft::resources in the reference): device, stream,
 // workspace.  One per host thread, like the reference handle.
 struct resources {
+  int kind              = 0;        // 0 = one device; 1 = the multi-GPU clique handle (mg.hpp)
   int device            = 0;
   cudaStream_t stream   = nullptr;  // caller-set; default stream otherwise
   int sm_count          = 0;

@@ -15,6 +15,7 @@
 #include <algorithm>
 #include <cstring>
 #include <fstream>
+#include <queue>
 #include <mutex>
 #include <cmath>
 #include <numeric>
@@ -445,6 +446,95 @@ void serialize(raft::resources& res, std::ostream& os, const index<int64_t>& idx
   CUVS_EXPECTS(os.good(), "Error writing the index");
 }
 
+std::vector<int> list_owners(const std::vector<uint32_t>& list_sizes, int shard_count)
+{
+  CUVS_EXPECTS(shard_count >= 1, "invalid number of shards %d", shard_count);
+  const size_t n = list_sizes.size();
+  std::vector<int> owner(n, 0);
+  if (shard_count == 1) { return owner; }
+  std::vector<uint32_t> order(n);
+  for (size_t i = 0; i < n; i++) { order[i] = uint32_t(i); }
+  std::stable_sort(order.begin(), order.end(),
+                   [&](uint32_t a, uint32_t b) { return list_sizes[a] > list_sizes[b]; });
+  // (rows held, rank) min-heap
+  using slot = std::pair<uint64_t, int>;
+  std::priority_queue<slot, std::vector<slot>, std::greater<slot>> load;
+  for (int r = 0; r < shard_count; r++) { load.push({0, r}); }
+  for (uint32_t l : order) {
+    slot s = load.top();
+    load.pop();
+    owner[l] = s.second;
+    // an empty list still counts as one unit so that empty lists spread evenly too
+    s.first += std::max<uint32_t>(list_sizes[l], 1u);
+    load.push(s);
+  }
+  return owner;
+}
+
+void serialize_list_sharded(const std::vector<raft::resources*>& res, std::ostream& os,
+                            const std::vector<const index<int64_t>*>& shards)
+{
+  CUVS_EXPECTS(!shards.empty() && shards.size() == res.size(), "serialize_list_sharded: no shards");
+  const index<int64_t>& m = *shards[0];
+  const uint32_t n_lists  = m.n_lists();
+  std::vector<uint32_t> sizes(n_lists, 0);
+  std::vector<int> holder(n_lists, 0);
+  int64_t total = 0;
+  for (size_t r = 0; r < shards.size(); r++) {
+    CUVS_EXPECTS(shards[r]->n_lists() == n_lists, "serialize_list_sharded: shards of different indexes");
+    const auto& hs = shards[r]->host_list_sizes();
+    for (uint32_t l = 0; l < n_lists; l++) {
+      if (hs[l] > 0) {
+        CUVS_EXPECTS(sizes[l] == 0, "serialize_list_sharded: list %u is held by two shards", l);
+        sizes[l]  = hs[l];
+        holder[l] = int(r);
+        total += hs[l];
+      }
+    }
+  }
+  int saved = 0;
+  CUDA_TRY(cudaGetDevice(&saved));
+  CUDA_TRY(cudaSetDevice(res[0]->device));
+  write_scalar<int32_t>(os, 4);
+  write_scalar<int64_t>(os, total);
+  write_scalar<uint32_t>(os, m.dim());
+  write_scalar<uint32_t>(os, m.pq_bits());
+  write_scalar<uint32_t>(os, m.pq_dim());
+  write_scalar<bool>(os, m.conservative_memory_allocation());
+  write_scalar<int32_t>(os, int32_t(m.metric()));
+  write_scalar<int32_t>(os, int32_t(m.codebook_kind()));
+  write_scalar<int32_t>(os, int32_t(list_layout::INTERLEAVED));
+  write_scalar<uint32_t>(os, n_lists);
+  const uint64_t first = m.codebook_kind() == codebook_gen::PER_SUBSPACE ? m.pq_dim() : n_lists;
+  write_device_f32(*res[0], os, m.pq_centers(), {first, m.pq_len(), m.pq_book_size()});
+  write_device_f32(*res[0], os, m.centers(), {n_lists, m.dim_ext()});
+  write_device_f32(*res[0], os, m.centers_rot(), {n_lists, m.rot_dim()});
+  write_device_f32(*res[0], os, m.rotation_matrix(), {m.rot_dim(), m.dim()});
+  write_header(os, "<u4", {n_lists});
+  os.write(reinterpret_cast<const char*>(sizes.data()), std::streamsize(size_t(n_lists) * 4));
+  const uint64_t row_bytes = uint64_t(m.n_pieces()) * kIndexGroupVecLen;
+  std::vector<uint8_t> hcodes;
+  std::vector<int64_t> hids;
+  for (uint32_t l = 0; l < n_lists; l++) {
+    write_scalar<uint32_t>(os, sizes[l]);
+    if (sizes[l] == 0) { continue; }
+    const index<int64_t>& s = *shards[holder[l]];
+    const uint64_t r0       = s.host_row_offsets()[l];
+    const uint64_t rows     = round_up<uint64_t>(sizes[l], kIndexGroupSize);
+    hcodes.resize(rows * row_bytes);
+    hids.resize(sizes[l]);
+    CUDA_TRY(cudaSetDevice(res[holder[l]]->device));
+    CUDA_TRY(cudaMemcpy(hcodes.data(), s.codes() + r0 * row_bytes, rows * row_bytes, cudaMemcpyDeviceToHost));
+    CUDA_TRY(cudaMemcpy(hids.data(), s.ids() + r0, size_t(sizes[l]) * 8, cudaMemcpyDeviceToHost));
+    write_header(os, "|u1", {rows / kIndexGroupSize, m.n_pieces(), kIndexGroupSize, kIndexGroupVecLen});
+    os.write(reinterpret_cast<const char*>(hcodes.data()), std::streamsize(rows * row_bytes));
+    write_header(os, "<i8", {sizes[l]});
+    os.write(reinterpret_cast<const char*>(hids.data()), std::streamsize(uint64_t(sizes[l]) * 8));
+  }
+  CUDA_TRY(cudaSetDevice(saved));
+  CUVS_EXPECTS(os.good(), "Error writing the index");
+}
+
 void serialize(raft::resources& res, const std::string& filename, const index<int64_t>& idx)
 {
   std::ofstream of(filename, std::ios::out | std::ios::binary);
@@ -502,8 +592,9 @@ void deserialize(raft::resources& res, std::istream& is, index<int64_t>* out, in
                (unsigned long long)total, (long long)n_rows);
   std::vector<uint32_t> kept(sizes);
   if (shard_count > 1) {
+    const std::vector<int> owner = list_owners(sizes, shard_count);
     for (uint32_t l = 0; l < n_lists; l++) {
-      if (shard_of_list(l, shard_count) != shard_rank) { kept[l] = 0; }
+      if (owner[l] != shard_rank) { kept[l] = 0; }
     }
   }
   idx.allocate_lists(kept, res.stream);
@@ -629,17 +720,22 @@ void deserialize_mg_rank(raft::resources& res, const std::string& filename, int 
   *id_offset = m == 1 ? offset : 0;  // SHARDED: ids are local to a rank's rows (snmg.cuh:351-355)
 }
 
+void serialize_mg_header(std::ostream& os, const char* dtype_string, int mode, int n_ranks)
+{
+  char d[4] = {0, 0, 0, 0};
+  std::strncpy(d, dtype_string, 4);
+  os.write(d, 4);
+  write_scalar<int32_t>(os, mode);
+  write_scalar<int32_t>(os, n_ranks);
+}
+
 void serialize_mg(raft::resources& res, const std::string& filename, int mode, const char* dtype_string,
                   const std::vector<const index<int64_t>*>& per_rank)
 {
   CUVS_EXPECTS(mode == 0 || mode == 1, "invalid distribution mode %d", mode);
   std::ofstream of(filename, std::ios::out | std::ios::binary);
   CUVS_EXPECTS(bool(of), "Cannot open file %s", filename.c_str());
-  char d[4] = {0, 0, 0, 0};
-  std::strncpy(d, dtype_string, 4);
-  of.write(d, 4);
-  write_scalar<int32_t>(of, mode);
-  write_scalar<int32_t>(of, int32_t(per_rank.size()));
+  serialize_mg_header(of, dtype_string, mode, int(per_rank.size()));
   for (auto* ix : per_rank) { serialize(res, of, *ix); }
   of.close();
   CUVS_EXPECTS(bool(of), "Error writing output %s", filename.c_str());

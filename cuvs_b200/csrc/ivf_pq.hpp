@@ -267,7 +267,8 @@ void search_any(raft::resources& res, const search_params& params, const index<i
 // Probe selection alone, asynchronous on the handle's stream: probes [n_queries, n_probes] u32,
 // ascending by (score, list id).
 void select_probes_any(raft::resources& res, const index<int64_t>& idx, const void* queries,
-                       elem_t qtype, uint32_t n_queries, uint32_t n_probes, uint32_t* probes);
+                       elem_t qtype, uint32_t n_queries, uint32_t n_probes, uint32_t* probes,
+                       cudaDataType_t coarse_search_dtype = CUDA_R_32F);
 void build_any(raft::resources& res, const index_params& params, const void* dataset,
                elem_t dtype, int64_t n_rows, uint32_t dim, bool on_device, index<int64_t>* idx);
 void extend_any(raft::resources& res, const void* new_vectors, elem_t dtype, int64_t n_rows,
@@ -338,9 +339,18 @@ void deserialize_mg_rank(raft::resources& res, const std::string& filename, int 
                          index<int64_t>* idx, int* mode, int64_t* id_offset);
 void serialize_mg(raft::resources& res, const std::string& filename, int mode, const char* dtype_string,
                   const std::vector<const index<int64_t>*>& per_rank);
+// the head of such a file: four bytes of dtype string, mode and number of ranks as scalar records
+void serialize_mg_header(std::ostream& os, const char* dtype_string, int mode, int n_ranks);
 
-// Which rank of a list-sharded deployment holds list `label`.
-inline int shard_of_list(uint32_t label, int shard_count) { return int(label % uint32_t(shard_count)); }
+// Which rank of a list-sharded deployment holds each list: lists are dealt in order of descending
+// size (ties by list id), each to the rank holding the fewest rows so far (ties to the lowest rank),
+// so that the ranks hold about the same number of rows however skewed the list sizes are.  A pure
+// function of the sizes: every rank computes the same map from the header of the index file.
+std::vector<int> list_owners(const std::vector<uint32_t>& list_sizes, int shard_count);
+// One index stream (format version 4) out of the shards of a list-sharded index: model arrays from
+// shard 0, every list from the shard that holds it.  res[r] / shards[r] live on rank r's device.
+void serialize_list_sharded(const std::vector<raft::resources*>& res, std::ostream& os,
+                            const std::vector<const index<int64_t>*>& shards);
 
 namespace helpers {
 // Bit-packed codes u8 [n_rows, ceil(pq_dim*pq_bits/8)] of rows [offset, offset+n_rows) of one list

@@ -148,9 +148,9 @@ __global__ void prep_queries_kernel(const T* __restrict__ queries, uint32_t dim,
 // One warp per query: chunk_index[q, p] = sum_{p' <= p} list_sizes[probes[q, p']]; list_count[l]++
 // for every probe of a non-empty list.
 __global__ void chunk_and_count_kernel(const uint32_t* __restrict__ probes,
-                                       const uint32_t* __restrict__ list_sizes, uint32_t n_queries,
-                                       uint32_t n_probes, uint32_t* __restrict__ chunk_index,
-                                       uint32_t* __restrict__ list_count)
+                                       const uint32_t* __restrict__ list_sizes, uint32_t n_lists,
+                                       uint32_t n_queries, uint32_t n_probes,
+                                       uint32_t* __restrict__ chunk_index, uint32_t* __restrict__ list_count)
 {
   const uint32_t q    = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const uint32_t lane = threadIdx.x & 31;
@@ -161,7 +161,7 @@ __global__ void chunk_and_count_kernel(const uint32_t* __restrict__ probes,
     uint32_t v       = 0;
     if (p < n_probes) {
       const uint32_t label = probes[size_t(q) * n_probes + p];
-      v                    = list_sizes[label];
+      v                    = label < n_lists ? list_sizes[label] : 0u;  // a list id out of range (caller-given probes) scans nothing
       if (v > 0) { atomicAdd(list_count + label, 1u); }  // empty lists never reach the work list
     }
 #pragma unroll
@@ -271,7 +271,7 @@ __global__ void scan_stats_kernel(const uint32_t* __restrict__ list_count,
 // {pair id, query, list, list size, sample offset, first row of the list (lo, hi), 0}.
 __global__ void scatter_pairs_kernel(const uint32_t* __restrict__ probes,
                                      const uint32_t* __restrict__ chunk_index,
-                                     const uint32_t* __restrict__ list_sizes,
+                                     const uint32_t* __restrict__ list_sizes, uint32_t n_lists,
                                      const uint64_t* __restrict__ row_off, uint32_t n_pairs,
                                      uint32_t n_probes, uint32_t* __restrict__ cursor,
                                      uint4* __restrict__ work, uint64_t* __restrict__ out_keys, uint32_t k,
@@ -281,7 +281,7 @@ __global__ void scatter_pairs_kernel(const uint32_t* __restrict__ probes,
   if (i >= n_pairs) { return; }
   if (i < n_queries) { query_kth[i] = kEmptyScore; }  // no bound on any query's k-th best yet
   const uint32_t label = probes[i];
-  if (list_sizes[label] == 0) {
+  if (label >= n_lists || list_sizes[label] == 0) {
     // nothing to scan (e.g. a list owned by another GPU): the pair's result slots are empty
     if (out_keys) {
       for (uint32_t t = 0; t < k; t++) { out_keys[size_t(i) * k + t] = kEmptyKey; }
@@ -300,7 +300,7 @@ __global__ void scatter_pairs_kernel(const uint32_t* __restrict__ probes,
 // slots and the per-query bounds in one launch.  One warp per query; `n_work` counts the non-empty
 // pairs and must be zero on entry.
 __global__ void small_batch_pairs_kernel(const uint32_t* __restrict__ probes,
-                                         const uint32_t* __restrict__ list_sizes,
+                                         const uint32_t* __restrict__ list_sizes, uint32_t n_lists,
                                          const uint64_t* __restrict__ row_off, uint32_t n_queries,
                                          uint32_t n_probes, uint32_t* __restrict__ chunk_index,
                                          uint4* __restrict__ work, uint32_t* __restrict__ n_work,
@@ -316,7 +316,7 @@ __global__ void small_batch_pairs_kernel(const uint32_t* __restrict__ probes,
     uint32_t label = 0, size = 0;
     if (p < n_probes) {
       label = probes[size_t(q) * n_probes + p];
-      size  = list_sizes[label];
+      size  = label < n_lists ? list_sizes[label] : 0u;
     }
     uint32_t v = size;
 #pragma unroll
@@ -774,7 +774,7 @@ void search_any(raft::resources& res, const search_params& params, const index<i
       // small batch: one launch, pairs in arrival order (a sort by list has nothing to gain here)
       CUDA_TRY(cudaMemsetAsync(d_counter, 0, 8, stream));
       small_batch_pairs_kernel<<<ceildiv<uint32_t>(nq * 32, 128), 128, 0, stream>>>(
-        d_probes, idx.list_sizes(), idx.row_offsets(), nq, n_probes, d_chunk, d_order, d_counter + 1, d_kth,
+        d_probes, idx.list_sizes(), n_lists, idx.row_offsets(), nq, n_probes, d_chunk, d_order, d_counter + 1, d_kth,
         store_all ? nullptr : d_keys, k);
       CUDA_TRY(cudaGetLastError());
       res.launches += 1;
@@ -782,7 +782,7 @@ void search_any(raft::resources& res, const search_params& params, const index<i
       // counting sort of the pairs by list
       CUDA_TRY(cudaMemsetAsync(d_count, 0, (size_t(n_lists) + 1) * 4, stream));
       chunk_and_count_kernel<<<ceildiv<uint32_t>(nq * 32, 256), 256, 0, stream>>>(
-        d_probes, idx.list_sizes(), nq, n_probes, d_chunk, d_count);
+        d_probes, idx.list_sizes(), n_lists, nq, n_probes, d_chunk, d_count);
       if (stats) {
         scan_stats_kernel<<<ceildiv<uint32_t>(n_lists, 256), 256, 0, stream>>>(d_count, idx.list_sizes(),
                                                                                 n_lists, res.d_stats);
@@ -791,7 +791,7 @@ void search_any(raft::resources& res, const search_params& params, const index<i
       // d_counter[0] = 0 (work counter), d_counter[1] = d_count[n_lists] = number of work items
       exclusive_scan_kernel<<<1, 1024, 0, stream>>>(d_count, n_lists, d_counter);
       scatter_pairs_kernel<<<ceildiv<uint32_t>(n_pairs, 256), 256, 0, stream>>>(
-        d_probes, d_chunk, idx.list_sizes(), idx.row_offsets(), n_pairs, n_probes, d_count, d_order,
+        d_probes, d_chunk, idx.list_sizes(), n_lists, idx.row_offsets(), n_pairs, n_probes, d_count, d_order,
         store_all ? nullptr : d_keys, k, d_kth, nq);
       CUDA_TRY(cudaGetLastError());
       res.launches += 3;
@@ -902,36 +902,54 @@ void set_coarse_mode(int mode)
 void set_scan_codebook_home(int home) { scan_codebook_home() = home; }
 
 void select_probes_any(raft::resources& res, const index<int64_t>& idx, const void* queries,
-                       elem_t qtype, uint32_t n_queries, uint32_t n_probes, uint32_t* probes)
+                       elem_t qtype, uint32_t n_queries, uint32_t n_probes, uint32_t* probes,
+                       cudaDataType_t coarse_search_dtype)
 {
   if (n_queries == 0) { return; }
   const uint32_t n_lists = idx.n_lists();
   CUVS_EXPECTS(n_probes > 0 && n_probes <= n_lists, "n_probes must be within [1, n_lists]");
+  CUVS_EXPECTS(coarse_search_dtype == CUDA_R_32F || coarse_search_dtype == CUDA_R_8I,
+               "Unsupported coarse_search_dtype (only CUDA_R_32F and CUDA_R_8I are supported by this engine)");
+  const bool coarse_i8 = coarse_search_dtype == CUDA_R_8I;
+  CUVS_EXPECTS(!coarse_i8 || idx.dim_ext_int8() <= 1024,
+               "coarse_search_dtype CUDA_R_8I: dim = %u is too large for this engine (at most 1022)", idx.dim());
   const DistanceType metric = idx.metric();
   const bool is_l2  = metric == DistanceType::L2Expanded || metric == DistanceType::L2SqrtExpanded;
-  const bool use_tc = coarse_mode() != 1 && coarse_tc_usable(n_lists, n_probes, idx.dim_ext());
+  const uint32_t cdim_ext = coarse_i8 ? idx.dim_ext_int8() : idx.dim_ext();
+  index<int64_t>::int8_operands op8{};
+  if (coarse_i8) { op8 = idx.int8_coarse_operands(res.stream); }
+  const bool use_tc = coarse_mode() != 1 && coarse_tc_usable(n_lists, n_probes, cdim_ext);
   const uint32_t batch = std::min<uint32_t>(n_queries, 16384);
   ws_layout lay;
-  const size_t o_fq = lay.add(size_t(batch) * idx.dim_ext() * 4);
+  const size_t o_fq = lay.add(size_t(batch) * cdim_ext * 4);
   const size_t o_rq = lay.add(size_t(batch) * idx.rot_dim() * 4);
-  const size_t cws  = use_tc ? coarse_tc_workspace_bytes(batch, n_lists, idx.dim_ext())
+  const size_t cws  = use_tc ? coarse_tc_workspace_bytes(batch, n_lists, cdim_ext)
                              : coarse_workspace_bytes(batch, n_lists, n_probes);
   const size_t o_c  = lay.add(cws);
   res.ws.reserve(lay.total());
   char* ws   = res.ws.base();
   auto* d_fq = reinterpret_cast<float*>(ws + o_fq);
   auto* d_rq = reinterpret_cast<float*>(ws + o_rq);
+  const float alpha = is_l2 ? -2.0f : -1.0f;
   for (uint32_t q0 = 0; q0 < n_queries; q0 += batch) {
     const uint32_t nq = std::min(batch, n_queries - q0);
     const char* qptr  = static_cast<const char*>(queries) + size_t(q0) * idx.dim() * elem_size(qtype);
-    launch_prep(res, idx, qptr, qtype, nq, d_fq, d_rq);
-    if (use_tc) {
+    uint32_t* out     = probes + size_t(q0) * n_probes;
+    launch_prep(res, idx, qptr, qtype, nq, d_fq, d_rq, coarse_i8 ? op8.rotation : nullptr);
+    if (coarse_i8) {
+      if (use_tc) {
+        select_clusters_tc(res, op8.centers, op8.centers, op8.centers, op8.centers_max_norm, n_lists, cdim_ext,
+                           alpha, d_fq, nq, n_probes, out, nullptr, ws + o_c, cws, /*exact_operands=*/true);
+      } else {
+        select_clusters(res, op8.centers, n_lists, cdim_ext, alpha, d_fq, nq, n_probes, out, nullptr,
+                        ws + o_c, cws);
+      }
+    } else if (use_tc) {
       select_clusters_tc(res, idx.centers(), idx.centers_hi(), idx.centers_lo(), idx.centers_max_norm(),
-                         n_lists, idx.dim_ext(), is_l2 ? -2.0f : -1.0f, d_fq, nq, n_probes,
-                         probes + size_t(q0) * n_probes, nullptr, ws + o_c, cws);
+                         n_lists, idx.dim_ext(), alpha, d_fq, nq, n_probes, out, nullptr, ws + o_c, cws);
     } else {
-      select_clusters(res, idx.centers(), n_lists, idx.dim_ext(), is_l2 ? -2.0f : -1.0f, d_fq, nq,
-                      n_probes, probes + size_t(q0) * n_probes, nullptr, ws + o_c, cws);
+      select_clusters(res, idx.centers(), n_lists, idx.dim_ext(), alpha, d_fq, nq, n_probes, out, nullptr,
+                      ws + o_c, cws);
     }
   }
 }
@@ -973,15 +991,80 @@ void coarse_only(raft::resources& res, const index<int64_t>& idx, const void* qu
   }
 }
 
+namespace {
+// Large-k merge, step 1: part-major results -> one row of n_parts * k scores per query, smallest
+// wanted first (inner-product results negated), absent results (id INT64_MAX) at +inf.
+__global__ void merge_rows_kernel(const float* __restrict__ in_dist, const int64_t* __restrict__ in_ids,
+                                  size_t stride_d, size_t stride_i, uint32_t n_parts, uint32_t n_queries,
+                                  uint32_t k, int select_min, float* __restrict__ rows)
+{
+  const uint64_t i = blockIdx.x * uint64_t(blockDim.x) + threadIdx.x;
+  const uint64_t n = uint64_t(n_queries) * n_parts * k;
+  if (i >= n) { return; }
+  const uint32_t q    = uint32_t(i / (uint64_t(n_parts) * k));
+  const uint32_t t    = uint32_t(i - uint64_t(q) * n_parts * k);
+  const uint32_t part = t / k, pos = t - part * k;
+  const size_t src    = size_t(q) * k + pos;
+  const int64_t id    = in_ids[part * stride_i + src];
+  const float d       = in_dist[part * stride_d + src];
+  rows[i]             = id == kOutOfBoundsRecord ? INFINITY : (select_min ? d : -d);
+}
+// step 3: selected positions -> ids and distances
+__global__ void merge_take_kernel(const float* __restrict__ in_dist, const int64_t* __restrict__ in_ids,
+                                  size_t stride_d, size_t stride_i, uint32_t n_queries, uint32_t k,
+                                  int select_min, const uint32_t* __restrict__ sel_idx,
+                                  const float* __restrict__ sel_scores, float* __restrict__ out_dist,
+                                  int64_t* __restrict__ out_ids)
+{
+  const uint64_t i = blockIdx.x * uint64_t(blockDim.x) + threadIdx.x;
+  if (i >= uint64_t(n_queries) * k) { return; }
+  const uint32_t q = uint32_t(i / k);
+  int64_t id       = kOutOfBoundsRecord;
+  float d          = select_min ? INFINITY : -INFINITY;
+  if (sel_scores[i] < INFINITY) {
+    const uint32_t t    = sel_idx[i];
+    const uint32_t part = t / k, pos = t - part * k;
+    const size_t src    = size_t(q) * k + pos;
+    id                  = in_ids[part * stride_i + src];
+    d                   = in_dist[part * stride_d + src];
+  }
+  out_ids[i]  = id;
+  out_dist[i] = d;
+}
+}  // namespace
+
 namespace detail {
 void knn_merge_parts(raft::resources& res, const float* in_dist, const int64_t* in_ids,
                      float* out_dist, int64_t* out_ids, uint32_t n_parts, uint32_t n_queries,
                      uint32_t k, bool select_min, size_t part_stride_dist, size_t part_stride_ids)
 {
-  CUVS_EXPECTS(k > 0 && k <= 128, "knn_merge_parts supports 0 < k <= 128, got %u", k);
+  CUVS_EXPECTS(k > 0 && k <= 4096, "knn_merge_parts supports 0 < k <= 4096, got %u", k);
   if (n_queries == 0) { return; }
   const size_t sd = part_stride_dist ? part_stride_dist : size_t(n_queries) * k;
   const size_t si = part_stride_ids ? part_stride_ids : size_t(n_queries) * k;
+  if (k > 128) {
+    // beyond the register top-k: the row selection of the store-all search path over the n_parts * k
+    // candidates of a query (the reference's warp-sort merge stops at 1024,
+    // cpp/src/neighbors/detail/knn_merge_parts.cuh:133-170)
+    const uint32_t row_len = n_parts * k;
+    ws_layout lay;
+    const size_t o_rows = lay.add(size_t(n_queries) * row_len * 4);
+    const size_t o_idx  = lay.add(size_t(n_queries) * k * 4);
+    const size_t o_sc   = lay.add(size_t(n_queries) * k * 4);
+    res.ws.reserve(lay.total());
+    auto* rows = reinterpret_cast<float*>(res.ws.base() + o_rows);
+    auto* idx  = reinterpret_cast<uint32_t*>(res.ws.base() + o_idx);
+    auto* sc   = reinterpret_cast<float*>(res.ws.base() + o_sc);
+    const uint64_t n = uint64_t(n_queries) * row_len;
+    merge_rows_kernel<<<unsigned(ceildiv<uint64_t>(n, 256)), 256, 0, res.stream>>>(
+      in_dist, in_ids, sd, si, n_parts, n_queries, k, select_min, rows);
+    select_rows(res, rows, n_queries, row_len, k, idx, sc);
+    merge_take_kernel<<<unsigned(ceildiv<uint64_t>(uint64_t(n_queries) * k, 256)), 256, 0, res.stream>>>(
+      in_dist, in_ids, sd, si, n_queries, k, select_min, idx, sc, out_dist, out_ids);
+    CUDA_TRY(cudaGetLastError());
+    res.launches += 2;
+    return;
+  }
   const int blocks = int(ceildiv<uint32_t>(n_queries * 32, 128));
   const int kpl    = kpl_for_k(k);
   switch (kpl) {

@@ -1,14 +1,17 @@
-"""List-sharded multi-GPU IVF-PQ search, one process per GPU over ``torch.distributed``.
+"""List-sharded multi-GPU IVF-PQ search, one process per GPU.
 
-Every rank holds the global coarse model and the inverted lists it owns (list ``l`` belongs to rank
-``l % n_ranks``).  A search runs the ordinary single-GPU search on every rank for the whole query
-batch -- the probes chosen are identical on every rank, a rank scans only the ones it owns -- then
-all-gathers the per-rank top-k (``n_queries * k * 12`` bytes per rank, ids already global) and
-merges them on the GPU.  The merged result equals the single-GPU search on the unsharded index.
+Every rank holds the global coarse model and the inverted lists it owns (lists are dealt in order of
+descending size, each to the rank holding the fewest rows so far: ``list_owners``).  ``search`` is ONE
+call into the C++ host side (``cuvsMultiGpuIvfPqSearchRank``), which enqueues the whole step on the
+handle's stream: probes of this rank's slice of the batch -> NCCL all-gather -> scan of the owned lists
+for the whole batch -> all-gather of the per-rank top-k blocks (ids already global) -> merge.  The
+merged result equals the single-GPU search on the unsharded index.  ``torch.distributed`` is used only
+to hand the NCCL id to the other ranks when the communicator is made.
 
 Reference behaviour this replaces: sharded search with merge in
 cpp/src/neighbors/mg/snmg.cuh:249-561 (one process, one OpenMP thread per GPU, ncclSend/ncclRecv to
-the root, knn_merge_parts); index distribution in snmg.cuh:48-58.
+the root, knn_merge_parts); index distribution in snmg.cuh:48-58.  The single-process interface of the
+reference (``cuvsMultiGpuIvfPqSearch`` and friends) is mirrored by ``cuvs_b200.mg_ivf_pq``.
 """
 from __future__ import annotations
 
@@ -22,9 +25,72 @@ from . import ivf_pq
 from .common import DLTensorRef, Resources, default_resources
 
 
-def shard_of_list(label: int, n_ranks: int) -> int:
-    """Owner rank of an inverted list (same rule as the C++ loader)."""
-    return int(label) % int(n_ranks)
+def list_owners(list_sizes, n_ranks: int):
+    """Owner rank of every inverted list (the rule of the C++ shard loader), as a list of ints."""
+    import numpy as np
+    sizes = np.ascontiguousarray(np.asarray(list_sizes), dtype=np.uint32)
+    owners = np.zeros(sizes.shape[0], dtype=np.int32)
+    L.check(L.load().cuvsMultiGpuIvfPqListOwners(sizes.ctypes.data_as(C.POINTER(C.c_uint32)),
+                                                 C.c_uint32(sizes.shape[0]), C.c_int(n_ranks),
+                                                 owners.ctypes.data_as(C.POINTER(C.c_int32))))
+    return owners.tolist()
+
+
+class RankComm:
+    """This rank's end of the exchanges of the list-sharded search: an NCCL communicator of its own
+    (made from an id that rank 0 creates and the process group hands round) plus the exchange buffers
+    the C++ side sizes once and keeps."""
+
+    def __init__(self, group=None, resources: Resources | None = None):
+        self._lib = L.load()
+        self.rank, self.n_ranks = _rank_world(group)
+        res = resources or default_resources()
+        cid = L.CommId()
+        if self.n_ranks > 1:
+            box = [None]
+            if self.rank == 0:
+                L.check(self._lib.cuvsMultiGpuCommIdCreate(C.byref(cid)))
+                box[0] = bytes(cid.bytes)
+            dist.broadcast_object_list(box, src=dist.get_global_rank(group, 0) if group is not None else 0,
+                                       group=group)
+            C.memmove(C.byref(cid), box[0], 128)
+        self.handle = C.c_void_p()
+        if self.n_ranks > 1:
+            L.check(self._lib.cuvsMultiGpuRankCommCreate(res.handle, C.byref(cid), C.c_int(self.rank),
+                                                         C.c_int(self.n_ranks), C.byref(self.handle)))
+        else:
+            L.check(self._lib.cuvsMultiGpuRankCommAdopt(None, 0, 1, C.byref(self.handle)))
+
+    def stats(self, reset: bool = True):
+        """Per-call stage times in ms of the searches made while the handle's stage timing was on:
+        dict(select, gather_probes, scan, gather_results, merge, batches)."""
+        ms = (C.c_double * 5)()
+        n = C.c_uint64(0)
+        L.check(self._lib.cuvsMultiGpuRankCommStats(self.handle, ms, C.byref(n), C.c_bool(reset)))
+        b = max(1, n.value)
+        names = ("select_ms", "gather_probes_ms", "scan_ms", "gather_results_ms", "merge_ms")
+        out = {k: ms[i] / b for i, k in enumerate(names)}
+        out["batches"] = n.value
+        return out
+
+    def __del__(self):
+        try:
+            if getattr(self, "handle", None):
+                self._lib.cuvsMultiGpuRankCommDestroy(self.handle)
+                self.handle = None
+        except Exception:
+            pass
+
+
+_default_comm = {}
+
+
+def default_comm(group=None) -> RankComm:
+    key = (torch.cuda.current_device(), id(group))
+    c = _default_comm.get(key)
+    if c is None:
+        c = _default_comm[key] = RankComm(group)
+    return c
 
 
 def _rank_world(group=None):
@@ -89,8 +155,8 @@ def translate_ids(neighbors: torch.Tensor, id_offset: int) -> torch.Tensor:
 
 
 def search_reference_mg(search_params: ivf_pq.SearchParams, index: ivf_pq.Index, mode: int, id_offset: int,
-                        queries, k: int, select_min: bool = True, group=None,
-                        resources: Resources | None = None, sync: bool = True):
+                        queries, k: int, group=None, resources: Resources | None = None, sync: bool = True,
+                        metric: str = "sqeuclidean"):
     """Search an index loaded with :func:`load_reference_mg`, with the reference's semantics
     (cpp/src/neighbors/mg/snmg.cuh:249-561): SHARDED -- every rank searches its own rows for the whole
     batch, ids are made global, the per-rank lists are merged; REPLICATED -- the batch is split between
@@ -105,7 +171,8 @@ def search_reference_mg(search_params: ivf_pq.SearchParams, index: ivf_pq.Index,
                 res.sync()
             return d, i
         part_d, part_i = gather_parts(d, i, group)
-        return merge_parts(part_d, part_i, select_min, res, sync)
+        # larger is better for inner product, smaller otherwise (snmg.cuh:263: is_min_close(metric))
+        return merge_parts(part_d, part_i, metric != "inner_product", res, sync)
     n = queries.shape[0]
     if w == 1:
         return ivf_pq.search(search_params, index, queries, k, resources=res, sync=sync)
@@ -171,38 +238,6 @@ def select_probes(shard: ivf_pq.Index, queries, n_probes: int, resources: Resour
     return probes
 
 
-def shared_probes(shard: ivf_pq.Index, queries, n_probes: int, group=None,
-                  resources: Resources | None = None):
-    """Probe selection shared between the ranks: rank r selects the probes of the r-th slice of the
-    batch (the global coarse model is replicated, so every rank would choose the same lists), the
-    slices are all-gathered (n_queries * n_probes * 4 bytes in total)."""
-    rank, w = _rank_world(group)
-    n = queries.shape[0]
-    if w == 1:
-        return select_probes(shard, queries, n_probes, resources)
-    s = -(-n // w)
-    lo, hi = min(n, rank * s), min(n, (rank + 1) * s)
-    every = torch.empty((w * s, n_probes), dtype=torch.uint32, device=queries.device)
-    if _in_place_gather(group):
-        # this rank's slice is written where the gather wants it and gathered in place (rows past
-        # n exist only as padding of the last slice and are never read)
-        if hi > lo:
-            select_probes(shard, queries[lo:hi], n_probes, resources, out=every[lo:hi])
-        mine = every[rank * s:(rank + 1) * s]
-    else:
-        mine = torch.zeros((s, n_probes), dtype=torch.uint32, device=queries.device)
-        if hi > lo:
-            mine[: hi - lo] = select_probes(shard, queries[lo:hi], n_probes, resources)
-    # NCCL has no uint32: exchange the same bytes as int32
-    dist.all_gather_into_tensor(every.view(torch.int32), mine.view(torch.int32), group=group)
-    return every[:n]
-
-
-def _in_place_gather(group=None) -> bool:
-    """NCCL gathers in place when a rank's input is its own slot of the output."""
-    return dist.get_backend(group) == "nccl"
-
-
 def search_with_probes(search_params: ivf_pq.SearchParams, shard: ivf_pq.Index, queries, probes,
                        k: int, resources: Resources | None = None, sync: bool = True, out=None):
     """Fine search of this rank's lists for given probes; `out` = optional (distances, neighbors)."""
@@ -223,29 +258,24 @@ def search_with_probes(search_params: ivf_pq.SearchParams, shard: ivf_pq.Index, 
 
 
 def search(search_params: ivf_pq.SearchParams, shard: ivf_pq.Index, queries, k: int,
-           select_min: bool = True, group=None, resources: Resources | None = None,
-           sync: bool = True):
-    """Sharded search: every rank passes the same queries and gets the same merged result.
-    Probe selection is split between the ranks by query slice, the code scan by inverted list."""
+           group=None, resources: Resources | None = None, sync: bool = True, comm: RankComm | None = None,
+           out=None):
+    """Sharded search: every rank passes the same queries (device tensor) and gets the same merged
+    result ``(distances, neighbors)``.  One call into the C++ step (see the module text); whether the
+    smallest or the largest distances win follows from the index metric.  ``out``: optional
+    ``(distances, neighbors)`` to fill."""
     res = resources or default_resources()
-    _, w = _rank_world(group)
-    if w == 1:
-        return ivf_pq.search(search_params, shard, queries, k, resources=res, sync=sync)
-    n_probes = min(search_params.n_probes, shard.n_lists)
-    probes = shared_probes(shard, queries, n_probes, group, res)
+    res.use_current_stream()
+    comm = comm or default_comm(group)
     n = queries.shape[0]
-    nk = n * k
-    if _in_place_gather(group) and nk % 2 == 0 and nk > 0:
-        # one exchange for ids and distances: every rank's block is [n*k int64 ids | n*k f32
-        # distances], written by the search straight into this rank's slot of the gathered buffer
-        rank = dist.get_rank(group)
-        blocks = torch.empty((w, nk * 12), dtype=torch.uint8, device=queries.device)
-        part_i = blocks[:, :nk * 8].view(torch.int64).view(w, n, k)
-        part_d = blocks[:, nk * 8:].view(torch.float32).view(w, n, k)
-        search_with_probes(search_params, shard, queries, probes, k, res, sync=False,
-                           out=(part_d[rank], part_i[rank]))
-        dist.all_gather_into_tensor(blocks, blocks[rank], group=group)
-        return merge_parts(part_d, part_i, select_min, res, sync)
-    d, i = search_with_probes(search_params, shard, queries, probes, k, res, sync=False)
-    part_d, part_i = gather_parts(d, i, group)
-    return merge_parts(part_d, part_i, select_min, res, sync)
+    if out is not None:
+        d, i = out
+    else:
+        d = torch.empty((n, k), dtype=torch.float32, device=queries.device)
+        i = torch.empty((n, k), dtype=torch.int64, device=queries.device)
+    a, b, c = DLTensorRef(queries), DLTensorRef(i), DLTensorRef(d)
+    L.check(L.load().cuvsMultiGpuIvfPqSearchRank(res.handle, comm.handle, search_params._p, shard._h, a.ref(),
+                                                 b.ref(), c.ref()))
+    if sync:
+        res.sync()
+    return d, i

@@ -63,6 +63,18 @@ CUVS_EXPORT cuvsError_t cuvsStreamSync(cuvsResources_t res);
 CUVS_EXPORT cuvsError_t cuvsDeviceIdGet(cuvsResources_t res, int* device_id);
 /* c/include/cuvs/core/c_api.h:175 -- pre-sizes the workspace so that search allocates nothing */
 CUVS_EXPORT cuvsError_t cuvsResourcesSetWorkspacePool(cuvsResources_t res, size_t initial_size_bytes);
+/* c/include/cuvs/core/c_api.h:185 -- the multi-GPU handle (raft::device_resources_snmg in the
+ * reference): the root rank's handle plus one handle, stream and NCCL communicator per visible device.
+ * It is accepted wherever a cuvsResources_t is (it then acts as the root rank's handle). */
+CUVS_EXPORT cuvsError_t cuvsMultiGpuResourcesCreate(cuvsResources_t* res);
+/* c/include/cuvs/core/c_api.h:195 -- device_ids: int32 host tensor [n] */
+CUVS_EXPORT cuvsError_t cuvsMultiGpuResourcesCreateWithDeviceIds(cuvsResources_t* res,
+                                                                 DLManagedTensor* device_ids);
+/* c/include/cuvs/core/c_api.h:204 */
+CUVS_EXPORT cuvsError_t cuvsMultiGpuResourcesDestroy(cuvsResources_t res);
+/* c/include/cuvs/core/c_api.h:213 -- this engine keeps one grow-only workspace per rank instead of a
+ * pool: the call reserves that share of each device's free memory for it */
+CUVS_EXPORT cuvsError_t cuvsMultiGpuResourcesSetMemoryPool(cuvsResources_t res, int percent_of_free_memory);
 /* c/include/cuvs/core/c_api.h:230 -- plain cudaMalloc on the handle's device */
 CUVS_EXPORT cuvsError_t cuvsRMMAlloc(cuvsResources_t res, void** ptr, size_t bytes);
 /* c/include/cuvs/core/c_api.h:240 */

@@ -1,15 +1,21 @@
 /*
- * List-sharded multi-GPU IVF-PQ, one process per GPU.
+ * Multi-GPU IVF-PQ.
  *
- * The reference's multi-GPU layer (c/include/cuvs/neighbors/mg_ivf_pq.h, cpp/src/neighbors/mg/snmg.cuh)
- * drives all GPUs from one process with one OpenMP thread per rank.  Here every rank is its own
- * process holding an ordinary cuvsIvfPqIndex_t that contains the global coarse model and the
- * inverted lists this rank owns (list l belongs to rank l % n_ranks; the others are empty).  Every
- * rank runs the ordinary cuvsIvfPqSearch on the whole query batch -- probe selection is global and
- * identical everywhere, a rank only scans the probes it owns -- and the per-rank top-k lists, which
- * already carry global ids, are exchanged by the host framework (NCCL all-gather) and merged with
- * cuvsMultiGpuIvfPqMergeParts.  The union of the ranks' candidates is exactly the single-GPU
- * candidate set, so the merged result equals the single-GPU search.
+ * Part 1 -- the reference's interface (c/include/cuvs/neighbors/mg_ivf_pq.h, mg_common.h): one process
+ * drives all GPUs of a node through a multi-GPU resources handle (cuvsMultiGpuResourcesCreate); index
+ * parameters carry a distribution mode, search parameters a replicated-search mode, a merge mode and a
+ * batch size; datasets, queries and results are host tensors.  Same names, structs, defaults and checks.
+ * What differs inside: a SHARDED index built here is sharded by inverted list, not by rows -- one
+ * global coarse model on every GPU, every list on exactly one GPU -- so a search probes n_probes lists
+ * in all (not n_probes per GPU) and returns what a single-GPU search of the whole index returns.
+ * Row-sharded and replicated index files written by the reference load and search with the reference's
+ * semantics.
+ *
+ * Part 2 -- one process per GPU (no counterpart in the reference): every rank holds an ordinary
+ * cuvsIvfPqIndex_t with the global coarse model and the lists it owns, joins an NCCL communicator, and
+ * ONE call per batch (cuvsMultiGpuIvfPqSearchRank) enqueues the whole step on the handle's stream:
+ * probes of this rank's slice of the batch -> all-gather -> scan of the owned lists -> all-gather of the
+ * per-rank top-k blocks -> merge.  The building blocks of that step are exported too.
  */
 #ifndef CUVS_B200_MG_IVF_PQ_H_
 #define CUVS_B200_MG_IVF_PQ_H_
@@ -20,10 +26,151 @@
 extern "C" {
 #endif
 
+/* ---------------------------------------------------------------------------------------------
+ * Part 1: the reference's single-process interface
+ * --------------------------------------------------------------------------------------------- */
+
+/* c/include/cuvs/neighbors/mg_common.h:24-29 */
+typedef enum {
+  CUVS_NEIGHBORS_MG_REPLICATED = 0,
+  CUVS_NEIGHBORS_MG_SHARDED    = 1
+} cuvsMultiGpuDistributionMode;
+/* c/include/cuvs/neighbors/mg_common.h:34-39 */
+typedef enum {
+  CUVS_NEIGHBORS_MG_LOAD_BALANCER = 0,
+  CUVS_NEIGHBORS_MG_ROUND_ROBIN   = 1
+} cuvsMultiGpuReplicatedSearchMode;
+/* c/include/cuvs/neighbors/mg_common.h:44-49 -- accepted; both values run this engine's one
+ * all-gather + merge */
+typedef enum {
+  CUVS_NEIGHBORS_MG_MERGE_ON_ROOT_RANK = 0,
+  CUVS_NEIGHBORS_MG_TREE_MERGE         = 1
+} cuvsMultiGpuShardedMergeMode;
+
+/* c/include/cuvs/neighbors/mg_ivf_pq.h:29-34 */
+struct cuvsMultiGpuIvfPqIndexParams {
+  cuvsIvfPqIndexParams_t base_params;
+  cuvsMultiGpuDistributionMode mode;
+};
+typedef struct cuvsMultiGpuIvfPqIndexParams* cuvsMultiGpuIvfPqIndexParams_t;
+/* c/include/cuvs/neighbors/mg_ivf_pq.h:45 (defaults: base defaults, mode SHARDED) */
+CUVS_EXPORT cuvsError_t cuvsMultiGpuIvfPqIndexParamsCreate(cuvsMultiGpuIvfPqIndexParams_t* index_params);
+/* c/include/cuvs/neighbors/mg_ivf_pq.h:53 */
+CUVS_EXPORT cuvsError_t cuvsMultiGpuIvfPqIndexParamsDestroy(cuvsMultiGpuIvfPqIndexParams_t index_params);
+
+/* c/include/cuvs/neighbors/mg_ivf_pq.h:69-78 */
+struct cuvsMultiGpuIvfPqSearchParams {
+  cuvsIvfPqSearchParams_t base_params;
+  cuvsMultiGpuReplicatedSearchMode search_mode;
+  cuvsMultiGpuShardedMergeMode merge_mode;
+  int64_t n_rows_per_batch;
+};
+typedef struct cuvsMultiGpuIvfPqSearchParams* cuvsMultiGpuIvfPqSearchParams_t;
+/* c/include/cuvs/neighbors/mg_ivf_pq.h:88 (defaults: LOAD_BALANCER, TREE_MERGE, 1 << 20 rows per batch) */
+CUVS_EXPORT cuvsError_t cuvsMultiGpuIvfPqSearchParamsCreate(cuvsMultiGpuIvfPqSearchParams_t* params);
+/* c/include/cuvs/neighbors/mg_ivf_pq.h:96 */
+CUVS_EXPORT cuvsError_t cuvsMultiGpuIvfPqSearchParamsDestroy(cuvsMultiGpuIvfPqSearchParams_t params);
+
+/* c/include/cuvs/neighbors/mg_ivf_pq.h:111-116 */
+typedef struct {
+  uintptr_t addr;
+  DLDataType dtype;
+} cuvsMultiGpuIvfPqIndex;
+typedef cuvsMultiGpuIvfPqIndex* cuvsMultiGpuIvfPqIndex_t;
+/* c/include/cuvs/neighbors/mg_ivf_pq.h:124 */
+CUVS_EXPORT cuvsError_t cuvsMultiGpuIvfPqIndexCreate(cuvsMultiGpuIvfPqIndex_t* index);
+/* c/include/cuvs/neighbors/mg_ivf_pq.h:132 */
+CUVS_EXPORT cuvsError_t cuvsMultiGpuIvfPqIndexDestroy(cuvsMultiGpuIvfPqIndex_t index);
+
+/* c/include/cuvs/neighbors/mg_ivf_pq.h:153 -- dataset: host tensor f32/f16/i8/u8 [n_rows, dim].  One
+ * global index is built on the root rank and dealt out: by list (SHARDED) or whole (REPLICATED). */
+CUVS_EXPORT cuvsError_t cuvsMultiGpuIvfPqBuild(cuvsResources_t res,
+                                               cuvsMultiGpuIvfPqIndexParams_t params,
+                                               DLManagedTensor* dataset_tensor,
+                                               cuvsMultiGpuIvfPqIndex_t index);
+/* c/include/cuvs/neighbors/mg_ivf_pq.h:177 -- queries, neighbors (int64), distances (f32): host tensors */
+CUVS_EXPORT cuvsError_t cuvsMultiGpuIvfPqSearch(cuvsResources_t res,
+                                                cuvsMultiGpuIvfPqSearchParams_t params,
+                                                cuvsMultiGpuIvfPqIndex_t index,
+                                                DLManagedTensor* queries_tensor,
+                                                DLManagedTensor* neighbors_tensor,
+                                                DLManagedTensor* distances_tensor);
+/* c/include/cuvs/neighbors/mg_ivf_pq.h:202 -- new_indices_tensor may be NULL */
+CUVS_EXPORT cuvsError_t cuvsMultiGpuIvfPqExtend(cuvsResources_t res,
+                                                cuvsMultiGpuIvfPqIndex_t index,
+                                                DLManagedTensor* new_vectors_tensor,
+                                                DLManagedTensor* new_indices_tensor);
+/* c/include/cuvs/neighbors/mg_ivf_pq.h:224 -- the reference's multi-GPU file format; a list-sharded
+ * index is written as a REPLICATED file (the merged index once per rank) */
+CUVS_EXPORT cuvsError_t cuvsMultiGpuIvfPqSerialize(cuvsResources_t res,
+                                                   cuvsMultiGpuIvfPqIndex_t index,
+                                                   const char* filename);
+/* c/include/cuvs/neighbors/mg_ivf_pq.h:245 -- REPLICATED or row-SHARDED files of the reference */
+CUVS_EXPORT cuvsError_t cuvsMultiGpuIvfPqDeserialize(cuvsResources_t res,
+                                                     const char* filename,
+                                                     cuvsMultiGpuIvfPqIndex_t index);
+/* c/include/cuvs/neighbors/mg_ivf_pq.h:266 -- a single-GPU index file replicated on every GPU */
+CUVS_EXPORT cuvsError_t cuvsMultiGpuIvfPqDistribute(cuvsResources_t res,
+                                                    const char* filename,
+                                                    cuvsMultiGpuIvfPqIndex_t index);
+/* No counterpart in the reference: a single-GPU index file dealt out by inverted list (lists in order
+ * of descending size, each to the GPU holding the fewest rows so far). */
+CUVS_EXPORT cuvsError_t cuvsMultiGpuIvfPqDistributeByList(cuvsResources_t res,
+                                                          const char* filename,
+                                                          cuvsMultiGpuIvfPqIndex_t index);
+
+/* ---------------------------------------------------------------------------------------------
+ * Part 2: one process per GPU (no counterpart in the reference)
+ * --------------------------------------------------------------------------------------------- */
+
+/* An NCCL unique id (128 bytes), made by one rank and handed to the others by the host framework. */
+typedef struct {
+  char bytes[128];
+} cuvsMultiGpuCommId;
+typedef struct cuvsMultiGpuRankCommOpaque* cuvsMultiGpuRankComm_t;
+CUVS_EXPORT cuvsError_t cuvsMultiGpuCommIdCreate(cuvsMultiGpuCommId* id);
+/* Joins the communicator (collective: returns when all n_ranks ranks have called it).  The device of
+ * `res` must be current.  Exchange buffers are sized on first use and then kept. */
+CUVS_EXPORT cuvsError_t cuvsMultiGpuRankCommCreate(cuvsResources_t res,
+                                                   const cuvsMultiGpuCommId* id,
+                                                   int rank,
+                                                   int n_ranks,
+                                                   cuvsMultiGpuRankComm_t* comm);
+/* Same around an existing ncclComm_t (not destroyed with the object). */
+CUVS_EXPORT cuvsError_t cuvsMultiGpuRankCommAdopt(void* nccl_comm,
+                                                  int rank,
+                                                  int n_ranks,
+                                                  cuvsMultiGpuRankComm_t* comm);
+CUVS_EXPORT cuvsError_t cuvsMultiGpuRankCommDestroy(cuvsMultiGpuRankComm_t comm);
+/* The list-sharded search of one batch, called by every rank with the same queries (device tensors):
+ * probes of this rank's slice -> all-gather -> scan of the lists this rank holds -> all-gather of the
+ * per-rank blocks -> merge.  Asynchronous on the handle's stream; every rank gets the whole result,
+ * equal to cuvsIvfPqSearch on the unsharded index. */
+CUVS_EXPORT cuvsError_t cuvsMultiGpuIvfPqSearchRank(cuvsResources_t res,
+                                                    cuvsMultiGpuRankComm_t comm,
+                                                    cuvsIvfPqSearchParams_t search_params,
+                                                    cuvsIvfPqIndex_t shard,
+                                                    DLManagedTensor* queries,
+                                                    DLManagedTensor* neighbors,
+                                                    DLManagedTensor* distances);
+/* Stage times of cuvsMultiGpuIvfPqSearchRank calls made while the handle's stage timing was on
+ * (cuvsB200StatsEnable): stage_ms[5] = {probe slice, all-gather of the probes, scan of the owned lists,
+ * all-gather of the result blocks, merge}, milliseconds summed over *batches calls.  Waits for the calls
+ * it reports on. */
+CUVS_EXPORT cuvsError_t cuvsMultiGpuRankCommStats(cuvsMultiGpuRankComm_t comm,
+                                                  double* stage_ms,
+                                                  uint64_t* batches,
+                                                  bool reset);
+/* The rule that deals lists to ranks: owners[l] for list sizes given on the host. */
+CUVS_EXPORT cuvsError_t cuvsMultiGpuIvfPqListOwners(const uint32_t* list_sizes,
+                                                    uint32_t n_lists,
+                                                    int n_ranks,
+                                                    int32_t* owners);
+
 /* Stands in for cuvsMultiGpuIvfPqDistribute (c/include/cuvs/neighbors/mg_ivf_pq.h:266;
  * cpp/src/neighbors/mg/snmg.cuh:48-58) in a one-process-per-GPU deployment: loads a single-GPU
- * index file (format version 4) and keeps the payload of the lists owned by `rank` only; the
- * payload of the other lists is skipped in the file, never read. */
+ * index file (format version 4) and keeps the payload of the lists owned by `rank` only (the rule of
+ * cuvsMultiGpuIvfPqListOwners); the payload of the other lists is skipped in the file, never read. */
 CUVS_EXPORT cuvsError_t cuvsMultiGpuIvfPqDistributeShard(cuvsResources_t res,
                                                          const char* filename,
                                                          int rank,

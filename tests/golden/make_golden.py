@@ -1,7 +1,7 @@
 """Generates tests/golden/ref_pin.npz from the reference's own code.
 
-Run in an environment where the reference checkout is present (its location is the argument,
-by default the one oracle/Makefile uses):
+Run in an environment where the reference checkout is present (its location is the argument, else
+the environment variable CUVS_REFERENCE_ROOT, else a `reference` folder beside this repository):
     python tests/golden/make_golden.py [reference_root]
 It builds oracle/_ref/libref_pin.so (two reference headers compiled on the host, see
 oracle/ref_pin.cpp) and records, for seeded inputs,
@@ -21,7 +21,7 @@ sys.path.insert(0, ROOT)
 from oracle import oracle as O  # noqa: E402
 
 
-def main(reference_root="/root/reference"):
+def main(reference_root=None):
     so = O.build_ref_pin(reference_root)
     if so is None:
         raise SystemExit("reference checkout not found; cannot regenerate the golden fixture")

@@ -17,23 +17,32 @@ def main():
     dist.init_process_group("nccl", device_id=torch.device("cuda", int(os.environ["LOCAL_RANK"])))
     from cuvs_b200 import ivf_pq, mg
     q = torch.from_numpy(np.load(qpath)).cuda()
-    full = ivf_pq.load(path)
-    shard = mg.load_shard(path)
-    assert int(shard.list_sizes.sum().item()) < int(full.list_sizes.sum().item())
-    for k, p, lut in ((10, 8, np.float32), (40, 24, np.float16), (100, 12, np.uint8)):
-        sp = ivf_pq.SearchParams(n_probes=p, lut_dtype=lut)
-        d0, i0 = ivf_pq.search(sp, full, q, k)
-        d1, i1 = mg.search(sp, shard, q, k)
-        # distances bit for bit; ids wherever the distance is not shared with a neighbour in the row
-        # or with the k-th place (the merge orders equal distances by id, the single-GPU path by
-        # position in the probed lists)
-        assert (d0.view(torch.int32) == d1.view(torch.int32)).all(), (rank, k, p)
-        tied = torch.zeros_like(i0, dtype=torch.bool)
-        tied[:, 1:] |= d0[:, 1:] == d0[:, :-1]
-        tied[:, :-1] |= d0[:, :-1] == d0[:, 1:]
-        tied |= d0 == d0[:, -1:]
-        assert ((i0 == i1) | tied).all(), (rank, k, p)
-        assert tied.float().mean().item() < 0.2, (rank, k, p)
+    for suffix, lut_cases in (("", ((10, 8, np.float32), (40, 24, np.float16), (100, 12, np.uint8), (200, 16, np.float32))),
+                              (".ip", ((10, 8, np.float32), (150, 10, np.float16)))):
+        full = ivf_pq.load(path + suffix)
+        shard = mg.load_shard(path + suffix)
+        assert int(shard.list_sizes.sum().item()) < int(full.list_sizes.sum().item())
+        for k, p, lut in lut_cases:
+            sp = ivf_pq.SearchParams(n_probes=p, lut_dtype=lut)
+            d0, i0 = ivf_pq.search(sp, full, q, k)
+            for rep in range(2):          # the second call reuses the exchange buffers
+                d1, i1 = mg.search(sp, shard, q, k)
+                # distances bit for bit; ids wherever the distance is not shared with a neighbour in the
+                # row or with the k-th place (the merge orders equal distances by part, the single-GPU
+                # path by position in the probed lists)
+                assert (d0.view(torch.int32) == d1.view(torch.int32)).all(), (rank, k, p, suffix)
+                tied = torch.zeros_like(i0, dtype=torch.bool)
+                tied[:, 1:] |= d0[:, 1:] == d0[:, :-1]
+                tied[:, :-1] |= d0[:, :-1] == d0[:, 1:]
+                tied |= d0 == d0[:, -1:]
+                assert ((i0 == i1) | tied).all(), (rank, k, p, suffix)
+                assert tied.float().mean().item() < 0.2, (rank, k, p, suffix)
+        # int8 coarse search: the shared probe selection honours coarse_search_dtype
+        if suffix == "":
+            sp = ivf_pq.SearchParams(n_probes=8, coarse_search_dtype=np.int8)
+            d0, i0 = ivf_pq.search(sp, full, q, 10)
+            d1, i1 = mg.search(sp, shard, q, 10)
+            assert (d0.view(torch.int32) == d1.view(torch.int32)).all(), "int8 coarse"
     dist.barrier()
     dist.destroy_process_group()
     if rank == 0:

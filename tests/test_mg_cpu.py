@@ -40,8 +40,9 @@ def _worker(rank, world, port, path, q, k, n_probes, out):
     from oracle import oracle as O
     ix = O.OracleIndex.load(path)
     # keep the lists this rank owns (the rule of the C++ shard loader)
+    owners = mg.list_owners(ix.list_sizes, world)
     for l in range(ix.n_lists):
-        if mg.shard_of_list(l, world) != rank:
+        if owners[l] != rank:
             ix.list_sizes[l] = 0
             ix.list_codes[l] = np.zeros(0, np.uint8)
             ix.list_ids[l] = np.zeros(0, np.int64)
@@ -70,7 +71,17 @@ def test_sharded_search_equals_unsharded(oracle_mod, small_l2, tmp_path):
 
 
 def test_ownership_rule():
+    """Lists are dealt in order of descending size, each to the rank holding the fewest rows so far:
+    equal sizes come out round-robin, skewed sizes come out balanced."""
     from cuvs_b200 import mg
-    owners = [mg.shard_of_list(l, 8) for l in range(64)]
+    owners = mg.list_owners([100] * 64, 8)
     assert owners[:9] == [0, 1, 2, 3, 4, 5, 6, 7, 0]
     assert all(owners.count(r) == 8 for r in range(8))
+    rng = np.random.default_rng(0)
+    sizes = (rng.pareto(1.5, 5000) * 300).astype(np.uint32)       # heavy-tailed list sizes
+    owners = np.array(mg.list_owners(sizes, 8))
+    load = np.array([sizes[owners == r].sum() for r in range(8)], dtype=np.float64)
+    assert load.max() <= max(load.mean() * 1.01, float(sizes.max()))
+    naive = np.array([sizes[np.arange(5000) % 8 == r].sum() for r in range(8)], dtype=np.float64)
+    assert load.max() - load.min() <= naive.max() - naive.min()
+    assert mg.list_owners([5, 0, 7], 1) == [0, 0, 0]

@@ -22,6 +22,9 @@ def test_two_ranks_over_nccl_equal_the_single_gpu_search(oracle_mod, tmp_path):
     ix = oracle_mod.build_index(x, 96, pq_dim=24, pq_bits=8, kmeans_iters=3, seed=0)
     path, qpath = str(tmp_path / "mg.ivfpq"), str(tmp_path / "q.npy")
     ix.save(path)
+    # the same data as an inner-product index: there the LARGEST distances win the merge
+    oracle_mod.build_index(x, 96, pq_dim=24, pq_bits=8, metric=oracle_mod.InnerProduct, kmeans_iters=3,
+                           seed=0).save(path + ".ip")
     np.save(qpath, q)
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     worker = os.path.join(os.path.dirname(os.path.abspath(__file__)), "mg_worker.py")
