@@ -84,7 +84,7 @@ class MgSearchParamsStruct(C.Structure):
 
 
 class CommId(C.Structure):
-    _fields_ = [("bytes", C.c_char * 128)]
+    _fields_ = [("bytes", C.c_ubyte * 128)]
 
 
 class SearchStats(C.Structure):

@@ -1140,19 +1140,8 @@ void select_clusters_tc(raft::resources& res, const float* centers, const float*
   const float eps_rel = float(dim_ext + 8) * 2.4e-7f + 3.1e-5f +
                         (exact_operands ? 0.0f : (products == 1 ? 9.8e-4f : (products == 2 ? 4.9e-4f : 0.0f)));
   auto launch = [&](auto kernel) {
-    // every instantiation needs its shared-memory limit raised once
-    static thread_local const void* configured[8] = {};
-    bool seen = false;
-    for (const void* c : configured) { seen = seen || c == reinterpret_cast<const void*>(kernel); }
-    if (!seen) {
-      CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kSmemBytes)));
-      for (const void*& c : configured) {
-        if (c == nullptr) {
-          c = reinterpret_cast<const void*>(kernel);
-          break;
-        }
-      }
-    }
+    // every instantiation needs its shared-memory limit raised once per device
+    ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), kSmemBytes);
     kernel<<<grid, kThreads, kSmemBytes, stream>>>(m_a_hi, m_a_lo, m_b_hi, m_b_lo, p);
   };
   if (four_by_4) {
@@ -1177,7 +1166,6 @@ void select_clusters_tc(raft::resources& res, const float* centers, const float*
   uint32_t cap     = 2;
   while (cap < 2 * C) { cap <<= 1; }  // room for ties at the selection threshold
   const size_t fin_smem = size_t(cap) * 8 + size_t(dim_ext) * 4 + size_t(n_cand) * 4;
-  static size_t fin_configured = 48 * 1024;
   // the half-tile-maxima threshold is tight only when C is small against the number of half tiles
   // rows rescored per round: all 64 a query can select if they fit 48 KB of shared memory, else fewer
   uint32_t fin_rows = kFinRows;
@@ -1194,11 +1182,7 @@ void select_clusters_tc(raft::resources& res, const float* centers, const float*
         scores_out, redo_list, words + 2, fin_rows);
     }
   } else {
-    if (fin_smem > fin_configured) {
-      CUDA_TRY(cudaFuncSetAttribute(coarse_finish_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    int(fin_smem)));
-      fin_configured = fin_smem;
-    }
+    if (fin_smem > 48 * 1024) { ensure_dynamic_smem(reinterpret_cast<const void*>(coarse_finish_kernel), fin_smem); }
     coarse_finish_kernel<<<n_queries, 256, fin_smem, stream>>>(cand_key, cand_bnd, n_cand, kph, centers, fq,
                                                                n_lists, dim_ext, alpha, n_probes, C, cap,
                                                                cmax, eps_rel, probes, scores_out, redo_list,

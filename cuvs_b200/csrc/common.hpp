@@ -7,6 +7,7 @@
 #include <cstdarg>
 #include <cstdint>
 #include <cstdio>
+#include <map>
 #include <stdexcept>
 #include <string>
 #include <vector>
@@ -57,6 +58,21 @@ template <typename T>
 CUVS_HD constexpr T round_up(T a, T b)
 {
   return ceildiv(a, b) * b;
+}
+
+// Raises a kernel's limit of dynamic shared memory to `bytes` on the current device unless this thread
+// has already raised it that far there (the attribute belongs to the device's context, so a process
+// that drives several devices needs it once per device).
+inline void ensure_dynamic_smem(const void* kernel, size_t bytes)
+{
+  static thread_local std::map<std::pair<const void*, int>, size_t> done;
+  int dev = 0;
+  CUDA_TRY(cudaGetDevice(&dev));
+  size_t& have = done[{kernel, dev}];
+  if (bytes > have) {
+    CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(bytes)));
+    have = bytes;
+  }
 }
 
 // One grow-only device buffer carved into aligned slices per call.

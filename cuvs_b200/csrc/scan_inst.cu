@@ -14,11 +14,7 @@ template <int LutKind, bool OutHalf, bool IsIP, int KPL>
 void launch_one(const scan_params& p, int grid, size_t smem, cudaStream_t stream)
 {
   auto kernel = scan_kernel<PQ_BITS, LutKind, OutHalf, IsIP, KPL>;
-  static thread_local size_t configured = 0;
-  if (smem > configured) {
-    CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
-    configured = smem;
-  }
+  ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), smem);
   kernel<<<grid, 1024, smem, stream>>>(p);
   CUDA_TRY(cudaGetLastError());
 }

@@ -50,7 +50,7 @@ class RankComm:
             box = [None]
             if self.rank == 0:
                 L.check(self._lib.cuvsMultiGpuCommIdCreate(C.byref(cid)))
-                box[0] = bytes(cid.bytes)
+                box[0] = C.string_at(C.addressof(cid), 128)     # all 128 bytes, NULs included
             dist.broadcast_object_list(box, src=dist.get_global_rank(group, 0) if group is not None else 0,
                                        group=group)
             C.memmove(C.byref(cid), box[0], 128)
