@@ -166,6 +166,8 @@ SIGNATURES = {
                              _P(DLManagedTensor), C.c_int, _P(C.c_uint32)],
     "cuvsB200SetCoarseMode": [C.c_int],
     "cuvsB200SetScanCodebookHome": [C.c_int],
+    "cuvsB200CoarseTimeouts": [C.c_size_t, _P(C.c_uint64)],
+    "cuvsB200SetCoarseWaitTest": [C.c_uint32, C.c_uint32],
     "cuvsB200StatsEnable": [C.c_size_t, C.c_bool],
     "cuvsB200StatsGet": [C.c_size_t, _P(SearchStats), C.c_bool],
     "cuvsIvfPqPredictNoAlloc": [C.c_size_t, _P(IndexStruct), _P(DLManagedTensor), _P(DLManagedTensor)],

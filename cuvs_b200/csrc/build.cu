@@ -634,6 +634,77 @@ label_ctx labeling_of(DistanceType m)
   return {-2.0f, -0.5f, m == DistanceType::CosineExpanded};
 }
 
+// Labelling of many rows against one set of centres.  Where the shape allows, the tensor-core coarse
+// path does it (probe selection with n_probes = 1: exact rescoring and guard make its answer the
+// defining one, ties to the lowest list id) -- an order of magnitude faster than the SIMT product on
+// the 10^5 .. 10^6 lists of the large configurations; otherwise the SIMT kernel.
+__global__ void max_row_sumsq_kernel(const float* __restrict__ m, uint32_t n_rows, uint32_t n_cols,
+                                     uint32_t* __restrict__ out_bits)
+{
+  const uint32_t row = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (row >= n_rows) { return; }
+  float ss = 0.0f;
+  for (uint32_t k = lane; k < n_cols; k += 32) {
+    const float v = m[size_t(row) * n_cols + k];
+    ss            = __fmaf_rn(v, v, ss);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) { ss += __shfl_xor_sync(kFullMask, ss, o); }
+  if (lane == 0) { atomicMax(out_bits, __float_as_uint(ss)); }  // non-negative floats order as integers
+}
+
+class nearest_labeler {
+ public:
+  nearest_labeler(raft::resources& res, const float* centers, uint32_t n_lists, uint32_t dim_ext, float alpha)
+    : res_(res), centers_(centers), n_lists_(n_lists), dim_ext_(dim_ext), alpha_(alpha)
+  {
+    use_tc_ = coarse_tc_usable(n_lists, 1, dim_ext);
+    if (!use_tc_) { return; }
+    const size_t nc = size_t(n_lists) * dim_ext;
+    hi_.resize(nc);
+    lo_.resize(nc);
+    split_centers_tf32(res.stream, centers, nc, hi_.data(), lo_.data());
+    dev_array<uint32_t> mx(1);
+    CUDA_TRY(cudaMemsetAsync(mx.data(), 0, 4, res.stream));
+    max_row_sumsq_kernel<<<ceildiv<uint32_t>(n_lists * 32, 256), 256, 0, res.stream>>>(centers, n_lists, dim_ext,
+                                                                                        mx.data());
+    uint32_t bits = 0;
+    CUDA_TRY(cudaMemcpyAsync(&bits, mx.data(), 4, cudaMemcpyDeviceToHost, res.stream));
+    res.sync();
+    float ss;
+    std::memcpy(&ss, &bits, 4);
+    // the lanes sum in another order than a sequential loop: a generous margin on the bound
+    cmax_ = std::sqrt(ss) * 1.001f;
+    res.launches += 2;
+  }
+  // labels[i] = nearest list of row i of x_ext [n_rows, dim_ext]; `best` is scratch of n_rows * 8 bytes
+  void run(const float* x_ext, uint32_t n_rows, uint32_t* labels, unsigned long long* best)
+  {
+    if (!use_tc_) {
+      assign_nearest(res_, centers_, n_lists_, dim_ext_, alpha_, x_ext, n_rows, labels, best);
+      return;
+    }
+    const uint32_t batch = std::min<uint32_t>(n_rows, 16384);
+    const size_t need    = coarse_tc_workspace_bytes(batch, n_lists_, dim_ext_);
+    if (ws_.size() < need) { ws_.resize(need); }
+    for (uint32_t r0 = 0; r0 < n_rows; r0 += batch) {
+      const uint32_t nr = std::min(batch, n_rows - r0);
+      select_clusters_tc(res_, centers_, hi_.data(), lo_.data(), cmax_, n_lists_, dim_ext_, alpha_,
+                         x_ext + size_t(r0) * dim_ext_, nr, 1, labels + r0, nullptr, ws_.data(), ws_.size());
+    }
+  }
+
+ private:
+  raft::resources& res_;
+  const float* centers_;
+  uint32_t n_lists_, dim_ext_;
+  float alpha_;
+  bool use_tc_ = false;
+  float cmax_  = 0.0f;
+  dev_array<float> hi_, lo_;
+  dev_array<uint8_t> ws_;
+};
+
 // Host rows -> device staging (no-op for device data).
 const void* stage_rows(raft::resources& res, const void* data, elem_t t, uint64_t r0, uint64_t nr,
                        uint32_t dim, bool on_device, dev_array<uint8_t>& staging)
@@ -950,12 +1021,12 @@ void extend_any(raft::resources& res, const void* new_vectors, elem_t dtype, int
   CUDA_TRY(cudaMemsetAsync(counts.data(), 0, size_t(n_lists) * 4, stream));
 
   // pass 1: labels + histogram
+  nearest_labeler labeler(res, idx->centers(), n_lists, dim_ext, lc.alpha);
   for (uint64_t r0 = 0; r0 < n; r0 += chunk) {
     const uint64_t nr = std::min(chunk, n - r0);
     const void* src   = stage_rows(res, new_vectors, dtype, r0, nr, dim, on_device, staging);
     to_float_ext(res, src, dtype, nr, 1, dim, dim_ext, lc.pad, lc.normalize, x_ext.data());
-    assign_nearest(res, idx->centers(), n_lists, dim_ext, lc.alpha, x_ext.data(), uint32_t(nr),
-                   labels.data() + r0, best.data());
+    labeler.run(x_ext.data(), uint32_t(nr), labels.data() + r0, best.data());
     if (!on_device) { res.sync(); }
   }
   histogram_kernel<<<unsigned(ceildiv<uint64_t>(n, 256)), 256, 0, stream>>>(labels.data(), n, counts.data());
@@ -1023,12 +1094,12 @@ void transform_any(raft::resources& res, const index<int64_t>& idx, const void* 
   const uint32_t flat  = ceildiv(idx.pq_dim() * idx.pq_bits(), 8u);
   dev_array<float> x_ext(chunk * dim_ext);
   dev_array<unsigned long long> best(chunk);
+  nearest_labeler labeler(res, idx.centers(), idx.n_lists(), dim_ext, lc.alpha);
   for (uint64_t r0 = 0; r0 < n; r0 += chunk) {
     const uint32_t nr = uint32_t(std::min(chunk, n - r0));
     const char* src   = static_cast<const char*>(dataset) + r0 * dim * elem_size(dtype);
     to_float_ext(res, src, dtype, nr, 1, dim, dim_ext, lc.pad, lc.normalize, x_ext.data());
-    assign_nearest(res, idx.centers(), idx.n_lists(), dim_ext, lc.alpha, x_ext.data(), nr,
-                   out_labels + r0, best.data());
+    labeler.run(x_ext.data(), nr, out_labels + r0, best.data());
     launch_encode(res, idx, x_ext.data(), out_labels + r0, nullptr, nullptr, nr, false,
                   out_codes + r0 * flat, nullptr, nullptr, 0);
     res.sync();
@@ -1086,8 +1157,8 @@ void build_any(raft::resources& res, const index_params& params, const void* dat
   res.launches += 2;
   const uint32_t iters = std::max<uint32_t>(1, params.kmeans_n_iters);
   for (uint32_t it = 0; it < iters; it++) {
-    assign_nearest(res, idx.centers(), n_lists, dim_ext, lc.alpha, train.data(), uint32_t(n_train),
-                   labels.data(), best.data());
+    nearest_labeler(res, idx.centers(), n_lists, dim_ext, lc.alpha)
+      .run(train.data(), uint32_t(n_train), labels.data(), best.data());
     CUDA_TRY(cudaMemsetAsync(sums.data(), 0, sums.size() * 4, stream));
     CUDA_TRY(cudaMemsetAsync(counts.data(), 0, size_t(n_lists) * 4, stream));
     accumulate_kernel<<<unsigned(ceildiv<uint64_t>(n_train * 32, 256)), 256, 0, stream>>>(
@@ -1098,8 +1169,8 @@ void build_any(raft::resources& res, const index_params& params, const void* dat
     CUDA_TRY(cudaGetLastError());
     res.launches += 2;
   }
-  assign_nearest(res, idx.centers(), n_lists, dim_ext, lc.alpha, train.data(), uint32_t(n_train),
-                 labels.data(), best.data());
+  nearest_labeler(res, idx.centers(), n_lists, dim_ext, lc.alpha)
+    .run(train.data(), uint32_t(n_train), labels.data(), best.data());
 
   // ---- rotation, rotated centers ----
   {

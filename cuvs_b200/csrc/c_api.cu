@@ -739,6 +739,25 @@ extern "C" cuvsError_t cuvsB200SetCoarseMode(int mode)
   });
 }
 
+extern "C" cuvsError_t cuvsB200CoarseTimeouts(cuvsResources_t res, uint64_t* n_batches)
+{
+  return translate_exceptions([=] {
+    CUVS_EXPECTS(n_batches != nullptr, "null output pointer");
+    auto* r = res_of(res);
+    r->adopt_tc_verdict();
+    *n_batches = r->tc_timeouts;
+  });
+}
+
+extern "C" cuvsError_t cuvsB200SetCoarseWaitTest(uint32_t spin_limit, uint32_t skip_stage)
+{
+  return translate_exceptions([=] {
+    // a limit below 1000 iterations could fire on a healthy but busy GPU
+    CUVS_EXPECTS(spin_limit == 0 || spin_limit >= 1000, "spin_limit must be 0 or at least 1000");
+    ivf_pq::set_coarse_tc_wait_test(spin_limit, skip_stage);
+  });
+}
+
 extern "C" cuvsError_t cuvsB200SetScanCodebookHome(int home)
 {
   return translate_exceptions([=] {

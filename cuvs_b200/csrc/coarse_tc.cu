@@ -67,19 +67,6 @@ constexpr uint32_t kSpinLimit  = 1u << 21;  // bounded waits (each try_wait slee
 
 enum { ERR_NONE = 0, ERR_TIMEOUT = 1 };
 
-#ifdef TC_PROFILE
-// debug build only: cycles the three roles spend waiting on their barriers
-__device__ unsigned long long g_tc_prof[16];
-#define TC_WAIT(idx, expr)                                          \
-  [&]() {                                                           \
-    const long long t0_ = clock64();                                \
-    const bool r_ = (expr);                                         \
-    atomicAdd(&g_tc_prof[idx], (unsigned long long)(clock64() - t0_)); \
-    return r_;                                                      \
-  }()
-#else
-#define TC_WAIT(idx, expr) (expr)
-#endif
 
 // ------------------------------------------------------------------------------------------------
 // operand split
@@ -122,9 +109,9 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
 // Bounded wait: false on time-out.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity)
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t limit)
 {
-  for (uint32_t it = 0; it < kSpinLimit; it++) {
+  for (uint32_t it = 0; it < limit; it++) {
     uint32_t done;
     asm volatile(
       "{\n\t.reg .pred p;\n\t"
@@ -199,6 +186,8 @@ struct tc_params {
   uint32_t* cand_key;    // [n_queries, n_tiles, 2, keys per half tile] packed keys (larger = closer)
   uint32_t* cand_bound;  // [n_queries, n_tiles, 2, 2] key bounding everything a 64-column unit dropped
   uint32_t* error;     // error word
+  uint32_t spin_limit;  // iterations a bounded wait may take (about a microsecond each)
+  uint32_t skip_kb;     // test only: 1 + index of an operand stage the producer leaves unfilled, 0 = none
 };
 
 template <int kStreams, int kKeep, int kProducts>
@@ -230,9 +219,6 @@ coarse_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
   __shared__ uint32_t s_failed;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-#ifdef TC_PROFILE
-  const long long tc_start = clock64();
-#endif
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kNS; s++) {
@@ -272,9 +258,18 @@ coarse_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
         const uint32_t q0 = (g / p.n_tiles) * kBM;
         const int n0      = int((g % p.n_tiles) * kBN);
         for (uint32_t kb = 0; kb < p.k_blocks; kb++) {
-          if (!TC_WAIT(0, mbar_wait(bar_empty + stage * 8, phase ^ 1u))) {
+          if (!mbar_wait(bar_empty + stage * 8, phase ^ 1u, p.spin_limit)) {
             ok = false;
             break;
+          }
+          if (p.skip_kb != 0 && i == 0 && kb + 1 == p.skip_kb) {
+            // test only: this stage is never filled, so the wait for it runs out (bounded) and the
+            // kernel reports a time-out instead of finishing
+            if (++stage == kNS) {
+              stage = 0;
+              phase ^= 1u;
+            }
+            continue;
           }
           const uint32_t dst = base_a + stage * kStageB;
           const uint32_t bar = bar_full + stage * 8;
@@ -310,14 +305,14 @@ coarse_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
       for (uint32_t i = 0; ok && i < n_my_tiles; i++) {
         const uint32_t acc       = i & 1u;
         const uint32_t acc_phase = (i >> 1) & 1u;
-        if (!TC_WAIT(1, mbar_wait(bar_tempty + acc * 8, acc_phase ^ 1u))) {
+        if (!mbar_wait(bar_tempty + acc * 8, acc_phase ^ 1u, p.spin_limit)) {
           ok = false;
           break;
         }
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + acc * kBN;
         for (uint32_t kb = 0; kb < p.k_blocks; kb++) {
-          if (!TC_WAIT(2, mbar_wait(bar_full + stage * 8, phase))) {
+          if (!mbar_wait(bar_full + stage * 8, phase, p.spin_limit)) {
             ok = false;
             break;
           }
@@ -362,7 +357,7 @@ coarse_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
       const uint32_t q         = (g / p.n_tiles) * kBM + row;
       const uint32_t acc       = i & 1u;
       const uint32_t acc_phase = (i >> 1) & 1u;
-      if (ok && !(lane == 0 && warp == 2 ? TC_WAIT(3, mbar_wait(bar_tfull + acc * 8, acc_phase)) : mbar_wait(bar_tfull + acc * 8, acc_phase))) { ok = false; }
+      if (ok && !mbar_wait(bar_tfull + acc * 8, acc_phase, p.spin_limit)) { ok = false; }
       // a time-out on any lane ends the loop for the whole warp
       if (__any_sync(kFullMask, !ok)) {
         ok = false;
@@ -447,13 +442,6 @@ coarse_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
   // ---------------- teardown ----------------
   tc_fence_before();
   __syncthreads();
-#ifdef TC_PROFILE
-  if (threadIdx.x == 0) {
-    atomicAdd(&g_tc_prof[4], (unsigned long long)(clock64() - tc_start));
-    atomicAdd(&g_tc_prof[5], 1ull);
-    atomicAdd(&g_tc_prof[6], (unsigned long long)n_my_tiles);
-  }
-#endif
   if (s_failed) {
     // give copies that are still in flight time to land before the shared memory is released
     for (int i = 0; i < 64; i++) { __nanosleep(1000); }
@@ -481,8 +469,11 @@ coarse_finish_kernel(const uint32_t* __restrict__ cand_key, const uint32_t* __re
                      uint32_t n_lists, uint32_t dim_ext, float alpha, uint32_t n_probes, uint32_t C,
                      uint32_t cap /* pow2 >= C */, float cmax, float eps_rel,
                      uint32_t* __restrict__ probes, float* __restrict__ scores_out,
-                     uint32_t* __restrict__ redo_list, uint32_t* __restrict__ redo_count)
+                     uint32_t* __restrict__ redo_list, uint32_t* __restrict__ redo_count,
+                     const uint32_t* __restrict__ error_word)
 {
+  // the GEMM gave up on a wait: its candidates are incomplete, every query is redone exactly
+  if (*error_word != 0u) { return; }
   extern __shared__ uint64_t s_keys[];                 // [cap] keys; the query; the candidates
   float* s_q      = reinterpret_cast<float*>(s_keys + cap);
   uint32_t* key   = reinterpret_cast<uint32_t*>(s_q + dim_ext);  // [n_cand] staged once
@@ -708,8 +699,10 @@ coarse_finish_small_kernel(const uint32_t* __restrict__ cand_key, const uint32_t
                            uint32_t n_probes, uint32_t C, float cmax, float eps_rel,
                            uint32_t* __restrict__ probes, float* __restrict__ scores_out,
                            uint32_t* __restrict__ redo_list, uint32_t* __restrict__ redo_count,
-                           uint32_t rows_per_round)
+                           uint32_t rows_per_round, const uint32_t* __restrict__ error_word)
 {
+  // the GEMM gave up on a wait: its candidates are incomplete, every query is redone exactly
+  if (*error_word != 0u) { return; }
   // dynamic: query [dim_ext] | rows to rescore [rows_per_round][dim_ext + 1]
   extern __shared__ float s_dyn[];
   float* s_q    = s_dyn;
@@ -889,7 +882,7 @@ coarse_fallback_kernel(const uint32_t* __restrict__ redo_list, const uint32_t* _
                        uint32_t dim_ext, float alpha, uint32_t n_probes, uint32_t cap,
                        float* __restrict__ scratch /* [gridDim.x, n_lists] */,
                        uint32_t* __restrict__ probes, float* __restrict__ scores_out,
-                       uint32_t* __restrict__ n_fallback)
+                       uint32_t* __restrict__ n_fallback, const uint32_t* __restrict__ error_word)
 {
   extern __shared__ uint64_t s_keys[];  // [cap], then the query
   float* s_q = reinterpret_cast<float*>(s_keys + cap);
@@ -897,10 +890,12 @@ coarse_fallback_kernel(const uint32_t* __restrict__ redo_list, const uint32_t* _
   __shared__ uint32_t s_prefix, s_remaining, s_count, s_eq_taken;
   const uint32_t tid = threadIdx.x;
   float* row         = scratch + size_t(blockIdx.x) * n_lists;
-  const uint32_t n_redo = min(*redo_count, n_queries);
+  // after a time-out of the GEMM nothing it produced is trusted: all queries are redone here
+  const bool redo_all   = *error_word != 0u;
+  const uint32_t n_redo = redo_all ? n_queries : min(*redo_count, n_queries);
   if (blockIdx.x == 0 && tid == 0) { *n_fallback = n_redo; }
   for (uint32_t ri = blockIdx.x; ri < n_redo; ri += gridDim.x) {
-    const uint32_t q = redo_list[ri];
+    const uint32_t q = redo_all ? ri : redo_list[ri];
     for (uint32_t i = tid; i < dim_ext; i += 256) { s_q[i] = fq[size_t(q) * dim_ext + i]; }
     __syncthreads();
     for (uint32_t l = tid; l < n_lists; l += 256) {
@@ -1039,9 +1034,24 @@ int& tc_products_ref()
   return products;
 }
 
+// test hook: a shorter limit for the bounded waits and one operand stage left unfilled
+struct tc_fault {
+  uint32_t spin_limit = 0, skip_kb = 0;
+};
+tc_fault& tc_fault_ref()
+{
+  static tc_fault f;
+  return f;
+}
+
 }  // namespace
 
 void set_coarse_tc_products(int products) { tc_products_ref() = products; }
+void set_coarse_tc_wait_test(uint32_t spin_limit, uint32_t skip_kb)
+{
+  tc_fault_ref().spin_limit = spin_limit;
+  tc_fault_ref().skip_kb    = skip_kb;
+}
 
 bool coarse_tc_usable(uint32_t n_lists, uint32_t n_probes, uint32_t dim_ext)
 {
@@ -1122,21 +1132,17 @@ void select_clusters_tc(raft::resources& res, const float* centers, const float*
   p.cand_key  = cand_key;
   p.cand_bound = cand_bnd;
   p.error     = words;
+  p.spin_limit = tc_fault_ref().spin_limit ? tc_fault_ref().spin_limit : kSpinLimit;
+  p.skip_kb    = tc_fault_ref().skip_kb;
   const uint32_t q_tiles = ceildiv<uint32_t>(n_queries, kBM);
   p.n_work               = q_tiles * n_tiles;
   const uint32_t grid    = std::min<uint32_t>(uint32_t(res.sm_count), p.n_work);
   // Products of the TF32 split per K step: 3 (hi*hi + lo*hi + hi*lo, error ~ fp32 rounding),
   // 2 (without hi*lo: |error| <= 2^-11 |q||c|) or 1 (hi*hi only: <= 2^-10 |q||c|).  Fewer products
   // make the GEMM cheaper and the guard's error bound wider; the probes stay exact either way.
+  res.adopt_tc_verdict();  // what the last batch of this handle reported, if it has arrived
   int products = exact_operands ? 1 : tc_products_ref();
-  if (products == 0) {
-    // adopt the verdict on the last batch of this handle, if it has arrived
-    if (res.tc_redo_pending && cudaEventQuery(res.tc_redo_event) == cudaSuccess) {
-      res.tc_redo_pending = false;
-      if (uint64_t(res.pinned[8]) * 256 > res.tc_redo_queries && res.tc_products < 3) { res.tc_products++; }
-    }
-    products = res.tc_products;
-  }
+  if (products == 0) { products = res.tc_products; }
   const float eps_rel = float(dim_ext + 8) * 2.4e-7f + 3.1e-5f +
                         (exact_operands ? 0.0f : (products == 1 ? 9.8e-4f : (products == 2 ? 4.9e-4f : 0.0f)));
   auto launch = [&](auto kernel) {
@@ -1175,33 +1181,35 @@ void select_clusters_tc(raft::resources& res, const float* centers, const float*
     if (kph == 16) {
       coarse_finish_small_kernel<16><<<n_queries, 256, fin_small_smem, stream>>>(
         cand_key, cand_bnd, n_cand, centers, fq, n_lists, dim_ext, alpha, n_probes, C, cmax, eps_rel, probes,
-        scores_out, redo_list, words + 2, fin_rows);
+        scores_out, redo_list, words + 2, fin_rows, words);
     } else {
       coarse_finish_small_kernel<8><<<n_queries, 256, fin_small_smem, stream>>>(
         cand_key, cand_bnd, n_cand, centers, fq, n_lists, dim_ext, alpha, n_probes, C, cmax, eps_rel, probes,
-        scores_out, redo_list, words + 2, fin_rows);
+        scores_out, redo_list, words + 2, fin_rows, words);
     }
   } else {
     if (fin_smem > 48 * 1024) { ensure_dynamic_smem(reinterpret_cast<const void*>(coarse_finish_kernel), fin_smem); }
     coarse_finish_kernel<<<n_queries, 256, fin_smem, stream>>>(cand_key, cand_bnd, n_cand, kph, centers, fq,
                                                                n_lists, dim_ext, alpha, n_probes, C, cap,
                                                                cmax, eps_rel, probes, scores_out, redo_list,
-                                                               words + 2);
+                                                               words + 2, words);
   }
   uint32_t cap_fb = 2;
   while (cap_fb < n_probes) { cap_fb <<= 1; }
   const size_t fb_smem = size_t(cap_fb) * 8 + size_t(dim_ext) * 4;
   coarse_fallback_kernel<<<64, 256, fb_smem, stream>>>(redo_list, words + 2, centers, fq, n_queries, n_lists,
                                                        dim_ext, alpha, n_probes, cap_fb, scratch, probes,
-                                                       scores_out, words + 1);
+                                                       scores_out, words + 1, words);
   CUDA_TRY(cudaGetLastError());
   res.launches += 4;
-  if (!exact_operands && tc_products_ref() == 0 && !res.tc_redo_pending && res.tc_products < 3) {
-    // how many queries this batch redid exactly: read back without waiting, looked at before a later batch
+  if (!res.tc_redo_pending) {
+    // the error word and how many queries this batch redid exactly: read back without waiting, looked
+    // at before a later batch and at the handle's next synchronisation
     if (!res.tc_redo_event) { CUDA_TRY(cudaEventCreateWithFlags(&res.tc_redo_event, cudaEventDisableTiming)); }
-    CUDA_TRY(cudaMemcpyAsync(res.pinned + 8, words + 1, 4, cudaMemcpyDeviceToHost, stream));
+    CUDA_TRY(cudaMemcpyAsync(res.pinned + 8, words, 8, cudaMemcpyDeviceToHost, stream));
     CUDA_TRY(cudaEventRecord(res.tc_redo_event, stream));
     res.tc_redo_queries = n_queries;
+    res.tc_redo_adapts  = !exact_operands && tc_products_ref() == 0;
     res.tc_redo_pending = true;
   }
 }
@@ -1228,12 +1236,3 @@ void coarse_tc_status(raft::resources& res, const void* workspace, uint32_t n_qu
 
 }  // namespace cuvs::neighbors::ivf_pq
 
-#ifdef TC_PROFILE
-extern "C" __attribute__((visibility("default"))) void cuvsB200TcProfile(unsigned long long* out16)
-{
-  cudaDeviceSynchronize();
-  cudaMemcpyFromSymbol(out16, cuvs::neighbors::ivf_pq::g_tc_prof, 16 * sizeof(unsigned long long));
-  unsigned long long zero[16] = {};
-  cudaMemcpyToSymbol(cuvs::neighbors::ivf_pq::g_tc_prof, zero, sizeof(zero));
-}
-#endif

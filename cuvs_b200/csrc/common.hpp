@@ -151,12 +151,16 @@ struct resources {
   cudaEvent_t tc_redo_event  = nullptr;
   bool tc_redo_pending       = false;
   uint32_t tc_redo_queries   = 0;
+  bool tc_redo_adapts        = false;
+  void adopt_tc_verdict();
+  // batches whose coarse GEMM gave up on a bounded wait (their probes were recomputed exactly)
+  uint64_t tc_timeouts       = 0;
 
   resources();
   ~resources();
   resources(const resources&)            = delete;
   resources& operator=(const resources&) = delete;
-  void sync() const { CUDA_TRY(cudaStreamSynchronize(stream)); }
+  void sync();
 };
 
 }  // namespace cuvs_b200

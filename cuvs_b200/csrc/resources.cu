@@ -23,6 +23,25 @@ resources::~resources()
   if (pinned) { cudaFreeHost(pinned); }
 }
 
+void resources::adopt_tc_verdict()
+{
+  if (!tc_redo_pending || cudaEventQuery(tc_redo_event) != cudaSuccess) { return; }
+  tc_redo_pending = false;
+  if (pinned[8] != 0u) {
+    // the coarse GEMM of that batch gave up on a bounded wait; its probes were all recomputed exactly
+    tc_timeouts++;
+  } else if (tc_redo_adapts && uint64_t(pinned[9]) * 256 > tc_redo_queries && tc_products < 3) {
+    // more than 1/256 of the batch failed the exactness guard: one more product of the TF32 split
+    tc_products++;
+  }
+}
+
+void resources::sync()
+{
+  CUDA_TRY(cudaStreamSynchronize(stream));
+  adopt_tc_verdict();
+}
+
 void resources::stats_enable(bool on)
 {
   if (on && !d_stats) {

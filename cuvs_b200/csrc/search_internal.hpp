@@ -48,6 +48,9 @@ void coarse_only(raft::resources& res, const index<int64_t>& idx, const void* qu
 
 // products of the TF32 split the tensor-core coarse GEMM issues per K step (1, 2 or 3)
 void set_coarse_tc_products(int products);
+// test hook of the bounded waits of the tensor-core coarse kernel: iterations a wait may take (0 = the
+// default) and 1 + index of an operand stage left unfilled (0 = none)
+void set_coarse_tc_wait_test(uint32_t spin_limit, uint32_t skip_kb);
 void set_coarse_mode(int mode);  // process-wide override used by tests: 0 auto, 1 SIMT, 2 tensor core
 // process-wide override used by tests: 0 = the per-subspace codebook goes to tensor memory where it
 // fits, 1 = never (shared memory, else global memory)

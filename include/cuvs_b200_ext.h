@@ -51,6 +51,18 @@ CUVS_EXPORT cuvsError_t cuvsB200SetCoarseMode(int mode);
  * 1 = never tensor memory (shared memory, else global memory). */
 CUVS_EXPORT cuvsError_t cuvsB200SetScanCodebookHome(int home);
 
+/* No counterpart in the reference.  Every wait inside the tensor-core probe-selection kernel is bounded;
+ * when one runs out the kernel sets an error word, frees what it holds and returns, the stages behind
+ * it recompute the probes of every query of that batch with the exact path, and the handle counts the
+ * event.  This call returns that count (after waiting for nothing: it reports the batches whose
+ * verdict has arrived; cuvsStreamSync first makes that all of them). */
+CUVS_EXPORT cuvsError_t cuvsB200CoarseTimeouts(cuvsResources_t res, uint64_t* n_batches);
+/* No counterpart in the reference; for tests of the above.  spin_limit: iterations (about a microsecond
+ * each) a wait of that kernel may take, 0 = the default of about two seconds; skip_stage: 1 + index of
+ * an operand stage of each CTA's first tile that is never filled, so that the wait for it runs out;
+ * 0 = none.  Process-wide. */
+CUVS_EXPORT cuvsError_t cuvsB200SetCoarseWaitTest(uint32_t spin_limit, uint32_t skip_stage);
+
 #ifdef __cplusplus
 }
 #endif

@@ -367,6 +367,44 @@ def test_coarse_tensor_core_products_all_give_the_exact_probes(ivf, many_lists, 
     assert st[1] <= len(q) // 20          # the exact redo stays the exception
 
 
+def test_a_wait_that_runs_out_is_reported_and_the_probes_stay_exact(ivf, many_lists):
+    """Every wait in the tensor-core coarse kernel is bounded.  Here one operand stage is never filled
+    and the limit is shortened to a few milliseconds: the kernel gives up, sets its error word and
+    returns; the stages behind it recompute every query of the batch exactly; the handle counts the
+    event; the search result is the one of a healthy run; the GPU keeps answering."""
+    import ctypes as C
+    from cuvs_b200 import _lib as L
+    from cuvs_b200.common import default_resources
+    x, g = many_lists
+    q = make_mixture(300, 64, 512, 0.25, seed=90)
+    lib = L.load()
+    res = default_resources()
+    n0 = C.c_uint64(0)
+    p1, s1, _ = coarse_select(g, q, 20, 1)
+    d1, i1 = gpu_search(ivf, g, q, 10, 20, "f16")
+    L.check(lib.cuvsStreamSync(res.handle))
+    L.check(lib.cuvsB200CoarseTimeouts(res.handle, C.byref(n0)))
+    try:
+        L.check(lib.cuvsB200SetCoarseWaitTest(4000, 2))
+        p2, s2, st = coarse_select(g, q, 20, 2)
+        assert st[0] == 1, "the kernel should have reported the wait that ran out"
+        assert st[1] == len(q), "every query of the batch is redone exactly"
+        assert (p1 == p2).all() and (s1.view(np.uint32) == s2.view(np.uint32)).all()
+        d2, i2 = gpu_search(ivf, g, q, 10, 20, "f16")
+    finally:
+        L.check(lib.cuvsB200SetCoarseWaitTest(0, 0))
+    assert (i1 == i2).all() and (d1.view(np.uint32) == d2.view(np.uint32)).all()
+    L.check(lib.cuvsStreamSync(res.handle))
+    n1 = C.c_uint64(0)
+    L.check(lib.cuvsB200CoarseTimeouts(res.handle, C.byref(n1)))
+    assert n1.value > n0.value
+    # and a healthy run afterwards
+    p3, s3, st3 = coarse_select(g, q, 20, 2)
+    assert st3[0] == 0 and (p3 == p1).all()
+    with pytest.raises(L.CuvsError, match="spin_limit"):
+        L.check(lib.cuvsB200SetCoarseWaitTest(10, 0))
+
+
 @pytest.mark.parametrize("k,lut,internal", [(129, "f32", "f32"), (200, "f16", "f32"), (513, "fp8", "f16")])
 def test_search_parity_large_k_store_all_path(ivf, oracle_mod, small_l2, k, lut, internal):
     """k > 128 switches to the mode where the scan stores every score and a selection follows
