@@ -1,18 +1,23 @@
 #!/usr/bin/env python
 """Benchmark of the IVF-PQ search path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--config 1..5]
 
-Workload (N = 1): the deep-embedding-shaped configuration -- 10,000,000 x 96 fp32 L2-normalised
-draws from a 4,096-component anisotropic Gaussian mixture (seed 1), 10,000 queries, n_lists 50,000,
-pq_dim 48, pq_bits 8, k = 10, fp16 look-up table, fp32 internal distances, n_probes swept over
-{20, 50, 100, 200}, one batch of 10,000 queries per step.  The public dataset this imitates is not
-available offline; the seeded synthetic generator below stands in for it.
+Workload (default, --config 2): the deep-embedding-shaped configuration -- 10,000,000 x 96 fp32
+L2-normalised draws from a 4,096-component anisotropic Gaussian mixture (seed 1), 10,000 queries,
+n_lists 50,000, pq_dim 48, pq_bits 8, k = 10, fp16 look-up table, fp32 internal distances, n_probes
+swept over {20, 50, 100, 200}, one batch of 10,000 queries per step.  --config 1, 3, 4, 5 run the other
+four benchmark configurations (3 and 4 at the size one GPU holds: 100 M rows and the 125 M-row prefix).
+The public datasets these imitate are not available offline; the seeded synthetic generators below
+stand in for them.
 
 A step = one search of the whole query batch.  `value` is queries/s with queries resident in HBM;
 `e2e` is the same through the C interface with pinned host buffers and the copies inside the timed
 region.  Times come from CUDA events on the stream the library launches on (torch's current
-stream); the code-scan kernel is timed by the library's own events around its launch.
+stream); the code-scan kernel is timed by the library's own events around its launch.  `parity`
+compares, id for id, what the GPU search returned for the CPU leg's sample of queries with what the
+CPU oracle returned for them; with several GPUs `mg_parity` compares the merged result with the
+single-GPU result of the same index.
 
 --impl reference times the CPU oracle (the port of the reference search arithmetic, all host
 threads) on a bounded sample of the same queries against the same index.
@@ -35,17 +40,37 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
-WORKLOAD = dict(name="deep-embedding-shaped L2, 10M x 96 f32", n_rows=10_000_000, dim=96,
-                n_components=4096, seed=1, n_queries=10_000, n_lists=50_000, pq_dim=48, pq_bits=8,
-                k=10, probes=(20, 50, 100, 200), lut="float16", internal="float32",
-                kmeans_n_iters=10, kmeans_trainset_fraction=0.1, refine_ratio=2)
-# A second, optional workload (--workload sift): the SIFT-shaped integer configuration in miniature
-# (one GPU's share of it): long lists, 8-bit look-up table, k = 100 -- the regime where the code scan
-# rather than the look-up-table build dominates.  Not the headline; used for the scan roofline.
-SIFT_WORKLOAD = dict(name="SIFT-shaped L2, 20M x 128 u8", kind="sift", n_rows=20_000_000, dim=128,
-                     n_components=16384, seed=2, n_queries=10_000, n_lists=20_000, pq_dim=64,
-                     pq_bits=8, k=100, probes=(64,), lut="uint8", internal="float32",
-                     kmeans_n_iters=10, kmeans_trainset_fraction=0.1, refine_ratio=1)
+# The five benchmark configurations.  `gen` names the generator; `batches` are the small batches whose
+# latency is reported beside the throughput batch; `refine_ratio` > 1 re-ranks refine_ratio * k
+# candidates exactly (the reference benchmark's own route to high recall with PQ).
+CONFIGS = {
+    1: dict(name="config 1: small L2, 100k x 128 f32", gen="uniform_centers", n_rows=100_000, dim=128,
+            n_components=1024, seed=0, n_queries=1000, n_lists=1024, pq_dim=64, pq_bits=8, k=10,
+            probes=(32,), lut="float32", internal="float32", kmeans_n_iters=20,
+            kmeans_trainset_fraction=0.5, refine_ratio=1, metric="sqeuclidean", batches=(1, 100)),
+    2: dict(name="deep-embedding-shaped L2, 10M x 96 f32", gen="deep", n_rows=10_000_000, dim=96,
+            n_components=4096, seed=1, n_queries=10_000, n_lists=50_000, pq_dim=48, pq_bits=8,
+            k=10, probes=(20, 50, 100, 200), lut="float16", internal="float32",
+            kmeans_n_iters=10, kmeans_trainset_fraction=0.1, refine_ratio=2, metric="sqeuclidean",
+            batches=(1, 100)),
+    3: dict(name="SIFT-shaped L2, 100M x 128 u8", gen="sift", n_rows=100_000_000, dim=128,
+            n_components=16384, seed=2, n_queries=10_000, n_lists=100_000, pq_dim=64, pq_bits=8, k=100,
+            probes=(64,), lut="uint8", internal="float32", kmeans_n_iters=8,
+            kmeans_trainset_fraction=0.02, refine_ratio=1, metric="sqeuclidean", batches=(1, 100)),
+    4: dict(name="int8 L2, 125M-row prefix of 1B x 128 i8", gen="int8", n_rows=125_000_000, dim=128,
+            n_components=65536, seed=3, n_queries=10_000, n_lists=262_144, pq_dim=64, pq_bits=8, k=10,
+            probes=(128,), lut="uint8", internal="float32", kmeans_n_iters=6,
+            kmeans_trainset_fraction=0.02, refine_ratio=1, metric="sqeuclidean", batches=(1, 100)),
+    5: dict(name="text-embedding-shaped inner product, 10M x 768 f16, 4-bit codes", gen="vmf",
+            n_rows=10_000_000, dim=768, n_components=2048, seed=4, n_queries=10_000, n_lists=32_768,
+            pq_dim=384, pq_bits=4, k=10, probes=(100,), lut="float16", internal="float32",
+            kmeans_n_iters=8, kmeans_trainset_fraction=0.1, refine_ratio=1, metric="inner_product",
+            batches=(1, 10)),
+}
+# A slice of configuration 3 run beside the headline workload (its own scan roofline: long lists, 8-bit
+# look-up table, k = 100 -- the regime where the code scan rather than the table build dominates).
+LONG_LISTS = dict(CONFIGS[3], name="config 3 slice: SIFT-shaped L2, 4M x 128 u8", n_rows=4_000_000,
+                  n_lists=4000, n_components=2048, n_queries=10_000, kmeans_trainset_fraction=0.1)
 METRIC = "IVF-PQ search QPS @ recall@10>=0.95"
 FALLBACK_HBM_GBS = 6650.0
 
@@ -61,19 +86,35 @@ def log(*a):
 def mixture_model(wl, device):
     import torch
     g = torch.Generator(device="cpu").manual_seed(wl["seed"] * 7919 + 17)
-    if wl.get("kind") == "sift":
-        # centres in [0, 120] plus a per-dimension exponential offset (mean 20): mass skewed to 0-40
-        centers = torch.rand(wl["n_components"], wl["dim"], generator=g) * 60.0
-        centers = centers + torch.empty(wl["n_components"], wl["dim"]).exponential_(1.0 / 20.0, generator=g)
-        scales = torch.full((wl["n_components"], wl["dim"]), 12.0)
-        return centers.to(device), scales.to(device)
-    centers = torch.randn(wl["n_components"], wl["dim"], generator=g)
+    nc, dim = wl["n_components"], wl["dim"]
+    kind = wl["gen"]
+    if kind == "sift":
+        # centres in [0, 60] plus a per-dimension exponential offset (mean 20): mass skewed to 0-40
+        centers = torch.rand(nc, dim, generator=g) * 60.0
+        centers = centers + torch.empty(nc, dim).exponential_(1.0 / 20.0, generator=g)
+        return centers.to(device), torch.tensor(12.0, device=device)
+    if kind == "int8":
+        centers = torch.rand(nc, dim, generator=g) * 200.0 - 100.0
+        return centers.to(device), torch.tensor(12.0, device=device)
+    if kind == "uniform_centers":
+        centers = torch.rand(nc, dim, generator=g) * 2.0 - 1.0
+        return centers.to(device), torch.tensor(0.15, device=device)
+    if kind == "vmf":
+        # unit centres; isotropic noise whose norm makes the mean cosine to the centre about 0.8
+        centers = torch.nn.functional.normalize(torch.randn(nc, dim, generator=g), dim=1)
+        return centers.to(device), torch.tensor(0.75 / np.sqrt(dim), device=device)
+    centers = torch.randn(nc, dim, generator=g)
     lo, hi = np.log(0.05), np.log(0.5)
-    scales = torch.exp(torch.rand(wl["n_components"], wl["dim"], generator=g) * (hi - lo) + lo)
+    scales = torch.exp(torch.rand(nc, dim, generator=g) * (hi - lo) + lo)
     # per-component scale is relative to the centre norm, so clusters keep their identity after
     # the rows are L2-normalised
-    scales = scales * (centers.norm(dim=1, keepdim=True) / np.sqrt(wl["dim"]))
+    scales = scales * (centers.norm(dim=1, keepdim=True) / np.sqrt(dim))
     return centers.to(device), scales.to(device)
+
+
+def data_dtype(wl):
+    import torch
+    return {"sift": torch.uint8, "int8": torch.int8, "vmf": torch.float16}.get(wl["gen"], torch.float32)
 
 
 def gen_rows(wl, model, start, count, device, stream_id=0):
@@ -81,17 +122,23 @@ def gen_rows(wl, model, start, count, device, stream_id=0):
     centers, scales = model
     g = torch.Generator(device=device).manual_seed(wl["seed"] * 1_000_003 + start + stream_id * 977)
     comp = torch.randint(0, wl["n_components"], (count,), generator=g, device=device)
-    x = centers[comp] + scales[comp] * torch.randn(count, wl["dim"], generator=g, device=device)
-    if wl.get("kind") == "sift":
+    noise = torch.randn(count, wl["dim"], generator=g, device=device)
+    x = centers[comp] + (scales[comp] if scales.dim() == 2 else scales) * noise
+    kind = wl["gen"]
+    if kind == "sift":
         return x.round_().clamp_(0, 255).to(torch.uint8)
-    return torch.nn.functional.normalize(x, dim=1)
+    if kind == "int8":
+        return x.round_().clamp_(-128, 127).to(torch.int8)
+    if kind == "uniform_centers":
+        return x
+    x = torch.nn.functional.normalize(x, dim=1)
+    return x.to(torch.float16) if kind == "vmf" else x
 
 
 def gen_dataset(wl, device):
     import torch
     model = mixture_model(wl, device)
-    x = torch.empty((wl["n_rows"], wl["dim"]), device=device,
-                    dtype=torch.uint8 if wl.get("kind") == "sift" else torch.float32)
+    x = torch.empty((wl["n_rows"], wl["dim"]), device=device, dtype=data_dtype(wl))
     step = 1_000_000
     for s in range(0, wl["n_rows"], step):
         c = min(step, wl["n_rows"] - s)
@@ -100,18 +147,20 @@ def gen_dataset(wl, device):
     return x, q
 
 
-def ground_truth(x, q, k):
-    """Exact top-k by squared L2 distance, fp32, in row chunks."""
+def ground_truth(x, q, k, metric="sqeuclidean"):
+    """Exact top-k in fp32, in row chunks: smallest squared L2 distance, or largest inner product."""
     import torch
     q = q.float()
+    ip = metric == "inner_product"
     qn = (q * q).sum(1, keepdim=True)
     best_d = torch.full((q.shape[0], k), float("inf"), device=q.device)
     best_i = torch.zeros((q.shape[0], k), dtype=torch.int64, device=q.device)
     step = 200_000
     for s in range(0, x.shape[0], step):
         xb = x[s:s + step].float()
-        d = qn + (xb * xb).sum(1)[None, :] - 2.0 * (q @ xb.T)
-        dd, ii = torch.topk(d, k, dim=1, largest=False)
+        dots = q @ xb.T
+        d = -dots if ip else qn + (xb * xb).sum(1)[None, :] - 2.0 * dots
+        dd, ii = torch.topk(d, min(k, d.shape[1]), dim=1, largest=False)
         cat_d = torch.cat([best_d, dd], 1)
         cat_i = torch.cat([best_i, ii + s], 1)
         best_d, sel = torch.topk(cat_d, k, dim=1, largest=False)
@@ -187,8 +236,22 @@ def cache_dir(wl):
     return d
 
 
-def prepare_fixture(wl, device, need_dataset=False):
-    """Returns dict(index_path, queries (device), truth (device), build_s).  Builds what is missing."""
+def lut_np(wl):
+    return {"float32": np.float32, "float16": np.float16, "uint8": np.uint8}[wl["lut"]]
+
+
+def k0_of(wl):
+    return int(wl["refine_ratio"] * wl["k"]) if wl["refine_ratio"] > 1 else wl["k"]
+
+
+def single_result_path(d, p, k0):
+    return os.path.join(d, f"single_p{p}_k{k0}.npz")
+
+
+def prepare_fixture(wl, device, need_dataset=False, single_results=False):
+    """Returns dict(index_path, queries (device), truth (device), build_s).  Builds what is missing.
+    `single_results`: also keep, beside the index, what the single-GPU search returns for every
+    n_probes of the workload (k0 candidates, before refinement) -- the multi-GPU parity check reads it."""
     import torch
 
     from cuvs_b200 import ivf_pq
@@ -200,17 +263,17 @@ def prepare_fixture(wl, device, need_dataset=False):
         t0 = time.time()
         x, q = gen_dataset(wl, device)
         torch.cuda.synchronize()
-        log(f"[bench] generated {tuple(x.shape)} in {time.time() - t0:.1f}s")
+        log(f"[bench] generated {tuple(x.shape)} {x.dtype} in {time.time() - t0:.1f}s")
         t0 = time.time()
         params = ivf_pq.IndexParams(n_lists=wl["n_lists"], pq_dim=wl["pq_dim"], pq_bits=wl["pq_bits"],
-                                    kmeans_n_iters=wl["kmeans_n_iters"],
+                                    metric=wl["metric"], kmeans_n_iters=wl["kmeans_n_iters"],
                                     kmeans_trainset_fraction=wl["kmeans_trainset_fraction"])
         index = ivf_pq.build(params, x)
         torch.cuda.synchronize()
         out["build_s"] = time.time() - t0
         log(f"[bench] built index in {out['build_s']:.1f}s")
         t0 = time.time()
-        truth = ground_truth(x, q, wl["k"])
+        truth = ground_truth(x, q, wl["k"], wl["metric"])
         torch.cuda.synchronize()
         log(f"[bench] exact ground truth in {time.time() - t0:.1f}s")
         ivf_pq.save(ipath, index)
@@ -221,9 +284,48 @@ def prepare_fixture(wl, device, need_dataset=False):
         open(done, "w").write("ok")
     out["queries"] = torch.from_numpy(np.load(qpath)).to(device)
     out["truth"] = torch.from_numpy(np.load(tpath)).to(device)
+    k0 = k0_of(wl)
+    if single_results and not all(os.path.exists(single_result_path(d, p, k0)) for p in wl["probes"]):
+        index = ivf_pq.load(ipath)
+        nq = out["queries"].shape[0]
+        for p in wl["probes"]:
+            sp = ivf_pq.SearchParams(n_probes=p, lut_dtype=lut_np(wl),
+                                     internal_distance_dtype={"float32": np.float32, "float16": np.float16}[wl["internal"]],
+                                     max_internal_batch_size=nq)
+            dd, ii = ivf_pq.search(sp, index, out["queries"], k0)
+            np.savez(single_result_path(d, p, k0), d=dd.cpu().numpy(), i=ii.cpu().numpy())
+        del index
+        torch.cuda.empty_cache()
     if need_dataset:      # regenerated from the seeds (refinement reads the original vectors)
         out["dataset"] = gen_dataset(wl, device)[0]
     return out
+
+
+# --------------------------------------------------------------------------------------------
+# parity: GPU result against another result of the same queries, id for id
+# --------------------------------------------------------------------------------------------
+def parity_record(d_gpu, i_gpu, d_ref, i_ref, tol):
+    """Rows must hold the same ids in the same places with bit-equal distances; a row may differ only
+    where distances tie within `tol` (relative): every id the GPU returned that the other side did not
+    must lie within tol of the other side's distance at that place or of its k-th distance."""
+    d_gpu, i_gpu, d_ref, i_ref = (np.asarray(a) for a in (d_gpu, i_gpu, d_ref, i_ref))
+    same = (i_gpu == i_ref).all(axis=1)
+    bits = (d_gpu.view(np.uint32) == d_ref.view(np.uint32)) | ~np.isfinite(d_ref)
+    identical = int((same & bits.all(axis=1)).sum())
+    tie_rows, failed = 0, 0
+    for r in np.nonzero(~(same & bits.all(axis=1)))[0]:
+        ref = dict(zip(i_ref[r].tolist(), d_ref[r].tolist()))
+        kth = float(d_ref[r][-1])
+        ok = True
+        for idv, dv in zip(i_gpu[r].tolist(), d_gpu[r].tolist()):
+            want = ref.get(idv, kth)
+            if not (abs(dv - want) <= tol * max(abs(want), 1e-30) + 1e-30):
+                ok = False
+                break
+        tie_rows += int(ok)
+        failed += int(not ok)
+    return {"rows": int(same.shape[0]), "identical": identical, "tie_rows": tie_rows, "failed_rows": failed,
+            "tol": tol, "passed": failed == 0 and tie_rows <= max(1, same.shape[0] // 50)}
 
 
 # --------------------------------------------------------------------------------------------
@@ -232,9 +334,12 @@ def prepare_fixture(wl, device, need_dataset=False):
 def cpu_baseline(index_path, queries_np, wl, n_probes, budget_s=12.0, steps=1, warmup=0,
                  dataset_np=None):
     """The CPU port on all host threads: IVF-PQ search for k0 candidates and, when the workload
-    refines, exact re-ranking of those candidates with numpy."""
+    refines, exact re-ranking of those candidates with numpy.  Also returns what the search itself
+    (before re-ranking) found for the sample, for the parity check against the GPU."""
     from oracle import oracle as O
     t0 = time.time()
+    # all host cores, whatever OMP_NUM_THREADS the launcher put into the environment
+    O.lib().orc_set_num_threads(os.cpu_count() or 1)
     ix = O.OracleIndex.load(index_path)
     ix.flat()
     log(f"[bench] oracle loaded the index in {time.time() - t0:.1f}s")
@@ -242,14 +347,18 @@ def cpu_baseline(index_path, queries_np, wl, n_probes, budget_s=12.0, steps=1, w
     lut = {"float32": O.CUDA_R_32F, "float16": O.CUDA_R_16F, "uint8": O.CUDA_R_8U}[wl["lut"]]
     internal = {"float32": O.CUDA_R_32F, "float16": O.CUDA_R_16F}[wl["internal"]]
     k = wl["k"]
-    k0 = int(wl["refine_ratio"] * k) if (wl["refine_ratio"] > 1 and dataset_np is not None) else k
+    k0 = k0_of(wl) if dataset_np is not None else k
+    ip = wl["metric"] == "inner_product"
+    found = {}
 
     def run(q):
         d, i = O.search(ix, q, k0, n_probes=n_probes, lut_dtype=lut, internal_dtype=internal)
+        found["d"], found["i"] = d, i
         if k0 > k:
             safe = np.where(i == O.OUT_OF_BOUNDS, 0, i)
-            v = dataset_np[safe]                                   # [n, k0, dim]
-            dd = ((v - q[:, None, :]) ** 2).sum(2)
+            v = dataset_np[safe].astype(np.float32)                # [n, k0, dim]
+            qf = q.astype(np.float32)
+            dd = -(v * qf[:, None, :]).sum(2) if ip else ((v - qf[:, None, :]) ** 2).sum(2)
             dd = np.where(i == O.OUT_OF_BOUNDS, np.inf, dd)
             o = np.argsort(dd, axis=1)[:, :k]
             i = np.take_along_axis(i, o, 1)
@@ -272,7 +381,7 @@ def cpu_baseline(index_path, queries_np, wl, n_probes, budget_s=12.0, steps=1, w
     if k0 > k:
         what += f", {k0} candidates re-ranked exactly"
     return {"value": n / dt, "unit": "queries/s", "cores": int(cores), "kind": "port",
-            "sample": what + "; same index file; C port of the reference arithmetic, OpenMP over queries"}, dt, n
+            "sample": what + "; same index file; C port of the reference arithmetic, OpenMP over queries"}, dt, n, found
 
 
 # --------------------------------------------------------------------------------------------
@@ -294,14 +403,60 @@ DRAM_BYTES_PER_UNIQUE_GROUP = 1826.0
 
 
 def workload_from_args(args):
-    wl = dict(SIFT_WORKLOAD if args.workload == "sift" else WORKLOAD)
+    if args.workload == "sift" and args.config == 2:      # older spelling of a configuration-3 slice
+        wl = dict(CONFIGS[3], name="SIFT-shaped L2, 20M x 128 u8", n_rows=20_000_000, n_lists=20_000,
+                  kmeans_trainset_fraction=0.1, kmeans_n_iters=10)
+    else:
+        wl = dict(CONFIGS[args.config])
     if args.rows:
-        per_list = wl["n_rows"] // wl["n_lists"]
+        per_list = max(1, wl["n_rows"] // wl["n_lists"])
         wl.update(n_rows=args.rows, n_lists=max(64, args.rows // per_list),
                   n_queries=min(wl["n_queries"], max(100, args.rows // 100)))
+        wl["name"] += f" (shrunk to {args.rows} rows)"
     if args.refine_ratio is not None:
         wl["refine_ratio"] = args.refine_ratio
     return wl
+
+
+def long_list_record(res, device, peak, steps):
+    """The scan kernel on long lists: a 4 M-row slice of configuration 3 (lists of about 1,000 rows,
+    8-bit look-up table, k = 100, n_probes 64), its own roofline figures."""
+    import ctypes as C
+
+    import torch
+
+    from cuvs_b200 import _lib as L
+    from cuvs_b200 import ivf_pq
+    wl = dict(LONG_LISTS)
+    fx = prepare_fixture(wl, device)
+    index = ivf_pq.load(fx["index_path"])
+    q = fx["queries"]
+    nq, k, p = q.shape[0], wl["k"], wl["probes"][0]
+    sp = ivf_pq.SearchParams(n_probes=p, lut_dtype=np.uint8, max_internal_batch_size=nq)
+    lib = L.load()
+    d, i = ivf_pq.search(sp, index, q, k, resources=res)
+    rec = recall_at_k(i, fx["truth"])
+    stats = L.SearchStats()
+    L.check(lib.cuvsB200StatsEnable(res.handle, True))
+    L.check(lib.cuvsB200StatsGet(res.handle, C.byref(stats), True))
+    for _ in range(max(3, steps)):
+        ivf_pq.search(sp, index, q, k, resources=res, sync=False)
+    L.check(lib.cuvsB200StatsGet(res.handle, C.byref(stats), True))
+    L.check(lib.cuvsB200StatsEnable(res.handle, False))
+    b = max(1, stats.batches)
+    n_pieces = -(-wl["pq_dim"] // (128 // wl["pq_bits"]))
+    scan_ms = stats.scan_ms / b
+    algo = stats.scan_groups / b * n_pieces * 512
+    ach = algo / (scan_ms * 1e-3) / 1e9
+    del index
+    torch.cuda.empty_cache()
+    return {"workload": wl["name"], "n_lists": wl["n_lists"], "n_probes": p, "k": k, "lut_dtype": "uint8",
+            "recall_at_k": round(rec, 4), "ms_per_batch": round(sum(getattr(stats, f) for f in
+                                                                    ("prep_ms", "coarse_ms", "sort_ms", "scan_ms", "merge_ms")) / b, 4),
+            "roofline": {"bound": "hbm", "kernel": "scan_kernel", "achieved": round(ach, 1), "peak": peak,
+                         "unit": "GB/s", "frac": round(ach / peak, 4), "kernel_ms": round(scan_ms, 4),
+                         "algorithmic_bytes_per_launch": int(algo),
+                         "unique_bytes_per_launch": int(stats.unique_groups / b * n_pieces * 512)}}
 
 
 def run_ours(args):
@@ -312,7 +467,7 @@ def run_ours(args):
 
     from cuvs_b200 import _lib as L
     from cuvs_b200 import ivf_pq, mg, refine
-    from cuvs_b200.common import default_resources
+    from cuvs_b200.common import Resources, default_resources
 
     wl = workload_from_args(args)
     probes = tuple(int(p) for p in args.probes.split(",")) if args.probes else wl["probes"]
@@ -329,12 +484,13 @@ def run_ours(args):
     res = default_resources()
     lib = L.load()
     k = wl["k"]
-    k0 = int(wl["refine_ratio"] * k) if wl["refine_ratio"] > 1 else k
+    k0 = k0_of(wl)
     refining = k0 > k
+    metric = wl["metric"]
 
     # ---- fixture: rank 0 builds (or finds) it, everyone loads its shard ----
     if rank == 0:
-        fx = prepare_fixture(wl, device, need_dataset=refining)
+        fx = prepare_fixture(wl, device, need_dataset=refining, single_results=world > 1)
     if world > 1:
         dist.barrier()
     if rank != 0:
@@ -343,8 +499,9 @@ def run_ours(args):
     queries, truth = fx["queries"], fx["truth"]
     dataset = fx.get("dataset")
     nq = queries.shape[0]
-    lut_dt = {"float32": np.float32, "float16": np.float16, "uint8": np.uint8}[wl["lut"]]
+    lut_dt = lut_np(wl)
     int_dt = {"float32": np.float32, "float16": np.float16}[wl["internal"]]
+    comm = mg.RankComm(None, res) if world > 1 else None
 
     def make_sp(p):
         return ivf_pq.SearchParams(n_probes=p, lut_dtype=lut_dt, internal_distance_dtype=int_dt,
@@ -355,17 +512,20 @@ def run_ours(args):
     out_i0 = torch.empty((nq, k), dtype=torch.int64, device=device)
     out_d0 = torch.empty((nq, k), dtype=torch.float32, device=device)
 
+    def ann_search(sp, q, r, cm, ci, cd):
+        """IVF-PQ search for k0 candidates: one call into the C++ host side either way (with several
+        GPUs the call enqueues probe slice, all-gathers, scan and merge)."""
+        if world > 1:
+            return mg.search(sp, index, q, k0, resources=r, sync=False, comm=cm, out=(cd, ci))
+        return ivf_pq.search(sp, index, q, k0, ci, cd, r, sync=False)
+
     def one_search(sp, q=None, outs=None):
-        """The whole step: IVF-PQ search for k0 candidates (+ merge across ranks) and, with a
-        refine ratio above 1, exact re-ranking down to k."""
+        """The whole step: the search above and, with a refine ratio above 1, exact re-ranking to k."""
         q = queries if q is None else q
         out_i, out_d = outs if outs is not None else (out_i0, out_d0)
-        if world > 1:
-            d, i = mg.search(sp, index, q, k0, True, None, res, sync=False)
-        else:
-            d, i = ivf_pq.search(sp, index, q, k0, cand_i, cand_d, res, sync=False)
+        d, i = ann_search(sp, q, res, comm, cand_i, cand_d)
         if refining:
-            d, i = refine(dataset, q, i, k=k, metric="sqeuclidean", indices=out_i, distances=out_d,
+            d, i = refine(dataset, q, i, k=k, metric=metric, indices=out_i, distances=out_d,
                           resources=res, sync=False)
         elif outs is not None:
             out_i.copy_(i)
@@ -397,107 +557,140 @@ def run_ours(args):
             t = torch.tensor([ms], device=device)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             ms = t.item()
-        return ms / steps
+        return ms / steps, t_host / steps * 1e3
 
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
 
-    # ---- recall / QPS sweep over n_probes ----
-    sweep = []
-    for p in probes:
+    # ---- recall / QPS sweep over n_probes (the configuration's list, plus smaller values that show
+    # where recall starts to fall: on this generator it saturates early) ----
+    def sweep_entry(p):
         sp = make_sp(p)
         d, i = one_search(sp)
         torch.cuda.synchronize()
         rec = recall_at_k(i, truth)
-        ms = timed(lambda: one_search(sp), max(2, min(args.steps, 5)), 2)
-        sweep.append({"n_probes": p, "recall_at_10": round(rec, 4), "qps": round(nq / ms * 1e3, 1),
-                      "ms_per_batch": round(ms, 3)})
-        log(f"[bench] n_probes={p}: recall@10={rec:.4f}  {nq / ms * 1e3:,.0f} q/s")
-    ok = [s for s in sweep if s["recall_at_10"] >= 0.95]
+        rec_ann = recall_at_k(cand_i[:, :k], truth) if refining else rec
+        ms, _ = timed(lambda: one_search(sp), max(2, min(args.steps, 5)), 2)
+        log(f"[bench] n_probes={p}: recall@{k}={rec:.4f} (without refinement {rec_ann:.4f})  {nq / ms * 1e3:,.0f} q/s")
+        return {"n_probes": p, f"recall_at_{k}": round(rec, 4), "recall_without_refinement": round(rec_ann, 4),
+                "qps": round(nq / ms * 1e3, 1), "ms_per_batch": round(ms, 3)}
+
+    sweep = [sweep_entry(p) for p in probes]
+    below = [] if (args.probes or args.no_e2e) else [sweep_entry(p) for p in (1, 2, 5, 10) if p < min(probes)]
+    rkey = f"recall_at_{k}"
+    ok = [s for s in sweep if s[rkey] >= 0.95]
     if ok:
         chosen, target_met = ok[0], True
     else:
-        best = max(s["recall_at_10"] for s in sweep)
-        chosen = [s for s in sweep if s["recall_at_10"] >= best - 0.005][0]
+        best = max(s[rkey] for s in sweep)
+        chosen = [s for s in sweep if s[rkey] >= best - 0.005][0]
         target_met = False
     p_star = chosen["n_probes"]
     sp = make_sp(p_star)
+
+    # ---- multi-GPU parity: the merged result against the single-GPU search of the same index ----
+    mg_parity = None
+    if world > 1 and rank == 0:
+        ref = np.load(single_result_path(fx["dir"], p_star, k0)) if os.path.exists(
+            single_result_path(fx["dir"], p_star, k0)) else None
+    if world > 1:
+        d, i = ann_search(sp, queries, res, comm, cand_i, cand_d)
+        torch.cuda.synchronize()
+        if rank == 0 and ref is not None:
+            # equal distances may come out in another order across parts: tolerance 0 on the values
+            mg_parity = parity_record(d.cpu().numpy(), i.cpu().numpy(), ref["d"], ref["i"], 0.0)
+            mg_parity["against"] = "single-GPU search of the same index file, same queries, same n_probes"
+            log(f"[bench] multi-GPU parity: {mg_parity}")
 
     # ---- the timed region: K steps, device-resident queries ----
     L.check(lib.cuvsB200StatsEnable(res.handle, True))
     stats = L.SearchStats()
     one_search(sp)
     L.check(lib.cuvsB200StatsGet(res.handle, C.byref(stats), True))
+    if comm is not None:
+        comm.stats(reset=True)
     launches_before = stats.launches
-    ms_step = timed(lambda: one_search(sp), args.steps, args.warmup)
+    ms_step, host_ms = timed(lambda: one_search(sp), args.steps, args.warmup)
     ms_single = ms_step
-    # Throughput mode: two batches in flight per GPU, each on its own stream and resources handle
-    # (the serving pattern of the reference's benchmark in throughput mode: several host threads, one
-    # stream each), so that the small kernels (and, with several GPUs, the NCCL exchanges) of one batch
-    # fill the tails of the other's large kernels.
-    # The per-kernel figures above (stage times, roofline, launches) come from the single-stream pass.
-    n_streams = 1
-    if True:
-        from cuvs_b200.common import Resources
-        n_streams = 2
-        lanes = []
-        for _ in range(n_streams):
-            lanes.append(dict(stream=torch.cuda.Stream(device), res=Resources(),
-                              ci=torch.empty_like(cand_i), cd=torch.empty_like(cand_d),
-                              oi=torch.empty_like(out_i0), od=torch.empty_like(out_d0)))
-        lane_state = {"i": 0}
-
-        def lane_search(q, outs=None, stream_wait=None):
-            """One step on the next lane; returns the lane (its stream carries the step)."""
-            lane = lanes[lane_state["i"] % n_streams]
-            lane_state["i"] += 1
-            with torch.cuda.stream(lane["stream"]):
-                if stream_wait is not None:
-                    for ev in stream_wait:
-                        lane["stream"].wait_event(ev)
-                lane["res"].use_current_stream()
-                if world > 1:
-                    d, i = mg.search(sp, index, q, k0, True, None, lane["res"], sync=False)
-                else:
-                    d, i = ivf_pq.search(sp, index, q, k0, lane["ci"], lane["cd"], lane["res"], sync=False)
-                oi, od = outs if outs is not None else (lane["oi"], lane["od"])
-                if refining:
-                    refine(dataset, q, i, k=k, metric="sqeuclidean", indices=oi, distances=od,
-                           resources=lane["res"], sync=False)
-                elif outs is not None:
-                    oi.copy_(i)
-                    od.copy_(d)
-            return lane
-
-        def lanes_join():
-            main = torch.cuda.current_stream()
-            for lane in lanes:
-                main.wait_stream(lane["stream"])
-
-        for lane in lanes:
-            lane["stream"].wait_stream(torch.cuda.current_stream())
-        ms_step = timed(lambda: lane_search(queries), args.steps, args.warmup + n_streams, tail=lanes_join)
-        log(f"[bench] {n_streams} batches in flight: {ms_step:.4f} ms/step (one at a time: {ms_single:.4f})")
     L.check(lib.cuvsB200StatsGet(res.handle, C.byref(stats), True))
     n_calls = args.steps + args.warmup
     gpu_launches = int(round((stats.launches - launches_before) * args.steps / n_calls))
-    scan_ms = stats.scan_ms / max(1, stats.batches)
+    nb = max(1, stats.batches)
+    scan_ms = stats.scan_ms / nb
     n_pieces = -(-wl["pq_dim"] // (128 // wl["pq_bits"]))
-    bytes_scan = stats.scan_groups / max(1, stats.batches) * n_pieces * 512
-    bytes_unique = stats.unique_groups / max(1, stats.batches) * n_pieces * 512
-    stage = {k2: round(getattr(stats, k2) / max(1, stats.batches), 4)
-             for k2 in ("prep_ms", "coarse_ms", "sort_ms", "scan_ms", "merge_ms")}
+    bytes_scan = stats.scan_groups / nb * n_pieces * 512
+    bytes_unique = stats.unique_groups / nb * n_pieces * 512
+    unique_groups = stats.unique_groups / nb
+    if comm is None:
+        stage = {k2: round(getattr(stats, k2) / nb, 4)
+                 for k2 in ("prep_ms", "coarse_ms", "sort_ms", "scan_ms", "merge_ms")}
+    else:
+        # the one-call step of a rank: its own five stages; the scan stage contains the fine search
+        # whose kernel time is reported beside it
+        cs = comm.stats(reset=True)
+        stage = {"select_probes_slice_ms": round(cs["select_ms"], 4),
+                 "allgather_probes_ms": round(cs["gather_probes_ms"], 4),
+                 "scan_owned_lists_ms": round(cs["scan_ms"], 4), "scan_kernel_ms": round(scan_ms, 4),
+                 "allgather_results_ms": round(cs["gather_results_ms"], 4),
+                 "merge_parts_ms": round(cs["merge_ms"], 4)}
+    stage["host_issue_ms"] = round(host_ms, 4)
     L.check(lib.cuvsB200StatsEnable(res.handle, False))
+    ms_ann_only = None
     if refining:
-        stage["refine_ms"] = round(timed(lambda: refine(dataset, queries, cand_i, k=k, indices=out_i0,
-                                                        distances=out_d0, resources=res, sync=False),
-                                         args.steps, 1), 4)
+        t, _ = timed(lambda: refine(dataset, queries, cand_i, k=k, metric=metric, indices=out_i0,
+                                    distances=out_d0, resources=res, sync=False), args.steps, 1)
+        stage["refine_ms"] = round(t, 4)
+        ms_ann_only, _ = timed(lambda: ann_search(sp, queries, res, comm, cand_i, cand_d), args.steps, 2)
 
-    # ---- the configuration's small batches (1 and 100 queries): latency per call, synchronised ----
+    # Throughput mode: two batches in flight per GPU, each on its own stream, resources handle and (with
+    # several GPUs) communicator -- the serving pattern of the reference's benchmark in throughput
+    # mode: several host threads, one stream each -- so that the small kernels and the exchanges of one
+    # batch fill the tails of the other's large kernels.  The per-kernel figures above (stage times,
+    # roofline, launches) come from the single-stream pass.
+    n_streams = 2
+    lanes = []
+    for _ in range(n_streams):
+        r = Resources()
+        lanes.append(dict(stream=torch.cuda.Stream(device), res=r,
+                          comm=mg.RankComm(None, r) if world > 1 else None,
+                          ci=torch.empty_like(cand_i), cd=torch.empty_like(cand_d),
+                          oi=torch.empty_like(out_i0), od=torch.empty_like(out_d0)))
+    lane_state = {"i": 0}
+
+    def lane_search(q, outs=None, stream_wait=None):
+        """One step on the next lane; returns the lane (its stream carries the step)."""
+        lane = lanes[lane_state["i"] % n_streams]
+        lane_state["i"] += 1
+        with torch.cuda.stream(lane["stream"]):
+            if stream_wait is not None:
+                for ev in stream_wait:
+                    lane["stream"].wait_event(ev)
+            lane["res"].use_current_stream()
+            d, i = ann_search(sp, q, lane["res"], lane["comm"], lane["ci"], lane["cd"])
+            oi, od = outs if outs is not None else (lane["oi"], lane["od"])
+            if refining:
+                refine(dataset, q, i, k=k, metric=metric, indices=oi, distances=od,
+                       resources=lane["res"], sync=False)
+            elif outs is not None:
+                oi.copy_(i)
+                od.copy_(d)
+        return lane
+
+    def lanes_join():
+        main = torch.cuda.current_stream()
+        for lane in lanes:
+            main.wait_stream(lane["stream"])
+
+    for lane in lanes:
+        lane["stream"].wait_stream(torch.cuda.current_stream())
+    ms_step, _ = timed(lambda: lane_search(queries), args.steps, args.warmup + n_streams, tail=lanes_join)
+    log(f"[bench] {n_streams} batches in flight: {ms_step:.4f} ms/step (one at a time: {ms_single:.4f})")
+
+    # ---- the configuration's small batches: latency per call, synchronised ----
     small = []
     if not args.no_e2e:
-        for b in (1, 100):
+        for b in wl["batches"]:
             if b >= nq:
                 continue
             qb = queries[:b].contiguous()
@@ -507,12 +700,9 @@ def run_ours(args):
             ob_d = torch.empty((b, k), dtype=torch.float32, device=device)
 
             def small_step():
-                if world > 1:
-                    d, i = mg.search(sp, index, qb, k0, True, None, res, sync=False)
-                else:
-                    d, i = ivf_pq.search(sp, index, qb, k0, cb_i, cb_d, res, sync=False)
+                d, i = ann_search(sp, qb, res, comm, cb_i, cb_d)
                 if refining:
-                    refine(dataset, qb, i, k=k, metric="sqeuclidean", indices=ob_i, distances=ob_d,
+                    refine(dataset, qb, i, k=k, metric=metric, indices=ob_i, distances=ob_d,
                            resources=res, sync=False)
                 torch.cuda.synchronize()      # latency mode: the caller waits for every batch
 
@@ -546,23 +736,15 @@ def run_ours(args):
     def e2e_step():
         s = e2e_state["step"]
         slot = s & 1
-        main = torch.cuda.current_stream()
         with torch.cuda.stream(s_in):
             if s >= 2:
                 s_in.wait_event(ev_done[slot])       # the search two steps back has read this buffer
             q_dev[slot].copy_(q_host, non_blocking=True)
             ev_in[slot].record(s_in)
-        if n_streams > 1:
-            # the search runs on its lane's stream, behind this step's input copy and the result
-            # copy that last used the output buffer
-            lane = lane_search(q_dev[slot], o_dev[slot], [ev_in[slot]] + ([ev_out[slot]] if s >= 2 else []))
-            ev_done[slot].record(lane["stream"])
-        else:
-            main.wait_event(ev_in[slot])
-            if s >= 2:
-                main.wait_event(ev_out[slot])        # its results have left this output buffer
-            one_search(sp, q_dev[slot], o_dev[slot])
-            ev_done[slot].record(main)
+        # the search runs on its lane's stream, behind this step's input copy and the result copy that
+        # last used the output buffer
+        lane = lane_search(q_dev[slot], o_dev[slot], [ev_in[slot]] + ([ev_out[slot]] if s >= 2 else []))
+        ev_done[slot].record(lane["stream"])
         with torch.cuda.stream(s_out):
             s_out.wait_event(ev_done[slot])
             i_host[slot].copy_(o_dev[slot][0], non_blocking=True)
@@ -574,13 +756,12 @@ def run_ours(args):
         main = torch.cuda.current_stream()
         for ev in ev_out:
             main.wait_event(ev)
-        if n_streams > 1:
-            lanes_join()
+        lanes_join()
 
     if args.no_e2e:
         ms_e2e, e2e_rec = float("nan"), float("nan")
     else:
-        ms_e2e = timed(e2e_step, args.steps, args.warmup, tail=e2e_tail)
+        ms_e2e, _ = timed(e2e_step, args.steps, args.warmup, tail=e2e_tail)
         last = (e2e_state["step"] - 1) & 1
         e2e_rec = recall_at_k(i_host[last].to(device), truth)
     clocks = sampler.stop() if rank == 0 else None
@@ -593,29 +774,37 @@ def run_ours(args):
 
     peak, peak_kind = hbm_peak()
     achieved = bytes_scan / (scan_ms * 1e-3) / 1e9 if scan_ms > 0 else None
-    traffic = int(DRAM_BYTES_PER_UNIQUE_GROUP * stats.unique_groups / max(1, stats.batches))
+    traffic = int(DRAM_BYTES_PER_UNIQUE_GROUP * unique_groups) if wl["gen"] == "deep" else None
+    config = {"workload": wl["name"], "n_rows": wl["n_rows"], "dim": wl["dim"],
+              "n_lists": wl["n_lists"], "pq_dim": wl["pq_dim"], "pq_bits": wl["pq_bits"], "metric": metric,
+              "k": k, "recall_k": k, "batch": nq, "n_probes": p_star, "lut_dtype": wl["lut"],
+              "internal_distance_dtype": wl["internal"], "refine_ratio": wl["refine_ratio"],
+              rkey: chosen[rkey], "recall_without_refinement": chosen["recall_without_refinement"],
+              "recall_target_met": target_met, "sweep": sweep, "sweep_below_the_configured_probes": below,
+              "recall_note": "recall does not depend on n_probes on this generator (queries fall next to their "
+                             "component's lists): the operating point is the first configured n_probes; what "
+                             "lifts recall over 0.95 is the exact re-ranking" if refining else None,
+              "small_batches": small,
+              "parallelism": f"list-sharded x{world}, one process per GPU, one C++ call per batch" if world > 1
+              else "single GPU",
+              "batches_in_flight": n_streams, "ms_per_step_one_batch_in_flight": round(ms_single, 4),
+              "ms_per_step_without_refinement": round(ms_ann_only, 4) if ms_ann_only else round(ms_single, 4),
+              "l2": f"inputs larger than L2: {wl['n_rows'] * n_pieces * 16 // 1_000_000} MB of codes per pass",
+              "stage_ms": stage, "build_s": fx.get("build_s")}
     line = {
         "metric": METRIC, "value": round(nq / ms_step * 1e3, 1), "unit": "queries/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(ms_step, 4), "higher_is_better": True,
-        "scaling": "strong" if world > 1 else "weak", "vs_baseline": None,
+        # the index and the query batch are the same at every number of GPUs
+        "scaling": "strong", "vs_baseline": None,
         "dtype": "f32" if wl["lut"] != "uint8" else "f32 (8-bit float look-up table)",
         "data": "synthetic",
-        "config": {"workload": wl["name"], "n_rows": wl["n_rows"], "dim": wl["dim"],
-                   "n_lists": wl["n_lists"], "pq_dim": wl["pq_dim"], "pq_bits": wl["pq_bits"],
-                   "k": k, "recall_k": k, "batch": nq, "n_probes": p_star, "lut_dtype": wl["lut"],
-                   "internal_distance_dtype": wl["internal"], "refine_ratio": wl["refine_ratio"],
-                   "recall_at_10": chosen["recall_at_10"],
-                   "recall_target_met": target_met, "sweep": sweep, "small_batches": small,
-                   "parallelism": f"list-sharded x{world}" if world > 1 else "single GPU",
-                   "batches_in_flight": n_streams, "ms_per_step_one_batch_in_flight": round(ms_single, 4),
-                   "l2": f"inputs larger than L2: {wl['n_rows'] * n_pieces * 16 // 1_000_000} MB of codes per pass",
-                   "stage_ms": stage, "build_s": fx.get("build_s")},
+        "config": config,
         "e2e": {"value": round(nq / ms_e2e * 1e3, 1), "unit": "queries/s",
                 "h2d_bytes_per_step": int(q_host.numel() * q_host.element_size()),
                 "d2h_bytes_per_step": int(nq * k * 12), "ms_per_step": round(ms_e2e, 4),
                 "copies": "every step, double-buffered on side streams (overlap the neighbouring steps)",
-                "recall_at_10": round(e2e_rec, 4)},
+                rkey: round(e2e_rec, 4)},
         "gpu_launches": gpu_launches,
         "clocks": clocks,
         "roofline": {"bound": "hbm", "kernel": "scan_kernel (LUT build + code scan + top-k)",
@@ -626,15 +815,41 @@ def run_ours(args):
                      "unique_bytes_per_launch": int(bytes_unique),
                      "kernel_ms": round(scan_ms, 4)},
     }
+    if mg_parity is not None:
+        line["mg_parity"] = mg_parity
+    failed = mg_parity is not None and not mg_parity["passed"]
     if world == 1 and not args.no_cpu:
-        cb, _, _ = cpu_baseline(fx["index_path"], queries.cpu().numpy(), wl, p_star,
-                                dataset_np=dataset.cpu().numpy() if refining else None)
-        cb["value"] = round(cb["value"], 1)
-        line["cpu_baseline"] = cb
+        index_gb = os.path.getsize(fx["index_path"]) / 1e9
+        if index_gb > 3.0:
+            line["cpu_baseline"] = {"value": None, "unit": "queries/s", "cores": os.cpu_count(), "kind": "port",
+                                    "sample": f"skipped: the oracle would have to load a {index_gb:.1f} GB index "
+                                              "through Python; the CPU leg runs on --config 1 and 2"}
+        else:
+            q_np = queries.cpu().numpy()
+            cb, _, n_cpu, found = cpu_baseline(fx["index_path"], q_np, wl, p_star,
+                                               dataset_np=dataset.cpu().numpy() if refining else None)
+            cb["value"] = round(cb["value"], 1)
+            line["cpu_baseline"] = cb
+            # id-level parity of the timed configuration: the GPU's candidates (before re-ranking)
+            # for the CPU leg's sample against the oracle's
+            d, i = ivf_pq.search(sp, index, queries[:n_cpu].contiguous(), k0, resources=res)
+            tol = 1e-5 if wl["lut"] == "float32" else 1e-2
+            par = parity_record(d.cpu().numpy(), i.cpu().numpy(), found["d"][:n_cpu], found["i"][:n_cpu], tol)
+            par["against"] = "CPU oracle, same index file, same queries, before re-ranking"
+            line["parity"] = par
+            log(f"[bench] parity: {par}")
+            failed = failed or not par["passed"]
+    if world == 1 and args.config == 2 and not args.rows and not args.no_e2e and args.workload == "deep":
+        del index
+        torch.cuda.empty_cache()
+        line["config"]["long_lists"] = long_list_record(res, device, peak, args.steps)
     emit(line)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+    if failed:
+        log("[bench] PARITY FAILED")
+        sys.exit(3)
 
 
 def run_reference(args):
@@ -646,23 +861,26 @@ def run_reference(args):
     import torch
     if not torch.cuda.is_available():
         emit({"impl": "reference",
-              "unavailable": "the 10M-vector index fixture is built on the GPU; no GPU here"})
+              "unavailable": "the index fixture is built on the GPU; no GPU here"})
         return
     torch.cuda.set_device(0)
     k = wl["k"]
-    k0 = int(wl["refine_ratio"] * k) if wl["refine_ratio"] > 1 else k
+    k0 = k0_of(wl)
     fx = prepare_fixture(wl, torch.device("cuda", 0), need_dataset=k0 > k)
+    if os.path.getsize(fx["index_path"]) / 1e9 > 3.0:
+        emit({"impl": "reference",
+              "unavailable": "the CPU port loads the index through Python; this configuration's index is too large for that"})
+        return
     # operating point: the same rule as the GPU arm, evaluated with the GPU search (fixture work)
     from cuvs_b200 import ivf_pq, refine
     index = ivf_pq.load(fx["index_path"])
-    lut_dt = {"float32": np.float32, "float16": np.float16, "uint8": np.uint8}[wl["lut"]]
     recs = []
     for p in wl["probes"]:
-        d, i = ivf_pq.search(ivf_pq.SearchParams(n_probes=p, lut_dtype=lut_dt,
+        d, i = ivf_pq.search(ivf_pq.SearchParams(n_probes=p, lut_dtype=lut_np(wl),
                                                  max_internal_batch_size=fx["queries"].shape[0]),
                              index, fx["queries"], k0)
         if k0 > k:
-            d, i = refine(fx["dataset"], fx["queries"], i, k=k)
+            d, i = refine(fx["dataset"], fx["queries"], i, k=k, metric=wl["metric"])
         recs.append((p, recall_at_k(i, fx["truth"])))
     ok = [p for p, r in recs if r >= 0.95]
     best = max(r for _, r in recs)
@@ -671,16 +889,17 @@ def run_reference(args):
     dataset_np = fx["dataset"].cpu().numpy() if k0 > k else None
     fx.pop("dataset", None)
     torch.cuda.empty_cache()
-    cb, dt, n = cpu_baseline(fx["index_path"], fx["queries"].cpu().numpy(), wl, p_star,
-                             budget_s=8.0, steps=args.steps, warmup=args.warmup, dataset_np=dataset_np)
+    cb, dt, n, _ = cpu_baseline(fx["index_path"], fx["queries"].cpu().numpy(), wl, p_star,
+                                budget_s=8.0, steps=args.steps, warmup=args.warmup, dataset_np=dataset_np)
     line = {"impl": "reference", "metric": METRIC, "value": round(cb["value"], 1), "unit": "queries/s",
             "n_gpus": int(os.environ.get("WORLD_SIZE", "1")), "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": round(dt * 1e3, 3), "higher_is_better": True, "scaling": "weak",
+            "ms_per_step": round(dt * 1e3, 3), "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": wl["name"], "n_rows": wl["n_rows"], "dim": wl["dim"],
                        "n_lists": wl["n_lists"], "pq_dim": wl["pq_dim"], "pq_bits": wl["pq_bits"],
-                       "k": wl["k"], "batch": n, "n_probes": p_star, "lut_dtype": wl["lut"],
-                       "internal_distance_dtype": wl["internal"], "refine_ratio": wl["refine_ratio"]},
+                       "metric": wl["metric"], "k": wl["k"], "batch": n, "n_probes": p_star,
+                       "lut_dtype": wl["lut"], "internal_distance_dtype": wl["internal"],
+                       "refine_ratio": wl["refine_ratio"]},
             "cpu_baseline": dict(cb, value=round(cb["value"], 1)),
             "e2e": {"value": round(cb["value"], 1), "unit": "queries/s", "h2d_bytes_per_step": 0,
                     "d2h_bytes_per_step": 0},
@@ -711,8 +930,10 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--rows", type=int, default=0, help="shrink the dataset (testing only)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--config", type=int, default=2, choices=[1, 2, 3, 4, 5],
+                    help="which of the five benchmark configurations to run (default: 2, the headline)")
     ap.add_argument("--workload", default="deep", choices=["deep", "sift"],
-                    help="deep = the headline configuration; sift = long-list integer data (scan roofline)")
+                    help="sift = a 20 M-row slice of configuration 3 (older spelling; see --config)")
     ap.add_argument("--probes", default="", help="comma-separated n_probes to sweep (default: the workload's)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end leg (profiling runs)")
     ap.add_argument("--refine-ratio", type=float, default=None,
