@@ -1197,7 +1197,7 @@ void build_any(raft::resources& res, const index_params& params, const void* dat
     res.launches++;
     const size_t smem = size_t(book) * len * 8 + size_t(book) * 4;
     CUVS_EXPECTS(smem <= 200 * 1024, "pq_len = %u is too large for codebook training", len);
-    CUDA_TRY(cudaFuncSetAttribute(train_codebooks_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+    ensure_dynamic_smem(reinterpret_cast<const void*>(train_codebooks_kernel), smem);
     const int pq_iters = 25;
     if (!per_cluster) {
       train_codebooks_kernel<<<pq_dim, 1024, smem, stream>>>(resid.data(), uint32_t(n_pq), rot_dim, pq_dim,

@@ -60,20 +60,11 @@ CUVS_HD constexpr T round_up(T a, T b)
   return ceildiv(a, b) * b;
 }
 
-// Raises a kernel's limit of dynamic shared memory to `bytes` on the current device unless this thread
-// has already raised it that far there (the attribute belongs to the device's context, so a process
-// that drives several devices needs it once per device).
-inline void ensure_dynamic_smem(const void* kernel, size_t bytes)
-{
-  static thread_local std::map<std::pair<const void*, int>, size_t> done;
-  int dev = 0;
-  CUDA_TRY(cudaGetDevice(&dev));
-  size_t& have = done[{kernel, dev}];
-  if (bytes > have) {
-    CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(bytes)));
-    have = bytes;
-  }
-}
+// Raises a kernel's limit of dynamic shared memory to `bytes` on the current device unless it has
+// already been raised that far there.  The attribute belongs to the device's context -- one value for
+// all threads of the process, one per device -- and setting it again LOWERS it if the new value is
+// smaller, so the record of what has been set is process-wide and the limit only ever grows.
+void ensure_dynamic_smem(const void* kernel, size_t bytes);
 
 // One grow-only device buffer carved into aligned slices per call.
 class workspace {

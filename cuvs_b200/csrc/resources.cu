@@ -1,6 +1,22 @@
 #include "common.hpp"
 
+#include <mutex>
+
 namespace cuvs_b200 {
+
+void ensure_dynamic_smem(const void* kernel, size_t bytes)
+{
+  static std::mutex lock;
+  static std::map<std::pair<const void*, int>, size_t> done;
+  int dev = 0;
+  CUDA_TRY(cudaGetDevice(&dev));
+  std::lock_guard<std::mutex> guard(lock);
+  size_t& have = done[{kernel, dev}];
+  if (bytes > have) {
+    CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(bytes)));
+    have = bytes;
+  }
+}
 
 resources::resources()
 {
