@@ -59,6 +59,8 @@ struct scan_params {
   // codebook in tensor memory: columns allocated (0 = not used), byte offset in shared memory of
   // the word that receives the allocation's address
   uint32_t tmem_cols, tmem_slot_off;
+  // host only: whether the launcher may pick an instantiation made for this exact shape
+  int allow_fixed_shape;
 };
 
 enum { LUT_F32 = 0, LUT_F16 = 1, LUT_FP8 = 2 };
@@ -397,10 +399,14 @@ __device__ __forceinline__ void fill_codebook_tmem(uint32_t tmem_lane_a, const f
 // miss L1 (the shared-memory carve-out leaves it almost no room): 1.57 ms against 1.50 ms per launch
 // on the 10 M-row workload.
 constexpr int kTmemLoadCols = 8;
-template <int PqBits, int LutKind, bool IsIP, int LEN>
+template <int PqBits, int LutKind, bool IsIP, int LEN, int PQD = 0, int GT = 0>
 __device__ __forceinline__ void build_lut_tmem(uint32_t tmem_lane_a, uint32_t base_a, uint32_t lut_a,
-                                               uint32_t pq_dim, uint32_t gt, uint32_t gthreads)
+                                               uint32_t pq_dim_rt, uint32_t gt, uint32_t gthreads_rt)
 {
+  // PQD / GT > 0 fix pq_dim and the threads of a group at compile time (the benchmark shapes): every
+  // trip count, stride and offset below is then a constant and the loop is straight-line code
+  const uint32_t pq_dim   = PQD > 0 ? uint32_t(PQD) : pq_dim_rt;
+  const uint32_t gthreads = GT > 0 ? uint32_t(GT) : gthreads_rt;
   constexpr uint32_t kBook  = 1u << PqBits;
   constexpr uint32_t kUPJ   = kBook / 4;
   constexpr uint32_t kJPerM = 128u / kUPJ;
@@ -472,6 +478,31 @@ __device__ __forceinline__ void build_lut_tmem(uint32_t tmem_lane_a, uint32_t ba
     bd += bd_step;
     out += out_step;
   };
+  // every thread runs the same number of subspaces and none falls beyond pq_dim: no checks at all
+  constexpr bool kUniform = PQD > 0 && GT > 0 && (uint32_t(PQD) % ((GT > 0 ? uint32_t(GT) : kUPJ) / kUPJ) == 0u);
+  if constexpr (kUniform) {
+    constexpr uint32_t kIters = uint32_t(PQD) / (uint32_t(GT) / kUPJ);
+    static_assert(kIters % kPerLoad == 0, "whole tensor-memory loads only");
+#pragma unroll
+    for (uint32_t i = 0; i < kIters; i += kPerLoad) {
+      uint32_t c[kLoad];
+      tmem_ld<kLoad>(taddr + i / kPerLoad * uint32_t(kLoad), c);
+      tmem_wait_ld();
+      entry(c, std::integral_constant<int, 0>{});
+      advance();
+      if constexpr (kPerLoad >= 2) {
+        entry(c, std::integral_constant<int, 1>{});
+        advance();
+      }
+      if constexpr (kPerLoad >= 4) {
+        entry(c, std::integral_constant<int, 2>{});
+        advance();
+        entry(c, std::integral_constant<int, 3>{});
+        advance();
+      }
+    }
+    return;
+  }
   // Whole loads first, without per-subspace checks where the warp shares its subspace; then the rest.
   const uint32_t n_whole = kWarpSameJ ? (n_iter / kPerLoad) * kPerLoad : 0u;
   uint32_t i             = 0;
@@ -620,16 +651,23 @@ __device__ __forceinline__ void score_piece(accum<LutKind, OutHalf, IsIP>& acc, 
   score_codes<PqBits, LutKind, OutHalf, IsIP, Full, 0>(acc, w, row_a, n_valid);
 }
 
-template <int PqBits, int LutKind, bool OutHalf, bool IsIP, int KPL>
+// PQD, GT, LEN > 0: pq_dim, threads per group and pq_len fixed at compile time, codebook in tensor
+// memory (the shapes of the benchmark configurations; chosen by the launcher when the plan matches).
+template <int PqBits, int LutKind, bool OutHalf, bool IsIP, int KPL, int PQD = 0, int GT = 0, int LEN = 0>
 __global__ void __launch_bounds__(1024, 1) scan_kernel(const scan_params p)
 {
   using lut_t               = typename lut_elem<LutKind>::type;
   constexpr uint32_t kBook  = 1u << PqBits;
   constexpr int kPerPiece   = 128 / PqBits;
+  constexpr bool kFixed     = PQD > 0;
+  static_assert(!kFixed || (GT > 0 && LEN > 0), "a fixed shape fixes all three");
   extern __shared__ __align__(16) uint8_t smem[];
 
   const int tid      = threadIdx.x;
-  const int gthreads = int(p.group_threads);
+  const int gthreads = kFixed ? GT : int(p.group_threads);
+  const uint32_t pq_dim   = kFixed ? uint32_t(PQD) : p.pq_dim;
+  const uint32_t n_pieces = kFixed ? uint32_t((PQD + kPerPiece - 1) / kPerPiece) : p.n_pieces;
+  const uint32_t rot_dim  = kFixed ? uint32_t(PQD * LEN) : p.rot_dim;
   const int g        = tid / gthreads;
   const int gt       = tid - g * gthreads;
   const int gw       = gt >> 5;
@@ -667,10 +705,14 @@ __global__ void __launch_bounds__(1024, 1) scan_kernel(const scan_params p)
       // lane L of tensor memory is written by the threads with tid % 128 == L
       const uint32_t lane128 = uint32_t(tid) & 127u, part = uint32_t(tid) >> 7, n_parts = blockDim.x >> 7;
       const uint32_t lane_a  = tmem_base + ((lane128 & ~31u) << 16);
-      switch (p.pq_len) {
-        case 1: fill_codebook_tmem<PqBits, 1>(lane_a, p.pq_centers, p.pq_dim, lane128, p.group_threads / 128u, part, n_parts); break;
-        case 2: fill_codebook_tmem<PqBits, 2>(lane_a, p.pq_centers, p.pq_dim, lane128, p.group_threads / 128u, part, n_parts); break;
-        default: fill_codebook_tmem<PqBits, 4>(lane_a, p.pq_centers, p.pq_dim, lane128, p.group_threads / 128u, part, n_parts); break;
+      if constexpr (kFixed) {
+        fill_codebook_tmem<PqBits, LEN>(lane_a, p.pq_centers, pq_dim, lane128, uint32_t(gthreads) / 128u, part, n_parts);
+      } else {
+        switch (p.pq_len) {
+          case 1: fill_codebook_tmem<PqBits, 1>(lane_a, p.pq_centers, p.pq_dim, lane128, p.group_threads / 128u, part, n_parts); break;
+          case 2: fill_codebook_tmem<PqBits, 2>(lane_a, p.pq_centers, p.pq_dim, lane128, p.group_threads / 128u, part, n_parts); break;
+          default: fill_codebook_tmem<PqBits, 4>(lane_a, p.pq_centers, p.pq_dim, lane128, p.group_threads / 128u, part, n_parts); break;
+        }
       }
     }
     tmem_fence_before();
@@ -686,7 +728,7 @@ __global__ void __launch_bounds__(1024, 1) scan_kernel(const scan_params p)
   // this warp's window into tensor memory: lanes 32 * (warp % 4) .. + 31
   const uint32_t tmem_lane_a = tmem_base + (((uint32_t(tid) >> 5) & 3u) << 21);
 
-  const uint32_t len     = p.pq_len;
+  const uint32_t len     = kFixed ? uint32_t(LEN) : p.pq_len;
   const uint32_t k       = p.k;
   constexpr bool kStoreAll = KPL == 0;  // k too large for registers: write every score instead
   warp_topk<(KPL > 0 ? KPL : 1)> queue;
@@ -725,10 +767,10 @@ __global__ void __launch_bounds__(1024, 1) scan_kernel(const scan_params p)
     // ---- base diff ----
     if (gt == 0) { sts_b32(s_thr_a(), *reinterpret_cast<volatile uint32_t*>(p.query_kth + q)); }
     {
-      const float* rq = p.rot_q + size_t(q) * p.rot_dim;
-      const float* c  = p.centers_rot + size_t(label) * p.rot_dim;
+      const float* rq = p.rot_q + size_t(q) * rot_dim;
+      const float* c  = p.centers_rot + size_t(label) * rot_dim;
       // stored pre-duplicated for the packed arithmetic: L2 (d, d); inner product (-q, -q, q*c, q*c)
-      for (uint32_t i = gt; i < p.rot_dim; i += gthreads) {
+      for (uint32_t i = gt; i < rot_dim; i += gthreads) {
         if constexpr (!IsIP) {
           const float d = __fsub_rn(rq[i], __ldg(c + i));
           sts_b64(s_base_a() + 8u * i, pack2(d, d));
@@ -745,13 +787,15 @@ __global__ void __launch_bounds__(1024, 1) scan_kernel(const scan_params p)
     // (a load into registers here would hold four of them through the build); afterwards each piece
     // is requested one piece ahead of its use.
     const uint32_t n_groups = (n + 31u) >> 5;
-    const uint4* src = reinterpret_cast<const uint4*>(p.codes + first_row * size_t(p.n_pieces) * 16u) +
-                       size_t(gw) * p.n_pieces * 32u + lane;
+    const uint4* src = reinterpret_cast<const uint4*>(p.codes + first_row * size_t(n_pieces) * 16u) +
+                       size_t(gw) * n_pieces * 32u + lane;
     uint4 nxt = make_uint4(0u, 0u, 0u, 0u);
     if (uint32_t(gw) < n_groups) { asm volatile("prefetch.global.L2 [%0];" ::"l"(src)); }
 
     // ---- LUT ----
-    if (p.tmem_cols) {
+    if constexpr (kFixed) {
+      build_lut_tmem<PqBits, LutKind, IsIP, LEN, PQD, GT>(tmem_lane_a, s_base_a(), lut_a, pq_dim, gt, gthreads);
+    } else if (p.tmem_cols) {
       const uint32_t base_a = s_base_a();
       switch (len) {
         case 1: build_lut_tmem<PqBits, LutKind, IsIP, 1>(tmem_lane_a, base_a, lut_a, p.pq_dim, gt, gthreads); break;
@@ -813,24 +857,45 @@ __global__ void __launch_bounds__(1024, 1) scan_kernel(const scan_params p)
     if (uint32_t(gw) < n_groups) { nxt = __ldg(src); }
     {
       const uint32_t lut_base_a   = lut_a;
-      const uint32_t group_stride = uint32_t(n_gwarps) * p.n_pieces * 32u;  // in 16-byte pieces
+      const uint32_t group_stride = uint32_t(n_gwarps) * n_pieces * 32u;  // in 16-byte pieces
       constexpr uint32_t kPieceLutBytes = uint32_t(kPerPiece) * kBook * uint32_t(sizeof(lut_t));
       for (uint32_t gi = gw; gi < n_groups; gi += n_gwarps, src += group_stride) {
         accum<LutKind, OutHalf, IsIP> acc;
         acc.init();
-        uint32_t row_a = lut_base_a;
-        uint32_t j0    = 0;
-        for (uint32_t c = 0; c < p.n_pieces; c++, j0 += kPerPiece, row_a += kPieceLutBytes) {
-          const uint4 v = nxt;
-          if (c + 1 < p.n_pieces) {
-            nxt = __ldg(src + (c + 1) * 32u);
-          } else if (gi + n_gwarps < n_groups) {
-            nxt = __ldg(src + group_stride);
+        if constexpr (kFixed) {
+          // the pieces of a vector, unrolled: table rows at constant offsets, the next piece (or the
+          // first of this warp's next 32 rows) requested before the current one is looked up
+          constexpr uint32_t kPieces = uint32_t((PQD + kPerPiece - 1) / kPerPiece);
+          constexpr uint32_t kLast   = uint32_t(PQD) - (kPieces - 1u) * uint32_t(kPerPiece);
+#pragma unroll
+          for (uint32_t c = 0; c < kPieces; c++) {
+            const uint4 v = nxt;
+            if (c + 1 < kPieces) {
+              nxt = __ldg(src + (c + 1) * 32u);
+            } else if (gi + n_gwarps < n_groups) {
+              nxt = __ldg(src + group_stride);
+            }
+            if (c + 1 < kPieces || kLast == uint32_t(kPerPiece)) {
+              score_piece<PqBits, LutKind, OutHalf, IsIP, true>(acc, v, lut_base_a + c * kPieceLutBytes, 0);
+            } else {
+              score_piece<PqBits, LutKind, OutHalf, IsIP, false>(acc, v, lut_base_a + c * kPieceLutBytes, kLast);
+            }
           }
-          if (j0 + kPerPiece <= p.pq_dim) {
-            score_piece<PqBits, LutKind, OutHalf, IsIP, true>(acc, v, row_a, 0);
-          } else {
-            score_piece<PqBits, LutKind, OutHalf, IsIP, false>(acc, v, row_a, p.pq_dim - j0);
+        } else {
+          uint32_t row_a = lut_base_a;
+          uint32_t j0    = 0;
+          for (uint32_t c = 0; c < n_pieces; c++, j0 += kPerPiece, row_a += kPieceLutBytes) {
+            const uint4 v = nxt;
+            if (c + 1 < n_pieces) {
+              nxt = __ldg(src + (c + 1) * 32u);
+            } else if (gi + n_gwarps < n_groups) {
+              nxt = __ldg(src + group_stride);
+            }
+            if (j0 + kPerPiece <= pq_dim) {
+              score_piece<PqBits, LutKind, OutHalf, IsIP, true>(acc, v, row_a, 0);
+            } else {
+              score_piece<PqBits, LutKind, OutHalf, IsIP, false>(acc, v, row_a, pq_dim - j0);
+            }
           }
         }
         const float score    = acc.result(p.cosine != 0);

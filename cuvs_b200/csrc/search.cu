@@ -559,7 +559,9 @@ void launch_prep(raft::resources& res, const index<int64_t>& idx, const void* qp
 // ------------------------------------------------------------------------------------------------
 int& scan_codebook_home()
 {
-  static int home = 0;  // 0 = choose, 1 = never tensor memory (shared or global memory instead)
+  // 0 = choose, 1 = never tensor memory (shared or global memory instead), 2 = choose, but never an
+  // instantiation made for one exact shape (tests compare it with the general kernel)
+  static int home = 0;
   return home;
 }
 
@@ -839,6 +841,7 @@ void search_any(raft::resources& res, const search_params& params, const index<i
       sp.lut_bytes      = plan.lut_bytes;
       sp.base_bytes     = plan.base_bytes;
       sp.merge_bytes    = plan.merge_bytes;
+      sp.allow_fixed_shape = scan_codebook_home() != 2;
       const int grid    = int(std::min<uint32_t>(uint32_t(res.sm_count),
                                               ceildiv<uint32_t>(n_pairs, plan.n_groups)));
       launch_scan(sp, int(idx.pq_bits()), lut_kind, out_half, is_ip, kpl, grid, plan.total_bytes,
