@@ -605,6 +605,15 @@ struct accum {
       }
     }
   }
+  // the running sum (for L2, where every entry is non-negative, a lower bound of the final score)
+  __device__ __forceinline__ float partial() const
+  {
+    if constexpr (!OutHalf) {
+      return f;
+    } else {
+      return __half2float(h);
+    }
+  }
   __device__ __forceinline__ float result(bool cosine)
   {
     if constexpr (!OutHalf) {
@@ -859,9 +868,17 @@ __global__ void __launch_bounds__(1024, 1) scan_kernel(const scan_params p)
       const uint32_t lut_base_a   = lut_a;
       const uint32_t group_stride = uint32_t(n_gwarps) * n_pieces * 32u;  // in 16-byte pieces
       constexpr uint32_t kPieceLutBytes = uint32_t(kPerPiece) * kBook * uint32_t(sizeof(lut_t));
+      // L2 early stop (compute_score_impl.cuh:70-71 of the reference): table entries are non-negative,
+      // so a running sum already above the bound on the query's k-th best can only end above it -- the
+      // lane stops looking up (its final value is rejected by the same bound below).  Fewer active
+      // lanes per look-up means fewer bank-conflict replays, the kernel's limiter.
+      constexpr bool kEarlyStop = !IsIP && !kStoreAll;
       for (uint32_t gi = gw; gi < n_groups; gi += n_gwarps, src += group_stride) {
         accum<LutKind, OutHalf, IsIP> acc;
         acc.init();
+        [[maybe_unused]] float stop_at = 0.0f;
+        [[maybe_unused]] bool alive    = true;
+        if constexpr (kEarlyStop) { stop_at = ordered_to_float(lds_b32_volatile(s_thr_a())); }  // NaN = no bound yet
         if constexpr (kFixed) {
           // the pieces of a vector, unrolled: table rows at constant offsets, the next piece (or the
           // first of this warp's next 32 rows) requested before the current one is looked up
@@ -875,10 +892,15 @@ __global__ void __launch_bounds__(1024, 1) scan_kernel(const scan_params p)
             } else if (gi + n_gwarps < n_groups) {
               nxt = __ldg(src + group_stride);
             }
-            if (c + 1 < kPieces || kLast == uint32_t(kPerPiece)) {
-              score_piece<PqBits, LutKind, OutHalf, IsIP, true>(acc, v, lut_base_a + c * kPieceLutBytes, 0);
-            } else {
-              score_piece<PqBits, LutKind, OutHalf, IsIP, false>(acc, v, lut_base_a + c * kPieceLutBytes, kLast);
+            if (!kEarlyStop || alive) {
+              if (c + 1 < kPieces || kLast == uint32_t(kPerPiece)) {
+                score_piece<PqBits, LutKind, OutHalf, IsIP, true>(acc, v, lut_base_a + c * kPieceLutBytes, 0);
+              } else {
+                score_piece<PqBits, LutKind, OutHalf, IsIP, false>(acc, v, lut_base_a + c * kPieceLutBytes, kLast);
+              }
+            }
+            if constexpr (kEarlyStop) {
+              if (c + 1 < kPieces) { alive = alive && !(acc.partial() > stop_at); }
             }
           }
         } else {
@@ -891,11 +913,14 @@ __global__ void __launch_bounds__(1024, 1) scan_kernel(const scan_params p)
             } else if (gi + n_gwarps < n_groups) {
               nxt = __ldg(src + group_stride);
             }
-            if (j0 + kPerPiece <= pq_dim) {
-              score_piece<PqBits, LutKind, OutHalf, IsIP, true>(acc, v, row_a, 0);
-            } else {
-              score_piece<PqBits, LutKind, OutHalf, IsIP, false>(acc, v, row_a, pq_dim - j0);
+            if (!kEarlyStop || alive) {
+              if (j0 + kPerPiece <= pq_dim) {
+                score_piece<PqBits, LutKind, OutHalf, IsIP, true>(acc, v, row_a, 0);
+              } else {
+                score_piece<PqBits, LutKind, OutHalf, IsIP, false>(acc, v, row_a, pq_dim - j0);
+              }
             }
+            if constexpr (kEarlyStop) { alive = alive && !(acc.partial() > stop_at); }
           }
         }
         const float score    = acc.result(p.cosine != 0);
