@@ -413,6 +413,9 @@ def workload_from_args(args):
         wl.update(n_rows=args.rows, n_lists=max(64, args.rows // per_list),
                   n_queries=min(wl["n_queries"], max(100, args.rows // 100)))
         wl["name"] += f" (shrunk to {args.rows} rows)"
+    if args.lists:
+        wl["n_lists"] = args.lists
+        wl["name"] += f" ({args.lists} lists)"
     if args.refine_ratio is not None:
         wl["refine_ratio"] = args.refine_ratio
     return wl
@@ -929,6 +932,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--rows", type=int, default=0, help="shrink the dataset (testing only)")
+    ap.add_argument("--lists", type=int, default=0, help="override n_lists (profiling the coarse stage on a small dataset)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--config", type=int, default=2, choices=[1, 2, 3, 4, 5],
                     help="which of the five benchmark configurations to run (default: 2, the headline)")
