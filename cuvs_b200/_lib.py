@@ -178,6 +178,7 @@ SIGNATURES = {
     "cuvsDynamicBatchingIndexDestroy": [_P(DynamicBatchingIndexStruct)],
     "cuvsDynamicBatchingSearch": [C.c_size_t, _P(DynamicBatchingIndexStruct), C.c_double,
                                   _P(DLManagedTensor), _P(DLManagedTensor), _P(DLManagedTensor)],
+    "cuvsDynamicBatchingFailNext": [_P(DynamicBatchingIndexStruct)],
     "cuvsDynamicBatchingStats": [_P(DynamicBatchingIndexStruct), _P(C.c_uint64), _P(C.c_uint64)],
     "cuvsMultiGpuIvfPqDeserializeRank": [C.c_size_t, C.c_char_p, C.c_int, C.c_int, _P(IndexStruct), _P(C.c_int),
                                          _P(C.c_int64)],

@@ -838,6 +838,13 @@ extern "C" cuvsError_t cuvsDynamicBatchingSearch(cuvsResources_t res, cuvsDynami
                        uint32_t(neighbors->dl_tensor.shape[1]), nb, ds);
   });
 }
+extern "C" cuvsError_t cuvsDynamicBatchingFailNext(cuvsDynamicBatchingIndex_t index)
+{
+  return translate_exceptions([=] {
+    CUVS_EXPECTS(index && index->addr, "null argument");
+    db::fail_next_upstream_search(*reinterpret_cast<db::index<float, int64_t>*>(index->addr));
+  });
+}
 extern "C" cuvsError_t cuvsDynamicBatchingStats(cuvsDynamicBatchingIndex_t index, uint64_t* n_batches,
                                                 uint64_t* n_rows)
 {

@@ -27,7 +27,8 @@ constexpr uint32_t kMaxProbes = 4096;
 // scores[q, l] for a chunk of queries; block = 16x16 threads, 4x4 outputs per thread.
 __global__ void __launch_bounds__(256)
 coarse_scores_kernel(const float* __restrict__ centers, const float* __restrict__ fq, uint32_t n_lists,
-                     uint32_t n_queries, uint32_t dim_ext, float alpha, float* __restrict__ scores)
+                     uint32_t n_queries, uint32_t dim_ext, float alpha, int half_scores,
+                     float* __restrict__ scores)
 {
   __shared__ float s_c[kTileK][kTile + 1];
   __shared__ float s_q[kTileK][kTile + 1];
@@ -70,7 +71,12 @@ coarse_scores_kernel(const float* __restrict__ centers, const float* __restrict_
 #pragma unroll
     for (int j = 0; j < 4; j++) {
       const uint32_t l = l0 + tx + 16 * j;
-      if (l < n_lists) { scores[size_t(q) * n_lists + l] = __fmul_rn(alpha, acc[i][j]); }
+      if (l < n_lists) {
+        float v = __fmul_rn(alpha, acc[i][j]);
+        // fp16 coarse search: the score is a half-precision number
+        if (half_scores) { v = __half2float(__float2half_rn(v)); }
+        scores[size_t(q) * n_lists + l] = v;
+      }
     }
   }
 }
@@ -263,7 +269,8 @@ size_t coarse_workspace_bytes(uint32_t n_queries, uint32_t n_lists, uint32_t n_p
 
 void select_clusters(raft::resources& res, const float* centers, uint32_t n_lists, uint32_t dim_ext,
                      float alpha, const float* fq, uint32_t n_queries, uint32_t n_probes,
-                     uint32_t* probes, float* scores_out, void* workspace, size_t workspace_bytes)
+                     uint32_t* probes, float* scores_out, void* workspace, size_t workspace_bytes,
+                     bool half_scores)
 {
   CUVS_EXPECTS(n_probes <= kMaxProbes, "n_probes = %u: this engine supports n_probes <= %u", n_probes,
                kMaxProbes);
@@ -278,7 +285,7 @@ void select_clusters(raft::resources& res, const float* centers, uint32_t n_list
     const uint32_t nq = std::min(chunk, n_queries - q0);
     dim3 grid(ceildiv<uint32_t>(n_lists, kTile), ceildiv<uint32_t>(nq, kTile));
     coarse_scores_kernel<<<grid, 256, 0, res.stream>>>(centers, fq + size_t(q0) * dim_ext, n_lists,
-                                                       nq, dim_ext, alpha, scores);
+                                                       nq, dim_ext, alpha, half_scores ? 1 : 0, scores);
     select_probes_kernel<<<nq, 256, size_t(cap) * 8, res.stream>>>(
       scores, n_lists, n_probes, cap, probes + size_t(q0) * n_probes,
       scores_out ? scores_out + size_t(q0) * n_probes : nullptr);

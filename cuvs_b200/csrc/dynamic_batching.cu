@@ -4,6 +4,7 @@
 #include <chrono>
 #include <condition_variable>
 #include <mutex>
+#include <string>
 #include <vector>
 
 namespace cuvs::neighbors::dynamic_batching {
@@ -23,6 +24,12 @@ class batch_runner {
     CUVS_EXPECTS(params.max_batch_size > 0, "dynamic batching: max_batch_size must be positive");
     CUVS_EXPECTS(params.n_queues > 0, "dynamic batching: n_queues must be positive");
     sp_.max_internal_batch_size = std::max<uint32_t>(sp_.max_internal_batch_size, max_batch_);
+    {
+      // everything the upstream search would refuse about its parameters is refused here, once,
+      // instead of on the dispatcher thread of some later batch
+      raft::resources probe;
+      ivf_pq::check_search_params(probe, sp_, upstream_, k_);
+    }
     queues_.resize(params.n_queues);
     for (auto& q : queues_) {
       q.res = std::make_unique<raft::resources>();
@@ -59,6 +66,12 @@ class batch_runner {
   }
 
   uint64_t n_batches = 0, n_rows = 0;  // guarded by m_
+  // test hook (host side): the next upstream search throws instead of running
+  void fail_next()
+  {
+    std::lock_guard<std::mutex> lk(m_);
+    fail_next_ = true;
+  }
   uint32_t k() const { return k_; }
   uint32_t dim() const { return dim_; }
 
@@ -80,6 +93,7 @@ class batch_runner {
     std::vector<cudaEvent_t> in_events;   // input copies of the open batch
     std::vector<cudaEvent_t> out_events;  // result copies of the previous batch
     cudaEvent_t done      = nullptr;      // upstream search of the last batch (also guards d_queries)
+    std::string error;                    // why the batch in flight failed (empty = it has not)
   };
 
   static cudaEvent_t new_event()
@@ -128,14 +142,26 @@ class batch_runner {
     lk.unlock();
 
     // ---- this request's rows into the queue's input buffer, on the caller's stream ----
-    if (prev_done) { CUDA_TRY(cudaStreamWaitEvent(res.stream, prev_done, 0)); }
-    CUDA_TRY(cudaMemcpyAsync(q->d_queries + size_t(offset) * dim_, queries, size_t(rows) * dim_ * sizeof(float),
-                             cudaMemcpyDeviceToDevice, res.stream));
-    cudaEvent_t in_ev = new_event();
-    CUDA_TRY(cudaEventRecord(in_ev, res.stream));
+    // From here on an exception must not leave the queue's counters behind: a failure (of this
+    // request's copies, or of the upstream search on the dispatcher) is recorded in the queue, the
+    // protocol runs to its end so that nobody waits for a count that never arrives, and every
+    // request of the failed batch reports the error.
+    std::string my_error;
+    cudaEvent_t in_ev = nullptr;
+    try {
+      if (prev_done) { CUDA_TRY(cudaStreamWaitEvent(res.stream, prev_done, 0)); }
+      CUDA_TRY(cudaMemcpyAsync(q->d_queries + size_t(offset) * dim_, queries, size_t(rows) * dim_ * sizeof(float),
+                               cudaMemcpyDeviceToDevice, res.stream));
+      in_ev = new_event();
+      CUDA_TRY(cudaEventRecord(in_ev, res.stream));
+    } catch (const std::exception& e) {
+      my_error = e.what();
+      cudaGetLastError();
+    }
 
     lk.lock();
-    q->in_events.push_back(in_ev);
+    if (in_ev) { q->in_events.push_back(in_ev); }
+    if (!my_error.empty() && q->error.empty()) { q->error = my_error; }
     q->writers--;
     cv_.notify_all();
     if (dispatcher) {
@@ -149,48 +175,76 @@ class batch_runner {
       std::vector<cudaEvent_t> prev_out;
       prev_out.swap(q->out_events);
       cudaEvent_t old_done = q->done;
+      std::string err      = q->error;
+      if (fail_next_ && err.empty()) {
+        err        = "upstream search failed (injected by the test hook)";
+        fail_next_ = false;
+      }
       lk.unlock();
-      for (auto ev : prev_out) {  // results of the previous batch have left the output buffers
-        CUDA_TRY(cudaStreamWaitEvent(q->stream, ev, 0));
-        CUDA_TRY(cudaEventDestroy(ev));
+      cudaEvent_t done = nullptr;
+      try {
+        for (auto ev : prev_out) {  // results of the previous batch have left the output buffers
+          CUDA_TRY(cudaStreamWaitEvent(q->stream, ev, 0));
+        }
+        for (auto ev : wait_for) { CUDA_TRY(cudaStreamWaitEvent(q->stream, ev, 0)); }
+        if (err.empty()) {
+          ivf_pq::search_any(*q->res, sp_, upstream_, q->d_queries, ivf_pq::elem_t::f32, n_rows_batch, k_,
+                             q->d_neighbors, q->d_distances);
+        }
+        done = new_event();
+        CUDA_TRY(cudaEventRecord(done, q->stream));
+      } catch (const std::exception& e) {
+        if (err.empty()) { err = e.what(); }
+        cudaGetLastError();
       }
-      for (auto ev : wait_for) {
-        CUDA_TRY(cudaStreamWaitEvent(q->stream, ev, 0));
-        CUDA_TRY(cudaEventDestroy(ev));
-      }
-      ivf_pq::search_any(*q->res, sp_, upstream_, q->d_queries, ivf_pq::elem_t::f32, n_rows_batch, k_,
-                         q->d_neighbors, q->d_distances);
-      cudaEvent_t done = new_event();
-      CUDA_TRY(cudaEventRecord(done, q->stream));
-      if (old_done) { CUDA_TRY(cudaEventDestroy(old_done)); }
+      for (auto ev : prev_out) { cudaEventDestroy(ev); }
+      for (auto ev : wait_for) { cudaEventDestroy(ev); }
       lk.lock();
-      q->done = done;
-      q->st   = state::done;
-      n_batches++;
-      n_rows += n_rows_batch;
+      if (done) {
+        if (old_done) { cudaEventDestroy(old_done); }
+        q->done = done;
+      }
+      q->error = err;
+      q->st    = state::done;
+      if (err.empty()) {
+        n_batches++;
+        n_rows += n_rows_batch;
+      }
       cv_.notify_all();
     } else {
       cv_.wait(lk, [&] { return q->generation == my_gen && q->st == state::done; });
     }
-    cudaEvent_t done = q->done;
+    cudaEvent_t done        = q->done;
+    std::string batch_error = q->error;
     lk.unlock();
 
     // ---- this request's rows of the result, on the caller's stream ----
-    CUDA_TRY(cudaStreamWaitEvent(res.stream, done, 0));
-    CUDA_TRY(cudaMemcpyAsync(neighbors, q->d_neighbors + size_t(offset) * k_, size_t(rows) * k_ * sizeof(int64_t),
-                             cudaMemcpyDeviceToDevice, res.stream));
-    CUDA_TRY(cudaMemcpyAsync(distances, q->d_distances + size_t(offset) * k_, size_t(rows) * k_ * sizeof(float),
-                             cudaMemcpyDeviceToDevice, res.stream));
-    cudaEvent_t out_ev = new_event();
-    CUDA_TRY(cudaEventRecord(out_ev, res.stream));
+    cudaEvent_t out_ev = nullptr;
+    if (batch_error.empty()) {
+      try {
+        CUDA_TRY(cudaStreamWaitEvent(res.stream, done, 0));
+        CUDA_TRY(cudaMemcpyAsync(neighbors, q->d_neighbors + size_t(offset) * k_, size_t(rows) * k_ * sizeof(int64_t),
+                                 cudaMemcpyDeviceToDevice, res.stream));
+        CUDA_TRY(cudaMemcpyAsync(distances, q->d_distances + size_t(offset) * k_, size_t(rows) * k_ * sizeof(float),
+                                 cudaMemcpyDeviceToDevice, res.stream));
+        out_ev = new_event();
+        CUDA_TRY(cudaEventRecord(out_ev, res.stream));
+      } catch (const std::exception& e) {
+        batch_error = e.what();
+        cudaGetLastError();
+      }
+    }
 
     lk.lock();
-    q->out_events.push_back(out_ev);
+    if (out_ev) { q->out_events.push_back(out_ev); }
     if (--q->readers == 0) {
       q->st = state::idle;
       q->generation++;
+      q->error.clear();
       cv_.notify_all();
     }
+    lk.unlock();
+    if (!batch_error.empty()) { fail("dynamic batching: the batch of this request failed: %s", batch_error.c_str()); }
   }
 
   const ivf_pq::index<int64_t>& upstream_;
@@ -199,6 +253,7 @@ class batch_runner {
   std::vector<queue> queues_;
   std::mutex m_;
   std::condition_variable cv_;
+  bool fail_next_ = false;
 };
 
 }  // namespace detail
@@ -229,6 +284,8 @@ void search_checked(raft::resources& res, const search_params& params, const ind
   CUVS_EXPECTS(k == idx.runner->k(), "k is fixed at the construction of a dynamic batching index");
   search(res, params, idx, queries, n_queries, neighbors, distances);
 }
+
+void fail_next_upstream_search(const index<float, int64_t>& idx) { idx.runner->fail_next(); }
 
 void stats(const index<float, int64_t>& idx, uint64_t* n_batches, uint64_t* n_rows)
 {

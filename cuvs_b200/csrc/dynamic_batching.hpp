@@ -54,6 +54,10 @@ void search_checked(raft::resources& res, const search_params& params, const ind
                     const float* queries, uint32_t n_queries, uint32_t dim, uint32_t k, int64_t* neighbors,
                     float* distances);
 
+// test hook, host side only: the next upstream search of this index throws instead of running (every
+// request of that batch then reports the error; the queue stays usable)
+void fail_next_upstream_search(const index<float, int64_t>& idx);
+
 // counters for tests: batches dispatched, rows searched
 void stats(const index<float, int64_t>& idx, uint64_t* n_batches, uint64_t* n_rows);
 

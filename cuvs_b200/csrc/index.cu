@@ -138,6 +138,28 @@ index<int64_t>::int8_operands index<int64_t>::int8_coarse_operands(cudaStream_t 
   return {centers_i8f_.data(), rotation_i8f_.data(), centers_i8f_max_norm_};
 }
 
+__global__ void round_to_half_kernel(const float* __restrict__ in, size_t n, float* __restrict__ out)
+{
+  const size_t ix = blockIdx.x * size_t(blockDim.x) + threadIdx.x;
+  if (ix < n) { out[ix] = __half2float(__float2half_rn(in[ix])); }
+}
+
+index<int64_t>::half_operands index<int64_t>::half_coarse_operands(cudaStream_t stream) const
+{
+  static std::mutex lock;  // first use may come from several searching threads at once
+  std::lock_guard<std::mutex> guard(lock);
+  const size_t nc = size_t(n_lists_) * dim_ext(), nr = size_t(rot_dim()) * dim_;
+  if (centers_h_.size() != nc || rotation_h_.size() != nr) {
+    centers_h_.resize(nc);
+    rotation_h_.resize(nr);
+    round_to_half_kernel<<<unsigned(ceildiv<size_t>(nc, 256)), 256, 0, stream>>>(centers_.data(), nc, centers_h_.data());
+    round_to_half_kernel<<<unsigned(ceildiv<size_t>(nr, 256)), 256, 0, stream>>>(rotation_.data(), nr, rotation_h_.data());
+    CUDA_TRY(cudaGetLastError());
+    CUDA_TRY(cudaStreamSynchronize(stream));  // other streams may use the arrays right after this call
+  }
+  return {centers_h_.data(), rotation_h_.data()};
+}
+
 void index<int64_t>::allocate_lists(const std::vector<uint32_t>& sizes, cudaStream_t stream)
 {
   CUVS_EXPECTS(sizes.size() == n_lists_, "list size vector has the wrong length");
@@ -187,6 +209,8 @@ void index<int64_t>::recompute_internal_state(cudaStream_t stream)
   rotation_is_identity_ = ident;
   centers_i8f_.reset();  // rebuilt from the current model on next use
   rotation_i8f_.reset();
+  centers_h_.reset();
+  rotation_h_.reset();
   // derived data of the tensor-core coarse search
   const size_t nc = size_t(n_lists_) * dim_ext();
   std::vector<float> hc(nc);

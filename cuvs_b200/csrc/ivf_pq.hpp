@@ -216,6 +216,14 @@ class index<int64_t> {
     float centers_max_norm;
   };
   int8_operands int8_coarse_operands(cudaStream_t stream) const;
+  // Operands of the fp16 coarse search (coarse_search_dtype = CUDA_R_16F; the lazily cast centers of
+  // cpp/src/neighbors/ivf_pq_index.cu:599-622), created on first use: the padded centers and the
+  // rotation matrix rounded to half precision, held as fp32 numbers.
+  struct half_operands {
+    const float* centers;   // [n_lists, dim_ext]
+    const float* rotation;  // [rot_dim, dim]
+  };
+  half_operands half_coarse_operands(cudaStream_t stream) const;
 
   // (Re)create the arenas for the given list sizes; contents are zero codes / -1 ids.
   void allocate_lists(const std::vector<uint32_t>& sizes, cudaStream_t stream);
@@ -227,6 +235,7 @@ class index<int64_t> {
   dev_array<float> centers_hi_, centers_lo_;
   float centers_max_norm_ = 0.0f;
   mutable dev_array<float> centers_i8f_, rotation_i8f_;
+  mutable dev_array<float> centers_h_, rotation_h_;
   mutable float centers_i8f_max_norm_ = 0.0f;
   dev_array<uint32_t> list_sizes_;
   dev_array<uint64_t> row_off_;
@@ -264,6 +273,10 @@ void search_any(raft::resources& res, const search_params& params, const index<i
                 const void* queries, elem_t qtype, uint32_t n_queries, uint32_t k,
                 int64_t* neighbors, float* distances, const uint32_t* given_probes = nullptr,
                 bitset_view filter = {});
+// Every check the search makes on its parameters before it touches the GPU (argument ranges, dtype
+// pairing, a shared-memory plan for the look-up table): throws what the search would throw.
+void check_search_params(const raft::resources& res, const search_params& params, const index<int64_t>& idx,
+                         uint32_t k);
 // Probe selection alone, asynchronous on the handle's stream: probes [n_queries, n_probes] u32,
 // ascending by (score, list id).
 void select_probes_any(raft::resources& res, const index<int64_t>& idx, const void* queries,

@@ -83,12 +83,15 @@ template <> __device__ __forceinline__ int8_t map_to_int8<uint8_t>(uint8_t x) { 
 // int8 image of the query as numbers, dim_ext = round_up(dim + 2, 16) with 1 - m in column `dim` and
 // -128 (L2) or 0 in the m - 1 columns after it; `rotation` is the int8 image of the rotation matrix
 // and rot_q = (R8 * q8) / 128^2 (sums of integers below 2^24: exact in fp32 in any order).
-template <typename T, bool kInt8>
+// kMode 2 (coarse_search_dtype = CUDA_R_16F, ivf_pq_search.cuh:259-340): fq holds mapping<half> of the
+// query as numbers, `rotation` is the half-rounded rotation matrix, rot_q the fp32 chain over them.
+template <typename T, int kMode>
 __global__ void prep_queries_kernel(const T* __restrict__ queries, uint32_t dim, uint32_t dim_ext,
                                     uint32_t rot_dim, int is_l2, int cosine, int identity,
                                     const float* __restrict__ rotation, float* __restrict__ fq,
                                     float* __restrict__ rot_q)
 {
+  constexpr bool kInt8 = kMode == 1;
   extern __shared__ float s_buf[];  // [dim] query, [rot_dim] rotated (cosine only)
   float* s_q         = s_buf;
   float* s_r         = s_buf + dim;
@@ -99,6 +102,8 @@ __global__ void prep_queries_kernel(const T* __restrict__ queries, uint32_t dim,
     float v = 0.0f;
     if (i < dim) {
       v      = kInt8 ? static_cast<float>(map_to_int8<T>(src[i])) : map_to_float<T>(src[i]);
+      // mapping<half>: integer types and half are exact; fp32 is rounded to nearest
+      if constexpr (kMode == 2) { v = __half2float(__float2half_rn(v)); }
       s_q[i] = v;
     } else if constexpr (kInt8) {
       const uint32_t m = dim_ext - dim;
@@ -518,28 +523,33 @@ int& coarse_mode_ref()
 }
 int coarse_mode() { return coarse_mode_ref(); }
 
+// `rotation_alt`: the int8 (mode 1) or half-rounded (mode 2) image of the rotation matrix.
 void launch_prep(raft::resources& res, const index<int64_t>& idx, const void* qptr, elem_t qtype,
-                 uint32_t nq, float* d_fq, float* d_rq, const float* rotation_int8 = nullptr)
+                 uint32_t nq, float* d_fq, float* d_rq, const float* rotation_alt = nullptr, int mode = 0)
 {
   const DistanceType metric = idx.metric();
   const int is_l2  = metric == DistanceType::L2Expanded || metric == DistanceType::L2SqrtExpanded;
   const int cosine = metric == DistanceType::CosineExpanded;
-  const bool i8    = rotation_int8 != nullptr;
-  // the int8 image of an identity rotation is 127 on the diagonal: no shortcut there
-  const int ident  = !i8 && idx.rotation_is_identity();
-  const float* rot = i8 ? rotation_int8 : idx.rotation_matrix();
-  const uint32_t dim_ext = i8 ? idx.dim_ext_int8() : idx.dim_ext();
+  if (rotation_alt != nullptr && mode == 0) { mode = 1; }
+  // the int8 image of an identity rotation is 127 on the diagonal: no shortcut there (the half image
+  // of an identity matrix is the identity)
+  const int ident  = mode != 1 && idx.rotation_is_identity();
+  const float* rot = mode != 0 ? rotation_alt : idx.rotation_matrix();
+  const uint32_t dim_ext = mode == 1 ? idx.dim_ext_int8() : idx.dim_ext();
   const size_t smem = (size_t(idx.dim()) + idx.rot_dim()) * 4;
   const int threads = 128;
   cudaStream_t stream = res.stream;
   auto launch = [&](auto* q) {
     using T = std::remove_const_t<std::remove_pointer_t<decltype(q)>>;
-    if (i8) {
-      prep_queries_kernel<T, true><<<nq, threads, smem, stream>>>(q, idx.dim(), dim_ext, idx.rot_dim(), is_l2,
-                                                                  cosine, ident, rot, d_fq, d_rq);
+    if (mode == 1) {
+      prep_queries_kernel<T, 1><<<nq, threads, smem, stream>>>(q, idx.dim(), dim_ext, idx.rot_dim(), is_l2,
+                                                               cosine, ident, rot, d_fq, d_rq);
+    } else if (mode == 2) {
+      prep_queries_kernel<T, 2><<<nq, threads, smem, stream>>>(q, idx.dim(), dim_ext, idx.rot_dim(), is_l2,
+                                                               cosine, ident, rot, d_fq, d_rq);
     } else {
-      prep_queries_kernel<T, false><<<nq, threads, smem, stream>>>(q, idx.dim(), dim_ext, idx.rot_dim(), is_l2,
-                                                                   cosine, ident, rot, d_fq, d_rq);
+      prep_queries_kernel<T, 0><<<nq, threads, smem, stream>>>(q, idx.dim(), dim_ext, idx.rot_dim(), is_l2,
+                                                               cosine, ident, rot, d_fq, d_rq);
     }
   };
   switch (qtype) {
@@ -626,9 +636,8 @@ scan_plan plan_scan(const raft::resources& res, const index<int64_t>& idx, int l
 // ------------------------------------------------------------------------------------------------
 // search
 // ------------------------------------------------------------------------------------------------
-void search_any(raft::resources& res, const search_params& params, const index<int64_t>& idx,
-                const void* queries, elem_t qtype, uint32_t n_queries, uint32_t k,
-                int64_t* neighbors, float* distances, const uint32_t* given_probes, bitset_view filter)
+void check_search_params(const raft::resources& res, const search_params& params, const index<int64_t>& idx,
+                         uint32_t k)
 {
   // ivf_pq_search.cuh:901-917
   CUVS_EXPECTS(params.internal_distance_dtype == CUDA_R_16F ||
@@ -643,11 +652,12 @@ void search_any(raft::resources& res, const search_params& params, const index<i
                k, size_t(idx.size()));
   CUVS_EXPECTS(params.n_probes > 0,
                "n_probes (number of clusters to probe in the search) must be positive.");
-  CUVS_EXPECTS(params.coarse_search_dtype == CUDA_R_32F || params.coarse_search_dtype == CUDA_R_8I,
-               "Unsupported coarse_search_dtype (only CUDA_R_32F and CUDA_R_8I are supported by this engine)");
-  const bool coarse_i8 = params.coarse_search_dtype == CUDA_R_8I;
+  // ivf_pq_search.cuh:958-966
+  CUVS_EXPECTS(params.coarse_search_dtype == CUDA_R_32F || params.coarse_search_dtype == CUDA_R_16F ||
+                 params.coarse_search_dtype == CUDA_R_8I,
+               "Unsupported coarse_search_dtype (only CUDA_R_32F, CUDA_R_16F, and CUDA_R_8I are supported)");
   // integer scores and rotated queries stay exact in fp32 while dim_ext * 128 * 128 <= 2^24
-  CUVS_EXPECTS(!coarse_i8 || idx.dim_ext_int8() <= 1024,
+  CUVS_EXPECTS(params.coarse_search_dtype != CUDA_R_8I || idx.dim_ext_int8() <= 1024,
                "coarse_search_dtype CUDA_R_8I: dim = %u is too large for this engine (at most 1022)", idx.dim());
   const bool out_half = params.internal_distance_dtype == CUDA_R_16F;
   const int lut_kind =
@@ -658,6 +668,24 @@ void search_any(raft::resources& res, const search_params& params, const index<i
                "internal_distance_dtype should be not smaller than the size of the lut_dtype.",
                int(params.lut_dtype), int(params.internal_distance_dtype));
   CUVS_EXPECTS(k <= 4096, "k = %u: this engine supports k <= 4096", k);
+  const uint32_t n_probes = std::min<uint32_t>(params.n_probes, idx.n_lists());
+  CUVS_EXPECTS(uint64_t(idx.accum_sorted_sizes()[n_probes]) <= 0xFFFFFFFFull,
+               "The maximum sample size is too big.");
+  const DistanceType metric = idx.metric();
+  const bool is_l2 = metric == DistanceType::L2Expanded || metric == DistanceType::L2SqrtExpanded;
+  (void)plan_scan(res, idx, lut_kind, !is_l2, k > 128 ? 1 : k);  // throws when no plan exists
+}
+
+void search_any(raft::resources& res, const search_params& params, const index<int64_t>& idx,
+                const void* queries, elem_t qtype, uint32_t n_queries, uint32_t k,
+                int64_t* neighbors, float* distances, const uint32_t* given_probes, bitset_view filter)
+{
+  check_search_params(res, params, idx, k);
+  const bool coarse_i8 = params.coarse_search_dtype == CUDA_R_8I;
+  const bool coarse_h  = params.coarse_search_dtype == CUDA_R_16F;
+  const bool out_half = params.internal_distance_dtype == CUDA_R_16F;
+  const int lut_kind =
+    params.lut_dtype == CUDA_R_32F ? LUT_F32 : (params.lut_dtype == CUDA_R_16F ? LUT_F16 : LUT_FP8);
   // k <= 128: top-k fused into the scan (registers).  Larger k: the scan stores every score and a
   // separate selection follows (the reference's non-fused mode, ivf_pq_compute_similarity_impl.cuh:34-45).
   const bool store_all = k > 128;
@@ -682,8 +710,6 @@ void search_any(raft::resources& res, const search_params& params, const index<i
   const bool cosine = metric == DistanceType::CosineExpanded;
   const int kpl     = store_all ? 0 : kpl_for_k(k);
   const float scale = qtype == elem_t::u8 ? 256.0f : (qtype == elem_t::i8 ? 128.0f : 1.0f);
-  CUVS_EXPECTS(uint64_t(idx.accum_sorted_sizes()[n_probes]) <= 0xFFFFFFFFull,
-               "The maximum sample size is too big.");
 
   const scan_plan plan = plan_scan(res, idx, lut_kind, is_ip, store_all ? 1 : k);
   uint32_t batch = std::min<uint32_t>(n_queries, std::max<uint32_t>(1, params.max_internal_batch_size));
@@ -704,6 +730,8 @@ void search_any(raft::resources& res, const search_params& params, const index<i
   const uint32_t cdim_ext = coarse_i8 ? idx.dim_ext_int8() : idx.dim_ext();
   index<int64_t>::int8_operands op8{};
   if (coarse_i8) { op8 = idx.int8_coarse_operands(stream); }
+  index<int64_t>::half_operands oph{};
+  if (coarse_h) { oph = idx.half_coarse_operands(stream); }
   const size_t o_fq      = lay.add(size_t(batch) * cdim_ext * 4);
   const size_t o_rq      = lay.add(size_t(batch) * idx.rot_dim() * 4);
   const size_t o_probes  = lay.add(n_pairs_max * 4);
@@ -714,7 +742,9 @@ void search_any(raft::resources& res, const search_params& params, const index<i
   const size_t o_counter = lay.add(256);
   const size_t o_keys    = lay.add(store_all ? size_t(batch) * k * 8 : n_pairs_max * k * 8);
   const size_t o_all     = lay.add(store_all ? size_t(batch) * max_samples * 4 : 0);
-  const bool use_tc = coarse_mode() != 1 && coarse_tc_usable(n_lists, n_probes, cdim_ext);
+  // half-precision scores tie in large groups, which the tensor-core path's guard (made for fp32
+  // scores) does not settle: the fp16 coarse search runs on the exact SIMT path
+  const bool use_tc = !coarse_h && coarse_mode() != 1 && coarse_tc_usable(n_lists, n_probes, cdim_ext);
   const size_t coarse_ws =
     given_probes ? 0
                  : (use_tc ? coarse_tc_workspace_bytes(batch, n_lists, cdim_ext)
@@ -744,13 +774,17 @@ void search_any(raft::resources& res, const search_params& params, const index<i
     if (stats) { res.stats_mark(ev, 0); }
 
     // 1. cast / pad / rotate
-    launch_prep(res, idx, qptr, qtype, nq, d_fq, d_rq, coarse_i8 ? op8.rotation : nullptr);
+    launch_prep(res, idx, qptr, qtype, nq, d_fq, d_rq, coarse_i8 ? op8.rotation : (coarse_h ? oph.rotation : nullptr),
+                coarse_i8 ? 1 : (coarse_h ? 2 : 0));
 
     if (stats) { res.stats_mark(ev, 1); }
     // 2. coarse selection: probes sorted by (score, list id)
     if (given_probes) {
       CUDA_TRY(cudaMemcpyAsync(d_probes, given_probes + size_t(q0) * n_probes, size_t(nq) * n_probes * 4,
                                cudaMemcpyDeviceToDevice, stream));
+    } else if (coarse_h) {
+      select_clusters(res, oph.centers, n_lists, cdim_ext, is_l2 ? -2.0f : -1.0f, d_fq, nq, n_probes, d_probes,
+                      nullptr, d_coarse, coarse_ws, /*half_scores=*/true);
     } else if (coarse_i8) {
       // integer operands are exact in TF32 and their sums in fp32: one product, no split error
       if (use_tc) {
@@ -911,9 +945,11 @@ void select_probes_any(raft::resources& res, const index<int64_t>& idx, const vo
   if (n_queries == 0) { return; }
   const uint32_t n_lists = idx.n_lists();
   CUVS_EXPECTS(n_probes > 0 && n_probes <= n_lists, "n_probes must be within [1, n_lists]");
-  CUVS_EXPECTS(coarse_search_dtype == CUDA_R_32F || coarse_search_dtype == CUDA_R_8I,
-               "Unsupported coarse_search_dtype (only CUDA_R_32F and CUDA_R_8I are supported by this engine)");
+  CUVS_EXPECTS(coarse_search_dtype == CUDA_R_32F || coarse_search_dtype == CUDA_R_16F ||
+                 coarse_search_dtype == CUDA_R_8I,
+               "Unsupported coarse_search_dtype (only CUDA_R_32F, CUDA_R_16F, and CUDA_R_8I are supported)");
   const bool coarse_i8 = coarse_search_dtype == CUDA_R_8I;
+  const bool coarse_h  = coarse_search_dtype == CUDA_R_16F;
   CUVS_EXPECTS(!coarse_i8 || idx.dim_ext_int8() <= 1024,
                "coarse_search_dtype CUDA_R_8I: dim = %u is too large for this engine (at most 1022)", idx.dim());
   const DistanceType metric = idx.metric();
@@ -921,7 +957,9 @@ void select_probes_any(raft::resources& res, const index<int64_t>& idx, const vo
   const uint32_t cdim_ext = coarse_i8 ? idx.dim_ext_int8() : idx.dim_ext();
   index<int64_t>::int8_operands op8{};
   if (coarse_i8) { op8 = idx.int8_coarse_operands(res.stream); }
-  const bool use_tc = coarse_mode() != 1 && coarse_tc_usable(n_lists, n_probes, cdim_ext);
+  index<int64_t>::half_operands oph{};
+  if (coarse_h) { oph = idx.half_coarse_operands(res.stream); }
+  const bool use_tc = !coarse_h && coarse_mode() != 1 && coarse_tc_usable(n_lists, n_probes, cdim_ext);
   const uint32_t batch = std::min<uint32_t>(n_queries, 16384);
   ws_layout lay;
   const size_t o_fq = lay.add(size_t(batch) * cdim_ext * 4);
@@ -938,8 +976,12 @@ void select_probes_any(raft::resources& res, const index<int64_t>& idx, const vo
     const uint32_t nq = std::min(batch, n_queries - q0);
     const char* qptr  = static_cast<const char*>(queries) + size_t(q0) * idx.dim() * elem_size(qtype);
     uint32_t* out     = probes + size_t(q0) * n_probes;
-    launch_prep(res, idx, qptr, qtype, nq, d_fq, d_rq, coarse_i8 ? op8.rotation : nullptr);
-    if (coarse_i8) {
+    launch_prep(res, idx, qptr, qtype, nq, d_fq, d_rq, coarse_i8 ? op8.rotation : (coarse_h ? oph.rotation : nullptr),
+                coarse_i8 ? 1 : (coarse_h ? 2 : 0));
+    if (coarse_h) {
+      select_clusters(res, oph.centers, n_lists, cdim_ext, alpha, d_fq, nq, n_probes, out, nullptr, ws + o_c,
+                      cws, /*half_scores=*/true);
+    } else if (coarse_i8) {
       if (use_tc) {
         select_clusters_tc(res, op8.centers, op8.centers, op8.centers, op8.centers_max_norm, n_lists, cdim_ext,
                            alpha, d_fq, nq, n_probes, out, nullptr, ws + o_c, cws, /*exact_operands=*/true);

@@ -16,10 +16,12 @@ scan_plan plan_scan(const raft::resources& res, const index<int64_t>& idx, int l
 // Coarse stage (coarse.cu): for every query the n_probes lists with the smallest
 //   score[q, l] = alpha * sum_k centers[l, k] * fq[q, k]
 // sorted by (score, list id) ascending.  `scores_out` (optional) receives the selected scores.
+// `half_scores`: every score is rounded to half precision before the selection (fp16 coarse search).
 size_t coarse_workspace_bytes(uint32_t n_queries, uint32_t n_lists, uint32_t n_probes);
 void select_clusters(raft::resources& res, const float* centers, uint32_t n_lists, uint32_t dim_ext,
                      float alpha, const float* fq, uint32_t n_queries, uint32_t n_probes,
-                     uint32_t* probes, float* scores_out, void* workspace, size_t workspace_bytes);
+                     uint32_t* probes, float* scores_out, void* workspace, size_t workspace_bytes,
+                     bool half_scores = false);
 
 // Per row the k smallest (value, position), ascending (radix select + sort; k <= 4096).
 void select_rows(raft::resources& res, const float* rows, uint32_t n_rows, uint32_t row_len, uint32_t k,

@@ -45,6 +45,10 @@ class Index:
             L.load().cuvsDynamicBatchingIndexDestroy(h)
             self._h = None
 
+    def fail_next(self):
+        """Test hook (host side): the next upstream search of this index fails before it runs."""
+        L.check(L.load().cuvsDynamicBatchingFailNext(self._h))
+
     def stats(self):
         """(upstream searches launched, rows they carried)."""
         a, b = C.c_uint64(), C.c_uint64()

@@ -60,6 +60,11 @@ CUVS_EXPORT cuvsError_t cuvsDynamicBatchingStats(cuvsDynamicBatchingIndex_t inde
                                                  uint64_t* n_batches,
                                                  uint64_t* n_rows);
 
+/* Test hook, host side only (no counterpart in the reference): the next upstream search of this index
+ * fails before it runs.  Every request gathered into that batch returns CUVS_ERROR with the reason; the
+ * queue stays usable. */
+CUVS_EXPORT cuvsError_t cuvsDynamicBatchingFailNext(cuvsDynamicBatchingIndex_t index);
+
 #ifdef __cplusplus
 }
 #endif

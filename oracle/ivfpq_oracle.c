@@ -694,6 +694,87 @@ ORC_EXPORT void orc_select_clusters_int8(const orc_index* ix, const int8_t* c8, 
   free(all);
 }
 
+/* ============================ fp16 coarse search (coarse_search_dtype = CUDA_R_16F) ========== */
+/* ivf_pq_search.cuh:259-340 and :996-1025: queries, centers (with their norm column) and the rotation
+ * matrix are rounded to half precision, the products are library GEMMs whose accumulation the
+ * reference does not define, the scores are half-precision numbers and select_k leaves equal scores in
+ * unspecified order.  The rule restated here (and computed by the GPU path): fp32 fused multiply-adds
+ * over ascending k on the half-rounded operands, the scaled sum rounded once to half precision, probes
+ * ordered by (half score, list id); rotated queries by the same chain, kept in fp32. */
+static float round_to_half(float x) { return f16_to_f32(f32_to_f16(x)); }
+
+/* mapping<half> of one query element (ann_utils.cuh:168-199), widened to fp32 */
+static float map_query_f16(const void* q, int qtype, uint32_t i)
+{
+  switch (qtype) {
+    case Q_F32: return round_to_half(((const float*)q)[i]);
+    case Q_F16: return f16_to_f32(((const uint16_t*)q)[i]);
+    case Q_I8: return (float)((const int8_t*)q)[i] * (1.0f / 128.0f); /* exact in half precision */
+    default: return (float)((const uint8_t*)q)[i] * (1.0f / 256.0f);
+  }
+}
+
+ORC_EXPORT void orc_prepare_queries_f16(const orc_index* ix, const void* queries, int qtype, uint32_t n_q,
+                                        float* fq_ext /* [n_q, dim_ext] half values */, float* rot_q)
+{
+  init_tables();
+  const size_t qs = qtype_size(qtype);
+  for (uint32_t q = 0; q < n_q; q++) {
+    float* f = fq_ext + (size_t)q * ix->dim_ext;
+    const uint8_t* src = (const uint8_t*)queries + (size_t)q * ix->dim * qs;
+    for (uint32_t k = 0; k < ix->dim; k++) { f[k] = map_query_f16(src, qtype, k); }
+    for (uint32_t k = ix->dim; k < ix->dim_ext; k++) { f[k] = 0.0f; }
+    if (is_l2(ix->metric)) { f[ix->dim] = -0.5f; }
+    float* r = rot_q + (size_t)q * ix->rot_dim;
+    for (uint32_t i = 0; i < ix->rot_dim; i++) {
+      const float* row = ix->rotation + (size_t)i * ix->dim;
+      float acc        = 0.0f;
+      for (uint32_t k = 0; k < ix->dim; k++) { acc = fmaf(round_to_half(row[k]), f[k], acc); }
+      r[i] = acc;
+    }
+    if (ix->metric == M_COSINE) {
+      float ss = 0.0f;
+      for (uint32_t i = 0; i < ix->rot_dim; i++) { ss = fmaf(r[i], r[i], ss); }
+      float nrm = sqrtf(ss);
+      if (nrm > 0.0f) {
+        for (uint32_t i = 0; i < ix->rot_dim; i++) { r[i] = r[i] / nrm; }
+      }
+    }
+  }
+}
+
+ORC_EXPORT void orc_select_clusters_f16(const orc_index* ix, const float* fq_ext, uint32_t n_q,
+                                        uint32_t n_probes, uint32_t* probes, float* probe_scores)
+{
+  init_tables();
+  if (n_probes > ix->n_lists) { n_probes = ix->n_lists; }
+  const float alpha = is_l2(ix->metric) ? -2.0f : -1.0f;
+  float* ch = (float*)malloc((size_t)ix->n_lists * ix->dim_ext * sizeof(float));
+  for (size_t i = 0; i < (size_t)ix->n_lists * ix->dim_ext; i++) { ch[i] = round_to_half(ix->centers[i]); }
+#pragma omp parallel
+  {
+    cand_t* all = (cand_t*)malloc((size_t)ix->n_lists * sizeof(cand_t));
+#pragma omp for schedule(dynamic, 4)
+    for (int64_t q = 0; q < (int64_t)n_q; q++) {
+      const float* f = fq_ext + (size_t)q * ix->dim_ext;
+      for (uint32_t l = 0; l < ix->n_lists; l++) {
+        const float* c = ch + (size_t)l * ix->dim_ext;
+        float acc      = 0.0f;
+        for (uint32_t k = 0; k < ix->dim_ext; k++) { acc = fmaf(c[k], f[k], acc); }
+        all[l].s = round_to_half(alpha * acc);
+        all[l].i = l;
+      }
+      qsort(all, ix->n_lists, sizeof(cand_t), cand_cmp);
+      for (uint32_t p = 0; p < n_probes; p++) {
+        probes[(size_t)q * n_probes + p] = all[p].i;
+        if (probe_scores) { probe_scores[(size_t)q * n_probes + p] = all[p].s; }
+      }
+    }
+    free(all);
+  }
+  free(ch);
+}
+
 /* LUT of one (query, list) pair in its storage type (4, 2 or 1 bytes per entry). */
 ORC_EXPORT void orc_build_lut(const orc_index* ix, uint32_t label, const float* rot_q, int lut_dtype,
                               void* out)

@@ -580,6 +580,27 @@ def search_int8_coarse(ix: OracleIndex, queries: np.ndarray, k: int, n_probes: i
     return (ds, nb, probes, scores) if return_probes else (ds, nb)
 
 
+def search_f16_coarse(ix: OracleIndex, queries: np.ndarray, k: int, n_probes: int = 20,
+                      lut_dtype=CUDA_R_32F, internal_dtype=CUDA_R_32F, return_probes=False):
+    """search with coarse_search_dtype = CUDA_R_16F (ivf_pq_search.cuh:259-340, :996-1025): queries,
+    centers and rotation matrix rounded to half precision, half-precision coarse scores ordered by
+    (score, list id), rotated queries from the half-rounded operands; the fine search is the usual one."""
+    q = np.ascontiguousarray(queries)
+    n_q = q.shape[0]
+    n_probes = min(n_probes, ix.n_lists)
+    fq = np.zeros((n_q, ix.dim_ext), dtype=np.float32)
+    rq = np.zeros((n_q, ix.rot_dim), dtype=np.float32)
+    s = ix.c_struct()
+    lib().orc_prepare_queries_f16(C.byref(s), _ptr(q), C.c_int(_QTYPE[q.dtype]), C.c_uint32(n_q), _ptr(fq), _ptr(rq))
+    probes = np.zeros((n_q, n_probes), dtype=np.uint32)
+    scores = np.zeros((n_q, n_probes), dtype=np.float32)
+    lib().orc_select_clusters_f16(C.byref(s), _ptr(fq), C.c_uint32(n_q), C.c_uint32(n_probes), _ptr(probes),
+                                  _ptr(scores))
+    scale = {np.dtype(np.uint8): 256.0, np.dtype(np.int8): 128.0}.get(q.dtype, 1.0)
+    ds, nb, _ = search_probes(ix, rq, probes, k, lut_dtype, internal_dtype, scale)
+    return (ds, nb, probes, scores) if return_probes else (ds, nb)
+
+
 def build_lut(ix: OracleIndex, label: int, rot_q: np.ndarray, lut_dtype: int) -> np.ndarray:
     n = ix.pq_dim << ix.pq_bits
     dt = {CUDA_R_32F: np.float32, CUDA_R_16F: np.float16, CUDA_R_8U: np.uint8}[lut_dtype]

@@ -96,3 +96,48 @@ def test_argument_errors(setup):
         db.search(index, qd[:4, :32].contiguous())
     with pytest.raises(L.CuvsError, match="max_batch_size"):
         db.Index(g, sp, k=10, max_batch_size=0)
+
+
+def test_a_failed_upstream_search_fails_its_whole_batch_and_nobody_hangs(setup):
+    """The dispatcher thread's upstream search fails (injected on the host): every request gathered
+    into that batch gets the error, no thread is left waiting, and the next batch is served."""
+    import threading
+    from cuvs_b200 import dynamic_batching as db
+    from cuvs_b200 import _lib as L
+    from cuvs_b200.common import Resources
+    g, sp, qd, d_ref, i_ref = setup
+    index = db.Index(g, sp, k=10, max_batch_size=8, n_queues=1)
+    index.fail_next()
+    outcome = [None] * 8
+
+    def worker(t):
+        res = Resources()
+        stream = torch.cuda.Stream()
+        with torch.cuda.stream(stream):
+            res.use_current_stream()
+            try:
+                db.search(index, qd[t:t + 1], dispatch_timeout_ms=2000.0, resources=res)
+                outcome[t] = "ok"
+            except L.CuvsError as exc:
+                outcome[t] = str(exc)
+
+    threads = [threading.Thread(target=worker, args=(t,)) for t in range(8)]
+    for th in threads:
+        th.start()
+    for th in threads:
+        th.join(timeout=60)
+    assert not any(th.is_alive() for th in threads), "a caller is still waiting"
+    assert all(o is not None and "injected" in o for o in outcome), outcome
+    # the queue is usable again
+    d, i = db.search(index, qd[:8], dispatch_timeout_ms=0.1)
+    assert (i.cpu().numpy() == i_ref[:8]).all()
+
+
+def test_upstream_parameters_are_checked_when_the_index_is_made(setup):
+    from cuvs_b200 import dynamic_batching as db
+    from cuvs_b200 import ivf_pq
+    from cuvs_b200 import _lib as L
+    g, _, _, _, _ = setup
+    bad = ivf_pq.SearchParams(n_probes=4, lut_dtype=np.float32, internal_distance_dtype=np.float16)
+    with pytest.raises(L.CuvsError, match="lut_dtype / internal_distance_dtype"):
+        db.Index(g, bad, k=10)
