@@ -94,11 +94,3 @@ def test_int8_coarse_with_half_queries(ivf, oracle_mod, tmp_path):
     do, io = O.search_int8_coarse(ix, q, 10, n_probes=8)
     assert_parity(d, i, do, io, 1e-5)
 
-
-def test_fp16_coarse_search_is_refused(ivf, oracle_mod, tmp_path):
-    from cuvs_b200._lib import CuvsError
-    x, q, ix, path = build_case(oracle_mod, tmp_path, "f16c", n=2000, dim=32, n_lists=16, pq_dim=16, nq=8)
-    g = ivf.load(path)
-    sp = ivf.SearchParams(n_probes=4, coarse_search_dtype=np.float16)
-    with pytest.raises(CuvsError, match="Unsupported coarse_search_dtype"):
-        ivf.search(sp, g, torch.from_numpy(q).cuda(), 5)
