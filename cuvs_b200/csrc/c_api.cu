@@ -761,7 +761,7 @@ extern "C" cuvsError_t cuvsB200SetCoarseWaitTest(uint32_t spin_limit, uint32_t s
 extern "C" cuvsError_t cuvsB200SetScanCodebookHome(int home)
 {
   return translate_exceptions([=] {
-    CUVS_EXPECTS(home == 0 || home == 1, "home must be 0 or 1");
+    CUVS_EXPECTS(home >= 0 && home <= 3, "home must be 0, 1, 2 or 3");
     ivf_pq::set_scan_codebook_home(home);
   });
 }

@@ -61,6 +61,9 @@ struct scan_params {
   uint32_t tmem_cols, tmem_slot_off;
   // host only: whether the launcher may pick an instantiation made for this exact shape
   int allow_fixed_shape;
+  // look-up tables too large for shared memory: one table per CTA in global memory
+  // ([grid][pq_dim << pq_bits] entries of the table type), used by scan_glut_kernel
+  void* lut_global;
 };
 
 enum { LUT_F32 = 0, LUT_F16 = 1, LUT_FP8 = 2 };
@@ -973,8 +976,158 @@ __global__ void __launch_bounds__(1024, 1) scan_kernel(const scan_params p)
   }
 }
 
+// ---- look-up table in global memory -------------------------------------------------------------
+// The variant for tables that do not fit shared memory (the reference's third kernel,
+// ivf_pq_compute_similarity_impl.cuh:441-460, conf_no_smem_lut): one 256-thread CTA per pair at a time,
+// its table in a slice of a global scratch buffer (written and read through L1 / L2), base differences
+// and the merge buffer in shared memory.  Same arithmetic and same result as scan_kernel -- scalar
+// fused multiply-adds in the order of the reference's chain, one rounding to the table type, entries
+// summed in subspace order, the same 64-bit keys -- without its tuning: this is the rare path.
+template <int PqBits, int LutKind, bool OutHalf, bool IsIP, int KPL>
+__global__ void __launch_bounds__(256) scan_glut_kernel(const scan_params p)
+{
+  using lut_t              = typename lut_elem<LutKind>::type;
+  constexpr uint32_t kBook = 1u << PqBits;
+  constexpr uint32_t kMask = kBook - 1u;
+  constexpr int kPerPiece  = 128 / PqBits;
+  constexpr bool kStoreAll = KPL == 0;
+  extern __shared__ __align__(16) uint8_t smem[];
+  float* s_base     = reinterpret_cast<float*>(smem);                         // [rot_dim] or [rot_dim][2]
+  uint64_t* s_merge = reinterpret_cast<uint64_t*>(smem + p.base_bytes);       // [8 warps][k]
+  const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const uint32_t lut_size = p.pq_dim << PqBits;
+  lut_t* lut = static_cast<lut_t*>(p.lut_global) + size_t(blockIdx.x) * lut_size;
+  const uint32_t n_work = *p.n_work;
+  const uint32_t k      = p.k;
+  const uint32_t len    = p.pq_len;
+  warp_topk<(KPL > 0 ? KPL : 1)> queue;
+
+  for (uint32_t w = blockIdx.x; w < n_work; w += gridDim.x) {
+    const uint4 d0       = p.work[2 * size_t(w)];
+    const uint4 d1       = p.work[2 * size_t(w) + 1];
+    const uint32_t pair  = d0.x, q = d0.y, label = d0.z, n = d0.w;
+    const uint32_t sample_offset = d1.x;
+    const uint64_t first_row     = (uint64_t(d1.z) << 32) | d1.y;
+    __syncthreads();  // the previous pair's table and merge buffer are no longer read
+    {
+      const float* rq = p.rot_q + size_t(q) * p.rot_dim;
+      const float* c  = p.centers_rot + size_t(label) * p.rot_dim;
+      for (uint32_t i = tid; i < p.rot_dim; i += 256) {
+        if constexpr (!IsIP) {
+          s_base[i] = __fsub_rn(rq[i], c[i]);
+        } else {
+          s_base[2 * i]     = rq[i];
+          s_base[2 * i + 1] = __fmul_rn(c[i], rq[i]);
+        }
+      }
+    }
+    __syncthreads();
+    {
+      const float* pqc0 = p.per_cluster ? p.pq_centers + size_t(label) * len * kBook : p.pq_centers;
+      for (uint32_t e = tid; e < lut_size; e += 256) {
+        const uint32_t j = e >> PqBits, b = e & kMask;
+        const float* pqc = pqc0 + (p.per_cluster ? size_t(0) : size_t(j) * len * kBook) + b;
+        float score      = 0.0f;
+        for (uint32_t kk = 0; kk < len; kk++) {
+          const float pq_c = pqc[size_t(kk) * kBook];
+          const uint32_t d = j * len + kk;
+          if constexpr (!IsIP) {
+            const float diff = __fsub_rn(s_base[d], pq_c);
+            score            = __fmaf_rn(diff, diff, score);
+          } else {
+            score = __fsub_rn(score, s_base[2 * d + 1]);
+            score = __fmaf_rn(-s_base[2 * d], pq_c, score);
+          }
+        }
+        if constexpr (LutKind == LUT_F32) {
+          lut[e] = score;
+        } else if constexpr (LutKind == LUT_F16) {
+          lut[e] = __float2half_rn(score);
+        } else {
+          lut[e] = fp8_encode<IsIP>(score);
+        }
+      }
+    }
+    __syncthreads();  // block-wide visibility of the table written to global memory
+    const uint32_t thr0 = kStoreAll ? 0u : *reinterpret_cast<volatile uint32_t*>(p.query_kth + q);
+    queue.init(int(k));
+    const uint32_t n_groups = (n + 31u) >> 5;
+    const uint4* src = reinterpret_cast<const uint4*>(p.codes + first_row * size_t(p.n_pieces) * 16u);
+    for (uint32_t gi = warp; gi < n_groups; gi += 8) {
+      float f  = 0.0f;
+      __half h = __ushort_as_half(0);
+      uint32_t j = 0;
+      for (uint32_t c = 0; c < p.n_pieces; c++) {
+        const uint4 v       = src[(size_t(gi) * p.n_pieces + c) * 32u + lane];
+        const uint32_t wd[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int cc = 0; cc < kPerPiece; cc++, j++) {
+          if (j < p.pq_dim) {
+            const int bit = cc * PqBits, word = bit >> 5, sh = bit & 31;
+            uint32_t code = wd[word] >> sh;
+            if (sh + PqBits > 32) { code |= wd[word + 1 > 3 ? 3 : word + 1] << (32 - sh); }
+            code &= kMask;
+            const lut_t entry = lut[size_t(j) * kBook + code];
+            if constexpr (!OutHalf) {
+              if constexpr (LutKind == LUT_F32) {
+                f = __fadd_rn(f, entry);
+              } else if constexpr (LutKind == LUT_F16) {
+                f = __fadd_rn(f, __half2float(entry));
+              } else {
+                f = __fadd_rn(f, fp8_to_float<IsIP>(entry));
+              }
+            } else {
+              if constexpr (LutKind == LUT_F16) {
+                h = __hadd(h, entry);
+              } else if constexpr (LutKind == LUT_FP8) {
+                h = __hadd(h, fp8_to_half<IsIP>(entry));
+              }
+            }
+          }
+        }
+      }
+      float score;
+      if constexpr (!OutHalf) {
+        score = p.cosine ? __fadd_rn(f, 1.0f) : f;
+      } else {
+        if (p.cosine) { h = __hadd(h, __float2half(1.0f)); }
+        score = __half2float(h);
+      }
+      const uint32_t row = gi * 32u + lane;
+      bool valid         = row < n;
+      if (p.filter_bits != nullptr && valid) {
+        const int64_t id = p.ids[first_row + row];
+        valid = id >= 0 && uint64_t(id) < p.filter_nbits && ((p.filter_bits[id >> 5] >> (id & 31)) & 1u);
+      }
+      if constexpr (kStoreAll) {
+        if (valid) { p.all_scores[size_t(q) * p.max_samples + sample_offset + row] = score; }
+      } else {
+        const uint32_t ord = float_to_ordered(score);
+        queue.offer((uint64_t(ord) << 32) | (sample_offset + row), valid && ord <= thr0);
+      }
+    }
+    if constexpr (!kStoreAll) {
+      queue.store(s_merge + size_t(warp) * k, int(k));
+      __syncthreads();
+      if (warp == 0) {
+        const uint32_t others = 7u * k;
+        for (uint32_t t0 = 0; t0 < others; t0 += 32) {
+          const uint32_t t = t0 + lane;
+          queue.offer(t < others ? s_merge[k + t] : kEmptyKey, t < others);
+        }
+        queue.store(p.out_keys + size_t(pair) * k, int(k));
+        const uint32_t kth_score = uint32_t(queue.kth() >> 32);
+        if (lane == 0 && kth_score != kEmptyScore) { atomicMin(p.query_kth + q, kth_score); }
+      }
+    }
+  }
+}
+
 // Host-side launcher of one instantiation family (defined once per PqBits in scan_inst.cu).
 void launch_scan(const scan_params& p, int pq_bits, int lut_kind, bool out_half, bool is_ip,
                  int kpl, int grid, size_t smem_bytes, cudaStream_t stream);
+// the variant with the table in global memory (p.lut_global); kpl is 0 (store every score) or 4
+void launch_scan_glut(const scan_params& p, int pq_bits, int lut_kind, bool out_half, bool is_ip,
+                      int kpl, int grid, size_t smem_bytes, cudaStream_t stream);
 
 }  // namespace cuvs_b200

@@ -97,6 +97,40 @@ void launch_types(const scan_params& p, int lut_kind, bool out_half, int kpl, in
 
 }  // namespace
 
+template <int LutKind, bool OutHalf, bool IsIP>
+void launch_glut_kpl(const scan_params& p, int kpl, int grid, size_t smem, cudaStream_t stream)
+{
+  auto go = [&](auto kernel) {
+    ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), smem);
+    kernel<<<grid, 256, smem, stream>>>(p);
+    CUDA_TRY(cudaGetLastError());
+  };
+  if (kpl == 0) {
+    go(scan_glut_kernel<PQ_BITS, LutKind, OutHalf, IsIP, 0>);
+  } else {
+    go(scan_glut_kernel<PQ_BITS, LutKind, OutHalf, IsIP, 4>);
+  }
+}
+
+template <bool IsIP>
+void launch_glut_types(const scan_params& p, int lut_kind, bool out_half, int kpl, int grid, size_t smem,
+                       cudaStream_t stream)
+{
+  if (!out_half) {
+    switch (lut_kind) {
+      case LUT_F32: launch_glut_kpl<LUT_F32, false, IsIP>(p, kpl, grid, smem, stream); break;
+      case LUT_F16: launch_glut_kpl<LUT_F16, false, IsIP>(p, kpl, grid, smem, stream); break;
+      default: launch_glut_kpl<LUT_FP8, false, IsIP>(p, kpl, grid, smem, stream); break;
+    }
+  } else {
+    switch (lut_kind) {
+      case LUT_F16: launch_glut_kpl<LUT_F16, true, IsIP>(p, kpl, grid, smem, stream); break;
+      case LUT_FP8: launch_glut_kpl<LUT_FP8, true, IsIP>(p, kpl, grid, smem, stream); break;
+      default: fail("fp32 look-up table with fp16 internal distances is not a valid combination");
+    }
+  }
+}
+
 #define SCAN_FN_NAME2(b) launch_scan_bits_##b
 #define SCAN_FN_NAME(b) SCAN_FN_NAME2(b)
 
@@ -107,6 +141,19 @@ void SCAN_FN_NAME(PQ_BITS)(const scan_params& p, int lut_kind, bool out_half, bo
     launch_types<true>(p, lut_kind, out_half, kpl, grid, smem, stream);
   } else {
     launch_types<false>(p, lut_kind, out_half, kpl, grid, smem, stream);
+  }
+}
+
+#define GLUT_FN_NAME2(b) launch_scan_glut_bits_##b
+#define GLUT_FN_NAME(b) GLUT_FN_NAME2(b)
+
+void GLUT_FN_NAME(PQ_BITS)(const scan_params& p, int lut_kind, bool out_half, bool is_ip, int kpl,
+                           int grid, size_t smem, cudaStream_t stream)
+{
+  if (is_ip) {
+    launch_glut_types<true>(p, lut_kind, out_half, kpl, grid, smem, stream);
+  } else {
+    launch_glut_types<false>(p, lut_kind, out_half, kpl, grid, smem, stream);
   }
 }
 

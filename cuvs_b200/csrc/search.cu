@@ -25,6 +25,25 @@ void launch_scan_bits_6(const scan_params&, int, bool, bool, int, int, size_t, c
 void launch_scan_bits_7(const scan_params&, int, bool, bool, int, int, size_t, cudaStream_t);
 void launch_scan_bits_8(const scan_params&, int, bool, bool, int, int, size_t, cudaStream_t);
 
+void launch_scan_glut_bits_4(const scan_params&, int, bool, bool, int, int, size_t, cudaStream_t);
+void launch_scan_glut_bits_5(const scan_params&, int, bool, bool, int, int, size_t, cudaStream_t);
+void launch_scan_glut_bits_6(const scan_params&, int, bool, bool, int, int, size_t, cudaStream_t);
+void launch_scan_glut_bits_7(const scan_params&, int, bool, bool, int, int, size_t, cudaStream_t);
+void launch_scan_glut_bits_8(const scan_params&, int, bool, bool, int, int, size_t, cudaStream_t);
+
+void launch_scan_glut(const scan_params& p, int pq_bits, int lut_kind, bool out_half, bool is_ip, int kpl,
+                      int grid, size_t smem, cudaStream_t stream)
+{
+  switch (pq_bits) {
+    case 4: launch_scan_glut_bits_4(p, lut_kind, out_half, is_ip, kpl, grid, smem, stream); break;
+    case 5: launch_scan_glut_bits_5(p, lut_kind, out_half, is_ip, kpl, grid, smem, stream); break;
+    case 6: launch_scan_glut_bits_6(p, lut_kind, out_half, is_ip, kpl, grid, smem, stream); break;
+    case 7: launch_scan_glut_bits_7(p, lut_kind, out_half, is_ip, kpl, grid, smem, stream); break;
+    case 8: launch_scan_glut_bits_8(p, lut_kind, out_half, is_ip, kpl, grid, smem, stream); break;
+    default: fail("pq_bits must be within [4, 8]");
+  }
+}
+
 void launch_scan(const scan_params& p, int pq_bits, int lut_kind, bool out_half, bool is_ip, int kpl,
                  int grid, size_t smem, cudaStream_t stream)
 {
@@ -570,7 +589,8 @@ void launch_prep(raft::resources& res, const index<int64_t>& idx, const void* qp
 int& scan_codebook_home()
 {
   // 0 = choose, 1 = never tensor memory (shared or global memory instead), 2 = choose, but never an
-  // instantiation made for one exact shape (tests compare it with the general kernel)
+  // instantiation made for one exact shape (tests compare it with the general kernel), 3 = behave as
+  // if no look-up table fitted shared memory (the variant with the table in global memory)
   static int home = 0;
   return home;
 }
@@ -595,7 +615,8 @@ scan_plan plan_scan(const raft::resources& res, const index<int64_t>& idx, int l
   const uint32_t need_col = n_m * idx.pq_len() * 4;
   const bool tmem_ok      = pqc_bytes > 0 && scan_codebook_home() != 1 && need_col <= 512 &&
                        (idx.pq_len() == 1 || idx.pq_len() == 2 || idx.pq_len() == 4);
-  for (int home = tmem_ok ? 2 : (pqc_bytes > 0 ? 1 : 0); home >= 0; home--) {
+  // (test override 3: behave as if no table fitted shared memory)
+  for (int home = tmem_ok ? 2 : (pqc_bytes > 0 ? 1 : 0); home >= 0 && scan_codebook_home() != 3; home--) {
     if (home == 1 && pqc_bytes == 0) { continue; }
     for (int g = (home == 2 ? 8 : 4); g >= 1; g >>= 1) {
       const size_t merge_bytes = round_up<size_t>(size_t(1024 / g / 32) * k * 8, 16);
@@ -628,9 +649,17 @@ scan_plan plan_scan(const raft::resources& res, const index<int64_t>& idx, int l
       }
     }
   }
-  fail("IVF-PQ search: a look-up table of %zu bytes (pq_dim=%u, pq_bits=%u) does not fit in the %d "
-       "bytes of shared memory of this GPU; use a smaller lut_dtype",
-       lut_bytes, idx.pq_dim(), idx.pq_bits(), res.smem_optin);
+  // no table fits shared memory (ivf_pq_compute_similarity_impl.cuh:441-460, conf_no_smem_lut): the
+  // table of a CTA lives in global memory; shared memory holds base differences and the merge buffer
+  plan.lut_global  = 1;
+  plan.n_groups    = 1;
+  plan.group_threads = 256;
+  plan.lut_bytes   = uint32_t(lut_bytes);
+  plan.base_bytes  = uint32_t(round_up<size_t>(size_t(idx.rot_dim()) * (is_ip ? 8 : 4), 16));
+  plan.merge_bytes = uint32_t(round_up<size_t>(size_t(8) * k * 8, 16));
+  plan.total_bytes = size_t(plan.base_bytes) + plan.merge_bytes;
+  CUVS_EXPECTS(plan.total_bytes <= limit, "IVF-PQ search: rot_dim = %u is too large for this engine", idx.rot_dim());
+  return plan;
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -750,6 +779,9 @@ void search_any(raft::resources& res, const search_params& params, const index<i
                  : (use_tc ? coarse_tc_workspace_bytes(batch, n_lists, cdim_ext)
                            : coarse_workspace_bytes(batch, n_lists, n_probes));
   const size_t o_coarse  = lay.add(coarse_ws);
+  // tables in global memory: one per CTA of the (smaller) grid of that variant
+  const uint32_t glut_grid = uint32_t(std::min<size_t>(n_pairs_max, size_t(res.sm_count) * 4));
+  const size_t o_glut      = lay.add(plan.lut_global ? size_t(glut_grid) * plan.lut_bytes : 0);
   res.ws.reserve(lay.total());
   char* ws = res.ws.base();
   auto* d_fq      = reinterpret_cast<float*>(ws + o_fq);
@@ -876,10 +908,14 @@ void search_any(raft::resources& res, const search_params& params, const index<i
       sp.base_bytes     = plan.base_bytes;
       sp.merge_bytes    = plan.merge_bytes;
       sp.allow_fixed_shape = scan_codebook_home() != 2;
-      const int grid    = int(std::min<uint32_t>(uint32_t(res.sm_count),
-                                              ceildiv<uint32_t>(n_pairs, plan.n_groups)));
-      launch_scan(sp, int(idx.pq_bits()), lut_kind, out_half, is_ip, kpl, grid, plan.total_bytes,
-                  stream);
+      if (plan.lut_global) {
+        sp.lut_global = ws + o_glut;
+        launch_scan_glut(sp, int(idx.pq_bits()), lut_kind, out_half, is_ip, store_all ? 0 : 4,
+                         int(std::min<uint32_t>(glut_grid, n_pairs)), plan.total_bytes, stream);
+      } else {
+        const int grid = int(std::min<uint32_t>(uint32_t(res.sm_count), ceildiv<uint32_t>(n_pairs, plan.n_groups)));
+        launch_scan(sp, int(idx.pq_bits()), lut_kind, out_half, is_ip, kpl, grid, plan.total_bytes, stream);
+      }
       res.launches++;
     }
 

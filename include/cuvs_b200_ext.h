@@ -48,7 +48,8 @@ CUVS_EXPORT cuvsError_t cuvsB200CoarseSelect(cuvsResources_t res, void* index /*
 CUVS_EXPORT cuvsError_t cuvsB200SetCoarseMode(int mode);
 /* No counterpart in the reference: where the fine-search kernel of cuvsIvfPqSearch keeps a
  * per-subspace PQ codebook in this process: 0 = tensor memory where it fits (the default),
- * 1 = never tensor memory (shared memory, else global memory). */
+ * 1 = never tensor memory (shared memory, else global memory), 2 = as 0 but never a kernel instantiated
+ * for one exact shape, 3 = as if no look-up table fitted shared memory (tables in global memory). */
 CUVS_EXPORT cuvsError_t cuvsB200SetScanCodebookHome(int home);
 
 /* No counterpart in the reference.  Every wait inside the tensor-core probe-selection kernel is bounded;

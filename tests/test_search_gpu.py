@@ -27,13 +27,15 @@ def ivf():
     return ivf_pq
 
 
-@pytest.fixture(autouse=True, params=["codebook-auto", "codebook-not-in-tmem"])
+@pytest.fixture(autouse=True, params=["codebook-auto", "codebook-not-in-tmem", "lut-in-global-memory"])
 def scan_codebook_home(request, ivf):
-    """Every test of this module runs twice: with the fine-search kernel keeping the per-subspace
-    codebook in tensor memory wherever it fits (the default) and with tensor memory ruled out
-    (codebook in shared or global memory)."""
+    """Every test of this module runs three times: with the fine-search kernel keeping the per-subspace
+    codebook in tensor memory wherever it fits (the default), with tensor memory ruled out (codebook in
+    shared or global memory), and with the variant for look-up tables too large for shared memory
+    (one table per CTA in global memory) forced on every shape."""
     from cuvs_b200 import _lib as L
-    L.check(L.load().cuvsB200SetScanCodebookHome(0 if request.param == "codebook-auto" else 1))
+    L.check(L.load().cuvsB200SetScanCodebookHome(
+        {"codebook-auto": 0, "codebook-not-in-tmem": 1, "lut-in-global-memory": 3}[request.param]))
     yield
     L.check(L.load().cuvsB200SetScanCodebookHome(0))
 
@@ -454,3 +456,16 @@ def test_bitset_filter_parity(ivf, oracle_mod, small_l2):
         assert_parity(d, i, do, io, 1e-5 if lut == "f32" else 1e-2, max_tie_rows=0.05)
         found = i[i != O.OUT_OF_BOUNDS]
         assert allowed[found].all()
+
+
+def test_a_table_larger_than_shared_memory_goes_to_global_memory(ivf, oracle_mod, tmp_path):
+    """pq_dim 256 x 8 bits with an fp32 table is 256 KB: no shared-memory plan exists, the search takes
+    the variant with the table in global memory (the reference's conf_no_smem_lut) and still equals
+    the oracle."""
+    O = oracle_mod
+    x, q, ix, path = build_case(O, tmp_path, "wide", n=2500, dim=256, n_lists=16, pq_dim=256, pq_bits=8, nq=40)
+    g = ivf.load(path)
+    for k, p in ((10, 6), (150, 16)):
+        d, i = gpu_search(ivf, g, q, k, p, "f32")
+        do, io = O.search(ix, q, k, n_probes=p)
+        assert_parity(d, i, do, io, 1e-5)
