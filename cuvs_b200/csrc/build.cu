@@ -411,7 +411,13 @@ __global__ void encode_kernel(const float* __restrict__ x_ext, const uint32_t* _
     }
     if (lane == 0) { ids_out[arow] = src_ids ? src_ids[row] : id_base + int64_t(row); }
   } else {
+    // interleaved == 0: row `row` of a plain output matrix (transform); == 2: a slot of a FLAT list
     uint8_t* dst = codes_out + size_t(row) * flat_row_bytes;
+    if (interleaved == 2) {
+      const uint64_t arow = row_off[label] + slots[i];
+      dst                 = codes_out + arow * flat_row_bytes;
+      if (lane == 0) { ids_out[arow] = src_ids ? src_ids[row] : id_base + int64_t(row); }
+    }
     for (uint32_t byte = lane; byte < flat_row_bytes; byte += 32) {
       uint32_t v = 0;
       // collect the bits [byte*8, byte*8+8) of the stream
@@ -762,7 +768,9 @@ void launch_encode(raft::resources& res, const index<int64_t>& idx, const float*
   encode_kernel<<<ceildiv(n, warps), warps * 32, smem, res.stream>>>(
     x_ext, labels, order, slots, n, idx.centers(), idx.rotation_matrix(), idx.rotation_is_identity(),
     idx.pq_centers(), idx.codebook_kind() == codebook_gen::PER_CLUSTER, idx.dim(), idx.dim_ext(),
-    idx.rot_dim(), idx.pq_dim(), idx.pq_len(), idx.pq_bits(), interleaved, idx.row_offsets(), codes_out,
+    idx.rot_dim(), idx.pq_dim(), idx.pq_len(), idx.pq_bits(),
+    // 0: rows of a plain output matrix; 1: slots of interleaved lists; 2: slots of flat lists
+    interleaved ? (idx.codes_layout() == list_layout::FLAT ? 2 : 1) : 0, idx.row_offsets(), codes_out,
     ids_out, src_ids, id_base, ceildiv(idx.pq_dim() * idx.pq_bits(), 8u));
   CUDA_TRY(cudaGetLastError());
   res.launches++;
@@ -790,8 +798,7 @@ void resize_lists(raft::resources& res, index<int64_t>* idx, const std::vector<u
   if (any) {
     relocate_lists_kernel<<<n_lists, 128, 0, stream>>>(old_codes.data(), old_ids.data(), old_off.data(),
                                                        keep_d.data(), idx->row_offsets(),
-                                                       idx->n_pieces() * kIndexGroupVecLen, idx->codes(),
-                                                       idx->ids());
+                                                       idx->list_row_bytes(), idx->codes(), idx->ids());
     CUDA_TRY(cudaGetLastError());
     res.launches++;
   }
@@ -813,6 +820,13 @@ void unpack_contiguous_list_data(raft::resources& res, const index<int64_t>& idx
                "rows [%u, %u) exceed the size of list %u (%u)", offset, offset + n_rows, label,
                idx.host_list_sizes()[label]);
   if (n_rows == 0) { return; }
+  if (idx.codes_layout() == list_layout::FLAT) {
+    // the rows already are what the caller asks for
+    const size_t bpv = idx.bytes_per_vector();
+    CUDA_TRY(cudaMemcpyAsync(out_codes, idx.codes() + (idx.host_row_offsets()[label] + offset) * bpv,
+                             size_t(n_rows) * bpv, cudaMemcpyDeviceToDevice, res.stream));
+    return;
+  }
   const uint8_t* list = idx.codes() + idx.host_row_offsets()[label] * size_t(idx.n_pieces()) * 16;
   unpack_contiguous_kernel<<<ceildiv(n_rows, 128u), 128, 0, res.stream>>>(
     list, n_rows, offset, idx.pq_dim(), idx.pq_bits(), ceildiv(idx.pq_dim() * idx.pq_bits(), 8u), out_codes);
@@ -851,6 +865,9 @@ void check_rows(const index<int64_t>& idx, uint32_t label, uint32_t offset, uint
 }
 uint8_t* list_base(const index<int64_t>& idx, uint32_t label)
 {
+  // the helpers that read or write single codes address the interleaved layout (as the reference's do)
+  CUVS_EXPECTS(idx.codes_layout() == list_layout::INTERLEAVED,
+               "this helper supports the INTERLEAVED codes layout only");
   return idx.codes() + idx.host_row_offsets()[label] * size_t(idx.n_pieces()) * kIndexGroupVecLen;
 }
 // Grow list `label` by n_rows, write the new source ids; returns the first new row.
@@ -893,6 +910,12 @@ void pack_rows(raft::resources& res, index<int64_t>* idx, const uint8_t* codes, 
   CUVS_EXPECTS(idx != nullptr, "null index");
   check_rows(*idx, label, offset, n_rows);
   if (n_rows == 0) { return; }
+  if (kContiguous && idx->codes_layout() == list_layout::FLAT) {
+    const size_t bpv = idx->bytes_per_vector();
+    CUDA_TRY(cudaMemcpyAsync(idx->codes() + (idx->host_row_offsets()[label] + offset) * bpv, codes,
+                             size_t(n_rows) * bpv, cudaMemcpyDefault, res.stream));
+    return;
+  }
   const uint64_t n_threads = uint64_t(n_rows) * idx->n_pieces();
   pack_codes_kernel<kContiguous><<<unsigned(ceildiv<uint64_t>(n_threads, 256)), 256, 0, res.stream>>>(
     codes, n_rows, offset, idx->pq_dim(), idx->pq_bits(), idx->n_pieces(),
@@ -1113,13 +1136,11 @@ void build_any(raft::resources& res, const index_params& params, const void* dat
                int64_t n_rows_i, uint32_t dim, bool on_device, index<int64_t>* out)
 {
   CUVS_EXPECTS(n_rows_i > 0 && dim > 0, "build: empty dataset");
-  CUVS_EXPECTS(params.codes_layout == list_layout::INTERLEAVED,
-               "this engine builds the INTERLEAVED codes layout only");
   CUVS_EXPECTS(params.n_lists > 0, "n_lists must be positive");
   const uint64_t n_rows     = uint64_t(n_rows_i);
   const cudaStream_t stream = res.stream;
   index<int64_t> idx(params.metric, params.codebook_kind, params.n_lists, dim, params.pq_bits,
-                     params.pq_dim, params.conservative_memory_allocation);
+                     params.pq_dim, params.conservative_memory_allocation, params.codes_layout);
   const uint32_t n_lists = idx.n_lists(), dim_ext = idx.dim_ext(), rot_dim = idx.rot_dim();
   const uint32_t book = idx.pq_book_size(), len = idx.pq_len(), pq_dim = idx.pq_dim();
   const label_ctx lc  = labeling_of(idx.metric());

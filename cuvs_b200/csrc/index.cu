@@ -26,14 +26,15 @@ using cuvs_b200::ceildiv;
 using cuvs_b200::round_up;
 
 index<int64_t>::index(DistanceType metric, codebook_gen kind, uint32_t n_lists, uint32_t dim,
-                      uint32_t pq_bits, uint32_t pq_dim, bool conservative)
+                      uint32_t pq_bits, uint32_t pq_dim, bool conservative, list_layout codes_layout)
   : metric_(metric),
     codebook_kind_(kind),
     n_lists_(n_lists),
     dim_(dim),
     pq_bits_(pq_bits),
     pq_dim_(pq_dim == 0 ? calculate_pq_dim(dim) : pq_dim),
-    conservative_(conservative)
+    conservative_(conservative),
+    layout_(codes_layout)
 {
   // ivf_pq_index.cu:599-609
   CUVS_EXPECTS(pq_bits_ >= 4 && pq_bits_ <= 8,
@@ -169,7 +170,7 @@ void index<int64_t>::allocate_lists(const std::vector<uint32_t>& sizes, cudaStre
     h_row_off_[l + 1] = h_row_off_[l] + round_up<uint64_t>(sizes[l], kIndexGroupSize);
   }
   const uint64_t rows = h_row_off_.back();
-  codes_.resize(std::max<uint64_t>(rows, 32) * n_pieces() * kIndexGroupVecLen);
+  codes_.resize(round_up<uint64_t>(std::max<uint64_t>(rows, 32) * list_row_bytes(), 16));
   ids_.resize(std::max<uint64_t>(rows, 32));
   CUDA_TRY(cudaMemsetAsync(codes_.data(), 0, codes_.size(), stream));
   fill_i64_kernel<<<ceildiv<size_t>(ids_.size(), 256), 256, 0, stream>>>(ids_.data(), ids_.size(),
@@ -422,8 +423,9 @@ void serialize(raft::resources& res, std::ostream& os, const index<int64_t>& idx
   write_scalar<bool>(os, idx.conservative_memory_allocation());
   write_scalar<int32_t>(os, int32_t(idx.metric()));
   write_scalar<int32_t>(os, int32_t(idx.codebook_kind()));
-  write_scalar<int32_t>(os, int32_t(list_layout::INTERLEAVED));
+  write_scalar<int32_t>(os, int32_t(idx.codes_layout()));
   write_scalar<uint32_t>(os, idx.n_lists());
+  const bool flat = idx.codes_layout() == list_layout::FLAT;
 
   const uint64_t first = idx.codebook_kind() == codebook_gen::PER_SUBSPACE ? idx.pq_dim() : idx.n_lists();
   write_device_f32(res, os, idx.pq_centers(), {first, idx.pq_len(), idx.pq_book_size()});
@@ -436,7 +438,7 @@ void serialize(raft::resources& res, std::ostream& os, const index<int64_t>& idx
 
   // Lists: stage the arenas through host memory in chunks of whole lists.
   const auto& off          = idx.host_row_offsets();
-  const uint64_t row_bytes = uint64_t(idx.n_pieces()) * kIndexGroupVecLen;
+  const uint64_t row_bytes = idx.list_row_bytes();
   const uint64_t chunk_rows = std::max<uint64_t>(1u << 20, 1);  // rows per staging chunk (target)
   std::vector<uint8_t> hcodes;
   std::vector<int64_t> hids;
@@ -457,10 +459,17 @@ void serialize(raft::resources& res, std::ostream& os, const index<int64_t>& idx
     for (uint32_t i = l; i < l_end; i++) {
       write_scalar<uint32_t>(os, sizes[i]);
       if (sizes[i] == 0) { continue; }
-      const uint64_t g = ceildiv<uint64_t>(sizes[i], kIndexGroupSize);
-      write_header(os, "|u1", {g, idx.n_pieces(), kIndexGroupSize, kIndexGroupVecLen});
-      os.write(reinterpret_cast<const char*>(hcodes.data() + (off[i] - r0) * row_bytes),
-               std::streamsize(g * kIndexGroupSize * row_bytes));
+      if (flat) {
+        // ivf_list.cuh:108-132 with list_spec_flat: exactly `size` rows of bytes_per_vector bytes
+        write_header(os, "|u1", {sizes[i], idx.bytes_per_vector()});
+        os.write(reinterpret_cast<const char*>(hcodes.data() + (off[i] - r0) * row_bytes),
+                 std::streamsize(uint64_t(sizes[i]) * row_bytes));
+      } else {
+        const uint64_t g = ceildiv<uint64_t>(sizes[i], kIndexGroupSize);
+        write_header(os, "|u1", {g, idx.n_pieces(), kIndexGroupSize, kIndexGroupVecLen});
+        os.write(reinterpret_cast<const char*>(hcodes.data() + (off[i] - r0) * row_bytes),
+                 std::streamsize(g * kIndexGroupSize * row_bytes));
+      }
       write_header(os, "<i8", {sizes[i]});
       os.write(reinterpret_cast<const char*>(hids.data() + (off[i] - r0)),
                std::streamsize(uint64_t(sizes[i]) * 8));
@@ -500,6 +509,7 @@ void serialize_list_sharded(const std::vector<raft::resources*>& res, std::ostre
 {
   CUVS_EXPECTS(!shards.empty() && shards.size() == res.size(), "serialize_list_sharded: no shards");
   const index<int64_t>& m = *shards[0];
+  CUVS_EXPECTS(m.codes_layout() == list_layout::INTERLEAVED, "list-sharded indexes use the INTERLEAVED layout");
   const uint32_t n_lists  = m.n_lists();
   std::vector<uint32_t> sizes(n_lists, 0);
   std::vector<int> holder(n_lists, 0);
@@ -594,15 +604,15 @@ void deserialize(raft::resources& res, std::istream& is, index<int64_t>* out, in
   CUVS_EXPECTS(kind == 0 || kind == 1, "ivf_pq::deserialize: invalid codebook_gen value %d", kind);
   CUVS_EXPECTS(layout == 0 || layout == 1, "ivf_pq::deserialize: invalid list_layout value %d",
                layout);
-  CUVS_EXPECTS(layout == 1,
-               "IVF-PQ search requires INTERLEAVED codes layout. FLAT layout is not supported.");
   CUVS_EXPECTS(n_lists > 0 && n_lists <= kMaxIvfNLists,
                "ivf_pq::deserialize: n_lists=%u exceeds maximum %u", n_lists, kMaxIvfNLists);
   CUVS_EXPECTS(dim > 0 && dim <= (1u << 20) && pq_dim > 0 && pq_dim <= dim * 8u + 8u,
                "ivf_pq::deserialize: implausible dim=%u / pq_dim=%u", dim, pq_dim);
   CUVS_EXPECTS(n_rows >= 0, "ivf_pq::deserialize: negative size");
 
-  index<int64_t> idx(DistanceType(metric), codebook_gen(kind), n_lists, dim, pq_bits, pq_dim, cma);
+  index<int64_t> idx(DistanceType(metric), codebook_gen(kind), n_lists, dim, pq_bits, pq_dim, cma,
+                     list_layout(layout));
+  const bool flat = layout == int(list_layout::FLAT);
   read_device_f32(res, is, idx.pq_centers(), idx.pq_centers_size(), "pq_centers");
   read_device_f32(res, is, idx.centers(), uint64_t(n_lists) * idx.dim_ext(), "centers");
   read_device_f32(res, is, idx.centers_rot(), uint64_t(n_lists) * idx.rot_dim(), "centers_rot");
@@ -623,7 +633,7 @@ void deserialize(raft::resources& res, std::istream& is, index<int64_t>* out, in
   }
   idx.allocate_lists(kept, res.stream);
 
-  const uint64_t row_bytes = uint64_t(idx.n_pieces()) * kIndexGroupVecLen;
+  const uint64_t row_bytes = idx.list_row_bytes();
   const auto& off          = idx.host_row_offsets();
   // Consecutive lists are consecutive in the arenas, so payloads are staged back to back and
   // flushed with one copy per arena.
@@ -650,8 +660,10 @@ void deserialize(raft::resources& res, std::istream& is, index<int64_t>* out, in
                  sizes[l]);
     if (sz == 0) { continue; }
     const uint64_t rows = round_up<uint64_t>(sz, kIndexGroupSize);
+    // rows the record holds: whole 32-row groups (interleaved) or exactly `sz` (flat)
+    const uint64_t file_rows = flat ? uint64_t(sz) : rows;
     if (kept[l] == 0) {
-      skip_array(is, 1, rows * row_bytes, "list codes");
+      skip_array(is, 1, file_rows * row_bytes, "list codes");
       skip_array(is, 8, sz, "list indices");
       continue;
     }
@@ -659,7 +671,7 @@ void deserialize(raft::resources& res, std::istream& is, index<int64_t>* out, in
     size_t c0 = hcodes.size(), i0 = hids.size();
     hcodes.resize(c0 + rows * row_bytes);
     hids.resize(i0 + rows, kInvalidRecord);
-    read_array(is, hcodes.data() + c0, 1, rows * row_bytes, "list codes");
+    read_array(is, hcodes.data() + c0, 1, file_rows * row_bytes, "list codes");
     read_array(is, hids.data() + i0, 8, sz, "list indices");
     if (hids.size() >= stage_rows) { flush(); }
   }

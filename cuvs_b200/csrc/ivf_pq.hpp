@@ -162,12 +162,22 @@ class index<int64_t> {
  public:
   index() = default;
   index(DistanceType metric, codebook_gen kind, uint32_t n_lists, uint32_t dim, uint32_t pq_bits,
-        uint32_t pq_dim, bool conservative_memory_allocation);
+        uint32_t pq_dim, bool conservative_memory_allocation,
+        list_layout codes_layout = list_layout::INTERLEAVED);
 
   // observers, same names as the reference
   DistanceType metric() const { return metric_; }
   codebook_gen codebook_kind() const { return codebook_kind_; }
-  list_layout codes_layout() const { return list_layout::INTERLEAVED; }
+  // INTERLEAVED (searchable) or FLAT: every vector's codes as one bit-packed row of
+  // ceil(pq_dim * pq_bits / 8) bytes (list_spec_flat, ivf_pq.hpp:308-360; built, extended, stored and
+  // unpacked, but not searched -- as in the reference)
+  list_layout codes_layout() const { return layout_; }
+  uint32_t bytes_per_vector() const { return cuvs_b200::ceildiv(pq_dim_ * pq_bits_, 8u); }
+  // bytes one row of a list takes in the codes arena
+  uint32_t list_row_bytes() const
+  {
+    return layout_ == list_layout::FLAT ? bytes_per_vector() : n_pieces() * kIndexGroupVecLen;
+  }
   int64_t size() const { return size_; }
   uint32_t dim() const { return dim_; }
   uint32_t dim_ext() const { return cuvs_b200::round_up(dim_ + 1, 8u); }  // ivf_pq_index.cu:78-81
@@ -252,6 +262,7 @@ class index<int64_t> {
   uint32_t n_lists_ = 0, dim_ = 0, pq_bits_ = 8, pq_dim_ = 0;
   bool conservative_          = false;
   bool rotation_is_identity_  = false;
+  list_layout layout_         = list_layout::INTERLEAVED;
 };
 
 // ---- free functions (ivf_pq.hpp:702-2111) -----------------------------------------------------

@@ -681,6 +681,8 @@ void check_search_params(const raft::resources& res, const search_params& params
                k, size_t(idx.size()));
   CUVS_EXPECTS(params.n_probes > 0,
                "n_probes (number of clusters to probe in the search) must be positive.");
+  CUVS_EXPECTS(idx.codes_layout() == list_layout::INTERLEAVED,
+               "IVF-PQ search requires INTERLEAVED codes layout. FLAT layout is not supported for GPU search.");
   // ivf_pq_search.cuh:958-966
   CUVS_EXPECTS(params.coarse_search_dtype == CUDA_R_32F || params.coarse_search_dtype == CUDA_R_16F ||
                  params.coarse_search_dtype == CUDA_R_8I,

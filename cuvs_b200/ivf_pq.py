@@ -34,7 +34,8 @@ class IndexParams:
     def __init__(self, *, n_lists=1024, metric="sqeuclidean", metric_arg=2.0, kmeans_n_iters=20,
                  kmeans_trainset_fraction=0.5, pq_bits=8, pq_dim=0, codebook_kind="subspace",
                  force_random_rotation=False, add_data_on_build=True,
-                 conservative_memory_allocation=False, max_train_points_per_pq_code=256):
+                 conservative_memory_allocation=False, max_train_points_per_pq_code=256,
+                 codes_layout="interleaved"):
         lib = L.load()
         self._p = C.POINTER(L.IndexParamsStruct)()
         L.check(lib.cuvsIvfPqIndexParamsCreate(C.byref(self._p)))
@@ -55,6 +56,9 @@ class IndexParams:
         p.force_random_rotation = force_random_rotation
         p.conservative_memory_allocation = conservative_memory_allocation
         p.max_train_points_per_pq_code = max_train_points_per_pq_code
+        if codes_layout not in ("flat", "interleaved"):
+            raise ValueError("codes_layout must be 'flat' or 'interleaved'")
+        p.codes_layout = 0 if codes_layout == "flat" else 1
 
     def __del__(self):
         try:

@@ -285,6 +285,9 @@ class OracleIndex:
     list_codes: list = field(default_factory=list)   # per list u8 [groups, pieces, 32, 16]
     list_ids: list = field(default_factory=list)     # per list i64 [size]
     conservative_memory_allocation: bool = False
+    # 1 = INTERLEAVED (searchable); 0 = FLAT: list_codes[l] is u8 [size, ceil(pq_dim * pq_bits / 8)],
+    # one bit-packed row per vector (cpp/include/cuvs/neighbors/ivf_pq.hpp:308-360)
+    codes_layout: int = 1
     _flat: tuple | None = None
 
     @property
@@ -305,6 +308,8 @@ class OracleIndex:
 
     # -- flat arrays the C library walks -------------------------------------------------------
     def flat(self):
+        if self.codes_layout != 1:
+            raise ValueError("IVF-PQ search requires INTERLEAVED codes layout")
         if self._flat is None:
             lb = np.array([list_bytes(int(s), self.pq_dim, self.pq_bits) for s in self.list_sizes],
                           dtype=np.uint64)
@@ -346,7 +351,7 @@ class OracleIndex:
             write_record(f, np.bool_(self.conservative_memory_allocation))
             write_record(f, np.int32(self.metric))
             write_record(f, np.int32(self.codebook_kind))
-            write_record(f, np.int32(1))  # list_layout::INTERLEAVED
+            write_record(f, np.int32(self.codes_layout))
             write_record(f, np.uint32(self.n_lists))
             write_record(f, self.pq_centers.astype(np.float32))
             write_record(f, self.centers.astype(np.float32))
@@ -359,8 +364,12 @@ class OracleIndex:
                 write_record(f, np.uint32(s))
                 if s == 0:
                     continue
-                g = (s + 31) // 32
-                write_record(f, self.list_codes[l].reshape(-1)[:g * np_ * 512].reshape(g, np_, 32, 16))
+                if self.codes_layout == 0:
+                    bpv = (self.pq_dim * self.pq_bits + 7) // 8
+                    write_record(f, np.ascontiguousarray(self.list_codes[l], dtype=np.uint8).reshape(s, bpv))
+                else:
+                    g = (s + 31) // 32
+                    write_record(f, self.list_codes[l].reshape(-1)[:g * np_ * 512].reshape(g, np_, 32, 16))
                 write_record(f, np.asarray(self.list_ids[l][:s], dtype=np.int64))
         finally:
             if isinstance(path_or_file, (str, os.PathLike)):
@@ -381,8 +390,8 @@ class OracleIndex:
             metric = int(read_record(f))
             kind = int(read_record(f))
             layout = int(read_record(f))
-            if layout != 1:
-                raise ValueError("only the INTERLEAVED list layout is searchable")
+            if layout not in (0, 1):
+                raise ValueError(f"invalid list_layout value {layout}")
             n_lists = int(read_record(f))
             pq_centers = read_record(f).astype(np.float32)
             centers = read_record(f).astype(np.float32)
@@ -399,7 +408,7 @@ class OracleIndex:
                 codes.append(read_record(f).astype(np.uint8))
                 ids.append(read_record(f).astype(np.int64))
             ix = OracleIndex(metric, kind, dim, pq_dim, pq_bits, n_lists, pq_centers, centers,
-                             centers_rot, rotation, list_sizes, codes, ids, cma)
+                             centers_rot, rotation, list_sizes, codes, ids, cma, layout)
             assert ix.size == n_rows
             return ix
         finally:

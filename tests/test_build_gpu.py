@@ -129,3 +129,40 @@ def test_transform_equals_stored_codes(ivf):
         stored = g.list_data(l).cpu().numpy()
         assert (labels[stored_ids] == l).all()
         assert (codes[stored_ids] == stored).all()
+
+
+def test_flat_codes_layout_builds_extends_and_round_trips_but_is_not_searched(oracle_mod, tmp_path):
+    """codes_layout = FLAT (list_spec_flat, cpp/include/cuvs/neighbors/ivf_pq.hpp:308-360): every vector's
+    codes are one bit-packed row.  Such an index is built, extended, written, read and unpacked; its rows
+    are the rows `unpack_contiguous_list_data` gives for the interleaved index of the same build; the
+    search refuses it with the reference's message (ivf_pq_search.cuh:915-917)."""
+    import torch
+    from cuvs_b200 import ivf_pq
+    from cuvs_b200._lib import CuvsError
+    O = oracle_mod
+    x = make_mixture(5000, 40, 30, 0.2, seed=21)
+    xd = torch.from_numpy(x).cuda()
+    kw = dict(n_lists=20, pq_dim=20, pq_bits=6, kmeans_n_iters=4)
+    inter = ivf_pq.build(ivf_pq.IndexParams(**kw), xd[:4000])
+    flat = ivf_pq.build(ivf_pq.IndexParams(codes_layout="flat", **kw), xd[:4000])
+    ivf_pq.extend(inter, xd[4000:], torch.arange(4000, 5000, device="cuda"))
+    ivf_pq.extend(flat, xd[4000:], torch.arange(4000, 5000, device="cuda"))
+    assert len(flat) == 5000 and (flat.list_sizes == inter.list_sizes).all()
+    for l in (0, 7, 19):
+        assert (flat.list_data(l) == inter.list_data(l)).all()
+        assert (flat.list_indices(l) == inter.list_indices(l)).all()
+    # file: the layout scalar and per-list [size, bytes_per_vector] records
+    path = str(tmp_path / "flat.ivfpq")
+    ivf_pq.save(path, flat)
+    ix = O.OracleIndex.load(path)
+    assert ix.codes_layout == 0 and ix.size == 5000
+    for l in (0, 7, 19):
+        n = int(ix.list_sizes[l])
+        assert ix.list_codes[l].shape == (n, 15)
+        assert (ix.list_codes[l] == flat.list_data(l).cpu().numpy()).all()
+    ix.save(str(tmp_path / "flat2.ivfpq"))
+    assert open(path, "rb").read() == open(str(tmp_path / "flat2.ivfpq"), "rb").read()
+    back = ivf_pq.load(path)
+    assert (back.list_data(7) == flat.list_data(7)).all()
+    with pytest.raises(CuvsError, match="FLAT layout is not supported"):
+        ivf_pq.search(ivf_pq.SearchParams(n_probes=4), back, xd[:8].contiguous(), 5)
