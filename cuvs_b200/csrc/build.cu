@@ -394,7 +394,7 @@ __global__ void encode_kernel(const float* __restrict__ x_ext, const uint32_t* _
     if (lane == 0) { s_code[j] = uint8_t(best_b == 0xFFFFFFFFu ? 0 : best_b); }
   }
   __syncwarp();
-  if (interleaved) {
+  if (interleaved == 1) {
     const uint32_t cpp      = 128u / bits;
     const uint32_t n_pieces = ceildiv(pq_dim, cpp);
     const uint64_t arow     = row_off[label] + slots[i];
