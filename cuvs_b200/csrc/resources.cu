@@ -1,8 +1,41 @@
 #include "common.hpp"
 
+#include <nvtx3/nvToolsExt.h>
+
 #include <mutex>
 
 namespace cuvs_b200 {
+
+namespace {
+nvtxDomainHandle_t nvtx_domain()
+{
+  static nvtxDomainHandle_t d = nvtxDomainCreateA("cuvs");
+  return d;
+}
+}  // namespace
+
+nvtx_range::nvtx_range(const char* fmt, ...)
+{
+  nvtxDomainHandle_t d = nvtx_domain();
+  if (d == nullptr) { return; }  // no tool attached: the domain handle is null and nothing is recorded
+  char buf[256];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof(buf), fmt, ap);
+  va_end(ap);
+  nvtxEventAttributes_t attr{};
+  attr.version       = NVTX_VERSION;
+  attr.size          = NVTX_EVENT_ATTRIB_STRUCT_SIZE;
+  attr.messageType   = NVTX_MESSAGE_TYPE_ASCII;
+  attr.message.ascii = buf;
+  nvtxDomainRangePushEx(d, &attr);
+  pushed_ = true;
+}
+
+nvtx_range::~nvtx_range()
+{
+  if (pushed_) { nvtxDomainRangePop(nvtx_domain()); }
+}
 
 void ensure_dynamic_smem(const void* kernel, size_t bytes)
 {

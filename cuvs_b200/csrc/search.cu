@@ -711,6 +711,8 @@ void search_any(raft::resources& res, const search_params& params, const index<i
                 const void* queries, elem_t qtype, uint32_t n_queries, uint32_t k,
                 int64_t* neighbors, float* distances, const uint32_t* given_probes, bitset_view filter)
 {
+  nvtx_range fun_scope("ivf_pq::search(n_queries = %u, n_probes = %u, k = %u, dim = %zu)", n_queries,
+                       params.n_probes, k, size_t(idx.dim()));
   check_search_params(res, params, idx, k);
   const bool coarse_i8 = params.coarse_search_dtype == CUDA_R_8I;
   const bool coarse_h  = params.coarse_search_dtype == CUDA_R_16F;
@@ -803,6 +805,7 @@ void search_any(raft::resources& res, const search_params& params, const index<i
     const uint32_t n_pairs = nq * n_probes;
     const char* qptr       = static_cast<const char*>(queries) + size_t(q0) * idx.dim() * elem_size(qtype);
 
+    nvtx_range batch_scope("ivf_pq::search-batch(queries: %u - %u)", q0, q0 + nq);
     raft::resources::stage_events ev{};
     const bool stats = res.stats_enabled;
     if (stats) { res.stats_mark(ev, 0); }
@@ -813,6 +816,9 @@ void search_any(raft::resources& res, const search_params& params, const index<i
 
     if (stats) { res.stats_mark(ev, 1); }
     // 2. coarse selection: probes sorted by (score, list id)
+    {
+    nvtx_range select_scope("ivf_pq::search::select_clusters(n_probes = %u, n_queries = %u, n_lists = %u, dim = %u)",
+                            n_probes, nq, n_lists, idx.dim());
     if (given_probes) {
       CUDA_TRY(cudaMemcpyAsync(d_probes, given_probes + size_t(q0) * n_probes, size_t(nq) * n_probes * 4,
                                cudaMemcpyDeviceToDevice, stream));
@@ -837,7 +843,10 @@ void search_any(raft::resources& res, const search_params& params, const index<i
       select_clusters(res, idx.centers(), n_lists, idx.dim_ext(), is_l2 ? -2.0f : -1.0f, d_fq, nq,
                       n_probes, d_probes, nullptr, d_coarse, coarse_ws);
     }
+    }
 
+    nvtx_range worker_scope("ivf_pq::search-worker(n_queries = %u, n_probes = %u, k = %u, dim = %zu)", nq, n_probes,
+                            k, size_t(idx.dim()));
     if (stats) { res.stats_mark(ev, 2); }
     // 3. sample offsets + work list of the scan
     if (!stats && n_pairs <= 4096) {
