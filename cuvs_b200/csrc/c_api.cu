@@ -414,7 +414,7 @@ extern "C" cuvsError_t cuvsIvfPqBuildPrecomputed(cuvsResources_t res, cuvsIvfPqI
     auto* r   = res_of(res);
     auto ip   = convert(*params);
     auto* ix  = new index_t(ip.metric, ip.codebook_kind, ip.n_lists, dim, ip.pq_bits, ip.pq_dim,
-                            ip.conservative_memory_allocation);
+                            ip.conservative_memory_allocation, ip.codes_layout);
     try {
       auto* pqc = static_cast<float*>(checked_data(pq_centers, kDLFloat, 32, 3, true, "pq_centers"));
       auto* cen = static_cast<float*>(checked_data(centers, kDLFloat, 32, 2, true, "centers"));

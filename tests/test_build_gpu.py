@@ -143,10 +143,15 @@ def test_flat_codes_layout_builds_extends_and_round_trips_but_is_not_searched(or
     x = make_mixture(5000, 40, 30, 0.2, seed=21)
     xd = torch.from_numpy(x).cuda()
     kw = dict(n_lists=20, pq_dim=20, pq_bits=6, kmeans_n_iters=4)
-    inter = ivf_pq.build(ivf_pq.IndexParams(**kw), xd[:4000])
-    flat = ivf_pq.build(ivf_pq.IndexParams(codes_layout="flat", **kw), xd[:4000])
-    ivf_pq.extend(inter, xd[4000:], torch.arange(4000, 5000, device="cuda"))
-    ivf_pq.extend(flat, xd[4000:], torch.arange(4000, 5000, device="cuda"))
+    # one trained model, two empty indexes made from it (two independent trainings need not agree to the
+    # last bit: the k-means sums are accumulated with atomics), filled by the same two extend calls
+    model = ivf_pq.build(ivf_pq.IndexParams(add_data_on_build=False, **kw), xd[:4000])
+    parts = (model.pq_centers, model.centers, model.centers_rot, model.rotation_matrix)
+    inter = ivf_pq.build_precomputed(ivf_pq.IndexParams(**kw), 40, *parts)
+    flat = ivf_pq.build_precomputed(ivf_pq.IndexParams(codes_layout="flat", **kw), 40, *parts)
+    for index in (inter, flat):
+        ivf_pq.extend(index, xd[:4000], torch.arange(0, 4000, device="cuda"))
+        ivf_pq.extend(index, xd[4000:], torch.arange(4000, 5000, device="cuda"))
     assert len(flat) == 5000 and (flat.list_sizes == inter.list_sizes).all()
     for l in (0, 7, 19):
         assert (flat.list_data(l) == inter.list_data(l)).all()
