@@ -43,8 +43,12 @@ int main(int argc, char** argv)
   ip.kmeans_n_iters = 5;
   auto index = ivf_pq::build(res, ip, raft::make_host_matrix_view<const float, int64_t>(x.data(), n, dim));
   CHECK(index.size() == n && index.dim() == dim && index.pq_dim() == 16 && index.n_lists() == 32);
+  // a non-empty index wants the ids of the new rows (ivf_pq_build.cuh: "You must pass data indices
+  // when the index is non-empty.")
+  std::vector<int64_t> more_ids(size_t(n_more), 0);
+  for (int64_t i = 0; i < n_more; i++) { more_ids[size_t(i)] = n + i; }
   ivf_pq::extend(res, raft::make_host_matrix_view<const float, int64_t>(x.data() + size_t(n) * dim, n_more, dim),
-                 nullptr, &index);
+                 more_ids.data(), &index);
   CHECK(index.size() == n + n_more);
 
   float *d_q = nullptr, *d_dist = nullptr;
