@@ -186,7 +186,9 @@ __global__ void chunk_and_count_kernel(const uint32_t* __restrict__ probes,
     if (p < n_probes) {
       const uint32_t label = probes[size_t(q) * n_probes + p];
       v                    = label < n_lists ? list_sizes[label] : 0u;  // a list id out of range (caller-given probes) scans nothing
-      if (v > 0) { atomicAdd(list_count + label, 1u); }  // empty lists never reach the work list
+      // empty lists never reach the work list; the pairs of every query's nearest probe form a first
+      // segment of the work list (buckets [0, n_lists)), all other pairs a second one
+      if (v > 0) { atomicAdd(list_count + label + (p == 0 ? 0u : n_lists), 1u); }
     }
 #pragma unroll
     for (int d = 1; d < 32; d <<= 1) {
@@ -275,9 +277,10 @@ __global__ void scan_stats_kernel(const uint32_t* __restrict__ list_count,
 {
   const uint32_t l = blockIdx.x * blockDim.x + threadIdx.x;
   unsigned long long a = 0, b = 0;
-  if (l < n_lists && list_count[l] > 0) {
+  const uint32_t cnt = l < n_lists ? list_count[l] + list_count[n_lists + l] : 0u;  // both segments
+  if (cnt > 0) {
     const unsigned long long g = (list_sizes[l] + 31u) >> 5;
-    a = g * list_count[l];
+    a = g * cnt;
     b = g;
   }
 #pragma unroll
@@ -291,7 +294,11 @@ __global__ void scan_stats_kernel(const uint32_t* __restrict__ list_count,
   }
 }
 
-// Work list of the scan kernel, ordered by list: one 32-byte descriptor per (query, probe) pair
+// Work list of the scan kernel: first the pairs of every query's nearest probe, ordered by list, then all
+// other pairs, ordered by list.  The first segment gives every query a bound on its k-th best score
+// early, so that the rest of the scan discards most candidates (and, for L2, stops their look-ups)
+// sooner; within a segment the order by list keeps concurrent groups on the same bytes in L2.
+// One 32-byte descriptor per (query, probe) pair
 // {pair id, query, list, list size, sample offset, first row of the list (lo, hi), 0}.
 __global__ void scatter_pairs_kernel(const uint32_t* __restrict__ probes,
                                      const uint32_t* __restrict__ chunk_index,
@@ -314,7 +321,7 @@ __global__ void scatter_pairs_kernel(const uint32_t* __restrict__ probes,
   }
   const uint32_t q     = i / n_probes;
   const uint32_t pi    = i - q * n_probes;
-  const uint32_t pos   = atomicAdd(cursor + label, 1u);
+  const uint32_t pos   = atomicAdd(cursor + label + (pi == 0 ? 0u : n_lists), 1u);
   const uint64_t ro    = row_off[label];
   work[2 * size_t(pos)]     = make_uint4(i, q, label, list_sizes[label]);
   work[2 * size_t(pos) + 1] = make_uint4(pi > 0 ? chunk_index[i - 1] : 0u, uint32_t(ro), uint32_t(ro >> 32), 0u);
@@ -770,7 +777,7 @@ void search_any(raft::resources& res, const search_params& params, const index<i
   const size_t o_probes  = lay.add(n_pairs_max * 4);
   const size_t o_chunk   = lay.add(n_pairs_max * 4);
   const size_t o_order   = lay.add(n_pairs_max * 32);
-  const size_t o_count   = lay.add((size_t(n_lists) + 1) * 4);
+  const size_t o_count   = lay.add((size_t(n_lists) * 2 + 1) * 4);  // two segments of buckets, one per list each
   const size_t o_kth     = lay.add(size_t(batch) * 4);
   const size_t o_counter = lay.add(256);
   const size_t o_keys    = lay.add(store_all ? size_t(batch) * k * 8 : n_pairs_max * k * 8);
@@ -859,7 +866,7 @@ void search_any(raft::resources& res, const search_params& params, const index<i
       res.launches += 1;
     } else {
       // counting sort of the pairs by list
-      CUDA_TRY(cudaMemsetAsync(d_count, 0, (size_t(n_lists) + 1) * 4, stream));
+      CUDA_TRY(cudaMemsetAsync(d_count, 0, (size_t(n_lists) * 2 + 1) * 4, stream));
       chunk_and_count_kernel<<<ceildiv<uint32_t>(nq * 32, 256), 256, 0, stream>>>(
         d_probes, idx.list_sizes(), n_lists, nq, n_probes, d_chunk, d_count);
       if (stats) {
@@ -867,8 +874,8 @@ void search_any(raft::resources& res, const search_params& params, const index<i
                                                                                 n_lists, res.d_stats);
         res.stat_pairs += n_pairs;
       }
-      // d_counter[0] = 0 (work counter), d_counter[1] = d_count[n_lists] = number of work items
-      exclusive_scan_kernel<<<1, 1024, 0, stream>>>(d_count, n_lists, d_counter);
+      // d_counter[0] = 0 (work counter), d_counter[1] = d_count[2 * n_lists] = number of work items
+      exclusive_scan_kernel<<<1, 1024, 0, stream>>>(d_count, n_lists * 2, d_counter);
       scatter_pairs_kernel<<<ceildiv<uint32_t>(n_pairs, 256), 256, 0, stream>>>(
         d_probes, d_chunk, idx.list_sizes(), n_lists, idx.row_offsets(), n_pairs, n_probes, d_count, d_order,
         store_all ? nullptr : d_keys, k, d_kth, nq);
