@@ -631,7 +631,7 @@ struct accum {
 // Codes of one 16-byte piece -> LUT lookups.  `row_a` = shared-space address of the LUT row of the
 // piece's first subspace; `n_valid` = codes used in this piece.  The row offset of code C is an
 // immediate of the load, so a lookup costs: extract, scale-and-add, load, (convert,) add.
-template <int PqBits, int LutKind, bool OutHalf, bool IsIP, bool Full, int C>
+template <int PqBits, int LutKind, bool OutHalf, bool IsIP, bool Full, int C, int CEND = 128 / PqBits>
 __device__ __forceinline__ void score_codes(accum<LutKind, OutHalf, IsIP>& acc, const uint32_t (&w)[4],
                                             uint32_t row_a, uint32_t n_valid)
 {
@@ -639,7 +639,7 @@ __device__ __forceinline__ void score_codes(accum<LutKind, OutHalf, IsIP>& acc, 
   constexpr uint32_t kMask = kBook - 1u;
   constexpr int kPerPiece  = 128 / PqBits;
   constexpr uint32_t kElem = LutKind == LUT_F32 ? 4u : (LutKind == LUT_F16 ? 2u : 1u);
-  if constexpr (C < kPerPiece) {
+  if constexpr (C < kPerPiece && C < CEND) {
     constexpr int bit  = C * PqBits;
     constexpr int word = bit >> 5;
     constexpr int sh   = bit & 31;
@@ -652,7 +652,7 @@ __device__ __forceinline__ void score_codes(accum<LutKind, OutHalf, IsIP>& acc, 
       code = __funnelshift_r(w[word], w[word + 1 > 3 ? 3 : word + 1], sh) & kMask;
     }
     if (Full || uint32_t(C) < n_valid) { acc.template add<uint32_t(C) * kBook * kElem>(row_a + code * kElem); }
-    score_codes<PqBits, LutKind, OutHalf, IsIP, Full, C + 1>(acc, w, row_a, n_valid);
+    score_codes<PqBits, LutKind, OutHalf, IsIP, Full, C + 1, CEND>(acc, w, row_a, n_valid);
   }
 }
 template <int PqBits, int LutKind, bool OutHalf, bool IsIP, bool Full>
@@ -661,6 +661,14 @@ __device__ __forceinline__ void score_piece(accum<LutKind, OutHalf, IsIP>& acc, 
 {
   const uint32_t w[4] = {v.x, v.y, v.z, v.w};
   score_codes<PqBits, LutKind, OutHalf, IsIP, Full, 0>(acc, w, row_a, n_valid);
+}
+// codes [C0, C1) of a piece
+template <int PqBits, int LutKind, bool OutHalf, bool IsIP, bool Full, int C0, int C1>
+__device__ __forceinline__ void score_part(accum<LutKind, OutHalf, IsIP>& acc, const uint4& v,
+                                           uint32_t row_a, uint32_t n_valid)
+{
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+  score_codes<PqBits, LutKind, OutHalf, IsIP, Full, C0, C1>(acc, w, row_a, n_valid);
 }
 
 // PQD, GT, LEN > 0: pq_dim, threads per group and pq_len fixed at compile time, codebook in tensor
@@ -895,15 +903,25 @@ __global__ void __launch_bounds__(1024, 1) scan_kernel(const scan_params p)
             } else if (gi + n_gwarps < n_groups) {
               nxt = __ldg(src + group_stride);
             }
-            if (!kEarlyStop || alive) {
+            if constexpr (kEarlyStop) {
+              // two halves per piece, the bound checked after each
+              constexpr int kHalfPiece = kPerPiece / 2;
+              if (c + 1 < kPieces || kLast == uint32_t(kPerPiece)) {
+                if (alive) { score_part<PqBits, LutKind, OutHalf, IsIP, true, 0, kHalfPiece>(acc, v, lut_base_a + c * kPieceLutBytes, 0); }
+                alive = alive && !(acc.partial() > stop_at);
+                if (alive) { score_part<PqBits, LutKind, OutHalf, IsIP, true, kHalfPiece, kPerPiece>(acc, v, lut_base_a + c * kPieceLutBytes, 0); }
+              } else {
+                if (alive) { score_part<PqBits, LutKind, OutHalf, IsIP, false, 0, kHalfPiece>(acc, v, lut_base_a + c * kPieceLutBytes, kLast); }
+                alive = alive && !(acc.partial() > stop_at);
+                if (alive) { score_part<PqBits, LutKind, OutHalf, IsIP, false, kHalfPiece, kPerPiece>(acc, v, lut_base_a + c * kPieceLutBytes, kLast); }
+              }
+              if (c + 1 < kPieces) { alive = alive && !(acc.partial() > stop_at); }
+            } else {
               if (c + 1 < kPieces || kLast == uint32_t(kPerPiece)) {
                 score_piece<PqBits, LutKind, OutHalf, IsIP, true>(acc, v, lut_base_a + c * kPieceLutBytes, 0);
               } else {
                 score_piece<PqBits, LutKind, OutHalf, IsIP, false>(acc, v, lut_base_a + c * kPieceLutBytes, kLast);
               }
-            }
-            if constexpr (kEarlyStop) {
-              if (c + 1 < kPieces) { alive = alive && !(acc.partial() > stop_at); }
             }
           }
         } else {
