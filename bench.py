@@ -784,9 +784,10 @@ def run_ours(args):
               "internal_distance_dtype": wl["internal"], "refine_ratio": wl["refine_ratio"],
               rkey: chosen[rkey], "recall_without_refinement": chosen["recall_without_refinement"],
               "recall_target_met": target_met, "sweep": sweep, "sweep_below_the_configured_probes": below,
-              "recall_note": "recall does not depend on n_probes on this generator (queries fall next to their "
-                             "component's lists): the operating point is the first configured n_probes; what "
-                             "lifts recall over 0.95 is the exact re-ranking" if refining else None,
+              "recall_note": "on this generator recall is flat over the configured n_probes (queries fall next to "
+                             "their component's lists) and falls only below about 10 probes (see "
+                             "sweep_below_the_configured_probes): the operating point is the first configured "
+                             "n_probes; what lifts recall over 0.95 is the exact re-ranking" if refining else None,
               "small_batches": small,
               "parallelism": f"list-sharded x{world}, one process per GPU, one C++ call per batch" if world > 1
               else "single GPU",

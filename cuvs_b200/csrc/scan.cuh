@@ -11,15 +11,23 @@
 //   score      .. detail/jit_lto_kernels/compute_score_impl.cuh:20-79 (entries summed in subspace
 //                 order in the internal distance type)
 //
-// Execution shape (differs from the reference): a persistent grid of one 1024-thread CTA per SM.
-// A CTA keeps the per-subspace PQ codebook in shared memory for its whole life and is split into
-// G independent thread groups (G = 1, 2 or 4, as shared memory allows); each group pulls pairs
-// from a global counter, owns one LUT, and synchronises on its own named barrier.  Pairs are
-// ordered by list so that co-resident groups stream the same bytes out of L2.  LUT entries are
-// computed two at a time with packed fp32x2 arithmetic (IEEE round-to-nearest, identical bits to
-// scalar FMA).  Each warp scores 32 vectors per step (one 16-byte load per lane per code piece,
-// 512 contiguous bytes per warp) and keeps a sorted top-k across its lanes; a per-query bound
-// shared through global memory lets later probes discard almost every candidate with one compare.
+// Execution shape (differs from the reference): a persistent grid of one 1024-thread CTA per SM,
+// split into G independent thread groups (G = 8, 4, 2 or 1, as shared memory allows); each group
+// pulls pairs from a global counter, owns one LUT and one base-difference vector, and synchronises
+// on its own named barrier.  The per-subspace PQ codebook lives where the launch plan puts it:
+// in tensor memory (written once per CTA with tcgen05.st, read per thread with tcgen05.ld), in
+// shared memory, or in global memory.  The work list holds every query's nearest probe first (so
+// that a bound on the k-th best score exists early), then the rest, each segment ordered by list
+// so that co-resident groups stream the same bytes out of L2.  LUT entries are computed two at a
+// time with packed fp32x2 arithmetic (IEEE round-to-nearest, identical bits to scalar FMA).  Each
+// warp scores 32 vectors per step (one 16-byte load per lane per code piece, 512 contiguous bytes
+// per warp) and keeps a sorted top-k across its lanes; a per-query bound shared through global
+// memory lets later probes discard almost every candidate with one compare, and for L2 metrics a
+// lane whose partial sum already exceeds that bound stops its look-ups (checked twice per piece;
+// the sum only grows, so no kept candidate is lost).  The benchmark shapes (pq_dim, groups, pq_len)
+// are instantiated with compile-time trip counts (scan_inst.cu); every other shape runs the
+// run-time loops.  scan_glut_kernel is the variant whose table lives in global memory, for tables
+// that no shared-memory plan can hold.
 #pragma once
 
 #include "topk.cuh"
