@@ -644,43 +644,19 @@ label_ctx labeling_of(DistanceType m)
 // path does it (probe selection with n_probes = 1: exact rescoring and guard make its answer the
 // defining one, ties to the lowest list id) -- an order of magnitude faster than the SIMT product on
 // the 10^5 .. 10^6 lists of the large configurations; otherwise the SIMT kernel.
-__global__ void max_row_sumsq_kernel(const float* __restrict__ m, uint32_t n_rows, uint32_t n_cols,
-                                     uint32_t* __restrict__ out_bits)
-{
-  const uint32_t row = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
-  if (row >= n_rows) { return; }
-  float ss = 0.0f;
-  for (uint32_t k = lane; k < n_cols; k += 32) {
-    const float v = m[size_t(row) * n_cols + k];
-    ss            = __fmaf_rn(v, v, ss);
-  }
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) { ss += __shfl_xor_sync(kFullMask, ss, o); }
-  if (lane == 0) { atomicMax(out_bits, __float_as_uint(ss)); }  // non-negative floats order as integers
-}
-
 class nearest_labeler {
  public:
-  nearest_labeler(raft::resources& res, const float* centers, uint32_t n_lists, uint32_t dim_ext, float alpha)
-    : res_(res), centers_(centers), n_lists_(n_lists), dim_ext_(dim_ext), alpha_(alpha)
+  // `dim`: index of the |c|^2 column of the centre rows (rows carry -0.5 there)
+  nearest_labeler(raft::resources& res, const float* centers, uint32_t n_lists, uint32_t dim, uint32_t dim_ext,
+                  float alpha)
+    : res_(res), centers_(centers), n_lists_(n_lists), dim_ext_(dim_ext), ext_col_(dim), alpha_(alpha)
   {
     use_tc_ = coarse_tc_usable(n_lists, 1, dim_ext);
     if (!use_tc_) { return; }
     const size_t nc = size_t(n_lists) * dim_ext;
     hi_.resize(nc);
     lo_.resize(nc);
-    split_centers_tf32(res.stream, centers, nc, hi_.data(), lo_.data());
-    dev_array<uint32_t> mx(1);
-    CUDA_TRY(cudaMemsetAsync(mx.data(), 0, 4, res.stream));
-    max_row_sumsq_kernel<<<ceildiv<uint32_t>(n_lists * 32, 256), 256, 0, res.stream>>>(centers, n_lists, dim_ext,
-                                                                                        mx.data());
-    uint32_t bits = 0;
-    CUDA_TRY(cudaMemcpyAsync(&bits, mx.data(), 4, cudaMemcpyDeviceToHost, res.stream));
-    res.sync();
-    float ss;
-    std::memcpy(&ss, &bits, 4);
-    // the lanes sum in another order than a sequential loop: a generous margin on the bound
-    cmax_ = std::sqrt(ss) * 1.001f;
+    prepare_tc_centers(res.stream, centers, n_lists, dim_ext, ext_col_, hi_.data(), lo_.data(), &cmax_, &ext_scale_);
     res.launches += 2;
   }
   // labels[i] = nearest list of row i of x_ext [n_rows, dim_ext]; `best` is scratch of n_rows * 8 bytes
@@ -696,17 +672,19 @@ class nearest_labeler {
     for (uint32_t r0 = 0; r0 < n_rows; r0 += batch) {
       const uint32_t nr = std::min(batch, n_rows - r0);
       select_clusters_tc(res_, centers_, hi_.data(), lo_.data(), cmax_, n_lists_, dim_ext_, alpha_,
-                         x_ext + size_t(r0) * dim_ext_, nr, 1, labels + r0, nullptr, ws_.data(), ws_.size());
+                         x_ext + size_t(r0) * dim_ext_, nr, 1, labels + r0, nullptr, ws_.data(), ws_.size(), false,
+                         ext_col_, ext_scale_);
     }
   }
 
  private:
   raft::resources& res_;
   const float* centers_;
-  uint32_t n_lists_, dim_ext_;
+  uint32_t n_lists_, dim_ext_, ext_col_;
   float alpha_;
-  bool use_tc_ = false;
-  float cmax_  = 0.0f;
+  bool use_tc_     = false;
+  float cmax_      = 0.0f;
+  float ext_scale_ = 1.0f;
   dev_array<float> hi_, lo_;
   dev_array<uint8_t> ws_;
 };
@@ -1044,7 +1022,7 @@ void extend_any(raft::resources& res, const void* new_vectors, elem_t dtype, int
   CUDA_TRY(cudaMemsetAsync(counts.data(), 0, size_t(n_lists) * 4, stream));
 
   // pass 1: labels + histogram
-  nearest_labeler labeler(res, idx->centers(), n_lists, dim_ext, lc.alpha);
+  nearest_labeler labeler(res, idx->centers(), n_lists, dim, dim_ext, lc.alpha);
   for (uint64_t r0 = 0; r0 < n; r0 += chunk) {
     const uint64_t nr = std::min(chunk, n - r0);
     const void* src   = stage_rows(res, new_vectors, dtype, r0, nr, dim, on_device, staging);
@@ -1117,7 +1095,7 @@ void transform_any(raft::resources& res, const index<int64_t>& idx, const void* 
   const uint32_t flat  = ceildiv(idx.pq_dim() * idx.pq_bits(), 8u);
   dev_array<float> x_ext(chunk * dim_ext);
   dev_array<unsigned long long> best(chunk);
-  nearest_labeler labeler(res, idx.centers(), idx.n_lists(), dim_ext, lc.alpha);
+  nearest_labeler labeler(res, idx.centers(), idx.n_lists(), dim, dim_ext, lc.alpha);
   for (uint64_t r0 = 0; r0 < n; r0 += chunk) {
     const uint32_t nr = uint32_t(std::min(chunk, n - r0));
     const char* src   = static_cast<const char*>(dataset) + r0 * dim * elem_size(dtype);
@@ -1178,7 +1156,7 @@ void build_any(raft::resources& res, const index_params& params, const void* dat
   res.launches += 2;
   const uint32_t iters = std::max<uint32_t>(1, params.kmeans_n_iters);
   for (uint32_t it = 0; it < iters; it++) {
-    nearest_labeler(res, idx.centers(), n_lists, dim_ext, lc.alpha)
+    nearest_labeler(res, idx.centers(), n_lists, dim, dim_ext, lc.alpha)
       .run(train.data(), uint32_t(n_train), labels.data(), best.data());
     CUDA_TRY(cudaMemsetAsync(sums.data(), 0, sums.size() * 4, stream));
     CUDA_TRY(cudaMemsetAsync(counts.data(), 0, size_t(n_lists) * 4, stream));
@@ -1190,7 +1168,7 @@ void build_any(raft::resources& res, const index_params& params, const void* dat
     CUDA_TRY(cudaGetLastError());
     res.launches += 2;
   }
-  nearest_labeler(res, idx.centers(), n_lists, dim_ext, lc.alpha)
+  nearest_labeler(res, idx.centers(), n_lists, dim, dim_ext, lc.alpha)
     .run(train.data(), uint32_t(n_train), labels.data(), best.data());
 
   // ---- rotation, rotated centers ----

@@ -36,6 +36,8 @@
 #include <cuda.h>
 
 #include <algorithm>
+#include <cmath>
+#include <cstring>
 #include <type_traits>
 #include <mutex>
 
@@ -78,15 +80,37 @@ __device__ __forceinline__ float to_tf32(float x)
   return __uint_as_float(r);
 }
 
-__global__ void split_tf32_kernel(const float* __restrict__ in, size_t n, float* __restrict__ hi,
-                                  float* __restrict__ lo)
+// Column `ext_col` of every row (row length `dim_ext`) is multiplied by `col_scale`, a power of two
+// (exact, and it commutes with the split); ext_col >= dim_ext leaves every column alone.
+__global__ void split_tf32_kernel(const float* __restrict__ in, size_t n, uint32_t dim_ext, uint32_t ext_col,
+                                  float col_scale, float* __restrict__ hi, float* __restrict__ lo)
 {
   const size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x;
   if (i >= n) { return; }
-  const float x = in[i];
+  float x = in[i];
+  if (uint32_t(i % dim_ext) == ext_col) { x *= col_scale; }
   const float h = to_tf32(x);
   hi[i]         = h;
   lo[i]         = to_tf32(x - h);
+}
+
+// One warp per row: bits of the largest sum of squares of a row, the column `ext_col` multiplied by
+// `col_scale` first (col_scale = 0 leaves it out).  Non-negative floats order as integers.
+__global__ void max_row_sumsq_scaled_kernel(const float* __restrict__ rows, uint32_t n_rows, uint32_t dim_ext,
+                                            uint32_t ext_col, float col_scale, uint32_t* __restrict__ out_bits)
+{
+  const uint32_t row  = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const uint32_t lane = threadIdx.x & 31u;
+  if (row >= n_rows) { return; }
+  float ss = 0.0f;
+  for (uint32_t k = lane; k < dim_ext; k += 32) {
+    float v = rows[size_t(row) * dim_ext + k];
+    if (k == ext_col) { v *= col_scale; }
+    ss = __fmaf_rn(v, v, ss);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) { ss += __shfl_xor_sync(kFullMask, ss, o); }
+  if (lane == 0) { atomicMax(out_bits, __float_as_uint(ss)); }
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -470,7 +494,7 @@ coarse_finish_kernel(const uint32_t* __restrict__ cand_key, const uint32_t* __re
                      uint32_t cap /* pow2 >= C */, float cmax, float eps_rel,
                      uint32_t* __restrict__ probes, float* __restrict__ scores_out,
                      uint32_t* __restrict__ redo_list, uint32_t* __restrict__ redo_count,
-                     const uint32_t* __restrict__ error_word)
+                     const uint32_t* __restrict__ error_word, uint32_t ext_col, float ext_scale)
 {
   // the GEMM gave up on a wait: its candidates are incomplete, every query is redone exactly
   if (*error_word != 0u) { return; }
@@ -493,7 +517,8 @@ coarse_finish_kernel(const uint32_t* __restrict__ cand_key, const uint32_t* __re
   for (uint32_t i = tid; i < dim_ext; i += 256) {
     const float v = fq[size_t(q) * dim_ext + i];
     s_q[i]        = v;
-    qq += v * v;
+    const float w = i == ext_col ? v * ext_scale : v;  // the norm of the row the GEMM multiplied
+    qq += w * w;
   }
   if (tid == 0) {
     s_prefix    = 0;
@@ -699,7 +724,8 @@ coarse_finish_small_kernel(const uint32_t* __restrict__ cand_key, const uint32_t
                            uint32_t n_probes, uint32_t C, float cmax, float eps_rel,
                            uint32_t* __restrict__ probes, float* __restrict__ scores_out,
                            uint32_t* __restrict__ redo_list, uint32_t* __restrict__ redo_count,
-                           uint32_t rows_per_round, const uint32_t* __restrict__ error_word)
+                           uint32_t rows_per_round, const uint32_t* __restrict__ error_word, uint32_t ext_col,
+                           float ext_scale)
 {
   // the GEMM gave up on a wait: its candidates are incomplete, every query is redone exactly
   if (*error_word != 0u) { return; }
@@ -746,7 +772,8 @@ coarse_finish_small_kernel(const uint32_t* __restrict__ cand_key, const uint32_t
   for (uint32_t i = tid; i < dim_ext; i += 256) {
     const float v = fq[size_t(q) * dim_ext + i];
     s_q[i]        = v;
-    qq += v * v;
+    const float w = i == ext_col ? v * ext_scale : v;  // the norm of the row the GEMM multiplied
+    qq += w * w;
   }
 #pragma unroll
   for (int d = 16; d > 0; d >>= 1) { qq += __shfl_xor_sync(kFullMask, qq, d); }
@@ -1079,18 +1106,57 @@ size_t coarse_tc_workspace_bytes(uint32_t n_queries, uint32_t n_lists, uint32_t 
   return lay.total();
 }
 
-void split_centers_tf32(cudaStream_t stream, const float* centers, size_t n, float* hi, float* lo)
+// Derived operands of the tensor-core coarse search: TF32 split of the centre rows with the norm
+// column (`ext_col`, holding |c|^2 for L2 metrics) divided by a power of two s ~ max |c|, and the
+// largest norm of a row so prepared.  The query side multiplies its own entry of that column by s, so
+// the products are unchanged while the Cauchy-Schwarz bound |q'||c'| that the guard's error term
+// scales with no longer carries |c|^2 against 0.5: on data with large norms (8-bit integer vectors)
+// the bound tightens by about |c|.  ext_col >= dim_ext: nothing is rescaled.  Synchronises the stream.
+void prepare_tc_centers(cudaStream_t stream, const float* centers, uint32_t n_lists, uint32_t dim_ext,
+                        uint32_t ext_col, float* hi, float* lo, float* cmax, float* ext_scale)
 {
+  *cmax      = 0.0f;
+  *ext_scale = 1.0f;
+  const size_t n = size_t(n_lists) * dim_ext;
   if (n == 0) { return; }
-  split_tf32_kernel<<<unsigned(ceildiv<size_t>(n, 256)), 256, 0, stream>>>(centers, n, hi, lo);
+  uint32_t* d_bits = nullptr;
+  CUDA_TRY(cudaMalloc(&d_bits, 8));
+  CUDA_TRY(cudaMemsetAsync(d_bits, 0, 8, stream));
+  const unsigned blocks = ceildiv<uint32_t>(n_lists * 32u, 256u);
+  uint32_t bits[2]      = {0, 0};
+  float s               = 1.0f;
+  if (ext_col < dim_ext) {
+    max_row_sumsq_scaled_kernel<<<blocks, 256, 0, stream>>>(centers, n_lists, dim_ext, ext_col, 0.0f, d_bits);
+    CUDA_TRY(cudaMemcpyAsync(bits, d_bits, 4, cudaMemcpyDeviceToHost, stream));
+    CUDA_TRY(cudaStreamSynchronize(stream));
+    float ss;
+    std::memcpy(&ss, &bits[0], 4);
+    const float nrm = std::sqrt(ss);
+    if (std::isfinite(nrm) && nrm > 0.0f) {
+      int e = 0;
+      std::frexp(nrm, &e);  // nrm = m * 2^e, m in [0.5, 1)
+      s = std::ldexp(1.0f, std::max(-60, std::min(60, e)));
+    }
+  }
+  max_row_sumsq_scaled_kernel<<<blocks, 256, 0, stream>>>(centers, n_lists, dim_ext, ext_col, 1.0f / s, d_bits + 1);
+  split_tf32_kernel<<<unsigned(ceildiv<size_t>(n, 256)), 256, 0, stream>>>(centers, n, dim_ext, ext_col, 1.0f / s,
+                                                                          hi, lo);
   CUDA_TRY(cudaGetLastError());
+  CUDA_TRY(cudaMemcpyAsync(bits + 1, d_bits + 1, 4, cudaMemcpyDeviceToHost, stream));
+  CUDA_TRY(cudaStreamSynchronize(stream));
+  CUDA_TRY(cudaFree(d_bits));
+  float ss;
+  std::memcpy(&ss, &bits[1], 4);
+  // the lanes sum in another order than a sequential loop: a margin on the bound
+  *cmax      = std::sqrt(ss) * 1.001f;
+  *ext_scale = s;
 }
 
 void select_clusters_tc(raft::resources& res, const float* centers, const float* centers_hi,
                         const float* centers_lo, float cmax, uint32_t n_lists, uint32_t dim_ext,
                         float alpha, const float* fq, uint32_t n_queries, uint32_t n_probes,
                         uint32_t* probes, float* scores_out, void* workspace, size_t workspace_bytes,
-                        bool exact_operands)
+                        bool exact_operands, uint32_t ext_col, float ext_scale)
 {
   CUVS_EXPECTS(alpha < 0.0f, "the tensor-core coarse search expects a negative scale");
   CUVS_EXPECTS(workspace_bytes >= coarse_tc_workspace_bytes(n_queries, n_lists, dim_ext),
@@ -1115,8 +1181,9 @@ void select_clusters_tc(raft::resources& res, const float* centers, const float*
   float* scratch  = reinterpret_cast<float*>(ws + lay.add(size_t(64) * n_lists * 4));
   cudaStream_t stream = res.stream;
 
+  if (ext_scale == 1.0f) { ext_col = dim_ext; }
   split_tf32_kernel<<<unsigned(ceildiv<size_t>(size_t(n_queries) * dim_ext, 256)), 256, 0, stream>>>(
-    fq, size_t(n_queries) * dim_ext, fq_hi, fq_lo);
+    fq, size_t(n_queries) * dim_ext, dim_ext, ext_col, ext_scale, fq_hi, fq_lo);
   CUDA_TRY(cudaMemsetAsync(words, 0, 12, stream));
 
   const CUtensorMap m_a_hi = make_map(fq_hi, n_queries, dim_ext, kBM);
@@ -1181,18 +1248,18 @@ void select_clusters_tc(raft::resources& res, const float* centers, const float*
     if (kph == 16) {
       coarse_finish_small_kernel<16><<<n_queries, 256, fin_small_smem, stream>>>(
         cand_key, cand_bnd, n_cand, centers, fq, n_lists, dim_ext, alpha, n_probes, C, cmax, eps_rel, probes,
-        scores_out, redo_list, words + 2, fin_rows, words);
+        scores_out, redo_list, words + 2, fin_rows, words, ext_col, ext_scale);
     } else {
       coarse_finish_small_kernel<8><<<n_queries, 256, fin_small_smem, stream>>>(
         cand_key, cand_bnd, n_cand, centers, fq, n_lists, dim_ext, alpha, n_probes, C, cmax, eps_rel, probes,
-        scores_out, redo_list, words + 2, fin_rows, words);
+        scores_out, redo_list, words + 2, fin_rows, words, ext_col, ext_scale);
     }
   } else {
     if (fin_smem > 48 * 1024) { ensure_dynamic_smem(reinterpret_cast<const void*>(coarse_finish_kernel), fin_smem); }
     coarse_finish_kernel<<<n_queries, 256, fin_smem, stream>>>(cand_key, cand_bnd, n_cand, kph, centers, fq,
                                                                n_lists, dim_ext, alpha, n_probes, C, cap,
                                                                cmax, eps_rel, probes, scores_out, redo_list,
-                                                               words + 2, words);
+                                                               words + 2, words, ext_col, ext_scale);
   }
   uint32_t cap_fb = 2;
   while (cap_fb < n_probes) { cap_fb <<= 1; }

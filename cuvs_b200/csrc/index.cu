@@ -212,27 +212,16 @@ void index<int64_t>::recompute_internal_state(cudaStream_t stream)
   rotation_i8f_.reset();
   centers_h_.reset();
   rotation_h_.reset();
-  // derived data of the tensor-core coarse search
+  // derived data of the tensor-core coarse search: the split centre rows with the |c|^2 column of the
+  // L2 metrics rebalanced against the queries' -0.5 (the other metrics multiply that column by zero)
   const size_t nc = size_t(n_lists_) * dim_ext();
-  std::vector<float> hc(nc);
-  CUDA_TRY(cudaMemcpyAsync(hc.data(), centers_.data(), nc * 4, cudaMemcpyDeviceToHost, stream));
-  CUDA_TRY(cudaStreamSynchronize(stream));
-  double mx = 0.0;
-  for (uint32_t l = 0; l < n_lists_; l++) {
-    double ss = 0.0;
-    for (uint32_t k = 0; k < dim_ext(); k++) {
-      const double v = hc[size_t(l) * dim_ext() + k];
-      ss += v * v;
-    }
-    mx = std::max(mx, ss);
-  }
-  centers_max_norm_ = float(std::sqrt(mx)) * 1.0001f;
   if (centers_hi_.size() != nc) {
     centers_hi_.resize(nc);
     centers_lo_.resize(nc);
   }
-  split_centers_tf32(stream, centers_.data(), nc, centers_hi_.data(), centers_lo_.data());
-  CUDA_TRY(cudaStreamSynchronize(stream));
+  const bool norm_column = metric_ == DistanceType::L2Expanded || metric_ == DistanceType::L2SqrtExpanded;
+  prepare_tc_centers(stream, centers_.data(), n_lists_, dim_ext(), norm_column ? dim_ : dim_ext(),
+                     centers_hi_.data(), centers_lo_.data(), &centers_max_norm_, &centers_ext_scale_);
 }
 
 // ------------------------------------------------------------------------------------------------

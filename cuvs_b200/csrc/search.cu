@@ -845,7 +845,7 @@ void search_any(raft::resources& res, const search_params& params, const index<i
     } else if (use_tc) {
       select_clusters_tc(res, idx.centers(), idx.centers_hi(), idx.centers_lo(), idx.centers_max_norm(),
                          n_lists, idx.dim_ext(), is_l2 ? -2.0f : -1.0f, d_fq, nq, n_probes, d_probes,
-                         nullptr, d_coarse, coarse_ws);
+                         nullptr, d_coarse, coarse_ws, false, idx.dim(), idx.centers_ext_scale());
     } else {
       select_clusters(res, idx.centers(), n_lists, idx.dim_ext(), is_l2 ? -2.0f : -1.0f, d_fq, nq,
                       n_probes, d_probes, nullptr, d_coarse, coarse_ws);
@@ -1045,7 +1045,8 @@ void select_probes_any(raft::resources& res, const index<int64_t>& idx, const vo
       }
     } else if (use_tc) {
       select_clusters_tc(res, idx.centers(), idx.centers_hi(), idx.centers_lo(), idx.centers_max_norm(),
-                         n_lists, idx.dim_ext(), alpha, d_fq, nq, n_probes, out, nullptr, ws + o_c, cws);
+                         n_lists, idx.dim_ext(), alpha, d_fq, nq, n_probes, out, nullptr, ws + o_c, cws, false,
+                         idx.dim(), idx.centers_ext_scale());
     } else {
       select_clusters(res, idx.centers(), n_lists, idx.dim_ext(), alpha, d_fq, nq, n_probes, out, nullptr,
                       ws + o_c, cws);
@@ -1081,7 +1082,7 @@ void coarse_only(raft::resources& res, const index<int64_t>& idx, const void* qu
   if (use_tc) {
     select_clusters_tc(res, idx.centers(), idx.centers_hi(), idx.centers_lo(), idx.centers_max_norm(),
                        n_lists, idx.dim_ext(), is_l2 ? -2.0f : -1.0f, d_fq, n_queries, n_probes, probes,
-                       scores, ws + o_c, cws);
+                       scores, ws + o_c, cws, false, idx.dim(), idx.centers_ext_scale());
     coarse_tc_status(res, ws + o_c, n_queries, n_lists, idx.dim_ext(), &status[0], &status[1]);
   } else {
     select_clusters(res, idx.centers(), n_lists, idx.dim_ext(), is_l2 ? -2.0f : -1.0f, d_fq, n_queries,

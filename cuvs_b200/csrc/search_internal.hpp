@@ -33,12 +33,17 @@ void select_rows(raft::resources& res, const float* rows, uint32_t n_rows, uint3
 // one product per K step, and the guard allows for no split error.
 bool coarse_tc_usable(uint32_t n_lists, uint32_t n_probes, uint32_t dim_ext);
 size_t coarse_tc_workspace_bytes(uint32_t n_queries, uint32_t n_lists, uint32_t dim_ext);
-void split_centers_tf32(cudaStream_t stream, const float* centers, size_t n, float* hi, float* lo);
+// Prepares `hi` / `lo` (TF32 split of the centre rows) with column `ext_col` (the |c|^2 column of L2
+// metrics; >= dim_ext: none) divided by a power of two `ext_scale` close to the largest |c|, and `cmax`,
+// the largest norm of a row so prepared; select_clusters_tc is given the same ext_col / ext_scale and
+// multiplies the queries' entry of that column by it.  Synchronises the stream.
+void prepare_tc_centers(cudaStream_t stream, const float* centers, uint32_t n_lists, uint32_t dim_ext,
+                        uint32_t ext_col, float* hi, float* lo, float* cmax, float* ext_scale);
 void select_clusters_tc(raft::resources& res, const float* centers, const float* centers_hi,
                         const float* centers_lo, float cmax, uint32_t n_lists, uint32_t dim_ext,
                         float alpha, const float* fq, uint32_t n_queries, uint32_t n_probes,
                         uint32_t* probes, float* scores_out, void* workspace, size_t workspace_bytes,
-                        bool exact_operands = false);
+                        bool exact_operands = false, uint32_t ext_col = ~0u, float ext_scale = 1.0f);
 void coarse_tc_status(raft::resources& res, const void* workspace, uint32_t n_queries, uint32_t n_lists,
                       uint32_t dim_ext, uint32_t* error, uint32_t* n_fallback);
 

@@ -259,6 +259,7 @@ class index<int64_t> {
   float* centers_hi() const { return centers_hi_.data(); }
   float* centers_lo() const { return centers_lo_.data(); }
   float centers_max_norm() const { return centers_max_norm_; }
+  float centers_ext_scale() const { return centers_ext_scale_; }
   uint64_t total_rows_padded() const { return h_row_off_.empty() ? 0 : h_row_off_.back(); }
   // Operands of the int8 coarse search (coarse_search_dtype = CUDA_R_8I; centers_int8 and
   // rotation_matrix_int8 of cpp/src/neighbors/ivf_pq_index.cu:624-738), created on first use.  The
@@ -289,6 +290,7 @@ class index<int64_t> {
   dev_array<float> pq_centers_, centers_, centers_rot_, rotation_;
   dev_array<float> centers_hi_, centers_lo_;
   float centers_max_norm_ = 0.0f;
+  float centers_ext_scale_ = 1.0f;
   mutable dev_array<float> centers_i8f_, rotation_i8f_;
   mutable dev_array<float> centers_h_, rotation_h_;
   mutable float centers_i8f_max_norm_ = 0.0f;
