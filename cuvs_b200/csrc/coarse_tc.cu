@@ -7,16 +7,19 @@
 // materialised here.
 //
 // Pipeline per batch
-//   1. split_tf32_kernel: every fp32 operand x is written as hi = tf32(x), lo = tf32(x - hi)
-//      (centers once per index, queries per batch).
+//   1. operand split: every fp32 operand x is written as hi = tf32(x), lo = tf32(x - hi) (centres once
+//      per index, prepare_tc_centers; queries per batch, split_queries_kernel).  Two exact power-of-two
+//      rescalings ride on it: the |c|^2 column of the L2 operands is balanced against the queries'
+//      -0.5 (tightens the norm product the guard's error bound scales with), and every query row is
+//      scaled so that its dot products lie in (-0.5, 0.5) (lets the epilogue build keys with float adds).
 //   2. coarse_tc_kernel: one persistent CTA per SM walks the output tiles (128 queries x 256
 //      lists); K in blocks of 16 floats (one 64-byte swizzle atom), four pipeline stages.  Per K
 //      step one, two or three products of the split accumulate into TMEM: hi*hi (+ lo*hi (+ hi*lo)).
 //      Warp 0 issues TMA loads (no multicast), warp 1 issues the MMAs, sixteen epilogue warps read
 //      the accumulator with tcgen05.ld (thread = query row, warp = 32 rows x 64 columns) and keep,
 //      per row and per 64-list unit, the eight largest dot products in registers, as packed
-//      32-bit keys (order-preserving image of the value, low 7 bits replaced by the column tag):
-//      insertion is a branch-free chain of integer max/min.  Two variants: two independent
+//      32-bit keys (the value in fixed point with 16 fractional bits, low 7 bits the column tag;
+//      built with four float additions): insertion is a branch-free chain of integer max/min.  Two variants: two independent
 //      top-4 chains (column % 2) or one top-8 chain; the last key of a chain bounds everything the
 //      chain dropped.  Two TMEM accumulators let the epilogue of one tile overlap the MMAs of the
 //      next.
@@ -92,6 +95,43 @@ __global__ void split_tf32_kernel(const float* __restrict__ in, size_t n, uint32
   const float h = to_tf32(x);
   hi[i]         = h;
   lo[i]         = to_tf32(x - h);
+}
+
+// The query operand of the GEMM, one warp per query row: the norm column multiplied by `col_scale`
+// (see prepare_tc_centers), then the whole row by a power of two 2^e chosen per query so that every
+// product of the row, |u| <= |q'| * cmax, lands in (-0.5, 0.5):  |q'| * cmax * (1 + 2^-9) * 2^e in
+// [0.25, 0.5).  The GEMM's epilogue turns such a value into a sortable key with float additions alone
+// (see there); the finish kernels undo the scale (row_scale[q] = 2^e, exact).  Then the TF32 split.
+__global__ void split_queries_kernel(const float* __restrict__ fq, uint32_t n_queries, uint32_t dim_ext,
+                                     uint32_t ext_col, float col_scale, float cmax, float* __restrict__ hi,
+                                     float* __restrict__ lo, float* __restrict__ row_scale)
+{
+  const uint32_t q    = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const uint32_t lane = threadIdx.x & 31u;
+  if (q >= n_queries) { return; }
+  const float* src = fq + size_t(q) * dim_ext;
+  float ss         = 0.0f;
+  for (uint32_t k = lane; k < dim_ext; k += 32) {
+    float v = src[k];
+    if (k == ext_col) { v *= col_scale; }
+    ss = __fmaf_rn(v, v, ss);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) { ss += __shfl_xor_sync(kFullMask, ss, o); }
+  // bound = m * 2^(E - 126), m in [0.5, 1)  ->  scale 2^(125 - E) puts it in [0.25, 0.5)
+  const float bound = sqrtf(ss) * cmax * 1.002f;
+  const int E       = int((__float_as_uint(bound) >> 23) & 0xFFu);
+  float scale       = 1.0f;
+  if (E >= 1 && E <= 250) { scale = __uint_as_float(uint32_t(252 - E) << 23); }
+  for (uint32_t k = lane; k < dim_ext; k += 32) {
+    float v = src[k];
+    if (k == ext_col) { v *= col_scale; }
+    v *= scale;
+    const float h                = to_tf32(v);
+    hi[size_t(q) * dim_ext + k] = h;
+    lo[size_t(q) * dim_ext + k] = to_tf32(v - h);
+  }
+  if (lane == 0) { row_scale[q] = scale; }
 }
 
 // One warp per row: bits of the largest sum of squares of a row, the column `ext_col` multiplied by
@@ -388,8 +428,12 @@ coarse_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
         break;
       }
       tc_fence_after();
-      // Packed key: order-preserving image of the dot product with its low 7 bits replaced by
-      // (127 - column in the 128-column half tile); empty / out-of-range columns are key 0.
+      // Packed key.  The query rows were scaled so that every dot product u lies in (-0.5, 0.5)
+      // (split_queries_kernel).  u + 192 rounds u to a multiple of 2^-16 (the ulp of [128, 256)),
+      // - 192 is exact, + (1.5 + tag * 2^-23) is exact and lands in [1, 2): the bits of the result are a
+      // sortable key whose low 7 bits are tag = 127 - column in the 128-column half tile.  Four float
+      // additions on the FMA pipe instead of shift / logic operations on the integer pipe, which the
+      // min / max chains below already fill.  Empty / out-of-range columns are key 0.
       uint32_t key[kStreams][kKeep];
 #pragma unroll
       for (int st = 0; st < kStreams; st++) {
@@ -404,18 +448,17 @@ coarse_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
         tmem_ld32(tmem_base + ((quarter * 32u) << 16) + acc * kBN + col0 + c, r);
         const uint32_t list0 = n0 + c;
         const bool full      = list0 + 32 <= p.n_lists;
-        // The epilogue is bound by the integer pipe, so the per-element sequence is kept minimal:
-        // shift, xor (order-preserving image), and-or with this 32-column group's tag base, xor with
-        // the column (the base ends in five one bits, so base ^ e == base - e), then the insert.
         // The range check exists only in the version used by the last, partial list tile.
-        const uint32_t tag_base = 127u - (sub * kUnit + c);
+        const float tag_base = 1.5f + float(127u - (sub * kUnit + c)) * 0x1p-23f;
         auto take = [&](auto full_c) {
           constexpr bool kFull = decltype(full_c)::value;
 #pragma unroll
           for (int e = 0; e < 32; e++) {
-            const uint32_t u = r[e];
-            uint32_t k = u ^ (uint32_t(int32_t(u) >> 31) | 0x80000000u);
-            k          = ((k & ~127u) | tag_base) ^ uint32_t(e);
+            float t = __fadd_rn(__uint_as_float(r[e]), 192.0f);
+            t       = __fadd_rn(t, -192.0f);
+            t       = __fadd_rn(t, tag_base);
+            t       = __fadd_rn(t, -float(e) * 0x1p-23f);
+            uint32_t k = __float_as_uint(t);
             if constexpr (!kFull) {
               if (list0 + e >= p.n_lists) { k = 0u; }
             }
@@ -423,9 +466,11 @@ coarse_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
             // key[t], k)) -- 2 * kKeep - 1 independent min/max
             uint32_t up[kKeep];
 #pragma unroll
-            for (int t = 0; t < kKeep; t++) { up[t] = max(key[e % kStreams][t], k); }
+            for (int t2 = 0; t2 < kKeep; t2++) { up[t2] = max(key[e % kStreams][t2], k); }
 #pragma unroll
-            for (int t = kKeep - 1; t > 0; t--) { key[e % kStreams][t] = min(key[e % kStreams][t - 1], up[t]); }
+            for (int t2 = kKeep - 1; t2 > 0; t2--) {
+              key[e % kStreams][t2] = min(key[e % kStreams][t2 - 1], up[t2]);
+            }
             key[e % kStreams][0] = up[0];
           }
         };
@@ -484,7 +529,11 @@ constexpr uint32_t kMaxC = 1024;
 
 // Key helpers shared with the GEMM epilogue.
 __device__ __forceinline__ bool key_valid(uint32_t key) { return key >= 0x00800000u; }
-__device__ __forceinline__ float key_value(uint32_t key) { return ordered_to_float(key & ~127u); }
+// the dot product a key stands for (to within 2^-17 / row scale): key bits = 1.5 + u * scale + tag * 2^-23
+__device__ __forceinline__ float key_value(uint32_t key, float inv_row_scale)
+{
+  return __fmul_rn(__fadd_rn(__uint_as_float(key & ~127u), -1.5f), inv_row_scale);
+}
 
 __global__ void __launch_bounds__(256)
 coarse_finish_kernel(const uint32_t* __restrict__ cand_key, const uint32_t* __restrict__ cand_bound,
@@ -494,7 +543,8 @@ coarse_finish_kernel(const uint32_t* __restrict__ cand_key, const uint32_t* __re
                      uint32_t cap /* pow2 >= C */, float cmax, float eps_rel,
                      uint32_t* __restrict__ probes, float* __restrict__ scores_out,
                      uint32_t* __restrict__ redo_list, uint32_t* __restrict__ redo_count,
-                     const uint32_t* __restrict__ error_word, uint32_t ext_col, float ext_scale)
+                     const uint32_t* __restrict__ error_word, uint32_t ext_col, float ext_scale,
+                     const float* __restrict__ row_scale)
 {
   // the GEMM gave up on a wait: its candidates are incomplete, every query is redone exactly
   if (*error_word != 0u) { return; }
@@ -513,6 +563,7 @@ coarse_finish_kernel(const uint32_t* __restrict__ cand_key, const uint32_t* __re
     for (uint32_t i = tid; i < n_cand / 4; i += 256) { dst[i] = __ldg(src + i); }
   }
 
+  const float inv_row_scale = 1.0f / __ldg(row_scale + q);  // a power of two: exact
   float qq = 0.0f;
   for (uint32_t i = tid; i < dim_ext; i += 256) {
     const float v = fq[size_t(q) * dim_ext + i];
@@ -585,7 +636,7 @@ coarse_finish_kernel(const uint32_t* __restrict__ cand_key, const uint32_t* __re
   uint32_t tile_key = s_tb[0];
 #pragma unroll
   for (int w = 1; w < 8; w++) { tile_key = max(tile_key, s_tb[w]); }
-  const float tilebound = key_valid(tile_key) ? key_value(tile_key) : -INFINITY;
+  const float tilebound = key_valid(tile_key) ? key_value(tile_key, inv_row_scale) : -INFINITY;
   const uint32_t n_sel  = min(s_count, cap);
   const bool overflow   = s_count > cap;
   // exact rescoring: the defining FMA chain, ascending k
@@ -628,10 +679,10 @@ coarse_finish_kernel(const uint32_t* __restrict__ cand_key, const uint32_t* __re
     float qnorm = 0.0f;
     for (int w = 0; w < 8; w++) { qnorm += s_red[w]; }
     qnorm = sqrtf(qnorm);
-    // |tensor-core - exact| (accumulation order, dropped lo*lo term) plus the 7 low bits the packed
-    // keys give up (a relative 2^-16 of the value)
+    // |tensor-core - exact| (accumulation order, dropped lo*lo term) plus the rounding of the packed
+    // keys (2^-17 of the scaled row, i.e. at most 2^-15 * 1.002 of |q| * cmax)
     const float eps       = eps_rel * qnorm * cmax;
-    const float t_c       = key_valid(~T) ? key_value(~T) : -INFINITY;  // C-th largest key, as a value
+    const float t_c       = key_valid(~T) ? key_value(~T, inv_row_scale) : -INFINITY;  // C-th largest key, as a value
     const float unseen    = fmaxf(t_c, tilebound);
     bool ok               = !overflow && n_sel >= n_probes;
     if (ok) {
@@ -725,7 +776,7 @@ coarse_finish_small_kernel(const uint32_t* __restrict__ cand_key, const uint32_t
                            uint32_t* __restrict__ probes, float* __restrict__ scores_out,
                            uint32_t* __restrict__ redo_list, uint32_t* __restrict__ redo_count,
                            uint32_t rows_per_round, const uint32_t* __restrict__ error_word, uint32_t ext_col,
-                           float ext_scale)
+                           float ext_scale, const float* __restrict__ row_scale)
 {
   // the GEMM gave up on a wait: its candidates are incomplete, every query is redone exactly
   if (*error_word != 0u) { return; }
@@ -768,6 +819,7 @@ coarse_finish_small_kernel(const uint32_t* __restrict__ cand_key, const uint32_t
       for (int i = 0; i < KPH; i++) { keys[s][i] = 0; }
     }
   }
+  const float inv_row_scale = 1.0f / __ldg(row_scale + q);  // a power of two: exact
   float qq = 0.0f;
   for (uint32_t i = tid; i < dim_ext; i += 256) {
     const float v = fq[size_t(q) * dim_ext + i];
@@ -830,7 +882,7 @@ coarse_finish_small_kernel(const uint32_t* __restrict__ cand_key, const uint32_t
   uint32_t tile_key = s_tb[0];
 #pragma unroll
   for (int w = 1; w < 8; w++) { tile_key = max(tile_key, s_tb[w]); }
-  const float tilebound = key_valid(tile_key) ? key_value(tile_key) : -INFINITY;
+  const float tilebound = key_valid(tile_key) ? key_value(tile_key, inv_row_scale) : -INFINITY;
   const uint32_t n_sel  = min(s_count, 64u);
   const bool overflow   = s_count > 64u;
 
@@ -886,7 +938,7 @@ coarse_finish_small_kernel(const uint32_t* __restrict__ cand_key, const uint32_t
       qnorm = sqrtf(qnorm);
       const float eps = eps_rel * qnorm * cmax;
       // every list that was not rescored has a key below t0 or was dropped by its half tile
-      const float t_c    = key_valid(t0) ? key_value(t0) : -INFINITY;
+      const float t_c    = key_valid(t0) ? key_value(t0, inv_row_scale) : -INFINITY;
       const float unseen = fmaxf(t_c, tilebound);
       bool ok            = !overflow && n_sel >= n_probes;
       if (ok) {
@@ -902,6 +954,66 @@ coarse_finish_small_kernel(const uint32_t* __restrict__ cand_key, const uint32_t
 // ------------------------------------------------------------------------------------------------
 // exact redo of flagged queries
 // ------------------------------------------------------------------------------------------------
+constexpr uint32_t kFbSlots = 64;  // queries redone per round = blocks of coarse_fallback_kernel = scratch rows
+constexpr uint32_t kFbGroup = 8;   // queries whose chains one thread carries at a time
+
+// Exact scores of the first kFbSlots queries to redo, spread over the whole grid: one block per 256
+// lists; 256 lists x 32 columns at a time go through shared memory (a warp reads 128 contiguous bytes
+// of one row), every thread continues the defining chain (ascending k, fused multiply-add) of its own
+// list for up to kFbGroup queries.  scratch[slot][list] = alpha * dot.
+__global__ void __launch_bounds__(256)
+coarse_fallback_scores_kernel(const uint32_t* __restrict__ redo_list, const uint32_t* __restrict__ redo_count,
+                              const float* __restrict__ centers, const float* __restrict__ fq,
+                              uint32_t n_queries, uint32_t n_lists, uint32_t dim_ext, float alpha,
+                              float* __restrict__ scratch, uint32_t n_slots,
+                              const uint32_t* __restrict__ error_word)
+{
+  extern __shared__ float s_f[];
+  float* s_tile = s_f;             // [256 lists][32 columns + 1]
+  float* s_qs   = s_f + 256 * 33;  // [kFbGroup][dim_ext]
+  const uint32_t tid    = threadIdx.x;
+  const bool redo_all   = *error_word != 0u;
+  const uint32_t n_redo = redo_all ? n_queries : min(*redo_count, n_queries);
+  const uint32_t R      = min(n_redo, n_slots);
+  const uint32_t l0     = blockIdx.x * 256u;
+  for (uint32_t j0 = 0; j0 < R; j0 += kFbGroup) {
+    const uint32_t nj = min(kFbGroup, R - j0);
+    __syncthreads();
+    for (uint32_t i = tid; i < nj * dim_ext; i += 256) {
+      const uint32_t j = i / dim_ext, k = i - j * dim_ext;
+      const uint32_t q = redo_all ? (j0 + j) : redo_list[j0 + j];
+      s_qs[i]          = fq[size_t(q) * dim_ext + k];
+    }
+    float acc[kFbGroup];
+#pragma unroll
+    for (uint32_t j = 0; j < kFbGroup; j++) { acc[j] = 0.0f; }
+    for (uint32_t k0 = 0; k0 < dim_ext; k0 += 32) {
+      const uint32_t kc = min(32u, dim_ext - k0);
+      __syncthreads();
+      for (uint32_t r = tid >> 5; r < 256; r += 8) {
+        const uint32_t l = l0 + r, lane = tid & 31u;
+        if (l < n_lists && lane < kc) { s_tile[r * 33 + lane] = __ldg(centers + size_t(l) * dim_ext + k0 + lane); }
+      }
+      __syncthreads();
+      if (l0 + tid < n_lists) {
+        for (uint32_t k = 0; k < kc; k++) {
+          const float c = s_tile[tid * 33 + k];
+#pragma unroll
+          for (uint32_t j = 0; j < kFbGroup; j++) {
+            if (j < nj) { acc[j] = __fmaf_rn(c, s_qs[j * dim_ext + k0 + k], acc[j]); }
+          }
+        }
+      }
+    }
+    if (l0 + tid < n_lists) {
+#pragma unroll
+      for (uint32_t j = 0; j < kFbGroup; j++) {
+        if (j < nj) { scratch[size_t(j0 + j) * n_lists + l0 + tid] = __fmul_rn(alpha, acc[j]); }
+      }
+    }
+  }
+}
+
 __global__ void __launch_bounds__(256)
 coarse_fallback_kernel(const uint32_t* __restrict__ redo_list, const uint32_t* __restrict__ redo_count,
                        const float* __restrict__ centers,
@@ -925,11 +1037,15 @@ coarse_fallback_kernel(const uint32_t* __restrict__ redo_list, const uint32_t* _
     const uint32_t q = redo_all ? ri : redo_list[ri];
     for (uint32_t i = tid; i < dim_ext; i += 256) { s_q[i] = fq[size_t(q) * dim_ext + i]; }
     __syncthreads();
-    for (uint32_t l = tid; l < n_lists; l += 256) {
-      const float* c = centers + size_t(l) * dim_ext;
-      float acc      = 0.0f;
-      for (uint32_t k = 0; k < dim_ext; k++) { acc = __fmaf_rn(__ldg(c + k), s_q[k], acc); }
-      row[l] = __fmul_rn(alpha, acc);
+    // the first gridDim.x queries were scored by coarse_fallback_scores_kernel (row = slot); later
+    // rounds (many queries to redo: rare) score here, one chain per thread
+    if (ri >= gridDim.x) {
+      for (uint32_t l = tid; l < n_lists; l += 256) {
+        const float* c = centers + size_t(l) * dim_ext;
+        float acc      = 0.0f;
+        for (uint32_t k = 0; k < dim_ext; k++) { acc = __fmaf_rn(__ldg(c + k), s_q[k], acc); }
+        row[l] = __fmul_rn(alpha, acc);
+      }
     }
     if (tid == 0) {
       s_prefix    = 0;
@@ -1102,7 +1218,8 @@ size_t coarse_tc_workspace_bytes(uint32_t n_queries, uint32_t n_lists, uint32_t 
   lay.add(size_t(n_queries) * n_tiles * 4 * 4);          // bound per 64-column unit
   lay.add(size_t(n_queries) * 4);            // queries to redo exactly
   lay.add(256);                              // error word, fallback counter, redo counter
-  lay.add(size_t(64) * n_lists * 4);         // fallback scratch rows
+  lay.add(size_t(kFbSlots) * n_lists * 4);   // fallback scratch rows
+  lay.add(size_t(n_queries) * 4);            // power-of-two scale of every query row
   return lay.total();
 }
 
@@ -1178,12 +1295,13 @@ void select_clusters_tc(raft::resources& res, const float* centers, const float*
   auto* cand_bnd  = reinterpret_cast<uint32_t*>(ws + lay.add(size_t(n_queries) * n_tiles * 4 * 4));
   auto* redo_list = reinterpret_cast<uint32_t*>(ws + lay.add(size_t(n_queries) * 4));
   auto* words     = reinterpret_cast<uint32_t*>(ws + lay.add(256));
-  float* scratch  = reinterpret_cast<float*>(ws + lay.add(size_t(64) * n_lists * 4));
+  float* scratch  = reinterpret_cast<float*>(ws + lay.add(size_t(kFbSlots) * n_lists * 4));
+  float* row_scale = reinterpret_cast<float*>(ws + lay.add(size_t(n_queries) * 4));
   cudaStream_t stream = res.stream;
 
   if (ext_scale == 1.0f) { ext_col = dim_ext; }
-  split_tf32_kernel<<<unsigned(ceildiv<size_t>(size_t(n_queries) * dim_ext, 256)), 256, 0, stream>>>(
-    fq, size_t(n_queries) * dim_ext, dim_ext, ext_col, ext_scale, fq_hi, fq_lo);
+  split_queries_kernel<<<ceildiv<uint32_t>(n_queries * 32u, 256u), 256, 0, stream>>>(
+    fq, n_queries, dim_ext, ext_col, ext_scale, cmax, fq_hi, fq_lo, row_scale);
   CUDA_TRY(cudaMemsetAsync(words, 0, 12, stream));
 
   const CUtensorMap m_a_hi = make_map(fq_hi, n_queries, dim_ext, kBM);
@@ -1248,27 +1366,31 @@ void select_clusters_tc(raft::resources& res, const float* centers, const float*
     if (kph == 16) {
       coarse_finish_small_kernel<16><<<n_queries, 256, fin_small_smem, stream>>>(
         cand_key, cand_bnd, n_cand, centers, fq, n_lists, dim_ext, alpha, n_probes, C, cmax, eps_rel, probes,
-        scores_out, redo_list, words + 2, fin_rows, words, ext_col, ext_scale);
+        scores_out, redo_list, words + 2, fin_rows, words, ext_col, ext_scale, row_scale);
     } else {
       coarse_finish_small_kernel<8><<<n_queries, 256, fin_small_smem, stream>>>(
         cand_key, cand_bnd, n_cand, centers, fq, n_lists, dim_ext, alpha, n_probes, C, cmax, eps_rel, probes,
-        scores_out, redo_list, words + 2, fin_rows, words, ext_col, ext_scale);
+        scores_out, redo_list, words + 2, fin_rows, words, ext_col, ext_scale, row_scale);
     }
   } else {
     if (fin_smem > 48 * 1024) { ensure_dynamic_smem(reinterpret_cast<const void*>(coarse_finish_kernel), fin_smem); }
     coarse_finish_kernel<<<n_queries, 256, fin_smem, stream>>>(cand_key, cand_bnd, n_cand, kph, centers, fq,
                                                                n_lists, dim_ext, alpha, n_probes, C, cap,
                                                                cmax, eps_rel, probes, scores_out, redo_list,
-                                                               words + 2, words, ext_col, ext_scale);
+                                                               words + 2, words, ext_col, ext_scale, row_scale);
   }
   uint32_t cap_fb = 2;
   while (cap_fb < n_probes) { cap_fb <<= 1; }
   const size_t fb_smem = size_t(cap_fb) * 8 + size_t(dim_ext) * 4;
-  coarse_fallback_kernel<<<64, 256, fb_smem, stream>>>(redo_list, words + 2, centers, fq, n_queries, n_lists,
+  const size_t fs_smem = (size_t(256) * 33 + size_t(kFbGroup) * dim_ext) * 4;
+  ensure_dynamic_smem(reinterpret_cast<const void*>(coarse_fallback_scores_kernel), fs_smem);
+  coarse_fallback_scores_kernel<<<ceildiv<uint32_t>(n_lists, 256u), 256, fs_smem, stream>>>(
+    redo_list, words + 2, centers, fq, n_queries, n_lists, dim_ext, alpha, scratch, kFbSlots, words);
+  coarse_fallback_kernel<<<kFbSlots, 256, fb_smem, stream>>>(redo_list, words + 2, centers, fq, n_queries, n_lists,
                                                        dim_ext, alpha, n_probes, cap_fb, scratch, probes,
                                                        scores_out, words + 1, words);
   CUDA_TRY(cudaGetLastError());
-  res.launches += 4;
+  res.launches += 5;
   if (!res.tc_redo_pending) {
     // the error word and how many queries this batch redid exactly: read back without waiting, looked
     // at before a later batch and at the handle's next synchronisation
