@@ -734,7 +734,8 @@ extern "C" cuvsError_t cuvsB200CoarseSelect(cuvsResources_t res, void* index_han
 extern "C" cuvsError_t cuvsB200SetCoarseMode(int mode)
 {
   return translate_exceptions([=] {
-    CUVS_EXPECTS((mode >= 0 && mode <= 2) || (mode >= 11 && mode <= 13), "mode must be 0, 1, 2, 11, 12 or 13");
+    CUVS_EXPECTS((mode >= 0 && mode <= 2) || (mode >= 11 && mode <= 13) || mode == 21 || mode == 22,
+                 "mode must be 0, 1, 2, 11, 12, 13, 21 or 22");
     ivf_pq::set_coarse_mode(mode);
   });
 }

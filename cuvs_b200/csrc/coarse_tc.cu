@@ -254,32 +254,45 @@ struct tc_params {
   uint32_t skip_kb;     // test only: 1 + index of an operand stage the producer leaves unfilled, 0 = none
 };
 
-template <int kStreams, int kKeep, int kProducts>
+// kARes ("query operand resident"): the whole K extent of the 128-query operand tile (hi and lo) stays
+// in shared memory while the CTA walks consecutive list tiles of that query tile, and only the list
+// operand streams through the stages -- half the operand bytes out of L2 per output tile.  Needs the
+// query tile to leave room for at least four list stages (k_blocks <= 8 with two products).
+template <int kStreams, int kKeep, int kProducts, bool kARes>
 __global__ void __launch_bounds__(kThreads, 1)
 coarse_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
                  const __grid_constant__ CUtensorMap map_b_hi, const __grid_constant__ CUtensorMap map_b_lo,
                  const tc_params p)
 {
+  static_assert(!kARes || kProducts <= 2, "the resident-query variant stages one list operand");
   // Only the operands the chosen number of products reads are staged, and the 192 KB of stage memory
   // hold as many stages of that size as fit: 4 x 48 KB (three products), 6 x 32 KB (two), 8 x 24 KB
   // (one).  With fewer than three products the loop is bound by the latency of the operand loads,
   // so more of them in flight is what shortens it.
-  constexpr uint32_t kOffALo = kBM * kBK * 4;
-  constexpr uint32_t kOffBHi = kBM * kBK * 4 * (kProducts >= 2 ? 2 : 1);
+  constexpr uint32_t kATile  = kBM * kBK * 4;  // one K block of the query tile: 8 KB
+  constexpr uint32_t kOffALo = kATile;
+  constexpr uint32_t kOffBHi = kARes ? 0u : kATile * (kProducts >= 2 ? 2 : 1);
   constexpr uint32_t kOffBLo = kOffBHi + kBN * kBK * 4;
   constexpr uint32_t kStageB = kOffBHi + kBN * kBK * 4 * (kProducts >= 3 ? 2 : 1);
-  constexpr int kNS          = int((kStages * kStageBytes) / kStageB);
+  constexpr int kMaxNS       = 8;
+  // resident variant: [query tile: k_blocks x hi, k_blocks x lo][list stages]
+  const uint32_t a_bytes = kARes ? p.k_blocks * kATile * (kProducts >= 2 ? 2u : 1u) : 0u;
+  const int kNS = kARes ? int(min(uint32_t(kMaxNS), (kStages * kStageBytes - a_bytes) / kStageB))
+                        : int((kStages * kStageBytes) / kStageB);
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_a  = smem_u32(smem_raw);
   const uint32_t base_a = (raw_a + 1023u) & ~1023u;             // tiles need 1024-byte alignment
   uint8_t* base_p       = smem_raw + (base_a - raw_a);
   uint64_t* bars        = reinterpret_cast<uint64_t*>(base_p + kStages * kStageBytes);
-  // bars: full[kNS], empty[kNS], tmem_full[2], tmem_empty[2], then the TMEM address slot
+  // bars: full[8], empty[8], tmem_full[2], tmem_empty[2], query tile full / empty, then the TMEM address slot
   const uint32_t bar_full   = smem_u32(bars);
-  const uint32_t bar_empty  = bar_full + kNS * 8;
-  const uint32_t bar_tfull  = bar_empty + kNS * 8;
+  const uint32_t bar_empty  = bar_full + kMaxNS * 8;
+  const uint32_t bar_tfull  = bar_empty + kMaxNS * 8;
   const uint32_t bar_tempty = bar_tfull + 2 * 8;
-  uint32_t* tmem_slot       = reinterpret_cast<uint32_t*>(bars + 2 * kNS + 4);
+  const uint32_t bar_afull  = bar_tempty + 2 * 8;
+  const uint32_t bar_aempty = bar_afull + 8;
+  uint32_t* tmem_slot       = reinterpret_cast<uint32_t*>(bars + 2 * kMaxNS + 6);
+  const uint32_t stage_base = base_a + a_bytes;
   __shared__ uint32_t s_failed;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -293,6 +306,8 @@ coarse_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
       mbar_init(bar_tfull + a * 8, 1);
       mbar_init(bar_tempty + a * 8, kEpiWarps);  // one arrival per epilogue warp
     }
+    mbar_init(bar_afull, 1);
+    mbar_init(bar_aempty, 1);
     s_failed = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -306,21 +321,45 @@ coarse_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
   tc_fence_after();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
 
-  // Persistent CTAs (one per SM): output tiles blockIdx.x, blockIdx.x + gridDim.x, ... of the
-  // n_work = query tiles x list tiles, list tile fastest, so every SM gets the same number of tiles
-  // to within one.
-  uint32_t n_my_tiles = 0;
-  if (blockIdx.x < p.n_work) { n_my_tiles = (p.n_work - blockIdx.x + gridDim.x - 1) / gridDim.x; }
+  // Persistent CTAs (one per SM) over the n_work = query tiles x list tiles, list tile fastest, every SM
+  // the same number of tiles to within one: tiles blockIdx.x, blockIdx.x + gridDim.x, ... -- or, with
+  // the query operand resident, one contiguous run of tiles (the query tile changes once or twice).
+  uint32_t n_my_tiles = 0, first_tile = blockIdx.x, tile_step = gridDim.x;
+  if constexpr (kARes) {
+    first_tile = uint32_t(uint64_t(p.n_work) * blockIdx.x / gridDim.x);
+    n_my_tiles = uint32_t(uint64_t(p.n_work) * (blockIdx.x + 1) / gridDim.x) - first_tile;
+    tile_step  = 1;
+  } else {
+    if (blockIdx.x < p.n_work) { n_my_tiles = (p.n_work - blockIdx.x + gridDim.x - 1) / gridDim.x; }
+  }
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
     if (lane == 0) {
-      uint32_t stage = 0, phase = 0;
+      uint32_t stage = 0, phase = 0, a_loads = 0, q_tile_now = 0xFFFFFFFFu;
       bool ok = true;
       for (uint32_t i = 0; ok && i < n_my_tiles; i++) {
-        const uint32_t g  = blockIdx.x + i * gridDim.x;
+        const uint32_t g  = first_tile + i * tile_step;
         const uint32_t q0 = (g / p.n_tiles) * kBM;
         const int n0      = int((g % p.n_tiles) * kBN);
+        if constexpr (kARes) {
+          if (g / p.n_tiles != q_tile_now) {
+            // a new query tile: once the MMAs that read the old one have finished, load all its K blocks
+            q_tile_now = g / p.n_tiles;
+            if (!mbar_wait(bar_aempty, (a_loads & 1u) ^ 1u, p.spin_limit)) {
+              ok = false;
+              break;
+            }
+            a_loads++;
+            mbar_arrive_expect_tx(bar_afull, a_bytes);
+            for (uint32_t kb = 0; kb < p.k_blocks; kb++) {
+              tma_load_2d(base_a + kb * kATile, &map_a_hi, bar_afull, int(kb * kBK), int(q0));
+              if constexpr (kProducts >= 2) {
+                tma_load_2d(base_a + (p.k_blocks + kb) * kATile, &map_a_lo, bar_afull, int(kb * kBK), int(q0));
+              }
+            }
+          }
+        }
         for (uint32_t kb = 0; kb < p.k_blocks; kb++) {
           if (!mbar_wait(bar_empty + stage * 8, phase ^ 1u, p.spin_limit)) {
             ok = false;
@@ -335,13 +374,16 @@ coarse_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
             }
             continue;
           }
-          const uint32_t dst = base_a + stage * kStageB;
+          const uint32_t dst = stage_base + stage * kStageB;
           const uint32_t bar = bar_full + stage * 8;
           // operands the chosen number of products needs: 1: hi*hi; 2: + lo*hi; 3: + hi*lo
-          constexpr uint32_t kBytes = (kBM + kBN + (kProducts >= 2 ? kBM : 0) + (kProducts >= 3 ? kBN : 0)) * kBK * 4;
+          constexpr uint32_t kBytes =
+            ((kARes ? 0 : kBM + (kProducts >= 2 ? kBM : 0)) + kBN + (kProducts >= 3 ? kBN : 0)) * kBK * 4;
           mbar_arrive_expect_tx(bar, kBytes);
-          tma_load_2d(dst, &map_a_hi, bar, int(kb * kBK), int(q0));
-          if constexpr (kProducts >= 2) { tma_load_2d(dst + kOffALo, &map_a_lo, bar, int(kb * kBK), int(q0)); }
+          if constexpr (!kARes) {
+            tma_load_2d(dst, &map_a_hi, bar, int(kb * kBK), int(q0));
+            if constexpr (kProducts >= 2) { tma_load_2d(dst + kOffALo, &map_a_lo, bar, int(kb * kBK), int(q0)); }
+          }
           tma_load_2d(dst + kOffBHi, &map_b_hi, bar, int(kb * kBK), n0);
           if constexpr (kProducts >= 3) {
             tma_load_2d(dst + kOffBLo, &map_b_lo, bar, int(kb * kBK), n0);
@@ -364,7 +406,7 @@ coarse_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
       // instruction descriptor: fp32 accumulate, tf32 x tf32, both K-major, N = 256, M = 128
       constexpr uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | (uint32_t(kBN >> 3) << 17) |
                                  (uint32_t(kBM >> 4) << 24);
-      uint32_t stage = 0, phase = 0;
+      uint32_t stage = 0, phase = 0, a_loads = 0, q_tile_now = 0xFFFFFFFFu;
       bool ok = true;
       for (uint32_t i = 0; ok && i < n_my_tiles; i++) {
         const uint32_t acc       = i & 1u;
@@ -372,6 +414,17 @@ coarse_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
         if (!mbar_wait(bar_tempty + acc * 8, acc_phase ^ 1u, p.spin_limit)) {
           ok = false;
           break;
+        }
+        if constexpr (kARes) {
+          const uint32_t g = first_tile + i * tile_step;
+          if (g / p.n_tiles != q_tile_now) {
+            q_tile_now = g / p.n_tiles;
+            if (!mbar_wait(bar_afull, a_loads & 1u, p.spin_limit)) {
+              ok = false;
+              break;
+            }
+            a_loads++;
+          }
         }
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + acc * kBN;
@@ -381,9 +434,9 @@ coarse_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
             break;
           }
           tc_fence_after();
-          const uint32_t sa      = base_a + stage * kStageB;
-          const uint64_t d_a_hi  = make_desc(sa);
-          const uint64_t d_a_lo  = make_desc(sa + kOffALo);
+          const uint32_t sa      = stage_base + stage * kStageB;
+          const uint64_t d_a_hi  = make_desc(kARes ? base_a + kb * kATile : sa);
+          const uint64_t d_a_lo  = make_desc(kARes ? base_a + (p.k_blocks + kb) * kATile : sa + kOffALo);
           const uint64_t d_b_hi  = make_desc(sa + kOffBHi);
           const uint64_t d_b_lo  = make_desc(sa + kOffBLo);
 #pragma unroll
@@ -400,6 +453,11 @@ coarse_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
           }
         }
         if (ok) { tc_commit(bar_tfull + acc * 8); }
+        if constexpr (kARes) {
+          // last tile of this query tile: the query operand may be replaced once these MMAs are done
+          const uint32_t g = first_tile + i * tile_step;
+          if (ok && i + 1 < n_my_tiles && (g + tile_step) / p.n_tiles != q_tile_now) { tc_commit(bar_aempty); }
+        }
       }
       if (!ok) {
         atomicExch(p.error, ERR_TIMEOUT);
@@ -416,7 +474,7 @@ coarse_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
     const uint32_t row     = quarter * 32 + lane;
     bool ok = true;
     for (uint32_t i = 0; i < n_my_tiles; i++) {
-      const uint32_t g         = blockIdx.x + i * gridDim.x;
+      const uint32_t g         = first_tile + i * tile_step;
       const uint32_t tile      = g % p.n_tiles;
       const uint32_t q         = (g / p.n_tiles) * kBM + row;
       const uint32_t acc       = i & 1u;
@@ -544,7 +602,7 @@ coarse_finish_kernel(const uint32_t* __restrict__ cand_key, const uint32_t* __re
                      uint32_t* __restrict__ probes, float* __restrict__ scores_out,
                      uint32_t* __restrict__ redo_list, uint32_t* __restrict__ redo_count,
                      const uint32_t* __restrict__ error_word, uint32_t ext_col, float ext_scale,
-                     const float* __restrict__ row_scale)
+                     const float* __restrict__ row_scale, float down_thr)
 {
   // the GEMM gave up on a wait: its candidates are incomplete, every query is redone exactly
   if (*error_word != 0u) { return; }
@@ -689,8 +747,14 @@ coarse_finish_kernel(const uint32_t* __restrict__ cand_key, const uint32_t* __re
       const float last_dot = ordered_to_float(uint32_t(s_keys[n_probes - 1] >> 32)) / alpha;
       // all lists rescored (n_sel == every valid candidate == every list) needs no proof
       ok = (last_dot - unseen > eps) || (n_sel >= n_lists);
+      // would the guard also hold with one product less (a wider error bound)?  Counted for the
+      // handle's choice of the number of products; no effect on this batch.
+      if (ok && n_sel < n_lists && !(last_dot - unseen > down_thr * eps)) { atomicAdd(redo_count + 1, 1u); }
     }
-    if (!ok) { redo_list[atomicAdd(redo_count, 1u)] = q; }
+    if (!ok) {
+      redo_list[atomicAdd(redo_count, 1u)] = q;
+      atomicAdd(redo_count + 1, 1u);
+    }
   }
 }
 
@@ -776,7 +840,7 @@ coarse_finish_small_kernel(const uint32_t* __restrict__ cand_key, const uint32_t
                            uint32_t* __restrict__ probes, float* __restrict__ scores_out,
                            uint32_t* __restrict__ redo_list, uint32_t* __restrict__ redo_count,
                            uint32_t rows_per_round, const uint32_t* __restrict__ error_word, uint32_t ext_col,
-                           float ext_scale, const float* __restrict__ row_scale)
+                           float ext_scale, const float* __restrict__ row_scale, float down_thr)
 {
   // the GEMM gave up on a wait: its candidates are incomplete, every query is redone exactly
   if (*error_word != 0u) { return; }
@@ -945,8 +1009,12 @@ coarse_finish_small_kernel(const uint32_t* __restrict__ cand_key, const uint32_t
         const float last_dot = ordered_to_float(uint32_t(last_key >> 32)) / alpha;
         // all lists rescored (n_sel == every valid candidate == every list) needs no proof
         ok = (last_dot - unseen > eps) || (n_sel >= n_lists);
+        if (ok && n_sel < n_lists && !(last_dot - unseen > down_thr * eps)) { atomicAdd(redo_count + 1, 1u); }
       }
-      if (!ok) { redo_list[atomicAdd(redo_count, 1u)] = q; }
+      if (!ok) {
+        redo_list[atomicAdd(redo_count, 1u)] = q;
+        atomicAdd(redo_count + 1, 1u);
+      }
     }
   }
 }
@@ -1177,6 +1245,12 @@ int& tc_products_ref()
   return products;
 }
 
+bool& tc_resident_ref()
+{
+  static bool on = true;
+  return on;
+}
+
 // test hook: a shorter limit for the bounded waits and one operand stage left unfilled
 struct tc_fault {
   uint32_t spin_limit = 0, skip_kb = 0;
@@ -1190,6 +1264,7 @@ tc_fault& tc_fault_ref()
 }  // namespace
 
 void set_coarse_tc_products(int products) { tc_products_ref() = products; }
+void set_coarse_tc_resident(bool on) { tc_resident_ref() = on; }
 void set_coarse_tc_wait_test(uint32_t spin_limit, uint32_t skip_kb)
 {
   tc_fault_ref().spin_limit = spin_limit;
@@ -1302,7 +1377,7 @@ void select_clusters_tc(raft::resources& res, const float* centers, const float*
   if (ext_scale == 1.0f) { ext_col = dim_ext; }
   split_queries_kernel<<<ceildiv<uint32_t>(n_queries * 32u, 256u), 256, 0, stream>>>(
     fq, n_queries, dim_ext, ext_col, ext_scale, cmax, fq_hi, fq_lo, row_scale);
-  CUDA_TRY(cudaMemsetAsync(words, 0, 12, stream));
+  CUDA_TRY(cudaMemsetAsync(words, 0, 16, stream));  // error, queries redone, redo counter, would-fail counter
 
   const CUtensorMap m_a_hi = make_map(fq_hi, n_queries, dim_ext, kBM);
   const CUtensorMap m_a_lo = make_map(fq_lo, n_queries, dim_ext, kBM);
@@ -1328,28 +1403,38 @@ void select_clusters_tc(raft::resources& res, const float* centers, const float*
   res.adopt_tc_verdict();  // what the last batch of this handle reported, if it has arrived
   int products = exact_operands ? 1 : tc_products_ref();
   if (products == 0) { products = res.tc_products; }
-  const float eps_rel = float(dim_ext + 8) * 2.4e-7f + 3.1e-5f +
-                        (exact_operands ? 0.0f : (products == 1 ? 9.8e-4f : (products == 2 ? 4.9e-4f : 0.0f)));
+  const float eps_base = float(dim_ext + 8) * 2.4e-7f + 3.1e-5f;
+  const float eps_split[4] = {0.0f, 9.8e-4f, 4.9e-4f, 0.0f};
+  const float eps_rel = eps_base + (exact_operands ? 0.0f : eps_split[products]);
+  // A query would pass the guard with one product less if its margin exceeds that level's bound plus
+  // the largest change of the unseen maximum between the two levels (the sum of both bounds).
+  const float down_thr = (exact_operands || products == 1)
+                           ? 0.0f
+                           : 1.5f + 2.0f * (eps_base + eps_split[products - 1]) / eps_rel;
   auto launch = [&](auto kernel) {
     // every instantiation needs its shared-memory limit raised once per device
     ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), kSmemBytes);
     kernel<<<grid, kThreads, kSmemBytes, stream>>>(m_a_hi, m_a_lo, m_b_hi, m_b_lo, p);
   };
+  // query operand resident in shared memory when it leaves room for at least four list stages
+  const uint32_t a_bytes = p.k_blocks * uint32_t(kBM * kBK * 4) * (products >= 2 ? 2u : 1u);
+  const bool resident    = products <= 2 && a_bytes + 4u * uint32_t(kBN * kBK * 4) <= kStages * kStageBytes &&
+                        tc_resident_ref();
   if (four_by_4) {
     if (products == 1) {
-      launch(coarse_tc_kernel<2, 4, 1>);
+      resident ? launch(coarse_tc_kernel<2, 4, 1, true>) : launch(coarse_tc_kernel<2, 4, 1, false>);
     } else if (products == 2) {
-      launch(coarse_tc_kernel<2, 4, 2>);
+      resident ? launch(coarse_tc_kernel<2, 4, 2, true>) : launch(coarse_tc_kernel<2, 4, 2, false>);
     } else {
-      launch(coarse_tc_kernel<2, 4, 3>);
+      launch(coarse_tc_kernel<2, 4, 3, false>);
     }
   } else {
     if (products == 1) {
-      launch(coarse_tc_kernel<1, 8, 1>);
+      resident ? launch(coarse_tc_kernel<1, 8, 1, true>) : launch(coarse_tc_kernel<1, 8, 1, false>);
     } else if (products == 2) {
-      launch(coarse_tc_kernel<1, 8, 2>);
+      resident ? launch(coarse_tc_kernel<1, 8, 2, true>) : launch(coarse_tc_kernel<1, 8, 2, false>);
     } else {
-      launch(coarse_tc_kernel<1, 8, 3>);
+      launch(coarse_tc_kernel<1, 8, 3, false>);
     }
   }
   CUDA_TRY(cudaGetLastError());
@@ -1366,18 +1451,18 @@ void select_clusters_tc(raft::resources& res, const float* centers, const float*
     if (kph == 16) {
       coarse_finish_small_kernel<16><<<n_queries, 256, fin_small_smem, stream>>>(
         cand_key, cand_bnd, n_cand, centers, fq, n_lists, dim_ext, alpha, n_probes, C, cmax, eps_rel, probes,
-        scores_out, redo_list, words + 2, fin_rows, words, ext_col, ext_scale, row_scale);
+        scores_out, redo_list, words + 2, fin_rows, words, ext_col, ext_scale, row_scale, down_thr);
     } else {
       coarse_finish_small_kernel<8><<<n_queries, 256, fin_small_smem, stream>>>(
         cand_key, cand_bnd, n_cand, centers, fq, n_lists, dim_ext, alpha, n_probes, C, cmax, eps_rel, probes,
-        scores_out, redo_list, words + 2, fin_rows, words, ext_col, ext_scale, row_scale);
+        scores_out, redo_list, words + 2, fin_rows, words, ext_col, ext_scale, row_scale, down_thr);
     }
   } else {
     if (fin_smem > 48 * 1024) { ensure_dynamic_smem(reinterpret_cast<const void*>(coarse_finish_kernel), fin_smem); }
     coarse_finish_kernel<<<n_queries, 256, fin_smem, stream>>>(cand_key, cand_bnd, n_cand, kph, centers, fq,
                                                                n_lists, dim_ext, alpha, n_probes, C, cap,
                                                                cmax, eps_rel, probes, scores_out, redo_list,
-                                                               words + 2, words, ext_col, ext_scale, row_scale);
+                                                               words + 2, words, ext_col, ext_scale, row_scale, down_thr);
   }
   uint32_t cap_fb = 2;
   while (cap_fb < n_probes) { cap_fb <<= 1; }
@@ -1395,7 +1480,7 @@ void select_clusters_tc(raft::resources& res, const float* centers, const float*
     // the error word and how many queries this batch redid exactly: read back without waiting, looked
     // at before a later batch and at the handle's next synchronisation
     if (!res.tc_redo_event) { CUDA_TRY(cudaEventCreateWithFlags(&res.tc_redo_event, cudaEventDisableTiming)); }
-    CUDA_TRY(cudaMemcpyAsync(res.pinned + 8, words, 8, cudaMemcpyDeviceToHost, stream));
+    CUDA_TRY(cudaMemcpyAsync(res.pinned + 8, words, 16, cudaMemcpyDeviceToHost, stream));
     CUDA_TRY(cudaEventRecord(res.tc_redo_event, stream));
     res.tc_redo_queries = n_queries;
     res.tc_redo_adapts  = !exact_operands && tc_products_ref() == 0;

@@ -981,7 +981,10 @@ void search_any(raft::resources& res, const search_params& params, const index<i
 void set_coarse_mode(int mode)
 {
   // 0 auto, 1 exact SIMT path, 2 tensor-core path; 11 / 12 / 13: tensor-core path with 1 / 2 / 3
-  // products of the TF32 split
+  // products of the TF32 split; 21 / 22: the same with 1 / 2 products and every operand streamed
+  // (no query tile kept resident in shared memory)
+  set_coarse_tc_resident(!(mode == 21 || mode == 22));
+  if (mode == 21 || mode == 22) { mode -= 10; }
   if (mode >= 11 && mode <= 13) {
     set_coarse_tc_products(mode - 10);
     mode = 2;

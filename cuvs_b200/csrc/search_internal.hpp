@@ -55,6 +55,9 @@ void coarse_only(raft::resources& res, const index<int64_t>& idx, const void* qu
 
 // products of the TF32 split the tensor-core coarse GEMM issues per K step (1, 2 or 3)
 void set_coarse_tc_products(int products);
+// process-wide override used by tests: false = the tensor-core coarse GEMM streams both operands even
+// where the query tile could stay resident in shared memory
+void set_coarse_tc_resident(bool on);
 // test hook of the bounded waits of the tensor-core coarse kernel: iterations a wait may take (0 = the
 // default) and 1 + index of an operand stage left unfilled (0 = none)
 void set_coarse_tc_wait_test(uint32_t spin_limit, uint32_t skip_kb);

@@ -152,9 +152,11 @@ struct resources {
   void stats_resolve();
 
   // Tensor-core coarse stage: products of the TF32 split per K step used by this handle (starts at
-  // two, raised when a finished batch had to redo more than 1/256 of its queries exactly); the count
-  // of the last batch arrives in pinned[8] once tc_redo_event has completed.
+  // two; raised when a finished batch had to redo more than 1/256 of its queries exactly, lowered when
+  // all but 1/1024 of a batch would have passed the guard with one product less); the counters of the
+  // last batch arrive in pinned[8..11] once tc_redo_event has completed.
   int tc_products            = 2;
+  int tc_products_floor      = 1;  // raised when a level produced too many exact redos
   cudaEvent_t tc_redo_event  = nullptr;
   bool tc_redo_pending       = false;
   uint32_t tc_redo_queries   = 0;

@@ -44,7 +44,8 @@ CUVS_EXPORT cuvsError_t cuvsB200CoarseSelect(cuvsResources_t res, void* index /*
 /* No counterpart in the reference: force the probe-selection path used by cuvsIvfPqSearch in this
  * process (0 = automatic, 1 = exact SIMT path, 2 = tensor-core path where it applies; 11, 12, 13 =
  * tensor-core path with exactly 1, 2 or 3 products of the TF32 operand split per K step instead
- * of the per-handle adaptive choice). */
+ * of the per-handle adaptive choice; 21, 22 = as 11, 12 but with both operands streamed, no query
+ * tile kept resident in shared memory). */
 CUVS_EXPORT cuvsError_t cuvsB200SetCoarseMode(int mode);
 /* No counterpart in the reference: where the fine-search kernel of cuvsIvfPqSearch keeps a
  * per-subspace PQ codebook in this process: 0 = tensor memory where it fits (the default),

@@ -349,18 +349,20 @@ def test_search_is_identical_under_both_coarse_paths(ivf, many_lists):
     assert (i1 == i2).all() and (d1.view(np.uint32) == d2.view(np.uint32)).all()
 
 
-@pytest.mark.parametrize("products", [1, 2, 3])
-def test_coarse_tensor_core_products_all_give_the_exact_probes(ivf, many_lists, products):
+@pytest.mark.parametrize("mode", [11, 12, 13, 21, 22])
+def test_coarse_tensor_core_products_all_give_the_exact_probes(ivf, many_lists, mode):
     """The tensor-core coarse GEMM may issue 1, 2 or 3 products of the TF32 operand split per K step
     (a handle starts with 2 and raises the number if too many queries need the exact redo); the guard
-    widens its error bound accordingly, so the probes and their scores equal the exact path's."""
+    widens its error bound accordingly, so the probes and their scores equal the exact path's.
+    Modes 11 and 12 keep the query tile resident in shared memory on this shape, 21 and 22 stream
+    both operands."""
     from cuvs_b200 import _lib as L
     x, g = many_lists
     q = make_mixture(700, 64, 512, 0.25, seed=81)
     lib = L.load()
     try:
         p1, s1, _ = coarse_select(g, q, 20, 1)
-        L.check(lib.cuvsB200SetCoarseMode(10 + products))
+        L.check(lib.cuvsB200SetCoarseMode(mode))
         p2, s2, st = coarse_select(g, q, 20, 2)
     finally:
         L.check(lib.cuvsB200SetCoarseMode(0))
