@@ -228,8 +228,19 @@ class ClockSampler:
 # --------------------------------------------------------------------------------------------
 # fixture: dataset, index file, ground truth -- cached in a temp dir for back-to-back runs
 # --------------------------------------------------------------------------------------------
+def builder_version():
+    """Hash of the sources that decide what an index built here contains (a cached fixture of another
+    builder is not reused)."""
+    h = hashlib.sha1()
+    here = os.path.dirname(os.path.abspath(__file__))
+    for name in ("build.cu", "index.cu"):
+        with open(os.path.join(here, "cuvs_b200", "csrc", name), "rb") as f:
+            h.update(f.read())
+    return h.hexdigest()[:8]
+
+
 def cache_dir(wl):
-    key = hashlib.sha1(json.dumps(wl, sort_keys=True, default=str).encode()).hexdigest()[:12]
+    key = hashlib.sha1((json.dumps(wl, sort_keys=True, default=str) + builder_version()).encode()).hexdigest()[:12]
     base = "/dev/shm" if os.path.isdir("/dev/shm") else tempfile.gettempdir()
     d = os.path.join(base, f"cuvs_b200_bench_{key}")
     os.makedirs(d, exist_ok=True)

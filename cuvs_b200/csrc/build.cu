@@ -13,9 +13,12 @@
 //     squared distance, lowest code on ties
 //     (cpp/src/neighbors/ivf_pq/ivf_pq_process_and_fill_codes.cuh:84-126); codes written in the
 //     interleaved layout (cpp/src/neighbors/ivf_pq/ivf_pq_codepacking.cuh:135-168)
-// The coarse clustering is plain Lloyd k-means with re-seeding of empty clusters (the reference
-// uses balanced hierarchical k-means); unlike the reference's atomic slot allocation, vectors are
-// placed in a list in input order, so extend is deterministic.
+// The coarse clustering is Lloyd k-means over all lists at once with the reference's balancing step
+// between iterations (underfull clusters restart next to overfull ones, size-sorted donors,
+// cpp/src/cluster/detail/kmeans_balanced.cuh:616-720) and re-seeding of empty clusters; the reference
+// first clusters hierarchically (mesoclusters) to make training cheap, which the tensor-core
+// labelling makes unnecessary here.  Unlike the reference's atomic slot allocation, vectors are placed
+// in a list in input order, so extend is deterministic.
 #include "ivf_pq.hpp"
 #include "search_internal.hpp"
 #include "topk.cuh"
@@ -177,6 +180,55 @@ __global__ void rotate_centers_kernel(const float* __restrict__ centers, const f
   float acc      = 0.0f;
   for (uint32_t k = 0; k < dim; k++) { acc = __fmaf_rn(R[k], c[k], acc); }
   out[i] = acc;
+}
+
+// Balancing step of the coarse k-means (the reference's adjust_centers with size-sorted donors,
+// cpp/src/cluster/detail/kmeans_balanced.cuh:520-720): one pseudo-random member row per cluster ...
+__global__ void pick_member_kernel(const uint32_t* __restrict__ labels, uint64_t n, uint32_t seed,
+                                   unsigned long long* __restrict__ member /* [n_lists], zeroed */)
+{
+  const uint64_t i = blockIdx.x * uint64_t(blockDim.x) + threadIdx.x;
+  if (i >= n) { return; }
+  // the row with the largest hash wins: a different member every iteration
+  uint32_t h = uint32_t(i) * 2654435761u + seed * 40503u;
+  h ^= h >> 15;
+  h *= 2246822519u;
+  h ^= h >> 13;
+  atomicMax(member + labels[i], (static_cast<unsigned long long>(h) << 32) | uint32_t(i));
+}
+
+// ... and, per (receiver, donor) pair, the receiver's centre re-initialised next to the donor's centre,
+// a small step (`offset`) towards one of the donor's rows, so that the next assignment splits the large
+// cluster.  One block per pair; norm column and zero tail rewritten.
+__global__ void adjust_centers_kernel(float* __restrict__ centers, const uint32_t* __restrict__ pairs /* [n_pairs][2] */,
+                                      const unsigned long long* __restrict__ member,
+                                      const float* __restrict__ x_ext, uint32_t dim, uint32_t dim_ext,
+                                      float offset, int normalize)
+{
+  __shared__ float s_red[4];
+  const uint32_t receiver = pairs[2 * blockIdx.x], donor = pairs[2 * blockIdx.x + 1];
+  const uint64_t row      = member[donor] & 0xFFFFFFFFull;
+  float* c                = centers + size_t(receiver) * dim_ext;
+  const float* d          = centers + size_t(donor) * dim_ext;
+  const float* x          = x_ext + row * dim_ext;
+  float ss                = 0.0f;
+  for (uint32_t i = threadIdx.x; i < dim; i += blockDim.x) {
+    const float v = d[i] + offset * (x[i] - d[i]);
+    c[i]          = v;
+    ss += v * v;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) { ss += __shfl_xor_sync(kFullMask, ss, o); }
+  if ((threadIdx.x & 31) == 0) { s_red[threadIdx.x >> 5] = ss; }
+  __syncthreads();
+  float norm2 = 0.0f;
+  for (uint32_t w = 0; w < (blockDim.x >> 5); w++) { norm2 += s_red[w]; }
+  if (normalize && norm2 > 0.0f) {
+    const float inv = 1.0f / sqrtf(norm2);
+    for (uint32_t i = threadIdx.x; i < dim; i += blockDim.x) { c[i] *= inv; }
+    norm2 = 1.0f;
+  }
+  for (uint32_t i = dim + threadIdx.x; i < dim_ext; i += blockDim.x) { c[i] = i == dim ? norm2 : 0.0f; }
 }
 
 // Recompute column `dim` (squared norm) and the zero tail of padded centers in place.
@@ -628,6 +680,11 @@ uint64_t chunk_rows_for(uint32_t dim_ext)
   const uint64_t budget = 1ull << 30;  // bytes of converted rows per chunk
   return std::max<uint64_t>(1024, std::min<uint64_t>(1u << 20, budget / (uint64_t(dim_ext) * 4)));
 }
+
+// balanced k-means defaults of the reference (cpp/include/cuvs/cluster/kmeans.hpp:181-204)
+constexpr double kBalanceLower  = 0.333;
+constexpr double kBalanceUpper  = 3.0;
+constexpr float kCentroidOffset = 0.01f;
 
 struct label_ctx {
   float alpha;
@@ -1167,6 +1224,43 @@ void build_any(raft::resources& res, const index_params& params, const void* dat
                                                          idx.centers());
     CUDA_TRY(cudaGetLastError());
     res.launches += 2;
+    // Balancing (not after the last step, whose means are final): clusters sorted by size, the i-th
+    // smallest paired with the i-th largest; where the small one is underfull (< 1/3 of the average)
+    // or the large one overfull (> 3 x the average), the small one restarts next to the large one.
+    if (it + 1 < iters && n_lists >= 2) {
+      std::vector<uint32_t> h_counts(n_lists);
+      CUDA_TRY(cudaMemcpyAsync(h_counts.data(), counts.data(), size_t(n_lists) * 4, cudaMemcpyDeviceToHost, stream));
+      res.sync();
+      std::vector<uint32_t> order(n_lists);
+      for (uint32_t l = 0; l < n_lists; l++) { order[l] = l; }
+      std::sort(order.begin(), order.end(), [&](uint32_t a, uint32_t b) {
+        return h_counts[a] != h_counts[b] ? h_counts[a] < h_counts[b] : a < b;
+      });
+      const double avg = double(n_train) / double(n_lists);
+      std::vector<uint32_t> h_pairs;
+      for (uint32_t i = 0; i < n_lists / 2; i++) {
+        const uint32_t small = order[i], large = order[n_lists - 1 - i];
+        const bool underfull = double(h_counts[small]) < avg * kBalanceLower;
+        const bool overfull  = double(h_counts[large]) > avg * kBalanceUpper;
+        if (!underfull && !overfull) { break; }  // sizes are sorted: no later pair qualifies either
+        if (h_counts[large] < 2) { break; }
+        h_pairs.push_back(small);
+        h_pairs.push_back(large);
+      }
+      if (!h_pairs.empty()) {
+        dev_array<uint32_t> d_pairs(h_pairs.size());
+        dev_array<unsigned long long> member(n_lists);
+        CUDA_TRY(cudaMemcpyAsync(d_pairs.data(), h_pairs.data(), h_pairs.size() * 4, cudaMemcpyHostToDevice, stream));
+        CUDA_TRY(cudaMemsetAsync(member.data(), 0, size_t(n_lists) * 8, stream));
+        pick_member_kernel<<<unsigned(ceildiv<uint64_t>(n_train, 256)), 256, 0, stream>>>(labels.data(), n_train,
+                                                                                         it + 1, member.data());
+        adjust_centers_kernel<<<unsigned(h_pairs.size() / 2), 128, 0, stream>>>(
+          idx.centers(), d_pairs.data(), member.data(), train.data(), dim, dim_ext, kCentroidOffset, lc.normalize);
+        CUDA_TRY(cudaGetLastError());
+        res.sync();  // the pair list and the member table are released here
+        res.launches += 2;
+      }
+    }
   }
   nearest_labeler(res, idx.centers(), n_lists, dim, dim_ext, lc.alpha)
     .run(train.data(), uint32_t(n_train), labels.data(), best.data());
