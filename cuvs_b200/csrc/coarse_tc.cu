@@ -602,21 +602,40 @@ coarse_finish_kernel(const uint32_t* __restrict__ cand_key, const uint32_t* __re
                      uint32_t* __restrict__ probes, float* __restrict__ scores_out,
                      uint32_t* __restrict__ redo_list, uint32_t* __restrict__ redo_count,
                      const uint32_t* __restrict__ error_word, uint32_t ext_col, float ext_scale,
-                     const float* __restrict__ row_scale, float down_thr)
+                     const float* __restrict__ row_scale, float down_thr, int by_maxima)
 {
   // the GEMM gave up on a wait: its candidates are incomplete, every query is redone exactly
   if (*error_word != 0u) { return; }
-  extern __shared__ uint64_t s_keys[];                 // [cap] keys; the query; the candidates
+  extern __shared__ uint64_t s_keys[];                 // [cap] keys; the query; the values to select among
   float* s_q      = reinterpret_cast<float*>(s_keys + cap);
-  uint32_t* key   = reinterpret_cast<uint32_t*>(s_q + dim_ext);  // [n_cand] staged once
+  // by_maxima: [n_cand / kph] largest key of every half tile; else [n_cand] every candidate key
+  uint32_t* key   = reinterpret_cast<uint32_t*>(s_q + dim_ext);
   __shared__ uint32_t s_hist[256];
   __shared__ uint32_t s_prefix, s_remaining, s_count;
   __shared__ float s_red[8];
   __shared__ uint32_t s_tb[8];
   const uint32_t q    = blockIdx.x;
   const uint32_t tid  = threadIdx.x;
-  {
-    const uint4* src = reinterpret_cast<const uint4*>(cand_key + size_t(q) * n_cand);
+  // by_maxima (C small against the number of half tiles): the threshold comes from the half-tile maxima
+  // alone -- at least C keys are >= the C-th largest maximum, so every key at or above it is taken (a
+  // superset of the C best keys, little larger); the candidate keys stay in global memory, read once
+  // here and again only for the half tiles that qualify.  Otherwise all keys are staged and the C-th
+  // largest key itself is the threshold.
+  const uint32_t n_half  = n_cand / kph;
+  const uint32_t n_sel_from = by_maxima ? n_half : n_cand;
+  const uint32_t* my_key = cand_key + size_t(q) * n_cand;
+  if (by_maxima) {
+    for (uint32_t h = tid; h < n_half; h += 256) {
+      const uint4* src = reinterpret_cast<const uint4*>(my_key + size_t(h) * kph);
+      uint32_t mx      = 0;
+      for (uint32_t i = 0; i < kph / 4; i++) {
+        const uint4 v = __ldg(src + i);
+        mx            = max(max(mx, v.x), max(v.y, max(v.z, v.w)));
+      }
+      key[h] = mx;
+    }
+  } else {
+    const uint4* src = reinterpret_cast<const uint4*>(my_key);
     uint4* dst       = reinterpret_cast<uint4*>(key);
     for (uint32_t i = tid; i < n_cand / 4; i += 256) { dst[i] = __ldg(src + i); }
   }
@@ -644,7 +663,7 @@ coarse_finish_kernel(const uint32_t* __restrict__ cand_key, const uint32_t* __re
     __syncthreads();
     const uint32_t prefix = s_prefix;
     const uint32_t mask   = pass == 0 ? 0u : (0xFFFFFFFFu << (shift + 8));
-    for (uint32_t i = tid; i < n_cand; i += 256) {
+    for (uint32_t i = tid; i < n_sel_from; i += 256) {
       const uint32_t kk = key[i];
       if (!key_valid(kk)) { continue; }
       const uint32_t o = ~kk;
@@ -667,23 +686,37 @@ coarse_finish_kernel(const uint32_t* __restrict__ cand_key, const uint32_t* __re
     }
     __syncthreads();
   }
-  const uint32_t T = s_prefix;  // complement of the C-th largest key
+  const uint32_t T = s_prefix;  // complement of the C-th largest key (half-tile maximum)
   if (tid == 0) { s_count = 0; }
   for (uint32_t i = tid; i < cap; i += 256) { s_keys[i] = kEmptyKey; }
   __syncthreads();
   // gather everything at least as good as the threshold; then the bound on what the half tiles dropped
   uint32_t tb = 0;
-  for (uint32_t i = tid; i < n_cand; i += 256) {
-    const uint32_t kk = key[i];
-    if (!key_valid(kk)) { continue; }
-    if (~kk <= T) {
-      const uint32_t slot = atomicAdd(&s_count, 1u);
-      // list id = tile * 256 + half * 128 + column; i / kph enumerates (tile, half)
-      if (slot < cap) { s_keys[slot] = (i / kph) * kHalf + (127u - (kk & 127u)); }
+  if (by_maxima) {
+    for (uint32_t h = tid; h < n_half; h += 256) {
+      const uint32_t mx = key[h];
+      if (!key_valid(mx) || ~mx > T) { continue; }
+      for (uint32_t i = 0; i < kph; i++) {
+        const uint32_t kk = __ldg(my_key + size_t(h) * kph + i);
+        if (key_valid(kk) && ~kk <= T) {
+          const uint32_t slot = atomicAdd(&s_count, 1u);
+          // list id = tile * 256 + half * 128 + column; h enumerates (tile, half)
+          if (slot < cap) { s_keys[slot] = h * kHalf + (127u - (kk & 127u)); }
+        }
+      }
+    }
+  } else {
+    for (uint32_t i = tid; i < n_cand; i += 256) {
+      const uint32_t kk = key[i];
+      if (!key_valid(kk)) { continue; }
+      if (~kk <= T) {
+        const uint32_t slot = atomicAdd(&s_count, 1u);
+        if (slot < cap) { s_keys[slot] = (i / kph) * kHalf + (127u - (kk & 127u)); }
+      }
     }
   }
   {
-    const uint32_t n_bnd = 2 * (n_cand / kph);  // one bound per 64-column unit
+    const uint32_t n_bnd = 2 * n_half;  // one bound per 64-column unit
     const uint32_t* bnd  = cand_bound + size_t(q) * n_bnd;
     for (uint32_t i = tid; i < n_bnd; i += 256) { tb = max(tb, bnd[i]); }
   }
@@ -1441,7 +1474,8 @@ void select_clusters_tc(raft::resources& res, const float* centers, const float*
 
   uint32_t cap     = 2;
   while (cap < 2 * C) { cap <<= 1; }  // room for ties at the selection threshold
-  const size_t fin_smem = size_t(cap) * 8 + size_t(dim_ext) * 4 + size_t(n_cand) * 4;
+  const bool by_maxima  = C * 4 <= n_tiles * 2;  // C small against the number of half tiles
+  const size_t fin_smem = size_t(cap) * 8 + size_t(dim_ext) * 4 + size_t(by_maxima ? n_cand / kph : n_cand) * 4;
   // the half-tile-maxima threshold is tight only when C is small against the number of half tiles
   // rows rescored per round: all 64 a query can select if they fit 48 KB of shared memory, else fewer
   uint32_t fin_rows = kFinRows;
@@ -1462,7 +1496,7 @@ void select_clusters_tc(raft::resources& res, const float* centers, const float*
     coarse_finish_kernel<<<n_queries, 256, fin_smem, stream>>>(cand_key, cand_bnd, n_cand, kph, centers, fq,
                                                                n_lists, dim_ext, alpha, n_probes, C, cap,
                                                                cmax, eps_rel, probes, scores_out, redo_list,
-                                                               words + 2, words, ext_col, ext_scale, row_scale, down_thr);
+                                                               words + 2, words, ext_col, ext_scale, row_scale, down_thr, by_maxima ? 1 : 0);
   }
   uint32_t cap_fb = 2;
   while (cap_fb < n_probes) { cap_fb <<= 1; }

@@ -313,7 +313,7 @@ def many_lists(ivf):
     return x, g
 
 
-@pytest.mark.parametrize("nq,n_probes", [(1, 1), (7, 20), (128, 32), (300, 40), (1000, 20)])
+@pytest.mark.parametrize("nq,n_probes", [(1, 1), (7, 20), (128, 32), (300, 40), (1000, 20), (500, 64)])
 def test_coarse_tensor_core_path_equals_exact_path(ivf, oracle_mod, many_lists, tmp_path, nq, n_probes):
     x, g = many_lists
     q = make_mixture(nq, 64, 512, 0.25, seed=71 + nq)
@@ -332,6 +332,21 @@ def test_coarse_tensor_core_path_equals_exact_path(ivf, oracle_mod, many_lists, 
     po, so = oracle_mod.select_clusters(ix, fq, n_probes)
     assert (po == p1).all()
     assert (so.view(np.uint32) == s1.view(np.uint32)).all()
+
+
+def test_coarse_tensor_core_path_with_more_than_512_half_tiles(ivf):
+    """70,000 lists: the finish kernel that takes its threshold from the half-tile maxima and re-reads
+    only the qualifying half tiles' keys; probes and scores equal the exact path's."""
+    x = make_mixture(140000, 32, 4096, 0.3, seed=90)
+    g = ivf.build(ivf.IndexParams(n_lists=70000, pq_dim=16, kmeans_n_iters=2,
+                                  kmeans_trainset_fraction=1.0), torch.from_numpy(x).cuda())
+    q = make_mixture(600, 32, 4096, 0.3, seed=91)
+    for n_probes in (20, 100):
+        p1, s1, _ = coarse_select(g, q, n_probes, 1)
+        p2, s2, st = coarse_select(g, q, n_probes, 2)
+        assert st[0] == 0
+        assert (p1 == p2).all() and (s1.view(np.uint32) == s2.view(np.uint32)).all()
+        assert st[1] <= len(q) // 20
 
 
 def test_search_is_identical_under_both_coarse_paths(ivf, many_lists):
