@@ -407,10 +407,11 @@ def hbm_peak():
 
 
 # DRAM bytes (read + write) per DISTINCT 32-row group scanned in a launch, from the ncu capture of the
-# scan kernel on a 4 M-row case of this workload (246.8 MB over 135,125 distinct groups of
-# 3 x 512 B; summary under profiles/).  Traffic grows with the distinct groups of a launch, so the
-# full-size figure is this constant times the launch's distinct groups.
-DRAM_BYTES_PER_UNIQUE_GROUP = 1826.0
+# scan kernel on a 4 M-row case of this workload (354.9 MB over 135,125 distinct groups of
+# 3 x 512 B: the work list makes two passes over the lists, so a list can be fetched twice).  Traffic
+# grows with the distinct groups of a launch, so the full-size figure is this constant times the
+# launch's distinct groups.
+DRAM_BYTES_PER_UNIQUE_GROUP = 2626.0
 
 
 def workload_from_args(args):
@@ -732,32 +733,34 @@ def run_ours(args):
 
     # ---- end to end: pinned host buffers, copies inside the timed region ----
     # Every step copies its queries host -> device and its results device -> host.  The copies run on
-    # their own streams with two sets of buffers, so that step s+1's input copy and step s-1's
-    # result copy overlap step s's search (a serving loop's usual double buffering); the timed
-    # region ends only when the last result has reached the host.
+    # their own streams with four sets of buffers (two batches are in flight, so two sets would make
+    # an input copy wait for the search two steps back to finish): step s+1's and s+2's input copies
+    # and step s-1's result copy overlap step s's search (a serving loop's usual multi-buffering); the
+    # timed region ends only when the last result has reached the host.
+    n_slots = 4
     q_host = queries.cpu().pin_memory()
-    q_dev = [torch.empty_like(queries) for _ in range(2)]
+    q_dev = [torch.empty_like(queries) for _ in range(n_slots)]
     o_dev = [(torch.empty((nq, k), dtype=torch.int64, device=device),
-              torch.empty((nq, k), dtype=torch.float32, device=device)) for _ in range(2)]
-    i_host = [torch.empty((nq, k), dtype=torch.int64).pin_memory() for _ in range(2)]
-    d_host = [torch.empty((nq, k), dtype=torch.float32).pin_memory() for _ in range(2)]
+              torch.empty((nq, k), dtype=torch.float32, device=device)) for _ in range(n_slots)]
+    i_host = [torch.empty((nq, k), dtype=torch.int64).pin_memory() for _ in range(n_slots)]
+    d_host = [torch.empty((nq, k), dtype=torch.float32).pin_memory() for _ in range(n_slots)]
     s_in, s_out = torch.cuda.Stream(device), torch.cuda.Stream(device)
-    ev_in = [torch.cuda.Event() for _ in range(2)]
-    ev_done = [torch.cuda.Event() for _ in range(2)]
-    ev_out = [torch.cuda.Event() for _ in range(2)]
+    ev_in = [torch.cuda.Event() for _ in range(n_slots)]
+    ev_done = [torch.cuda.Event() for _ in range(n_slots)]
+    ev_out = [torch.cuda.Event() for _ in range(n_slots)]
     e2e_state = {"step": 0}
 
     def e2e_step():
         s = e2e_state["step"]
-        slot = s & 1
+        slot = s % n_slots
         with torch.cuda.stream(s_in):
-            if s >= 2:
-                s_in.wait_event(ev_done[slot])       # the search two steps back has read this buffer
+            if s >= n_slots:
+                s_in.wait_event(ev_done[slot])       # the search n_slots steps back has read this buffer
             q_dev[slot].copy_(q_host, non_blocking=True)
             ev_in[slot].record(s_in)
         # the search runs on its lane's stream, behind this step's input copy and the result copy that
         # last used the output buffer
-        lane = lane_search(q_dev[slot], o_dev[slot], [ev_in[slot]] + ([ev_out[slot]] if s >= 2 else []))
+        lane = lane_search(q_dev[slot], o_dev[slot], [ev_in[slot]] + ([ev_out[slot]] if s >= n_slots else []))
         ev_done[slot].record(lane["stream"])
         with torch.cuda.stream(s_out):
             s_out.wait_event(ev_done[slot])
@@ -776,7 +779,7 @@ def run_ours(args):
         ms_e2e, e2e_rec = float("nan"), float("nan")
     else:
         ms_e2e, _ = timed(e2e_step, args.steps, args.warmup, tail=e2e_tail)
-        last = (e2e_state["step"] - 1) & 1
+        last = (e2e_state["step"] - 1) % n_slots
         e2e_rec = recall_at_k(i_host[last].to(device), truth)
     clocks = sampler.stop() if rank == 0 else None
 
@@ -818,7 +821,7 @@ def run_ours(args):
         "e2e": {"value": round(nq / ms_e2e * 1e3, 1), "unit": "queries/s",
                 "h2d_bytes_per_step": int(q_host.numel() * q_host.element_size()),
                 "d2h_bytes_per_step": int(nq * k * 12), "ms_per_step": round(ms_e2e, 4),
-                "copies": "every step, double-buffered on side streams (overlap the neighbouring steps)",
+                "copies": "every step, on side streams with four sets of buffers (overlap the neighbouring steps)",
                 rkey: round(e2e_rec, 4)},
         "gpu_launches": gpu_launches,
         "clocks": clocks,
