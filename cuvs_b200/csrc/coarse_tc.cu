@@ -1344,8 +1344,8 @@ void prepare_tc_centers(cudaStream_t stream, const float* centers, uint32_t n_li
   *ext_scale = 1.0f;
   const size_t n = size_t(n_lists) * dim_ext;
   if (n == 0) { return; }
-  uint32_t* d_bits = nullptr;
-  CUDA_TRY(cudaMalloc(&d_bits, 8));
+  dev_array<uint32_t> bits_buf(2);
+  uint32_t* d_bits = bits_buf.data();
   CUDA_TRY(cudaMemsetAsync(d_bits, 0, 8, stream));
   const unsigned blocks = ceildiv<uint32_t>(n_lists * 32u, 256u);
   uint32_t bits[2]      = {0, 0};
@@ -1369,7 +1369,6 @@ void prepare_tc_centers(cudaStream_t stream, const float* centers, uint32_t n_li
   CUDA_TRY(cudaGetLastError());
   CUDA_TRY(cudaMemcpyAsync(bits + 1, d_bits + 1, 4, cudaMemcpyDeviceToHost, stream));
   CUDA_TRY(cudaStreamSynchronize(stream));
-  CUDA_TRY(cudaFree(d_bits));
   float ss;
   std::memcpy(&ss, &bits[1], 4);
   // the lanes sum in another order than a sequential loop: a margin on the bound
