@@ -117,6 +117,27 @@ def test_extend_and_ids(ivf, oracle_mod):
         ivf.extend(g, xd[:10], None)
 
 
+def test_lists_are_balanced_on_skewed_data(ivf):
+    """Balanced k-means (the reference's adjust_centers step, cpp/src/cluster/detail/kmeans_balanced.cuh:616-720):
+    on a mixture whose components differ 50-fold in weight, no list ends far above the mean size and few
+    end far below it.  Plain Lloyd leaves the heavy components in a few huge lists."""
+    import torch
+    rng = np.random.default_rng(5)
+    n, dim, n_comp, n_lists = 200_000, 32, 48, 1024
+    cent = rng.uniform(-1.0, 1.0, size=(n_comp, dim)).astype(np.float32)
+    w = np.geomspace(1.0, 50.0, n_comp)
+    comp = rng.choice(n_comp, size=n, p=w / w.sum())
+    x = (cent[comp] + 0.2 * rng.standard_normal((n, dim))).astype(np.float32)
+    g = ivf.build(ivf.IndexParams(n_lists=n_lists, pq_dim=16, kmeans_n_iters=12, kmeans_trainset_fraction=0.5),
+                  torch.from_numpy(x).cuda())
+    sizes = g.list_sizes.to(torch.int64).cpu().numpy()
+    assert sizes.sum() == n
+    mean = n / n_lists
+    print(f"list sizes: max {sizes.max() / mean:.2f} x mean, {np.mean(sizes < mean / 4):.3f} below a quarter of it")
+    assert sizes.max() <= 4.0 * mean
+    assert np.mean(sizes < mean / 4) <= 0.05
+
+
 def test_transform_equals_stored_codes(ivf):
     """python/cuvs/cuvs/tests/test_ivf_pq.py test_transform: codes of `transform` equal what build stored."""
     x = make_mixture(4000, 32, 32, 0.15, seed=50)
