@@ -64,6 +64,7 @@ struct scan_params {
   // shared memory plan
   uint32_t n_groups, group_threads;
   uint32_t pqc_in_smem, smem_pqc_bytes, smem_group_bytes, lut_bytes, base_bytes, merge_bytes;
+  uint32_t base_double;  // base_bytes holds two base-difference buffers
   // codebook in tensor memory: columns allocated (0 = not used), byte offset in shared memory of
   // the word that receives the allocation's address
   uint32_t tmem_cols, tmem_slot_off;
@@ -711,7 +712,9 @@ __global__ void __launch_bounds__(1024, 1) scan_kernel(const scan_params p)
   const uint32_t lut_a   = smem_addr(smem) + goff;
   // (recomputed from the parameters where used, so that none of them occupies a register for the
   // life of the kernel)
-  const auto s_base_a = [&] { return lut_a + p.lut_bytes; };
+  // (two base-difference buffers when the plan has room: the warps that idle during the merge of a
+  // pair prepare the next pair's vector in the other one)
+  const auto s_base_a = [&](uint32_t buf) { return lut_a + p.lut_bytes + (p.base_double ? buf * (p.base_bytes >> 1) : 0u); };
   const auto s_item_a = [&] { return lut_a + p.lut_bytes + p.base_bytes + p.merge_bytes; };
   const auto s_thr_a  = [&] { return s_item_a() + 8u; };
 
@@ -767,6 +770,25 @@ __global__ void __launch_bounds__(1024, 1) scan_kernel(const scan_params p)
   const uint32_t n_work = __ldg(p.n_work);
   constexpr uint32_t claim = 1u;
   if (gt == 0) { sts_b32(s_item_a(), atomicAdd(p.work_counter, claim)); }
+  // the base difference of one (query, list): stored pre-duplicated for the packed arithmetic, L2 (d, d),
+  // inner product (-q, -q, q*c, q*c); written by threads first, first + step, ...
+  const auto write_base = [&](uint32_t base_a, uint32_t q_, uint32_t label_, uint32_t first, uint32_t step) {
+    const float* rq = p.rot_q + size_t(q_) * rot_dim;
+    const float* c  = p.centers_rot + size_t(label_) * rot_dim;
+    for (uint32_t i = first; i < rot_dim; i += step) {
+      if constexpr (!IsIP) {
+        const float d = __fsub_rn(rq[i], __ldg(c + i));
+        sts_b64(base_a + 8u * i, pack2(d, d));
+      } else {
+        const float qv = rq[i];
+        const float y  = __fmul_rn(__ldg(c + i), qv);
+        sts_b128(base_a + 16u * i, pack2(-qv, -qv), pack2(y, y));
+      }
+    }
+  };
+  const bool prefetch_base = p.base_double != 0 && n_gwarps > 1 && !kStoreAll;
+  uint32_t cur   = 0;      // buffer that holds (or receives) the current pair's base difference
+  bool have_base = false;  // the current pair's base difference and bound were prepared during the last merge
   for (uint32_t it = 0;; it++) {
     group_bar(bar_id, gthreads);
     const uint32_t w = lds_b32_volatile(s_item_a() + 4u * ((it / claim) & 1u)) + (it % claim);
@@ -789,27 +811,16 @@ __global__ void __launch_bounds__(1024, 1) scan_kernel(const scan_params p)
       if constexpr (!kStoreAll) {
         for (uint32_t i = gt; i < k; i += gthreads) { out[i] = kEmptyKey; }
       }
+      have_base = false;
       continue;
     }
 
-    // ---- base diff ----
-    if (gt == 0) { sts_b32(s_thr_a(), *reinterpret_cast<volatile uint32_t*>(p.query_kth + q)); }
-    {
-      const float* rq = p.rot_q + size_t(q) * rot_dim;
-      const float* c  = p.centers_rot + size_t(label) * rot_dim;
-      // stored pre-duplicated for the packed arithmetic: L2 (d, d); inner product (-q, -q, q*c, q*c)
-      for (uint32_t i = gt; i < rot_dim; i += gthreads) {
-        if constexpr (!IsIP) {
-          const float d = __fsub_rn(rq[i], __ldg(c + i));
-          sts_b64(s_base_a() + 8u * i, pack2(d, d));
-        } else {
-          const float qv = rq[i];
-          const float y  = __fmul_rn(__ldg(c + i), qv);
-          sts_b128(s_base_a() + 16u * i, pack2(-qv, -qv), pack2(y, y));
-        }
-      }
+    // ---- base diff (unless the idle warps of the last merge prepared it) ----
+    if (!have_base) {
+      if (gt == 0) { sts_b32(s_thr_a(), *reinterpret_cast<volatile uint32_t*>(p.query_kth + q)); }
+      write_base(s_base_a(cur), q, label, uint32_t(gt), uint32_t(gthreads));
+      group_bar(bar_id, gthreads);
     }
-    group_bar(bar_id, gthreads);
 
     // The first 16-byte piece of this warp's first group is brought to L2 now, behind the LUT build
     // (a load into registers here would hold four of them through the build); afterwards each piece
@@ -822,16 +833,16 @@ __global__ void __launch_bounds__(1024, 1) scan_kernel(const scan_params p)
 
     // ---- LUT ----
     if constexpr (kFixed) {
-      build_lut_tmem<PqBits, LutKind, IsIP, LEN, PQD, GT>(tmem_lane_a, s_base_a(), lut_a, pq_dim, gt, gthreads);
+      build_lut_tmem<PqBits, LutKind, IsIP, LEN, PQD, GT>(tmem_lane_a, s_base_a(cur), lut_a, pq_dim, gt, gthreads);
     } else if (p.tmem_cols) {
-      const uint32_t base_a = s_base_a();
+      const uint32_t base_a = s_base_a(cur);
       switch (len) {
         case 1: build_lut_tmem<PqBits, LutKind, IsIP, 1>(tmem_lane_a, base_a, lut_a, p.pq_dim, gt, gthreads); break;
         case 2: build_lut_tmem<PqBits, LutKind, IsIP, 2>(tmem_lane_a, base_a, lut_a, p.pq_dim, gt, gthreads); break;
         default: build_lut_tmem<PqBits, LutKind, IsIP, 4>(tmem_lane_a, base_a, lut_a, p.pq_dim, gt, gthreads); break;
       }
     } else if (p.pqc_in_smem) {
-      const uint32_t pqc_a = smem_addr(s_pqc), base_a = s_base_a();
+      const uint32_t pqc_a = smem_addr(s_pqc), base_a = s_base_a(cur);
       switch (len) {
         case 1: build_lut_smem<PqBits, LutKind, IsIP, 1>(pqc_a, base_a, lut_a, p.pq_dim, len, gt, gthreads); break;
         case 2: build_lut_smem<PqBits, LutKind, IsIP, 2>(pqc_a, base_a, lut_a, p.pq_dim, len, gt, gthreads); break;
@@ -843,7 +854,8 @@ __global__ void __launch_bounds__(1024, 1) scan_kernel(const scan_params p)
       // shared memory): same arithmetic, generic addressing
       constexpr uint32_t kPairs = kBook / 2;
       lut_t* s_lut        = reinterpret_cast<lut_t*>(smem + goff);
-      const float* s_base = reinterpret_cast<const float*>(smem + goff + p.lut_bytes);
+      const float* s_base = reinterpret_cast<const float*>(smem + goff + p.lut_bytes +
+                                                          (p.base_double ? cur * (p.base_bytes >> 1) : 0u));
       const float* pqc = p.per_cluster ? p.pq_centers + size_t(label) * len * kBook : p.pq_centers;
       const uint32_t b        = (uint32_t(gt) % kPairs) * 2u;
       const uint32_t j_first  = uint32_t(gt) / kPairs;
@@ -978,6 +990,22 @@ __global__ void __launch_bounds__(1024, 1) scan_kernel(const scan_params p)
     uint64_t* s_merge = reinterpret_cast<uint64_t*>(smem + goff + p.lut_bytes + p.base_bytes);
     queue.store(s_merge + size_t(gw) * k, int(k));
     group_bar(bar_id, gthreads);
+    // While warp 0 merges, the other warps prepare the next pair: its base difference into the other
+    // buffer and the query's bound (every warp has finished scanning, so the bound's slot is free).  The
+    // next work item was claimed after the barrier at the top of this iteration.
+    have_base = false;
+    if (prefetch_base) {
+      const uint32_t w_next = lds_b32_volatile(s_item_a() + 4u * ((it + 1u) & 1u));
+      if (w_next < n_work) {
+        have_base = true;
+        cur ^= 1u;
+        if (gw != 0) {
+          const uint4 nd = __ldg(p.work + 2 * size_t(w_next));
+          if (gt == 32) { sts_b32(s_thr_a(), *reinterpret_cast<volatile uint32_t*>(p.query_kth + nd.y)); }
+          write_base(s_base_a(cur), nd.y, nd.z, uint32_t(gt) - 32u, uint32_t(gthreads) - 32u);
+        }
+      }
+    }
     if (gw == 0) {
       const uint32_t others = uint32_t(n_gwarps - 1) * k;
       for (uint32_t t0 = 0; t0 < others; t0 += 32) {

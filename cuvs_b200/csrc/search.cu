@@ -627,8 +627,12 @@ scan_plan plan_scan(const raft::resources& res, const index<int64_t>& idx, int l
     if (home == 1 && pqc_bytes == 0) { continue; }
     for (int g = (home == 2 ? 8 : 4); g >= 1; g >>= 1) {
       const size_t merge_bytes = round_up<size_t>(size_t(1024 / g / 32) * k * 8, 16);
-      const size_t group_bytes = lut_bytes + base_bytes + merge_bytes + 16;
-      const size_t total       = (home == 1 ? pqc_bytes : 0) + size_t(g) * group_bytes + 16;
+      const size_t fixed_part  = (home == 1 ? pqc_bytes : 0) + 16;
+      // a second base-difference buffer per group where it fits (the next pair's vector is prepared
+      // while the current pair's queues are merged)
+      const bool base_double   = fixed_part + size_t(g) * (lut_bytes + 2 * base_bytes + merge_bytes + 16) <= limit;
+      const size_t group_bytes = lut_bytes + (base_double ? 2 : 1) * base_bytes + merge_bytes + 16;
+      const size_t total       = fixed_part + size_t(g) * group_bytes;
       if (total <= limit) {
         plan.n_groups      = g;
         plan.group_threads = 1024 / g;
@@ -636,7 +640,8 @@ scan_plan plan_scan(const raft::resources& res, const index<int64_t>& idx, int l
         plan.pqc_bytes     = home == 1 ? uint32_t(pqc_bytes) : 0;
         plan.group_bytes   = uint32_t(group_bytes);
         plan.lut_bytes     = uint32_t(lut_bytes);
-        plan.base_bytes    = uint32_t(base_bytes);
+        plan.base_bytes    = uint32_t((base_double ? 2 : 1) * base_bytes);
+        plan.base_double   = base_double ? 1 : 0;
         plan.merge_bytes   = uint32_t(merge_bytes);
         plan.total_bytes   = total;
         plan.tmem_slot_off = uint32_t(total - 16);
@@ -924,6 +929,7 @@ void search_any(raft::resources& res, const search_params& params, const index<i
       sp.smem_group_bytes = plan.group_bytes;
       sp.lut_bytes      = plan.lut_bytes;
       sp.base_bytes     = plan.base_bytes;
+      sp.base_double    = plan.base_double;
       sp.merge_bytes    = plan.merge_bytes;
       sp.allow_fixed_shape = scan_codebook_home() != 2;
       if (plan.lut_global) {

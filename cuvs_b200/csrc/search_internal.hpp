@@ -7,7 +7,7 @@ namespace cuvs::neighbors::ivf_pq {
 
 struct scan_plan {
   uint32_t n_groups, group_threads, pqc_in_smem, pqc_bytes, group_bytes, lut_bytes, base_bytes,
-    merge_bytes, tmem_cols, tmem_slot_off, lut_global;
+    merge_bytes, tmem_cols, tmem_slot_off, lut_global, base_double;
   size_t total_bytes;
 };
 scan_plan plan_scan(const raft::resources& res, const index<int64_t>& idx, int lut_kind, bool is_ip,
