@@ -411,7 +411,10 @@ __device__ __forceinline__ void fill_codebook_tmem(uint32_t tmem_lane_a, const f
 // miss L1 (the shared-memory carve-out leaves it almost no room): 1.57 ms against 1.50 ms per launch
 // on the 10 M-row workload.
 constexpr int kTmemLoadCols = 8;
-template <int PqBits, int LutKind, bool IsIP, int LEN, int PQD = 0, int GT = 0>
+// I0 / I1 (uniform compile-time shapes only): build the thread's subspaces number I0 .. I1 - 1 of its
+// PQD / (GT / units per subspace); I1 < 0 = all.  Subspaces are dealt to threads round robin, so a
+// range of iterations is a range of subspaces: the table can be built a code piece at a time.
+template <int PqBits, int LutKind, bool IsIP, int LEN, int PQD = 0, int GT = 0, int I0 = 0, int I1 = -1>
 __device__ __forceinline__ void build_lut_tmem(uint32_t tmem_lane_a, uint32_t base_a, uint32_t lut_a,
                                                uint32_t pq_dim_rt, uint32_t gt, uint32_t gthreads_rt)
 {
@@ -495,8 +498,14 @@ __device__ __forceinline__ void build_lut_tmem(uint32_t tmem_lane_a, uint32_t ba
   if constexpr (kUniform) {
     constexpr uint32_t kIters = uint32_t(PQD) / (uint32_t(GT) / kUPJ);
     static_assert(kIters % kPerLoad == 0, "whole tensor-memory loads only");
+    constexpr uint32_t kBegin = uint32_t(I0);
+    constexpr uint32_t kEnd   = I1 < 0 ? kIters : uint32_t(I1);
+    static_assert(kBegin % kPerLoad == 0 && kEnd % kPerLoad == 0 && kEnd <= kIters, "whole loads only");
+    j += kBegin * j_stride;
+    bd += kBegin * bd_step;
+    out += kBegin * out_step;
 #pragma unroll
-    for (uint32_t i = 0; i < kIters; i += kPerLoad) {
+    for (uint32_t i = kBegin; i < kEnd; i += kPerLoad) {
       uint32_t c[kLoad];
       tmem_ld<kLoad>(taddr + i / kPerLoad * uint32_t(kLoad), c);
       tmem_wait_ld();
@@ -796,6 +805,7 @@ __global__ void __launch_bounds__(1024, 1) scan_kernel(const scan_params p)
     if (gt == 0 && (it % claim) == 0) {
       sts_b32(s_item_a() + 4u * (((it / claim) + 1u) & 1u), atomicAdd(p.work_counter, claim));
     }
+    if (gt == 0) { sts_b32(s_item_a() + 12u, 0u); }  // "some lane survived the first piece" (lazy table build)
 
     const uint4 d0       = __ldg(p.work + 2 * size_t(w));
     const uint4 d1       = __ldg(p.work + 2 * size_t(w) + 1);
@@ -831,6 +841,99 @@ __global__ void __launch_bounds__(1024, 1) scan_kernel(const scan_params p)
     uint4 nxt = make_uint4(0u, 0u, 0u, 0u);
     if (uint32_t(gw) < n_groups) { asm volatile("prefetch.global.L2 [%0];" ::"l"(src)); }
 
+    // ---- short lists of the compile-time L2 shapes: the table is built a piece at a time ----
+    // Rows of the first code piece are built and every vector of the list is scored on that piece
+    // alone (partial sums stay in registers, up to kLazyRows groups of 32 rows per warp).  If by then
+    // every lane of the group has passed the query's bound -- four pairs in ten on the 96-d benchmark
+    // shape -- the other two thirds of the table are never built and nothing is offered to the queues;
+    // otherwise the rest is built and the survivors go on.  Same sums in the same order.
+    constexpr int kLazyRows = 4;
+    constexpr bool kLazyShape = []() {
+      // (k <= 32 only: with more keys per lane the extra code costs the long-list kernels 2%)
+      if constexpr (kFixed && !IsIP && KPL == 1) {
+        constexpr uint32_t js = uint32_t(GT) / (kBook / 4u);  // subspaces built per iteration of a thread
+        return js > 0 && uint32_t(PQD) > uint32_t(kPerPiece) && uint32_t(PQD) % js == 0 &&
+               uint32_t(kPerPiece) % js == 0;
+      } else {
+        return false;
+      }
+    }();
+    bool lazy = false;
+    if constexpr (kLazyShape) {
+      lazy = n_groups <= uint32_t(kLazyRows * n_gwarps) && p.filter_bits == nullptr;
+      if (lazy) {
+        constexpr uint32_t kIt0    = uint32_t(kPerPiece) / (uint32_t(GT) / (kBook / 4u));
+        constexpr uint32_t kPieces = uint32_t((PQD + kPerPiece - 1) / kPerPiece);
+        constexpr uint32_t kLast   = uint32_t(PQD) - (kPieces - 1u) * uint32_t(kPerPiece);
+        constexpr uint32_t kPieceLutBytes = uint32_t(kPerPiece) * kBook * uint32_t(sizeof(lut_t));
+        constexpr int kHalfPiece   = kPerPiece / 2;
+        const uint32_t group_stride = uint32_t(n_gwarps) * n_pieces * 32u;  // in 16-byte pieces
+        build_lut_tmem<PqBits, LutKind, IsIP, LEN, PQD, GT, 0, int(kIt0)>(tmem_lane_a, s_base_a(cur), lut_a, pq_dim,
+                                                                          gt, gthreads);
+        uint4 v0[kLazyRows];
+#pragma unroll
+        for (int r = 0; r < kLazyRows; r++) {
+          v0[r] = make_uint4(0u, 0u, 0u, 0u);
+          if (uint32_t(gw + r * n_gwarps) < n_groups) { v0[r] = __ldg(src + size_t(r) * group_stride); }
+        }
+        group_bar(bar_id, gthreads);
+        queue.init(int(k));
+        const float stop_at = ordered_to_float(lds_b32_volatile(s_thr_a()));  // NaN = no bound yet
+        accum<LutKind, OutHalf, IsIP> acc[kLazyRows];
+        bool alv[kLazyRows];
+        bool any = false;
+#pragma unroll
+        for (int r = 0; r < kLazyRows; r++) {
+          acc[r].init();
+          alv[r] = uint32_t(gw + r * n_gwarps) < n_groups;
+          if (alv[r]) { score_part<PqBits, LutKind, OutHalf, IsIP, true, 0, kHalfPiece>(acc[r], v0[r], lut_a, 0); }
+          alv[r] = alv[r] && !(acc[r].partial() > stop_at);
+          if (alv[r]) { score_part<PqBits, LutKind, OutHalf, IsIP, true, kHalfPiece, kPerPiece>(acc[r], v0[r], lut_a, 0); }
+          alv[r] = alv[r] && !(acc[r].partial() > stop_at);
+          any    = any || alv[r];
+        }
+        if (__any_sync(kFullMask, any) && lane == 0) { sts_b32(s_item_a() + 12u, 1u); }
+        group_bar(bar_id, gthreads);
+        if (lds_b32_volatile(s_item_a() + 12u) != 0u) {
+          build_lut_tmem<PqBits, LutKind, IsIP, LEN, PQD, GT, int(kIt0), -1>(tmem_lane_a, s_base_a(cur), lut_a, pq_dim,
+                                                                             gt, gthreads);
+          group_bar(bar_id, gthreads);
+#pragma unroll
+          for (int r = 0; r < kLazyRows; r++) {
+            const uint32_t gi = uint32_t(gw + r * n_gwarps);
+            if (gi >= n_groups) { continue; }
+            if (__any_sync(kFullMask, alv[r])) {
+#pragma unroll
+              for (uint32_t c = 1; c < kPieces; c++) {
+                const uint4 v     = __ldg(src + size_t(r) * group_stride + c * 32u);
+                const uint32_t la = lut_a + c * kPieceLutBytes;
+                if (c + 1 < kPieces || kLast == uint32_t(kPerPiece)) {
+                  if (alv[r]) { score_part<PqBits, LutKind, OutHalf, IsIP, true, 0, kHalfPiece>(acc[r], v, la, 0); }
+                  alv[r] = alv[r] && !(acc[r].partial() > stop_at);
+                  if (alv[r]) { score_part<PqBits, LutKind, OutHalf, IsIP, true, kHalfPiece, kPerPiece>(acc[r], v, la, 0); }
+                } else {
+                  if (alv[r]) { score_part<PqBits, LutKind, OutHalf, IsIP, false, 0, kHalfPiece>(acc[r], v, la, kLast); }
+                  alv[r] = alv[r] && !(acc[r].partial() > stop_at);
+                  if (alv[r]) { score_part<PqBits, LutKind, OutHalf, IsIP, false, kHalfPiece, kPerPiece>(acc[r], v, la, kLast); }
+                }
+                if (c + 1 < kPieces) { alv[r] = alv[r] && !(acc[r].partial() > stop_at); }
+              }
+            }
+            // a lane that stopped early holds a partial sum above the bound: rejected below like any other
+            const float score  = acc[r].result(p.cosine != 0);
+            const uint32_t row = gi * 32u + lane;
+            const uint32_t ord = float_to_ordered(score);
+            const uint64_t key = (uint64_t(ord) << 32) | (sample_offset + row);
+            const uint32_t thr = lds_b32_volatile(s_thr_a());
+            const uint64_t before = queue.kth();
+            queue.offer(key, row < n && alv[r] && ord <= thr);
+            if (queue.kth() != before && lane == 0) { atoms_min_u32(s_thr_a(), uint32_t(queue.kth() >> 32)); }
+          }
+        }
+      }
+    }
+
+    if (!lazy) {
     // ---- LUT ----
     if constexpr (kFixed) {
       build_lut_tmem<PqBits, LutKind, IsIP, LEN, PQD, GT>(tmem_lane_a, s_base_a(cur), lut_a, pq_dim, gt, gthreads);
@@ -984,6 +1087,8 @@ __global__ void __launch_bounds__(1024, 1) scan_kernel(const scan_params p)
         }
       }
     }
+
+    }  // !lazy
 
     if constexpr (!kStoreAll) {
     // ---- merge the warps' queues, write k keys ----
