@@ -658,12 +658,12 @@ def run_ours(args):
         stage["refine_ms"] = round(t, 4)
         ms_ann_only, _ = timed(lambda: ann_search(sp, queries, res, comm, cand_i, cand_d), args.steps, 2)
 
-    # Throughput mode: two batches in flight per GPU, each on its own stream, resources handle and (with
+    # Throughput mode: three batches in flight per GPU (--in-flight), each on its own stream, resources handle and (with
     # several GPUs) communicator -- the serving pattern of the reference's benchmark in throughput
     # mode: several host threads, one stream each -- so that the small kernels and the exchanges of one
     # batch fill the tails of the other's large kernels.  The per-kernel figures above (stage times,
     # roofline, launches) come from the single-stream pass.
-    n_streams = 2
+    n_streams = max(1, args.in_flight)
     lanes = []
     for _ in range(n_streams):
         r = Resources()
@@ -944,6 +944,8 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--in-flight", type=int, default=3, dest="in_flight",
+                    help="batches in flight per GPU in the throughput passes (streams / resources handles)")
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--rows", type=int, default=0, help="shrink the dataset (testing only)")
