@@ -24,7 +24,10 @@
 // per warp) and keeps a sorted top-k across its lanes; a per-query bound shared through global
 // memory lets later probes discard almost every candidate with one compare, and for L2 metrics a
 // lane whose partial sum already exceeds that bound stops its look-ups (checked twice per piece;
-// the sum only grows, so no kept candidate is lost).  The benchmark shapes (pq_dim, groups, pq_len)
+// the sum only grows, so no kept candidate is lost).  While warp 0 merges a pair's queues the other
+// warps prepare the next pair's base difference; for short lists of the compile-time L2 shapes the
+// table is built a code piece at a time and its remainder skipped when no lane survives the first
+// piece.  The benchmark shapes (pq_dim, groups, pq_len)
 // are instantiated with compile-time trip counts (scan_inst.cu); every other shape runs the
 // run-time loops.  scan_glut_kernel is the variant whose table lives in global memory, for tables
 // that no shared-memory plan can hold.
