@@ -28,6 +28,7 @@ struct nccl_api {
   decltype(&ncclCommInitAll) CommInitAll     = nullptr;
   decltype(&ncclCommDestroy) CommDestroy     = nullptr;
   decltype(&ncclAllGather) AllGather         = nullptr;
+  decltype(&ncclAllReduce) AllReduce         = nullptr;
   decltype(&ncclGroupStart) GroupStart       = nullptr;
   decltype(&ncclGroupEnd) GroupEnd           = nullptr;
   decltype(&ncclGetErrorString) ErrorString  = nullptr;
@@ -58,6 +59,7 @@ const nccl_api& nccl()
     api.CommInitAll  = reinterpret_cast<decltype(api.CommInitAll)>(sym("ncclCommInitAll"));
     api.CommDestroy  = reinterpret_cast<decltype(api.CommDestroy)>(sym("ncclCommDestroy"));
     api.AllGather    = reinterpret_cast<decltype(api.AllGather)>(sym("ncclAllGather"));
+    api.AllReduce    = reinterpret_cast<decltype(api.AllReduce)>(sym("ncclAllReduce"));
     api.GroupStart   = reinterpret_cast<decltype(api.GroupStart)>(sym("ncclGroupStart"));
     api.GroupEnd     = reinterpret_cast<decltype(api.GroupEnd)>(sym("ncclGroupEnd"));
     api.ErrorString  = reinterpret_cast<decltype(api.ErrorString)>(sym("ncclGetErrorString"));
@@ -216,9 +218,21 @@ void rank_comm::gather_probes(cudaStream_t stream)
 }
 
 void rank_comm::scan(raft::resources& res, const ivf_pq::search_params& p, const index<int64_t>& shard,
-                     const void* queries, elem_t qtype)
+                     const void* queries, elem_t qtype, bool exchange_bounds)
 {
   uint8_t* block = blocks_.data() + size_t(rank_) * block_bytes_;
+  // One process per GPU: between the nearest-probe pairs and the rest the ranks min-reduce their bounds
+  // on every query's k-th best score (4 bytes per query), so that each prunes like the single-GPU search.
+  struct hook_guard {
+    raft::resources& r;
+    ~hook_guard() { r.scan_phase_hook = nullptr; }
+  } guard{res};
+  if (exchange_bounds && n_ranks_ > 1) {
+    ncclComm* comm = comm_;
+    res.scan_phase_hook = [comm](cudaStream_t stream, uint32_t* kth, uint32_t n) {
+      NCCL_TRY(nccl().AllReduce(kth, kth, n, ncclUint32, ncclMin, comm, stream));
+    };
+  }
   ivf_pq::search_any(res, p, shard, queries, qtype, nq_, k_, reinterpret_cast<int64_t*>(block),
                      reinterpret_cast<float*>(block + ids_bytes_), probes_.data());
 }
@@ -267,7 +281,7 @@ void search_rank(raft::resources& res, rank_comm& comm, const ivf_pq::search_par
   comm.mark(res, 1);
   comm.gather_probes(res.stream);
   comm.mark(res, 2);
-  comm.scan(res, params, shard, queries, qtype);
+  comm.scan(res, params, shard, queries, qtype, /*exchange_bounds=*/true);
   comm.mark(res, 3);
   comm.gather_results(res.stream);
   comm.mark(res, 4);

@@ -76,8 +76,10 @@ class rank_comm {
   void select(raft::resources& res, const ivf_pq::search_params& p, const index<int64_t>& shard,
               const void* queries, elem_t qtype, uint32_t nq, uint32_t k);
   void gather_probes(cudaStream_t stream);
+  // `exchange_bounds` (one process per GPU only: it issues a collective of its own): the ranks share
+  // their per-query bounds between the nearest-probe pairs and the rest
   void scan(raft::resources& res, const ivf_pq::search_params& p, const index<int64_t>& shard,
-            const void* queries, elem_t qtype);
+            const void* queries, elem_t qtype, bool exchange_bounds = false);
   void gather_results(cudaStream_t stream);
   void merge(raft::resources& res, bool select_min, int64_t* neighbors, float* distances);
   // by-rows shards: plain search of the whole batch into this rank's block, ids += id_offset

@@ -270,6 +270,8 @@ __global__ void __launch_bounds__(1024) exclusive_scan_kernel(uint32_t* __restri
   }
 }
 
+__global__ void copy_u32_kernel(uint32_t* __restrict__ dst, const uint32_t* __restrict__ src) { *dst = *src; }
+
 // Counters for the benchmark: sum over pairs, and over distinct probed lists, of ceil(size / 32).
 __global__ void scan_stats_kernel(const uint32_t* __restrict__ list_count,
                                   const uint32_t* __restrict__ list_sizes, uint32_t n_lists,
@@ -861,7 +863,8 @@ void search_any(raft::resources& res, const search_params& params, const index<i
                             k, size_t(idx.dim()));
     if (stats) { res.stats_mark(ev, 2); }
     // 3. sample offsets + work list of the scan
-    if (!stats && n_pairs <= 4096) {
+    const bool sorted_pairs = stats || n_pairs > 4096;
+    if (!sorted_pairs) {
       // small batch: one launch, pairs in arrival order (a sort by list has nothing to gain here)
       CUDA_TRY(cudaMemsetAsync(d_counter, 0, 8, stream));
       small_batch_pairs_kernel<<<ceildiv<uint32_t>(nq * 32, 128), 128, 0, stream>>>(
@@ -936,6 +939,22 @@ void search_any(raft::resources& res, const search_params& params, const index<i
         sp.lut_global = ws + o_glut;
         launch_scan_glut(sp, int(idx.pq_bits()), lut_kind, out_half, is_ip, store_all ? 0 : 4,
                          int(std::min<uint32_t>(glut_grid, n_pairs)), plan.total_bytes, stream);
+      } else if (res.scan_phase_hook && n_pairs > 4096 && !store_all && n_lists >= 1) {
+        // (every condition here is the same on every rank: the hook is a collective)
+        // List-sharded search: every rank knows a query's k-th best only over the lists it owns, which
+        // prunes less than the single-GPU search does.  So: the segment of nearest-probe pairs first
+        // (after the scatter the cursor of its last bucket is the segment's end), the ranks exchange
+        // the bounds they have (a min-reduction: any rank's k-th best bounds the global one from
+        // above), then the other pairs with the shared bound.
+        sp.n_work = d_count + (n_lists - 1);
+        const int grid1 = int(std::min<uint32_t>(uint32_t(res.sm_count), ceildiv<uint32_t>(nq, plan.n_groups)));
+        launch_scan(sp, int(idx.pq_bits()), lut_kind, out_half, is_ip, kpl, grid1, plan.total_bytes, stream);
+        res.scan_phase_hook(stream, d_kth, nq);
+        copy_u32_kernel<<<1, 1, 0, stream>>>(d_counter, d_count + (n_lists - 1));  // claims restart at segment two
+        sp.n_work      = d_counter + 1;
+        const int grid = int(std::min<uint32_t>(uint32_t(res.sm_count), ceildiv<uint32_t>(n_pairs, plan.n_groups)));
+        launch_scan(sp, int(idx.pq_bits()), lut_kind, out_half, is_ip, kpl, grid, plan.total_bytes, stream);
+        res.launches += 2;
       } else {
         const int grid = int(std::min<uint32_t>(uint32_t(res.sm_count), ceildiv<uint32_t>(n_pairs, plan.n_groups)));
         launch_scan(sp, int(idx.pq_bits()), lut_kind, out_half, is_ip, kpl, grid, plan.total_bytes, stream);

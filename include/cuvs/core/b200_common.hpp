@@ -7,6 +7,7 @@
 #include <cstdarg>
 #include <cstdint>
 #include <cstdio>
+#include <functional>
 #include <map>
 #include <stdexcept>
 #include <string>
@@ -155,6 +156,10 @@ struct resources {
   // two; raised when a finished batch had to redo more than 1/256 of its queries exactly, lowered when
   // all but 1/1024 of a batch would have passed the guard with one product less); the counters of the
   // last batch arrive in pinned[8..11] once tc_redo_event has completed.
+  // List-sharded multi-GPU search: when set, the fine search scans the pairs of every query's nearest
+  // probe first, calls this with (stream, per-query bounds on the k-th best ordered score, n_queries)
+  // -- the caller enqueues a min-reduction of the bounds over the ranks -- and then scans the rest.
+  std::function<void(cudaStream_t, uint32_t*, uint32_t)> scan_phase_hook;
   int tc_products            = 2;
   int tc_products_floor      = 1;  // raised when a level produced too many exact redos
   cudaEvent_t tc_redo_event  = nullptr;
