@@ -20,7 +20,10 @@
 // Two ways to drive it:
 //   one process per GPU ... `rank_comm` + `search_rank`: ONE call per batch enqueues the whole step
 //                           (probe slice -> all-gather -> scan -> all-gather -> merge) on the handle's
-//                           stream, on buffers sized once per communicator;
+//                           stream, on buffers sized once per communicator; the scan is two launches
+//                           (nearest-probe pairs, then the rest) with a min-reduction of the per-query
+//                           bounds on the k-th best score between them, so that every rank prunes with
+//                           what all ranks have found;
 //   one process, all GPUs . `snmg_resources` + `mg_index` + `search`: the reference's shape (host
 //                           tensors in and out), one host thread issuing the same step on every device
 //                           with the collectives grouped.
