@@ -407,11 +407,11 @@ def hbm_peak():
 
 
 # DRAM bytes (read + write) per DISTINCT 32-row group scanned in a launch, from the ncu capture of the
-# scan kernel on a 4 M-row case of this workload (354.9 MB over 135,125 distinct groups of
+# scan kernel on a 4 M-row case of this workload (312.3 MB over 134,482 distinct groups of
 # 3 x 512 B: the work list makes two passes over the lists, so a list can be fetched twice).  Traffic
 # grows with the distinct groups of a launch, so the full-size figure is this constant times the
 # launch's distinct groups.
-DRAM_BYTES_PER_UNIQUE_GROUP = 2626.0
+DRAM_BYTES_PER_UNIQUE_GROUP = 2322.0
 
 
 def workload_from_args(args):
