@@ -680,7 +680,7 @@ scan_plan plan_scan(const raft::resources& res, const index<int64_t>& idx, int l
 // search
 // ------------------------------------------------------------------------------------------------
 void check_search_params(const raft::resources& res, const search_params& params, const index<int64_t>& idx,
-                         uint32_t k)
+                         uint32_t k, bool shard)
 {
   // ivf_pq_search.cuh:901-917
   CUVS_EXPECTS(params.internal_distance_dtype == CUDA_R_16F ||
@@ -690,7 +690,9 @@ void check_search_params(const raft::resources& res, const search_params& params
                  params.lut_dtype == CUDA_R_8U,
                "lut_dtype must be CUDA_R_16F, CUDA_R_32F or CUDA_R_8U");
   CUVS_EXPECTS(k > 0, "parameter `k` in top-k must be positive.");
-  CUVS_EXPECTS(int64_t(k) <= idx.size(),
+  // (a shard of a list-sharded index may hold fewer than k rows: its result is padded, and an error on
+  // one rank alone would leave the other ranks waiting in a collective)
+  CUVS_EXPECTS(shard || int64_t(k) <= idx.size(),
                "parameter `k` (%u) in top-k must not be larger that the total size of the index (%zu)",
                k, size_t(idx.size()));
   CUVS_EXPECTS(params.n_probes > 0,
@@ -727,7 +729,7 @@ void search_any(raft::resources& res, const search_params& params, const index<i
 {
   nvtx_range fun_scope("ivf_pq::search(n_queries = %u, n_probes = %u, k = %u, dim = %zu)", n_queries,
                        params.n_probes, k, size_t(idx.dim()));
-  check_search_params(res, params, idx, k);
+  check_search_params(res, params, idx, k, /*shard=*/given_probes != nullptr);
   const bool coarse_i8 = params.coarse_search_dtype == CUDA_R_8I;
   const bool coarse_h  = params.coarse_search_dtype == CUDA_R_16F;
   const bool out_half = params.internal_distance_dtype == CUDA_R_16F;

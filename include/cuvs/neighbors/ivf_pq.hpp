@@ -349,8 +349,9 @@ struct bitset_filter : public base_filter {
 namespace cuvs::neighbors::ivf_pq {
 // Every check the search makes on its parameters before it touches the GPU (argument ranges, dtype
 // pairing, a shared-memory plan for the look-up table): throws what the search would throw.
+// `shard`: the index is one rank's part of a list-sharded index, which may hold fewer than k rows.
 void check_search_params(const raft::resources& res, const search_params& params, const index<int64_t>& idx,
-                         uint32_t k);
+                         uint32_t k, bool shard = false);
 // Probe selection alone, asynchronous on the handle's stream: probes [n_queries, n_probes] u32,
 // ascending by (score, list id).
 void select_probes_any(raft::resources& res, const index<int64_t>& idx, const void* queries,

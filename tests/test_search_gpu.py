@@ -285,6 +285,34 @@ def test_list_sharded_search_merges_to_the_unsharded_result(ivf, oracle_mod, sma
     assert (i2 == i_full).all()
 
 
+def test_a_shard_with_fewer_rows_than_k_is_searched_and_padded(ivf, small_l2):
+    """One rank of a many-way list sharding holds fewer rows than k.  The sharded entry must not refuse
+    it (an error on one rank alone would leave the others waiting in a collective): the rank returns what
+    it has and pads; the merge over all ranks equals the unsharded result."""
+    from cuvs_b200 import mg
+    q = torch.from_numpy(small_l2["q"][:50]).cuda()
+    full = ivf.load(small_l2["path"])
+    n_ranks, k = 16, 300
+    sp = ivf.SearchParams(n_probes=int(full.n_lists))
+    d_full, i_full = ivf.search(sp, full, q, k)
+    probes = mg.select_probes(full, q, int(full.n_lists))
+    parts = []
+    small = 0
+    for r in range(n_ranks):
+        shard = mg.load_shard(small_l2["path"], r, n_ranks)
+        small += int(shard.list_sizes.to(torch.int64).sum().item()) < k
+        parts.append(mg.search_with_probes(sp, shard, q, probes, k))
+    assert small > 0, "the case needs at least one shard smaller than k"
+    d, i = mg.merge_parts(torch.stack([p[0] for p in parts]), torch.stack([p[1] for p in parts]), True)
+    assert (d.view(torch.int32) == d_full.view(torch.int32)).all()
+    # ids equal except inside runs of equal distances (the merge orders those by id)
+    tie = torch.zeros_like(i, dtype=torch.bool)
+    eq = d[:, 1:] == d[:, :-1]
+    tie[:, 1:] |= eq
+    tie[:, :-1] |= eq
+    assert ((i == i_full) | tie).all()
+
+
 # ------------------------------------------------------------------------------------------------
 # probe selection stage alone: exact SIMT path, tensor-core path and the oracle must agree
 # ------------------------------------------------------------------------------------------------
