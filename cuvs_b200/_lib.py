@@ -213,6 +213,7 @@ SIGNATURES = {
     "cuvsMultiGpuIvfPqSearchRank": [C.c_size_t, C.c_void_p, _P(SearchParamsStruct), _P(IndexStruct),
                                     _P(DLManagedTensor), _P(DLManagedTensor), _P(DLManagedTensor)],
     "cuvsMultiGpuRankCommStats": [C.c_void_p, _P(C.c_double), _P(C.c_uint64), C.c_bool],
+    "cuvsMultiGpuRankCommSetMergeMode": [C.c_void_p, C.c_int],
     "cuvsMultiGpuIvfPqListOwners": [_P(C.c_uint32), C.c_uint32, C.c_int, _P(C.c_int32)],
 }
 

@@ -405,6 +405,15 @@ extern "C" cuvsError_t cuvsMultiGpuRankCommStats(cuvsMultiGpuRankComm_t comm, do
   });
 }
 
+extern "C" cuvsError_t cuvsMultiGpuRankCommSetMergeMode(cuvsMultiGpuRankComm_t comm, int mode)
+{
+  return translate_exceptions([=] {
+    CUVS_EXPECTS(comm != nullptr, "null argument");
+    CUVS_EXPECTS(mode >= 0 && mode <= 2, "mode must be 0, 1 or 2");
+    reinterpret_cast<mg::rank_comm*>(comm)->set_merge_mode(mode);
+  });
+}
+
 extern "C" cuvsError_t cuvsMultiGpuIvfPqListOwners(const uint32_t* list_sizes, uint32_t n_lists, int n_ranks, int32_t* owners)
 {
   return translate_exceptions([=] {

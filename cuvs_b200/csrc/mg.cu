@@ -29,6 +29,8 @@ struct nccl_api {
   decltype(&ncclCommDestroy) CommDestroy     = nullptr;
   decltype(&ncclAllGather) AllGather         = nullptr;
   decltype(&ncclAllReduce) AllReduce         = nullptr;
+  decltype(&ncclSend) Send                   = nullptr;
+  decltype(&ncclRecv) Recv                   = nullptr;
   decltype(&ncclGroupStart) GroupStart       = nullptr;
   decltype(&ncclGroupEnd) GroupEnd           = nullptr;
   decltype(&ncclGetErrorString) ErrorString  = nullptr;
@@ -60,6 +62,8 @@ const nccl_api& nccl()
     api.CommDestroy  = reinterpret_cast<decltype(api.CommDestroy)>(sym("ncclCommDestroy"));
     api.AllGather    = reinterpret_cast<decltype(api.AllGather)>(sym("ncclAllGather"));
     api.AllReduce    = reinterpret_cast<decltype(api.AllReduce)>(sym("ncclAllReduce"));
+    api.Send         = reinterpret_cast<decltype(api.Send)>(sym("ncclSend"));
+    api.Recv         = reinterpret_cast<decltype(api.Recv)>(sym("ncclRecv"));
     api.GroupStart   = reinterpret_cast<decltype(api.GroupStart)>(sym("ncclGroupStart"));
     api.GroupEnd     = reinterpret_cast<decltype(api.GroupEnd)>(sym("ncclGroupEnd"));
     api.ErrorString  = reinterpret_cast<decltype(api.ErrorString)>(sym("ncclGetErrorString"));
@@ -267,6 +271,63 @@ void rank_comm::merge(raft::resources& res, bool select_min, int64_t* neighbors,
                                   block_bytes_ / 4, block_bytes_ / 8);
 }
 
+void rank_comm::exchange_slices(cudaStream_t stream)
+{
+  // rows [j * slice_, ...) of this rank's block go to rank j; this rank's rows arrive from every rank
+  const size_t part_ids   = round_up<size_t>(size_t(slice_) * k_ * 8, 16);
+  const size_t part_bytes = part_ids + round_up<size_t>(size_t(slice_) * k_ * 4, 16);
+  const size_t need       = size_t(n_ranks_) * part_bytes;
+  if (parts_.size() < need) { parts_.resize(need + need / 4); }
+  const uint8_t* block = blocks_.data() + size_t(rank_) * block_bytes_;
+  const auto* ids      = reinterpret_cast<const int64_t*>(block);
+  const auto* ds       = reinterpret_cast<const float*>(block + ids_bytes_);
+  const uint32_t my_lo = std::min<uint32_t>(nq_, uint32_t(rank_) * slice_);
+  const uint32_t my_n  = std::min<uint32_t>(nq_, my_lo + slice_) - my_lo;
+  NCCL_TRY(nccl().GroupStart());
+  for (int j = 0; j < n_ranks_; j++) {
+    const uint32_t lo = std::min<uint32_t>(nq_, uint32_t(j) * slice_);
+    const uint32_t n  = std::min<uint32_t>(nq_, lo + slice_) - lo;
+    if (n > 0) {
+      NCCL_TRY(nccl().Send(ids + size_t(lo) * k_, size_t(n) * k_, ncclInt64, j, comm_, stream));
+      NCCL_TRY(nccl().Send(ds + size_t(lo) * k_, size_t(n) * k_, ncclFloat, j, comm_, stream));
+    }
+    if (my_n > 0) {
+      uint8_t* part = parts_.data() + size_t(j) * part_bytes;
+      NCCL_TRY(nccl().Recv(part, size_t(my_n) * k_, ncclInt64, j, comm_, stream));
+      NCCL_TRY(nccl().Recv(part + part_ids, size_t(my_n) * k_, ncclFloat, j, comm_, stream));
+    }
+  }
+  NCCL_TRY(nccl().GroupEnd());
+}
+
+void rank_comm::merge_slice_and_gather(raft::resources& res, bool select_min, int64_t* neighbors, float* distances)
+{
+  const size_t part_ids   = round_up<size_t>(size_t(slice_) * k_ * 8, 16);
+  const size_t part_bytes = part_ids + round_up<size_t>(size_t(slice_) * k_ * 4, 16);
+  const uint32_t my_lo    = std::min<uint32_t>(nq_, uint32_t(rank_) * slice_);
+  const uint32_t my_n     = std::min<uint32_t>(nq_, my_lo + slice_) - my_lo;
+  // the merged slices are gathered in place where the batch divides evenly, else through padded buffers
+  const bool even   = size_t(slice_) * n_ranks_ == nq_;
+  const size_t rows = size_t(slice_) * n_ranks_;
+  int64_t* fin_i    = even ? neighbors : out_neighbors(rows * k_);
+  float* fin_d      = even ? distances : out_distances(rows * k_);
+  if (my_n > 0) {
+    ivf_pq::detail::knn_merge_parts(res, reinterpret_cast<const float*>(parts_.data() + part_ids),
+                                    reinterpret_cast<const int64_t*>(parts_.data()),
+                                    fin_d + size_t(rank_) * slice_ * k_, fin_i + size_t(rank_) * slice_ * k_,
+                                    uint32_t(n_ranks_), my_n, k_, select_min, part_bytes / 4, part_bytes / 8);
+  }
+  const size_t count = size_t(slice_) * k_;
+  NCCL_TRY(nccl().GroupStart());
+  NCCL_TRY(nccl().AllGather(fin_i + size_t(rank_) * count, fin_i, count, ncclInt64, comm_, res.stream));
+  NCCL_TRY(nccl().AllGather(fin_d + size_t(rank_) * count, fin_d, count, ncclFloat, comm_, res.stream));
+  NCCL_TRY(nccl().GroupEnd());
+  if (!even) {
+    CUDA_TRY(cudaMemcpyAsync(neighbors, fin_i, size_t(nq_) * k_ * 8, cudaMemcpyDeviceToDevice, res.stream));
+    CUDA_TRY(cudaMemcpyAsync(distances, fin_d, size_t(nq_) * k_ * 4, cudaMemcpyDeviceToDevice, res.stream));
+  }
+}
+
 void search_rank(raft::resources& res, rank_comm& comm, const ivf_pq::search_params& params,
                  const index<int64_t>& shard, const void* queries, elem_t qtype, uint32_t nq, uint32_t k,
                  int64_t* neighbors, float* distances)
@@ -283,9 +344,15 @@ void search_rank(raft::resources& res, rank_comm& comm, const ivf_pq::search_par
   comm.mark(res, 2);
   comm.scan(res, params, shard, queries, qtype, /*exchange_bounds=*/true);
   comm.mark(res, 3);
-  comm.gather_results(res.stream);
-  comm.mark(res, 4);
-  comm.merge(res, is_min_close(shard.metric()), neighbors, distances);
+  if (comm.merge_by_slice()) {
+    comm.exchange_slices(res.stream);
+    comm.mark(res, 4);
+    comm.merge_slice_and_gather(res, is_min_close(shard.metric()), neighbors, distances);
+  } else {
+    comm.gather_results(res.stream);
+    comm.mark(res, 4);
+    comm.merge(res, is_min_close(shard.metric()), neighbors, distances);
+  }
   comm.mark(res, 5);
 }
 

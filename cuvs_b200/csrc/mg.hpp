@@ -85,6 +85,14 @@ class rank_comm {
             const void* queries, elem_t qtype, bool exchange_bounds = false);
   void gather_results(cudaStream_t stream);
   void merge(raft::resources& res, bool select_min, int64_t* neighbors, float* distances);
+  // The same two phases with the merge shared out by query slice: every rank receives only its own
+  // slice of every rank's block (send/receive pairs, 1/n_ranks of the all-gather's bytes), merges that
+  // slice, and the merged slices are all-gathered.  Chosen by search_rank for three ranks or more.
+  void exchange_slices(cudaStream_t stream);
+  void merge_slice_and_gather(raft::resources& res, bool select_min, int64_t* neighbors, float* distances);
+  // 0 = by the number of ranks, 1 = always by slice, 2 = always the whole-block all-gather
+  void set_merge_mode(int mode) { merge_mode_ = mode; }
+  bool merge_by_slice() const { return merge_mode_ == 1 || (merge_mode_ == 0 && n_ranks_ >= 3); }
   // by-rows shards: plain search of the whole batch into this rank's block, ids += id_offset
   void search_rows(raft::resources& res, const ivf_pq::search_params& p, const index<int64_t>& part,
                    const void* queries, elem_t qtype, uint32_t nq, uint32_t k, int64_t id_offset);
@@ -105,11 +113,13 @@ class rank_comm {
   ncclComm* comm_ = nullptr;
   bool owns_      = false;
   int rank_ = 0, n_ranks_ = 1;
+  int merge_mode_ = 0;
   // state of the batch in flight
   uint32_t nq_ = 0, k_ = 0, n_probes_ = 0, slice_ = 0;
   size_t block_bytes_ = 0, ids_bytes_ = 0;
   ivf_pq::dev_array<uint32_t> probes_;  // [n_ranks * slice, n_probes]
   ivf_pq::dev_array<uint8_t> blocks_;   // [n_ranks][ids i64 [nq, k] | distances f32 [nq, k]]
+  ivf_pq::dev_array<uint8_t> parts_;    // [n_ranks][ids i64 [slice, k] | distances f32 [slice, k]] of this rank's slice
   ivf_pq::dev_array<uint8_t> queries_;
   ivf_pq::dev_array<float> out_d_;
   ivf_pq::dev_array<int64_t> out_i_;

@@ -61,6 +61,11 @@ class RankComm:
         else:
             L.check(self._lib.cuvsMultiGpuRankCommAdopt(None, 0, 1, C.byref(self.handle)))
 
+    def set_merge_mode(self, mode: int):
+        """0 = by the number of ranks (three or more: merge shared out by query slice), 1 = always by
+        slice, 2 = always one all-gather of whole blocks.  Same result; same mode on every rank."""
+        L.check(self._lib.cuvsMultiGpuRankCommSetMergeMode(self.handle, C.c_int(mode)))
+
     def stats(self, reset: bool = True):
         """Per-call stage times in ms of the searches made while the handle's stage timing was on:
         dict(select, gather_probes, scan, gather_results, merge, batches)."""

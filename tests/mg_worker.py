@@ -37,6 +37,22 @@ def main():
                 tied |= d0 == d0[:, -1:]
                 assert ((i0 == i1) | tied).all(), (rank, k, p, suffix)
                 assert tied.float().mean().item() < 0.2, (rank, k, p, suffix)
+        # the merge shared out by query slice (what three or more ranks use) gives the same result,
+        # also when the batch does not divide evenly and for k beyond the register merge
+        comm = mg.default_comm()
+        comm.set_merge_mode(1)
+        for k, p, nq in ((10, 8, q.shape[0]), (40, 12, q.shape[0] - 1), (200, 16, 7)):
+            sp = ivf_pq.SearchParams(n_probes=p)
+            qs = q[:nq].contiguous()
+            d0, i0 = ivf_pq.search(sp, full, qs, k)
+            d1, i1 = mg.search(sp, shard, qs, k)
+            assert (d0.view(torch.int32) == d1.view(torch.int32)).all(), ("slice merge", rank, k, suffix)
+            tied = torch.zeros_like(i0, dtype=torch.bool)
+            tied[:, 1:] |= d0[:, 1:] == d0[:, :-1]
+            tied[:, :-1] |= d0[:, :-1] == d0[:, 1:]
+            tied |= d0 == d0[:, -1:]
+            assert ((i0 == i1) | tied).all(), ("slice merge ids", rank, k, suffix)
+        comm.set_merge_mode(0)
         # int8 coarse search: the shared probe selection honours coarse_search_dtype
         if suffix == "":
             sp = ivf_pq.SearchParams(n_probes=8, coarse_search_dtype=np.int8)
