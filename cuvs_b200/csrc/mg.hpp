@@ -87,12 +87,13 @@ class rank_comm {
   void merge(raft::resources& res, bool select_min, int64_t* neighbors, float* distances);
   // The same two phases with the merge shared out by query slice: every rank receives only its own
   // slice of every rank's block (send/receive pairs, 1/n_ranks of the all-gather's bytes), merges that
-  // slice, and the merged slices are all-gathered.  Chosen by search_rank for three ranks or more.
+  // slice, and the merged slices are all-gathered.  Off unless asked for: on four GPUs it measured no
+  // faster than the whole-block all-gather (the blocks are a few MB; two collectives cost what one saves).
   void exchange_slices(cudaStream_t stream);
   void merge_slice_and_gather(raft::resources& res, bool select_min, int64_t* neighbors, float* distances);
-  // 0 = by the number of ranks, 1 = always by slice, 2 = always the whole-block all-gather
+  // 0 / 2 = one all-gather of whole blocks, every rank merges everything (the default); 1 = by slice
   void set_merge_mode(int mode) { merge_mode_ = mode; }
-  bool merge_by_slice() const { return merge_mode_ == 1 || (merge_mode_ == 0 && n_ranks_ >= 3); }
+  bool merge_by_slice() const { return merge_mode_ == 1; }
   // by-rows shards: plain search of the whole batch into this rank's block, ids += id_offset
   void search_rows(raft::resources& res, const ivf_pq::search_params& p, const index<int64_t>& part,
                    const void* queries, elem_t qtype, uint32_t nq, uint32_t k, int64_t id_offset);

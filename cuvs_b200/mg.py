@@ -62,8 +62,8 @@ class RankComm:
             L.check(self._lib.cuvsMultiGpuRankCommAdopt(None, 0, 1, C.byref(self.handle)))
 
     def set_merge_mode(self, mode: int):
-        """0 = by the number of ranks (three or more: merge shared out by query slice), 1 = always by
-        slice, 2 = always one all-gather of whole blocks.  Same result; same mode on every rank."""
+        """0 or 2 = one all-gather of whole blocks, every rank merges everything (the default); 1 = the
+        merge shared out by query slice.  Same result; same mode on every rank."""
         L.check(self._lib.cuvsMultiGpuRankCommSetMergeMode(self.handle, C.c_int(mode)))
 
     def stats(self, reset: bool = True):

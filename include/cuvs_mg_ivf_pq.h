@@ -161,11 +161,10 @@ CUVS_EXPORT cuvsError_t cuvsMultiGpuRankCommStats(cuvsMultiGpuRankComm_t comm,
                                                   double* stage_ms,
                                                   uint64_t* batches,
                                                   bool reset);
-/* How cuvsMultiGpuIvfPqSearchRank exchanges and merges the per-rank results: 0 = by the number of ranks
- * (three or more: every rank receives and merges only its own slice of the queries, the merged slices
- * are all-gathered; two: one all-gather of the whole blocks, every rank merges everything), 1 = always by
- * slice, 2 = always whole blocks.  The result is the same either way; every rank of a communicator
- * must use the same mode. */
+/* How cuvsMultiGpuIvfPqSearchRank exchanges and merges the per-rank results: 0 or 2 = one all-gather of
+ * the whole blocks, every rank merges everything (the default); 1 = by slice: every rank receives and
+ * merges only its own slice of the queries (send/receive pairs), the merged slices are all-gathered.
+ * The result is the same either way; every rank of a communicator must use the same mode. */
 CUVS_EXPORT cuvsError_t cuvsMultiGpuRankCommSetMergeMode(cuvsMultiGpuRankComm_t comm, int mode);
 /* The rule that deals lists to ranks: owners[l] for list sizes given on the host. */
 CUVS_EXPORT cuvsError_t cuvsMultiGpuIvfPqListOwners(const uint32_t* list_sizes,

@@ -37,7 +37,7 @@ def main():
                 tied |= d0 == d0[:, -1:]
                 assert ((i0 == i1) | tied).all(), (rank, k, p, suffix)
                 assert tied.float().mean().item() < 0.2, (rank, k, p, suffix)
-        # the merge shared out by query slice (what three or more ranks use) gives the same result,
+        # the merge shared out by query slice (optional mode) gives the same result,
         # also when the batch does not divide evenly and for k beyond the register merge
         comm = mg.default_comm()
         comm.set_merge_mode(1)
