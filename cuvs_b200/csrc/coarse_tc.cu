@@ -1434,7 +1434,7 @@ void select_clusters_tc(raft::resources& res, const float* centers, const float*
   // make the GEMM cheaper and the guard's error bound wider; the probes stay exact either way.
   res.adopt_tc_verdict();  // what the last batch of this handle reported, if it has arrived
   int products = exact_operands ? 1 : tc_products_ref();
-  if (products == 0) { products = res.tc_products; }
+  if (products == 0) { products = res.tc_levels[n_probes].products; }
   const float eps_base = float(dim_ext + 8) * 2.4e-7f + 3.1e-5f;
   const float eps_split[4] = {0.0f, 9.8e-4f, 4.9e-4f, 0.0f};
   const float eps_rel = eps_base + (exact_operands ? 0.0f : eps_split[products]);
@@ -1515,7 +1515,8 @@ void select_clusters_tc(raft::resources& res, const float* centers, const float*
     if (!res.tc_redo_event) { CUDA_TRY(cudaEventCreateWithFlags(&res.tc_redo_event, cudaEventDisableTiming)); }
     CUDA_TRY(cudaMemcpyAsync(res.pinned + 8, words, 16, cudaMemcpyDeviceToHost, stream));
     CUDA_TRY(cudaEventRecord(res.tc_redo_event, stream));
-    res.tc_redo_queries = n_queries;
+    res.tc_redo_queries  = n_queries;
+    res.tc_redo_n_probes = n_probes;
     res.tc_redo_adapts  = !exact_operands && tc_products_ref() == 0;
     res.tc_redo_pending = true;
   }

@@ -79,14 +79,17 @@ void resources::adopt_tc_verdict()
   if (pinned[8] != 0u) {
     // the coarse GEMM of that batch gave up on a bounded wait; its probes were all recomputed exactly
     tc_timeouts++;
-  } else if (tc_redo_adapts && uint64_t(pinned[9]) * 256 > tc_redo_queries && tc_products < 3) {
-    // more than 1/256 of the batch failed the exactness guard: one more product of the TF32 split,
-    // and never fewer again on this handle
-    tc_products++;
-    tc_products_floor = tc_products;
-  } else if (tc_redo_adapts && tc_products > tc_products_floor && uint64_t(pinned[11]) * 1024 <= tc_redo_queries) {
-    // (almost) every query of the batch would have passed the guard with one product less
-    tc_products--;
+  } else if (tc_redo_adapts) {
+    tc_level& lv = tc_levels[tc_redo_n_probes];
+    if (uint64_t(pinned[9]) * 256 > tc_redo_queries && lv.products < 3) {
+      // more than 1/256 of the batch failed the exactness guard: one more product of the TF32 split,
+      // and never fewer again on this handle for this n_probes
+      lv.products++;
+      lv.floor = lv.products;
+    } else if (lv.products > lv.floor && uint64_t(pinned[11]) * 1024 <= tc_redo_queries) {
+      // (almost) every query of the batch would have passed the guard with one product less
+      lv.products--;
+    }
   }
 }
 

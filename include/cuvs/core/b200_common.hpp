@@ -152,7 +152,7 @@ struct resources {
   void stats_mark(stage_events& ev, int i);
   void stats_resolve();
 
-  // Tensor-core coarse stage: products of the TF32 split per K step used by this handle (starts at
+  // Tensor-core coarse stage: products of the TF32 split per K step used by this handle (start at
   // two; raised when a finished batch had to redo more than 1/256 of its queries exactly, lowered when
   // all but 1/1024 of a batch would have passed the guard with one product less); the counters of the
   // last batch arrive in pinned[8..11] once tc_redo_event has completed.
@@ -160,8 +160,14 @@ struct resources {
   // probe first, calls this with (stream, per-query bounds on the k-th best ordered score, n_queries)
   // -- the caller enqueues a min-reduction of the bounds over the ranks -- and then scans the rest.
   std::function<void(cudaStream_t, uint32_t*, uint32_t)> scan_phase_hook;
-  int tc_products            = 2;
-  int tc_products_floor      = 1;  // raised when a level produced too many exact redos
+  // The level is kept per n_probes (the guard's margin depends on it: a handle that once served
+  // n_probes = 200 must not pay for that when it serves n_probes = 20).
+  struct tc_level {
+    int products = 2;
+    int floor    = 1;  // raised when a level produced too many exact redos
+  };
+  std::map<uint32_t, tc_level> tc_levels;
+  uint32_t tc_redo_n_probes  = 0;  // n_probes of the batch whose counters are in flight
   cudaEvent_t tc_redo_event  = nullptr;
   bool tc_redo_pending       = false;
   uint32_t tc_redo_queries   = 0;
