@@ -798,7 +798,10 @@ __global__ void __launch_bounds__(1024, 1) scan_kernel(const scan_params p)
       }
     }
   };
-  const bool prefetch_base = p.base_double != 0 && n_gwarps > 1 && !kStoreAll;
+  // (compiled in only for L2 with k <= 32, where it was measured to pay: the k = 100 and inner-product
+  // kernels ran 2-3% slower with the extra code)
+  constexpr bool kCanPrefetch = !IsIP && KPL == 1;
+  const bool prefetch_base    = kCanPrefetch && p.base_double != 0 && n_gwarps > 1;
   uint32_t cur   = 0;      // buffer that holds (or receives) the current pair's base difference
   bool have_base = false;  // the current pair's base difference and bound were prepared during the last merge
   for (uint32_t it = 0;; it++) {
@@ -1102,6 +1105,7 @@ __global__ void __launch_bounds__(1024, 1) scan_kernel(const scan_params p)
     // buffer and the query's bound (every warp has finished scanning, so the bound's slot is free).  The
     // next work item was claimed after the barrier at the top of this iteration.
     have_base = false;
+    if constexpr (kCanPrefetch) {
     if (prefetch_base) {
       const uint32_t w_next = lds_b32_volatile(s_item_a() + 4u * ((it + 1u) & 1u));
       if (w_next < n_work) {
@@ -1113,6 +1117,7 @@ __global__ void __launch_bounds__(1024, 1) scan_kernel(const scan_params p)
           write_base(s_base_a(cur), nd.y, nd.z, uint32_t(gt) - 32u, uint32_t(gthreads) - 32u);
         }
       }
+    }
     }
     if (gw == 0) {
       const uint32_t others = uint32_t(n_gwarps - 1) * k;
